@@ -1,0 +1,145 @@
+/*
+ * pimb200.h — C ABI of libpimb200.so: the B200 (sm_100a) device back end for the
+ * fp16 recurrent / decode hot path of PimAiCompiler's stream executor.
+ *
+ * Every entry point takes plain device pointers, sizes and an opaque stream
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream) and returns
+ * an int status (PIMB200_OK == 0).  Nothing here owns or frees caller memory;
+ * outputs may alias caller buffers at any 2-byte aligned offset (fast paths
+ * engage when pointers are 16-byte aligned and the inner extent is a multiple
+ * of 8 halves, other cases take a slower kernel — never a silent skip).
+ *
+ * All "half" pointers are IEEE fp16 device memory.  Arithmetic is fp16 storage,
+ * fp32 accumulate, one rounding to fp16 at the op's output.
+ *
+ * Each declaration cites the interface of the reference it replaces
+ * (paths relative to the PimAiCompiler tree).
+ */
+#ifndef PIMB200_H_
+#define PIMB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+enum {
+    PIMB200_OK = 0,
+    PIMB200_ERR_BAD_ARG = 1,       /* null pointer, non-positive size, bad enum            */
+    PIMB200_ERR_UNSUPPORTED = 2,   /* a shape this build has no kernel for                 */
+    PIMB200_ERR_LAUNCH = 3,        /* CUDA reported an error at launch / sync              */
+    PIMB200_ERR_TIMEOUT = 4,       /* a bounded device-side wait ran out (kernel returned) */
+    PIMB200_ERR_NOT_INIT = 5,      /* pimb200_init() was not called for the current device */
+    PIMB200_ERR_NO_MEMORY = 6      /* device allocation failed                             */
+};
+
+/* activation fused into the GEMV/GEMM epilogue.
+ * Replaces PimActFunc{NONE, ACT_RELU} (runtime/source/executor/op_executor/aten_ops.cpp:614-622). */
+enum { PIMB200_ACT_NONE = 0, PIMB200_ACT_RELU = 1 };
+
+const char* pimb200_status_string(int status);
+
+/* Library/device lifetime.  Replaces PimInitialize(RT_TYPE_HIP, PIM_FP16) / PimDeinitialize()
+ * (runtime/source/nn_runtime.cpp:32, 85) and the rocBLAS warm-up (nn_runtime.cpp:62-73).
+ * init allocates the per-device scratch used by the split-K GEMV; idempotent per device. */
+int pimb200_init(int device);
+int pimb200_shutdown(int device);
+
+/* ---- batch-1 GEMV family ------------------------------------------------ */
+
+/* MV:  y[N] = act(W[N,K] · x[K] + bias[N]);  W row-major, bias may be NULL.
+ * Replaces the W_X_I PimExecuteGemm call of customAtenAddmm/customAtenMatmul
+ * (aten_ops.cpp:662-694, 804-840) and rocblas_gemv_template_Axy / addmv_kernel_Axy
+ * (runtime/include/executor/op_executor/custom_ops.h:141-214, 300-381). */
+int pimb200_gemv_mv(const void* W, const void* x, const void* bias, void* y,
+                    int N, int K, int act, void* stream);
+
+/* VM:  y[N] = act(x[K] · A[K,N] + bias[N]);  A row-major K x N, bias may be NULL.
+ * Replaces the I_X_W PimExecuteGemm call (aten_ops.cpp:626-661, 771-803) and
+ * rocblas_gemv_template_xAy / addmv_kernel_xAy (custom_ops.h:66-139, 216-298).
+ * Uses the per-device split-K scratch allocated by pimb200_init. */
+int pimb200_gemv_vm(const void* x, const void* A, const void* bias, void* y,
+                    int K, int N, int act, void* stream);
+
+/* VV:  y[0] = sum_k a[k]*b[k].  Replaces the VV branch of customAtenMatmul (aten_ops.cpp:841-882). */
+int pimb200_dot_vv(const void* a, const void* b, void* y, int K, void* stream);
+
+/* Single-row bmm:  y[n] = sum_k x[k]*A[k,n] (GNMT attention context, k = source length).
+ * Replaces rocblas_bmm_template_xAy / bmm_kernel_xAy (custom_ops.h:435-466); accumulates in
+ * fp32 (the reference kernel accumulates in fp16). */
+int pimb200_bmm_row(const void* x, const void* A, void* y, int k, int n, void* stream);
+
+/* Batched-stream GEMM:  Y[j, n] = act(sum_k X[j,k]*W[n,k] + bias[n]),  j < J.
+ * X row-major [J, ldx>=K], W row-major [N,K], Y row-major [J, ldy>=N].
+ * y_is_f32 != 0 stores fp32 (used for LSTM gate pre-activations), else fp16.
+ * Replaces the MM-class fall-backs at::addmm / at::matmul / at::linear
+ * (aten_ops.cpp:47-51, 304-307, 362, 695-711) and the MULTISTREAM fan-out
+ * (runtime/source/executor/op_executor/stream_ops_executor.cpp:27-50). */
+int pimb200_gemm_wx(const void* W, const void* X, const void* bias, void* Y,
+                    int N, int K, int J, int ldx, int ldy, int act, int y_is_f32, void* stream);
+
+/* ---- glue ops ------------------------------------------------------------ */
+
+/* C[m,n] = A[m,n] + B[m,n]   (broadcast_b == 0)   or   A[m,n] + B[n] (broadcast_b != 0).
+ * C may alias A (the reference writes in place into A).  Any n (tail handled).
+ * Replaces custom_add / add_kernel / add_kernel_unsym (custom_ops.h:383-433). */
+int pimb200_add_f16(const void* A, const void* B, void* C, int m, int n, int broadcast_b, void* stream);
+
+/* Strided 2-D copy of raw elements:  dst[r*dst_pitch + c] = src[r*src_pitch + c], r < rows, c < row_bytes
+ * (pitches in bytes).  Building block for cat / copy_ into slices of a pre-allocated buffer.
+ * Replaces atenCopy_ (aten_ops.cpp:126-129) on device tensors. */
+int pimb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                    size_t row_bytes, size_t rows, void* stream);
+
+/* Concatenate n_src row-major blocks along the inner dimension:
+ * dst[o, off_i : off_i+inner_bytes[i]] = src[i][o, :], o < outer.  dst row pitch = sum(inner_bytes).
+ * Replaces atenCat (aten_ops.cpp:97) for contiguous inputs. */
+int pimb200_cat(void* dst, const void* const* src, const size_t* inner_bytes, int n_src,
+                size_t outer, void* stream);
+
+/* ---- fused multi-layer LSTM ---------------------------------------------- */
+
+typedef struct pimb200_lstm pimb200_lstm;
+
+/* One-time weight layout step.  params = the flat list at::lstm takes:
+ * (w_ih[4H,I_l], w_hh[4H,H] [, b_ih[4H], b_hh[4H]]) per direction per layer, gate order i,f,g,o,
+ * each a contiguous fp16 device buffer.  Packs gate-interleaved rows (row u*4+g) and the
+ * summed bias in fp32 into memory owned by the handle.
+ * Replaces ModelBuilder::buildLstmParameterVector / reArangeLstmWeights
+ * (runtime/source/builder/model_builder.cpp:158-224, 226-319). */
+int pimb200_lstm_create(const void* const* params, int n_params, int num_layers, int bidirectional,
+                        int input_size, int hidden_size, int has_biases, pimb200_lstm** out);
+int pimb200_lstm_destroy(pimb200_lstm* h);
+
+/* variant selection for A/B profiling: 0 = automatic, 1 = streamed per-step kernels,
+ * 2 = persistent weight-stationary kernel (fails with UNSUPPORTED when the shape does not fit). */
+enum { PIMB200_LSTM_AUTO = 0, PIMB200_LSTM_STREAMED = 1, PIMB200_LSTM_PERSISTENT = 2 };
+int pimb200_lstm_set_variant(pimb200_lstm* h, int variant);
+
+/* Forward pass, padded input:  x [T,B,I] (or [B,T,I] when batch_first), h0/c0 [L*D,B,H]
+ * (NULL = zeros), y [T,B,D*H] (or [B,T,D*H]), hn/cn [L*D,B,H] (may be NULL).
+ * Replaces atenLstm1 -> at::lstm (aten_ops.cpp:328-335) and executeMIOpenLSTM1's
+ * miopenRNNForwardInference call (runtime/source/executor/op_executor/miopen_ops_executor.cpp:22-241).
+ * y / hn / cn may point into slices of larger caller buffers (the reference's in-place
+ * "custom cat" aliasing, miopen_ops_executor.cpp:193-228). */
+int pimb200_lstm_forward(pimb200_lstm* h, const void* x, int T, int B, const void* h0, const void* c0,
+                         void* y, void* hn, void* cn, int batch_first, void* stream);
+
+/* Forward pass, packed sequence:  data [sum(batch_sizes), I], batch_sizes = T host int64 values,
+ * non-increasing; y [sum(batch_sizes), D*H]; h0/c0/hn/cn [L*D, batch_sizes[0], H].
+ * Replaces atenLstm2 -> at::lstm(data, batch_sizes, ...) (aten_ops.cpp:337-344) and
+ * executeMIOpenLSTM2 (miopen_ops_executor.cpp:243-421). */
+int pimb200_lstm_forward_packed(pimb200_lstm* h, const void* data, const int64_t* batch_sizes, int T,
+                                const void* h0, const void* c0, void* y, void* hn, void* cn, void* stream);
+
+/* The last device-side status of a handle's asynchronous work: call after synchronising the
+ * stream; returns PIMB200_ERR_TIMEOUT when a bounded wait inside the persistent kernel gave up. */
+int pimb200_lstm_last_status(pimb200_lstm* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIMB200_H_ */

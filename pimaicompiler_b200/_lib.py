@@ -1,0 +1,85 @@
+"""ctypes binding of libpimb200.so — the only way Python code in this package reaches the kernels.
+
+There is no fall-back: if the shared library is missing or a symbol declared in
+``include/pimb200.h`` is absent, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(PKG_DIR)
+LIB_PATH = os.path.join(PKG_DIR, "libpimb200.so")
+HEADER_PATH = os.path.join(ROOT, "include", "pimb200.h")
+
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_TIMEOUT, ERR_NOT_INIT, ERR_NO_MEMORY = range(7)
+ACT_NONE, ACT_RELU = 0, 1
+LSTM_AUTO, LSTM_STREAMED, LSTM_PERSISTENT = 0, 1, 2
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes); must list every function declared in include/pimb200.h
+SIGNATURES = {
+    "pimb200_status_string": (C.c_char_p, [_i]),
+    "pimb200_init": (_i, [_i]),
+    "pimb200_shutdown": (_i, [_i]),
+    "pimb200_gemv_mv": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pimb200_gemv_vm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pimb200_dot_vv": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "pimb200_bmm_row": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "pimb200_gemm_wx": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "pimb200_add_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pimb200_copy_2d": (_i, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
+    "pimb200_cat": (_i, [_vp, C.POINTER(_vp), C.POINTER(_sz), _i, _sz, _vp]),
+    "pimb200_lstm_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "pimb200_lstm_destroy": (_i, [_vp]),
+    "pimb200_lstm_set_variant": (_i, [_vp, _i]),
+    "pimb200_lstm_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "pimb200_lstm_forward_packed": (_i, [_vp, _vp, C.POINTER(C.c_int64), _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "pimb200_lstm_last_status": (_i, [_vp]),
+}
+
+_lib = None
+
+
+def declared_symbols() -> list[str]:
+    """Function names declared in include/pimb200.h (parsed from the header text)."""
+    with open(HEADER_PATH) as f:
+        text = f.read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pimb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib() -> C.CDLL:
+    """Load libpimb200.so once and attach argument types.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m pimaicompiler_b200.build` "
+            "(there is no CPU or PyTorch fall-back for these ops)")
+    handle = C.CDLL(LIB_PATH)
+    for name in declared_symbols():
+        if not hasattr(handle, name):
+            raise RuntimeError(f"libpimb200.so does not export {name}, which include/pimb200.h declares")
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = handle
+    return _lib
+
+
+class Pimb200Error(RuntimeError):
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib().pimb200_status_string(status).decode()
+        super().__init__(f"{where}: status {status} ({msg})")
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise Pimb200Error(status, where)

@@ -1,0 +1,608 @@
+// Fused multi-layer LSTM forward (inference), fp16 storage / fp32 accumulate.
+//
+// Math (PyTorch gate order i,f,g,o — the order at::lstm uses, which the reference calls at
+// runtime/source/executor/op_executor/aten_ops.cpp:328-344):
+//     z      = W_ih x_t + b_ih + W_hh h_{t-1} + b_hh
+//     c_t    = sigmoid(z_f) * c_{t-1} + sigmoid(z_i) * tanh(z_g)
+//     h_t    = sigmoid(z_o) * tanh(c_t)
+//
+// Structure per (layer, direction):
+//   1. whole-sequence input projection  G[T*B, 4H] = X · Wp_ih^T  (one dense GEMM, fp32 result)
+//   2. the recurrence over T, in one of two variants:
+//        streamed   — one launch per timestep; W_hh is re-read (from L2/HBM) every step with
+//                     128-bit loads; any B, any H; the form used by seq_len==1 decoder calls
+//        persistent — one cooperative launch for all T steps; every CTA keeps its slice of W_hh in
+//                     shared memory for the whole sequence, hidden states travel between CTAs as
+//                     64-bit {value, step-tag} words polled from L2 (a data-carrying grid
+//                     barrier, one L2 round trip per step); B == 1
+// Weights are stored gate-interleaved (packed row u*4+g = original row g*H+u) so the four gate
+// rows of one hidden unit are contiguous and its four pre-activations are one float4 of G.
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+namespace pimb200 {
+int launch_gemm_wx_simt(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
+                        int ldy, int act, int y_is_f32, cudaStream_t st);
+int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
+                   int ldy, int act, int y_is_f32, cudaStream_t st);
+}  // namespace pimb200
+
+using namespace pimb200;
+
+// ---------------------------------------------------------------------------------------------
+// weight packing
+// ---------------------------------------------------------------------------------------------
+__global__ void lstm_pack_matrix_kernel(const __half* __restrict__ src, __half* __restrict__ dst, int H, int cols) {
+    // dst[(u*4+g), :] = src[(g*H+u), :]
+    const size_t total = (size_t)4 * H * cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t prow = i / cols;
+        const int c = (int)(i - prow * cols);
+        const int u = (int)(prow >> 2), g = (int)(prow & 3);
+        dst[i] = src[((size_t)g * H + u) * cols + c];
+    }
+}
+__global__ void lstm_pack_bias_kernel(const __half* __restrict__ b_ih, const __half* __restrict__ b_hh,
+                                      float* __restrict__ dst, int H) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= 4 * H) return;
+    const int u = i >> 2, g = i & 3;
+    float v = 0.f;
+    if (b_ih) v += __half2float(b_ih[g * H + u]);
+    if (b_hh) v += __half2float(b_hh[g * H + u]);
+    dst[i] = v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// streamed recurrence: one launch per timestep
+// ---------------------------------------------------------------------------------------------
+struct StepArgs {
+    const __half* Whh;        // packed [4H, H]
+    const float* bias;        // packed [4H]
+    const float* G;           // gate pre-activations of this timestep, sequence b at G + b*g_bstride
+    long g_bstride;
+    const __half* hprev_seq;  // h_{t-1} of sequence b at hprev_seq + b*hp_bstride, valid for b < n_prev
+    long hp_bstride;
+    int n_prev;
+    const __half* h0;         // initial state of sequence b at h0 + b*H (NULL = zeros), used for b >= n_prev
+    float* c;                 // running cell state, fp32 [B, H]
+    __half* hout;             // h_t of sequence b at hout + b*ho_bstride
+    long ho_bstride;
+    __half* hn;               // optional final-state outputs [B, H]
+    __half* cn;
+    int H;
+    int B;
+};
+
+template <int BT, bool VEC>
+__global__ void __launch_bounds__(256) lstm_step_kernel(StepArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int u = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (u >= a.H) return;
+    const int H = a.H;
+    const __half* w = a.Whh + (size_t)u * 4 * H;
+    for (int b0 = 0; b0 < a.B; b0 += BT) {
+        float acc[4][BT];
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < BT; ++j) acc[g][j] = 0.f;
+        const __half* hp[BT];
+#pragma unroll
+        for (int j = 0; j < BT; ++j) {
+            const int b = min(b0 + j, a.B - 1);
+            hp[j] = (b < a.n_prev) ? a.hprev_seq + (size_t)b * a.hp_bstride : (a.h0 ? a.h0 + (size_t)b * H : nullptr);
+        }
+        if (VEC) {
+            const int H8 = H >> 3;
+#pragma unroll 2
+            for (int c = lane; c < H8; c += 32) {
+                uint4 wv[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) wv[g] = __ldg(reinterpret_cast<const uint4*>(w + (size_t)g * H) + c);
+#pragma unroll
+                for (int j = 0; j < BT; ++j) {
+                    if (hp[j]) {
+                        float xf[8];
+                        widen8(__ldcg(reinterpret_cast<const uint4*>(hp[j]) + c), xf);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) acc[g][j] = dot8f(wv[g], xf, acc[g][j]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < H; k += 32) {
+                float wf[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) wf[g] = __half2float(w[(size_t)g * H + k]);
+#pragma unroll
+                for (int j = 0; j < BT; ++j) {
+                    if (hp[j]) {
+                        const float hv = __half2float(__ldcg(hp[j] + k));
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) acc[g][j] = fmaf(wf[g], hv, acc[g][j]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < BT; ++j) acc[g][j] = warp_sum(acc[g][j]);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < BT; ++j) {
+                const int b = b0 + j;
+                if (b >= a.B) break;
+                const float* gx = a.G + (size_t)b * a.g_bstride + (size_t)u * 4;
+                const float zi = acc[0][j] + gx[0] + a.bias[u * 4 + 0];
+                const float zf = acc[1][j] + gx[1] + a.bias[u * 4 + 1];
+                const float zg = acc[2][j] + gx[2] + a.bias[u * 4 + 2];
+                const float zo = acc[3][j] + gx[3] + a.bias[u * 4 + 3];
+                float* cp = a.c + (size_t)b * H + u;
+                const float cnew = sigmoidf_(zf) * (*cp) + sigmoidf_(zi) * tanhf_(zg);
+                const float hnew = sigmoidf_(zo) * tanhf_(cnew);
+                *cp = cnew;
+                const __half hh = __float2half_rn(hnew);
+                a.hout[(size_t)b * a.ho_bstride + u] = hh;
+                if (a.hn) a.hn[(size_t)b * H + u] = hh;
+                if (a.cn) a.cn[(size_t)b * H + u] = __float2half_rn(cnew);
+            }
+        }
+    }
+}
+
+__global__ void lstm_init_c_kernel(float* __restrict__ c, const __half* __restrict__ c0, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) c[i] = c0 ? __half2float(c0[i]) : 0.f;
+}
+// final states of sequences that never became active cannot occur (batch_sizes[0] == B), but the
+// padded path with T steps needs hn/cn even when the caller passes h0 only: handled by the step kernel.
+
+// ---------------------------------------------------------------------------------------------
+// persistent weight-stationary recurrence (B == 1)
+// ---------------------------------------------------------------------------------------------
+constexpr int kPersistMaxWordsPerThread = 8;
+constexpr int kPersistPollLimit = 1 << 21;  // bounded wait: ~seconds, then the kernel gives up
+
+__device__ __forceinline__ void ll_store(unsigned long long* p, uint32_t data, uint32_t tag) {
+    const unsigned long long v = ((unsigned long long)tag << 32) | data;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ll_load(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct PersistArgs {
+    const __half* Whh;      // packed [4H, H]
+    const float* bias;      // packed [4H]
+    const float* G;         // [T, 4H] row stride g_tstride floats
+    long g_tstride;
+    const __half* h0;       // [H] or NULL
+    const __half* c0;       // [H] or NULL
+    __half* y;              // h_t at y + t*y_tstride + u
+    long y_tstride;
+    __half* hn;             // optional [H]
+    __half* cn;             // optional [H]
+    unsigned long long* xchg;  // [2][H] exchange words
+    uint32_t tag_base;      // tag of step s output = tag_base + s + 1
+    int* status;            // device status word, set to PIMB200_ERR_TIMEOUT when a wait runs out
+    int H, T, U;            // U = hidden units per CTA
+    int reverse;
+    int poll_limit;
+};
+
+__global__ void __launch_bounds__(512) lstm_persistent_kernel(PersistArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, U = a.U, T = a.T;
+    const int H8 = H >> 3;
+    __half* Ws = reinterpret_cast<__half*>(smem_raw);                    // [U*4][H]
+    __half* hs = Ws + (size_t)U * 4 * H;                                 // [2][H]
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int u0 = blockIdx.x * U;
+    const int nu = min(U, H - u0);  // units this CTA owns
+    const int u = u0 + warp;
+    const bool owner = (warp < nu);
+
+    // one-time: this CTA's slice of W_hh goes to shared memory and stays there for all T steps
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
+        uint4* dst = reinterpret_cast<uint4*>(Ws);
+        const int n16 = nu * 4 * H8;
+        for (int i = tid; i < n16; i += nthr) dst[i] = ldg_stream_v4(src + i);
+    }
+    // h_{-1}
+    for (int i = tid; i < H; i += nthr) hs[i] = a.h0 ? a.h0[i] : __float2half_rn(0.f);
+
+    float c = 0.f;
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 gx = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (owner && lane == 0) {
+        c = a.c0 ? __half2float(a.c0[u]) : 0.f;
+        bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
+        const int t0 = a.reverse ? T - 1 : 0;
+        gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)u * 4));
+    }
+    __syncthreads();
+
+    for (int s = 0; s < T; ++s) {
+        const int t = a.reverse ? T - 1 - s : s;
+        const __half* hcur = hs + (size_t)(s & 1) * H;
+        float4 gx_next = gx;
+        if (owner) {
+            if (lane == 0 && s + 1 < T) {
+                const int tn = a.reverse ? t - 1 : t + 1;
+                gx_next = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)u * 4));
+            }
+            const uint4* w4 = reinterpret_cast<const uint4*>(Ws + (size_t)warp * 4 * H);
+            const uint4* h4 = reinterpret_cast<const uint4*>(hcur);
+            float zi = 0.f, zf = 0.f, zg = 0.f, zo = 0.f;
+            for (int cidx = lane; cidx < H8; cidx += 32) {
+                float xf[8];
+                widen8(h4[cidx], xf);
+                zi = dot8f(w4[cidx], xf, zi);
+                zf = dot8f(w4[H8 + cidx], xf, zf);
+                zg = dot8f(w4[2 * H8 + cidx], xf, zg);
+                zo = dot8f(w4[3 * H8 + cidx], xf, zo);
+            }
+            zi = warp_sum(zi);
+            zf = warp_sum(zf);
+            zg = warp_sum(zg);
+            zo = warp_sum(zo);
+            if (lane == 0) {
+                zi += gx.x + bias4.x;
+                zf += gx.y + bias4.y;
+                zg += gx.z + bias4.z;
+                zo += gx.w + bias4.w;
+                c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
+                const float hnew = sigmoidf_(zo) * tanhf_(c);
+                const __half hh = __float2half_rn(hnew);
+                // publish first (it is on every other CTA's critical path), then the plain output
+                ll_store(a.xchg + (size_t)(s & 1) * H + u, (uint32_t)__half_as_ushort(hh), a.tag_base + s + 1);
+                a.y[(size_t)t * a.y_tstride + u] = hh;
+                if (s == T - 1) {
+                    if (a.hn) a.hn[u] = hh;
+                    if (a.cn) a.cn[u] = __float2half_rn(c);
+                }
+            }
+        }
+        gx = gx_next;
+        int timed_out = 0;
+        if (s + 1 < T) {
+            // gather h_s from every CTA: each thread polls its words until all carry this step's tag
+            const unsigned long long* src = a.xchg + (size_t)(s & 1) * H;
+            __half* hnext = hs + (size_t)((s + 1) & 1) * H;
+            const uint32_t want = a.tag_base + s + 1;
+            unsigned long long v[kPersistMaxWordsPerThread];
+            int polls = 0;
+            while (true) {
+                bool ok = true;
+#pragma unroll
+                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
+                    const int idx = tid + j * nthr;
+                    if (idx < H) v[j] = ll_load(src + idx);
+                }
+#pragma unroll
+                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
+                    const int idx = tid + j * nthr;
+                    if (idx < H) ok = ok && ((uint32_t)(v[j] >> 32) == want);
+                }
+                if (ok) break;
+                if (++polls >= a.poll_limit) {
+                    timed_out = 1;
+                    break;
+                }
+                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) {
+                    timed_out = 1;  // another CTA already gave up
+                    break;
+                }
+            }
+            if (!timed_out) {
+#pragma unroll
+                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
+                    const int idx = tid + j * nthr;
+                    if (idx < H) hnext[idx] = __ushort_as_half((unsigned short)(v[j] & 0xffffu));
+                }
+            } else {
+                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            }
+        }
+        if (__syncthreads_or(timed_out)) return;  // whole CTA leaves together
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct pimb200_lstm {
+    int L = 0, D = 1, I = 0, H = 0, has_biases = 0, device = 0;
+    int variant = PIMB200_LSTM_AUTO;
+    int sm_count = kNumSmB200;
+    int max_smem_optin = 0;
+    std::vector<__half*> w_ih, w_hh;  // per (l*D+d), packed
+    std::vector<float*> bias;         // per (l*D+d), packed fp32
+    // workspace, grown on demand
+    float* G = nullptr;
+    size_t G_cap = 0;
+    __half* ybuf[2] = {nullptr, nullptr};
+    size_t y_cap[2] = {0, 0};
+    float* cstate = nullptr;
+    size_t c_cap = 0;
+    unsigned long long* xchg = nullptr;  // [2][H]
+    int* d_status = nullptr;
+    uint32_t tag_counter = 0;
+    int poll_limit = kPersistPollLimit;
+    std::mutex mu;
+};
+
+static int in_size(const pimb200_lstm* h, int l) { return l == 0 ? h->I : h->D * h->H; }
+
+extern "C" int pimb200_lstm_destroy(pimb200_lstm* h) {
+    if (!h) return PIMB200_OK;
+    cudaSetDevice(h->device);
+    for (auto p : h->w_ih) cudaFree(p);
+    for (auto p : h->w_hh) cudaFree(p);
+    for (auto p : h->bias) cudaFree(p);
+    cudaFree(h->G);
+    cudaFree(h->ybuf[0]);
+    cudaFree(h->ybuf[1]);
+    cudaFree(h->cstate);
+    cudaFree(h->xchg);
+    cudaFree(h->d_status);
+    delete h;
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int num_layers, int bidirectional,
+                                   int input_size, int hidden_size, int has_biases, pimb200_lstm** out) {
+    if (!params || !out || num_layers <= 0 || input_size <= 0 || hidden_size <= 0) return PIMB200_ERR_BAD_ARG;
+    const int D = bidirectional ? 2 : 1;
+    const int per = has_biases ? 4 : 2;
+    if (n_params != per * D * num_layers) return PIMB200_ERR_BAD_ARG;
+    for (int i = 0; i < n_params; ++i)
+        if (!params[i]) return PIMB200_ERR_BAD_ARG;
+    pimb200_lstm* h = new pimb200_lstm();
+    h->L = num_layers; h->D = D; h->I = input_size; h->H = hidden_size; h->has_biases = has_biases ? 1 : 0;
+    int rc = PIMB200_OK;
+    auto fail = [&](int code) { pimb200_lstm_destroy(h); return code; };
+    if (cudaGetDevice(&h->device) != cudaSuccess) return fail(PIMB200_ERR_LAUNCH);
+    cudaDeviceGetAttribute(&h->sm_count, cudaDevAttrMultiProcessorCount, h->device);
+    cudaDeviceGetAttribute(&h->max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, h->device);
+    const int H = hidden_size;
+    for (int l = 0; l < num_layers; ++l) {
+        for (int d = 0; d < D; ++d) {
+            const int Il = in_size(h, l);
+            const void* const* p = params + (size_t)(l * D + d) * per;
+            __half *wi = nullptr, *wh = nullptr;
+            float* bs = nullptr;
+            if (cudaMalloc(&wi, (size_t)4 * H * Il * 2) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+            h->w_ih.push_back(wi);
+            if (cudaMalloc(&wh, (size_t)4 * H * H * 2) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+            h->w_hh.push_back(wh);
+            if (cudaMalloc(&bs, (size_t)4 * H * 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+            h->bias.push_back(bs);
+            lstm_pack_matrix_kernel<<<296, 256>>>(static_cast<const __half*>(p[0]), wi, H, Il);
+            lstm_pack_matrix_kernel<<<296, 256>>>(static_cast<const __half*>(p[1]), wh, H, H);
+            lstm_pack_bias_kernel<<<ceil_div(4 * H, 256), 256>>>(
+                has_biases ? static_cast<const __half*>(p[2]) : nullptr,
+                has_biases ? static_cast<const __half*>(p[3]) : nullptr, bs, H);
+        }
+    }
+    if (cudaMalloc(&h->xchg, (size_t)2 * H * 8) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+    if (cudaMalloc(&h->d_status, 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+    cudaMemset(h->xchg, 0, (size_t)2 * H * 8);
+    cudaMemset(h->d_status, 0, 4);
+    if ((rc = cuda_status(cudaDeviceSynchronize())) != PIMB200_OK) return fail(rc);
+    *out = h;
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_lstm_set_variant(pimb200_lstm* h, int variant) {
+    if (!h || variant < 0 || variant > 2) return PIMB200_ERR_BAD_ARG;
+    h->variant = variant;
+    return PIMB200_OK;
+}
+
+// test hook: shrink the bounded wait so a withheld arrival is detected quickly (not part of the public header's
+// stable surface, but exported so host-side fault tests can reach it)
+extern "C" int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit) {
+    if (!h || limit <= 0) return PIMB200_ERR_BAD_ARG;
+    h->poll_limit = limit;
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_lstm_last_status(pimb200_lstm* h) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    int v = 0;
+    PIMB200_CUDA_TRY(cudaMemcpy(&v, h->d_status, 4, cudaMemcpyDeviceToHost));
+    if (v != 0) PIMB200_CUDA_TRY(cudaMemset(h->d_status, 0, 4));
+    return v;
+}
+
+template <typename T>
+static int grow(T** p, size_t* cap, size_t need_elems) {
+    if (*cap >= need_elems) return PIMB200_OK;
+    PIMB200_CUDA_TRY(cudaDeviceSynchronize());  // earlier launches may still use the old block
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    PIMB200_CUDA_TRY(cudaMalloc(p, need_elems * sizeof(T)));
+    *cap = need_elems;
+    return PIMB200_OK;
+}
+
+struct PersistPlan { bool ok; int U, ncta, threads; size_t smem; };
+static PersistPlan plan_persistent(const pimb200_lstm* h) {
+    PersistPlan p{false, 0, 0, 0, 0};
+    const int H = h->H;
+    if (H % 8 != 0) return p;
+    int U = ceil_div(H, h->sm_count);
+    if (U > 16) return p;
+    p.U = U;
+    p.ncta = ceil_div(H, U);
+    int threads = U * 32;
+    const int min_thr = ceil_div(H, kPersistMaxWordsPerThread);
+    if (threads < min_thr) threads = ceil_div(min_thr, 32) * 32;
+    if (threads < 128) threads = 128;
+    if (threads > 512) return p;
+    p.threads = threads;
+    p.smem = (size_t)U * 4 * H * 2 + (size_t)2 * H * 2;
+    if ((int)p.smem > h->max_smem_optin) return p;
+    p.ok = true;
+    return p;
+}
+
+// one (layer, direction) recurrence over a padded batch or a packed sequence
+struct SeqLayout {
+    int T, B;                       // B = batch_sizes[0] for packed input
+    const int64_t* batch_sizes;     // NULL for padded input
+    std::vector<long> row0;         // packed: first row of timestep t
+};
+
+static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool reverse, const float* G, long g_tstride,
+                          long g_bstride, const __half* h0, const __half* c0, __half* y, long y_tstride,
+                          long y_bstride, __half* hn, __half* cn, cudaStream_t st) {
+    const int H = h->H, T = sq.T, B = sq.B;
+    const bool packed = sq.batch_sizes != nullptr;
+    bool use_persistent = false;
+    PersistPlan pp = plan_persistent(h);
+    if (h->variant == PIMB200_LSTM_PERSISTENT) {
+        if (!pp.ok || B != 1 || packed) return PIMB200_ERR_UNSUPPORTED;
+        use_persistent = true;
+    } else if (h->variant == PIMB200_LSTM_AUTO) {
+        use_persistent = pp.ok && B == 1 && !packed && T >= 8;
+    }
+    if (use_persistent) {
+        PersistArgs a;
+        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride;
+        a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.hn = hn; a.cn = cn;
+        a.xchg = h->xchg; a.tag_base = h->tag_counter; a.status = h->d_status;
+        a.H = H; a.T = T; a.U = pp.U; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+        h->tag_counter += (uint32_t)T + 1u;
+        PIMB200_CUDA_TRY(cudaFuncSetAttribute(lstm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)pp.smem));
+        void* kargs[] = {&a};
+        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)lstm_persistent_kernel, dim3(pp.ncta),
+                                                     dim3(pp.threads), kargs, pp.smem, st));
+        return PIMB200_OK;
+    }
+    // streamed
+    int rc = grow(&h->cstate, &h->c_cap, (size_t)B * H);
+    if (rc != PIMB200_OK) return rc;
+    lstm_init_c_kernel<<<ceil_div(B * H, 256), 256, 0, st>>>(h->cstate, c0, B * H);
+    const bool vec = (H % 8 == 0) && aligned16(h0 ? h0 : h->w_hh[ld]) && aligned16(y) && (y_bstride % 8 == 0) &&
+                     (y_tstride % 8 == 0);
+    for (int s = 0; s < T; ++s) {
+        const int t = reverse ? T - 1 - s : s;
+        const int tp = reverse ? t + 1 : t - 1;  // timestep that produced h_prev
+        StepArgs a;
+        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.H = H; a.h0 = h0; a.c = h->cstate;
+        a.hp_bstride = y_bstride; a.ho_bstride = y_bstride; a.g_bstride = g_bstride;
+        if (packed) {
+            a.B = (int)sq.batch_sizes[t];
+            a.G = G + (size_t)sq.row0[t] * g_tstride;
+            a.hout = y + (size_t)sq.row0[t] * y_tstride;
+            if (s == 0) { a.n_prev = 0; a.hprev_seq = nullptr; }
+            else { a.n_prev = (int)std::min<int64_t>(sq.batch_sizes[tp], a.B); a.hprev_seq = y + (size_t)sq.row0[tp] * y_tstride; }
+            // forward: a sequence's last active step is its final state, so refresh hn/cn every step
+            const bool write_final = reverse ? (s == T - 1) : true;
+            a.hn = write_final ? hn : nullptr;
+            a.cn = write_final ? cn : nullptr;
+        } else {
+            a.B = B;
+            a.G = G + (size_t)t * g_tstride;
+            a.hout = y + (size_t)t * y_tstride;
+            if (s == 0) { a.n_prev = 0; a.hprev_seq = nullptr; }
+            else { a.n_prev = B; a.hprev_seq = y + (size_t)tp * y_tstride; }
+            a.hn = (s == T - 1) ? hn : nullptr;
+            a.cn = (s == T - 1) ? cn : nullptr;
+        }
+        if (a.B <= 0) continue;
+        const int grid = ceil_div(H, 8);
+        if (vec) {
+            if (a.B == 1) lstm_step_kernel<1, true><<<grid, 256, 0, st>>>(a);
+            else if (a.B == 2) lstm_step_kernel<2, true><<<grid, 256, 0, st>>>(a);
+            else lstm_step_kernel<4, true><<<grid, 256, 0, st>>>(a);
+        } else {
+            if (a.B == 1) lstm_step_kernel<1, false><<<grid, 256, 0, st>>>(a);
+            else lstm_step_kernel<4, false><<<grid, 256, 0, st>>>(a);
+        }
+    }
+    return launch_status();
+}
+
+static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& sq, const __half* h0,
+                             const __half* c0, __half* y, __half* hn, __half* cn, int batch_first,
+                             cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(h->mu);
+    const int H = h->H, D = h->D, L = h->L, T = sq.T, B = sq.B;
+    const bool packed = sq.batch_sizes != nullptr;
+    long rows = 0;  // rows of the flattened [rows, features] activations
+    if (packed) rows = sq.row0[T - 1] + (long)sq.batch_sizes[T - 1];
+    else rows = (long)T * B;
+    int rc;
+    if ((rc = grow(&h->G, &h->G_cap, (size_t)rows * 4 * H)) != PIMB200_OK) return rc;
+    if (L > 1 && (rc = grow(&h->ybuf[0], &h->y_cap[0], (size_t)rows * D * H)) != PIMB200_OK) return rc;
+    if (L > 2 && (rc = grow(&h->ybuf[1], &h->y_cap[1], (size_t)rows * D * H)) != PIMB200_OK) return rc;
+    for (int l = 0; l < L; ++l) {
+        const int Il = in_size(h, l);
+        const bool first = (l == 0), last = (l == L - 1);
+        const __half* X = first ? x : h->ybuf[(l - 1) & 1];
+        __half* Y = last ? y : h->ybuf[l & 1];
+        // row index of (t, b): user layout on the outermost tensors, time-major in between
+        long in_t, in_b, out_t, out_b;
+        if (packed) { in_t = 1; in_b = 1; out_t = 1; out_b = 1; }  // row = row0[t] + b
+        else {
+            in_t = (first && batch_first) ? 1 : B;  in_b = (first && batch_first) ? T : 1;
+            out_t = (last && batch_first) ? 1 : B;  out_b = (last && batch_first) ? T : 1;
+        }
+        for (int d = 0; d < D; ++d) {
+            const int ld = l * D + d;
+            rc = launch_gemm_wx(h->w_ih[ld], X, nullptr, h->G, 4 * H, Il, (int)rows, Il, 4 * H, PIMB200_ACT_NONE, 1,
+                                st);
+            if (rc != PIMB200_OK) return rc;
+            const __half* h0_ld = h0 ? h0 + (size_t)ld * B * H : nullptr;
+            const __half* c0_ld = c0 ? c0 + (size_t)ld * B * H : nullptr;
+            __half* hn_ld = hn ? hn + (size_t)ld * B * H : nullptr;
+            __half* cn_ld = cn ? cn + (size_t)ld * B * H : nullptr;
+            rc = run_recurrence(h, ld, sq, d == 1, h->G, in_t * 4 * H, in_b * 4 * H, h0_ld, c0_ld,
+                                Y + (size_t)d * H, out_t * (long)D * H, out_b * (long)D * H, hn_ld, cn_ld, st);
+            if (rc != PIMB200_OK) return rc;
+        }
+    }
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_lstm_forward(pimb200_lstm* h, const void* x, int T, int B, const void* h0, const void* c0,
+                                    void* y, void* hn, void* cn, int batch_first, void* stream) {
+    if (!h || !x || !y || T <= 0 || B <= 0) return PIMB200_ERR_BAD_ARG;
+    SeqLayout sq;
+    sq.T = T; sq.B = B; sq.batch_sizes = nullptr;
+    return lstm_forward_impl(h, static_cast<const __half*>(x), sq, static_cast<const __half*>(h0),
+                             static_cast<const __half*>(c0), static_cast<__half*>(y), static_cast<__half*>(hn),
+                             static_cast<__half*>(cn), batch_first ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pimb200_lstm_forward_packed(pimb200_lstm* h, const void* data, const int64_t* batch_sizes, int T,
+                                           const void* h0, const void* c0, void* y, void* hn, void* cn,
+                                           void* stream) {
+    if (!h || !data || !y || !batch_sizes || T <= 0) return PIMB200_ERR_BAD_ARG;
+    SeqLayout sq;
+    sq.T = T; sq.B = (int)batch_sizes[0]; sq.batch_sizes = batch_sizes;
+    if (sq.B <= 0) return PIMB200_ERR_BAD_ARG;
+    sq.row0.resize(T);
+    long acc = 0;
+    for (int t = 0; t < T; ++t) {
+        if (batch_sizes[t] <= 0 || (t > 0 && batch_sizes[t] > batch_sizes[t - 1])) return PIMB200_ERR_BAD_ARG;
+        sq.row0[t] = acc;
+        acc += (long)batch_sizes[t];
+    }
+    return lstm_forward_impl(h, static_cast<const __half*>(data), sq, static_cast<const __half*>(h0),
+                             static_cast<const __half*>(c0), static_cast<__half*>(y), static_cast<__half*>(hn),
+                             static_cast<__half*>(cn), 0, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,216 @@
+"""Thin tensor-level wrappers over the C ABI (``include/pimb200.h``).
+
+torch is used for device memory and streams only: every function passes raw ``data_ptr()``
+values and sizes through ctypes into libpimb200.so.  Nothing here computes on the host and
+nothing falls back to a PyTorch op.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import ACT_NONE, ACT_RELU, LSTM_AUTO, LSTM_PERSISTENT, LSTM_STREAMED, check  # noqa: F401
+
+_initialised: set[int] = set()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _req_half_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.float16:
+            raise TypeError("expected a CUDA fp16 tensor")
+        if not t.is_contiguous():
+            raise ValueError("expected a contiguous tensor")
+
+
+def init(device: Optional[int] = None) -> None:
+    """pimb200_init for ``device`` (default: the current device); idempotent."""
+    dev = torch.cuda.current_device() if device is None else int(device)
+    if dev in _initialised:
+        return
+    check(_lib.lib().pimb200_init(dev), "pimb200_init")
+    _initialised.add(dev)
+
+
+def shutdown(device: Optional[int] = None) -> None:
+    dev = torch.cuda.current_device() if device is None else int(device)
+    check(_lib.lib().pimb200_shutdown(dev), "pimb200_shutdown")
+    _initialised.discard(dev)
+
+
+def gemv_mv(W: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[N] = act(W[N,K] @ x[K] + bias)."""
+    _req_half_cuda(W, x, bias)
+    N, K = W.shape
+    assert x.numel() == K
+    y = out if out is not None else torch.empty(N, dtype=torch.float16, device=W.device)
+    check(_lib.lib().pimb200_gemv_mv(_ptr(W), _ptr(x), _ptr(bias), _ptr(y), N, K, act, _stream()), "gemv_mv")
+    return y
+
+
+def gemv_vm(x: torch.Tensor, A: torch.Tensor, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[N] = act(x[K] @ A[K,N] + bias)."""
+    _req_half_cuda(A, x, bias)
+    init(A.device.index)
+    K, N = A.shape
+    assert x.numel() == K
+    y = out if out is not None else torch.empty(N, dtype=torch.float16, device=A.device)
+    check(_lib.lib().pimb200_gemv_vm(_ptr(x), _ptr(A), _ptr(bias), _ptr(y), K, N, act, _stream()), "gemv_vm")
+    return y
+
+
+def dot_vv(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    _req_half_cuda(a, b)
+    assert a.numel() == b.numel()
+    y = torch.empty(1, dtype=torch.float16, device=a.device)
+    check(_lib.lib().pimb200_dot_vv(_ptr(a), _ptr(b), _ptr(y), a.numel(), _stream()), "dot_vv")
+    return y
+
+
+def bmm_row(x: torch.Tensor, A: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[n] = x[k] @ A[k,n] (single-row batched matmul of the GNMT attention context)."""
+    _req_half_cuda(x, A)
+    k, n = A.shape[-2], A.shape[-1]
+    assert x.numel() == k
+    y = out if out is not None else torch.empty(n, dtype=torch.float16, device=A.device)
+    check(_lib.lib().pimb200_bmm_row(_ptr(x), _ptr(A), _ptr(y), k, n, _stream()), "bmm_row")
+    return y
+
+
+def gemm_wx(W: torch.Tensor, X: torch.Tensor, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
+            out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Y[J,N] = act(X[J,K] @ W[N,K]^T + bias)."""
+    _req_half_cuda(W, X, bias)
+    N, K = W.shape
+    J = X.shape[0]
+    assert X.shape[1] == K
+    if out is None:
+        out = torch.empty(J, N, dtype=torch.float32 if out_f32 else torch.float16, device=W.device)
+    check(_lib.lib().pimb200_gemm_wx(_ptr(W), _ptr(X), _ptr(bias), _ptr(out), N, K, J, K, out.stride(0), act,
+                                     1 if out.dtype == torch.float32 else 0, _stream()), "gemm_wx")
+    return out
+
+
+def add_f16(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A + B, same shape, or B a single row broadcast over the rows of A."""
+    _req_half_cuda(A, B)
+    n = A.shape[-1]
+    m = A.numel() // n
+    bcast = 0 if B.numel() == A.numel() else 1
+    if bcast and B.numel() != n:
+        raise ValueError("B must match A or be one row of it")
+    C_ = out if out is not None else torch.empty_like(A)
+    check(_lib.lib().pimb200_add_f16(_ptr(A), _ptr(B), _ptr(C_), m, n, bcast, _stream()), "add_f16")
+    return C_
+
+
+def copy_2d(dst: torch.Tensor, dst_off_bytes: int, dst_pitch: int, src: torch.Tensor, src_off_bytes: int,
+            src_pitch: int, row_bytes: int, rows: int) -> None:
+    check(_lib.lib().pimb200_copy_2d(dst.data_ptr() + dst_off_bytes, dst_pitch, src.data_ptr() + src_off_bytes,
+                                     src_pitch, row_bytes, rows, _stream()), "copy_2d")
+
+
+def cat(tensors: Sequence[torch.Tensor], dim: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """aten::cat for contiguous CUDA tensors of one dtype, via strided device copies."""
+    nonempty = [t for t in tensors if t.numel() > 0]
+    ref = nonempty[0] if nonempty else tensors[0]
+    nd = ref.dim()
+    dim = dim % nd
+    shape = list(ref.shape)
+    shape[dim] = sum(t.shape[dim] for t in nonempty)
+    if out is None:
+        out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
+    if not nonempty or out.numel() == 0:
+        return out
+    outer = 1
+    for s in shape[:dim]:
+        outer *= s
+    es = ref.element_size()
+    n = len(nonempty)
+    srcs = (C.c_void_p * n)(*[t.data_ptr() for t in nonempty])
+    inner = (C.c_size_t * n)(*[(t.numel() // max(outer, 1)) * es for t in nonempty])
+    for t in nonempty:
+        if not t.is_contiguous() or t.dtype != ref.dtype:
+            raise ValueError("cat operands must be contiguous and share a dtype")
+    check(_lib.lib().pimb200_cat(out.data_ptr(), srcs, inner, n, outer, _stream()), "cat")
+    return out
+
+
+class Lstm:
+    """Packed-weight handle of one aten::lstm node (``pimb200_lstm_create`` ... ``_destroy``)."""
+
+    def __init__(self, params: Sequence[torch.Tensor], num_layers: int, bidirectional: bool, input_size: int,
+                 hidden_size: int, has_biases: bool = True):
+        for p in params:
+            _req_half_cuda(p)
+        self.L, self.D = num_layers, 2 if bidirectional else 1
+        self.I, self.H = input_size, hidden_size
+        self.device = params[0].device
+        arr = (C.c_void_p * len(params))(*[p.data_ptr() for p in params])
+        handle = C.c_void_p()
+        check(_lib.lib().pimb200_lstm_create(arr, len(params), num_layers, 1 if bidirectional else 0, input_size,
+                                             hidden_size, 1 if has_biases else 0, C.byref(handle)), "lstm_create")
+        self._h = handle
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().pimb200_lstm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_variant(self, variant: int) -> None:
+        check(_lib.lib().pimb200_lstm_set_variant(self._h, variant), "lstm_set_variant")
+
+    def last_status(self) -> int:
+        return _lib.lib().pimb200_lstm_last_status(self._h)
+
+    def forward(self, x: torch.Tensor, h0: Optional[torch.Tensor] = None, c0: Optional[torch.Tensor] = None,
+                batch_first: bool = False, out=None):
+        _req_half_cuda(x, h0, c0)
+        if batch_first:
+            B, T, _ = x.shape
+        else:
+            T, B, _ = x.shape
+        DH = self.D * self.H
+        if out is None:
+            y = torch.empty((B, T, DH) if batch_first else (T, B, DH), dtype=torch.float16, device=x.device)
+            hn = torch.empty(self.L * self.D, B, self.H, dtype=torch.float16, device=x.device)
+            cn = torch.empty_like(hn)
+        else:
+            y, hn, cn = out
+        check(_lib.lib().pimb200_lstm_forward(self._h, _ptr(x), T, B, _ptr(h0), _ptr(c0), _ptr(y), _ptr(hn),
+                                              _ptr(cn), 1 if batch_first else 0, _stream()), "lstm_forward")
+        return y, hn, cn
+
+    def forward_packed(self, data: torch.Tensor, batch_sizes: torch.Tensor, h0: Optional[torch.Tensor] = None,
+                       c0: Optional[torch.Tensor] = None):
+        _req_half_cuda(data, h0, c0)
+        bs = [int(v) for v in batch_sizes.tolist()]
+        T = len(bs)
+        B = bs[0]
+        arr = (C.c_int64 * T)(*bs)
+        y = torch.empty(data.shape[0], self.D * self.H, dtype=torch.float16, device=data.device)
+        hn = torch.empty(self.L * self.D, B, self.H, dtype=torch.float16, device=data.device)
+        cn = torch.empty_like(hn)
+        check(_lib.lib().pimb200_lstm_forward_packed(self._h, _ptr(data), arr, T, _ptr(h0), _ptr(c0), _ptr(y),
+                                                     _ptr(hn), _ptr(cn), _stream()), "lstm_forward_packed")
+        return y, hn, cn

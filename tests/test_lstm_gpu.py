@@ -1,0 +1,166 @@
+"""GPU parity of the fused LSTM through the C ABI: both recurrence variants against the C oracle,
+the libtorch golden fixtures, and libtorch CPU at the baseline's C1 shape."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as co
+from tests.util import CONTRACT_ATOL, CONTRACT_RTOL, assert_close, h16, lstm_params, to_dev
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+# vs the fp32 oracle: h is rounded to fp16 every step (rel 2^-11 of values in (-1,1)) and the
+# rounding feeds back through the recurrence; the contract bound is 2e-2 / 1e-2
+LSTM_ATOL = 4e-3
+LSTM_RTOL = 4e-3
+
+
+def _ops():
+    from pimaicompiler_b200 import ops
+    return ops
+
+
+def _run(ops, ps, x, h0, c0, L, bi, hb, bf, variant):
+    T = x.shape[1] if bf else x.shape[0]
+    I, H = x.shape[2], ps[1].shape[1]
+    m = ops.Lstm([to_dev(p) for p in ps], L, bi, I, H, hb)
+    m.set_variant(variant)
+    y, hn, cn = m.forward(to_dev(x), None if h0 is None else to_dev(h0), None if c0 is None else to_dev(c0), bf)
+    torch.cuda.synchronize()
+    assert m.last_status() == 0
+    return y, hn, cn
+
+
+@pytest.mark.parametrize("path", sorted(p for p in glob.glob(os.path.join(GOLD, "lstm_*.npz")) if "packed" not in p))
+def test_lstm_golden_streamed(path):
+    ops = _ops()
+    z = np.load(path)
+    T, B, I, H, L, bi, hb, bf = [int(v) for v in z["cfg"]]
+    ps, i = [], 0
+    while f"p{i}" in z:
+        ps.append(torch.from_numpy(z[f"p{i}"]).float())
+        i += 1
+    y, hn, cn = _run(ops, ps, torch.from_numpy(z["x"]).float(), torch.from_numpy(z["h0"]).float(),
+                     torch.from_numpy(z["c0"]).float(), L, bool(bi), bool(hb), bool(bf), ops.LSTM_STREAMED)
+    assert_close(y, z["y"], LSTM_ATOL, LSTM_RTOL, "y")
+    assert_close(hn, z["hn"], LSTM_ATOL, LSTM_RTOL, "hn")
+    assert_close(cn, z["cn"], LSTM_ATOL, LSTM_RTOL, "cn")
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "lstm_packed_*.npz"))))
+def test_lstm_golden_packed(path):
+    ops = _ops()
+    z = np.load(path)
+    T, B, I, H, L, bi, hb, bf = [int(v) for v in z["cfg"]]
+    ps, i = [], 0
+    while f"p{i}" in z:
+        ps.append(torch.from_numpy(z[f"p{i}"]).cuda())
+        i += 1
+    m = ops.Lstm(ps, L, bool(bi), I, H, True)
+    y, hn, cn = m.forward_packed(torch.from_numpy(z["data"]).cuda(), torch.from_numpy(z["batch_sizes"]),
+                                 torch.from_numpy(z["h0"]).cuda(), torch.from_numpy(z["c0"]).cuda())
+    assert_close(y, z["y"], LSTM_ATOL, LSTM_RTOL, "packed y")
+    assert_close(hn, z["hn"], LSTM_ATOL, LSTM_RTOL, "packed hn")
+    assert_close(cn, z["cn"], LSTM_ATOL, LSTM_RTOL, "packed cn")
+
+
+# (T, B, I, H, L, bidirectional, has_biases, batch_first, nonzero state)
+CASES = [
+    (1, 1, 8, 8, 1, False, True, False, True),
+    (2, 1, 16, 24, 2, False, True, False, False),
+    (20, 1, 240, 128, 2, False, True, False, True),
+    (16, 1, 64, 320, 2, False, True, False, True),      # prediction-net width
+    (12, 1, 40, 1024, 1, False, True, False, True),
+    (9, 1, 32, 64, 3, True, True, False, True),
+    (10, 1, 32, 64, 2, False, False, True, False),
+    (7, 5, 24, 40, 2, True, True, True, True),           # B > 1: streamed only
+    (3, 2, 7, 5, 2, False, True, False, True),           # odd sizes: scalar path
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("variant", ["streamed", "persistent"])
+def test_lstm_matches_oracle(case, variant):
+    ops = _ops()
+    T, B, I, H, L, bi, hb, bf, nz = case
+    if variant == "persistent" and (B != 1 or H % 8):
+        pytest.skip("persistent variant is batch-1, H % 8 == 0")
+    D = 2 if bi else 1
+    g = torch.Generator().manual_seed(T * 131 + H)
+    ps = lstm_params(L, D, I, H, g, has_biases=hb)
+    x = h16(torch.randn((B, T, I) if bf else (T, B, I), generator=g))
+    h0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5) if nz else None
+    c0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5) if nz else None
+    ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, bi, hb, None if h0 is None else h0.numpy(),
+                  None if c0 is None else c0.numpy(), bf)
+    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, ops.LSTM_STREAMED if variant == "streamed" else ops.LSTM_PERSISTENT)
+    for name, a, b in zip(("y", "hn", "cn"), got, ref):
+        assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"{variant} {name} {case}")
+
+
+@pytest.mark.parametrize("variant", ["streamed", "persistent"])
+def test_lstm_baseline_c1_vs_libtorch(variant):
+    # C1: 2 layers, input 240, hidden 1024, T=200, B=1; x~N(0,1); params~U(-1/32,1/32); h0=c0=0; seed 0
+    ops = _ops()
+    torch.manual_seed(0)
+    T, I, H, L = 200, 240, 1024, 2
+    x = h16(torch.randn(T, 1, I))
+    ps = []
+    for l in range(L):
+        Il = I if l == 0 else H
+        ps += [h16((torch.rand(4 * H, Il) * 2 - 1) / 32), h16((torch.rand(4 * H, H) * 2 - 1) / 32),
+               h16((torch.rand(4 * H) * 2 - 1) / 32), h16((torch.rand(4 * H) * 2 - 1) / 32)]
+    z = torch.zeros(L, 1, H)
+    y_ref, hn_ref, cn_ref = torch.lstm(x, [z, z], ps, True, L, 0.0, False, False, False)
+    y, hn, cn = _run(ops, ps, x, None, None, L, False, True, False,
+                     ops.LSTM_STREAMED if variant == "streamed" else ops.LSTM_PERSISTENT)
+    assert_close(y, y_ref, CONTRACT_ATOL, CONTRACT_RTOL, "C1 y (contract)")
+    e = assert_close(y, y_ref, LSTM_ATOL, LSTM_RTOL, "C1 y")
+    assert_close(hn, hn_ref, LSTM_ATOL, LSTM_RTOL, "C1 hn")
+    assert_close(cn, cn_ref, 2 * LSTM_ATOL, LSTM_RTOL, "C1 cn")
+    print(f"C1 {variant}: max abs err {e:.2e}")
+
+
+def test_lstm_variants_agree_and_repeat():
+    # same handle, three calls in a row: step tags of the persistent exchange must not collide
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    T, I, H, L = 33, 64, 256, 2
+    ps = lstm_params(L, 1, I, H, g)
+    x = h16(torch.randn(T, 1, I, generator=g))
+    m = ops.Lstm([to_dev(p) for p in ps], L, False, I, H, True)
+    m.set_variant(ops.LSTM_STREAMED)
+    ys, hs, cs = m.forward(to_dev(x))
+    m.set_variant(ops.LSTM_PERSISTENT)
+    for _ in range(3):
+        yp, hp, cp = m.forward(to_dev(x))
+        torch.cuda.synchronize()
+        assert m.last_status() == 0
+        assert_close(yp, ys, 1e-3, 1e-3, "persistent vs streamed")
+        assert_close(cp, cs, 2e-3, 1e-3, "persistent vs streamed cn")
+
+
+def test_lstm_outputs_alias_slices_of_caller_buffers():
+    # GNMT-style in-place "custom cat": y goes into the first half of a {1,1,2048} buffer, (h,c) into
+    # slots of an {8,1,1024} state buffer (miopen_ops_executor.cpp:193-228)
+    ops = _ops()
+    g = torch.Generator().manual_seed(6)
+    I = H = 1024
+    ps = lstm_params(1, 1, I, H, g)
+    x = h16(torch.randn(1, 1, I, generator=g))
+    h0 = h16(torch.randn(1, 1, H, generator=g) * 0.5)
+    c0 = h16(torch.randn(1, 1, H, generator=g) * 0.5)
+    ref = co.lstm(x.numpy(), [p.numpy() for p in ps], 1, False, True, h0.numpy(), c0.numpy())
+    cat_buf = torch.full((1, 1, 2048), 5.0, dtype=torch.float16, device="cuda")
+    state_buf = torch.full((8, 1, 1024), 5.0, dtype=torch.float16, device="cuda")
+    m = ops.Lstm([to_dev(p) for p in ps], 1, False, I, H, True)
+    m.forward(to_dev(x), to_dev(h0), to_dev(c0), out=(cat_buf[..., :1024], state_buf[2:3], state_buf[3:4]))
+    torch.cuda.synchronize()
+    assert_close(cat_buf[..., :1024], ref[0], LSTM_ATOL, LSTM_RTOL, "aliased y")
+    assert_close(state_buf[2:3], ref[1], LSTM_ATOL, LSTM_RTOL, "aliased hn")
+    assert_close(state_buf[3:4], ref[2], LSTM_ATOL, LSTM_RTOL, "aliased cn")
+    assert (cat_buf[..., 1024:] == 5).all() and (state_buf[:2] == 5).all() and (state_buf[4:] == 5).all()
