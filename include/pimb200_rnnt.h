@@ -1,0 +1,65 @@
+/*
+ * pimb200_rnnt.h — C ABI of the device-resident RNN-T greedy decoder in libpimb200.so.
+ *
+ * The reference has no single function for this: it interprets the RNN-T TorchScript graph op by op
+ * (StreamExecutor::inferenceModel, runtime/source/executor/stream_executor.cpp:136-202), the greedy
+ * loop being a prim::Loop walked by the host (prim_ops_executor.cpp:744-922) around aten::embedding
+ * (aten_ops_executor.cpp:1276-1287), two seq_len==1 aten::lstm calls, the split joint addmm pair
+ * (compiler/include/frontend/optimizer/remove_cat_for_addmm.h:77-79) and an argmax read back per frame.
+ * These entry points run the same arithmetic for one model family (RNN-T, greedy, at most one symbol per
+ * frame) with the loop on the device.  Weights are passed exactly as the TorchScript constants hold them
+ * (at::lstm flat parameter lists, nn.Linear weight/bias, nn.Embedding weight), fp16, device memory.
+ */
+#ifndef PIMB200_RNNT_H_
+#define PIMB200_RNNT_H_
+
+#include "pimb200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct pimb200_rnnt_config {
+    int feat_dim;      /* 240  */
+    int enc_hidden;    /* 1024 */
+    int pre_layers;    /* 2    */
+    int post_layers;   /* 3    */
+    int stack_factor;  /* 2: consecutive frames concatenated between the two encoder stacks */
+    int pred_hidden;   /* 320  */
+    int pred_layers;   /* 2 (only value supported) */
+    int joint_hidden;  /* 512  */
+    int vocab;         /* 29, blank included */
+    int blank;         /* 28; also the start-of-sequence input of the prediction network */
+    int max_symbols;   /* 1 (only value supported) */
+} pimb200_rnnt_config;
+
+typedef struct pimb200_rnnt_weights {
+    const void* const* pre_params;  int n_pre;   /* at::lstm list of LSTM(feat_dim -> enc_hidden, pre_layers)      */
+    const void* const* post_params; int n_post;  /* at::lstm list of LSTM(stack*enc_hidden -> enc_hidden, post_layers) */
+    const void* embedding;                       /* [vocab, pred_hidden]                                            */
+    const void* const* pred_params; int n_pred;  /* at::lstm list of LSTM(pred_hidden -> pred_hidden, 2)           */
+    const void* joint_w1; const void* joint_b1;  /* [joint_hidden, enc_hidden + pred_hidden], [joint_hidden]        */
+    const void* joint_w2; const void* joint_b2;  /* [vocab, joint_hidden], [vocab]                                  */
+} pimb200_rnnt_weights;
+
+typedef struct pimb200_rnnt pimb200_rnnt;
+
+/* Packs the weights (device-to-device) into memory owned by the handle. */
+int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200_rnnt_weights* w, pimb200_rnnt** out);
+int pimb200_rnnt_destroy(pimb200_rnnt* h);
+
+/* Decodes n_utts utterances of T frames each: feats [n_utts, T, feat_dim] fp16.
+ * tokens [n_utts, T/stack] int32 (emitted labels, in order), n_tokens [n_utts] int32,
+ * logits (optional, may be NULL) [n_utts, T/stack, vocab] fp32 joint outputs of every frame.
+ * Asynchronous on `stream`; all pointers are device memory. */
+int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, int n_utts, int32_t* tokens,
+                        int32_t* n_tokens, float* logits, void* stream);
+
+/* Reports how the greedy kernel was configured: CTAs per cluster, which matrices are staged in shared
+ * memory (bit 0..4 = W_hh0, W_ih1, W_hh1, joint W1 pred half, joint W2) and the dynamic shared memory per CTA. */
+int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t* smem_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIMB200_RNNT_H_ */

@@ -115,3 +115,29 @@ def lstm_packed(data, batch_sizes, params, num_layers, bidirectional, has_biases
                              int(bidirectional), int(has_biases), arr, _f(h0), _f(c0), _f(y), _f(hn), _f(cn),
                              int(emulate_fp16))
     return y, hn, cn
+
+
+def rnnt_greedy(w, feats, cfg, forced=None):
+    """oracle_rnnt_greedy: returns (tokens, logits [Tp,V], choice [Tp]).  `w` holds numpy/torch fp32 arrays
+    with the fields of oracle.torch_oracle.RnntWeights."""
+    def arr(t):
+        return _c(t.numpy() if hasattr(t, "numpy") else t)
+    feats = arr(feats)
+    T = feats.shape[0]
+    Tp = T // cfg.stack_factor
+    pre, pre_arr = _params([arr(p) for p in w.pre])
+    post, post_arr = _params([arr(p) for p in w.post])
+    pred, pred_arr = _params([arr(p) for p in w.pred])
+    emb, w1, b1, w2, b2 = (arr(t) for t in (w.embedding, w.w1, w.b1, w.w2, w.b2))
+    tokens = np.zeros(max(Tp, 1), np.int32)
+    logits = np.zeros((Tp, cfg.vocab), np.float32)
+    choice = np.zeros(max(Tp, 1), np.int32)
+    ip = C.POINTER(C.c_int)
+    forced_arr = None if forced is None else np.ascontiguousarray(forced, dtype=np.int32)
+    fn = lib().oracle_rnnt_greedy
+    fn.restype = C.c_int
+    n = fn(_f(feats), T, cfg.feat_dim, cfg.enc_hidden, cfg.pre_layers, cfg.post_layers, cfg.stack_factor,
+           cfg.pred_hidden, cfg.joint_hidden, cfg.vocab, cfg.blank, pre_arr, post_arr, _f(emb), pred_arr,
+           _f(w1), _f(b1), _f(w2), _f(b2), None if forced_arr is None else forced_arr.ctypes.data_as(ip),
+           tokens.ctypes.data_as(ip), _f(logits), choice.ctypes.data_as(ip))
+    return tokens[:n].tolist(), logits, choice[:Tp].tolist()

@@ -12,7 +12,7 @@ import re
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG_DIR)
 LIB_PATH = os.path.join(PKG_DIR, "libpimb200.so")
-HEADER_PATH = os.path.join(ROOT, "include", "pimb200.h")
+HEADER_PATHS = [os.path.join(ROOT, "include", "pimb200.h"), os.path.join(ROOT, "include", "pimb200_rnnt.h")]
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_TIMEOUT, ERR_NOT_INIT, ERR_NO_MEMORY = range(7)
 ACT_NONE, ACT_RELU = 0, 1
@@ -39,17 +39,37 @@ SIGNATURES = {
     "pimb200_lstm_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "pimb200_lstm_forward_packed": (_i, [_vp, _vp, C.POINTER(C.c_int64), _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "pimb200_lstm_last_status": (_i, [_vp]),
+    "pimb200_rnnt_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
+    "pimb200_rnnt_destroy": (_i, [_vp]),
+    "pimb200_rnnt_decode": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp]),
+    "pimb200_rnnt_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_sz)]),
 }
+
+
+class RnntConfigC(C.Structure):
+    """struct pimb200_rnnt_config (include/pimb200_rnnt.h)."""
+    _fields_ = [(n, _i) for n in ("feat_dim", "enc_hidden", "pre_layers", "post_layers", "stack_factor",
+                                  "pred_hidden", "pred_layers", "joint_hidden", "vocab", "blank", "max_symbols")]
+
+
+class RnntWeightsC(C.Structure):
+    """struct pimb200_rnnt_weights (include/pimb200_rnnt.h)."""
+    _fields_ = [("pre_params", C.POINTER(_vp)), ("n_pre", _i), ("post_params", C.POINTER(_vp)), ("n_post", _i),
+                ("embedding", _vp), ("pred_params", C.POINTER(_vp)), ("n_pred", _i),
+                ("joint_w1", _vp), ("joint_b1", _vp), ("joint_w2", _vp), ("joint_b2", _vp)]
 
 _lib = None
 
 
 def declared_symbols() -> list[str]:
-    """Function names declared in include/pimb200.h (parsed from the header text)."""
-    with open(HEADER_PATH) as f:
-        text = f.read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(pimb200_[a-z0-9_]+)\s*\(", text)))
+    """Function names declared in include/*.h (parsed from the header text)."""
+    names = set()
+    for path in HEADER_PATHS:
+        with open(path) as f:
+            text = f.read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(pimb200_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def lib() -> C.CDLL:
@@ -64,7 +84,7 @@ def lib() -> C.CDLL:
     handle = C.CDLL(LIB_PATH)
     for name in declared_symbols():
         if not hasattr(handle, name):
-            raise RuntimeError(f"libpimb200.so does not export {name}, which include/pimb200.h declares")
+            raise RuntimeError(f"libpimb200.so does not export {name}, which include/*.h declares")
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(handle, name)
         fn.restype = res

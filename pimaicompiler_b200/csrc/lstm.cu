@@ -55,6 +55,15 @@ __global__ void lstm_pack_bias_kernel(const __half* __restrict__ b_ih, const __h
     dst[i] = v;
 }
 
+namespace pimb200 {
+void lstm_pack_matrix(const __half* src, __half* dst, int H, int cols, cudaStream_t st) {
+    lstm_pack_matrix_kernel<<<296, 256, 0, st>>>(src, dst, H, cols);
+}
+void lstm_pack_bias(const __half* b_ih, const __half* b_hh, float* dst, int H, cudaStream_t st) {
+    lstm_pack_bias_kernel<<<ceil_div(4 * H, 256), 256, 0, st>>>(b_ih, b_hh, dst, H);
+}
+}  // namespace pimb200
+
 // ---------------------------------------------------------------------------------------------
 // streamed recurrence: one launch per timestep
 // ---------------------------------------------------------------------------------------------

@@ -1,0 +1,442 @@
+// Device-resident RNN-T greedy decode.
+//
+// The reference runs the whole RNN-T model as one interpreted TorchScript graph: the encoder LSTMs are
+// aten::lstm nodes, and the greedy loop is a prim::Loop walked by the host
+// (runtime/source/executor/stream_executor.cpp:153-186, prim_ops_executor.cpp:744-922) that costs, per
+// decoded frame, an embedding lookup with a device->host sync (aten_ops_executor.cpp:1276-1287), two
+// seq_len==1 aten::lstm calls, the split joint addmm pair + ReLU + addmm (remove_cat_for_addmm.h:77-79,
+// fuse_activation.cpp:88-93) and an argmax read back by the host.  Here the encoder is the fused LSTM of
+// lstm.cu plus one dense GEMM for the encoder half of the joint, and the whole greedy loop is ONE kernel:
+// a thread-block cluster keeps the prediction network and the joint in shared memory, exchanges hidden
+// states through distributed shared memory, and every CTA takes the blank/emit decision redundantly from
+// identical inputs, so no host round trip and no decision broadcast is needed.
+//
+// Model (sizes are run-time arguments; the defaults are the benchmark's):
+//   enc  : LSTM(F -> EH, pre_layers) -> stack `stack` frames -> LSTM(stack*EH -> EH, post_layers)
+//   pred : Embedding(V, PH) -> LSTM(PH -> PH, 2 layers); start-of-sequence input is the blank row
+//   joint: Linear(EH+PH -> JH) -> ReLU -> Linear(JH -> V); greedy, at most one symbol per frame
+#include <cooperative_groups.h>
+
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "pimb200_rnnt.h"
+
+namespace cg = cooperative_groups;
+using namespace pimb200;
+
+namespace pimb200 {
+int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
+                   int ldy, int act, int y_is_f32, cudaStream_t st);
+}
+namespace pimb200 {
+void lstm_pack_matrix(const __half* src, __half* dst, int H, int cols, cudaStream_t st);
+void lstm_pack_bias(const __half* b_ih, const __half* b_hh, float* dst, int H, cudaStream_t st);
+}
+
+__global__ void rnnt_add_bias_rows_kernel(float* __restrict__ P0, const float* __restrict__ bias, int n, int rows) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n * rows) P0[i] += bias[i % n];
+}
+__global__ void rnnt_widen_kernel(const __half* __restrict__ src, float* __restrict__ dst, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = __half2float(src[i]);
+}
+
+struct GreedyArgs {
+    // per-utterance inputs/outputs
+    const float* E;        // [n_utts][Tp][JH]  encoder half of the joint, bias b1 included
+    int* tokens;           // [n_utts][Tp]
+    int* n_tokens;         // [n_utts]
+    float* logits;         // optional [n_utts][Tp][V]
+    int n_utts, Tp;
+    // prediction network (gate-interleaved packed rows u*4+g)
+    const float* P0;       // [V][4PH]  W_ih0 . emb[k] + b_ih0 + b_hh0
+    const __half* Whh0;    // [4PH][PH]
+    const __half* Wih1;    // [4PH][PH]
+    const __half* Whh1;    // [4PH][PH]
+    const float* bias1;    // [4PH]
+    // joint
+    const __half* W1p;     // [JH][PH]   prediction half of the first joint matrix
+    const __half* W2;      // [V][JH]
+    const float* b2;       // [V]
+    int PH, JH, V, blank;
+    int smem_mask;         // bit i set = matrix i (Whh0, Wih1, Whh1, W1p, W2) is staged in shared memory
+};
+
+__device__ __forceinline__ float dot_row(const __half* __restrict__ w, const __half* __restrict__ h, int K8, int lane) {
+    float acc = 0.f;
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+    const uint4* h4 = reinterpret_cast<const uint4*>(h);
+    for (int c = lane; c < K8; c += 32) acc = dot8(w4[c], h4[c], acc);
+    return acc;
+}
+
+__global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
+    const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nwarps = nthr >> 5;
+    const int PH = a.PH, JH = a.JH, V = a.V, PH8 = PH >> 3, JH8 = JH >> 3;
+    const int UP = (PH + C - 1) / C, u0 = rank * UP, nu = max(0, min(UP, PH - u0));
+    const int JP = (JH + C - 1) / C, j0 = rank * JP, nj = max(0, min(JP, JH - j0));
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* sp = smem_raw;
+    auto carve = [&](size_t bytes) {
+        unsigned char* p = sp;
+        sp += (bytes + 15) & ~size_t(15);
+        return p;
+    };
+    __half* h0buf = reinterpret_cast<__half*>(carve((size_t)2 * PH * 2));   // [2][PH]
+    __half* h1buf = reinterpret_cast<__half*>(carve((size_t)2 * PH * 2));   // [2][PH]
+    float* Pj = reinterpret_cast<float*>(carve((size_t)JH * 4));            // pred half of the joint
+    __half* zs = reinterpret_cast<__half*>(carve((size_t)JH * 2));          // relu(E + Pj), fp16 like the op's output
+    float* zrow = reinterpret_cast<float*>(carve((size_t)4 * UP * 4));      // gate pre-activations of my units
+    float* lg = reinterpret_cast<float*>(carve((size_t)(V + 1) * 4));       // logits
+    const size_t slice = (size_t)4 * UP * PH * 2;
+    // weight slices: staged in shared memory when they fit, else read in place (L2)
+    const __half* Whh0 = a.Whh0 + (size_t)u0 * 4 * PH;
+    const __half* Wih1 = a.Wih1 + (size_t)u0 * 4 * PH;
+    const __half* Whh1 = a.Whh1 + (size_t)u0 * 4 * PH;
+    const __half* W1p = a.W1p + (size_t)j0 * PH;
+    const __half* W2 = a.W2;
+    auto stage = [&](const __half* g, size_t halves, size_t cap_bytes) {
+        __half* s = reinterpret_cast<__half*>(carve(cap_bytes));
+        const uint4* g4 = reinterpret_cast<const uint4*>(g);
+        uint4* s4 = reinterpret_cast<uint4*>(s);
+        for (size_t i = tid; i < halves / 8; i += nthr) s4[i] = __ldg(g4 + i);
+        return (const __half*)s;
+    };
+    if (a.smem_mask & 1) Whh0 = stage(Whh0, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 2) Wih1 = stage(Wih1, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 4) Whh1 = stage(Whh1, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 8) W1p = stage(W1p, (size_t)nj * PH, (size_t)JP * PH * 2);
+    if (a.smem_mask & 16) W2 = stage(W2, (size_t)V * JH, (size_t)V * JH * 2);
+
+    // One evaluation of the prediction network for input token `tok`, from the state left by the previous
+    // evaluation (buffers of parity (e-1)&1), into buffers of parity e&1; then the pred half of the joint.
+    float c_l0 = 0.f, c_l1 = 0.f;  // cell states of unit u0+tid (threads tid < nu), fp32 for the whole utterance
+    auto pred_eval = [&](int tok, int e) {
+        const __half* h0prev = h0buf + (size_t)((e + 1) & 1) * PH;
+        __half* h0new_local = h0buf + (size_t)(e & 1) * PH;
+        const __half* h1prev = h1buf + (size_t)((e + 1) & 1) * PH;
+        __half* h1new_local = h1buf + (size_t)(e & 1) * PH;
+        // layer 0
+        for (int r = warp; r < 4 * nu; r += nwarps) {
+            float z = warp_sum(dot_row(Whh0 + (size_t)r * PH, h0prev, PH8, lane));
+            if (lane == 0) zrow[r] = z + a.P0[(size_t)tok * 4 * PH + (size_t)u0 * 4 + r];
+        }
+        __syncthreads();
+        if (tid < nu) {
+            const float zi = zrow[tid * 4], zf = zrow[tid * 4 + 1], zg = zrow[tid * 4 + 2], zo = zrow[tid * 4 + 3];
+            c_l0 = sigmoidf_(zf) * c_l0 + sigmoidf_(zi) * tanhf_(zg);
+            const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
+            for (int d = 0; d < C; ++d) cluster.map_shared_rank(h0new_local, d)[u0 + tid] = hh;
+        }
+        cluster.sync();
+        // layer 1
+        for (int r = warp; r < 4 * nu; r += nwarps) {
+            float z = dot_row(Wih1 + (size_t)r * PH, h0new_local, PH8, lane) +
+                      dot_row(Whh1 + (size_t)r * PH, h1prev, PH8, lane);
+            z = warp_sum(z);
+            if (lane == 0) zrow[r] = z + a.bias1[(size_t)u0 * 4 + r];
+        }
+        __syncthreads();
+        if (tid < nu) {
+            const float zi = zrow[tid * 4], zf = zrow[tid * 4 + 1], zg = zrow[tid * 4 + 2], zo = zrow[tid * 4 + 3];
+            c_l1 = sigmoidf_(zf) * c_l1 + sigmoidf_(zi) * tanhf_(zg);
+            const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
+            for (int d = 0; d < C; ++d) cluster.map_shared_rank(h1new_local, d)[u0 + tid] = hh;
+        }
+        cluster.sync();
+        // prediction half of the joint: Pj[j] = W1p[j,:] . h1
+        for (int q = warp; q < nj; q += nwarps) {
+            float v = warp_sum(dot_row(W1p + (size_t)q * PH, h1new_local, PH8, lane));
+            if (lane == 0)
+                for (int d = 0; d < C; ++d) cluster.map_shared_rank(Pj, d)[j0 + q] = v;
+        }
+        cluster.sync();
+    };
+
+    for (int utt = cluster_id; utt < a.n_utts; utt += n_clusters) {
+        const float* E = a.E + (size_t)utt * a.Tp * JH;
+        int* tokens = a.tokens + (size_t)utt * a.Tp;
+        float* logits = a.logits ? a.logits + (size_t)utt * a.Tp * V : nullptr;
+        for (int i = tid; i < 2 * PH; i += nthr) {
+            h0buf[i] = __float2half_rn(0.f);
+            h1buf[i] = __float2half_rn(0.f);
+        }
+        c_l0 = 0.f;
+        c_l1 = 0.f;
+        cluster.sync();  // staged weights and zeroed states visible; nobody still writes into my buffers
+        int e = 0, n_emit = 0;
+        pred_eval(a.blank, e++);  // start of sequence: the blank row of the embedding, zero state
+        float e_next[2] = {0.f, 0.f};  // E[t+1] for z elements tid and tid+nthr
+        if (a.Tp > 0) {
+            if (tid < JH) e_next[0] = __ldcg(E + tid);
+            if (tid + nthr < JH) e_next[1] = __ldcg(E + tid + nthr);
+        }
+        for (int t = 0; t < a.Tp; ++t) {
+            const float e_cur0 = e_next[0], e_cur1 = e_next[1];
+            if (t + 1 < a.Tp) {
+                if (tid < JH) e_next[0] = __ldcg(E + (size_t)(t + 1) * JH + tid);
+                if (tid + nthr < JH) e_next[1] = __ldcg(E + (size_t)(t + 1) * JH + tid + nthr);
+            }
+            if (tid < JH) zs[tid] = __float2half_rn(fmaxf(e_cur0 + Pj[tid], 0.f));
+            if (tid + nthr < JH) zs[tid + nthr] = __float2half_rn(fmaxf(e_cur1 + Pj[tid + nthr], 0.f));
+            __syncthreads();
+            for (int r = warp; r < V; r += nwarps) {
+                float v = warp_sum(dot_row(W2 + (size_t)r * JH, zs, JH8, lane));
+                if (lane == 0) lg[r] = v + a.b2[r];
+            }
+            __syncthreads();
+            int best = 0;
+            float bv = lg[0];
+            for (int r = 1; r < V; ++r) {
+                const float v = lg[r];
+                if (v > bv) { bv = v; best = r; }
+            }
+            if (rank == 0 && logits && tid < V) logits[(size_t)t * V + tid] = lg[tid];
+            if (best != a.blank) {
+                if (rank == 0 && tid == 0) tokens[n_emit] = best;
+                ++n_emit;
+                pred_eval(best, e++);  // commits the pending state and evaluates the new label
+            }
+        }
+        if (rank == 0 && tid == 0) a.n_tokens[utt] = n_emit;
+    }
+    cluster.sync();  // no CTA leaves while a peer may still address its shared memory
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+struct pimb200_rnnt {
+    pimb200_rnnt_config cfg;
+    int device = 0;
+    pimb200_lstm* pre = nullptr;
+    pimb200_lstm* post = nullptr;
+    __half *W1e = nullptr, *W1p = nullptr, *W2 = nullptr, *b1 = nullptr;
+    float* b2 = nullptr;
+    __half *Whh0 = nullptr, *Wih1 = nullptr, *Whh1 = nullptr;
+    float *P0 = nullptr, *bias1 = nullptr;
+    // workspace (grown on demand)
+    __half *y_pre = nullptr, *y_post = nullptr;
+    float* E = nullptr;
+    size_t cap_frames = 0;  // frames*utts capacity of the three buffers above
+    int cluster = 0;        // CTAs per cluster
+    int smem_mask = 0;
+    size_t smem_bytes = 0;
+    std::mutex mu;
+};
+
+static size_t greedy_smem(const pimb200_rnnt_config& c, int C, int mask) {
+    auto al = [](size_t b) { return (b + 15) & ~size_t(15); };
+    const int PH = c.pred_hidden, JH = c.joint_hidden, V = c.vocab;
+    const int UP = (PH + C - 1) / C, JP = (JH + C - 1) / C;
+    size_t s = al((size_t)2 * PH * 2) * 2 + al((size_t)JH * 4) + al((size_t)JH * 2) + al((size_t)4 * UP * 4) +
+               al((size_t)(V + 1) * 4);
+    const size_t slice = al((size_t)4 * UP * PH * 2);
+    if (mask & 1) s += slice;
+    if (mask & 2) s += slice;
+    if (mask & 4) s += slice;
+    if (mask & 8) s += al((size_t)JP * PH * 2);
+    if (mask & 16) s += al((size_t)V * JH * 2);
+    return s;
+}
+
+extern "C" int pimb200_rnnt_destroy(pimb200_rnnt* h) {
+    if (!h) return PIMB200_OK;
+    cudaSetDevice(h->device);
+    pimb200_lstm_destroy(h->pre);
+    pimb200_lstm_destroy(h->post);
+    void* ptrs[] = {h->W1e, h->W1p, h->W2, h->b1, h->b2, h->Whh0, h->Wih1, h->Whh1, h->P0, h->bias1,
+                    h->y_pre, h->y_post, h->E};
+    for (void* p : ptrs) cudaFree(p);
+    delete h;
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200_rnnt_weights* w,
+                                   pimb200_rnnt** out) {
+    if (!cfg || !w || !out) return PIMB200_ERR_BAD_ARG;
+    const pimb200_rnnt_config c = *cfg;
+    if (c.feat_dim <= 0 || c.enc_hidden <= 0 || c.pre_layers <= 0 || c.post_layers <= 0 || c.stack_factor <= 0 ||
+        c.pred_hidden <= 0 || c.joint_hidden <= 0 || c.vocab <= 1 || c.blank < 0 || c.blank >= c.vocab)
+        return PIMB200_ERR_BAD_ARG;
+    if (!w->pre_params || !w->post_params || !w->pred_params || !w->embedding || !w->joint_w1 || !w->joint_b1 ||
+        !w->joint_w2 || !w->joint_b2)
+        return PIMB200_ERR_BAD_ARG;
+    if (c.pred_layers != 2 || c.max_symbols != 1 || w->n_pred != 8) return PIMB200_ERR_UNSUPPORTED;
+    if (c.pred_hidden % 8 || c.joint_hidden % 8 || c.joint_hidden > 1024 || c.vocab > 512) return PIMB200_ERR_UNSUPPORTED;
+    pimb200_rnnt* h = new pimb200_rnnt();
+    h->cfg = c;
+    auto fail = [&](int code) { pimb200_rnnt_destroy(h); return code; };
+    if (cudaGetDevice(&h->device) != cudaSuccess) return fail(PIMB200_ERR_LAUNCH);
+    int rc;
+    if ((rc = pimb200_lstm_create(w->pre_params, w->n_pre, c.pre_layers, 0, c.feat_dim, c.enc_hidden, 1, &h->pre)))
+        return fail(rc);
+    if ((rc = pimb200_lstm_create(w->post_params, w->n_post, c.post_layers, 0, c.stack_factor * c.enc_hidden,
+                                  c.enc_hidden, 1, &h->post)))
+        return fail(rc);
+    const int EH = c.enc_hidden, PH = c.pred_hidden, JH = c.joint_hidden, V = c.vocab;
+#define RNNT_ALLOC(ptr, bytes)                                                      \
+    if (cudaMalloc(&(ptr), (bytes)) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY)
+    RNNT_ALLOC(h->W1e, (size_t)JH * EH * 2);
+    RNNT_ALLOC(h->W1p, (size_t)JH * PH * 2);
+    RNNT_ALLOC(h->W2, (size_t)V * JH * 2);
+    RNNT_ALLOC(h->b1, (size_t)JH * 2);
+    RNNT_ALLOC(h->b2, (size_t)V * 4);
+    RNNT_ALLOC(h->Whh0, (size_t)4 * PH * PH * 2);
+    RNNT_ALLOC(h->Wih1, (size_t)4 * PH * PH * 2);
+    RNNT_ALLOC(h->Whh1, (size_t)4 * PH * PH * 2);
+    RNNT_ALLOC(h->P0, (size_t)V * 4 * PH * 4);
+    RNNT_ALLOC(h->bias1, (size_t)4 * PH * 4);
+    __half* wih0_packed = nullptr;
+    float* bias0 = nullptr;
+    RNNT_ALLOC(wih0_packed, (size_t)4 * PH * PH * 2);
+    if (cudaMalloc(&bias0, (size_t)4 * PH * 4) != cudaSuccess) { cudaFree(wih0_packed); return fail(PIMB200_ERR_NO_MEMORY); }
+#undef RNNT_ALLOC
+    const size_t w1_pitch = (size_t)(EH + PH) * 2;
+    cudaMemcpy2D(h->W1e, (size_t)EH * 2, w->joint_w1, w1_pitch, (size_t)EH * 2, JH, cudaMemcpyDeviceToDevice);
+    cudaMemcpy2D(h->W1p, (size_t)PH * 2, static_cast<const __half*>(w->joint_w1) + EH, w1_pitch, (size_t)PH * 2, JH,
+                 cudaMemcpyDeviceToDevice);
+    cudaMemcpy(h->W2, w->joint_w2, (size_t)V * JH * 2, cudaMemcpyDeviceToDevice);
+    cudaMemcpy(h->b1, w->joint_b1, (size_t)JH * 2, cudaMemcpyDeviceToDevice);
+    rnnt_widen_kernel<<<ceil_div(V, 256), 256>>>(static_cast<const __half*>(w->joint_b2), h->b2, V);
+    const void* const* pp = w->pred_params;  // (w_ih0, w_hh0, b_ih0, b_hh0, w_ih1, w_hh1, b_ih1, b_hh1)
+    lstm_pack_matrix(static_cast<const __half*>(pp[0]), wih0_packed, PH, PH, nullptr);
+    lstm_pack_matrix(static_cast<const __half*>(pp[1]), h->Whh0, PH, PH, nullptr);
+    lstm_pack_matrix(static_cast<const __half*>(pp[4]), h->Wih1, PH, PH, nullptr);
+    lstm_pack_matrix(static_cast<const __half*>(pp[5]), h->Whh1, PH, PH, nullptr);
+    lstm_pack_bias(static_cast<const __half*>(pp[2]), static_cast<const __half*>(pp[3]), bias0, PH, nullptr);
+    lstm_pack_bias(static_cast<const __half*>(pp[6]), static_cast<const __half*>(pp[7]), h->bias1, PH, nullptr);
+    // P0[k] = W_ih0 . emb[k] + b_ih0 + b_hh0: one GEMM over the V embedding rows, then the bias on every row
+    rc = launch_gemm_wx(wih0_packed, static_cast<const __half*>(w->embedding), nullptr, h->P0, 4 * PH, PH, V, PH,
+                        4 * PH, PIMB200_ACT_NONE, 1, nullptr);
+    rnnt_add_bias_rows_kernel<<<ceil_div(4 * PH * V, 256), 256>>>(h->P0, bias0, 4 * PH, V);
+    cudaError_t e = cudaDeviceSynchronize();
+    cudaFree(wih0_packed);
+    cudaFree(bias0);
+    if (rc != PIMB200_OK) return fail(rc);
+    if (e != cudaSuccess) return fail(cuda_status(e));
+
+    // cluster size and what fits in shared memory
+    int max_smem = 0;
+    cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, h->device);
+    cudaFuncSetAttribute(rnnt_greedy_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cudaFuncSetAttribute(rnnt_greedy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    const int candidates[2] = {16, 8};
+    for (int ci = 0; ci < 2 && h->cluster == 0; ++ci) {
+        const int C = candidates[ci];
+        int mask = 0;
+        // stage in priority order while the budget lasts: W2 (read every frame) first, then the pred matrices
+        const int order[5] = {16, 1, 2, 4, 8};
+        for (int k = 0; k < 5; ++k)
+            if (greedy_smem(c, C, mask | order[k]) <= (size_t)max_smem) mask |= order[k];
+        const size_t smem = greedy_smem(c, C, mask);
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3(C);
+        lc.blockDim = dim3(512);
+        lc.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        lc.attrs = at;
+        lc.numAttrs = 1;
+        int n_clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, rnnt_greedy_kernel, &lc) == cudaSuccess && n_clusters >= 1) {
+            h->cluster = C;
+            h->smem_mask = mask;
+            h->smem_bytes = smem;
+        } else {
+            cudaGetLastError();
+        }
+    }
+    if (h->cluster == 0) return fail(PIMB200_ERR_UNSUPPORTED);
+    *out = h;
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t* smem_bytes) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    if (cluster_size) *cluster_size = h->cluster;
+    if (smem_mask) *smem_mask = h->smem_mask;
+    if (smem_bytes) *smem_bytes = h->smem_bytes;
+    return PIMB200_OK;
+}
+
+template <typename T>
+static int regrow(T** p, size_t elems) {
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    PIMB200_CUDA_TRY(cudaMalloc(p, elems * sizeof(T)));
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, int n_utts, int32_t* tokens,
+                                   int32_t* n_tokens, float* logits, void* stream) {
+    if (!h || !feats || !tokens || !n_tokens || T <= 0 || n_utts <= 0) return PIMB200_ERR_BAD_ARG;
+    const pimb200_rnnt_config& c = h->cfg;
+    const int Tp = T / c.stack_factor;
+    if (Tp <= 0) return PIMB200_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int EH = c.enc_hidden, JH = c.joint_hidden;
+    const size_t need = (size_t)n_utts * T;
+    if (need > h->cap_frames) {
+        PIMB200_CUDA_TRY(cudaDeviceSynchronize());
+        int rc;
+        if ((rc = regrow(&h->y_pre, need * EH))) return rc;
+        if ((rc = regrow(&h->y_post, need * EH))) return rc;   // Tp*EH used
+        if ((rc = regrow(&h->E, need * JH))) return rc;        // Tp*JH used
+        h->cap_frames = need;
+    }
+    const __half* x = static_cast<const __half*>(feats);
+    for (int u = 0; u < n_utts; ++u) {
+        __half* y1 = h->y_pre + (size_t)u * T * EH;
+        __half* y2 = h->y_post + (size_t)u * Tp * EH;
+        int rc = pimb200_lstm_forward(h->pre, x + (size_t)u * T * c.feat_dim, T, 1, nullptr, nullptr, y1, nullptr,
+                                      nullptr, 0, stream);
+        if (rc != PIMB200_OK) return rc;
+        // time stacking: `stack` consecutive frames side by side is a reinterpretation of the same memory
+        rc = pimb200_lstm_forward(h->post, y1, Tp, 1, nullptr, nullptr, y2, nullptr, nullptr, 0, stream);
+        if (rc != PIMB200_OK) return rc;
+    }
+    // encoder half of the joint for every frame of every utterance: one dense GEMM (y_post is contiguous over utts
+    // only when T is a multiple of stack; handle the general case per utterance)
+    if (T % c.stack_factor == 0 || n_utts == 1) {
+        int rc = launch_gemm_wx(h->W1e, h->y_post, h->b1, h->E, JH, EH, n_utts * Tp, EH, JH, PIMB200_ACT_NONE, 1, st);
+        if (rc != PIMB200_OK) return rc;
+    } else {
+        for (int u = 0; u < n_utts; ++u) {
+            int rc = launch_gemm_wx(h->W1e, h->y_post + (size_t)u * Tp * EH, h->b1, h->E + (size_t)u * Tp * JH, JH,
+                                    EH, Tp, EH, JH, PIMB200_ACT_NONE, 1, st);
+            if (rc != PIMB200_OK) return rc;
+        }
+    }
+    GreedyArgs a;
+    a.E = h->E; a.tokens = tokens; a.n_tokens = n_tokens; a.logits = logits; a.n_utts = n_utts; a.Tp = Tp;
+    a.P0 = h->P0; a.Whh0 = h->Whh0; a.Wih1 = h->Wih1; a.Whh1 = h->Whh1; a.bias1 = h->bias1;
+    a.W1p = h->W1p; a.W2 = h->W2; a.b2 = h->b2;
+    a.PH = c.pred_hidden; a.JH = JH; a.V = c.vocab; a.blank = c.blank; a.smem_mask = h->smem_mask;
+    const int C = h->cluster;
+    int max_clusters = kNumSmB200 / C;
+    if (max_clusters < 1) max_clusters = 1;
+    const int n_clusters = n_utts < max_clusters ? n_utts : max_clusters;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(C * n_clusters);
+    lc.blockDim = dim3(512);
+    lc.dynamicSmemBytes = h->smem_bytes;
+    lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, rnnt_greedy_kernel, a));
+    return PIMB200_OK;
+}

@@ -1,0 +1,79 @@
+"""Host-side handle of the device-resident RNN-T greedy decoder (``include/pimb200_rnnt.h``)."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import check
+
+
+def _arr(ts: Sequence[torch.Tensor]):
+    return (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+class RnntDecoder:
+    """Packs the model once; ``decode`` runs encoder + greedy loop on the device, no host round trips.
+
+    ``cfg`` needs the attributes of ``struct pimb200_rnnt_config``; the weight tensors are CUDA fp16,
+    laid out as the TorchScript constants are (at::lstm flat lists, Linear weight/bias, Embedding weight).
+    """
+
+    def __init__(self, cfg, pre: Sequence[torch.Tensor], post: Sequence[torch.Tensor], embedding: torch.Tensor,
+                 pred: Sequence[torch.Tensor], w1: torch.Tensor, b1: torch.Tensor, w2: torch.Tensor,
+                 b2: torch.Tensor):
+        for t in [*pre, *post, embedding, *pred, w1, b1, w2, b2]:
+            if not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous():
+                raise TypeError("RNN-T weights must be contiguous CUDA fp16 tensors")
+        self.cfg = cfg
+        self.device = w1.device
+        c = _lib.RnntConfigC(*[int(getattr(cfg, n)) for n, _ in _lib.RnntConfigC._fields_])
+        keep = (_arr(pre), _arr(post), _arr(pred))
+        w = _lib.RnntWeightsC(keep[0], len(pre), keep[1], len(post), embedding.data_ptr(), keep[2], len(pred),
+                              w1.data_ptr(), b1.data_ptr(), w2.data_ptr(), b2.data_ptr())
+        h = C.c_void_p()
+        check(_lib.lib().pimb200_rnnt_create(C.byref(c), C.byref(w), C.byref(h)), "rnnt_create")
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().pimb200_rnnt_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def info(self) -> dict:
+        cs, mask, sm = C.c_int(), C.c_int(), C.c_size_t()
+        check(_lib.lib().pimb200_rnnt_info(self._h, C.byref(cs), C.byref(mask), C.byref(sm)), "rnnt_info")
+        return {"cluster_size": cs.value, "smem_mask": mask.value, "smem_bytes": sm.value}
+
+    def decode_into(self, feats: torch.Tensor, tokens: torch.Tensor, n_tokens: torch.Tensor,
+                    logits: Optional[torch.Tensor] = None) -> None:
+        """Asynchronous decode of feats [n_utts, T, feat_dim] into preallocated device outputs."""
+        n_utts, T, _ = feats.shape
+        check(_lib.lib().pimb200_rnnt_decode(self._h, feats.data_ptr(), T, n_utts, tokens.data_ptr(),
+                                             n_tokens.data_ptr(), None if logits is None else logits.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream), "rnnt_decode")
+
+    def decode(self, feats: torch.Tensor, want_logits: bool = False):
+        """feats [n_utts, T, feat_dim] (or [T, feat_dim]) CUDA fp16 -> list of token lists (+ logits)."""
+        if feats.dim() == 2:
+            feats = feats.unsqueeze(0)
+        feats = feats.contiguous()
+        n_utts, T, _ = feats.shape
+        Tp = T // self.cfg.stack_factor
+        tokens = torch.zeros(n_utts, Tp, dtype=torch.int32, device=feats.device)
+        n_tokens = torch.zeros(n_utts, dtype=torch.int32, device=feats.device)
+        logits = torch.empty(n_utts, Tp, self.cfg.vocab, dtype=torch.float32, device=feats.device) if want_logits \
+            else None
+        self.decode_into(feats, tokens, n_tokens, logits)
+        n = n_tokens.cpu().tolist()
+        tk = tokens.cpu()
+        out = [tk[u, : n[u]].tolist() for u in range(n_utts)]
+        return (out, logits) if want_logits else out

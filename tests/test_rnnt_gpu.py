@@ -1,0 +1,89 @@
+"""GPU parity of the device-resident RNN-T greedy decode against the libtorch-CPU and C oracles."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle as co
+from oracle import torch_oracle as to
+from tests.util import CONTRACT_ATOL, CONTRACT_RTOL, assert_close
+
+pytestmark = pytest.mark.gpu
+MARGIN = 1e-2  # token ids must match wherever the oracle's top-2 logit margin exceeds this
+
+
+def _decoder(cfg, w):
+    from pimaicompiler_b200.rnnt import RnntDecoder
+    d = lambda t: t.to(torch.float16).cuda().contiguous()
+    return RnntDecoder(cfg, [d(p) for p in w.pre], [d(p) for p in w.post], d(w.embedding), [d(p) for p in w.pred],
+                       d(w.w1), d(w.b1), d(w.w2), d(w.b2))
+
+
+def _check_utterance(cfg, w, feats, got_tokens, got_logits, oracle):
+    """Follow-mode check: the oracle replays the GPU's decisions, so every frame is comparable; the GPU's
+    decision must equal the oracle's argmax at every frame whose oracle margin exceeds MARGIN."""
+    Tp = got_logits.shape[0]
+    got_choice = got_logits.argmax(1)
+    # the GPU's per-frame decisions, reconstructed from its logits (it emits iff argmax != blank)
+    forced = got_choice.tolist()
+    emitted = [k for k in forced if k != cfg.blank]
+    assert emitted == got_tokens, "token list is not the sequence of non-blank argmaxes of the returned logits"
+    _, ref_logits, ref_choice = oracle(w, feats, cfg, forced)
+    ref_logits = np.asarray(ref_logits)
+    assert_close(got_logits, ref_logits, CONTRACT_ATOL, CONTRACT_RTOL, "joint logits")
+    srt = np.sort(ref_logits, axis=1)
+    margin = srt[:, -1] - srt[:, -2]
+    decided = margin > MARGIN
+    assert (np.asarray(ref_choice)[decided] == np.asarray(forced)[decided]).all(), "token mismatch at a decided frame"
+    err = float(np.abs(got_logits - ref_logits).max())
+    return int(decided.sum()), Tp, err
+
+
+@pytest.mark.parametrize("seed,gain,logit_gain", [(0, 1.0, 1.0), (1, 2.0, 6.0), (2, 3.0, 10.0)])
+def test_rnnt_small_model_vs_c_oracle(seed, gain, logit_gain):
+    cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=32, joint_hidden=48, vocab=11, blank=10)
+    w = to.make_rnnt_weights(cfg, seed=seed, gain=gain, logit_gain=logit_gain)
+    dec = _decoder(cfg, w)
+    for T in (2, 9, 40, 61):
+        feats = to.make_features(T, cfg, 100 + T)
+        toks, logits = dec.decode(feats.to(torch.float16).cuda(), want_logits=True)
+        _check_utterance(cfg, w, feats, toks[0], logits[0].cpu().numpy(), co.rnnt_greedy)
+
+
+def test_rnnt_baseline_config_vs_libtorch():
+    # the benchmark's architecture, a 2 s utterance (the oracle stays within seconds), mixed decisions
+    cfg = to.RnntConfig()
+    w = to.make_rnnt_weights(cfg, seed=0, gain=1.0, logit_gain=1.0)
+    dec = _decoder(cfg, w)
+    info = dec.info()
+    print("greedy kernel:", info)
+    feats = to.make_features(200, cfg, 7)
+    toks, logits = dec.decode(feats.to(torch.float16).cuda(), want_logits=True)
+    nd, Tp, err = _check_utterance(cfg, w, feats, toks[0], logits[0].cpu().numpy(), to.rnnt_greedy)
+    print(f"decided frames {nd}/{Tp}, max logit err {err:.2e}")
+    # free-running oracle: identical transcript when every frame is decided
+    ref_tokens, ref_logits, _ = to.rnnt_greedy(w, feats, cfg)
+    srt = np.sort(ref_logits.numpy(), axis=1)
+    if ((srt[:, -1] - srt[:, -2]) > MARGIN).all():
+        assert toks[0] == ref_tokens
+
+
+def test_rnnt_baseline_config_blank_mix():
+    cfg = to.RnntConfig()
+    w = to.make_rnnt_weights(cfg, seed=5, gain=2.0, logit_gain=8.0)
+    dec = _decoder(cfg, w)
+    feats = to.make_features(120, cfg, 9)
+    toks, logits = dec.decode(feats.to(torch.float16).cuda(), want_logits=True)
+    _check_utterance(cfg, w, feats, toks[0], logits[0].cpu().numpy(), to.rnnt_greedy)
+
+
+def test_rnnt_batch_of_utterances_matches_single():
+    cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=32, joint_hidden=48, vocab=11, blank=10)
+    w = to.make_rnnt_weights(cfg, seed=4, gain=2.0, logit_gain=6.0)
+    dec = _decoder(cfg, w)
+    n, T = 13, 30   # more utterances than clusters fit on the device
+    feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
+    toks, logits = dec.decode(feats, want_logits=True)
+    for i in range(n):
+        ti, li = dec.decode(feats[i], want_logits=True)
+        assert ti[0] == toks[i]
+        assert torch.equal(li[0], logits[i])
