@@ -139,6 +139,19 @@ int pimb200_lstm_forward_packed(pimb200_lstm* h, const void* data, const int64_t
  * stream; returns PIMB200_ERR_TIMEOUT when a bounded wait inside the persistent kernel gave up. */
 int pimb200_lstm_last_status(pimb200_lstm* h);
 
+/* Timing hook: while enabled, every recurrence launch sequence (all T steps of one layer and direction)
+ * is bracketed by CUDA events on the launching stream.  profile_read waits for those events and returns
+ * their summed device time, how many recurrences ran and their algorithmic W_hh bytes
+ * (T * 4H*H * 2 each), then clears the record.  Stands where the reference wraps each op in
+ * PROFILE_SCOPE + a device-wide sync (runtime/source/executor/stream_executor.cpp:204-258). */
+int pimb200_lstm_profile_enable(pimb200_lstm* h, int enable);
+int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrences, double* bytes);
+
+/* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
+ * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are
+ * inside MIOpen. */
+int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit);
+
 #ifdef __cplusplus
 }
 #endif

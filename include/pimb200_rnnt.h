@@ -59,6 +59,10 @@ int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, int n_utts, i
  * memory (bit 0..4 = W_hh0, W_ih1, W_hh1, joint W1 pred half, joint W2) and the dynamic shared memory per CTA. */
 int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t* smem_bytes);
 
+/* pimb200_lstm_profile_enable / _read applied to both encoder stacks of the handle. */
+int pimb200_rnnt_profile_enable(pimb200_rnnt* h, int enable);
+int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long* recurrences, double* bytes);
+
 #ifdef __cplusplus
 }
 #endif

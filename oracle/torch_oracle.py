@@ -3,79 +3,16 @@
 97, 304-307, 328-344, 362), driven from Python, fp32, on the host cores.
 
 Test infrastructure and the benchmark's CPU arm only; the product package never imports this.
-Also holds the seeded synthetic RNN-T model (random-init weights of the benchmark's architecture;
-the real checkpoints and speech corpora are not available offline).
+The seeded synthetic RNN-T model it runs comes from pimaicompiler_b200.synthetic.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
 from typing import List, Optional
 
 import torch
 
 
-@dataclass
-class RnntConfig:
-    feat_dim: int = 240
-    enc_hidden: int = 1024
-    pre_layers: int = 2
-    post_layers: int = 3
-    stack_factor: int = 2
-    pred_hidden: int = 320
-    pred_layers: int = 2
-    joint_hidden: int = 512
-    vocab: int = 29
-    blank: int = 28
-    max_symbols: int = 1
-
-
-@dataclass
-class RnntWeights:
-    """fp32 CPU tensors whose values are fp16-representable (both sides of a parity test use them)."""
-    pre: List[torch.Tensor] = field(default_factory=list)
-    post: List[torch.Tensor] = field(default_factory=list)
-    embedding: Optional[torch.Tensor] = None
-    pred: List[torch.Tensor] = field(default_factory=list)
-    w1: Optional[torch.Tensor] = None
-    b1: Optional[torch.Tensor] = None
-    w2: Optional[torch.Tensor] = None
-    b2: Optional[torch.Tensor] = None
-
-
-def _u(shape, fan_in, gen, gain=1.0):
-    k = gain / fan_in ** 0.5
-    return ((torch.rand(*shape, generator=gen) * 2 - 1) * k).to(torch.float16).to(torch.float32)
-
-
-def _lstm_params(L, I, H, gen, gain=1.0):
-    ps = []
-    for l in range(L):
-        Il = I if l == 0 else H
-        ps += [_u((4 * H, Il), H, gen, gain), _u((4 * H, H), H, gen, gain), _u((4 * H,), H, gen, gain),
-               _u((4 * H,), H, gen, gain)]
-    return ps
-
-
-def make_rnnt_weights(cfg: RnntConfig, seed: int = 0, gain: float = 1.0, logit_gain: float = 1.0) -> RnntWeights:
-    """U(-1/sqrt(fan_in), 1/sqrt(fan_in)) init (PyTorch's default for LSTM/Linear), N(0,1) embedding.
-    `gain`/`logit_gain` > 1 widen the distributions so tests can get a mix of blank and label decisions."""
-    g = torch.Generator().manual_seed(seed)
-    w = RnntWeights()
-    w.pre = _lstm_params(cfg.pre_layers, cfg.feat_dim, cfg.enc_hidden, g, gain)
-    w.post = _lstm_params(cfg.post_layers, cfg.stack_factor * cfg.enc_hidden, cfg.enc_hidden, g, gain)
-    w.embedding = torch.randn(cfg.vocab, cfg.pred_hidden, generator=g).to(torch.float16).to(torch.float32)
-    w.pred = _lstm_params(cfg.pred_layers, cfg.pred_hidden, cfg.pred_hidden, g, gain)
-    fan1 = cfg.enc_hidden + cfg.pred_hidden
-    w.w1 = _u((cfg.joint_hidden, fan1), fan1, g, gain)
-    w.b1 = _u((cfg.joint_hidden,), fan1, g, gain)
-    w.w2 = _u((cfg.vocab, cfg.joint_hidden), cfg.joint_hidden, g, gain * logit_gain)
-    w.b2 = _u((cfg.vocab,), cfg.joint_hidden, g, gain * logit_gain)
-    return w
-
-
-def make_features(T: int, cfg: RnntConfig, seed: int) -> torch.Tensor:
-    g = torch.Generator().manual_seed(seed)
-    return torch.randn(T, cfg.feat_dim, generator=g).to(torch.float16).to(torch.float32)
+from pimaicompiler_b200.synthetic import RnntConfig, RnntWeights, make_features, make_rnnt_weights  # noqa: F401,E402
 
 
 def rnnt_encoder(w: RnntWeights, feats: torch.Tensor, cfg: RnntConfig) -> torch.Tensor:

@@ -39,6 +39,11 @@ SIGNATURES = {
     "pimb200_lstm_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "pimb200_lstm_forward_packed": (_i, [_vp, _vp, C.POINTER(C.c_int64), _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "pimb200_lstm_last_status": (_i, [_vp]),
+    "pimb200_lstm_profile_enable": (_i, [_vp, _i]),
+    "pimb200_lstm_profile_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_long), C.POINTER(C.c_double)]),
+    "pimb200_lstm_set_poll_limit": (_i, [_vp, _i]),
+    "pimb200_rnnt_profile_enable": (_i, [_vp, _i]),
+    "pimb200_rnnt_profile_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_long), C.POINTER(C.c_double)]),
     "pimb200_rnnt_create": (_i, [_vp, _vp, C.POINTER(_vp)]),
     "pimb200_rnnt_destroy": (_i, [_vp]),
     "pimb200_rnnt_decode": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp]),

@@ -346,8 +346,22 @@ struct pimb200_lstm {
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
+    // optional timing of the recurrence launches (CUDA events on the launching stream)
+    bool prof = false;
+    std::vector<cudaEvent_t> prof_ev;   // pairs: begin, end
+    size_t prof_used = 0;
+    double prof_bytes = 0.0;            // algorithmic W_hh bytes of the timed launches
     std::mutex mu;
 };
+
+static void prof_mark(pimb200_lstm* h, cudaStream_t st) {
+    if (h->prof_used == h->prof_ev.size()) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) return;
+        h->prof_ev.push_back(e);
+    }
+    cudaEventRecord(h->prof_ev[h->prof_used++], st);
+}
 
 static int in_size(const pimb200_lstm* h, int l) { return l == 0 ? h->I : h->D * h->H; }
 
@@ -363,6 +377,7 @@ extern "C" int pimb200_lstm_destroy(pimb200_lstm* h) {
     cudaFree(h->cstate);
     cudaFree(h->xchg);
     cudaFree(h->d_status);
+    for (auto e : h->prof_ev) cudaEventDestroy(e);
     delete h;
     return PIMB200_OK;
 }
@@ -422,6 +437,35 @@ extern "C" int pimb200_lstm_set_variant(pimb200_lstm* h, int variant) {
 extern "C" int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit) {
     if (!h || limit <= 0) return PIMB200_ERR_BAD_ARG;
     h->poll_limit = limit;
+    return PIMB200_OK;
+}
+
+// Timing hook used by the benchmark: when enabled, every recurrence (all T steps of one layer/direction) is
+// bracketed by CUDA events on the launching stream.  read() synchronises those events and returns the summed
+// device time, the number of recurrences and their algorithmic W_hh bytes (T * 4H*H * 2 each), then clears.
+extern "C" int pimb200_lstm_profile_enable(pimb200_lstm* h, int enable) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lk(h->mu);
+    h->prof = enable != 0;
+    h->prof_used = 0;
+    h->prof_bytes = 0.0;
+    return PIMB200_OK;
+}
+extern "C" int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrences, double* bytes) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> lk(h->mu);
+    double ms = 0.0;
+    for (size_t i = 0; i + 1 < h->prof_used; i += 2) {
+        PIMB200_CUDA_TRY(cudaEventSynchronize(h->prof_ev[i + 1]));
+        float t = 0.f;
+        PIMB200_CUDA_TRY(cudaEventElapsedTime(&t, h->prof_ev[i], h->prof_ev[i + 1]));
+        ms += t;
+    }
+    if (total_ms) *total_ms = ms;
+    if (recurrences) *recurrences = (long)(h->prof_used / 2);
+    if (bytes) *bytes = h->prof_bytes;
+    h->prof_used = 0;
+    h->prof_bytes = 0.0;
     return PIMB200_OK;
 }
 
@@ -496,8 +540,13 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         PIMB200_CUDA_TRY(cudaFuncSetAttribute(lstm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               (int)pp.smem));
         void* kargs[] = {&a};
+        if (h->prof) prof_mark(h, st);
         PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)lstm_persistent_kernel, dim3(pp.ncta),
                                                      dim3(pp.threads), kargs, pp.smem, st));
+        if (h->prof) {
+            prof_mark(h, st);
+            h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
+        }
         return PIMB200_OK;
     }
     // streamed
@@ -506,6 +555,7 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     lstm_init_c_kernel<<<ceil_div(B * H, 256), 256, 0, st>>>(h->cstate, c0, B * H);
     const bool vec = (H % 8 == 0) && aligned16(h0 ? h0 : h->w_hh[ld]) && aligned16(y) && (y_bstride % 8 == 0) &&
                      (y_tstride % 8 == 0);
+    if (h->prof) prof_mark(h, st);
     for (int s = 0; s < T; ++s) {
         const int t = reverse ? T - 1 - s : s;
         const int tp = reverse ? t + 1 : t - 1;  // timestep that produced h_prev
@@ -541,6 +591,10 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
             if (a.B == 1) lstm_step_kernel<1, false><<<grid, 256, 0, st>>>(a);
             else lstm_step_kernel<4, false><<<grid, 256, 0, st>>>(a);
         }
+    }
+    if (h->prof) {
+        prof_mark(h, st);
+        h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
     }
     return launch_status();
 }

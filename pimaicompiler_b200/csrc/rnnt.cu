@@ -361,6 +361,28 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
     return PIMB200_OK;
 }
 
+extern "C" int pimb200_lstm_profile_enable(pimb200_lstm* h, int enable);
+extern "C" int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrences, double* bytes);
+
+extern "C" int pimb200_rnnt_profile_enable(pimb200_rnnt* h, int enable) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    pimb200_lstm_profile_enable(h->pre, enable);
+    return pimb200_lstm_profile_enable(h->post, enable);
+}
+extern "C" int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long* recurrences, double* bytes) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    double ms[2] = {0, 0}, by[2] = {0, 0};
+    long n[2] = {0, 0};
+    int rc = pimb200_lstm_profile_read(h->pre, &ms[0], &n[0], &by[0]);
+    if (rc != PIMB200_OK) return rc;
+    rc = pimb200_lstm_profile_read(h->post, &ms[1], &n[1], &by[1]);
+    if (rc != PIMB200_OK) return rc;
+    if (total_ms) *total_ms = ms[0] + ms[1];
+    if (recurrences) *recurrences = n[0] + n[1];
+    if (bytes) *bytes = by[0] + by[1];
+    return PIMB200_OK;
+}
+
 extern "C" int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t* smem_bytes) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     if (cluster_size) *cluster_size = h->cluster;

@@ -53,6 +53,15 @@ class RnntDecoder:
         check(_lib.lib().pimb200_rnnt_info(self._h, C.byref(cs), C.byref(mask), C.byref(sm)), "rnnt_info")
         return {"cluster_size": cs.value, "smem_mask": mask.value, "smem_bytes": sm.value}
 
+    def profile(self, enable: bool) -> None:
+        check(_lib.lib().pimb200_rnnt_profile_enable(self._h, 1 if enable else 0), "rnnt_profile_enable")
+
+    def profile_read(self) -> dict:
+        ms, n, by = C.c_double(), C.c_long(), C.c_double()
+        check(_lib.lib().pimb200_rnnt_profile_read(self._h, C.byref(ms), C.byref(n), C.byref(by)),
+              "rnnt_profile_read")
+        return {"ms": ms.value, "recurrences": n.value, "bytes": by.value}
+
     def decode_into(self, feats: torch.Tensor, tokens: torch.Tensor, n_tokens: torch.Tensor,
                     logits: Optional[torch.Tensor] = None) -> None:
         """Asynchronous decode of feats [n_utts, T, feat_dim] into preallocated device outputs."""
