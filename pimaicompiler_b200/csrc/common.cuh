@@ -89,10 +89,12 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// exp through the special-function unit, then an IEEE-rounded reciprocal: abs error ~1e-7, and no
+// division subroutine on the recurrence's critical path
+__device__ __forceinline__ float sigmoidf_(float x) { return __frcp_rn(1.0f + __expf(-x)); }
 __device__ __forceinline__ float tanhf_(float x) {
-    // tanh(x) = 2*sigmoid(2x) - 1, accurate to ~1e-6 abs with the fast exponential
-    return 2.0f / (1.0f + __expf(-2.0f * x)) - 1.0f;
+    // tanh(x) = 2*sigmoid(2x) - 1
+    return fmaf(2.0f, __frcp_rn(1.0f + __expf(-2.0f * x)), -1.0f);
 }
 
 }  // namespace pimb200

@@ -172,19 +172,30 @@ __global__ void lstm_init_c_kernel(float* __restrict__ c, const __half* __restri
 
 // ---------------------------------------------------------------------------------------------
 // persistent weight-stationary recurrence (B == 1)
+//
+// Grid: one CTA per SM (cooperative launch, so all CTAs are co-resident).  CTA c owns U = ceil(H/#SM) <= 7
+// hidden units = 4U gate rows of W_hh, kept in shared memory for all T steps (rows padded to 32 = two
+// m16 tiles; row pitch H+8 halves so ldmatrix is bank-conflict free).
+// Per step:
+//   1. z = W_slice[32 x H] . h[H]  on the tensor cores: mma.sync m16n8k16, fp32 accumulate; h sits in
+//      column 0 of the B operand (columns 1..7 are zero).  The 8 warps split K, partial sums meet in
+//      shared memory.
+//   2. warp 0 finishes the 4U sums, adds the hoisted input projection and bias, runs the gate math,
+//      keeps c in fp32 registers, and publishes the CTA's U new hidden values as ONE 16-byte word
+//      {7 x fp16, 16-bit step tag} with a single-copy-atomic st.relaxed.gpu.b128 into every replica of
+//      the exchange buffer.
+//   3. thread j polls word j of this CTA's replica until its tag is the current step's (data and flag
+//      arrive together: one L2 round trip, no separate barrier), and scatters the 7 values into the next
+//      step's h vector in shared memory.
+// Every wait is bounded: after poll_limit polls the CTA records PIMB200_ERR_TIMEOUT in the status word
+// and leaves; the others see the status (or run out themselves) and leave too.
 // ---------------------------------------------------------------------------------------------
-constexpr int kPersistMaxWordsPerThread = 8;
 constexpr int kPersistPollLimit = 1 << 21;  // bounded wait: ~seconds, then the kernel gives up
-
-__device__ __forceinline__ void ll_store(unsigned long long* p, uint32_t data, uint32_t tag) {
-    const unsigned long long v = ((unsigned long long)tag << 32) | data;
-    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long ll_load(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
+constexpr int kXchgCopies = 16;             // replicas of the hidden-state exchange buffer
+constexpr int kXchgWords = 160;             // 16-byte words per replica and parity (>= CTAs in the grid)
+constexpr int kPersistThreads = 256;
+constexpr int kPersistRows = 32;            // padded gate rows per CTA
+constexpr int kUnitsPerWord = 7;
 
 struct PersistArgs {
     const __half* Whh;      // packed [4H, H]
@@ -197,111 +208,179 @@ struct PersistArgs {
     long y_tstride;
     __half* hn;             // optional [H]
     __half* cn;             // optional [H]
-    unsigned long long* xchg;  // [2][H] exchange words
-    uint32_t tag_base;      // tag of step s output = tag_base + s + 1
+    uint4* xchg;            // [copies][2][kXchgWords] exchange words
+    int copies;
+    uint32_t tag_base;      // tag of step s output = (tag_base + s + 1) & 0xffff
     int* status;            // device status word, set to PIMB200_ERR_TIMEOUT when a wait runs out
     int H, T, U;            // U = hidden units per CTA
     int reverse;
     int poll_limit;
+    long long* trace;       // optional diagnostics: 8 int64 per CTA and step: clocks at step start, after publish, after gather, polls, after mma, after barrier, after gates
 };
 
-__global__ void __launch_bounds__(512) lstm_persistent_kernel(PersistArgs a) {
+__device__ __forceinline__ void st_b128_relaxed(uint4* p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    const unsigned long long lo = ((unsigned long long)y << 32) | x, hi = ((unsigned long long)w << 32) | z;
+    asm volatile("{ .reg .b128 q; mov.b128 q, {%1, %2}; st.relaxed.gpu.global.b128 [%0], q; }" ::"l"(p), "l"(lo), "l"(hi)
+                 : "memory");
+}
+__device__ __forceinline__ void ld_b128_relaxed(const uint4* p, uint32_t& x, uint32_t& y, uint32_t& z, uint32_t& w) {
+    unsigned long long lo, hi;
+    asm volatile("{ .reg .b128 q; ld.relaxed.gpu.global.b128 q, [%2]; mov.b128 {%0, %1}, q; }"
+                 : "=l"(lo), "=l"(hi)
+                 : "l"(p)
+                 : "memory");
+    x = (uint32_t)lo; y = (uint32_t)(lo >> 32); z = (uint32_t)hi; w = (uint32_t)(hi >> 32);
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(PersistArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, U = a.U, T = a.T;
-    const int H8 = H >> 3;
-    __half* Ws = reinterpret_cast<__half*>(smem_raw);                    // [U*4][H]
-    __half* hs = Ws + (size_t)U * 4 * H;                                 // [2][H]
-    const int tid = threadIdx.x, nthr = blockDim.x;
-    const int warp = tid >> 5, lane = tid & 31;
+    const int pitch = H + 8;                                               // halves per padded row
+    __half* Ws = reinterpret_cast<__half*>(smem_raw);                      // [32][pitch]
+    __half* hs = Ws + (size_t)kPersistRows * pitch;                        // [2][H]
+    float* part = reinterpret_cast<float*>(hs + (size_t)2 * H);            // [8 warps][32 rows]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x;
     const int u0 = blockIdx.x * U;
     const int nu = min(U, H - u0);  // units this CTA owns
-    const int u = u0 + warp;
-    const bool owner = (warp < nu);
+    const int ktiles = H >> 4;
+    const uint4* my_copy = a.xchg + (size_t)(blockIdx.x % a.copies) * 2 * kXchgWords;
 
     // one-time: this CTA's slice of W_hh goes to shared memory and stays there for all T steps
     {
+        const int H8 = H >> 3;
         const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
-        uint4* dst = reinterpret_cast<uint4*>(Ws);
-        const int n16 = nu * 4 * H8;
-        for (int i = tid; i < n16; i += nthr) dst[i] = ldg_stream_v4(src + i);
+        for (int i = tid; i < kPersistRows * H8; i += kPersistThreads) {
+            const int r = i / H8, c8 = i - r * H8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < 4 * nu) v = ldg_stream_v4(src + (size_t)r * H8 + c8);
+            *reinterpret_cast<uint4*>(Ws + (size_t)r * pitch + c8 * 8) = v;
+        }
     }
-    // h_{-1}
-    for (int i = tid; i < H; i += nthr) hs[i] = a.h0 ? a.h0[i] : __float2half_rn(0.f);
+    for (int i = tid; i < H; i += kPersistThreads) hs[i] = a.h0 ? a.h0[i] : __float2half_rn(0.f);
 
+    // gate lanes: warp 0, lane 4*j owns unit u0+j
+    const bool gate_lane = (warp == 0) && ((lane & 3) == 0) && ((lane >> 2) < nu);
+    const int u = u0 + (lane >> 2);
     float c = 0.f;
     float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 gx = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (owner && lane == 0) {
+    if (gate_lane) {
         c = a.c0 ? __half2float(a.c0[u]) : 0.f;
         bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
         const int t0 = a.reverse ? T - 1 : 0;
         gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)u * 4));
     }
+    // ldmatrix source row/column of this lane inside a 16x16 A tile
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int a_col = (lane >> 4) * 8;
     __syncthreads();
 
     for (int s = 0; s < T; ++s) {
         const int t = a.reverse ? T - 1 - s : s;
         const __half* hcur = hs + (size_t)(s & 1) * H;
-        float4 gx_next = gx;
-        if (owner) {
-            if (lane == 0 && s + 1 < T) {
-                const int tn = a.reverse ? t - 1 : t + 1;
-                gx_next = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)u * 4));
+        long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+        if (tr && tid == 0) tr[0] = clock64();
+        // ---- 1. partial matvec on the tensor cores; warps split K
+        float acc[2][4], acc2[2][4];  // two accumulator sets per m-tile: half as long a dependent mma chain
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][i] = acc2[m][i] = 0.f;
+        // four k-tiles per trip: their shared-memory loads are all issued before the first mma
+        for (int kt0 = warp; kt0 < ktiles; kt0 += 4 * (kPersistThreads / 32)) {
+            uint32_t b0[4], b1[4], af[4][2][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int kt = kt0 + q * (kPersistThreads / 32);
+                const int k0 = min(kt, ktiles - 1) << 4;
+                b0[q] = 0u;
+                b1[q] = 0u;
+                if (lane < 4 && kt < ktiles) {  // column 0 of the B operand = h; the other seven columns stay zero
+                    b0[q] = *reinterpret_cast<const uint32_t*>(hcur + k0 + 2 * lane);
+                    b1[q] = *reinterpret_cast<const uint32_t*>(hcur + k0 + 8 + 2 * lane);
+                }
+#pragma unroll
+                for (int m = 0; m < 2; ++m) ldmatrix_x4(af[q][m], Ws + (size_t)(m * 16 + a_row) * pitch + k0 + a_col);
             }
-            const uint4* w4 = reinterpret_cast<const uint4*>(Ws + (size_t)warp * 4 * H);
-            const uint4* h4 = reinterpret_cast<const uint4*>(hcur);
-            float zi = 0.f, zf = 0.f, zg = 0.f, zo = 0.f;
-            for (int cidx = lane; cidx < H8; cidx += 32) {
-                float xf[8];
-                widen8(h4[cidx], xf);
-                zi = dot8f(w4[cidx], xf, zi);
-                zf = dot8f(w4[H8 + cidx], xf, zf);
-                zg = dot8f(w4[2 * H8 + cidx], xf, zg);
-                zo = dot8f(w4[3 * H8 + cidx], xf, zo);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                for (int m = 0; m < 2; ++m) mma_16816((q & 1) ? acc2[m] : acc[m], af[q][m], b0[q], b1[q]);  // B is zero past the last tile
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            acc[m][0] += acc2[m][0];
+            acc[m][2] += acc2[m][2];
+        }
+        if (tr && tid == 0) tr[4] = clock64();
+        if ((lane & 3) == 0) {  // column 0 of the accumulator tile
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                part[warp * kPersistRows + m * 16 + (lane >> 2)] = acc[m][0];
+                part[warp * kPersistRows + m * 16 + (lane >> 2) + 8] = acc[m][2];
             }
-            zi = warp_sum(zi);
-            zf = warp_sum(zf);
-            zg = warp_sum(zg);
-            zo = warp_sum(zo);
-            if (lane == 0) {
-                zi += gx.x + bias4.x;
-                zf += gx.y + bias4.y;
-                zg += gx.z + bias4.z;
-                zo += gx.w + bias4.w;
+        }
+        __syncthreads();
+        // ---- 2. warp 0: finish the sums, gate math, publish
+        if (tr && tid == 0) tr[5] = clock64();
+        if (warp == 0) {
+            float z = 0.f;
+#pragma unroll
+            for (int w = 0; w < kPersistThreads / 32; ++w) z += part[w * kPersistRows + lane];
+            const float zf_ = __shfl_down_sync(0xffffffffu, z, 1);
+            const float zg_ = __shfl_down_sync(0xffffffffu, z, 2);
+            const float zo_ = __shfl_down_sync(0xffffffffu, z, 3);
+            uint32_t hbits = 0u;
+            __half hh = __float2half_rn(0.f);
+            if (gate_lane) {
+                const float zi = z + gx.x + bias4.x, zf = zf_ + gx.y + bias4.y, zg = zg_ + gx.z + bias4.z,
+                            zo = zo_ + gx.w + bias4.w;
                 c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
-                const float hnew = sigmoidf_(zo) * tanhf_(c);
-                const __half hh = __float2half_rn(hnew);
-                // publish first (it is on every other CTA's critical path), then the plain output
-                ll_store(a.xchg + (size_t)(s & 1) * H + u, (uint32_t)__half_as_ushort(hh), a.tag_base + s + 1);
+                hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
+                hbits = (uint32_t)__half_as_ushort(hh);
+            }
+            if (tr && tid == 0) tr[6] = clock64();
+            uint32_t hv[kUnitsPerWord];
+#pragma unroll
+            for (int j = 0; j < kUnitsPerWord; ++j) hv[j] = __shfl_sync(0xffffffffu, hbits, 4 * j);
+            const uint32_t tag16 = (a.tag_base + (uint32_t)s + 1u) & 0xffffu;
+            if (lane < a.copies)
+                st_b128_relaxed(a.xchg + ((size_t)lane * 2 + (s & 1)) * kXchgWords + blockIdx.x, hv[0] | (hv[1] << 16),
+                                hv[2] | (hv[3] << 16), hv[4] | (hv[5] << 16), hv[6] | (tag16 << 16));
+            if (gate_lane) {
                 a.y[(size_t)t * a.y_tstride + u] = hh;
                 if (s == T - 1) {
                     if (a.hn) a.hn[u] = hh;
                     if (a.cn) a.cn[u] = __float2half_rn(c);
                 }
+                if (s + 1 < T) {
+                    const int tn = a.reverse ? t - 1 : t + 1;
+                    gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)u * 4));
+                }
             }
         }
-        gx = gx_next;
-        int timed_out = 0;
-        if (s + 1 < T) {
-            // gather h_s from every CTA: each thread polls its words until all carry this step's tag
-            const unsigned long long* src = a.xchg + (size_t)(s & 1) * H;
-            __half* hnext = hs + (size_t)((s + 1) & 1) * H;
-            const uint32_t want = a.tag_base + s + 1;
-            unsigned long long v[kPersistMaxWordsPerThread];
-            int polls = 0;
+        if (tr && tid == 0) tr[1] = clock64();
+        // ---- 3. gather h_s: thread j waits for the word of CTA j
+        int timed_out = 0, polls = 0;
+        if (s + 1 < T && tid < n_cta) {
+            const uint4* src = my_copy + (size_t)(s & 1) * kXchgWords + tid;
+            const uint32_t want = (a.tag_base + (uint32_t)s + 1u) & 0xffffu;
+            uint32_t x, y, z, w;
             while (true) {
-                bool ok = true;
-#pragma unroll
-                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
-                    const int idx = tid + j * nthr;
-                    if (idx < H) v[j] = ll_load(src + idx);
-                }
-#pragma unroll
-                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
-                    const int idx = tid + j * nthr;
-                    if (idx < H) ok = ok && ((uint32_t)(v[j] >> 32) == want);
-                }
-                if (ok) break;
+                ld_b128_relaxed(src, x, y, z, w);
+                if ((w >> 16) == want) break;
                 if (++polls >= a.poll_limit) {
                     timed_out = 1;
                     break;
@@ -312,15 +391,17 @@ __global__ void __launch_bounds__(512) lstm_persistent_kernel(PersistArgs a) {
                 }
             }
             if (!timed_out) {
+                __half* hnext = hs + (size_t)((s + 1) & 1) * H + (size_t)tid * U;
+                const int n = min(U, H - tid * U);
+                const uint32_t vals[4] = {x, y, z, w};
 #pragma unroll
-                for (int j = 0; j < kPersistMaxWordsPerThread; ++j) {
-                    const int idx = tid + j * nthr;
-                    if (idx < H) hnext[idx] = __ushort_as_half((unsigned short)(v[j] & 0xffffu));
-                }
+                for (int j = 0; j < kUnitsPerWord; ++j)
+                    if (j < n) hnext[j] = __ushort_as_half((unsigned short)((vals[j >> 1] >> ((j & 1) * 16)) & 0xffffu));
             } else {
                 atomicExch(a.status, PIMB200_ERR_TIMEOUT);
             }
         }
+        if (tr && tid == 0) { tr[2] = clock64(); tr[3] = polls; }
         if (__syncthreads_or(timed_out)) return;  // whole CTA leaves together
     }
 }
@@ -342,10 +423,12 @@ struct pimb200_lstm {
     size_t y_cap[2] = {0, 0};
     float* cstate = nullptr;
     size_t c_cap = 0;
-    unsigned long long* xchg = nullptr;  // [2][H]
+    uint4* xchg = nullptr;  // [kXchgCopies][2][kXchgWords]
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
+    int xchg_copies = kXchgCopies;
+    long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
     // optional timing of the recurrence launches (CUDA events on the launching stream)
     bool prof = false;
     std::vector<cudaEvent_t> prof_ev;   // pairs: begin, end
@@ -417,9 +500,9 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
                 has_biases ? static_cast<const __half*>(p[3]) : nullptr, bs, H);
         }
     }
-    if (cudaMalloc(&h->xchg, (size_t)2 * H * 8) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+    if (cudaMalloc(&h->xchg, (size_t)kXchgCopies * 2 * kXchgWords * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
     if (cudaMalloc(&h->d_status, 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
-    cudaMemset(h->xchg, 0, (size_t)2 * H * 8);
+    cudaMemset(h->xchg, 0, (size_t)kXchgCopies * 2 * kXchgWords * 16);
     cudaMemset(h->d_status, 0, 4);
     if ((rc = cuda_status(cudaDeviceSynchronize())) != PIMB200_OK) return fail(rc);
     *out = h;
@@ -469,6 +552,19 @@ extern "C" int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long
     return PIMB200_OK;
 }
 
+// Diagnostics: a device buffer of n_cta * T * 8 int64 that the persistent kernel fills with per-step clocks.
+// Diagnostics / tuning: how many replicas of the exchange buffer the persistent kernel publishes into.
+extern "C" int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies) {
+    if (!h || copies < 1 || copies > kXchgCopies) return PIMB200_ERR_BAD_ARG;
+    h->xchg_copies = copies;
+    return PIMB200_OK;
+}
+extern "C" int pimb200_lstm_set_trace(pimb200_lstm* h, long long* device_buffer) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->trace = device_buffer;
+    return PIMB200_OK;
+}
+
 extern "C" int pimb200_lstm_last_status(pimb200_lstm* h) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     int v = 0;
@@ -493,18 +589,14 @@ struct PersistPlan { bool ok; int U, ncta, threads; size_t smem; };
 static PersistPlan plan_persistent(const pimb200_lstm* h) {
     PersistPlan p{false, 0, 0, 0, 0};
     const int H = h->H;
-    if (H % 8 != 0) return p;
-    int U = ceil_div(H, h->sm_count);
-    if (U > 16) return p;
+    if (H % 16 != 0) return p;                       // K is consumed in m16n8k16 tiles
+    const int U = ceil_div(H, h->sm_count);
+    if (U > kUnitsPerWord) return p;                 // one 16-byte exchange word per CTA
     p.U = U;
     p.ncta = ceil_div(H, U);
-    int threads = U * 32;
-    const int min_thr = ceil_div(H, kPersistMaxWordsPerThread);
-    if (threads < min_thr) threads = ceil_div(min_thr, 32) * 32;
-    if (threads < 128) threads = 128;
-    if (threads > 512) return p;
-    p.threads = threads;
-    p.smem = (size_t)U * 4 * H * 2 + (size_t)2 * H * 2;
+    if (p.ncta > kXchgWords || p.ncta > kPersistThreads) return p;
+    p.threads = kPersistThreads;
+    p.smem = (size_t)kPersistRows * (H + 8) * 2 + (size_t)2 * H * 2 + (size_t)(kPersistThreads / 32) * kPersistRows * 4;
     if ((int)p.smem > h->max_smem_optin) return p;
     p.ok = true;
     return p;
@@ -536,13 +628,21 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.hn = hn; a.cn = cn;
         a.xchg = h->xchg; a.tag_base = h->tag_counter; a.status = h->d_status;
         a.H = H; a.T = T; a.U = pp.U; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+        a.trace = h->trace;
+        a.copies = h->xchg_copies;
+        // step tags are 16 bits wide: start a fresh generation (zeroed buffer, tags from 1) before they could wrap
+        // onto a stale word left by an earlier launch
+        if ((h->tag_counter & 0xffffu) + (uint32_t)T + 1u > 0xffffu) {
+            PIMB200_CUDA_TRY(cudaMemsetAsync(h->xchg, 0, (size_t)kXchgCopies * 2 * kXchgWords * 16, st));
+            h->tag_counter = 0;
+            a.tag_base = 0;
+        }
         h->tag_counter += (uint32_t)T + 1u;
-        PIMB200_CUDA_TRY(cudaFuncSetAttribute(lstm_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              (int)pp.smem));
+        const void* fn = (const void*)lstm_persistent_kernel;
+        PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pp.smem));
         void* kargs[] = {&a};
         if (h->prof) prof_mark(h, st);
-        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)lstm_persistent_kernel, dim3(pp.ncta),
-                                                     dim3(pp.threads), kargs, pp.smem, st));
+        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(pp.ncta), dim3(pp.threads), kargs, pp.smem, st));
         if (h->prof) {
             prof_mark(h, st);
             h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
