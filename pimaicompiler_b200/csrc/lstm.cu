@@ -171,51 +171,60 @@ __global__ void lstm_init_c_kernel(float* __restrict__ c, const __half* __restri
 // padded path with T steps needs hn/cn even when the caller passes h0 only: handled by the step kernel.
 
 // ---------------------------------------------------------------------------------------------
-// persistent weight-stationary recurrence (B == 1)
+// persistent weight-stationary recurrence (1 <= B <= 8 sequences in lock step)
 //
 // Grid: one CTA per SM (cooperative launch, so all CTAs are co-resident).  CTA c owns U = ceil(H/#SM) <= 7
 // hidden units = 4U gate rows of W_hh, kept in shared memory for all T steps (rows padded to 32 = two
 // m16 tiles; row pitch H+8 halves so ldmatrix is bank-conflict free).
 // Per step:
-//   1. z = W_slice[32 x H] . h[H]  on the tensor cores: mma.sync m16n8k16, fp32 accumulate; h sits in
-//      column 0 of the B operand (columns 1..7 are zero).  The 8 warps split K, partial sums meet in
-//      shared memory.
-//   2. warp 0 finishes the 4U sums, adds the hoisted input projection and bias, runs the gate math,
-//      keeps c in fp32 registers, and publishes the CTA's U new hidden values as ONE 16-byte word
-//      {7 x fp16, 16-bit step tag} with a single-copy-atomic st.relaxed.gpu.b128 into every replica of
-//      the exchange buffer.
-//   3. thread j polls word j of this CTA's replica until its tag is the current step's (data and flag
-//      arrive together: one L2 round trip, no separate barrier), and scatters the 7 values into the next
-//      step's h vector in shared memory.
+//   1. Z[32 x 8] = W_slice[32 x H] . Hprev[H x 8]  on the tensor cores (mma.sync m16n8k16, fp32
+//      accumulate): column n of the B operand is the hidden state of sequence n, so up to eight
+//      sequences cost the same tensor work as one.  The 8 warps split K; partial sums meet in shared
+//      memory.
+//   2. thread (row, n) finishes one sum; warp j then holds the four gates of unit j for all sequences,
+//      lanes 0..B-1 add the hoisted input projection and bias, run the gate math and keep c in fp32
+//      registers for the whole sequence.
+//   3. the CTA publishes, per sequence, ONE 16-byte word {7 x fp16 hidden values, 16-bit step tag} with a
+//      single-copy-atomic st.relaxed.gpu.b128 into every replica of the exchange buffer.
+//   4. the threads poll the B * n_cta words of this CTA's replica until each carries the current step's
+//      tag (data and flag arrive together: one L2 round trip, no separate barrier) and scatter the values
+//      into the next step's h vectors in shared memory.
 // Every wait is bounded: after poll_limit polls the CTA records PIMB200_ERR_TIMEOUT in the status word
 // and leaves; the others see the status (or run out themselves) and leave too.
 // ---------------------------------------------------------------------------------------------
 constexpr int kPersistPollLimit = 1 << 21;  // bounded wait: ~seconds, then the kernel gives up
 constexpr int kXchgCopies = 16;             // replicas of the hidden-state exchange buffer
-constexpr int kXchgWords = 160;             // 16-byte words per replica and parity (>= CTAs in the grid)
+constexpr int kXchgWords = 160;             // 16-byte words per replica, parity and sequence (>= CTAs in the grid)
 constexpr int kPersistThreads = 256;
+constexpr int kPersistWarps = kPersistThreads / 32;
 constexpr int kPersistRows = 32;            // padded gate rows per CTA
 constexpr int kUnitsPerWord = 7;
+constexpr int kPersistMaxB = 8;             // sequences per launch = columns of one mma tile
+constexpr int kPollItems = kPersistMaxB * kXchgWords / kPersistThreads;  // words a thread may have to gather
+constexpr int kXchgMaxStride = 8;           // largest spacing of exchange words, in 16-byte units (8 = one word per 128-byte line)
+constexpr size_t kXchgBytes = (size_t)kXchgCopies * 2 * kPersistMaxB * kXchgWords * 16 * kXchgMaxStride;
 
 struct PersistArgs {
     const __half* Whh;      // packed [4H, H]
     const float* bias;      // packed [4H]
-    const float* G;         // [T, 4H] row stride g_tstride floats
-    long g_tstride;
-    const __half* h0;       // [H] or NULL
-    const __half* c0;       // [H] or NULL
-    __half* y;              // h_t at y + t*y_tstride + u
-    long y_tstride;
-    __half* hn;             // optional [H]
-    __half* cn;             // optional [H]
-    uint4* xchg;            // [copies][2][kXchgWords] exchange words
+    const float* G;         // gate pre-activations of (t, n) at G + t*g_tstride + n*g_bstride (floats)
+    long g_tstride, g_bstride;
+    const __half* h0;       // [B][H] or NULL
+    const __half* c0;       // [B][H] or NULL
+    __half* y;              // h_t of sequence n at y + t*y_tstride + n*y_bstride + u
+    long y_tstride, y_bstride;
+    __half* hn;             // optional [B][H]
+    __half* cn;             // optional [B][H]
+    uint4* xchg;            // [copies][2][kPersistMaxB][kXchgWords] exchange words
     int copies;
+    int wstride;            // spacing of consecutive exchange words in 16-byte units
     uint32_t tag_base;      // tag of step s output = (tag_base + s + 1) & 0xffff
     int* status;            // device status word, set to PIMB200_ERR_TIMEOUT when a wait runs out
-    int H, T, U;            // U = hidden units per CTA
+    int H, T, U, B;         // U = hidden units per CTA
     int reverse;
     int poll_limit;
-    long long* trace;       // optional diagnostics: 8 int64 per CTA and step: clocks at step start, after publish, after gather, polls, after mma, after barrier, after gates
+    long long* trace;       // optional diagnostics, 8 int64 per CTA and step: clocks at step start, after publish,
+                            // after gather, polls, after mma, after barrier, after gates
 };
 
 __device__ __forceinline__ void st_b128_relaxed(uint4* p, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
@@ -245,17 +254,19 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
 
 __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(PersistArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int H = a.H, U = a.U, T = a.T;
-    const int pitch = H + 8;                                               // halves per padded row
+    const int H = a.H, U = a.U, T = a.T, B = a.B;
+    const int pitch = H + 8;                                               // halves per padded row (weights and h)
     __half* Ws = reinterpret_cast<__half*>(smem_raw);                      // [32][pitch]
-    __half* hs = Ws + (size_t)kPersistRows * pitch;                        // [2][H]
-    float* part = reinterpret_cast<float*>(hs + (size_t)2 * H);            // [8 warps][32 rows]
+    __half* hs = Ws + (size_t)kPersistRows * pitch;                        // [2][B][pitch]
+    float* part = reinterpret_cast<float*>(hs + (size_t)2 * B * pitch);    // [8 warps][32 rows][8 cols]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(part + kPersistWarps * kPersistRows * 8);  // [8][8]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_cta = gridDim.x;
     const int u0 = blockIdx.x * U;
     const int nu = min(U, H - u0);  // units this CTA owns
     const int ktiles = H >> 4;
-    const uint4* my_copy = a.xchg + (size_t)(blockIdx.x % a.copies) * 2 * kXchgWords;
+    const int ws = a.wstride;
+    const uint4* my_copy = a.xchg + (size_t)(blockIdx.x % a.copies) * 2 * kPersistMaxB * kXchgWords * ws;
 
     // one-time: this CTA's slice of W_hh goes to shared memory and stays there for all T steps
     {
@@ -268,48 +279,55 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
             *reinterpret_cast<uint4*>(Ws + (size_t)r * pitch + c8 * 8) = v;
         }
     }
-    for (int i = tid; i < H; i += kPersistThreads) hs[i] = a.h0 ? a.h0[i] : __float2half_rn(0.f);
+    for (int i = tid; i < B * H; i += kPersistThreads) {
+        const int n = i / H, k = i - n * H;
+        hs[(size_t)n * pitch + k] = a.h0 ? a.h0[i] : __float2half_rn(0.f);
+    }
+    if (tid < 64) hpub[tid] = 0;
 
-    // gate lanes: warp 0, lane 4*j owns unit u0+j
-    const bool gate_lane = (warp == 0) && ((lane & 3) == 0) && ((lane >> 2) < nu);
-    const int u = u0 + (lane >> 2);
+    // gate lanes: warp j owns unit u0+j, its lane n (< B) owns sequence n
+    const bool gate_lane = (warp < nu) && (lane < B);
+    const int u = u0 + warp;
     float c = 0.f;
     float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 gx = make_float4(0.f, 0.f, 0.f, 0.f);
     if (gate_lane) {
-        c = a.c0 ? __half2float(a.c0[u]) : 0.f;
+        c = a.c0 ? __half2float(a.c0[(size_t)lane * H + u]) : 0.f;
         bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
         const int t0 = a.reverse ? T - 1 : 0;
-        gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)u * 4));
+        gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)lane * a.g_bstride +
+                                                    (size_t)u * 4));
     }
-    // ldmatrix source row/column of this lane inside a 16x16 A tile
+    // ldmatrix source row/column of this lane inside a 16x16 A tile; B-operand column (sequence) of this lane
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
     const int a_col = (lane >> 4) * 8;
+    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
     __syncthreads();
 
     for (int s = 0; s < T; ++s) {
         const int t = a.reverse ? T - 1 - s : s;
-        const __half* hcur = hs + (size_t)(s & 1) * H;
+        const __half* hcur = hs + (size_t)(s & 1) * B * pitch;
         long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
         if (tr && tid == 0) tr[0] = clock64();
-        // ---- 1. partial matvec on the tensor cores; warps split K
-        float acc[2][4], acc2[2][4];  // two accumulator sets per m-tile: half as long a dependent mma chain
+        // ---- 1. partial products on the tensor cores; warps split K
+        float acc[2][4];
 #pragma unroll
         for (int m = 0; m < 2; ++m)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[m][i] = acc2[m][i] = 0.f;
+            for (int i = 0; i < 4; ++i) acc[m][i] = 0.f;
         // four k-tiles per trip: their shared-memory loads are all issued before the first mma
-        for (int kt0 = warp; kt0 < ktiles; kt0 += 4 * (kPersistThreads / 32)) {
+        for (int kt0 = warp; kt0 < ktiles; kt0 += 4 * kPersistWarps) {
             uint32_t b0[4], b1[4], af[4][2][4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const int kt = kt0 + q * (kPersistThreads / 32);
+                const int kt = kt0 + q * kPersistWarps;
                 const int k0 = min(kt, ktiles - 1) << 4;
                 b0[q] = 0u;
                 b1[q] = 0u;
-                if (lane < 4 && kt < ktiles) {  // column 0 of the B operand = h; the other seven columns stay zero
-                    b0[q] = *reinterpret_cast<const uint32_t*>(hcur + k0 + 2 * lane);
-                    b1[q] = *reinterpret_cast<const uint32_t*>(hcur + k0 + 8 + 2 * lane);
+                if (b_n < B && kt < ktiles) {  // column n of the B operand = h of sequence n
+                    const __half* hp = hcur + (size_t)b_n * pitch + k0 + b_k;
+                    b0[q] = *reinterpret_cast<const uint32_t*>(hp);
+                    b1[q] = *reinterpret_cast<const uint32_t*>(hp + 8);
                 }
 #pragma unroll
                 for (int m = 0; m < 2; ++m) ldmatrix_x4(af[q][m], Ws + (size_t)(m * 16 + a_row) * pitch + k0 + a_col);
@@ -317,70 +335,78 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
 #pragma unroll
             for (int q = 0; q < 4; ++q)
 #pragma unroll
-                for (int m = 0; m < 2; ++m) mma_16816((q & 1) ? acc2[m] : acc[m], af[q][m], b0[q], b1[q]);  // B is zero past the last tile
-        }
-#pragma unroll
-        for (int m = 0; m < 2; ++m) {
-            acc[m][0] += acc2[m][0];
-            acc[m][2] += acc2[m][2];
+                for (int m = 0; m < 2; ++m) mma_16816(acc[m], af[q][m], b0[q], b1[q]);  // B is zero past the last tile
         }
         if (tr && tid == 0) tr[4] = clock64();
-        if ((lane & 3) == 0) {  // column 0 of the accumulator tile
 #pragma unroll
-            for (int m = 0; m < 2; ++m) {
-                part[warp * kPersistRows + m * 16 + (lane >> 2)] = acc[m][0];
-                part[warp * kPersistRows + m * 16 + (lane >> 2) + 8] = acc[m][2];
-            }
+        for (int m = 0; m < 2; ++m) {
+            float* p = part + ((size_t)warp * kPersistRows + m * 16 + (lane >> 2)) * 8 + b_k;
+            *reinterpret_cast<float2*>(p) = make_float2(acc[m][0], acc[m][1]);
+            *reinterpret_cast<float2*>(p + 8 * 8) = make_float2(acc[m][2], acc[m][3]);
         }
         __syncthreads();
-        // ---- 2. warp 0: finish the sums, gate math, publish
         if (tr && tid == 0) tr[5] = clock64();
-        if (warp == 0) {
+        // ---- 2. thread (row = tid/8, n = tid%8) finishes one sum; warp j then holds unit j: lane = gate*8 + n
+        {
             float z = 0.f;
 #pragma unroll
-            for (int w = 0; w < kPersistThreads / 32; ++w) z += part[w * kPersistRows + lane];
-            const float zf_ = __shfl_down_sync(0xffffffffu, z, 1);
-            const float zg_ = __shfl_down_sync(0xffffffffu, z, 2);
-            const float zo_ = __shfl_down_sync(0xffffffffu, z, 3);
-            uint32_t hbits = 0u;
-            __half hh = __float2half_rn(0.f);
+            for (int w = 0; w < kPersistWarps; ++w) z += part[(size_t)w * kPersistRows * 8 + tid];
+            const float zf_ = __shfl_down_sync(0xffffffffu, z, 8);
+            const float zg_ = __shfl_down_sync(0xffffffffu, z, 16);
+            const float zo_ = __shfl_down_sync(0xffffffffu, z, 24);
             if (gate_lane) {
                 const float zi = z + gx.x + bias4.x, zf = zf_ + gx.y + bias4.y, zg = zg_ + gx.z + bias4.z,
                             zo = zo_ + gx.w + bias4.w;
                 c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
-                hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
-                hbits = (uint32_t)__half_as_ushort(hh);
-            }
-            if (tr && tid == 0) tr[6] = clock64();
-            uint32_t hv[kUnitsPerWord];
-#pragma unroll
-            for (int j = 0; j < kUnitsPerWord; ++j) hv[j] = __shfl_sync(0xffffffffu, hbits, 4 * j);
-            const uint32_t tag16 = (a.tag_base + (uint32_t)s + 1u) & 0xffffu;
-            if (lane < a.copies)
-                st_b128_relaxed(a.xchg + ((size_t)lane * 2 + (s & 1)) * kXchgWords + blockIdx.x, hv[0] | (hv[1] << 16),
-                                hv[2] | (hv[3] << 16), hv[4] | (hv[5] << 16), hv[6] | (tag16 << 16));
-            if (gate_lane) {
-                a.y[(size_t)t * a.y_tstride + u] = hh;
+                const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
+                hpub[lane * 8 + warp] = __half_as_ushort(hh);
+                a.y[(size_t)t * a.y_tstride + (size_t)lane * a.y_bstride + u] = hh;
                 if (s == T - 1) {
-                    if (a.hn) a.hn[u] = hh;
-                    if (a.cn) a.cn[u] = __float2half_rn(c);
+                    if (a.hn) a.hn[(size_t)lane * H + u] = hh;
+                    if (a.cn) a.cn[(size_t)lane * H + u] = __float2half_rn(c);
                 }
                 if (s + 1 < T) {
                     const int tn = a.reverse ? t - 1 : t + 1;
-                    gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)u * 4));
+                    gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride +
+                                                                (size_t)lane * a.g_bstride + (size_t)u * 4));
                 }
             }
         }
-        if (tr && tid == 0) tr[1] = clock64();
-        // ---- 3. gather h_s: thread j waits for the word of CTA j
+        if (tr && tid == 0) tr[6] = clock64();
         int timed_out = 0, polls = 0;
-        if (s + 1 < T && tid < n_cta) {
-            const uint4* src = my_copy + (size_t)(s & 1) * kXchgWords + tid;
-            const uint32_t want = (a.tag_base + (uint32_t)s + 1u) & 0xffffu;
-            uint32_t x, y, z, w;
-            while (true) {
-                ld_b128_relaxed(src, x, y, z, w);
-                if ((w >> 16) == want) break;
+        if (s + 1 < T) {
+            __syncthreads();
+            // ---- 3. publish: thread (n, copy) writes sequence n's word into one replica
+            const uint32_t tag16 = (a.tag_base + (uint32_t)s + 1u) & 0xffffu;
+            if (tid < B * a.copies) {
+                const int n = tid / a.copies, cp = tid - n * a.copies;
+                const uint4 v = *reinterpret_cast<const uint4*>(hpub + n * 8);
+                st_b128_relaxed(a.xchg + ((((size_t)cp * 2 + (s & 1)) * kPersistMaxB + n) * kXchgWords + blockIdx.x) * ws, v.x,
+                                v.y, v.z, (v.w & 0xffffu) | (tag16 << 16));
+            }
+            if (tr && tid == 0) tr[1] = clock64();
+            // ---- 4. gather h_s of every sequence from every CTA
+            const uint4* src = my_copy + (size_t)(s & 1) * kPersistMaxB * kXchgWords * ws;
+            __half* hnext = hs + (size_t)((s + 1) & 1) * B * pitch;
+            const int n_items = B * n_cta;
+            uint32_t vx[kPollItems], vy[kPollItems], vz[kPollItems], vw[kPollItems];
+            unsigned pending = 0u;
+#pragma unroll
+            for (int k = 0; k < kPollItems; ++k)
+                if (tid + k * kPersistThreads < n_items) pending |= 1u << k;
+            while (pending) {
+#pragma unroll
+                for (int k = 0; k < kPollItems; ++k) {
+                    if (pending & (1u << k)) {
+                        const int item = tid + k * kPersistThreads;
+                        const int n = item / n_cta, cta = item - n * n_cta;
+                        ld_b128_relaxed(src + ((size_t)n * kXchgWords + cta) * ws, vx[k], vy[k], vz[k], vw[k]);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kPollItems; ++k)
+                    if ((pending & (1u << k)) && (vw[k] >> 16) == tag16) pending &= ~(1u << k);
+                if (!pending) break;
                 if (++polls >= a.poll_limit) {
                     timed_out = 1;
                     break;
@@ -391,12 +417,19 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
                 }
             }
             if (!timed_out) {
-                __half* hnext = hs + (size_t)((s + 1) & 1) * H + (size_t)tid * U;
-                const int n = min(U, H - tid * U);
-                const uint32_t vals[4] = {x, y, z, w};
 #pragma unroll
-                for (int j = 0; j < kUnitsPerWord; ++j)
-                    if (j < n) hnext[j] = __ushort_as_half((unsigned short)((vals[j >> 1] >> ((j & 1) * 16)) & 0xffffu));
+                for (int k = 0; k < kPollItems; ++k) {
+                    const int item = tid + k * kPersistThreads;
+                    if (item < n_items) {
+                        const int n = item / n_cta, cta = item - n * n_cta;
+                        __half* dst = hnext + (size_t)n * pitch + (size_t)cta * U;
+                        const int cnt = min(U, H - cta * U);
+                        const uint32_t vals[4] = {vx[k], vy[k], vz[k], vw[k]};
+#pragma unroll
+                        for (int j = 0; j < kUnitsPerWord; ++j)
+                            if (j < cnt) dst[j] = __ushort_as_half((unsigned short)((vals[j >> 1] >> ((j & 1) * 16)) & 0xffffu));
+                    }
+                }
             } else {
                 atomicExch(a.status, PIMB200_ERR_TIMEOUT);
             }
@@ -427,7 +460,8 @@ struct pimb200_lstm {
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
-    int xchg_copies = kXchgCopies;
+    int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
+    int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
     // optional timing of the recurrence launches (CUDA events on the launching stream)
     bool prof = false;
@@ -500,9 +534,9 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
                 has_biases ? static_cast<const __half*>(p[3]) : nullptr, bs, H);
         }
     }
-    if (cudaMalloc(&h->xchg, (size_t)kXchgCopies * 2 * kXchgWords * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+    if (cudaMalloc(&h->xchg, kXchgBytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
     if (cudaMalloc(&h->d_status, 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
-    cudaMemset(h->xchg, 0, (size_t)kXchgCopies * 2 * kXchgWords * 16);
+    cudaMemset(h->xchg, 0, kXchgBytes);
     cudaMemset(h->d_status, 0, 4);
     if ((rc = cuda_status(cudaDeviceSynchronize())) != PIMB200_OK) return fail(rc);
     *out = h;
@@ -559,6 +593,12 @@ extern "C" int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies) {
     h->xchg_copies = copies;
     return PIMB200_OK;
 }
+extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
+    if (!h || stride16 < 1 || stride16 > kXchgMaxStride) return PIMB200_ERR_BAD_ARG;
+    h->xchg_stride = stride16;
+    h->tag_counter = 0xffffu;  // forces a fresh tag generation (zeroed buffer) at the next launch
+    return PIMB200_OK;
+}
 extern "C" int pimb200_lstm_set_trace(pimb200_lstm* h, long long* device_buffer) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     h->trace = device_buffer;
@@ -586,6 +626,10 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 }
 
 struct PersistPlan { bool ok; int U, ncta, threads; size_t smem; };
+static size_t persist_smem(int H, int B) {
+    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)2 * B * (H + 8) * 2 +
+           (size_t)kPersistWarps * kPersistRows * 8 * 4 + 128;
+}
 static PersistPlan plan_persistent(const pimb200_lstm* h) {
     PersistPlan p{false, 0, 0, 0, 0};
     const int H = h->H;
@@ -596,8 +640,8 @@ static PersistPlan plan_persistent(const pimb200_lstm* h) {
     p.ncta = ceil_div(H, U);
     if (p.ncta > kXchgWords || p.ncta > kPersistThreads) return p;
     p.threads = kPersistThreads;
-    p.smem = (size_t)kPersistRows * (H + 8) * 2 + (size_t)2 * H * 2 + (size_t)(kPersistThreads / 32) * kPersistRows * 4;
-    if ((int)p.smem > h->max_smem_optin) return p;
+    p.smem = persist_smem(H, kPersistMaxB);
+    if ((int)persist_smem(H, 1) > h->max_smem_optin) return p;
     p.ok = true;
     return p;
 }
@@ -616,24 +660,28 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     const bool packed = sq.batch_sizes != nullptr;
     bool use_persistent = false;
     PersistPlan pp = plan_persistent(h);
+    const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
-        if (!pp.ok || B != 1 || packed) return PIMB200_ERR_UNSUPPORTED;
+        if (!fits) return PIMB200_ERR_UNSUPPORTED;
         use_persistent = true;
     } else if (h->variant == PIMB200_LSTM_AUTO) {
-        use_persistent = pp.ok && B == 1 && !packed && T >= 8;
+        use_persistent = fits && T >= 8;
     }
     if (use_persistent) {
         PersistArgs a;
-        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride;
-        a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.hn = hn; a.cn = cn;
+        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
+        a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
+        a.B = B;
+        pp.smem = persist_smem(H, B);
         a.xchg = h->xchg; a.tag_base = h->tag_counter; a.status = h->d_status;
         a.H = H; a.T = T; a.U = pp.U; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
         a.trace = h->trace;
         a.copies = h->xchg_copies;
+        a.wstride = h->xchg_stride > 0 ? h->xchg_stride : (B == 1 ? 8 : 2);
         // step tags are 16 bits wide: start a fresh generation (zeroed buffer, tags from 1) before they could wrap
         // onto a stale word left by an earlier launch
         if ((h->tag_counter & 0xffffu) + (uint32_t)T + 1u > 0xffffu) {
-            PIMB200_CUDA_TRY(cudaMemsetAsync(h->xchg, 0, (size_t)kXchgCopies * 2 * kXchgWords * 16, st));
+            PIMB200_CUDA_TRY(cudaMemsetAsync(h->xchg, 0, kXchgBytes, st));
             h->tag_counter = 0;
             a.tag_base = 0;
         }

@@ -63,23 +63,47 @@ struct GreedyArgs {
     const float* b2;       // [V]
     int PH, JH, V, blank;
     int smem_mask;         // bit i set = matrix i (Whh0, Wih1, Whh1, W1p, W2) is staged in shared memory
+    long long* trace;      // optional diagnostics: 8 clocks per frame of utterance 0 (cluster 0, CTA 0)
 };
 
-__device__ __forceinline__ float dot_row(const __half* __restrict__ w, const __half* __restrict__ h, int K8, int lane) {
-    float acc = 0.f;
-    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+constexpr int kGreedyThreads = 512;
+constexpr int kGreedyWarps = kGreedyThreads / 32;
+constexpr int kMaxRowsPerWarp = 8;   // rows of one phase a warp may own (rows / 16 warps, rounded up)
+
+// z[i] += W[row_i, :] . h for the rows row_i = warp + 16*i of a [rows x K] matrix: all rows of a warp
+// advance together, so their loads and FMA chains are independent and overlap
+template <int NR>
+__device__ __forceinline__ void rows_dot(const __half* __restrict__ W, int rows, int K, const __half* __restrict__ h,
+                                         int warp, int lane, float* z) {
+    const int K8 = K >> 3;
     const uint4* h4 = reinterpret_cast<const uint4*>(h);
-    for (int c = lane; c < K8; c += 32) acc = dot8(w4[c], h4[c], acc);
-    return acc;
+    for (int c = lane; c < K8; c += 32) {
+        float xf[8];
+        widen8(h4[c], xf);
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int r = warp + kGreedyWarps * i;
+            if (r < rows) z[i] = dot8f(reinterpret_cast<const uint4*>(W + (size_t)r * K)[c], xf, z[i]);
+        }
+    }
+}
+template <int NR>
+__device__ __forceinline__ void rows_reduce(float* z) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int i = 0; i < NR; ++i) z[i] += __shfl_xor_sync(0xffffffffu, z[i], o);
 }
 
-__global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
+template <int NRG, int NRJ, int NRV>  // rows per warp of the gate phases, the joint slice and the vocabulary
+__global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.num_blocks();
     const int rank = (int)cluster.block_rank();
     const int cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
-    const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nwarps = nthr >> 5;
-    const int PH = a.PH, JH = a.JH, V = a.V, PH8 = PH >> 3, JH8 = JH >> 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int nthr = kGreedyThreads;
+    const int PH = a.PH, JH = a.JH, V = a.V;
     const int UP = (PH + C - 1) / C, u0 = rank * UP, nu = max(0, min(UP, PH - u0));
     const int JP = (JH + C - 1) / C, j0 = rank * JP, nj = max(0, min(JP, JH - j0));
 
@@ -96,6 +120,9 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
     __half* zs = reinterpret_cast<__half*>(carve((size_t)JH * 2));          // relu(E + Pj), fp16 like the op's output
     float* zrow = reinterpret_cast<float*>(carve((size_t)4 * UP * 4));      // gate pre-activations of my units
     float* lg = reinterpret_cast<float*>(carve((size_t)(V + 1) * 4));       // logits
+    float* b2s = reinterpret_cast<float*>(carve((size_t)V * 4));            // output bias
+    float* bias1s = reinterpret_cast<float*>(carve((size_t)4 * UP * 4));    // layer-1 bias of my rows
+    float* P0s = reinterpret_cast<float*>(carve((size_t)V * 4 * UP * 4));   // [V][4UP] layer-0 input term of my rows
     const size_t slice = (size_t)4 * UP * PH * 2;
     // weight slices: staged in shared memory when they fit, else read in place (L2)
     const __half* Whh0 = a.Whh0 + (size_t)u0 * 4 * PH;
@@ -115,50 +142,86 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
     if (a.smem_mask & 4) Whh1 = stage(Whh1, (size_t)4 * nu * PH, slice);
     if (a.smem_mask & 8) W1p = stage(W1p, (size_t)nj * PH, (size_t)JP * PH * 2);
     if (a.smem_mask & 16) W2 = stage(W2, (size_t)V * JH, (size_t)V * JH * 2);
+    for (int i = tid; i < V; i += nthr) b2s[i] = a.b2[i];
+    for (int i = tid; i < 4 * nu; i += nthr) bias1s[i] = a.bias1[(size_t)u0 * 4 + i];
+    for (int i = tid; i < V * 4 * nu; i += nthr) {
+        const int k = i / (4 * nu), r = i - k * 4 * nu;
+        P0s[k * 4 * UP + r] = a.P0[(size_t)k * 4 * PH + (size_t)u0 * 4 + r];
+    }
+
+    // Gate threads: thread (j, d) = (tid / C, tid % C) keeps the cell state of unit u0+j and writes the new hidden
+    // value into CTA d, so the C copies of a unit are produced by C threads in parallel (same inputs, same result).
+    const int gj = tid / C, gd = tid - gj * C;
+    const bool gate_thread = gj < nu;
+    float c_l0 = 0.f, c_l1 = 0.f;  // fp32 cell states for the whole utterance
+    long long* trp = nullptr;
 
     // One evaluation of the prediction network for input token `tok`, from the state left by the previous
-    // evaluation (buffers of parity (e-1)&1), into buffers of parity e&1; then the pred half of the joint.
-    float c_l0 = 0.f, c_l1 = 0.f;  // cell states of unit u0+tid (threads tid < nu), fp32 for the whole utterance
+    // evaluation (buffers of parity (e+1)&1), into buffers of parity e&1; then the pred half of the joint.
     auto pred_eval = [&](int tok, int e) {
         const __half* h0prev = h0buf + (size_t)((e + 1) & 1) * PH;
         __half* h0new_local = h0buf + (size_t)(e & 1) * PH;
         const __half* h1prev = h1buf + (size_t)((e + 1) & 1) * PH;
         __half* h1new_local = h1buf + (size_t)(e & 1) * PH;
+        float z[NRG];
         // layer 0
-        for (int r = warp; r < 4 * nu; r += nwarps) {
-            float z = warp_sum(dot_row(Whh0 + (size_t)r * PH, h0prev, PH8, lane));
-            if (lane == 0) zrow[r] = z + a.P0[(size_t)tok * 4 * PH + (size_t)u0 * 4 + r];
+#pragma unroll
+        for (int i = 0; i < NRG; ++i) z[i] = 0.f;
+        rows_dot<NRG>(Whh0, 4 * nu, PH, h0prev, warp, lane, z);
+        rows_reduce<NRG>(z);
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < NRG; ++i) {
+                const int r = warp + kGreedyWarps * i;
+                if (r < 4 * nu) zrow[r] = z[i] + P0s[tok * 4 * UP + r];
+            }
         }
         __syncthreads();
-        if (tid < nu) {
-            const float zi = zrow[tid * 4], zf = zrow[tid * 4 + 1], zg = zrow[tid * 4 + 2], zo = zrow[tid * 4 + 3];
+        if (trp && tid == 0) trp[3] = clock64();
+        if (gate_thread) {
+            const float zi = zrow[gj * 4], zf = zrow[gj * 4 + 1], zg = zrow[gj * 4 + 2], zo = zrow[gj * 4 + 3];
             c_l0 = sigmoidf_(zf) * c_l0 + sigmoidf_(zi) * tanhf_(zg);
-            const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
-            for (int d = 0; d < C; ++d) cluster.map_shared_rank(h0new_local, d)[u0 + tid] = hh;
+            cluster.map_shared_rank(h0new_local, gd)[u0 + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
         }
         cluster.sync();
+        if (trp && tid == 0) trp[4] = clock64();
         // layer 1
-        for (int r = warp; r < 4 * nu; r += nwarps) {
-            float z = dot_row(Wih1 + (size_t)r * PH, h0new_local, PH8, lane) +
-                      dot_row(Whh1 + (size_t)r * PH, h1prev, PH8, lane);
-            z = warp_sum(z);
-            if (lane == 0) zrow[r] = z + a.bias1[(size_t)u0 * 4 + r];
+#pragma unroll
+        for (int i = 0; i < NRG; ++i) z[i] = 0.f;
+        rows_dot<NRG>(Wih1, 4 * nu, PH, h0new_local, warp, lane, z);
+        rows_dot<NRG>(Whh1, 4 * nu, PH, h1prev, warp, lane, z);
+        rows_reduce<NRG>(z);
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < NRG; ++i) {
+                const int r = warp + kGreedyWarps * i;
+                if (r < 4 * nu) zrow[r] = z[i] + bias1s[r];
+            }
         }
         __syncthreads();
-        if (tid < nu) {
-            const float zi = zrow[tid * 4], zf = zrow[tid * 4 + 1], zg = zrow[tid * 4 + 2], zo = zrow[tid * 4 + 3];
+        if (gate_thread) {
+            const float zi = zrow[gj * 4], zf = zrow[gj * 4 + 1], zg = zrow[gj * 4 + 2], zo = zrow[gj * 4 + 3];
             c_l1 = sigmoidf_(zf) * c_l1 + sigmoidf_(zi) * tanhf_(zg);
-            const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
-            for (int d = 0; d < C; ++d) cluster.map_shared_rank(h1new_local, d)[u0 + tid] = hh;
+            cluster.map_shared_rank(h1new_local, gd)[u0 + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
         }
         cluster.sync();
-        // prediction half of the joint: Pj[j] = W1p[j,:] . h1
-        for (int q = warp; q < nj; q += nwarps) {
-            float v = warp_sum(dot_row(W1p + (size_t)q * PH, h1new_local, PH8, lane));
-            if (lane == 0)
-                for (int d = 0; d < C; ++d) cluster.map_shared_rank(Pj, d)[j0 + q] = v;
+        if (trp && tid == 0) trp[5] = clock64();
+        // prediction half of the joint: Pj[j] = W1p[j,:] . h1 ; lane d delivers the value to CTA d
+        float zj[NRJ];
+#pragma unroll
+        for (int i = 0; i < NRJ; ++i) zj[i] = 0.f;
+        rows_dot<NRJ>(W1p, nj, PH, h1new_local, warp, lane, zj);
+        rows_reduce<NRJ>(zj);
+        if (lane < C) {
+#pragma unroll
+            for (int i = 0; i < NRJ; ++i) {
+                const int q = warp + kGreedyWarps * i;
+                if (q < nj) cluster.map_shared_rank(Pj, lane)[j0 + q] = zj[i];
+            }
         }
+        if (trp && tid == 0) trp[6] = clock64();
         cluster.sync();
+        if (trp && tid == 0) trp[7] = clock64();
     };
 
     for (int utt = cluster_id; utt < a.n_utts; utt += n_clusters) {
@@ -173,6 +236,7 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
         c_l1 = 0.f;
         cluster.sync();  // staged weights and zeroed states visible; nobody still writes into my buffers
         int e = 0, n_emit = 0;
+        trp = nullptr;
         pred_eval(a.blank, e++);  // start of sequence: the blank row of the embedding, zero state
         float e_next[2] = {0.f, 0.f};  // E[t+1] for z elements tid and tid+nthr
         if (a.Tp > 0) {
@@ -180,6 +244,8 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
             if (tid + nthr < JH) e_next[1] = __ldcg(E + tid + nthr);
         }
         for (int t = 0; t < a.Tp; ++t) {
+            trp = (a.trace && utt == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
+            if (trp && tid == 0) trp[0] = clock64();
             const float e_cur0 = e_next[0], e_cur1 = e_next[1];
             if (t + 1 < a.Tp) {
                 if (tid < JH) e_next[0] = __ldcg(E + (size_t)(t + 1) * JH + tid);
@@ -188,18 +254,35 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
             if (tid < JH) zs[tid] = __float2half_rn(fmaxf(e_cur0 + Pj[tid], 0.f));
             if (tid + nthr < JH) zs[tid + nthr] = __float2half_rn(fmaxf(e_cur1 + Pj[tid + nthr], 0.f));
             __syncthreads();
-            for (int r = warp; r < V; r += nwarps) {
-                float v = warp_sum(dot_row(W2 + (size_t)r * JH, zs, JH8, lane));
-                if (lane == 0) lg[r] = v + a.b2[r];
+            float zv[NRV];
+#pragma unroll
+            for (int i = 0; i < NRV; ++i) zv[i] = 0.f;
+            rows_dot<NRV>(W2, V, JH, zs, warp, lane, zv);
+            rows_reduce<NRV>(zv);
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < NRV; ++i) {
+                    const int r = warp + kGreedyWarps * i;
+                    if (r < V) lg[r] = zv[i] + b2s[r];
+                }
             }
             __syncthreads();
-            int best = 0;
-            float bv = lg[0];
-            for (int r = 1; r < V; ++r) {
+            if (trp && tid == 0) trp[1] = clock64();
+            // argmax, first maximum wins; every warp repeats it, so no broadcast is needed
+            float bv = -INFINITY;
+            int best = 0x7fffffff;
+            for (int r = lane; r < V; r += 32) {
                 const float v = lg[r];
                 if (v > bv) { bv = v; best = r; }
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+                if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
+            }
             if (rank == 0 && logits && tid < V) logits[(size_t)t * V + tid] = lg[tid];
+            if (trp && tid == 0) trp[2] = clock64();
             if (best != a.blank) {
                 if (rank == 0 && tid == 0) tokens[n_emit] = best;
                 ++n_emit;
@@ -209,6 +292,16 @@ __global__ void __launch_bounds__(512, 1) rnnt_greedy_kernel(GreedyArgs a) {
         if (rank == 0 && tid == 0) a.n_tokens[utt] = n_emit;
     }
     cluster.sync();  // no CTA leaves while a peer may still address its shared memory
+}
+
+using GreedyFn = void (*)(GreedyArgs);
+// rows per warp are compile-time (register arrays); pick the instantiation covering the run-time sizes
+static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
+    const int nrg = ceil_div(gate_rows, kGreedyWarps), nrj = ceil_div(joint_rows, kGreedyWarps),
+              nrv = ceil_div(vocab, kGreedyWarps);
+    if (nrg <= 5 && nrj <= 2 && nrv <= 2) return rnnt_greedy_kernel<5, 2, 2>;
+    if (nrg <= kMaxRowsPerWarp && nrj <= 4 && nrv <= 4) return rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4>;
+    return nullptr;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -227,6 +320,9 @@ struct pimb200_rnnt {
     __half *y_pre = nullptr, *y_post = nullptr;
     float* E = nullptr;
     size_t cap_frames = 0;  // frames*utts capacity of the three buffers above
+    long long* trace = nullptr;  // diagnostics buffer (not owned)
+    GreedyFn fn = nullptr;
+    int enc_batch = 8;      // utterances the encoder advances in lock step
     int cluster = 0;        // CTAs per cluster
     int smem_mask = 0;
     size_t smem_bytes = 0;
@@ -238,7 +334,7 @@ static size_t greedy_smem(const pimb200_rnnt_config& c, int C, int mask) {
     const int PH = c.pred_hidden, JH = c.joint_hidden, V = c.vocab;
     const int UP = (PH + C - 1) / C, JP = (JH + C - 1) / C;
     size_t s = al((size_t)2 * PH * 2) * 2 + al((size_t)JH * 4) + al((size_t)JH * 2) + al((size_t)4 * UP * 4) +
-               al((size_t)(V + 1) * 4);
+               al((size_t)(V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4) + al((size_t)V * 4 * UP * 4);
     const size_t slice = al((size_t)4 * UP * PH * 2);
     if (mask & 1) s += slice;
     if (mask & 2) s += slice;
@@ -327,11 +423,13 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
     // cluster size and what fits in shared memory
     int max_smem = 0;
     cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, h->device);
-    cudaFuncSetAttribute(rnnt_greedy_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    cudaFuncSetAttribute(rnnt_greedy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     const int candidates[2] = {16, 8};
     for (int ci = 0; ci < 2 && h->cluster == 0; ++ci) {
         const int C = candidates[ci];
+        GreedyFn fn = pick_greedy(4 * ceil_div(PH, C), ceil_div(JH, C), V);
+        if (!fn || C * ceil_div(PH, C) > kGreedyThreads) continue;   // one gate thread per (unit, destination CTA)
+        cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
         int mask = 0;
         // stage in priority order while the budget lasts: W2 (read every frame) first, then the pred matrices
         const int order[5] = {16, 1, 2, 4, 8};
@@ -348,8 +446,9 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
         lc.attrs = at;
         lc.numAttrs = 1;
         int n_clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&n_clusters, rnnt_greedy_kernel, &lc) == cudaSuccess && n_clusters >= 1) {
+        if (cudaOccupancyMaxActiveClusters(&n_clusters, fn, &lc) == cudaSuccess && n_clusters >= 1) {
             h->cluster = C;
+            h->fn = fn;
             h->smem_mask = mask;
             h->smem_bytes = smem;
         } else {
@@ -380,6 +479,19 @@ extern "C" int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long
     if (total_ms) *total_ms = ms[0] + ms[1];
     if (recurrences) *recurrences = n[0] + n[1];
     if (bytes) *bytes = by[0] + by[1];
+    return PIMB200_OK;
+}
+
+extern "C" int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n) {
+    if (!h || n < 1 || n > 8) return PIMB200_ERR_BAD_ARG;
+    h->enc_batch = n;
+    return PIMB200_OK;
+}
+
+// Diagnostics: device buffer of (T/stack)*8 int64 filled with per-frame clocks of utterance 0.
+extern "C" int pimb200_rnnt_set_trace(pimb200_rnnt* h, long long* device_buffer) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->trace = device_buffer;
     return PIMB200_OK;
 }
 
@@ -418,14 +530,18 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
         h->cap_frames = need;
     }
     const __half* x = static_cast<const __half*>(feats);
-    for (int u = 0; u < n_utts; ++u) {
+    // The encoder runs up to `enc_batch` utterances in lock step (one column of the recurrence's tensor-core
+    // tile each).  With batch-first tensors the time stacking between the two encoder stacks stays a pure
+    // reinterpretation of memory: [g, T, EH] viewed as [g, T/stack, stack*EH] (T a multiple of stack).
+    const int group = (T % c.stack_factor == 0) ? h->enc_batch : 1;
+    for (int u = 0; u < n_utts; u += group) {
+        const int g = (n_utts - u < group) ? (n_utts - u) : group;
         __half* y1 = h->y_pre + (size_t)u * T * EH;
         __half* y2 = h->y_post + (size_t)u * Tp * EH;
-        int rc = pimb200_lstm_forward(h->pre, x + (size_t)u * T * c.feat_dim, T, 1, nullptr, nullptr, y1, nullptr,
-                                      nullptr, 0, stream);
+        int rc = pimb200_lstm_forward(h->pre, x + (size_t)u * T * c.feat_dim, T, g, nullptr, nullptr, y1, nullptr,
+                                      nullptr, 1, stream);
         if (rc != PIMB200_OK) return rc;
-        // time stacking: `stack` consecutive frames side by side is a reinterpretation of the same memory
-        rc = pimb200_lstm_forward(h->post, y1, Tp, 1, nullptr, nullptr, y2, nullptr, nullptr, 0, stream);
+        rc = pimb200_lstm_forward(h->post, y1, Tp, g, nullptr, nullptr, y2, nullptr, nullptr, 1, stream);
         if (rc != PIMB200_OK) return rc;
     }
     // encoder half of the joint for every frame of every utterance: one dense GEMM (y_post is contiguous over utts
@@ -444,6 +560,7 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     a.E = h->E; a.tokens = tokens; a.n_tokens = n_tokens; a.logits = logits; a.n_utts = n_utts; a.Tp = Tp;
     a.P0 = h->P0; a.Whh0 = h->Whh0; a.Wih1 = h->Wih1; a.Whh1 = h->Whh1; a.bias1 = h->bias1;
     a.W1p = h->W1p; a.W2 = h->W2; a.b2 = h->b2;
+    a.trace = h->trace;
     a.PH = c.pred_hidden; a.JH = JH; a.V = c.vocab; a.blank = c.blank; a.smem_mask = h->smem_mask;
     const int C = h->cluster;
     int max_clusters = kNumSmB200 / C;
@@ -459,6 +576,6 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, rnnt_greedy_kernel, a));
+    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, h->fn, a));
     return PIMB200_OK;
 }

@@ -53,6 +53,10 @@ class RnntDecoder:
         check(_lib.lib().pimb200_rnnt_info(self._h, C.byref(cs), C.byref(mask), C.byref(sm)), "rnnt_info")
         return {"cluster_size": cs.value, "smem_mask": mask.value, "smem_bytes": sm.value}
 
+    def set_encoder_batch(self, n: int) -> None:
+        """Utterances the encoder advances in lock step (1..8)."""
+        check(_lib.lib().pimb200_rnnt_set_encoder_batch(self._h, int(n)), "rnnt_set_encoder_batch")
+
     def profile(self, enable: bool) -> None:
         check(_lib.lib().pimb200_rnnt_profile_enable(self._h, 1 if enable else 0), "rnnt_profile_enable")
 

@@ -78,7 +78,10 @@ CASES = [
     (12, 1, 40, 1024, 1, False, True, False, True),
     (9, 1, 32, 64, 3, True, True, False, True),
     (10, 1, 32, 64, 2, False, False, True, False),
-    (7, 5, 24, 40, 2, True, True, True, True),           # B > 1: streamed only
+    (7, 5, 24, 48, 2, True, True, True, True),           # B > 1, bidirectional, batch_first
+    (11, 8, 40, 128, 2, False, True, False, True),       # a full tile of sequences
+    (6, 8, 240, 1024, 1, False, True, True, False),      # eight utterances at the encoder width
+    (5, 11, 16, 32, 1, False, True, False, True),        # B > 8: streamed only
     (3, 2, 7, 5, 2, False, True, False, True),           # odd sizes: scalar path
 ]
 
@@ -88,8 +91,8 @@ CASES = [
 def test_lstm_matches_oracle(case, variant):
     ops = _ops()
     T, B, I, H, L, bi, hb, bf, nz = case
-    if variant == "persistent" and (B != 1 or H % 16):
-        pytest.skip("persistent variant is batch-1, H % 16 == 0")
+    if variant == "persistent" and (B > 8 or H % 16):
+        pytest.skip("persistent variant takes up to 8 sequences and H % 16 == 0")
     D = 2 if bi else 1
     g = torch.Generator().manual_seed(T * 131 + H)
     ps = lstm_params(L, D, I, H, g, has_biases=hb)

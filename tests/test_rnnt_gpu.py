@@ -83,7 +83,13 @@ def test_rnnt_batch_of_utterances_matches_single():
     n, T = 13, 30   # more utterances than clusters fit on the device
     feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
     toks, logits = dec.decode(feats, want_logits=True)
+    # lock-step encoding of up to 8 utterances must not change any utterance's result: the per-sequence
+    # arithmetic (tensor-core tile column, fp32 accumulation order) is the same at every batch size
+    dec.set_encoder_batch(1)
     for i in range(n):
         ti, li = dec.decode(feats[i], want_logits=True)
         assert ti[0] == toks[i]
         assert torch.equal(li[0], logits[i])
+    dec.set_encoder_batch(3)
+    toks3, logits3 = dec.decode(feats, want_logits=True)
+    assert toks3 == toks and torch.equal(logits3, logits)
