@@ -81,6 +81,12 @@ int pimb200_bmm_row(const void* x, const void* A, void* y, int k, int n, void* s
 int pimb200_gemm_wx(const void* W, const void* X, const void* bias, void* Y,
                     int N, int K, int J, int ldx, int ldy, int act, int y_is_f32, void* stream);
 
+/* Status of the tensor-core GEMM's bounded waits on the current device (0, or PIMB200_ERR_TIMEOUT if one gave up
+ * since the last call); synchronises the device.  pimb200_gemm_force_simt(1) routes every pimb200_gemm_wx call
+ * (and the LSTM input projections) to the SIMT kernel, for A/B profiling.  No counterpart in the reference. */
+int pimb200_gemm_last_status(void);
+int pimb200_gemm_force_simt(int on);
+
 /* ---- glue ops ------------------------------------------------------------ */
 
 /* C[m,n] = A[m,n] + B[m,n]   (broadcast_b == 0)   or   A[m,n] + B[n] (broadcast_b != 0).

@@ -30,6 +30,8 @@ SIGNATURES = {
     "pimb200_dot_vv": (_i, [_vp, _vp, _vp, _i, _vp]),
     "pimb200_bmm_row": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "pimb200_gemm_wx": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "pimb200_gemm_last_status": (_i, []),
+    "pimb200_gemm_force_simt": (_i, [_i]),
     "pimb200_add_f16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "pimb200_copy_2d": (_i, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "pimb200_cat": (_i, [_vp, C.POINTER(_vp), C.POINTER(_sz), _i, _sz, _vp]),

@@ -1,13 +1,354 @@
-// Dense contraction  Y[j,n] = act(sum_k X[j,k] W[n,k] + b[n])  — dispatch between the
-// tensor-core kernel and the SIMT fall-back.
+// Dense contraction  Y[j,n] = act(sum_k X[j,k] W[n,k] + b[n])  on the 5th-generation tensor cores.
+//
+// Used for the whole-sequence LSTM input projection (J = T*B rows), the encoder half of the RNN-T joint
+// and the batched-stream linear layers (J = 8..128).  Both operands are K-major, so the weight matrix is
+// the A operand (M = 128 weight rows per CTA) and the activations are the B operand (N = up to 128 rows
+// of X per CTA, any multiple of 16):  D[m, j] = sum_k W[m0+m, k] X[j0+j, k], accumulated in fp32 in
+// tensor memory.  TMEM lane = weight row, TMEM column = activation row, so the epilogue thread that owns
+// weight row m adds bias[m] once and, for a fixed j, the 32 lanes of a warp store 32 consecutive
+// elements of Y's row j.
+//
+// One CTA per output tile, warp-specialised:
+//   warp 0    TMA producer: cp.async.bulk.tensor (no multicast) of a [128 x 64] W tile and a [BN x 64] X tile
+//             per stage, 128-byte swizzle, completion on the stage's "full" mbarrier
+//   warp 1    allocates TMEM; one lane issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) four times per
+//             stage and commits the stage's "empty" mbarrier
+//   warps 2-5 epilogue: tcgen05.ld 32 columns at a time, bias / ReLU / convert, coalesced stores
+// Every mbarrier wait is bounded; when one runs out the kernel records an error in the status word,
+// lets outstanding bulk copies land (bounded), frees its TMEM and returns.
+// Shapes the TMA path cannot take (K or ldx not a multiple of 8, unaligned base) use the SIMT kernel.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pimb200 {
+
 int launch_gemm_wx_simt(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                         int ldy, int act, int y_is_f32, cudaStream_t st);
 
+namespace tc {
+
+constexpr int BM = 128;            // weight rows per CTA (UMMA M)
+constexpr int BN_MAX = 128;        // activation rows per CTA (UMMA N), runtime value in [16, 128]
+constexpr int BK = 64;             // halves per stage along K = one 128-byte swizzle row
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
+constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;    // 16 KiB
+constexpr int THREADS = 192;                      // 6 warps
+constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // bounded wait on every mbarrier: about two seconds
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait; false = gave up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 0xff) == 0xff) {
+            if (*abort_flag != 0) return false;                    // another role already gave up
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+        "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// K-major operand tile written by TMA with the 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);   // start address, 16-byte units
+    d |= (uint64_t)0 << 16;                        // leading byte offset: unused for a swizzled K-major tile
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+        "[%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    const __half* bias;   // [N] or NULL
+    void* Y;
+    int N, K, J, ldy, act, y_is_f32;
+    int bn;               // activation rows per CTA: multiple of 16 in [16, 128]
+    int tmem_cols;        // power of two >= max(32, bn)
+    int* status;          // device status word
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)STAGES * B_STAGE_BYTES);
+    // bars[0..S) full, [S..2S) empty, [2S] accumulator ready; then the TMEM base address
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accbar = smem_u32(bars + 2 * STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, j0 = blockIdx.y * a.bn;
+    const int kblocks = (a.K + BK - 1) / BK;
+    const volatile int* abort_flag = a.status;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)a.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint32_t stage_bytes = (uint32_t)A_STAGE_BYTES + (uint32_t)a.bn * BK * 2;
+            int issued = 0;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t it = (uint32_t)(kb / STAGES);
+                if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag)) { failed = true; break; }
+                mbar_expect_tx(full0 + 8 * s, stage_bytes);
+                tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_w, full0 + 8 * s, kb * BK, m0);
+                tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, j0);
+                ++issued;
+            }
+            if (failed) {
+                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                // let the copies already issued land before the CTA gives its shared memory back
+                const int first = issued > STAGES ? issued - STAGES : 0;
+                for (int kb = first; kb < issued; ++kb) {
+                    const int s = kb % STAGES;
+                    for (uint32_t i = 0; i < (1u << 20); ++i)
+                        if (mbar_try_wait(full0 + 8 * s, (uint32_t)(kb / STAGES) & 1)) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D = f32, A = B = f16, both K-major, N = bn, M = 128
+            const uint32_t idesc = (1u << 4) | ((uint32_t)(a.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t it = (uint32_t)(kb / STAGES);
+                if (!mbar_wait(full0 + 8 * s, it & 1, abort_flag)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
+                const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // advance 16 halves = 32 bytes inside the swizzle row: +2 in the descriptor's 16-byte units
+                    umma_f16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+            }
+            if (failed) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            umma_commit(accbar);  // accumulator complete (or whatever was issued, on failure) -> epilogue may proceed
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
+        const int q = warp & 3;
+        const int m = m0 + q * 32 + lane;
+        bool ok = mbar_wait(accbar, 0, abort_flag);
+        if (!ok) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        ok = ok && (*abort_flag == 0);
+        if (ok) {
+            const float bv = (a.bias && m < a.N) ? __half2float(a.bias[m]) : 0.f;
+            for (int c0 = 0; c0 < a.bn; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                if (m < a.N) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int j = j0 + c0 + c;
+                        if (c0 + c < a.bn && j < a.J) {
+                            float v = __uint_as_float(r[c]) + bv;
+                            if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
+                            if (a.y_is_f32)
+                                static_cast<float*>(a.Y)[(size_t)j * a.ldy + m] = v;
+                            else
+                                static_cast<__half*>(a.Y)[(size_t)j * a.ldy + m] = __float2half_rn(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)a.tmem_cols)
+                     : "memory");
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static std::mutex g_mu;
+static EncodeTiledFn g_encode = nullptr;
+static bool g_encode_tried = false;
+static int* g_status[64];
+static bool g_attr_set = false;
+
+static EncodeTiledFn get_encode() {
+    if (g_encode_tried) return g_encode;
+    g_encode_tried = true;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    else
+        cudaGetLastError();
+    return g_encode;
+}
+
+static bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                      uint32_t box_rows) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// returns PIMB200_ERR_UNSUPPORTED when the shape must take the SIMT kernel
+static int launch(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx, int ldy,
+                  int act, int y_is_f32, cudaStream_t st) {
+    if (K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
+    int dev = 0;
+    PIMB200_CUDA_TRY(cudaGetDevice(&dev));
+    int* status = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!get_encode()) return PIMB200_ERR_UNSUPPORTED;
+        if (!g_status[dev]) {
+            PIMB200_CUDA_TRY(cudaMalloc(&g_status[dev], sizeof(int)));
+            PIMB200_CUDA_TRY(cudaMemset(g_status[dev], 0, sizeof(int)));
+        }
+        status = g_status[dev];
+        if (!g_attr_set) {
+            PIMB200_CUDA_TRY(cudaFuncSetAttribute(gemm_wx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)SMEM_BYTES));
+            g_attr_set = true;
+        }
+    }
+    GemmArgs a;
+    a.bias = bias; a.Y = Y; a.N = N; a.K = K; a.J = J; a.ldy = ldy; a.act = act; a.y_is_f32 = y_is_f32;
+    a.bn = J >= BN_MAX ? BN_MAX : ((J + 15) / 16) * 16;
+    a.tmem_cols = a.bn <= 32 ? 32 : (a.bn <= 64 ? 64 : 128);
+    a.status = status;
+    CUtensorMap map_w, map_x;
+    if (!encode_2d(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return PIMB200_ERR_UNSUPPORTED;
+    if (!encode_2d(&map_x, X, (uint64_t)J, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)a.bn)) return PIMB200_ERR_UNSUPPORTED;
+    dim3 grid(ceil_div(N, BM), ceil_div(J, a.bn));
+    gemm_wx_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
+    return launch_status();
+}
+
+}  // namespace tc
+
+static int g_force_simt = 0;
+
 int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                    int ldy, int act, int y_is_f32, cudaStream_t st) {
+    if (!g_force_simt) {
+        const int rc = tc::launch(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st);
+        if (rc != PIMB200_ERR_UNSUPPORTED) return rc;
+    }
     return launch_gemm_wx_simt(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st);
 }
+
 }  // namespace pimb200
+
+// A/B switch for profiling: 1 = always the SIMT kernel.
+extern "C" int pimb200_gemm_force_simt(int on) {
+    pimb200::g_force_simt = on ? 1 : 0;
+    return PIMB200_OK;
+}
+
+// Status word of the tensor-core GEMM on the current device: 0, or PIMB200_ERR_TIMEOUT when one of its bounded
+// waits gave up since the last call.  Synchronises the device.
+extern "C" int pimb200_gemm_last_status(void) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return PIMB200_ERR_LAUNCH;
+    int* p = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(pimb200::tc::g_mu);
+        p = pimb200::tc::g_status[dev];
+    }
+    if (!p) return PIMB200_OK;
+    int v = 0;
+    if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return PIMB200_ERR_LAUNCH;
+    if (v != 0) cudaMemset(p, 0, sizeof(int));
+    return v;
+}

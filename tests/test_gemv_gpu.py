@@ -148,6 +148,28 @@ def test_batched_stream_gemm(N, K, B):
     assert_close(Y, ref, GEMV_ATOL, GEMV_RTOL, f"gemm {N}x{K} B={B}")
     Yf = ops.gemm_wx(to_dev(W), to_dev(X), None, ops.ACT_NONE, out_f32=True)
     assert_close(Yf, co.linear(W.numpy(), X.numpy()), 1e-3, 1e-4, f"gemm f32 {N}x{K} B={B}")
+    from pimaicompiler_b200 import _lib
+    assert _lib.lib().pimb200_gemm_last_status() == 0
+
+
+@pytest.mark.parametrize("N,K,J", [(4096, 240, 200), (512, 1024, 500), (4096, 2048, 130), (130, 72, 17), (128, 64, 16),
+                                   (256, 8, 3), (1280, 320, 29)])
+def test_dense_gemm_tensor_core_and_simt_agree_with_oracle(N, K, J):
+    # the LSTM input-projection / joint shapes, ragged tiles in every dimension, both kernels
+    ops = _ops()
+    from pimaicompiler_b200 import _lib
+    W, b, X = _c2_inputs(N, K, J, seed=21)
+    ref = co.linear(W.numpy(), X.numpy(), b.numpy())
+    for simt in (0, 1):
+        _lib.lib().pimb200_gemm_force_simt(simt)
+        try:
+            Yf = ops.gemm_wx(to_dev(W), to_dev(X), to_dev(b), ops.ACT_NONE, out_f32=True)
+            assert_close(Yf, ref, 1e-3, 1e-4, f"gemm f32 {N}x{K}x{J} simt={simt}")
+            Yh = ops.gemm_wx(to_dev(W), to_dev(X), to_dev(b), ops.ACT_RELU)
+            assert_close(Yh, np.maximum(ref, 0), GEMV_ATOL, GEMV_RTOL, f"gemm f16 {N}x{K}x{J} simt={simt}")
+        finally:
+            _lib.lib().pimb200_gemm_force_simt(0)
+    assert _lib.lib().pimb200_gemm_last_status() == 0
 
 
 def test_gemv_linearity_at_full_size():
