@@ -75,3 +75,42 @@ def make_rnnt_weights(cfg: RnntConfig, seed: int = 0, gain: float = 1.0, logit_g
 def make_features(T: int, cfg: RnntConfig, seed: int) -> torch.Tensor:
     g = torch.Generator().manual_seed(seed)
     return torch.randn(T, cfg.feat_dim, generator=g).to(torch.float16).to(torch.float32)
+
+
+class _RnntModule(torch.nn.Module):
+    """Container with the parameter names PipelineManager('...', 'RNNT') looks for.  forward() is the encoder only
+    (the greedy loop of the benchmark is data-dependent control flow; the reference interprets it op by op)."""
+
+    def __init__(self, cfg: RnntConfig):
+        super().__init__()
+        self.pre_rnn = torch.nn.LSTM(cfg.feat_dim, cfg.enc_hidden, cfg.pre_layers)
+        self.post_rnn = torch.nn.LSTM(cfg.stack_factor * cfg.enc_hidden, cfg.enc_hidden, cfg.post_layers)
+        self.pred_embed = torch.nn.Embedding(cfg.vocab, cfg.pred_hidden)
+        self.pred_rnn = torch.nn.LSTM(cfg.pred_hidden, cfg.pred_hidden, cfg.pred_layers)
+        self.joint1 = torch.nn.Linear(cfg.enc_hidden + cfg.pred_hidden, cfg.joint_hidden)
+        self.joint2 = torch.nn.Linear(cfg.joint_hidden, cfg.vocab)
+        self.stack = cfg.stack_factor
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y, _ = self.pre_rnn(x)
+        T, B, H = y.shape
+        Tp = T // self.stack
+        y = y[: Tp * self.stack].transpose(0, 1).reshape(B, Tp, self.stack * H).transpose(0, 1)
+        y, _ = self.post_rnn(y.contiguous())
+        return y
+
+
+def save_rnnt_torchscript(path: str, cfg: RnntConfig, w: RnntWeights) -> None:
+    """Writes a TorchScript file holding the synthetic RNN-T weights under the names PipelineManager reads."""
+    m = _RnntModule(cfg)
+    sd = {}
+    for prefix, ps, layers in (("pre_rnn", w.pre, cfg.pre_layers), ("post_rnn", w.post, cfg.post_layers),
+                               ("pred_rnn", w.pred, cfg.pred_layers)):
+        for l in range(layers):
+            for k, name in enumerate(("weight_ih", "weight_hh", "bias_ih", "bias_hh")):
+                sd[f"{prefix}.{name}_l{l}"] = ps[4 * l + k]
+    sd["pred_embed.weight"] = w.embedding
+    sd["joint1.weight"], sd["joint1.bias"] = w.w1, w.b1
+    sd["joint2.weight"], sd["joint2.bias"] = w.w2, w.b2
+    m.load_state_dict(sd)
+    torch.jit.script(m).save(path)
