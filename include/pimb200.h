@@ -64,6 +64,20 @@ int pimb200_gemv_mv(const void* W, const void* x, const void* bias, void* y,
 int pimb200_gemv_vm(const void* x, const void* A, const void* bias, void* y,
                     int K, int N, int act, void* stream);
 
+/* VM without any allocation: same result as pimb200_gemv_vm, for hosts that cannot let a plug-in allocate device
+ * memory (a server that owns the whole device through its own arena, or a loop that cannot afford the device-wide
+ * synchronisation of an allocation).  No counterpart in the reference.  The split-K scratch is a fixed array inside the
+ * library image (about 1 MiB on every GPU that loads the library, held until exit); no pimb200_init is needed and no
+ * call allocates or frees.  Limits: N <= PIMB200_VM_STATIC_MAX_N, K <= PIMB200_VM_STATIC_MAX_K, N a multiple of 8
+ * and A 16-byte aligned; anything else returns PIMB200_ERR_UNSUPPORTED and launches nothing.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that first call
+ * outside any stream capture.  All calls on a device share the one array: calls that may overlap on the GPU (different
+ * streams without ordering between them) race; order them, or use pimb200_gemv_vm. */
+#define PIMB200_VM_STATIC_MAX_N 32768
+#define PIMB200_VM_STATIC_MAX_K 1048576
+int pimb200_gemv_vm_static(const void* x, const void* A, const void* bias, void* y,
+                           int K, int N, int act, void* stream);
+
 /* VV:  y[0] = sum_k a[k]*b[k].  Replaces the VV branch of customAtenMatmul (aten_ops.cpp:841-882). */
 int pimb200_dot_vv(const void* a, const void* b, void* y, int K, void* stream);
 

@@ -27,6 +27,7 @@ SIGNATURES = {
     "pimb200_shutdown": (_i, [_i]),
     "pimb200_gemv_mv": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "pimb200_gemv_vm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pimb200_gemv_vm_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "pimb200_dot_vv": (_i, [_vp, _vp, _vp, _i, _vp]),
     "pimb200_bmm_row": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
     "pimb200_gemm_wx": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
