@@ -167,6 +167,8 @@ def run_gpu(args, rank, world, local):
     d = lambda t: t.to(torch.float16).to(dev).contiguous()
     dec = RnntDecoder(cfg, [d(p) for p in w.pre], [d(p) for p in w.post], d(w.embedding), [d(p) for p in w.pred],
                       d(w.w1), d(w.b1), d(w.w2), d(w.b2))
+    if args.encoder_batch:
+        dec.set_encoder_batch(args.encoder_batch)
     S = args.streams_per_gpu
     Tp = T_FRAMES // cfg.stack_factor
     g = torch.Generator().manual_seed(1000 + rank)
@@ -244,8 +246,10 @@ def run_gpu(args, rank, world, local):
     rec_s = prof["ms"] * 1e-3
     achieved = prof["bytes"] / rec_s / 1e9 if rec_s > 0 else 0.0
     share = prof["ms"] / sum(step_ms) if sum(step_ms) > 0 else 0.0
-    # per group of 8 utterances: (projection GEMM + recurrence) per LSTM layer; then one joint GEMM and one greedy kernel
-    launches_per_step = ((S + 7) // 8) * 2 * (cfg.pre_layers + cfg.post_layers) + 2
+    # per group of encoder-batch utterances: (projection GEMM + recurrence) per LSTM layer; then one joint GEMM and
+    # one greedy kernel
+    eb = args.encoder_batch or 32
+    launches_per_step = ((S + eb - 1) // eb) * 2 * (cfg.pre_layers + cfg.post_layers) + 2
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
@@ -297,6 +301,7 @@ def main():
     ap.add_argument("--streams-per-gpu", type=int, default=128)
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--encoder-batch", type=int, default=0, help="utterances per lock-step encoder group (0 = default)")
     args = ap.parse_args()
     if args.impl == "reference":
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed

@@ -16,7 +16,7 @@ HEADER_PATHS = [os.path.join(ROOT, "include", "pimb200.h"), os.path.join(ROOT, "
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_LAUNCH, ERR_TIMEOUT, ERR_NOT_INIT, ERR_NO_MEMORY = range(7)
 ACT_NONE, ACT_RELU = 0, 1
-LSTM_AUTO, LSTM_STREAMED, LSTM_PERSISTENT = 0, 1, 2
+LSTM_AUTO, LSTM_STREAMED, LSTM_PERSISTENT, LSTM_PERSISTENT_TAGGED = 0, 1, 2, 3
 
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 

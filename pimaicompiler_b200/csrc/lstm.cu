@@ -440,6 +440,206 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
 }
 
 // ---------------------------------------------------------------------------------------------
+// persistent weight-stationary recurrence, batched variant (2 <= B <= 32 sequences in lock step)
+//
+// Same ownership and tensor-core matvec as above (8 hidden units = 32 gate rows per CTA, H/8 CTAs), with NT tiles of
+// 8 sequences per mma pass, but a different exchange: strong (relaxed.gpu) loads cost the SM a few cycles each, so
+// polling B * n_cta tagged words does not scale with B.  Here a CTA writes its B x 8 new hidden values with plain
+// 16-byte stores, fences, and raises ONE 32-bit step flag; readers poll the n_cta flags (strong loads), fence, and
+// then fetch the data with ordinary coalesced 16-byte loads.  Two L2 round trips per step instead of one, but the
+// volume moves at full L2 bandwidth.
+// ---------------------------------------------------------------------------------------------
+constexpr int kBulkMaxB = 32;              // sequences per launch of the batched variant
+constexpr int kBulkFlagCopies = 8;         // replicas of the step flags
+
+struct BulkArgs {
+    const __half* Whh;
+    const float* bias;
+    const float* G;
+    long g_tstride, g_bstride;
+    const __half* h0;
+    const __half* c0;
+    __half* y;
+    long y_tstride, y_bstride;
+    int y_vec;              // 1 = (t, n) rows of y are 16-byte aligned: one uint4 store per sequence
+    __half* hn;
+    __half* cn;
+    uint4* data;            // [2 parities][n_cta][BP] 16-byte records: the 8 hidden values of (cta, sequence)
+    uint32_t* flags;        // [kBulkFlagCopies][2 parities][n_cta] step tags, one per 128-byte line
+    uint32_t tag_base;      // flag value of step s = tag_base + s + 1
+    int* status;
+    int H, T, B;
+    int reverse;
+    int poll_limit;
+    long long* trace;       // optional diagnostics, 8 clocks per CTA and step
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kernel(BulkArgs a) {
+    constexpr int BP = NT * 8;  // sequences, padded to whole mma tiles
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, T = a.T, B = a.B;
+    const int pitch = H + 8;
+    __half* Ws = reinterpret_cast<__half*>(smem_raw);                         // [32][pitch]
+    __half* hs = Ws + (size_t)kPersistRows * pitch;                           // [BP][pitch]
+    float* part = reinterpret_cast<float*>(hs + (size_t)BP * pitch);          // [8 warps][32 rows][BP]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(part + (size_t)kPersistWarps * kPersistRows * BP);  // [BP][8]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x, cta = blockIdx.x;
+    const int u0 = cta * 8;
+    const int ktiles = H >> 4;
+    {
+        const int H8 = H >> 3;
+        const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
+        for (int i = tid; i < kPersistRows * H8; i += kPersistThreads) {
+            const int r = i / H8, c8 = i - r * H8;
+            *reinterpret_cast<uint4*>(Ws + (size_t)r * pitch + c8 * 8) = ldg_stream_v4(src + (size_t)r * H8 + c8);
+        }
+    }
+    for (int i = tid; i < BP * H; i += kPersistThreads) {
+        const int n = i / H, k = i - n * H;
+        hs[(size_t)n * pitch + k] = (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
+    }
+    for (int i = tid; i < BP * 8; i += kPersistThreads) hpub[i] = 0;
+
+    // gate thread (unit = warp, sequence = lane)
+    const bool gate_thread = lane < B;
+    const int u = u0 + warp;
+    float c = 0.f;
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gx = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gate_thread) {
+        c = a.c0 ? __half2float(a.c0[(size_t)lane * H + u]) : 0.f;
+        bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
+        const int t0 = a.reverse ? T - 1 : 0;
+        gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)lane * a.g_bstride +
+                                                    (size_t)u * 4));
+    }
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int a_col = (lane >> 4) * 8;
+    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
+    __syncthreads();
+
+    for (int s = 0; s < T; ++s) {
+        const int t = a.reverse ? T - 1 - s : s;
+        const int par = s & 1;
+        long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+        if (tr && tid == 0) tr[0] = clock64();
+        // ---- 1. Z[32 x BP] partial products, warps split K
+        float acc[2][NT][4];
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[m][nt][i] = 0.f;
+        for (int kt0 = warp; kt0 < ktiles; kt0 += 2 * kPersistWarps) {
+            uint32_t af[2][2][4], b0[2][NT], b1[2][NT];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int kt = kt0 + q * kPersistWarps;
+                const bool live = kt < ktiles;
+                const int k0 = min(kt, ktiles - 1) << 4;
+#pragma unroll
+                for (int m = 0; m < 2; ++m) ldmatrix_x4(af[q][m], Ws + (size_t)(m * 16 + a_row) * pitch + k0 + a_col);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const __half* hp = hs + (size_t)(nt * 8 + b_n) * pitch + k0 + b_k;
+                    b0[q][nt] = live ? *reinterpret_cast<const uint32_t*>(hp) : 0u;
+                    b1[q][nt] = live ? *reinterpret_cast<const uint32_t*>(hp + 8) : 0u;
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma_16816(acc[m][nt], af[q][m], b0[q][nt], b1[q][nt]);
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                float* p = part + ((size_t)warp * kPersistRows + m * 16 + (lane >> 2)) * BP + nt * 8 + b_k;
+                *reinterpret_cast<float2*>(p) = make_float2(acc[m][nt][0], acc[m][nt][1]);
+                *reinterpret_cast<float2*>(p + 8 * BP) = make_float2(acc[m][nt][2], acc[m][nt][3]);
+            }
+        __syncthreads();
+        if (tr && tid == 0) tr[1] = clock64();
+        // ---- 2. gates of (unit = warp, sequence = lane)
+        if (gate_thread) {
+            float z[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int w = 0; w < kPersistWarps; ++w)
+#pragma unroll
+                for (int g = 0; g < 4; ++g) z[g] += part[((size_t)w * kPersistRows + warp * 4 + g) * BP + lane];
+            const float zi = z[0] + gx.x + bias4.x, zf = z[1] + gx.y + bias4.y, zg = z[2] + gx.z + bias4.z,
+                        zo = z[3] + gx.w + bias4.w;
+            c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
+            const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
+            hpub[lane * 8 + warp] = __half_as_ushort(hh);
+            if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)lane * a.y_bstride + u] = hh;
+            if (s == T - 1) {
+                if (a.hn) a.hn[(size_t)lane * H + u] = hh;
+                if (a.cn) a.cn[(size_t)lane * H + u] = __float2half_rn(c);
+            }
+            if (s + 1 < T) {
+                const int tn = a.reverse ? t - 1 : t + 1;
+                gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)lane * a.g_bstride +
+                                                            (size_t)u * 4));
+            }
+        }
+        __syncthreads();
+        if (tr && tid == 0) tr[2] = clock64();
+        // ---- 3. publish: one 16-byte record per sequence, to the output tensor and to the exchange buffer
+        if (tid < B) {
+            const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
+            if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)tid * a.y_bstride + u0) = v;
+            if (s + 1 < T) {
+                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+                __threadfence();  // the record is visible device-wide before the flag can be
+            }
+        }
+        if (s + 1 == T) break;
+        __syncthreads();
+        if (tr && tid == 0) tr[3] = clock64();
+        const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        // the flag goes to every replica; each flag has a 128-byte line of its own, so a line is polled by n_cta/replicas CTAs
+        if (tid < kBulkFlagCopies)
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+        // ---- 4. wait for every CTA's flag of this step
+        int timed_out = 0;
+        if (tid < n_cta) {
+            const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + tid) * 32;
+            int polls = 0;
+            while (true) {
+                uint32_t v;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (v == tag) break;
+                if (++polls >= a.poll_limit) { timed_out = 1; break; }
+                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+            }
+            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            if (tr && tid == 0) tr[4] = clock64();
+            __threadfence();  // acquire side: loads below are ordered after the flag reads
+            if (tr && tid == 0) tr[5] = clock64();
+        }
+        if (__syncthreads_or(timed_out)) return;
+        if (tr && tid == 0) tr[6] = clock64();
+        // ---- 5. fetch all records with plain coalesced loads: item = (cta, sequence)
+        {
+            const uint4* src = a.data + (size_t)par * n_cta * BP;
+            const int items = n_cta * BP;
+            for (int i = tid; i < items; i += kPersistThreads) {
+                const int n = i % BP, j = i / BP;
+                if (n < B) *reinterpret_cast<uint4*>(hs + (size_t)n * pitch + j * 8) = src[i];
+            }
+        }
+        __syncthreads();
+        if (tr && tid == 0) tr[7] = clock64();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct pimb200_lstm {
@@ -457,6 +657,9 @@ struct pimb200_lstm {
     float* cstate = nullptr;
     size_t c_cap = 0;
     uint4* xchg = nullptr;  // [kXchgCopies][2][kXchgWords]
+    uint4* bulk_data = nullptr;      // batched variant: [2][n_cta][32] records
+    uint32_t* bulk_flags = nullptr;  // [2][n_cta]
+    uint32_t bulk_tag = 0;
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
@@ -493,6 +696,8 @@ extern "C" int pimb200_lstm_destroy(pimb200_lstm* h) {
     cudaFree(h->ybuf[1]);
     cudaFree(h->cstate);
     cudaFree(h->xchg);
+    cudaFree(h->bulk_data);
+    cudaFree(h->bulk_flags);
     cudaFree(h->d_status);
     for (auto e : h->prof_ev) cudaEventDestroy(e);
     delete h;
@@ -537,6 +742,13 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
     if (cudaMalloc(&h->xchg, kXchgBytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
     if (cudaMalloc(&h->d_status, 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
     cudaMemset(h->xchg, 0, kXchgBytes);
+    {
+        const size_t ncta = (size_t)ceil_div(H, 8);
+        if (cudaMalloc(&h->bulk_data, 2 * ncta * kBulkMaxB * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+        const size_t flag_bytes = (size_t)kBulkFlagCopies * 2 * ncta * 128;
+        if (cudaMalloc(&h->bulk_flags, flag_bytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+        cudaMemset(h->bulk_flags, 0, flag_bytes);
+    }
     cudaMemset(h->d_status, 0, 4);
     if ((rc = cuda_status(cudaDeviceSynchronize())) != PIMB200_OK) return fail(rc);
     *out = h;
@@ -544,7 +756,7 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
 }
 
 extern "C" int pimb200_lstm_set_variant(pimb200_lstm* h, int variant) {
-    if (!h || variant < 0 || variant > 2) return PIMB200_ERR_BAD_ARG;
+    if (!h || variant < 0 || variant > 3) return PIMB200_ERR_BAD_ARG;
     h->variant = variant;
     return PIMB200_OK;
 }
@@ -625,6 +837,11 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
     return PIMB200_OK;
 }
 
+static size_t bulk_smem(int H, int nt) {
+    const int BP = nt * 8;
+    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * (H + 8) * 2 + (size_t)kPersistWarps * kPersistRows * BP * 4 +
+           (size_t)BP * 16;
+}
 struct PersistPlan { bool ok; int U, ncta, threads; size_t smem; };
 static size_t persist_smem(int H, int B) {
     return (size_t)kPersistRows * (H + 8) * 2 + (size_t)2 * B * (H + 8) * 2 +
@@ -661,11 +878,43 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     bool use_persistent = false;
     PersistPlan pp = plan_persistent(h);
     const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
+    const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : 4);
+    const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
+                           B <= kBulkMaxB && !packed && (int)bulk_smem(H, nt) <= h->max_smem_optin;
+    bool use_bulk = false;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
+        if (!fits && !bulk_fits) return PIMB200_ERR_UNSUPPORTED;
+        use_bulk = bulk_fits;
+        use_persistent = !use_bulk;
+    } else if (h->variant == PIMB200_LSTM_PERSISTENT_TAGGED) {
         if (!fits) return PIMB200_ERR_UNSUPPORTED;
         use_persistent = true;
     } else if (h->variant == PIMB200_LSTM_AUTO) {
-        use_persistent = fits && T >= 8;
+        use_bulk = bulk_fits && T >= 8;
+        use_persistent = !use_bulk && fits && T >= 8;
+    }
+    if (use_bulk) {
+        BulkArgs a;
+        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
+        a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
+        a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
+        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status;
+        a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+        a.trace = h->trace;
+        h->bulk_tag += (uint32_t)T + 1u;
+        const void* fn = nt == 1 ? (const void*)lstm_persistent_bulk_kernel<1>
+                       : nt == 2 ? (const void*)lstm_persistent_bulk_kernel<2>
+                                 : (const void*)lstm_persistent_bulk_kernel<4>;
+        const size_t smem = bulk_smem(H, nt);
+        PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        void* kargs[] = {&a};
+        if (h->prof) prof_mark(h, st);
+        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(kPersistThreads), kargs, smem, st));
+        if (h->prof) {
+            prof_mark(h, st);
+            h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
+        }
+        return PIMB200_OK;
     }
     if (use_persistent) {
         PersistArgs a;

@@ -322,7 +322,7 @@ struct pimb200_rnnt {
     size_t cap_frames = 0;  // frames*utts capacity of the three buffers above
     long long* trace = nullptr;  // diagnostics buffer (not owned)
     GreedyFn fn = nullptr;
-    int enc_batch = 8;      // utterances the encoder advances in lock step
+    int enc_batch = 32;     // utterances the encoder advances in lock step
     int cluster = 0;        // CTAs per cluster
     int smem_mask = 0;
     size_t smem_bytes = 0;
@@ -483,7 +483,7 @@ extern "C" int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long
 }
 
 extern "C" int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n) {
-    if (!h || n < 1 || n > 8) return PIMB200_ERR_BAD_ARG;
+    if (!h || n < 1 || n > 32) return PIMB200_ERR_BAD_ARG;
     h->enc_batch = n;
     return PIMB200_OK;
 }

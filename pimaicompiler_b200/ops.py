@@ -12,7 +12,8 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import ACT_NONE, ACT_RELU, LSTM_AUTO, LSTM_PERSISTENT, LSTM_STREAMED, check  # noqa: F401
+from ._lib import (ACT_NONE, ACT_RELU, LSTM_AUTO, LSTM_PERSISTENT, LSTM_PERSISTENT_TAGGED,  # noqa: F401
+                   LSTM_STREAMED, check)
 
 _initialised: set[int] = set()
 

@@ -54,7 +54,7 @@ class RnntDecoder:
         return {"cluster_size": cs.value, "smem_mask": mask.value, "smem_bytes": sm.value}
 
     def set_encoder_batch(self, n: int) -> None:
-        """Utterances the encoder advances in lock step (1..8)."""
+        """Utterances the encoder advances in lock step (1..32)."""
         check(_lib.lib().pimb200_rnnt_set_encoder_batch(self._h, int(n)), "rnnt_set_encoder_batch")
 
     def profile(self, enable: bool) -> None:

@@ -81,18 +81,23 @@ CASES = [
     (7, 5, 24, 48, 2, True, True, True, True),           # B > 1, bidirectional, batch_first
     (11, 8, 40, 128, 2, False, True, False, True),       # a full tile of sequences
     (6, 8, 240, 1024, 1, False, True, True, False),      # eight utterances at the encoder width
-    (5, 11, 16, 32, 1, False, True, False, True),        # B > 8: streamed only
+    (5, 11, 16, 32, 1, False, True, False, True),        # two tiles of sequences, the second ragged
+    (9, 32, 64, 256, 2, False, True, True, True),        # four full tiles, batch_first
+    (4, 19, 24, 1024, 1, True, True, False, True),       # ragged third tile, bidirectional, encoder width
+    (3, 40, 16, 32, 1, False, True, False, True),        # B > 32: streamed only
     (3, 2, 7, 5, 2, False, True, False, True),           # odd sizes: scalar path
 ]
 
 
 @pytest.mark.parametrize("case", CASES)
-@pytest.mark.parametrize("variant", ["streamed", "persistent"])
+@pytest.mark.parametrize("variant", ["streamed", "persistent", "tagged"])
 def test_lstm_matches_oracle(case, variant):
     ops = _ops()
     T, B, I, H, L, bi, hb, bf, nz = case
-    if variant == "persistent" and (B > 8 or H % 16):
-        pytest.skip("persistent variant takes up to 8 sequences and H % 16 == 0")
+    if variant == "persistent" and (B > 32 or H % 16):
+        pytest.skip("persistent variants take up to 32 sequences and H % 16 == 0")
+    if variant == "tagged" and (B > 8 or H % 16):
+        pytest.skip("tagged-word exchange takes up to 8 sequences and H % 16 == 0")
     D = 2 if bi else 1
     g = torch.Generator().manual_seed(T * 131 + H)
     ps = lstm_params(L, D, I, H, g, has_biases=hb)
@@ -101,7 +106,8 @@ def test_lstm_matches_oracle(case, variant):
     c0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5) if nz else None
     ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, bi, hb, None if h0 is None else h0.numpy(),
                   None if c0 is None else c0.numpy(), bf)
-    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, ops.LSTM_STREAMED if variant == "streamed" else ops.LSTM_PERSISTENT)
+    vid = {"streamed": ops.LSTM_STREAMED, "persistent": ops.LSTM_PERSISTENT, "tagged": ops.LSTM_PERSISTENT_TAGGED}[variant]
+    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, vid)
     for name, a, b in zip(("y", "hn", "cn"), got, ref):
         assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"{variant} {name} {case}")
 
