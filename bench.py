@@ -292,12 +292,136 @@ def run_gpu(args, rank, world, local):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# secondary workloads: the stand-alone op sweeps of the baseline (C2 GEMV/GEMM, C1 single aten::lstm)
+# ------------------------------------------------------------------------------------------------
+def _graph_time_us(calls, reps):
+    """Average device time of one call: all calls are captured into one CUDA graph (no host launch cost between
+    kernels), replayed `reps` times between two CUDA events on the launching stream."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for f in calls[:2]:
+            f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in calls:
+            f()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
+
+
+def run_c2(args):
+    """C2: y = Wx + b at batch 1 for the five (N,K) shapes (weights rotated over > 126 MB so every call streams from
+    HBM), and the same layers at batch 8/32/128 through the tensor-core GEMM."""
+    from pimaicompiler_b200 import build, ops
+    build.build()
+    ops.init()
+    peak, peak_src = load_peaks()
+    dev = torch.device("cuda", 0)
+    shapes = [(4096, 1024), (4096, 2048), (1024, 1024), (32320, 1024), (29, 512)]
+    g = torch.Generator().manual_seed(1)
+    results = []
+    sampler = ClockSampler(0)
+    sampler.start()
+    for (N, K) in shapes:
+        nb = max(2, min(96, int(400e6 // (N * K * 2)) + 1))       # > 126 MB of distinct weights where it matters
+        k = 1.0 / K ** 0.5
+        Ws = [((torch.rand(N, K, generator=g) * 2 - 1) * k).half().to(dev) for _ in range(nb)]
+        b = ((torch.rand(N, generator=g) * 2 - 1) * k).half().to(dev)
+        x = torch.randn(K, generator=g).half().to(dev)
+        y = torch.empty(N, dtype=torch.float16, device=dev)
+        us = _graph_time_us([(lambda W=W: ops.gemv_mv(W, x, b, out=y)) for W in Ws], args.steps * 10)
+        us_l2 = _graph_time_us([(lambda: ops.gemv_mv(Ws[0], x, b, out=y)) for _ in range(nb)], args.steps * 10)
+        As = [W.t().contiguous() for W in Ws[: min(nb, 24)]]
+        us_vm = _graph_time_us([(lambda A=A: ops.gemv_vm(x, A, b, out=y)) for A in As], args.steps * 10)
+        nbytes = 2 * (N * K + K + 2 * N)
+        row = {"N": N, "K": K, "B": 1, "bytes": nbytes, "mv_us": us, "mv_gbs": nbytes / us / 1e3,
+               "mv_frac_of_measured_hbm": nbytes / us / 1e3 / peak, "mv_l2_resident_us": us_l2,
+               "vm_us": us_vm, "vm_gbs": nbytes / us_vm / 1e3, "weights_rotated_mb": nb * N * K * 2 / 1e6}
+        results.append(row)
+        for B in (8, 32, 128):
+            X = torch.randn(B, K, generator=g).half().to(dev)
+            Y = torch.empty(B, N, dtype=torch.float16, device=dev)
+            usb = _graph_time_us([(lambda W=W: ops.gemm_wx(W, X, b, out=Y)) for W in Ws], args.steps * 10)
+            bb = 2 * (N * K + B * K + N + B * N)
+            results.append({"N": N, "K": K, "B": B, "bytes": bb, "gemm_us": usb, "gemm_gbs": bb / usb / 1e3,
+                            "gemm_tflops": 2.0 * B * N * K / usb / 1e6})
+        del Ws, As
+    clocks = sampler.stop()
+    big = next(r for r in results if r["N"] == 32320 and r["B"] == 1)
+    line = {"metric": "gemv_mv_hbm_gbs", "value": big["mv_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": 3, "ms_per_step": big["mv_us"] / 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "C2: aten::linear batch-1 GEMV sweep + batch 8/32/128 GEMM", "headline_shape": [32320, 1024],
+                       "l2": "weights rotated over more distinct buffers than fit the 126 MB L2",
+                       "timing": "CUDA graph of the rotated calls, CUDA events around the replays"},
+            "roofline": {"bound": "hbm", "kernel": "gemv_mv_vec_kernel<4> (32320x1024)", "achieved": big["mv_gbs"],
+                         "peak": peak, "unit": "GB/s", "frac": big["mv_gbs"] / peak, "peak_source": peak_src,
+                         "traffic": None},
+            "results": results, "clocks": clocks, "gpu_launches": None}
+    print(json.dumps(line), flush=True)
+
+
+def run_c1(args):
+    """C1: one aten::lstm, 2 layers, input 240, hidden 1024, T=200, batch 1 (seed 0), every recurrence variant."""
+    from pimaicompiler_b200 import build, ops
+    build.build()
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    T, I, H, L = 200, 240, 1024, 2
+    x = torch.randn(T, 1, I).half().to(dev)
+    ps = []
+    for l in range(L):
+        Il = I if l == 0 else H
+        ps += [((torch.rand(4 * H, Il) * 2 - 1) / 32).half().to(dev), ((torch.rand(4 * H, H) * 2 - 1) / 32).half().to(dev),
+               ((torch.rand(4 * H) * 2 - 1) / 32).half().to(dev), ((torch.rand(4 * H) * 2 - 1) / 32).half().to(dev)]
+    m = ops.Lstm(ps, L, False, I, H, True)
+    peak, peak_src = load_peaks()
+    res = {}
+    for name, v in (("streamed", ops.LSTM_STREAMED), ("persistent", ops.LSTM_PERSISTENT)):
+        m.set_variant(v)
+        out = m.forward(x)
+        for _ in range(3):
+            m.forward(x, out=out)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps * 5):
+            m.forward(x, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (args.steps * 5)
+        res[name] = {"us_per_call": us, "us_per_layer_step": us / (T * L),
+                     "w_hh_stream_gbs": T * L * 4 * H * H * 2 / us / 1e3}
+    best = res["persistent"]
+    line = {"metric": "lstm_c1_us_per_call", "value": best["us_per_call"], "unit": "us", "n_gpus": 1,
+            "steps": args.steps, "warmup": 3, "ms_per_step": best["us_per_call"] / 1e3, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "C1: aten::lstm L=2 I=240 H=1024 T=200 B=1"},
+            "roofline": {"bound": "hbm", "kernel": "lstm_persistent_kernel", "achieved": best["w_hh_stream_gbs"],
+                         "peak": peak, "unit": "GB/s", "frac": best["w_hh_stream_gbs"] / peak, "peak_source": peak_src,
+                         "traffic": None, "note": "whole call (projection GEMMs included); bytes = T*L*4H*H*2"},
+            "results": res, "gpu_launches": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1"],
+                    help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm")
     ap.add_argument("--streams-per-gpu", type=int, default=128)
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -306,6 +430,10 @@ def main():
     if args.impl == "reference":
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed
         run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
+        return
+    if args.workload in ("c1", "c2"):
+        if int(os.environ.get("RANK", "0")) == 0:
+            (run_c2 if args.workload == "c2" else run_c1)(args)
         return
     rank, world, local = dist_setup(args.gpus)
     try:

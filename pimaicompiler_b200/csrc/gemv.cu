@@ -13,25 +13,17 @@ namespace pimb200 {
 // =============================================================================================
 // MV:  y[n] = act(sum_k W[n,k] x[k] + b[n])
 // One warp owns R consecutive rows; a lane walks the row in 16-byte chunks (stride 32 chunks),
-// so a warp reads 512 contiguous bytes per row per iteration.  x is staged once per CTA in
-// shared memory.  R*unroll independent 16-byte loads are in flight per lane.
+// so a warp reads 512 contiguous bytes per row per iteration.  W bypasses L1 (read once); x is
+// read through L1 (it is a few KB and every warp reads all of it) — staging it in shared memory
+// first costs a barrier before the first weight load and measured slower.  R*unroll independent
+// 16-byte loads are in flight per lane.
 // =============================================================================================
-template <int R, bool XSMEM>
+template <int R>
 __global__ void __launch_bounds__(256) gemv_mv_vec_kernel(const __half* __restrict__ W, const __half* __restrict__ x,
                                                           const __half* __restrict__ bias, __half* __restrict__ y,
                                                           int N, int K, int act) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K8 = K >> 3;
-    const uint4* xs4;
-    if (XSMEM) {
-        uint4* s = reinterpret_cast<uint4*>(smem_raw);
-        const uint4* xg = reinterpret_cast<const uint4*>(x);
-        for (int c = threadIdx.x; c < K8; c += blockDim.x) s[c] = __ldg(xg + c);
-        __syncthreads();
-        xs4 = s;
-    } else {
-        xs4 = reinterpret_cast<const uint4*>(x);
-    }
+    const uint4* x4 = reinterpret_cast<const uint4*>(x);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = (blockIdx.x * (blockDim.x >> 5) + warp) * R;
     if (row0 >= N) return;
@@ -47,7 +39,7 @@ __global__ void __launch_bounds__(256) gemv_mv_vec_kernel(const __half* __restri
 #pragma unroll 4
     for (int c = lane; c < K8; c += 32) {
         float xf[8];
-        widen8(xs4[c], xf);
+        widen8(__ldg(x4 + c), xf);
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = dot8f(ldg_stream_v4(wrow[r] + c), xf, acc[r]);
     }
@@ -91,26 +83,14 @@ static int launch_gemv_mv(const __half* W, const __half* x, const __half* bias, 
         gemv_mv_generic_kernel<<<ceil_div(N, 8), 256, 0, st>>>(W, x, bias, y, N, K, act);
         return launch_status();
     }
-    const size_t xbytes = (size_t)K * 2;
-    const bool xsmem = xbytes <= 48 * 1024;
-    const size_t smem = xsmem ? xbytes : 0;
     // rows per warp: enough warps to cover every SM several times, else fewer rows per warp
     const long warps4 = ((long)N + 3) / 4, warps2 = ((long)N + 1) / 2;
     const long want = (long)kNumSmB200 * 8 * 2;
-    int R = warps4 >= want ? 4 : (warps2 >= want ? 2 : 1);
-    const int rows_per_cta = 8 * R;
-    const int grid = ceil_div(N, rows_per_cta);
-#define MV_LAUNCH(RR)                                                                               \
-    do {                                                                                            \
-        if (xsmem)                                                                                  \
-            gemv_mv_vec_kernel<RR, true><<<grid, 256, smem, st>>>(W, x, bias, y, N, K, act);        \
-        else                                                                                        \
-            gemv_mv_vec_kernel<RR, false><<<grid, 256, 0, st>>>(W, x, bias, y, N, K, act);          \
-    } while (0)
-    if (R == 4) MV_LAUNCH(4);
-    else if (R == 2) MV_LAUNCH(2);
-    else MV_LAUNCH(1);
-#undef MV_LAUNCH
+    const int R = warps4 >= want ? 4 : (warps2 >= want ? 2 : 1);
+    const int grid = ceil_div(N, 8 * R);
+    if (R == 4) gemv_mv_vec_kernel<4><<<grid, 256, 0, st>>>(W, x, bias, y, N, K, act);
+    else if (R == 2) gemv_mv_vec_kernel<2><<<grid, 256, 0, st>>>(W, x, bias, y, N, K, act);
+    else gemv_mv_vec_kernel<1><<<grid, 256, 0, st>>>(W, x, bias, y, N, K, act);
     return launch_status();
 }
 
@@ -143,7 +123,7 @@ __global__ void __launch_bounds__(256) gemv_vm_vec_kernel(const __half* __restri
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     if (col < N) {
-#pragma unroll 4
+#pragma unroll 8
         for (int k = k0 + warp * RPW + sub; k < k1; k += 8 * RPW) {
             const uint4 a = ldg_stream_v4(A + (size_t)k * N + col);
             const float xk = __half2float(__ldg(x + k));
@@ -232,8 +212,8 @@ VmPlan plan_gemv_vm(int K, int N, size_t max_partial_floats, int max_tiles) {
     const int tile = p.lpr * 8;
     p.tiles = ceil_div(N, tile);
     const int rows_per_pass = 8 * (32 / p.lpr);       // rows a CTA covers per pass
-    int want = ceil_div(2 * kNumSmB200, p.tiles);     // about two CTAs per SM
-    int max_by_rows = K / (rows_per_pass * 2);        // keep at least two passes per CTA
+    int want = ceil_div(4 * kNumSmB200, p.tiles);     // about four CTAs per SM
+    int max_by_rows = K / (rows_per_pass * 4);        // keep at least four passes per CTA
     if (max_by_rows < 1) max_by_rows = 1;
     int S = want < max_by_rows ? want : max_by_rows;
     if (S < 1) S = 1;
