@@ -1,0 +1,182 @@
+"""GNMT-style and Transformer-style greedy decode steps written once against a small backend interface, so the same
+model code runs on the libtorch-CPU oracle (fp32) and on the device ops of this library (fp16 through the C ABI).
+
+Random-init weights of the benchmark's architectures (C4: 4-layer LSTM decoder with normalised Bahdanau attention and a
+vocabulary projection; C5: Transformer decoder layers with a KV cache); the corpora and checkpoints are not available
+offline.  The hot ops (lstm with seq_len 1, batch-1 linear with fused ReLU, fp16 add, single-row bmm, cat / KV append)
+go through the backend; softmax, layer norm and tanh stay with torch on either side, as they do in the reference.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+def u(shape, fan_in, gen, gain=1.0):
+    k = gain / math.sqrt(fan_in)
+    return ((torch.rand(*shape, generator=gen) * 2 - 1) * k).to(torch.float16).to(torch.float32)
+
+
+class CpuBackend:
+    """libtorch CPU fp32: the calls the reference's default executors make."""
+    dev, dtype = "cpu", torch.float32
+
+    def put(self, t):
+        return t.clone()
+
+    def linear(self, x, W, b=None, relu=False):
+        y = torch.nn.functional.linear(x, W, b)
+        return torch.relu(y) if relu else y
+
+    def lstm_cell_stack(self, key, x, h, c, params, layers):
+        y, hn, cn = torch.lstm(x.view(1, 1, -1), [h, c], params, True, layers, 0.0, False, False, False)
+        return y.view(-1), hn, cn
+
+    def add(self, a, b):
+        return a + b
+
+    def bmm_row(self, x, A):
+        return x @ A
+
+    def cat(self, ts, dim):
+        return torch.cat(ts, dim)
+
+
+class PimBackend:
+    """fp16 device ops through libpimb200.so."""
+    dev, dtype = "cuda", torch.float16
+
+    def __init__(self):
+        from pimaicompiler_b200 import ops
+        self.ops = ops
+        ops.init()
+        self._lstm = {}
+
+    def put(self, t):
+        return t.to(torch.float16).cuda().contiguous()
+
+    def linear(self, x, W, b=None, relu=False):
+        o = self.ops
+        if x.dim() == 1:
+            return o.gemv_mv(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE)
+        return o.gemm_wx(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE)
+
+    def lstm_cell_stack(self, key, x, h, c, params, layers):
+        if key not in self._lstm:
+            self._lstm[key] = self.ops.Lstm(params, layers, False, params[0].shape[1], params[1].shape[1], True)
+        y, hn, cn = self._lstm[key].forward(x.view(1, 1, -1).contiguous(), h.contiguous(), c.contiguous())
+        return y.view(-1), hn, cn
+
+    def add(self, a, b):
+        return self.ops.add_f16(a.contiguous(), b.contiguous())
+
+    def bmm_row(self, x, A):
+        return self.ops.bmm_row(x.contiguous(), A.contiguous())
+
+    def cat(self, ts, dim):
+        return self.ops.cat([t.contiguous() for t in ts], dim)
+
+
+# ------------------------------------------------------------------------------------------------ GNMT-style decoder
+def make_gnmt(H, V, src_len, gen, gain=1.0):
+    w = {"emb": torch.randn(V, H, generator=gen).half().float() * 0.5,
+         "keys": torch.tanh(torch.randn(src_len, H, generator=gen)).half().float(),   # encoder states
+         "Wq": u((H, H), H, gen, gain), "Wk": u((H, H), H, gen, gain), "att_b": u((H,), H, gen, gain),
+         "att_v": u((H,), H, gen, gain), "att_g": torch.tensor(1.0),
+         "Wc": u((V, H), H, gen, gain), "bc": u((V,), H, gen, gain)}
+    for l in range(4):
+        I = H if l == 0 else 2 * H
+        w[f"l{l}"] = [u((4 * H, I), H, gen, gain), u((4 * H, H), H, gen, gain), u((4 * H,), H, gen, gain),
+                      u((4 * H,), H, gen, gain)]
+    return w
+
+
+def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
+    """Returns (token ids, logits [steps, V]).  One decoder step: LSTM1 -> attention context -> cat -> 3 LSTMs with
+    residual adds -> vocabulary projection -> argmax; `forced[t]` overrides the fed-back token ("follow" mode)."""
+    W = {k: ([be.put(t) for t in v] if isinstance(v, list) else be.put(v)) for k, v in w.items()}
+    keys_proj = be.linear(W["keys"], W["Wk"])                               # [S, H], once per sentence
+    v_norm = W["att_v"].float() / W["att_v"].float().norm() * float(w["att_g"])
+    hs = [torch.zeros(1, 1, H, dtype=be.dtype, device=be.dev) for _ in range(4)]
+    cs = [torch.zeros(1, 1, H, dtype=be.dtype, device=be.dev) for _ in range(4)]
+    tok, toks, logits = bos, [], []
+    for t in range(steps):
+        x = W["emb"][tok]
+        y0, hs[0], cs[0] = be.lstm_cell_stack("l0", x, hs[0], cs[0], W["l0"], 1)
+        q = be.linear(y0, W["Wq"])
+        e = torch.tanh((keys_proj.float() + q.float() + W["att_b"].float())) @ v_norm          # [S]
+        att = torch.softmax(e, 0).to(be.dtype)
+        ctx = be.bmm_row(att, W["keys"])                                    # [H]
+        x1 = be.cat([y0.view(1, H), ctx.view(1, H)], 1).view(-1)            # the {1,1,2048} buffer of the reference
+        y1, hs[1], cs[1] = be.lstm_cell_stack("l1", x1, hs[1], cs[1], W["l1"], 1)
+        x2 = be.cat([y1.view(1, H), ctx.view(1, H)], 1).view(-1)
+        y2, hs[2], cs[2] = be.lstm_cell_stack("l2", x2, hs[2], cs[2], W["l2"], 1)
+        r2 = be.add(y2, y1)                                                 # residual connections
+        x3 = be.cat([r2.view(1, H), ctx.view(1, H)], 1).view(-1)
+        y3, hs[3], cs[3] = be.lstm_cell_stack("l3", x3, hs[3], cs[3], W["l3"], 1)
+        r3 = be.add(y3, r2)
+        lg = be.linear(r3, W["Wc"], W["bc"]).float().cpu()
+        logits.append(lg)
+        best = int(torch.argmax(lg))
+        toks.append(best)
+        tok = best if forced is None else int(forced[t])
+    return toks, torch.stack(logits)
+
+
+# ------------------------------------------------------------------------------------ Transformer-style decoder
+def make_transformer(d, heads, ffn, V, layers, src_len, gen, gain=1.0):
+    w = {"emb": torch.randn(V, d, generator=gen).half().float() * 0.3, "Wo": u((V, d), d, gen, gain),
+         "mem": torch.randn(src_len, d, generator=gen).half().float() * 0.5, "layers": []}
+    for _ in range(layers):
+        L = {}
+        for name in ("sq", "sk", "sv", "so", "cq", "ck", "cv", "co"):
+            L[name] = u((d, d), d, gen, gain)
+            L[name + "_b"] = u((d,), d, gen, gain)
+        L["f1"], L["f1_b"] = u((ffn, d), d, gen, gain), u((ffn,), d, gen, gain)
+        L["f2"], L["f2_b"] = u((d, ffn), ffn, gen, gain), u((d,), ffn, gen, gain)
+        w["layers"].append(L)
+    return w
+
+
+def _attend(q, K, Vv, heads):
+    """q [d], K/V [t, d] -> [d]; per-head scaled dot-product attention (not a hot-path op: torch on either side)."""
+    d = q.numel()
+    hd = d // heads
+    qh = q.float().view(heads, 1, hd)
+    Kh = K.float().view(-1, heads, hd).transpose(0, 1)
+    Vh = Vv.float().view(-1, heads, hd).transpose(0, 1)
+    p = torch.softmax(qh @ Kh.transpose(1, 2) / math.sqrt(hd), -1)
+    return (p @ Vh).reshape(d)
+
+
+def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
+    ln = lambda x: torch.nn.functional.layer_norm(x.float(), (d,)).to(be.dtype)
+    P = lambda t: be.put(t)
+    emb, Wo, mem = P(w["emb"]), P(w["Wo"]), P(w["mem"])
+    Ls = [{k: P(v) for k, v in L.items()} for L in w["layers"]]
+    cross = [(be.linear(mem, L["ck"], L["ck_b"]), be.linear(mem, L["cv"], L["cv_b"])) for L in Ls]
+    kcache = [torch.zeros(0, d, dtype=be.dtype, device=be.dev) for _ in Ls]
+    vcache = [torch.zeros(0, d, dtype=be.dtype, device=be.dev) for _ in Ls]
+    tok, toks, logits = bos, [], []
+    for t in range(steps):
+        x = emb[tok]
+        for i, L in enumerate(Ls):
+            q = be.linear(x, L["sq"], L["sq_b"])
+            k = be.linear(x, L["sk"], L["sk_b"])
+            v = be.linear(x, L["sv"], L["sv_b"])
+            kcache[i] = be.cat([kcache[i], k.view(1, d)], 0) if kcache[i].shape[0] else k.view(1, d).clone()  # KV append
+            vcache[i] = be.cat([vcache[i], v.view(1, d)], 0) if vcache[i].shape[0] else v.view(1, d).clone()
+            a = _attend(q, kcache[i], vcache[i], heads).to(be.dtype)
+            x = ln(be.add(x, be.linear(a, L["so"], L["so_b"])))
+            cq = be.linear(x, L["cq"], L["cq_b"])
+            ca = _attend(cq, cross[i][0], cross[i][1], heads).to(be.dtype)
+            x = ln(be.add(x, be.linear(ca, L["co"], L["co_b"])))
+            f = be.linear(be.linear(x, L["f1"], L["f1_b"], relu=True), L["f2"], L["f2_b"])
+            x = ln(be.add(x, f))
+        lg = be.linear(x, Wo).float().cpu()
+        logits.append(lg)
+        best = int(torch.argmax(lg))
+        toks.append(best)
+        tok = best if forced is None else int(forced[t])
+    return toks, torch.stack(logits)

@@ -1,0 +1,43 @@
+"""GPU parity of the remaining benchmark configurations as test cases: a GNMT-style and a Transformer-style greedy
+decode whose hot ops run through the C ABI, against the same model on libtorch CPU fp32.  The oracle replays the
+device's token choices, so the logits of every step are comparable; token ids must equal the oracle's argmax wherever
+its top-2 margin exceeds 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from tests import decode_models as dm
+from tests.util import CONTRACT_ATOL, CONTRACT_RTOL, assert_close
+
+pytestmark = pytest.mark.gpu
+MARGIN = 1e-2
+
+
+def _check(gpu_toks, gpu_logits, ref_logits):
+    assert_close(gpu_logits, ref_logits, CONTRACT_ATOL, CONTRACT_RTOL, "decode logits")
+    srt = np.sort(ref_logits.numpy(), axis=1)
+    decided = (srt[:, -1] - srt[:, -2]) > MARGIN
+    ref_choice = ref_logits.argmax(1).numpy()
+    assert (ref_choice[decided] == np.asarray(gpu_toks)[decided]).all()
+    return int(decided.sum())
+
+
+@pytest.mark.parametrize("H,V,S,steps,gain", [(128, 500, 13, 12, 3.0), (1024, 32320, 37, 6, 2.0)])
+def test_gnmt_style_greedy_decode(H, V, S, steps, gain):
+    gen = torch.Generator().manual_seed(H + S)
+    w = dm.make_gnmt(H, V, S, gen, gain)
+    toks, logits = dm.gnmt_greedy(dm.PimBackend(), w, H, steps)
+    _, ref_logits = dm.gnmt_greedy(dm.CpuBackend(), w, H, steps, forced=toks)
+    n = _check(toks, logits, ref_logits)
+    print(f"GNMT H={H} V={V}: {n}/{steps} decided steps")
+
+
+@pytest.mark.parametrize("d,heads,ffn,V,layers,S,steps,gain", [(64, 4, 128, 300, 2, 9, 10, 3.0),
+                                                               (512, 8, 2048, 32000, 6, 40, 5, 2.0)])
+def test_transformer_style_greedy_decode(d, heads, ffn, V, layers, S, steps, gain):
+    gen = torch.Generator().manual_seed(d + S)
+    w = dm.make_transformer(d, heads, ffn, V, layers, S, gen, gain)
+    toks, logits = dm.transformer_greedy(dm.PimBackend(), w, d, heads, steps)
+    _, ref_logits = dm.transformer_greedy(dm.CpuBackend(), w, d, heads, steps, forced=toks)
+    n = _check(toks, logits, ref_logits)
+    print(f"Transformer d={d} V={V}: {n}/{steps} decided steps")
