@@ -174,3 +174,30 @@ def test_lstm_outputs_alias_slices_of_caller_buffers():
     assert_close(state_buf[2:3], ref[1], LSTM_ATOL, LSTM_RTOL, "aliased hn")
     assert_close(state_buf[3:4], ref[2], LSTM_ATOL, LSTM_RTOL, "aliased cn")
     assert (cat_buf[..., 1024:] == 5).all() and (state_buf[:2] == 5).all() and (state_buf[4:] == 5).all()
+
+
+@pytest.mark.parametrize("B", [1, 4])
+def test_persistent_bounded_wait_reports_timeout_and_context_survives(B):
+    # Fault handling without faulting anything: shrink the bounded wait to a single poll, so the hidden-state exchange
+    # cannot complete in time; the kernel must give up, record ERR_TIMEOUT and return, and the next call (normal
+    # limit) must still be correct.
+    ops = _ops()
+    from pimaicompiler_b200 import _lib
+    g = torch.Generator().manual_seed(17)
+    T, I, H, L = 64, 32, 256, 1
+    ps = lstm_params(L, 1, I, H, g)
+    x = h16(torch.randn(T, B, I, generator=g))
+    m = ops.Lstm([to_dev(p) for p in ps], L, False, I, H, True)
+    m.set_variant(ops.LSTM_PERSISTENT)
+    lib = _lib.lib()
+    assert lib.pimb200_lstm_set_poll_limit(m._h, 1) == 0
+    m.forward(to_dev(x))
+    torch.cuda.synchronize()                      # returns: nothing hangs
+    assert m.last_status() == _lib.ERR_TIMEOUT
+    assert m.last_status() == 0                   # reading clears it
+    assert lib.pimb200_lstm_set_poll_limit(m._h, 1 << 21) == 0
+    y, hn, cn = m.forward(to_dev(x))
+    torch.cuda.synchronize()
+    assert m.last_status() == 0
+    ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, False)
+    assert_close(y, ref[0], LSTM_ATOL, LSTM_RTOL, "after a timed-out launch")
