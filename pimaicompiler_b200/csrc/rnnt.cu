@@ -294,6 +294,290 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
     cluster.sync();  // no CTA leaves while a peer may still address its shared memory
 }
 
+// z[i][m] += W[row_i, :] . h_m for M hidden vectors at once: every weight chunk is loaded once and used M times
+template <int NR, int M>
+__device__ __forceinline__ void rows_dot_multi(const __half* __restrict__ W, int rows, int K, const __half* const* h,
+                                               unsigned live, int warp, int lane, float (*z)[M]) {
+    const int K8 = K >> 3;
+    for (int c = lane; c < K8; c += 32) {
+        uint4 wv[NR];
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+            const int r = min(warp + kGreedyWarps * i, rows - 1);
+            wv[i] = reinterpret_cast<const uint4*>(W + (size_t)r * K)[c];
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (live & (1u << m)) {
+                float xf[8];
+                widen8(reinterpret_cast<const uint4*>(h[m])[c], xf);
+#pragma unroll
+                for (int i = 0; i < NR; ++i) z[i][m] = dot8f(wv[i], xf, z[i][m]);
+            }
+        }
+    }
+}
+
+// The same greedy loop for M utterances per cluster in lock step.  The weights in shared memory, the cluster
+// barriers and the phase latencies are shared by the M utterances; each keeps its own prediction-network state,
+// emission count and transcript.  An utterance whose frame decided "blank" simply sits out the prediction-network
+// evaluation of that frame (the mask is the same in every CTA, because every CTA takes every decision).
+template <int NRG, int NRJ, int NRV, int M>
+__global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_multi_kernel(GreedyArgs a) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int nthr = kGreedyThreads;
+    const int PH = a.PH, JH = a.JH, V = a.V;
+    const int UP = (PH + C - 1) / C, u0 = rank * UP, nu = max(0, min(UP, PH - u0));
+    const int JP = (JH + C - 1) / C, j0 = rank * JP, nj = max(0, min(JP, JH - j0));
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* sp = smem_raw;
+    auto carve = [&](size_t bytes) {
+        unsigned char* p = sp;
+        sp += (bytes + 15) & ~size_t(15);
+        return p;
+    };
+    __half* h0buf = reinterpret_cast<__half*>(carve((size_t)M * 2 * PH * 2));   // [M][2][PH]
+    __half* h1buf = reinterpret_cast<__half*>(carve((size_t)M * 2 * PH * 2));
+    float* Pj = reinterpret_cast<float*>(carve((size_t)M * JH * 4));            // [M][JH]
+    __half* zs = reinterpret_cast<__half*>(carve((size_t)M * JH * 2));          // [M][JH]
+    float* zrow = reinterpret_cast<float*>(carve((size_t)M * 4 * UP * 4));      // [M][4UP]
+    float* lg = reinterpret_cast<float*>(carve((size_t)M * (V + 1) * 4));       // [M][V+1]
+    float* b2s = reinterpret_cast<float*>(carve((size_t)V * 4));
+    float* bias1s = reinterpret_cast<float*>(carve((size_t)4 * UP * 4));
+    const size_t slice = (size_t)4 * UP * PH * 2;
+    const __half* Whh0 = a.Whh0 + (size_t)u0 * 4 * PH;
+    const __half* Wih1 = a.Wih1 + (size_t)u0 * 4 * PH;
+    const __half* Whh1 = a.Whh1 + (size_t)u0 * 4 * PH;
+    const __half* W1p = a.W1p + (size_t)j0 * PH;
+    const __half* W2 = a.W2;
+    auto stage = [&](const __half* g, size_t halves, size_t cap_bytes) {
+        __half* s = reinterpret_cast<__half*>(carve(cap_bytes));
+        const uint4* g4 = reinterpret_cast<const uint4*>(g);
+        uint4* s4 = reinterpret_cast<uint4*>(s);
+        for (size_t i = tid; i < halves / 8; i += nthr) s4[i] = __ldg(g4 + i);
+        return (const __half*)s;
+    };
+    if (a.smem_mask & 1) Whh0 = stage(Whh0, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 2) Wih1 = stage(Wih1, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 4) Whh1 = stage(Whh1, (size_t)4 * nu * PH, slice);
+    if (a.smem_mask & 8) W1p = stage(W1p, (size_t)nj * PH, (size_t)JP * PH * 2);
+    if (a.smem_mask & 16) W2 = stage(W2, (size_t)V * JH, (size_t)V * JH * 2);
+    for (int i = tid; i < V; i += nthr) b2s[i] = a.b2[i];
+    for (int i = tid; i < 4 * nu; i += nthr) bias1s[i] = a.bias1[(size_t)u0 * 4 + i];
+
+    // gate threads: pair p = (unit j, utterance m), p < nu*M, replicated REP times; replica r writes to CTAs r, r+REP, ...
+    const int NG = nu * M;
+    const int REP = NG > 0 ? min(C, nthr / NG) : 1;
+    const int gp = tid % max(NG, 1), grep = tid / max(NG, 1);
+    const bool gate_thread = NG > 0 && grep < REP;
+    const int gj = gp / M, gm = gp - gj * M;
+    float c_l0 = 0.f, c_l1 = 0.f;
+
+    const int n_groups = (a.n_utts + M - 1) / M;
+    for (int grp = cluster_id; grp < n_groups; grp += n_clusters) {
+        const int utt0 = grp * M;
+        unsigned valid = 0;
+        for (int m = 0; m < M; ++m)
+            if (utt0 + m < a.n_utts) valid |= 1u << m;
+        for (int i = tid; i < M * 2 * PH; i += nthr) {
+            h0buf[i] = __float2half_rn(0.f);
+            h1buf[i] = __float2half_rn(0.f);
+        }
+        c_l0 = 0.f;
+        c_l1 = 0.f;
+        cluster.sync();
+        int e[M], n_emit[M], tok[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) { e[m] = 0; n_emit[m] = 0; tok[m] = a.blank; }
+
+        // prediction-network evaluation of the utterances in `mask`
+        auto pred_eval = [&](unsigned mask) {
+            const __half* hp[M];
+            float z[NRG][M];
+            // layer 0
+#pragma unroll
+            for (int m = 0; m < M; ++m) hp[m] = h0buf + ((size_t)m * 2 + ((e[m] + 1) & 1)) * PH;
+#pragma unroll
+            for (int i = 0; i < NRG; ++i)
+#pragma unroll
+                for (int m = 0; m < M; ++m) z[i][m] = 0.f;
+            rows_dot_multi<NRG, M>(Whh0, 4 * nu, PH, hp, mask, warp, lane, z);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < NRG; ++i)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) z[i][m] += __shfl_xor_sync(0xffffffffu, z[i][m], o);
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < NRG; ++i) {
+                    const int r = warp + kGreedyWarps * i;
+                    if (r < 4 * nu) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m)
+                            if (mask & (1u << m))
+                                zrow[m * 4 * UP + r] = z[i][m] + __ldg(a.P0 + (size_t)tok[m] * 4 * PH + (size_t)u0 * 4 + r);
+                    }
+                }
+            }
+            __syncthreads();
+            if (gate_thread && (mask & (1u << gm))) {
+                const float* zr = zrow + gm * 4 * UP + gj * 4;
+                c_l0 = sigmoidf_(zr[1]) * c_l0 + sigmoidf_(zr[0]) * tanhf_(zr[2]);
+                const __half hh = __float2half_rn(sigmoidf_(zr[3]) * tanhf_(c_l0));
+                __half* dstl = h0buf + ((size_t)gm * 2 + (e[gm] & 1)) * PH + u0 + gj;
+                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
+            }
+            cluster.sync();
+            // layer 1
+#pragma unroll
+            for (int i = 0; i < NRG; ++i)
+#pragma unroll
+                for (int m = 0; m < M; ++m) z[i][m] = 0.f;
+#pragma unroll
+            for (int m = 0; m < M; ++m) hp[m] = h0buf + ((size_t)m * 2 + (e[m] & 1)) * PH;
+            rows_dot_multi<NRG, M>(Wih1, 4 * nu, PH, hp, mask, warp, lane, z);
+#pragma unroll
+            for (int m = 0; m < M; ++m) hp[m] = h1buf + ((size_t)m * 2 + ((e[m] + 1) & 1)) * PH;
+            rows_dot_multi<NRG, M>(Whh1, 4 * nu, PH, hp, mask, warp, lane, z);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < NRG; ++i)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) z[i][m] += __shfl_xor_sync(0xffffffffu, z[i][m], o);
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < NRG; ++i) {
+                    const int r = warp + kGreedyWarps * i;
+                    if (r < 4 * nu) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m)
+                            if (mask & (1u << m)) zrow[m * 4 * UP + r] = z[i][m] + bias1s[r];
+                    }
+                }
+            }
+            __syncthreads();
+            if (gate_thread && (mask & (1u << gm))) {
+                const float* zr = zrow + gm * 4 * UP + gj * 4;
+                c_l1 = sigmoidf_(zr[1]) * c_l1 + sigmoidf_(zr[0]) * tanhf_(zr[2]);
+                const __half hh = __float2half_rn(sigmoidf_(zr[3]) * tanhf_(c_l1));
+                __half* dstl = h1buf + ((size_t)gm * 2 + (e[gm] & 1)) * PH + u0 + gj;
+                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
+            }
+            cluster.sync();
+            // prediction half of the joint
+            float zj[NRJ][M];
+#pragma unroll
+            for (int i = 0; i < NRJ; ++i)
+#pragma unroll
+                for (int m = 0; m < M; ++m) zj[i][m] = 0.f;
+#pragma unroll
+            for (int m = 0; m < M; ++m) hp[m] = h1buf + ((size_t)m * 2 + (e[m] & 1)) * PH;
+            rows_dot_multi<NRJ, M>(W1p, nj, PH, hp, mask, warp, lane, zj);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < NRJ; ++i)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) zj[i][m] += __shfl_xor_sync(0xffffffffu, zj[i][m], o);
+            if (lane < C) {
+#pragma unroll
+                for (int i = 0; i < NRJ; ++i) {
+                    const int q = warp + kGreedyWarps * i;
+                    if (q < nj) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m)
+                            if (mask & (1u << m)) cluster.map_shared_rank(Pj + (size_t)m * JH, lane)[j0 + q] = zj[i][m];
+                    }
+                }
+            }
+            cluster.sync();
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (mask & (1u << m)) ++e[m];
+        };
+
+        pred_eval(valid);  // start of sequence for every utterance of the group
+        for (int t = 0; t < a.Tp; ++t) {
+            // joint: z_m = relu(E_m[t] + Pj_m)
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                if (valid & (1u << m)) {
+                    const float* E = a.E + ((size_t)(utt0 + m) * a.Tp + t) * JH;
+                    for (int i = tid; i < JH; i += nthr)
+                        zs[m * JH + i] = __float2half_rn(fmaxf(__ldcg(E + i) + Pj[m * JH + i], 0.f));
+                }
+            }
+            __syncthreads();
+            float zv[NRV][M];
+#pragma unroll
+            for (int i = 0; i < NRV; ++i)
+#pragma unroll
+                for (int m = 0; m < M; ++m) zv[i][m] = 0.f;
+            const __half* zp[M];
+#pragma unroll
+            for (int m = 0; m < M; ++m) zp[m] = zs + (size_t)m * JH;
+            rows_dot_multi<NRV, M>(W2, V, JH, zp, valid, warp, lane, zv);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < NRV; ++i)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) zv[i][m] += __shfl_xor_sync(0xffffffffu, zv[i][m], o);
+            if (lane == 0) {
+#pragma unroll
+                for (int i = 0; i < NRV; ++i) {
+                    const int r = warp + kGreedyWarps * i;
+                    if (r < V) {
+#pragma unroll
+                        for (int m = 0; m < M; ++m) lg[m * (V + 1) + r] = zv[i][m] + b2s[r];
+                    }
+                }
+            }
+            __syncthreads();
+            unsigned emit = 0;
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                if (!(valid & (1u << m))) continue;
+                float bv = -INFINITY;
+                int best = 0x7fffffff;
+                for (int r = lane; r < V; r += 32) {
+                    const float v = lg[m * (V + 1) + r];
+                    if (v > bv) { bv = v; best = r; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+                    if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
+                }
+                if (rank == 0 && a.logits && tid < V)
+                    a.logits[((size_t)(utt0 + m) * a.Tp + t) * V + tid] = lg[m * (V + 1) + tid];
+                if (best != a.blank) {
+                    if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
+                    ++n_emit[m];
+                    tok[m] = best;
+                    emit |= 1u << m;
+                }
+            }
+            if (emit) pred_eval(emit);
+            else __syncthreads();  // zs / lg are rewritten next frame
+        }
+        if (rank == 0 && tid == 0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (valid & (1u << m)) a.n_tokens[utt0 + m] = n_emit[m];
+        }
+    }
+    cluster.sync();
+}
+
 using GreedyFn = void (*)(GreedyArgs);
 // rows per warp are compile-time (register arrays); pick the instantiation covering the run-time sizes
 static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
@@ -301,6 +585,13 @@ static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
               nrv = ceil_div(vocab, kGreedyWarps);
     if (nrg <= 5 && nrj <= 2 && nrv <= 2) return rnnt_greedy_kernel<5, 2, 2>;
     if (nrg <= kMaxRowsPerWarp && nrj <= 4 && nrv <= 4) return rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4>;
+    return nullptr;
+}
+constexpr int kGreedyMulti = 4;  // utterances per cluster of the lock-step variant
+static GreedyFn pick_greedy_multi(int gate_rows, int joint_rows, int vocab) {
+    const int nrg = ceil_div(gate_rows, kGreedyWarps), nrj = ceil_div(joint_rows, kGreedyWarps),
+              nrv = ceil_div(vocab, kGreedyWarps);
+    if (nrg <= 5 && nrj <= 2 && nrv <= 2) return rnnt_greedy_multi_kernel<5, 2, 2, kGreedyMulti>;
     return nullptr;
 }
 
@@ -322,6 +613,10 @@ struct pimb200_rnnt {
     size_t cap_frames = 0;  // frames*utts capacity of the three buffers above
     long long* trace = nullptr;  // diagnostics buffer (not owned)
     GreedyFn fn = nullptr;
+    GreedyFn fn_multi = nullptr;   // lock-step variant (kGreedyMulti utterances per cluster), when it fits
+    int smem_mask_multi = 0;
+    size_t smem_bytes_multi = 0;
+    int greedy_multi = 1;   // 0 = always one utterance per cluster
     int enc_batch = 32;     // utterances the encoder advances in lock step
     int cluster = 0;        // CTAs per cluster
     int smem_mask = 0;
@@ -329,12 +624,17 @@ struct pimb200_rnnt {
     std::mutex mu;
 };
 
-static size_t greedy_smem(const pimb200_rnnt_config& c, int C, int mask) {
+static size_t greedy_smem(const pimb200_rnnt_config& c, int C, int mask, int multi = 0) {
     auto al = [](size_t b) { return (b + 15) & ~size_t(15); };
     const int PH = c.pred_hidden, JH = c.joint_hidden, V = c.vocab;
     const int UP = (PH + C - 1) / C, JP = (JH + C - 1) / C;
-    size_t s = al((size_t)2 * PH * 2) * 2 + al((size_t)JH * 4) + al((size_t)JH * 2) + al((size_t)4 * UP * 4) +
-               al((size_t)(V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4) + al((size_t)V * 4 * UP * 4);
+    size_t s;
+    if (multi > 0)
+        s = al((size_t)multi * 2 * PH * 2) * 2 + al((size_t)multi * JH * 4) + al((size_t)multi * JH * 2) +
+            al((size_t)multi * 4 * UP * 4) + al((size_t)multi * (V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4);
+    else
+        s = al((size_t)2 * PH * 2) * 2 + al((size_t)JH * 4) + al((size_t)JH * 2) + al((size_t)4 * UP * 4) +
+            al((size_t)(V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4) + al((size_t)V * 4 * UP * 4);
     const size_t slice = al((size_t)4 * UP * PH * 2);
     if (mask & 1) s += slice;
     if (mask & 2) s += slice;
@@ -451,6 +751,22 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
             h->fn = fn;
             h->smem_mask = mask;
             h->smem_bytes = smem;
+            // the lock-step variant needs kGreedyMulti sets of state buffers: use it only with every matrix resident
+            GreedyFn fm = pick_greedy_multi(4 * ceil_div(PH, C), ceil_div(JH, C), V);
+            const size_t smem_m = greedy_smem(c, C, 31, kGreedyMulti);
+            if (fm && mask == 31 && smem_m <= (size_t)max_smem && ceil_div(PH, C) * kGreedyMulti <= kGreedyThreads) {
+                cudaFuncSetAttribute(fm, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                cudaFuncSetAttribute(fm, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                lc.dynamicSmemBytes = smem_m;
+                int ncl = 0;
+                if (cudaOccupancyMaxActiveClusters(&ncl, fm, &lc) == cudaSuccess && ncl >= 1) {
+                    h->fn_multi = fm;
+                    h->smem_mask_multi = 31;
+                    h->smem_bytes_multi = smem_m;
+                } else {
+                    cudaGetLastError();
+                }
+            }
         } else {
             cudaGetLastError();
         }
@@ -485,6 +801,13 @@ extern "C" int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long
 extern "C" int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n) {
     if (!h || n < 1 || n > 32) return PIMB200_ERR_BAD_ARG;
     h->enc_batch = n;
+    return PIMB200_OK;
+}
+
+// A/B switch: 0 = the greedy kernel always takes one utterance per cluster.
+extern "C" int pimb200_rnnt_set_greedy_multi(pimb200_rnnt* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->greedy_multi = on ? 1 : 0;
     return PIMB200_OK;
 }
 
@@ -565,17 +888,21 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     const int C = h->cluster;
     int max_clusters = kNumSmB200 / C;
     if (max_clusters < 1) max_clusters = 1;
-    const int n_clusters = n_utts < max_clusters ? n_utts : max_clusters;
+    // more utterances than clusters: several utterances per cluster in lock step
+    const bool multi = h->fn_multi && h->greedy_multi && n_utts > max_clusters && !h->trace;
+    const int groups = multi ? ceil_div(n_utts, kGreedyMulti) : n_utts;
+    const int n_clusters = groups < max_clusters ? groups : max_clusters;
+    if (multi) a.smem_mask = h->smem_mask_multi;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(C * n_clusters);
     lc.blockDim = dim3(512);
-    lc.dynamicSmemBytes = h->smem_bytes;
+    lc.dynamicSmemBytes = multi ? h->smem_bytes_multi : h->smem_bytes;
     lc.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, h->fn, a));
+    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, multi ? h->fn_multi : h->fn, a));
     return PIMB200_OK;
 }
