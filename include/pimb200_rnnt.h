@@ -59,6 +59,11 @@ int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, int n_utts, i
  * recurrence's tensor-core tiles.  1 reproduces strict batch-1 execution. */
 int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n);
 
+/* Which greedy kernel a crowded call (more utterances than clusters) uses: 1 (default) = the best available
+ * (tensor-core kernel, 8 utterances per cluster in lock step, when the shapes allow), 2 = the FMA lock-step kernel
+ * (4 per cluster), 0 = always one utterance per cluster.  For A/B measurements. */
+int pimb200_rnnt_set_greedy_multi(pimb200_rnnt* h, int mode);
+
 /* Reports how the greedy kernel was configured: CTAs per cluster, which matrices are staged in shared
  * memory (bit 0..4 = W_hh0, W_ih1, W_hh1, joint W1 pred half, joint W2) and the dynamic shared memory per CTA. */
 int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t* smem_bytes);

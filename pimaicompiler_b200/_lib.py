@@ -51,6 +51,7 @@ SIGNATURES = {
     "pimb200_rnnt_destroy": (_i, [_vp]),
     "pimb200_rnnt_decode": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp]),
     "pimb200_rnnt_set_encoder_batch": (_i, [_vp, _i]),
+    "pimb200_rnnt_set_greedy_multi": (_i, [_vp, _i]),
     "pimb200_rnnt_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_sz)]),
 }
 

@@ -578,6 +578,325 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_multi_kernel(Gr
     cluster.sync();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant of the greedy loop: 8 utterances per cluster, one column of an m16n8k16 tile each.
+// Every matrix-vector product of the loop becomes [rows x K] . [K x 8]; the weights sit in shared memory as
+// ldmatrix operands (16-byte chunks XOR-swizzled by row, no padding), the hidden vectors are the B operand.
+// Needs: 4*ceil(PH/C) and ceil(JH/C) multiples of 16, PH and JH multiples of 64, V <= 32.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaUtts = 8;
+
+__device__ __forceinline__ void g_ldmatrix_x4(uint32_t* r, const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void g_mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// element (r, k) of a swizzled [rows x K] matrix in shared memory (K % 64 == 0)
+__device__ __forceinline__ const __half* swz(const __half* base, int r, int k, int K) {
+    return base + (size_t)r * K + ((((k >> 3) ^ (r & 7)) << 3) | (k & 7));
+}
+__device__ __forceinline__ void stage_swizzled(__half* dst, const __half* src, int rows_valid, int rows_total, int K,
+                                               int tid, int nthr) {
+    const int K8 = K >> 3;
+    for (int i = tid; i < rows_total * K8; i += nthr) {
+        const int r = i / K8, c = i - r * K8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows_valid) v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)r * K) + c);
+        *reinterpret_cast<uint4*>(dst + (size_t)r * K + ((c ^ (r & 7)) << 3)) = v;
+    }
+}
+// acc += A[mt*16 .. +16, kt0*16 .. (kt0+nkt)*16) . B, A swizzled in shared memory, B = hb[n][k] with row pitch `bp`
+__device__ __forceinline__ void mma_rows_smem(float* acc, const __half* A, int K, int mt, int kt0, int nkt,
+                                              const __half* hb, int bp, int lane) {
+    const int a_row = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int a_col = (lane >> 4) * 8;
+    const __half* brow = hb + (size_t)(lane >> 2) * bp + (lane & 3) * 2;
+#pragma unroll 4
+    for (int kt = kt0; kt < kt0 + nkt; ++kt) {
+        const int k0 = kt << 4;
+        uint32_t af[4];
+        g_ldmatrix_x4(af, swz(A, a_row, k0 + a_col, K));
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
+        g_mma_16816(acc, af, b0, b1);
+    }
+}
+// same with A read straight from global memory (row-major, pitch K) through L1
+__device__ __forceinline__ void mma_rows_gmem(float* acc, const __half* A, int K, int mt, int kt0, int nkt,
+                                              const __half* hb, int bp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const __half* a_lo = A + (size_t)(mt * 16 + g) * K + 2 * t;
+    const __half* a_hi = a_lo + (size_t)8 * K;
+    const __half* brow = hb + (size_t)g * bp + 2 * t;
+#pragma unroll 5
+    for (int kt = kt0; kt < kt0 + nkt; ++kt) {
+        const int k0 = kt << 4;
+        uint32_t af[4];
+        af[0] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0));
+        af[1] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0));
+        af[2] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0 + 8));
+        af[3] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0 + 8));
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
+        g_mma_16816(acc, af, b0, b1);
+    }
+}
+// accumulator tile -> part[split][n][row] (fp32): thread holds (row g, cols 2t,2t+1) and (row g+8, same cols)
+__device__ __forceinline__ void store_acc(float* part, int ld, int mt, const float* acc, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    part[(size_t)(2 * t) * ld + mt * 16 + g] = acc[0];
+    part[(size_t)(2 * t + 1) * ld + mt * 16 + g] = acc[1];
+    part[(size_t)(2 * t) * ld + mt * 16 + g + 8] = acc[2];
+    part[(size_t)(2 * t + 1) * ld + mt * 16 + g + 8] = acc[3];
+}
+
+__global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(GreedyArgs a) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = (int)cluster.num_blocks();
+    const int rank = (int)cluster.block_rank();
+    const int cluster_id = blockIdx.x / C, n_clusters = gridDim.x / C;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int nthr = kGreedyThreads;
+    constexpr int M = kMmaUtts;
+    const int PH = a.PH, JH = a.JH, V = a.V;
+    const int UP = PH / C, u0 = rank * UP, RG = 4 * UP;      // gate rows of this CTA (multiple of 16)
+    const int JP = JH / C, j0 = rank * JP;                  // joint rows of this CTA (multiple of 16)
+    const int hp = PH + 8, zp = JH + 8;                      // pitches of the B-operand buffers
+    const int MTG = RG / 16, MTJ = JP / 16, KTP = PH / 16, KTJ = JH / 16;
+
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* sp = smem_raw;
+    auto carve = [&](size_t bytes) {
+        unsigned char* p = sp;
+        sp += (bytes + 15) & ~size_t(15);
+        return p;
+    };
+    __half* Whh0 = reinterpret_cast<__half*>(carve((size_t)RG * PH * 2));
+    __half* Wih1 = reinterpret_cast<__half*>(carve((size_t)RG * PH * 2));
+    __half* Whh1 = reinterpret_cast<__half*>(carve((size_t)RG * PH * 2));
+    __half* W2s = reinterpret_cast<__half*>(carve((size_t)32 * JH * 2));
+    __half* h0buf = reinterpret_cast<__half*>(carve((size_t)2 * M * hp * 2));   // [2][M][hp]
+    __half* h1buf = reinterpret_cast<__half*>(carve((size_t)2 * M * hp * 2));
+    __half* Pj = reinterpret_cast<__half*>(carve((size_t)M * JH * 2));           // [M][JH]
+    __half* zs = reinterpret_cast<__half*>(carve((size_t)M * zp * 2));           // [M][zp]
+    // partial sums: [2 splits][M][RG] for the gate phases, [4 splits][M][32] for the joint / logits phases
+    const int part_floats = 2 * M * RG > 4 * M * 32 ? 2 * M * RG : 4 * M * 32;
+    float* part = reinterpret_cast<float*>(carve((size_t)part_floats * 4));
+    const int gl = RG, jl = 32;   // row pitches of the two uses
+    float* lg = reinterpret_cast<float*>(carve((size_t)M * 32 * 4));             // [M][32]
+    float* b2s = reinterpret_cast<float*>(carve((size_t)32 * 4));
+    float* bias1s = reinterpret_cast<float*>(carve((size_t)RG * 4));
+    int* best_s = reinterpret_cast<int*>(carve((size_t)M * 4));
+    const __half* W1p = a.W1p + (size_t)j0 * PH;  // read through L1: no room left in shared memory
+
+    stage_swizzled(Whh0, a.Whh0 + (size_t)u0 * 4 * PH, RG, RG, PH, tid, nthr);
+    stage_swizzled(Wih1, a.Wih1 + (size_t)u0 * 4 * PH, RG, RG, PH, tid, nthr);
+    stage_swizzled(Whh1, a.Whh1 + (size_t)u0 * 4 * PH, RG, RG, PH, tid, nthr);
+    stage_swizzled(W2s, a.W2, V, 32, JH, tid, nthr);
+    for (int i = tid; i < 32; i += nthr) b2s[i] = i < V ? a.b2[i] : -INFINITY;
+    for (int i = tid; i < RG; i += nthr) bias1s[i] = a.bias1[(size_t)u0 * 4 + i];
+
+    // gate threads: pair p = (unit j, utterance n), replicated REP times; replica r serves CTAs r, r+REP, ...
+    const int NG = UP * M;
+    const int REP = min(C, nthr / NG);
+    const int gp = tid % NG, grep = tid / NG;
+    const bool gate_thread = grep < REP;
+    const int gj = gp / M, gn = gp - gj * M;
+    float c_l0 = 0.f, c_l1 = 0.f;
+
+    const int n_groups = (a.n_utts + M - 1) / M;
+    for (int grp = cluster_id; grp < n_groups; grp += n_clusters) {
+        const int utt0 = grp * M;
+        unsigned valid = 0;
+        for (int m = 0; m < M; ++m)
+            if (utt0 + m < a.n_utts) valid |= 1u << m;
+        for (int i = tid; i < 2 * M * hp; i += nthr) {
+            h0buf[i] = __float2half_rn(0.f);
+            h1buf[i] = __float2half_rn(0.f);
+        }
+        for (int i = tid; i < M * zp; i += nthr) zs[i] = __float2half_rn(0.f);
+        for (int i = tid; i < M * JH; i += nthr) Pj[i] = __float2half_rn(0.f);
+        c_l0 = 0.f;
+        c_l1 = 0.f;
+        cluster.sync();
+        // all utterances of a group evaluate the prediction network the same number of times only if they emit in
+        // the same frames; each keeps its own parity, packed one bit per utterance
+        unsigned par = 0;          // bit n = parity of utterance n's next evaluation
+        int n_emit[M], tok[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) { n_emit[m] = 0; tok[m] = a.blank; }
+
+        // Because an m16n8k16 pass always covers all 8 columns, the B operand of an evaluation must hold, for every
+        // column, the state that utterance will read: buffers are indexed [parity][n], and a column that sits the
+        // evaluation out simply produces a value nobody stores.
+        auto pred_eval = [&](unsigned mask) {
+            // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]); two K halves per m-tile
+            if (warp < 2 * MTG) {
+                const int mt = warp % MTG, kh = warp / MTG;
+                const int k_lo = kh ? KTP / 2 : 0, k_n = kh ? KTP - KTP / 2 : KTP / 2;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                // column n reads parity ((par>>n)&1)^1: gather per-lane base (lane's column = lane>>2)
+                const int n = lane >> 2;
+                const __half* hb = h0buf + ((size_t)((((par >> n) & 1u) ^ 1u) * M)) * hp;  // row n added inside
+                // mma_rows_smem indexes hb + (lane>>2)*bp: pass the parity-selected plane
+                mma_rows_smem(acc, Whh0, PH, mt, k_lo, k_n, hb, hp, lane);
+                store_acc(part + (size_t)kh * M * gl, gl, mt, acc, lane);
+            }
+            __syncthreads();
+            if (gate_thread && (mask & (1u << gn))) {
+                const float* p0 = a.P0 + (size_t)tok[gn] * 4 * PH + (size_t)(u0 + gj) * 4;
+                float z[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    z[g] = part[(size_t)gn * gl + gj * 4 + g] + part[(size_t)(M + gn) * gl + gj * 4 + g] + __ldg(p0 + g);
+                c_l0 = sigmoidf_(z[1]) * c_l0 + sigmoidf_(z[0]) * tanhf_(z[2]);
+                const __half hh = __float2half_rn(sigmoidf_(z[3]) * tanhf_(c_l0));
+                __half* dstl = h0buf + ((size_t)((par >> gn) & 1u) * M + gn) * hp + u0 + gj;
+                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
+            }
+            cluster.sync();
+            // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias; the two products go to two warp groups
+            if (warp < 2 * MTG) {
+                const int mt = warp % MTG, which = warp / MTG;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const int n = lane >> 2;
+                const unsigned pn = (par >> n) & 1u;
+                if (which == 0) mma_rows_smem(acc, Wih1, PH, mt, 0, KTP, h0buf + (size_t)(pn * M) * hp, hp, lane);
+                else mma_rows_smem(acc, Whh1, PH, mt, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
+                store_acc(part + (size_t)which * M * gl, gl, mt, acc, lane);
+            }
+            __syncthreads();
+            if (gate_thread && (mask & (1u << gn))) {
+                float z[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    z[g] = part[(size_t)gn * gl + gj * 4 + g] + part[(size_t)(M + gn) * gl + gj * 4 + g] + bias1s[gj * 4 + g];
+                c_l1 = sigmoidf_(z[1]) * c_l1 + sigmoidf_(z[0]) * tanhf_(z[2]);
+                const __half hh = __float2half_rn(sigmoidf_(z[3]) * tanhf_(c_l1));
+                __half* dstl = h1buf + ((size_t)((par >> gn) & 1u) * M + gn) * hp + u0 + gj;
+                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
+            }
+            cluster.sync();
+            // ---- prediction half of the joint: Pj[n][j0 + q] = W1p[q,:] . h1new[n]; four K quarters per m-tile
+            if (warp < 4 * MTJ) {
+                const int mt = warp % MTJ, kq = warp / MTJ;
+                const int per = (KTP + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTP - k_lo));
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                const int n = lane >> 2;
+                mma_rows_gmem(acc, W1p, PH, mt, k_lo, k_n, h1buf + (size_t)(((par >> n) & 1u) * M) * hp, hp, lane);
+                store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
+            }
+            __syncthreads();
+            {
+                // value v = (n, q): JP*M values, each delivered to every CTA; threads split the destinations
+                const int NV = JP * M, reps = max(1, min(C, nthr / NV));
+                const int v = tid % NV, r = tid / NV;
+                if (r < reps) {
+                    const int n = v / JP, q = v - n * JP;
+                    if (mask & (1u << n)) {
+                        const float sum = (part[(size_t)n * jl + q] + part[(size_t)(M + n) * jl + q]) +
+                                          (part[(size_t)(2 * M + n) * jl + q] + part[(size_t)(3 * M + n) * jl + q]);
+                        const __half hv = __float2half_rn(sum);
+                        for (int d = r; d < C; d += reps) cluster.map_shared_rank(Pj + (size_t)n * JH, d)[j0 + q] = hv;
+                    }
+                }
+            }
+            cluster.sync();
+            par ^= mask;
+        };
+
+        pred_eval(valid);  // start of sequence
+        // E of the next frame is fetched one frame ahead (its L2 latency would otherwise open every frame)
+        constexpr int EPF = 8;
+        const bool prefetch = M * JH <= EPF * nthr;
+        float e_next[EPF];
+        auto load_E = [&](int t) {
+#pragma unroll
+            for (int q = 0; q < EPF; ++q) {
+                const int i = tid + q * nthr;
+                const int n = i / JH, k = i - n * JH;
+                e_next[q] = (i < M * JH && (valid & (1u << n)) && t < a.Tp)
+                                ? __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k) : 0.f;
+            }
+        };
+        if (prefetch) load_E(0);
+        for (int t = 0; t < a.Tp; ++t) {
+            // ---- joint input z[n] = relu(E[n][t] + Pj[n]) in fp16
+            if (prefetch) {
+#pragma unroll
+                for (int q = 0; q < EPF; ++q) {
+                    const int i = tid + q * nthr;
+                    const int n = i / JH, k = i - n * JH;
+                    if (i < M * JH && (valid & (1u << n)))
+                        zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e_next[q] + __half2float(Pj[i]), 0.f));
+                }
+                load_E(t + 1);
+            } else {
+                for (int i = tid; i < M * JH; i += nthr) {
+                    const int n = i / JH, k = i - n * JH;
+                    if (valid & (1u << n)) {
+                        const float e = __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k);
+                        zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e + __half2float(Pj[i]), 0.f));
+                    }
+                }
+            }
+            __syncthreads();
+            // ---- logits[n][r] = W2[r,:] . z[n] + b2[r]: 2 m-tiles x 4 K quarters
+            if (warp < 8) {
+                const int mt = warp & 1, kq = warp >> 1;
+                const int per = (KTJ + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTJ - k_lo));
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_rows_smem(acc, W2s, JH, mt, k_lo, k_n, zs, zp, lane);
+                store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
+            }
+            __syncthreads();
+            if (tid < M * 32) {
+                const int n = tid >> 5, r = tid & 31;   // warp n handles utterance n, lane = vocabulary row
+                float v = (part[(size_t)n * jl + r] + part[(size_t)(M + n) * jl + r]) +
+                          (part[(size_t)(2 * M + n) * jl + r] + part[(size_t)(3 * M + n) * jl + r]) + b2s[r];
+                lg[tid] = v;
+                float bv = v;
+                int best = r;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+                    if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
+                }
+                if (r == 0) best_s[n] = best;
+                if (rank == 0 && a.logits && r < V && (valid & (1u << n)))
+                    a.logits[((size_t)(utt0 + n) * a.Tp + t) * V + r] = v;
+            }
+            __syncthreads();
+            unsigned emit = 0;
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const int best = best_s[m];
+                if ((valid & (1u << m)) && best != a.blank) {
+                    if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
+                    ++n_emit[m];
+                    tok[m] = best;
+                    emit |= 1u << m;
+                }
+            }
+            if (emit) pred_eval(emit);
+            else __syncthreads();
+        }
+        if (rank == 0 && tid == 0) {
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+                if (valid & (1u << m)) a.n_tokens[utt0 + m] = n_emit[m];
+        }
+    }
+    cluster.sync();
+}
+
 using GreedyFn = void (*)(GreedyArgs);
 // rows per warp are compile-time (register arrays); pick the instantiation covering the run-time sizes
 static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
@@ -586,6 +905,24 @@ static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
     if (nrg <= 5 && nrj <= 2 && nrv <= 2) return rnnt_greedy_kernel<5, 2, 2>;
     if (nrg <= kMaxRowsPerWarp && nrj <= 4 && nrv <= 4) return rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4>;
     return nullptr;
+}
+static size_t greedy_mma_smem(const pimb200_rnnt_config& c, int C) {
+    auto al = [](size_t b) { return (b + 15) & ~size_t(15); };
+    const int PH = c.pred_hidden, JH = c.joint_hidden, M = kMmaUtts;
+    const int RG = 4 * (PH / C);
+    const int part_floats = 2 * M * RG > 4 * M * 32 ? 2 * M * RG : 4 * M * 32;
+    return 3 * al((size_t)RG * PH * 2) + al((size_t)32 * JH * 2) + 2 * al((size_t)2 * M * (PH + 8) * 2) +
+           al((size_t)M * JH * 2) + al((size_t)M * (JH + 8) * 2) + al((size_t)part_floats * 4) + al((size_t)M * 32 * 4) +
+           al(32 * 4) + al((size_t)RG * 4) + al((size_t)M * 4);
+}
+static bool greedy_mma_fits(const pimb200_rnnt_config& c, int C, int max_smem) {
+    const int PH = c.pred_hidden, JH = c.joint_hidden;
+    if (PH % C || JH % C || PH % 64 || JH % 64 || c.vocab > 32) return false;
+    const int UP = PH / C, JP = JH / C;
+    if ((4 * UP) % 16 || JP % 16) return false;
+    if (2 * (4 * UP / 16) > kGreedyWarps || 4 * (JP / 16) > kGreedyWarps) return false;
+    if (UP * kMmaUtts > kGreedyThreads || JP * kMmaUtts > kGreedyThreads) return false;
+    return greedy_mma_smem(c, C) <= (size_t)max_smem;
 }
 constexpr int kGreedyMulti = 4;  // utterances per cluster of the lock-step variant
 static GreedyFn pick_greedy_multi(int gate_rows, int joint_rows, int vocab) {
@@ -613,6 +950,8 @@ struct pimb200_rnnt {
     size_t cap_frames = 0;  // frames*utts capacity of the three buffers above
     long long* trace = nullptr;  // diagnostics buffer (not owned)
     GreedyFn fn = nullptr;
+    bool mma_ok = false;           // tensor-core variant (kMmaUtts utterances per cluster) available
+    size_t smem_bytes_mma = 0;
     GreedyFn fn_multi = nullptr;   // lock-step variant (kGreedyMulti utterances per cluster), when it fits
     int smem_mask_multi = 0;
     size_t smem_bytes_multi = 0;
@@ -751,6 +1090,18 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
             h->fn = fn;
             h->smem_mask = mask;
             h->smem_bytes = smem;
+            if (greedy_mma_fits(c, C, max_smem)) {
+                cudaFuncSetAttribute(rnnt_greedy_mma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                cudaFuncSetAttribute(rnnt_greedy_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                lc.dynamicSmemBytes = greedy_mma_smem(c, C);
+                int ncl = 0;
+                if (cudaOccupancyMaxActiveClusters(&ncl, rnnt_greedy_mma_kernel, &lc) == cudaSuccess && ncl >= 1) {
+                    h->mma_ok = true;
+                    h->smem_bytes_mma = lc.dynamicSmemBytes;
+                } else {
+                    cudaGetLastError();
+                }
+            }
             // the lock-step variant needs kGreedyMulti sets of state buffers: use it only with every matrix resident
             GreedyFn fm = pick_greedy_multi(4 * ceil_div(PH, C), ceil_div(JH, C), V);
             const size_t smem_m = greedy_smem(c, C, 31, kGreedyMulti);
@@ -807,7 +1158,7 @@ extern "C" int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n) {
 // A/B switch: 0 = the greedy kernel always takes one utterance per cluster.
 extern "C" int pimb200_rnnt_set_greedy_multi(pimb200_rnnt* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
-    h->greedy_multi = on ? 1 : 0;
+    h->greedy_multi = on < 0 ? 0 : (on > 2 ? 2 : on);
     return PIMB200_OK;
 }
 
@@ -889,20 +1240,23 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     int max_clusters = kNumSmB200 / C;
     if (max_clusters < 1) max_clusters = 1;
     // more utterances than clusters: several utterances per cluster in lock step
-    const bool multi = h->fn_multi && h->greedy_multi && n_utts > max_clusters && !h->trace;
-    const int groups = multi ? ceil_div(n_utts, kGreedyMulti) : n_utts;
+    // greedy_multi: 0 = one utterance per cluster, 1 = best available, 2 = FMA lock-step variant (4 per cluster)
+    const bool crowded = n_utts > max_clusters && !h->trace;
+    const bool use_mma = h->mma_ok && h->greedy_multi == 1 && crowded;
+    const bool multi = !use_mma && h->fn_multi && h->greedy_multi >= 1 && crowded;
+    const int groups = use_mma ? ceil_div(n_utts, kMmaUtts) : (multi ? ceil_div(n_utts, kGreedyMulti) : n_utts);
     const int n_clusters = groups < max_clusters ? groups : max_clusters;
     if (multi) a.smem_mask = h->smem_mask_multi;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(C * n_clusters);
     lc.blockDim = dim3(512);
-    lc.dynamicSmemBytes = multi ? h->smem_bytes_multi : h->smem_bytes;
+    lc.dynamicSmemBytes = use_mma ? h->smem_bytes_mma : (multi ? h->smem_bytes_multi : h->smem_bytes);
     lc.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, multi ? h->fn_multi : h->fn, a));
+    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, use_mma ? rnnt_greedy_mma_kernel : (multi ? h->fn_multi : h->fn), a));
     return PIMB200_OK;
 }

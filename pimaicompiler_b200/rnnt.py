@@ -57,6 +57,10 @@ class RnntDecoder:
         """Utterances the encoder advances in lock step (1..32)."""
         check(_lib.lib().pimb200_rnnt_set_encoder_batch(self._h, int(n)), "rnnt_set_encoder_batch")
 
+    def set_greedy_multi(self, mode: int) -> None:
+        """Greedy kernel for crowded calls: 1 = best available, 2 = FMA lock-step, 0 = one utterance per cluster."""
+        check(_lib.lib().pimb200_rnnt_set_greedy_multi(self._h, int(mode)), "rnnt_set_greedy_multi")
+
     def profile(self, enable: bool) -> None:
         check(_lib.lib().pimb200_rnnt_profile_enable(self._h, 1 if enable else 0), "rnnt_profile_enable")
 

@@ -82,8 +82,9 @@ def test_rnnt_batch_of_utterances_matches_single():
     dec = _decoder(cfg, w)
     n, T = 13, 30   # more utterances than clusters fit on the device
     feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
+    dec.set_greedy_multi(2)   # FMA lock-step kernel: same summation order as the one-utterance kernel
     toks, logits = dec.decode(feats, want_logits=True)
-    # lock-step encoding of up to 8 utterances must not change any utterance's result: the per-sequence
+    # lock-step encoding of several utterances must not change any utterance's result: the per-sequence
     # arithmetic (tensor-core tile column, fp32 accumulation order) is the same at every batch size
     dec.set_encoder_batch(1)
     for i in range(n):
@@ -93,3 +94,40 @@ def test_rnnt_batch_of_utterances_matches_single():
     dec.set_encoder_batch(3)
     toks3, logits3 = dec.decode(feats, want_logits=True)
     assert toks3 == toks and torch.equal(logits3, logits)
+
+
+@pytest.mark.parametrize("n_utts", [12, 19])
+def test_rnnt_tensor_core_greedy_small_model(n_utts):
+    # a model whose shapes the tensor-core greedy kernel accepts (PH, JH multiples of 64, 16 CTAs per cluster); more
+    # utterances than clusters, so 8 share a cluster in lock step; every utterance checked against the C oracle
+    cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=64, joint_hidden=256, vocab=11, blank=10)
+    w = to.make_rnnt_weights(cfg, seed=6, gain=2.0, logit_gain=6.0)
+    w.b2[cfg.blank] += 2.3                     # lifts the blank logit into contention: blank and label frames mix
+    w.b2 = w.b2.to(torch.float16).to(torch.float32)
+    dec = _decoder(cfg, w)
+    T = 36
+    feats = [to.make_features(T, cfg, 300 + i) for i in range(n_utts)]
+    dev = torch.stack(feats).to(torch.float16).cuda()
+    dec.set_greedy_multi(1)
+    toks, logits = dec.decode(dev, want_logits=True)
+    blanks = 0
+    for i in range(n_utts):
+        lg = logits[i].cpu().numpy()
+        _check_utterance(cfg, w, feats[i], toks[i], lg, co.rnnt_greedy)
+        blanks += int((lg.argmax(1) == cfg.blank).sum())
+    assert 0 < blanks < n_utts * (T // 2)      # the utterances really do emit in different frames
+    # one utterance per cluster gives the same transcripts wherever the oracle is decided (checked above for both)
+    dec.set_greedy_multi(0)
+    toks0, logits0 = dec.decode(dev, want_logits=True)
+    assert_close(logits0, logits.cpu().numpy(), CONTRACT_ATOL, CONTRACT_RTOL, "mma vs one-per-cluster logits")
+
+
+def test_rnnt_tensor_core_greedy_baseline_config():
+    cfg = to.RnntConfig()
+    w = to.make_rnnt_weights(cfg, seed=5, gain=2.0, logit_gain=8.0)
+    dec = _decoder(cfg, w)
+    n, T = 12, 100
+    feats = [to.make_features(T, cfg, 400 + i) for i in range(n)]
+    toks, logits = dec.decode(torch.stack(feats).to(torch.float16).cuda(), want_logits=True)
+    for i in (0, 5, 11):
+        _check_utterance(cfg, w, feats[i], toks[i], logits[i].cpu().numpy(), to.rnnt_greedy)
