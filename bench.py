@@ -274,13 +274,13 @@ def run_gpu(args, rank, world, local):
                 "h2d_bytes_per_step": int(feats_host.numel() * 2),
                 "d2h_bytes_per_step": int(tokens_host.numel() * 4 + n_tokens_host.numel() * 4)},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "lstm_persistent_kernel (W_hh recurrence, all T steps per launch)",
+        "roofline": {"bound": "hbm", "kernel": "lstm_persistent_bulk_kernel<4> (W_hh recurrence, all T steps of 32 sequences per launch)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src,
-                     # dram__bytes_read+write of one T=1000, 8-sequence launch from the committed ncu capture
-                     # (profiles/lstm_persistent_kernel_rnnt_prenet_8_sequences.txt); that launch's algorithmic
+                     # dram__bytes_read+write of one T=1000, 32-sequence launch from the committed ncu capture
+                     # (profiles/lstm_persistent_bulk_kernel_rnnt_prenet_32_sequences.txt); that launch's algorithmic
                      # bytes are 8.39e9
-                     "traffic": 152.7e6,
+                     "traffic": 592.6e6,
                      "launches": prof["recurrences"], "avg_launch_ms": prof["ms"] / max(prof["recurrences"], 1),
                      "share_of_step_time": share,
                      "note": "algorithmic bytes = T * 4H*H * 2 per launch (W_hh once per timestep, the streamed "
