@@ -248,7 +248,7 @@ def run_gpu(args, rank, world, local):
     share = prof["ms"] / sum(step_ms) if sum(step_ms) > 0 else 0.0
     # per group of encoder-batch utterances: (projection GEMM + recurrence) per LSTM layer; then one joint GEMM and
     # one greedy kernel
-    eb = args.encoder_batch or 32
+    eb = args.encoder_batch or 64
     launches_per_step = ((S + eb - 1) // eb) * 2 * (cfg.pre_layers + cfg.post_layers) + 2
 
     cpu = None

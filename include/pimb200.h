@@ -135,7 +135,7 @@ int pimb200_lstm_create(const void* const* params, int n_params, int num_layers,
 int pimb200_lstm_destroy(pimb200_lstm* h);
 
 /* variant selection for A/B profiling: 0 = automatic, 1 = streamed per-step kernels,
- * 2 = persistent weight-stationary kernels (tagged-word exchange for one sequence, flag + bulk exchange for 2..32;
+ * 2 = persistent weight-stationary kernels (tagged-word exchange for one sequence, flag + bulk exchange for 2..64;
  * fails with UNSUPPORTED when the shape does not fit), 3 = persistent with the tagged-word exchange for up to 8. */
 enum { PIMB200_LSTM_AUTO = 0, PIMB200_LSTM_STREAMED = 1, PIMB200_LSTM_PERSISTENT = 2,
        PIMB200_LSTM_PERSISTENT_TAGGED = 3 };

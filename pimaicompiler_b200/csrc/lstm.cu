@@ -449,7 +449,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
 // then fetch the data with ordinary coalesced 16-byte loads.  Two L2 round trips per step instead of one, but the
 // volume moves at full L2 bandwidth.
 // ---------------------------------------------------------------------------------------------
-constexpr int kBulkMaxB = 32;              // sequences per launch of the batched variant
+constexpr int kBulkMaxB = 64;              // sequences per launch of the batched variants
 constexpr int kBulkFlagCopies = 8;         // replicas of the step flags
 
 struct BulkArgs {
@@ -640,6 +640,176 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
 }
 
 // ---------------------------------------------------------------------------------------------
+// wide variant of the batched persistent recurrence (up to 64 sequences): the same exchange protocol, but each warp
+// owns whole output tiles (one 16-row m-tile x NT/4 n-tiles of 8 sequences, all of K), so no partial sums cross
+// warps: the accumulators go straight to a [32 x BP] fp32 tile in shared memory and the gate threads read from there.
+// ---------------------------------------------------------------------------------------------
+template <int NT>  // 4 or 8 tiles of 8 sequences
+__global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
+    constexpr int BP = NT * 8;
+    constexpr int NPW = NT / 4;                    // n-tiles per warp
+    constexpr int PPT = (8 * BP) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, T = a.T, B = a.B;
+    const int pitch = H + 8;
+    __half* Ws = reinterpret_cast<__half*>(smem_raw);                         // [32][pitch]
+    __half* hs = Ws + (size_t)kPersistRows * pitch;                           // [BP][pitch]
+    float* zbuf = reinterpret_cast<float*>(hs + (size_t)BP * pitch);          // [32 rows][BP]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zbuf + (size_t)kPersistRows * BP);  // [BP][8]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x, cta = blockIdx.x;
+    const int u0 = cta * 8;
+    const int ktiles = H >> 4;
+    {
+        const int H8 = H >> 3;
+        const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
+        for (int i = tid; i < kPersistRows * H8; i += kPersistThreads) {
+            const int r = i / H8, c8 = i - r * H8;
+            *reinterpret_cast<uint4*>(Ws + (size_t)r * pitch + c8 * 8) = ldg_stream_v4(src + (size_t)r * H8 + c8);
+        }
+    }
+    for (int i = tid; i < BP * H; i += kPersistThreads) {
+        const int n = i / H, k = i - n * H;
+        hs[(size_t)n * pitch + k] = (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
+    }
+    for (int i = tid; i < BP * 8; i += kPersistThreads) hpub[i] = 0;
+
+    // gate pairs of this thread: pair p = tid + q*256 -> unit p / BP, sequence p % BP
+    int gu[PPT], gn[PPT];
+    float c[PPT];
+    float4 bias4[PPT], gx[PPT];
+#pragma unroll
+    for (int q = 0; q < PPT; ++q) {
+        const int p_ = tid + q * kPersistThreads;
+        gu[q] = p_ / BP;
+        gn[q] = p_ - gu[q] * BP;
+        c[q] = 0.f;
+        bias4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        gx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gn[q] < B) {
+            const int u = u0 + gu[q];
+            c[q] = a.c0 ? __half2float(a.c0[(size_t)gn[q] * H + u]) : 0.f;
+            bias4[q] = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
+            const int t0 = a.reverse ? T - 1 : 0;
+            gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)gn[q] * a.g_bstride +
+                                                           (size_t)u * 4));
+        }
+    }
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int a_col = (lane >> 4) * 8;
+    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
+    const int mt = warp & 1, nt0 = (warp >> 1) * NPW;   // this warp's output tiles
+    __syncthreads();
+
+    for (int s = 0; s < T; ++s) {
+        const int t = a.reverse ? T - 1 - s : s;
+        const int par = s & 1;
+        // ---- 1. Z tile(s) of this warp over all of K
+        float acc[NPW][4];
+#pragma unroll
+        for (int j = 0; j < NPW; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+        const __half* arow = Ws + (size_t)(mt * 16 + a_row) * pitch + a_col;
+        const __half* brow = hs + (size_t)(nt0 * 8 + b_n) * pitch + b_k;
+#pragma unroll 4
+        for (int kt = 0; kt < ktiles; ++kt) {
+            const int k0 = kt << 4;
+            uint32_t af[4];
+            ldmatrix_x4(af, arow + k0);
+#pragma unroll
+            for (int j = 0; j < NPW; ++j) {
+                const __half* hp = brow + (size_t)(j * 8) * pitch + k0;
+                mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(hp), *reinterpret_cast<const uint32_t*>(hp + 8));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NPW; ++j) {
+            float* p = zbuf + (size_t)(mt * 16 + (lane >> 2)) * BP + (nt0 + j) * 8 + b_k;
+            *reinterpret_cast<float2*>(p) = make_float2(acc[j][0], acc[j][1]);
+            *reinterpret_cast<float2*>(p + 8 * BP) = make_float2(acc[j][2], acc[j][3]);
+        }
+        __syncthreads();
+        // ---- 2. gates
+#pragma unroll
+        for (int q = 0; q < PPT; ++q) {
+            if (gn[q] < B) {
+                const int u = u0 + gu[q], n = gn[q];
+                const float* z = zbuf + (size_t)(gu[q] * 4) * BP + n;
+                const float zi = z[0] + gx[q].x + bias4[q].x, zf = z[BP] + gx[q].y + bias4[q].y,
+                            zg = z[2 * BP] + gx[q].z + bias4[q].z, zo = z[3 * BP] + gx[q].w + bias4[q].w;
+                c[q] = sigmoidf_(zf) * c[q] + sigmoidf_(zi) * tanhf_(zg);
+                const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
+                hpub[n * 8 + gu[q]] = __half_as_ushort(hh);
+                if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh;
+                if (s == T - 1) {
+                    if (a.hn) a.hn[(size_t)n * H + u] = hh;
+                    if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[q]);
+                }
+                if (s + 1 < T) {
+                    const int tn = a.reverse ? t - 1 : t + 1;
+                    gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)n * a.g_bstride +
+                                                                   (size_t)u * 4));
+                }
+            }
+        }
+        __syncthreads();
+        // ---- 3. publish
+        if (tid < B) {
+            const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
+            if (s + 1 < T) {
+                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+                __threadfence();
+            }
+            if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)tid * a.y_bstride + u0) = v;
+        }
+        if (s + 1 == T) break;
+        __syncthreads();
+        const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        if (tid < kBulkFlagCopies)
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+        // ---- 4. flags
+        int timed_out = 0;
+        if (tid < n_cta) {
+            const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + tid) * 32;
+            int polls = 0;
+            while (true) {
+                uint32_t v;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (v == tag) break;
+                if (++polls >= a.poll_limit) { timed_out = 1; break; }
+                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+            }
+            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            __threadfence();
+        }
+        if (__syncthreads_or(timed_out)) return;
+        // ---- 5. bulk fetch, eight 16-byte loads in flight per thread
+        {
+            const uint4* src = a.data + (size_t)par * n_cta * BP;
+            const int items = n_cta * BP;
+            for (int i0 = tid; i0 < items; i0 += 8 * kPersistThreads) {
+                uint4 v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int i = i0 + q * kPersistThreads;
+                    if (i < items) v[q] = src[i];
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int i = i0 + q * kPersistThreads;
+                    if (i < items) {
+                        const int n = i % BP, j = i / BP;
+                        if (n < B) *reinterpret_cast<uint4*>(hs + (size_t)n * pitch + j * 8) = v[q];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct pimb200_lstm {
@@ -663,6 +833,7 @@ struct pimb200_lstm {
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
+    int bulk_wide = 1;     // 1 = tile-owning warps for 17..64 sequences, 0 = K-split kernel (up to 32)
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
@@ -805,6 +976,12 @@ extern "C" int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies) {
     h->xchg_copies = copies;
     return PIMB200_OK;
 }
+// A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
+extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->bulk_wide = on ? 1 : 0;
+    return PIMB200_OK;
+}
 extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
     if (!h || stride16 < 1 || stride16 > kXchgMaxStride) return PIMB200_ERR_BAD_ARG;
     h->xchg_stride = stride16;
@@ -837,6 +1014,10 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
     return PIMB200_OK;
 }
 
+static size_t wide_smem(int H, int nt) {
+    const int BP = nt * 8;
+    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * (H + 8) * 2 + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16;
+}
 static size_t bulk_smem(int H, int nt) {
     const int BP = nt * 8;
     return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * (H + 8) * 2 + (size_t)kPersistWarps * kPersistRows * BP * 4 +
@@ -878,9 +1059,11 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     bool use_persistent = false;
     PersistPlan pp = plan_persistent(h);
     const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
-    const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : 4);
+    const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));
+    const bool wide = nt >= 4 && h->bulk_wide;   // warps own whole output tiles (no cross-warp partial sums)
+    const size_t bsmem = wide ? wide_smem(H, nt) : bulk_smem(H, nt);
     const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
-                           B <= kBulkMaxB && !packed && (int)bulk_smem(H, nt) <= h->max_smem_optin;
+                           B <= (h->bulk_wide ? kBulkMaxB : 32) && !packed && (int)bsmem <= h->max_smem_optin;
     bool use_bulk = false;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
         if (!fits && !bulk_fits) return PIMB200_ERR_UNSUPPORTED;
@@ -904,8 +1087,10 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         h->bulk_tag += (uint32_t)T + 1u;
         const void* fn = nt == 1 ? (const void*)lstm_persistent_bulk_kernel<1>
                        : nt == 2 ? (const void*)lstm_persistent_bulk_kernel<2>
-                                 : (const void*)lstm_persistent_bulk_kernel<4>;
-        const size_t smem = bulk_smem(H, nt);
+                       : !wide   ? (const void*)lstm_persistent_bulk_kernel<4>
+                       : nt == 4 ? (const void*)lstm_persistent_wide_kernel<4>
+                                 : (const void*)lstm_persistent_wide_kernel<8>;
+        const size_t smem = bsmem;
         PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void* kargs[] = {&a};
         if (h->prof) prof_mark(h, st);

@@ -54,7 +54,7 @@ class RnntDecoder:
         return {"cluster_size": cs.value, "smem_mask": mask.value, "smem_bytes": sm.value}
 
     def set_encoder_batch(self, n: int) -> None:
-        """Utterances the encoder advances in lock step (1..32)."""
+        """Utterances the encoder advances in lock step (1..64)."""
         check(_lib.lib().pimb200_rnnt_set_encoder_batch(self._h, int(n)), "rnnt_set_encoder_batch")
 
     def set_greedy_multi(self, mode: int) -> None:
