@@ -647,14 +647,17 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
 template <int NT>  // 4 or 8 tiles of 8 sequences
 __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
     constexpr int BP = NT * 8;
-    constexpr int NPW = NT / 4;                    // n-tiles per warp
+    constexpr int NPW = NT / 4;                      // n-tiles per warp
     constexpr int PPT = (8 * BP) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, T = a.T, B = a.B;
     const int pitch = H + 8;
     __half* Ws = reinterpret_cast<__half*>(smem_raw);                         // [32][pitch]
-    __half* hs = Ws + (size_t)kPersistRows * pitch;                           // [BP][pitch]
-    float* zbuf = reinterpret_cast<float*>(hs + (size_t)BP * pitch);          // [32 rows][BP]
+    // hidden states in the layout of the exchange records: hs[j][n][8] = units 8j..8j+7 of sequence n.  The gather is
+    // then one contiguous copy, and an mma B fragment (k = 16kt + 2t (+8), column n) reads 128 contiguous bytes per
+    // warp: no padding, no bank conflicts.
+    __half* hs = Ws + (size_t)kPersistRows * pitch;                           // [H/8][BP][8]
+    float* zbuf = reinterpret_cast<float*>(hs + (size_t)BP * H);              // [32 rows][BP]
     unsigned short* hpub = reinterpret_cast<unsigned short*>(zbuf + (size_t)kPersistRows * BP);  // [BP][8]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_cta = gridDim.x, cta = blockIdx.x;
@@ -670,12 +673,13 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
     }
     for (int i = tid; i < BP * H; i += kPersistThreads) {
         const int n = i / H, k = i - n * H;
-        hs[(size_t)n * pitch + k] = (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
+        hs[((size_t)(k >> 3) * BP + n) * 8 + (k & 7)] = (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
     }
     for (int i = tid; i < BP * 8; i += kPersistThreads) hpub[i] = 0;
 
     // gate pairs of this thread: pair p = tid + q*256 -> unit p / BP, sequence p % BP
     int gu[PPT], gn[PPT];
+    bool live[PPT];
     float c[PPT];
     float4 bias4[PPT], gx[PPT];
 #pragma unroll
@@ -683,10 +687,11 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
         const int p_ = tid + q * kPersistThreads;
         gu[q] = p_ / BP;
         gn[q] = p_ - gu[q] * BP;
+        live[q] = gn[q] < B;
         c[q] = 0.f;
         bias4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
         gx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (gn[q] < B) {
+        if (live[q]) {
             const int u = u0 + gu[q];
             c[q] = a.c0 ? __half2float(a.c0[(size_t)gn[q] * H + u]) : 0.f;
             bias4[q] = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
@@ -704,6 +709,8 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
     for (int s = 0; s < T; ++s) {
         const int t = a.reverse ? T - 1 - s : s;
         const int par = s & 1;
+        long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+        if (tr && tid == 0) tr[0] = clock64();
         // ---- 1. Z tile(s) of this warp over all of K
         float acc[NPW][4];
 #pragma unroll
@@ -711,16 +718,16 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
         const __half* arow = Ws + (size_t)(mt * 16 + a_row) * pitch + a_col;
-        const __half* brow = hs + (size_t)(nt0 * 8 + b_n) * pitch + b_k;
+        const __half* brow = hs + ((size_t)(nt0 * 8 + b_n)) * 8 + b_k;   // + (2kt [+1]) * BP * 8 per k-tile
 #pragma unroll 4
         for (int kt = 0; kt < ktiles; ++kt) {
-            const int k0 = kt << 4;
             uint32_t af[4];
-            ldmatrix_x4(af, arow + k0);
+            ldmatrix_x4(af, arow + (kt << 4));
 #pragma unroll
             for (int j = 0; j < NPW; ++j) {
-                const __half* hp = brow + (size_t)(j * 8) * pitch + k0;
-                mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(hp), *reinterpret_cast<const uint32_t*>(hp + 8));
+                const __half* hp = brow + (size_t)(2 * kt) * BP * 8 + j * 64;
+                mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(hp),
+                          *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8));
             }
         }
 #pragma unroll
@@ -730,30 +737,33 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
             *reinterpret_cast<float2*>(p + 8 * BP) = make_float2(acc[j][2], acc[j][3]);
         }
         __syncthreads();
-        // ---- 2. gates
+        if (tr && tid == 0) tr[1] = clock64();
+        // ---- 2. gates: the pairs of a thread are computed side by side (independent chains), stores are predicated
+        {
+            __half hh[PPT];
 #pragma unroll
-        for (int q = 0; q < PPT; ++q) {
-            if (gn[q] < B) {
-                const int u = u0 + gu[q], n = gn[q];
-                const float* z = zbuf + (size_t)(gu[q] * 4) * BP + n;
+            for (int q = 0; q < PPT; ++q) {
+                const float* z = zbuf + (size_t)(gu[q] * 4) * BP + gn[q];
                 const float zi = z[0] + gx[q].x + bias4[q].x, zf = z[BP] + gx[q].y + bias4[q].y,
                             zg = z[2 * BP] + gx[q].z + bias4[q].z, zo = z[3 * BP] + gx[q].w + bias4[q].w;
                 c[q] = sigmoidf_(zf) * c[q] + sigmoidf_(zi) * tanhf_(zg);
-                const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
-                hpub[n * 8 + gu[q]] = __half_as_ushort(hh);
-                if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh;
-                if (s == T - 1) {
-                    if (a.hn) a.hn[(size_t)n * H + u] = hh;
-                    if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[q]);
-                }
-                if (s + 1 < T) {
-                    const int tn = a.reverse ? t - 1 : t + 1;
-                    gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)n * a.g_bstride +
-                                                                   (size_t)u * 4));
+                hh[q] = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
+            }
+#pragma unroll
+            for (int q = 0; q < PPT; ++q) {
+                if (live[q]) {
+                    const int u = u0 + gu[q], n = gn[q];
+                    hpub[n * 8 + gu[q]] = __half_as_ushort(hh[q]);
+                    if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh[q];
+                    if (s == T - 1) {
+                        if (a.hn) a.hn[(size_t)n * H + u] = hh[q];
+                        if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[q]);
+                    }
                 }
             }
         }
         __syncthreads();
+        if (tr && tid == 0) tr[2] = clock64();
         // ---- 3. publish
         if (tid < B) {
             const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
@@ -765,6 +775,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
         }
         if (s + 1 == T) break;
         __syncthreads();
+        if (tr && tid == 0) tr[3] = clock64();
         const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
         if (tid < kBulkFlagCopies)
             asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
@@ -781,31 +792,35 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
                 if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
             }
             if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            if (tr && tid == 0) tr[4] = clock64();
             __threadfence();
+            if (tr && tid == 0) tr[5] = clock64();
         }
         if (__syncthreads_or(timed_out)) return;
-        // ---- 5. bulk fetch, eight 16-byte loads in flight per thread
+        if (tr && tid == 0) tr[6] = clock64();
+        // ---- 5. gather: the records of all CTAs are one contiguous block with the layout of hs; asynchronous 16-byte
+        //         copies straight into shared memory (L2 -> SMEM, no registers), all in flight at once
         {
             const uint4* src = a.data + (size_t)par * n_cta * BP;
+            const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(hs);
             const int items = n_cta * BP;
-            for (int i0 = tid; i0 < items; i0 += 8 * kPersistThreads) {
-                uint4 v[8];
+            for (int i = tid; i < items; i += kPersistThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)i * 16u), "l"(src + i) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            // next step's input-projection term: issued after the fences (a fence waits for loads in flight, and these
+            // may come from HBM) and behind the gather's copies; consumed after the next tensor-core phase
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int i = i0 + q * kPersistThreads;
-                    if (i < items) v[q] = src[i];
-                }
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int i = i0 + q * kPersistThreads;
-                    if (i < items) {
-                        const int n = i % BP, j = i / BP;
-                        if (n < B) *reinterpret_cast<uint4*>(hs + (size_t)n * pitch + j * 8) = v[q];
-                    }
+            for (int q = 0; q < PPT; ++q) {
+                if (live[q]) {
+                    const int tn = a.reverse ? t - 1 : t + 1;
+                    gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride +
+                                                                   (size_t)gn[q] * a.g_bstride + (size_t)(u0 + gu[q]) * 4));
                 }
             }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
+        if (tr && tid == 0) tr[7] = clock64();
     }
 }
 
@@ -833,7 +848,7 @@ struct pimb200_lstm {
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
-    int bulk_wide = 1;     // 1 = tile-owning warps for 17..64 sequences, 0 = K-split kernel (up to 32)
+    int bulk_wide = 1;     // 1 = tile-owning warps for 33..64 sequences, 2 = also for 17..32, 0 = K-split kernel only (up to 32)
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
@@ -979,7 +994,7 @@ extern "C" int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies) {
 // A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
-    h->bulk_wide = on ? 1 : 0;
+    h->bulk_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
     return PIMB200_OK;
 }
 extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
@@ -1016,7 +1031,7 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 
 static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
-    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * (H + 8) * 2 + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16;
+    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * H * 2 + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16;
 }
 static size_t bulk_smem(int H, int nt) {
     const int BP = nt * 8;
@@ -1060,7 +1075,8 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     PersistPlan pp = plan_persistent(h);
     const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
     const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));
-    const bool wide = nt >= 4 && h->bulk_wide;   // warps own whole output tiles (no cross-warp partial sums)
+    // 33..64 sequences: warps own whole output tiles; up to 32 the K-split kernel keeps the tensor pipes busier
+    const bool wide = nt >= 8 || (nt == 4 && h->bulk_wide == 2);
     const size_t bsmem = wide ? wide_smem(H, nt) : bulk_smem(H, nt);
     const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
                            B <= (h->bulk_wide ? kBulkMaxB : 32) && !packed && (int)bsmem <= h->max_smem_optin;
