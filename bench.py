@@ -26,6 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 T_FRAMES = 1000
+TRAFFIC_T1000 = 1.18e9   # bytes, lstm_persistent_wide_kernel<8>, T=1000, 64 sequences (ncu dram read+write)
 WORKLOAD = "C3: RNN-T greedy decode, 1000x240 frames per utterance, batch 1 per stream"
 
 
@@ -274,14 +275,17 @@ def run_gpu(args, rank, world, local):
                 "h2d_bytes_per_step": int(feats_host.numel() * 2),
                 "d2h_bytes_per_step": int(tokens_host.numel() * 4 + n_tokens_host.numel() * 4)},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "lstm_persistent_bulk_kernel<4> (W_hh recurrence, all T steps of 32 sequences per launch)",
+        "roofline": {"bound": "hbm", "kernel": "lstm_persistent_wide_kernel<8> (W_hh recurrence, all T steps of 64 sequences per launch)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src,
-                     # dram__bytes_read+write of one T=1000, 32-sequence launch from the committed ncu capture
-                     # (profiles/lstm_persistent_bulk_kernel_rnnt_prenet_32_sequences.txt); that launch's algorithmic
+                     # dram__bytes_read+write of one T=1000 launch from the committed ncu capture under profiles/
+                     # (fp32 gate pre-activations read once + fp16 outputs + one cold W_hh); that launch's algorithmic
                      # bytes are 8.39e9
-                     "traffic": 592.6e6,
+                     "traffic": TRAFFIC_T1000,
                      "launches": prof["recurrences"], "avg_launch_ms": prof["ms"] / max(prof["recurrences"], 1),
+                     "sequences_per_launch": min(eb, S),
+                     # what batch-1-per-stream execution would have to stream: every sequence its own W_hh per step
+                     "per_stream_equivalent_gbs": achieved * min(eb, S),
                      "share_of_step_time": share,
                      "note": "algorithmic bytes = T * 4H*H * 2 per launch (W_hh once per timestep, the streamed "
                              "formulation); the kernel serves them from shared memory"},
