@@ -169,6 +169,11 @@ int pimb200_lstm_last_status(pimb200_lstm* h);
 int pimb200_lstm_profile_enable(pimb200_lstm* h, int enable);
 int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrences, double* bytes);
 
+/* Opt-in A/B switch: 1 = run the recurrence of 17..64 lock-step sequences (H a multiple of 64) with tcgen05.mma and a
+ * tensor-memory accumulator instead of mma.sync.  Same results; measured slower on B200 for this shape class (32 useful
+ * rows per CTA), so the default is 0.  No counterpart in the reference. */
+int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on);
+
 /* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are
  * inside MIOpen. */

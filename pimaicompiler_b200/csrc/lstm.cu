@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "tc_common.cuh"
 
 namespace pimb200 {
 int launch_gemm_wx_simt(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
@@ -825,6 +826,243 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
 }
 
 // ---------------------------------------------------------------------------------------------
+// tcgen05 variant of the wide batched recurrence (17..64 sequences, H a multiple of 64).
+//
+// The per-step product Z[32 x BP] = W_slice[32 x H] . Hprev[H x BP] runs on the 5th-generation tensor cores: one
+// thread issues H/16 tcgen05.mma (kind::f16, M = 128, N = BP, K = 16) per step, the accumulator lives in tensor
+// memory, two warps read rows 0..31 back with tcgen05.ld.  Both operands sit in shared memory in the canonical
+// K-major 128-byte-swizzled layout, written by ordinary stores / cp.async (the gather writes each exchange record
+// straight to its swizzled place).  The instruction's M is 128 but a CTA owns 32 gate rows: the A descriptor of a
+// k-block simply runs on into the following shared memory, rows 32..127 of the accumulator are never read.
+// Exchange, gates and bounded waits are those of the wide kernel; every exit path frees the tensor memory.
+// Measured on B200 at H = 1024, 64 sequences: 14.9 us per step against 8.3 us for the mma.sync kernel.  With only 32
+// useful rows per CTA the instruction is shared-memory-bandwidth bound (each of the 64 MMAs of a step streams the
+// full 128-row A window, 6 KB with B), and the swizzled scatter of the gather costs more than the contiguous copy.
+// The kernel is therefore opt-in (pimb200_lstm_set_use_tc) and kept as the measured alternative.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {  // byte offset inside a [rows x 64 halves] tile
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_tc_kernel(BulkArgs a, int BP) {
+    using namespace pimb200::tc;
+    extern __shared__ unsigned char smem_raw_tc[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw_tc) + 1023) & ~uintptr_t(1023));
+    const int H = a.H, T = a.T, B = a.B;
+    const int kblocks = H >> 6;
+    const int a_kb_bytes = kPersistRows * 128;      // 4 KiB: 32 rows x 64 halves
+    const int b_kb_bytes = BP * 128;
+    unsigned char* sA = smem;                                           // [kblocks][32 x 128 B]
+    unsigned char* sB = sA + (size_t)kblocks * a_kb_bytes;              // [kblocks][BP x 128 B]; also absorbs A's over-read
+    float* zbuf = reinterpret_cast<float*>(sB + (size_t)kblocks * b_kb_bytes);   // [32][BP]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zbuf + (size_t)kPersistRows * BP);  // [BP][8]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(hpub + (size_t)BP * 8);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    const uint32_t bar_addr = smem_u32(bar);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x, cta = blockIdx.x;
+    const int u0 = cta * 8;
+    const int PPT = (8 * BP + kPersistThreads - 1) / kPersistThreads;  // (unit, sequence) pairs per thread: 1 or 2
+    const volatile int* abort_flag = a.status;
+
+    // W_hh slice -> A operand tiles
+    {
+        const int H8 = H >> 3;
+        const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
+        for (int i = tid; i < kPersistRows * H8; i += kPersistThreads) {
+            const int r = i / H8, c8 = i - r * H8;
+            *reinterpret_cast<uint4*>(sA + (size_t)(c8 >> 3) * a_kb_bytes + sw128_offset(r, c8 & 7)) =
+                ldg_stream_v4(src + (size_t)r * H8 + c8);
+        }
+    }
+    // h_{-1} -> B operand tiles (rows = sequences; rows >= B stay zero)
+    for (int i = tid; i < BP * (H >> 3); i += kPersistThreads) {
+        const int n = i / (H >> 3), c8 = i - n * (H >> 3);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (n < B && a.h0) v = *reinterpret_cast<const uint4*>(a.h0 + (size_t)n * H + c8 * 8);
+        *reinterpret_cast<uint4*>(sB + (size_t)(c8 >> 3) * b_kb_bytes + sw128_offset(n, c8 & 7)) = v;
+    }
+    for (int i = tid; i < BP * 8; i += kPersistThreads) hpub[i] = 0;
+    if (tid == 0) {
+        mbar_init(bar_addr, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int tmem_cols = BP <= 32 ? 32 : 64;
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // operand tiles were written by ordinary stores
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    // gate pairs of this thread: pair p = tid + q*256 -> unit p / BP, sequence p % BP
+    int gu[2], gn[2];
+    bool live[2];
+    float c[2];
+    float4 bias4[2], gx[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int p_ = tid + q * kPersistThreads;
+        gu[q] = p_ / BP;
+        gn[q] = p_ - gu[q] * BP;
+        live[q] = q < PPT && gu[q] < 8 && gn[q] < B;
+        c[q] = 0.f;
+        bias4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        gx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live[q]) {
+            const int u = u0 + gu[q];
+            c[q] = a.c0 ? __half2float(a.c0[(size_t)gn[q] * H + u]) : 0.f;
+            bias4[q] = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
+            const int t0 = a.reverse ? T - 1 : 0;
+            gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)gn[q] * a.g_bstride +
+                                                           (size_t)u * 4));
+        }
+        if (!live[q]) { gu[q] = 0; gn[q] = 0; }   // keeps the unconditional zbuf reads in bounds
+    }
+    // instruction descriptor: D = f32, A = B = f16, both K-major, N = BP, M = 128
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(BP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    int failed = 0;
+
+    for (int s = 0; s < T; ++s) {
+        const int t = a.reverse ? T - 1 - s : s;
+        const int par = s & 1;
+        long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+        if (tr && tid == 0) tr[0] = clock64();
+        // ---- 1. all of K on the tensor cores, issued by one thread
+        if (tid == 32) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)kb * a_kb_bytes));
+                const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)kb * b_kb_bytes));
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    umma_f16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            }
+            umma_commit(bar_addr);
+        }
+        // rows 0..31 of the accumulator -> zbuf: warps 0 and 4 own TMEM lanes 0..31, half of the columns each
+        if ((warp & 3) == 0 && warp < 8) {
+            if (!mbar_wait(bar_addr, (uint32_t)(s & 1), abort_flag)) failed = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (tr && tid == 0) tr[1] = clock64();
+            if (!failed) {
+                const int half = BP >> 1, c_begin = (warp >> 2) * half;
+                for (int c0 = c_begin; c0 < c_begin + half; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + (uint32_t)c0, r);
+#pragma unroll
+                    for (int q = 0; q < 16; q += 4)
+                        *reinterpret_cast<float4*>(zbuf + (size_t)lane * BP + c0 + q) =
+                            make_float4(__uint_as_float(r[q]), __uint_as_float(r[q + 1]), __uint_as_float(r[q + 2]),
+                                        __uint_as_float(r[q + 3]));
+                }
+            } else {
+                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        if (__syncthreads_or(failed)) { failed = 1; break; }
+        if (tr && tid == 0) tr[2] = clock64();
+        // ---- 2. gates
+        {
+            __half hh[2];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const float* z = zbuf + (size_t)(gu[q] * 4) * BP + gn[q];
+                const float zi = z[0] + gx[q].x + bias4[q].x, zf = z[BP] + gx[q].y + bias4[q].y,
+                            zg = z[2 * BP] + gx[q].z + bias4[q].z, zo = z[3 * BP] + gx[q].w + bias4[q].w;
+                c[q] = sigmoidf_(zf) * c[q] + sigmoidf_(zi) * tanhf_(zg);
+                hh[q] = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (live[q]) {
+                    const int u = u0 + gu[q], n = gn[q];
+                    hpub[n * 8 + gu[q]] = __half_as_ushort(hh[q]);
+                    if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh[q];
+                    if (s == T - 1) {
+                        if (a.hn) a.hn[(size_t)n * H + u] = hh[q];
+                        if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[q]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (tr && tid == 0) tr[3] = clock64();
+        // ---- 3. publish
+        if (tid < B) {
+            const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
+            if (s + 1 < T) {
+                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+                __threadfence();
+            }
+            if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)tid * a.y_bstride + u0) = v;
+        }
+        if (s + 1 == T) break;
+        __syncthreads();
+        if (tr && tid == 0) tr[4] = clock64();
+        const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        if (tid < kBulkFlagCopies)
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+        // ---- 4. flags
+        int timed_out = 0;
+        if (tid < n_cta) {
+            const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + tid) * 32;
+            int polls = 0;
+            while (true) {
+                uint32_t v;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (v == tag) break;
+                if (++polls >= a.poll_limit) { timed_out = 1; break; }
+                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+            }
+            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            __threadfence();
+        }
+        if (__syncthreads_or(timed_out)) { failed = 1; break; }
+        if (tr && tid == 0) tr[5] = clock64();
+        // ---- 5. gather: record (cta j, sequence n) = 16-byte chunk (j & 7) of row n in k-block j >> 3
+        {
+            const uint4* src = a.data + (size_t)par * n_cta * BP;
+            const uint32_t dst0 = smem_u32(sB);
+            const int items = n_cta * BP;
+            for (int i = tid; i < items; i += kPersistThreads) {
+                const int j = i / BP, n = i - j * BP;
+                const uint32_t dst = dst0 + (uint32_t)(j >> 3) * (uint32_t)b_kb_bytes + sw128_offset(n, j & 7);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + i) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                if (live[q]) {
+                    const int tn = a.reverse ? t - 1 : t + 1;
+                    gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride +
+                                                                   (size_t)gn[q] * a.g_bstride + (size_t)(u0 + gu[q]) * 4));
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the tensor core reads these tiles next
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tr && tid == 0) tr[6] = clock64();
+    }
+    // common exit: nobody may still use the tensor memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)tmem_cols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 struct pimb200_lstm {
@@ -848,6 +1086,7 @@ struct pimb200_lstm {
     int* d_status = nullptr;
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
+    int use_tc = 0;        // 1 = tcgen05 recurrence for 17..64 sequences (measured slower than mma.sync here: opt-in)
     int bulk_wide = 1;     // 1 = tile-owning warps for 33..64 sequences, 2 = also for 17..32, 0 = K-split kernel only (up to 32)
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
@@ -991,6 +1230,12 @@ extern "C" int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies) {
     h->xchg_copies = copies;
     return PIMB200_OK;
 }
+// A/B switch: 0 = never use the tcgen05 recurrence kernel.
+extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->use_tc = on ? 1 : 0;
+    return PIMB200_OK;
+}
 // A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
@@ -1032,6 +1277,9 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
     return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * H * 2 + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16;
+}
+static size_t tc_smem(int H, int BP) {
+    return (size_t)(H / 64) * (kPersistRows * 128 + BP * 128) + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16 + 64 + 1024;
 }
 static size_t bulk_smem(int H, int nt) {
     const int BP = nt * 8;
@@ -1080,6 +1328,34 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     const size_t bsmem = wide ? wide_smem(H, nt) : bulk_smem(H, nt);
     const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
                            B <= (h->bulk_wide ? kBulkMaxB : 32) && !packed && (int)bsmem <= h->max_smem_optin;
+    // tensor-core (tcgen05) recurrence: 17..64 sequences, H a multiple of 64
+    const int tc_bp = B <= 32 ? 32 : 64;   // accumulator columns; two warps read half of them each, 16 at a time
+    // the A descriptor of the last k-block runs 12 KiB past the weight tiles: the B tiles behind them must cover that
+    const bool tc_fits = h->use_tc && (H % 64 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B > 16 &&
+                         B <= kBulkMaxB && !packed && (size_t)(H / 64) * tc_bp * 128 >= 12288 &&
+                         (int)tc_smem(H, tc_bp) <= h->max_smem_optin;
+    if (tc_fits && (h->variant == PIMB200_LSTM_PERSISTENT || (h->variant == PIMB200_LSTM_AUTO && T >= 8))) {
+        BulkArgs a;
+        a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
+        a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
+        a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
+        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status;
+        a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+        a.trace = h->trace;
+        h->bulk_tag += (uint32_t)T + 1u;
+        int bp = tc_bp;
+        const size_t smem = tc_smem(H, bp);
+        PIMB200_CUDA_TRY(cudaFuncSetAttribute(lstm_persistent_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        void* kargs[] = {&a, &bp};
+        if (h->prof) prof_mark(h, st);
+        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel((const void*)lstm_persistent_tc_kernel, dim3(H / 8),
+                                                     dim3(kPersistThreads), kargs, smem, st));
+        if (h->prof) {
+            prof_mark(h, st);
+            h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
+        }
+        return PIMB200_OK;
+    }
     bool use_bulk = false;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
         if (!fits && !bulk_fits) return PIMB200_ERR_UNSUPPORTED;

@@ -204,3 +204,24 @@ def test_persistent_bounded_wait_reports_timeout_and_context_survives(B):
     assert m.last_status() == 0
     ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, False)
     assert_close(y, ref[0], LSTM_ATOL, LSTM_RTOL, "after a timed-out launch")
+
+
+@pytest.mark.parametrize("T,B,I,H", [(6, 64, 64, 1024), (9, 23, 32, 256), (5, 40, 16, 128)])
+def test_tcgen05_recurrence_variant_matches_oracle(T, B, I, H):
+    # the opt-in tensor-memory variant of the batched recurrence must give the same results as the default kernels
+    ops = _ops()
+    from pimaicompiler_b200 import _lib
+    g = torch.Generator().manual_seed(B * 7 + H)
+    ps = lstm_params(1, 1, I, H, g)
+    x = h16(torch.randn(T, B, I, generator=g))
+    h0 = h16(torch.randn(1, B, H, generator=g) * 0.5)
+    c0 = h16(torch.randn(1, B, H, generator=g) * 0.5)
+    ref = co.lstm(x.numpy(), [p.numpy() for p in ps], 1, False, True, h0.numpy(), c0.numpy())
+    m = ops.Lstm([to_dev(p) for p in ps], 1, False, I, H, True)
+    m.set_variant(ops.LSTM_PERSISTENT)
+    assert _lib.lib().pimb200_lstm_set_use_tc(m._h, 1) == 0
+    got = m.forward(to_dev(x), to_dev(h0), to_dev(c0))
+    torch.cuda.synchronize()
+    assert m.last_status() == 0
+    for name, a, b in zip(("y", "hn", "cn"), got, ref):
+        assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"tcgen05 recurrence {name}")
