@@ -735,6 +735,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         // Because an m16n8k16 pass always covers all 8 columns, the B operand of an evaluation must hold, for every
         // column, the state that utterance will read: buffers are indexed [parity][n], and a column that sits the
         // evaluation out simply produces a value nobody stores.
+        long long* trp = nullptr;
         auto pred_eval = [&](unsigned mask) {
             // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]); two K halves per m-tile
             if (warp < 2 * MTG) {
@@ -749,6 +750,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 store_acc(part + (size_t)kh * M * gl, gl, mt, acc, lane);
             }
             __syncthreads();
+            if (trp && tid == 0) trp[4] = clock64();
             if (gate_thread && (mask & (1u << gn))) {
                 const float* p0 = a.P0 + (size_t)tok[gn] * 4 * PH + (size_t)(u0 + gj) * 4;
                 float z[4];
@@ -761,6 +763,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
             }
             cluster.sync();
+            if (trp && tid == 0) trp[5] = clock64();
             // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias; the two products go to two warp groups
             if (warp < 2 * MTG) {
                 const int mt = warp % MTG, which = warp / MTG;
@@ -783,6 +786,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
             }
             cluster.sync();
+            if (trp && tid == 0) trp[6] = clock64();
             // ---- prediction half of the joint: Pj[n][j0 + q] = W1p[q,:] . h1new[n]; four K quarters per m-tile
             if (warp < 4 * MTJ) {
                 const int mt = warp % MTJ, kq = warp / MTJ;
@@ -808,6 +812,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 }
             }
             cluster.sync();
+            if (trp && tid == 0) trp[7] = clock64();
             par ^= mask;
         };
 
@@ -816,23 +821,28 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         constexpr int EPF = 8;
         const bool prefetch = M * JH <= EPF * nthr;
         float e_next[EPF];
+        // element q of a thread is (sequence n, column k) of the [M x JH] joint input; when JH equals the block size
+        // (the benchmark's 512) that is simply (q, tid) and no division is needed in the frame loop
+        const bool square = (JH == nthr);
         auto load_E = [&](int t) {
 #pragma unroll
             for (int q = 0; q < EPF; ++q) {
                 const int i = tid + q * nthr;
-                const int n = i / JH, k = i - n * JH;
+                const int n = square ? q : i / JH, k = square ? tid : i - (i / JH) * JH;
                 e_next[q] = (i < M * JH && (valid & (1u << n)) && t < a.Tp)
                                 ? __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k) : 0.f;
             }
         };
         if (prefetch) load_E(0);
         for (int t = 0; t < a.Tp; ++t) {
+            trp = (a.trace && grp == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
+            if (trp && tid == 0) trp[0] = clock64();
             // ---- joint input z[n] = relu(E[n][t] + Pj[n]) in fp16
             if (prefetch) {
 #pragma unroll
                 for (int q = 0; q < EPF; ++q) {
                     const int i = tid + q * nthr;
-                    const int n = i / JH, k = i - n * JH;
+                    const int n = square ? q : i / JH, k = square ? tid : i - (i / JH) * JH;
                     if (i < M * JH && (valid & (1u << n)))
                         zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e_next[q] + __half2float(Pj[i]), 0.f));
                 }
@@ -847,6 +857,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 }
             }
             __syncthreads();
+            if (trp && tid == 0) trp[1] = clock64();
             // ---- logits[n][r] = W2[r,:] . z[n] + b2[r]: 2 m-tiles x 4 K quarters
             if (warp < 8) {
                 const int mt = warp & 1, kq = warp >> 1;
@@ -856,6 +867,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
             }
             __syncthreads();
+            if (trp && tid == 0) trp[2] = clock64();
             if (tid < M * 32) {
                 const int n = tid >> 5, r = tid & 31;   // warp n handles utterance n, lane = vocabulary row
                 float v = (part[(size_t)n * jl + r] + part[(size_t)(M + n) * jl + r]) +
@@ -874,6 +886,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                     a.logits[((size_t)(utt0 + n) * a.Tp + t) * V + r] = v;
             }
             __syncthreads();
+            if (trp && tid == 0) trp[3] = clock64();
             unsigned emit = 0;
 #pragma unroll
             for (int m = 0; m < M; ++m) {
@@ -1241,7 +1254,7 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     if (max_clusters < 1) max_clusters = 1;
     // more utterances than clusters: several utterances per cluster in lock step
     // greedy_multi: 0 = one utterance per cluster, 1 = best available, 2 = FMA lock-step variant (4 per cluster)
-    const bool crowded = n_utts > max_clusters && !h->trace;
+    const bool crowded = n_utts > max_clusters;
     const bool use_mma = h->mma_ok && h->greedy_multi == 1 && crowded;
     const bool multi = !use_mma && h->fn_multi && h->greedy_multi >= 1 && crowded;
     const int groups = use_mma ? ceil_div(n_utts, kMmaUtts) : (multi ? ceil_div(n_utts, kGreedyMulti) : n_utts);

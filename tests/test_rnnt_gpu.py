@@ -131,3 +131,19 @@ def test_rnnt_tensor_core_greedy_baseline_config():
     toks, logits = dec.decode(torch.stack(feats).to(torch.float16).cuda(), want_logits=True)
     for i in (0, 5, 11):
         _check_utterance(cfg, w, feats[i], toks[i], logits[i].cpu().numpy(), to.rnnt_greedy)
+
+
+def test_rnnt_ragged_group_sizes_and_odd_frame_count():
+    # 70 utterances = one encoder group of 64 + one of 6, nine greedy groups of 8 (the last one ragged); and an odd
+    # number of frames, where the time stacking drops the last frame and the encoder falls back to one utterance at a time
+    cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=64, joint_hidden=256, vocab=11, blank=10)
+    w = to.make_rnnt_weights(cfg, seed=8, gain=2.0, logit_gain=6.0)
+    w.b2[cfg.blank] += 2.3
+    w.b2 = w.b2.to(torch.float16).to(torch.float32)
+    dec = _decoder(cfg, w)
+    for n_utts, T in ((70, 20), (11, 21)):
+        feats = [to.make_features(T, cfg, 500 + i) for i in range(n_utts)]
+        toks, logits = dec.decode(torch.stack(feats).to(torch.float16).cuda(), want_logits=True)
+        assert logits.shape == (n_utts, T // 2, cfg.vocab)
+        for i in (0, 5, n_utts - 7, n_utts - 1):
+            _check_utterance(cfg, w, feats[i], toks[i], logits[i].cpu().numpy(), co.rnnt_greedy)
