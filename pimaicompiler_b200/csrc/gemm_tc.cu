@@ -8,7 +8,7 @@
 // weight row m adds bias[m] once and, for a fixed j, the 32 lanes of a warp store 32 consecutive
 // elements of Y's row j.
 //
-// One CTA per output tile, warp-specialised:
+// Persistent CTAs (one per SM) loop over output tiles, warp-specialised, two accumulator stages in tensor memory:
 //   warp 0    TMA producer: cp.async.bulk.tensor (no multicast) of a [128 x 64] W tile and a [BN x 64] X tile
 //             per stage, 128-byte swizzle, completion on the stage's "full" mbarrier
 //   warp 1    allocates TMEM; one lane issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) four times per
@@ -40,16 +40,21 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;    // 16 KiB
 constexpr int THREADS = 192;                      // 6 warps
 constexpr size_t SMEM_BYTES = (size_t)STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;
+// warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 = epilogue
 
 struct GemmArgs {
     const __half* bias;   // [N] or NULL
     void* Y;
     int N, K, J, ldy, act, y_is_f32;
-    int bn;               // activation rows per CTA: multiple of 16 in [16, 128]
-    int tmem_cols;        // power of two >= max(32, bn)
+    int bn;               // activation rows per tile: multiple of 16 in [16, 128]
+    int tmem_cols;        // power of two >= max(32, 2 * bn): two accumulator stages
+    int m_tiles, j_tiles; // tiles along the weight rows and along the activation rows
     int* status;          // device status word
 };
 
+// Persistent: CTA b works on tiles b, b + gridDim.x, ...; consecutive tile numbers share the activation (j) block, so the
+// X tile stays hot in L2 while the CTAs of a wave walk down the weight rows.  Two accumulator stages in tensor memory
+// let the epilogue of one tile run under the MMAs of the next.
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs a) {
     extern __shared__ unsigned char smem_raw[];
@@ -58,12 +63,13 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     unsigned char* sA = smem;
     unsigned char* sB = smem + (size_t)STAGES * A_STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sB + (size_t)STAGES * B_STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S] accumulator ready; then the TMEM base address
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accbar = smem_u32(bars + 2 * STAGES);
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty; then the TMEM base
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t accf0 = smem_u32(bars + 2 * STAGES), acce0 = smem_u32(bars + 2 * STAGES + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, j0 = blockIdx.y * a.bn;
     const int kblocks = (a.K + BK - 1) / BK;
+    const int n_tiles = a.m_tiles * a.j_tiles;
     const volatile int* abort_flag = a.status;
 
     if (threadIdx.x == 0) {
@@ -71,7 +77,10 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accbar, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(accf0 + 8 * s, 1);
+            mbar_init(acce0 + 8 * s, 4);   // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -87,27 +96,29 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     bool failed = false;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer: one continuous stream of k-blocks over all tiles of this CTA ----------------
         if (lane == 0) {
             const uint32_t stage_bytes = (uint32_t)A_STAGE_BYTES + (uint32_t)a.bn * BK * 2;
-            int issued = 0;
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t it = (uint32_t)(kb / STAGES);
-                if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag)) { failed = true; break; }
-                mbar_expect_tx(full0 + 8 * s, stage_bytes);
-                tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_w, full0 + 8 * s, kb * BK, m0);
-                tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, j0);
-                ++issued;
+            int issued = 0;  // k-blocks issued so far = position in the shared-memory ring
+            for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x) {
+                const int m0 = (tile % a.m_tiles) * BM, j0 = (tile / a.m_tiles) * a.bn;
+                for (int kb = 0; kb < kblocks; ++kb, ++issued) {
+                    const int s = issued % STAGES;
+                    const uint32_t it = (uint32_t)(issued / STAGES);
+                    if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag)) { failed = true; break; }
+                    mbar_expect_tx(full0 + 8 * s, stage_bytes);
+                    tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_w, full0 + 8 * s, kb * BK, m0);
+                    tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, j0);
+                }
             }
             if (failed) {
                 atomicExch(a.status, PIMB200_ERR_TIMEOUT);
                 // let the copies already issued land before the CTA gives its shared memory back
                 const int first = issued > STAGES ? issued - STAGES : 0;
-                for (int kb = first; kb < issued; ++kb) {
-                    const int s = kb % STAGES;
+                for (int q = first; q < issued; ++q) {
+                    const int s = q % STAGES;
                     for (uint32_t i = 0; i < (1u << 20); ++i)
-                        if (mbar_try_wait(full0 + 8 * s, (uint32_t)(kb / STAGES) & 1)) break;
+                        if (mbar_try_wait(full0 + 8 * s, (uint32_t)(q / STAGES) & 1)) break;
                 }
             }
         }
@@ -116,37 +127,53 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (lane == 0) {
             // instruction descriptor: D = f32, A = B = f16, both K-major, N = bn, M = 128
             const uint32_t idesc = (1u << 4) | ((uint32_t)(a.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            for (int kb = 0; kb < kblocks; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t it = (uint32_t)(kb / STAGES);
-                if (!mbar_wait(full0 + 8 * s, it & 1, abort_flag)) { failed = true; break; }
+            int consumed = 0, local = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x, ++local) {
+                const int as = local & 1;                          // accumulator stage
+                const uint32_t ait = (uint32_t)(local >> 1);        // how often this stage has been used before
+                if (!mbar_wait(acce0 + 8 * as, (ait & 1) ^ 1, abort_flag)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
-                const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(as * a.bn);
+                for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
+                    const int s = consumed % STAGES;
+                    const uint32_t it = (uint32_t)(consumed / STAGES);
+                    if (!mbar_wait(full0 + 8 * s, it & 1, abort_flag)) { failed = true; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
+                    const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // advance 16 halves = 32 bytes inside the swizzle row: +2 in the descriptor's 16-byte units
-                    umma_f16(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advance 16 halves = 32 bytes inside the swizzle row: +2 in the descriptor's 16-byte units
+                        umma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
                 }
-                umma_commit(empty0 + 8 * s);  // the stage is free once these MMAs have read it
+                umma_commit(accf0 + 8 * as);      // this tile's accumulator is complete once everything above retires
             }
-            if (failed) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
-            umma_commit(accbar);  // accumulator complete (or whatever was issued, on failure) -> epilogue may proceed
+            if (failed) {
+                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                umma_commit(accf0);               // wake epilogue warps; they see the status word and leave
+                umma_commit(accf0 + 8);
+            }
         }
     } else {
         // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
         const int q = warp & 3;
-        const int m = m0 + q * 32 + lane;
-        bool ok = mbar_wait(accbar, 0, abort_flag);
-        if (!ok) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        ok = ok && (*abort_flag == 0);
-        if (ok) {
+        int local = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
+            const int as = local & 1;
+            const uint32_t ait = (uint32_t)(local >> 1);
+            const int m0 = (tile % a.m_tiles) * BM, j0 = (tile / a.m_tiles) * a.bn;
+            const int m = m0 + q * 32 + lane;
+            bool ok = mbar_wait(accf0 + 8 * as, ait & 1, abort_flag);
+            if (!ok) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (!ok || *abort_flag != 0) break;
             const float bv = (a.bias && m < a.N) ? __half2float(a.bias[m]) : 0.f;
             for (int c0 = 0; c0 < a.bn; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.bn + c0), r);
                 if (m < a.N) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
@@ -162,6 +189,10 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     }
                 }
             }
+            // this warp is done reading the stage: hand it back to the MMA issuer
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acce0 + 8 * as) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -232,12 +263,19 @@ static int launch(const __half* W, const __half* X, const __half* bias, void* Y,
     GemmArgs a;
     a.bias = bias; a.Y = Y; a.N = N; a.K = K; a.J = J; a.ldy = ldy; a.act = act; a.y_is_f32 = y_is_f32;
     a.bn = J >= BN_MAX ? BN_MAX : ((J + 15) / 16) * 16;
-    a.tmem_cols = a.bn <= 32 ? 32 : (a.bn <= 64 ? 64 : 128);
+    // two stages of bn columns; the epilogue reads 32 columns at a time, so the second stage needs its length rounded up
+    const int need_cols = a.bn + ((a.bn + 31) / 32) * 32;
+    a.tmem_cols = need_cols <= 32 ? 32 : (need_cols <= 64 ? 64 : (need_cols <= 128 ? 128 : 256));
+    a.m_tiles = ceil_div(N, BM);
+    a.j_tiles = ceil_div(J, a.bn);
     a.status = status;
     CUtensorMap map_w, map_x;
     if (!encode_2d(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return PIMB200_ERR_UNSUPPORTED;
     if (!encode_2d(&map_x, X, (uint64_t)J, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)a.bn)) return PIMB200_ERR_UNSUPPORTED;
-    dim3 grid(ceil_div(N, BM), ceil_div(J, a.bn));
+    const long tiles = (long)a.m_tiles * a.j_tiles;
+    int sms = kNumSmB200;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = (int)(tiles < sms ? tiles : sms);
     gemm_wx_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_w, map_x, a);
     return launch_status();
 }
