@@ -288,7 +288,7 @@ def run_gpu(args, rank, world, local):
                      "per_stream_equivalent_gbs": achieved * min(eb, S),
                      "share_of_step_time": share,
                      "note": "algorithmic bytes = T * 4H*H * 2 per launch (W_hh once per timestep, the streamed "
-                             "formulation); the kernel serves them from shared memory"},
+                             "formulation); the kernel keeps them in registers as mma fragments"},
         "clocks": clocks,
     }
     if cpu is not None:

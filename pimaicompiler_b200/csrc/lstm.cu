@@ -641,42 +641,70 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
 }
 
 // ---------------------------------------------------------------------------------------------
-// wide variant of the batched persistent recurrence (up to 64 sequences): the same exchange protocol, but each warp
-// owns whole output tiles (one 16-row m-tile x NT/4 n-tiles of 8 sequences, all of K), so no partial sums cross
-// warps: the accumulators go straight to a [32 x BP] fp32 tile in shared memory and the gate threads read from there.
+// wide variant of the batched persistent recurrence (up to 64 sequences, H a multiple of 16 up to 1024): the same
+// exchange protocol, but the CTA's slice of W_hh lives in REGISTERS as mma A fragments for the whole launch.  Warp w
+// owns k-tiles kq, kq+4, kq+8, ... (kq = w & 3) of both 16-row m-tiles and one half of the sequence tiles
+// (nh = w >> 2), so per k-tile it reads only B fragments from shared memory (1 KiB for 8 mma.sync; with A staged in
+// shared memory the tensor-core phase was bound by shared-memory bandwidth, 512 KiB per step).  The four K-partials
+// of a tile meet in a padded fp32 buffer that the gate threads sum.
+// The gather of the exchanged hidden states is one contiguous block, fetched by the bulk-copy engine in 16 KiB
+// copies that complete on one mbarrier.
 // ---------------------------------------------------------------------------------------------
+constexpr int kWideThreads = kPersistThreads;
+constexpr int kWideKq = 4;         // K-split of the tensor-core phase across warps
+constexpr int kWideMaxKtw = 16;    // k-tiles per warp held in registers (H <= 1024)
+
 template <int NT>  // 4 or 8 tiles of 8 sequences
-__global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
+__global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
     constexpr int BP = NT * 8;
-    constexpr int NPW = NT / 4;                      // n-tiles per warp
+    constexpr int NH = NT / 2;                       // n-tiles per warp
+    constexpr int ZP = BP + 8;                       // padded row pitch of the partial-sum tiles (floats)
     constexpr int PPT = (8 * BP) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, T = a.T, B = a.B;
-    const int pitch = H + 8;
-    __half* Ws = reinterpret_cast<__half*>(smem_raw);                         // [32][pitch]
     // hidden states in the layout of the exchange records: hs[j][n][8] = units 8j..8j+7 of sequence n.  The gather is
     // then one contiguous copy, and an mma B fragment (k = 16kt + 2t (+8), column n) reads 128 contiguous bytes per
     // warp: no padding, no bank conflicts.
-    __half* hs = Ws + (size_t)kPersistRows * pitch;                           // [H/8][BP][8]
-    float* zbuf = reinterpret_cast<float*>(hs + (size_t)BP * H);              // [32 rows][BP]
-    unsigned short* hpub = reinterpret_cast<unsigned short*>(zbuf + (size_t)kPersistRows * BP);  // [BP][8]
+    __half* hs = reinterpret_cast<__half*>(smem_raw);                         // [H/8][BP][8]
+    float* zpart = reinterpret_cast<float*>(hs + (size_t)BP * H);             // [kWideKq][32 rows][ZP]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + (size_t)kWideKq * kPersistRows * ZP);  // [BP][8]
+    uint64_t* gbar = reinterpret_cast<uint64_t*>(hpub + (size_t)BP * 8);
+    const uint32_t gbar_addr = (uint32_t)__cvta_generic_to_shared(gbar);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_cta = gridDim.x, cta = blockIdx.x;
     const int u0 = cta * 8;
     const int ktiles = H >> 4;
+    if (tid == 0) {
+        pimb200::tc::mbar_init(gbar_addr, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int kq = warp & (kWideKq - 1), nh = (warp >> 2) & 1;
+    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
+    // A fragments of this warp: afrag[i][m] = rows 16m..16m+15 of the slice, k-tile kWideKq*i + kq
+    uint32_t afrag[kWideMaxKtw][2][4];
     {
-        const int H8 = H >> 3;
-        const uint4* src = reinterpret_cast<const uint4*>(a.Whh + (size_t)u0 * 4 * H);
-        for (int i = tid; i < kPersistRows * H8; i += kPersistThreads) {
-            const int r = i / H8, c8 = i - r * H8;
-            *reinterpret_cast<uint4*>(Ws + (size_t)r * pitch + c8 * 8) = ldg_stream_v4(src + (size_t)r * H8 + c8);
+        const __half* wbase = a.Whh + (size_t)u0 * 4 * H;
+#pragma unroll
+        for (int i = 0; i < kWideMaxKtw; ++i) {
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    afrag[i][m][r] = 0u;
+                    if (kWideKq * i + kq < ktiles) {
+                        const int row = m * 16 + b_n + (r & 1) * 8;
+                        const int k = (kWideKq * i + kq) * 16 + b_k + (r >> 1) * 8;
+                        afrag[i][m][r] = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)row * H + k));
+                    }
+                }
+            }
         }
     }
-    for (int i = tid; i < BP * H; i += kPersistThreads) {
+    for (int i = tid; i < BP * H; i += kWideThreads) {
         const int n = i / H, k = i - n * H;
         hs[((size_t)(k >> 3) * BP + n) * 8 + (k & 7)] = (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
     }
-    for (int i = tid; i < BP * 8; i += kPersistThreads) hpub[i] = 0;
+    for (int i = tid; i < BP * 8; i += kWideThreads) hpub[i] = 0;
 
     // gate pairs of this thread: pair p = tid + q*256 -> unit p / BP, sequence p % BP
     int gu[PPT], gn[PPT];
@@ -701,10 +729,6 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
                                                            (size_t)u * 4));
         }
     }
-    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
-    const int a_col = (lane >> 4) * 8;
-    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
-    const int mt = warp & 1, nt0 = (warp >> 1) * NPW;   // this warp's output tiles
     __syncthreads();
 
     for (int s = 0; s < T; ++s) {
@@ -712,30 +736,43 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
         const int par = s & 1;
         long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
         if (tr && tid == 0) tr[0] = clock64();
-        // ---- 1. Z tile(s) of this warp over all of K
-        float acc[NPW][4];
+        // ---- 1. K-partial Z tiles of this warp
+        {
+            float acc[2][NH][4];
 #pragma unroll
-        for (int j = 0; j < NPW; ++j)
+            for (int m = 0; m < 2; ++m)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-        const __half* arow = Ws + (size_t)(mt * 16 + a_row) * pitch + a_col;
-        const __half* brow = hs + ((size_t)(nt0 * 8 + b_n)) * 8 + b_k;   // + (2kt [+1]) * BP * 8 per k-tile
-#pragma unroll 4
-        for (int kt = 0; kt < ktiles; ++kt) {
-            uint32_t af[4];
-            ldmatrix_x4(af, arow + (kt << 4));
+                for (int j = 0; j < NH; ++j)
 #pragma unroll
-            for (int j = 0; j < NPW; ++j) {
-                const __half* hp = brow + (size_t)(2 * kt) * BP * 8 + j * 64;
-                mma_16816(acc[j], af, *reinterpret_cast<const uint32_t*>(hp),
-                          *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8));
+                    for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+            const __half* brow = hs + ((size_t)(nh * NH * 8 + b_n)) * 8 + b_k;   // + (2kt [+1]) * BP * 8 per k-tile
+#pragma unroll
+            for (int i = 0; i < kWideMaxKtw; ++i) {
+                if (kWideKq * i + kq < ktiles) {   // warp-uniform
+                    const int kt = kWideKq * i + kq;
+                    const __half* hp = brow + (size_t)(2 * kt) * BP * 8;
+                    uint32_t b0[NH], b1[NH];
+#pragma unroll
+                    for (int j = 0; j < NH; ++j) {
+                        b0[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64);
+                        b1[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64 + (size_t)BP * 8);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NH; ++j) {
+                        mma_16816(acc[0][j], afrag[i][0], b0[j], b1[j]);
+                        mma_16816(acc[1][j], afrag[i][1], b0[j], b1[j]);
+                    }
+                }
             }
-        }
+            float* zq = zpart + (size_t)kq * kPersistRows * ZP;
 #pragma unroll
-        for (int j = 0; j < NPW; ++j) {
-            float* p = zbuf + (size_t)(mt * 16 + (lane >> 2)) * BP + (nt0 + j) * 8 + b_k;
-            *reinterpret_cast<float2*>(p) = make_float2(acc[j][0], acc[j][1]);
-            *reinterpret_cast<float2*>(p + 8 * BP) = make_float2(acc[j][2], acc[j][3]);
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int j = 0; j < NH; ++j) {
+                    float* p = zq + (size_t)(m * 16 + b_n) * ZP + (nh * NH + j) * 8 + b_k;
+                    *reinterpret_cast<float2*>(p) = make_float2(acc[m][j][0], acc[m][j][1]);
+                    *reinterpret_cast<float2*>(p + 8 * ZP) = make_float2(acc[m][j][2], acc[m][j][3]);
+                }
         }
         __syncthreads();
         if (tr && tid == 0) tr[1] = clock64();
@@ -744,9 +781,14 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
             __half hh[PPT];
 #pragma unroll
             for (int q = 0; q < PPT; ++q) {
-                const float* z = zbuf + (size_t)(gu[q] * 4) * BP + gn[q];
-                const float zi = z[0] + gx[q].x + bias4[q].x, zf = z[BP] + gx[q].y + bias4[q].y,
-                            zg = z[2 * BP] + gx[q].z + bias4[q].z, zo = z[3 * BP] + gx[q].w + bias4[q].w;
+                const float* z = zpart + (size_t)(gu[q] * 4) * ZP + gn[q];
+                float zi = gx[q].x + bias4[q].x, zf = gx[q].y + bias4[q].y, zg = gx[q].z + bias4[q].z,
+                      zo = gx[q].w + bias4[q].w;
+#pragma unroll
+                for (int k = 0; k < kWideKq; ++k) {
+                    const float* zk = z + (size_t)k * kPersistRows * ZP;
+                    zi += zk[0]; zf += zk[ZP]; zg += zk[2 * ZP]; zo += zk[3 * ZP];
+                }
                 c[q] = sigmoidf_(zf) * c[q] + sigmoidf_(zi) * tanhf_(zg);
                 hh[q] = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
             }
@@ -799,28 +841,37 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_wide_kerne
         }
         if (__syncthreads_or(timed_out)) return;
         if (tr && tid == 0) tr[6] = clock64();
-        // ---- 5. gather: the records of all CTAs are one contiguous block with the layout of hs; asynchronous 16-byte
-        //         copies straight into shared memory (L2 -> SMEM, no registers), all in flight at once
-        {
-            const uint4* src = a.data + (size_t)par * n_cta * BP;
+        // ---- 5. gather: the records of all CTAs are one contiguous block with the layout of hs, fetched by the bulk-copy
+        //         engine (no cluster multicast).  Nobody else waits here: the next step's tensor-core loop waits piece
+        //         by piece.
+        if (tid == 0) {
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP);
             const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(hs);
-            const int items = n_cta * BP;
-            for (int i = tid; i < items; i += kPersistThreads)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + (uint32_t)i * 16u), "l"(src + i) : "memory");
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            // next step's input-projection term: issued after the fences (a fence waits for loads in flight, and these
-            // may come from HBM) and behind the gather's copies; consumed after the next tensor-core phase
-#pragma unroll
-            for (int q = 0; q < PPT; ++q) {
-                if (live[q]) {
-                    const int tn = a.reverse ? t - 1 : t + 1;
-                    gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride +
-                                                                   (size_t)gn[q] * a.g_bstride + (size_t)(u0 + gu[q]) * 4));
-                }
+            const uint32_t total = (uint32_t)n_cta * BP * 16u;
+            asm volatile("fence.proxy.async;" ::: "memory");   // records were written through the generic proxy
+            pimb200::tc::mbar_expect_tx(gbar_addr, total);
+            for (uint32_t off = 0; off < total; off += 16384u) {
+                const uint32_t len = total - off < 16384u ? total - off : 16384u;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst0 + off),
+                             "l"(src + off), "r"(len), "r"(gbar_addr)
+                             : "memory");
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        __syncthreads();
+        // next step's input-projection term: issued after the fences (a fence waits for loads in flight, and these may
+        // come from HBM); consumed after the next tensor-core phase
+#pragma unroll
+        for (int q = 0; q < PPT; ++q) {
+            if (live[q]) {
+                const int tn = a.reverse ? t - 1 : t + 1;
+                gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)gn[q] * a.g_bstride +
+                                                               (size_t)(u0 + gu[q]) * 4));
+            }
+        }
+        if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status))) {
+            atomicExch(a.status, PIMB200_ERR_TIMEOUT);   // a bulk copy never completed within the wait limit
+            timed_out = 1;
+        }
+        if (__syncthreads_or(timed_out)) return;
         if (tr && tid == 0) tr[7] = clock64();
     }
 }
@@ -1276,7 +1327,7 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 
 static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
-    return (size_t)kPersistRows * (H + 8) * 2 + (size_t)BP * H * 2 + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16;
+    return (size_t)BP * H * 2 + (size_t)kWideKq * kPersistRows * (BP + 8) * 4 + (size_t)BP * 16 + 16;
 }
 static size_t tc_smem(int H, int BP) {
     return (size_t)(H / 64) * (kPersistRows * 128 + BP * 128) + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16 + 64 + 1024;
@@ -1324,10 +1375,12 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
     const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));
     // 33..64 sequences: warps own whole output tiles; up to 32 the K-split kernel keeps the tensor pipes busier
-    const bool wide = nt >= 8 || (nt == 4 && h->bulk_wide == 2);
+    // (the wide kernel keeps its W_hh slice in registers: H at most 1024)
+    const bool wide_ok = (H % 16 == 0) && H <= 16 * kWideKq * kWideMaxKtw;
+    const bool wide = wide_ok && (nt >= 8 || (nt == 4 && h->bulk_wide == 2));
     const size_t bsmem = wide ? wide_smem(H, nt) : bulk_smem(H, nt);
     const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
-                           B <= (h->bulk_wide ? kBulkMaxB : 32) && !packed && (int)bsmem <= h->max_smem_optin;
+                           B <= (h->bulk_wide ? kBulkMaxB : 32) && (nt <= 4 || wide) && !packed && (int)bsmem <= h->max_smem_optin;
     // tensor-core (tcgen05) recurrence: 17..64 sequences, H a multiple of 64
     const int tc_bp = B <= 32 ? 32 : 64;   // accumulator columns; two warps read half of them each, 16 at a time
     // the A descriptor of the last k-block runs 12 KiB past the weight tiles: the B tiles behind them must cover that
@@ -1386,7 +1439,7 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void* kargs[] = {&a};
         if (h->prof) prof_mark(h, st);
-        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(kPersistThreads), kargs, smem, st));
+        PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(wide ? kWideThreads : kPersistThreads), kargs, smem, st));
         if (h->prof) {
             prof_mark(h, st);
             h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
