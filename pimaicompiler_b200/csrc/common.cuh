@@ -89,12 +89,19 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// exp through the special-function unit, then an IEEE-rounded reciprocal: abs error ~1e-7, and no
-// division subroutine on the recurrence's critical path
-__device__ __forceinline__ float sigmoidf_(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+// exp and reciprocal both through the special-function unit (ex2.approx, rcp.approx: 1 ulp each, abs error of the
+// result ~2e-7, far below the fp16 rounding of h).  The IEEE-rounded reciprocal (rcp.rn) expands to a Newton sequence
+// with a guarded slow path; ten of those per LSTM cell ran back to back and made up most of the gate phase of the
+// recurrence kernels.
+__device__ __forceinline__ float rcp_approx(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_approx(1.0f + __expf(-x)); }
 __device__ __forceinline__ float tanhf_(float x) {
     // tanh(x) = 2*sigmoid(2x) - 1
-    return fmaf(2.0f, __frcp_rn(1.0f + __expf(-2.0f * x)), -1.0f);
+    return fmaf(2.0f, rcp_approx(1.0f + __expf(-2.0f * x)), -1.0f);
 }
 
 }  // namespace pimb200

@@ -646,7 +646,8 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
 // owns k-tiles kq, kq+4, kq+8, ... (kq = w & 3) of both 16-row m-tiles and one half of the sequence tiles
 // (nh = w >> 2), so per k-tile it reads only B fragments from shared memory (1 KiB for 8 mma.sync; with A staged in
 // shared memory the tensor-core phase was bound by shared-memory bandwidth, 512 KiB per step).  The four K-partials
-// of a tile meet in a padded fp32 buffer that the gate threads sum.
+// of a tile meet in a padded fp32 buffer (the four gates of a unit side by side, so a gate thread fetches a partial
+// with one 128-bit load) that the gate threads sum.
 // The gather of the exchanged hidden states is one contiguous block, fetched by the bulk-copy engine in 16 KiB
 // copies that complete on one mbarrier.
 // ---------------------------------------------------------------------------------------------
@@ -658,7 +659,7 @@ template <int NT>  // 4 or 8 tiles of 8 sequences
 __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
     constexpr int BP = NT * 8;
     constexpr int NH = NT / 2;                       // n-tiles per warp
-    constexpr int ZP = BP + 8;                       // padded row pitch of the partial-sum tiles (floats)
+    constexpr int ZP = BP + 1;                       // padded sequence pitch of the partial sums: [kq][unit][ZP][gate]
     constexpr int PPT = (8 * BP) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, T = a.T, B = a.B;
@@ -666,8 +667,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
     // then one contiguous copy, and an mma B fragment (k = 16kt + 2t (+8), column n) reads 128 contiguous bytes per
     // warp: no padding, no bank conflicts.
     __half* hs = reinterpret_cast<__half*>(smem_raw);                         // [H/8][BP][8]
-    float* zpart = reinterpret_cast<float*>(hs + (size_t)BP * H);             // [kWideKq][32 rows][ZP]
-    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + (size_t)kWideKq * kPersistRows * ZP);  // [BP][8]
+    float* zpart = reinterpret_cast<float*>(hs + (size_t)BP * H);             // [kWideKq][8 units][ZP][4 gates]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + (size_t)kWideKq * 8 * ZP * 4);  // [BP][8]
     uint64_t* gbar = reinterpret_cast<uint64_t*>(hpub + (size_t)BP * 8);
     const uint32_t gbar_addr = (uint32_t)__cvta_generic_to_shared(gbar);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -764,15 +765,18 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
                     }
                 }
             }
-            float* zq = zpart + (size_t)kq * kPersistRows * ZP;
+            // rows are gate rows (unit*4 + gate): scatter them so that the gates of a (unit, sequence) cell are adjacent;
+            // ZP = 1 mod 8 keeps the 32 lanes of each store on distinct banks
+            float* zq = zpart + (size_t)kq * 8 * ZP * 4;
 #pragma unroll
             for (int m = 0; m < 2; ++m)
 #pragma unroll
-                for (int j = 0; j < NH; ++j) {
-                    float* p = zq + (size_t)(m * 16 + b_n) * ZP + (nh * NH + j) * 8 + b_k;
-                    *reinterpret_cast<float2*>(p) = make_float2(acc[m][j][0], acc[m][j][1]);
-                    *reinterpret_cast<float2*>(p + 8 * ZP) = make_float2(acc[m][j][2], acc[m][j][3]);
-                }
+                for (int j = 0; j < NH; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int r = m * 16 + b_n + (i >> 1) * 8, n = (nh * NH + j) * 8 + b_k + (i & 1);
+                        zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][j][i];
+                    }
         }
         __syncthreads();
         if (tr && tid == 0) tr[1] = clock64();
@@ -781,13 +785,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
             __half hh[PPT];
 #pragma unroll
             for (int q = 0; q < PPT; ++q) {
-                const float* z = zpart + (size_t)(gu[q] * 4) * ZP + gn[q];
                 float zi = gx[q].x + bias4[q].x, zf = gx[q].y + bias4[q].y, zg = gx[q].z + bias4[q].z,
                       zo = gx[q].w + bias4[q].w;
 #pragma unroll
                 for (int k = 0; k < kWideKq; ++k) {
-                    const float* zk = z + (size_t)k * kPersistRows * ZP;
-                    zi += zk[0]; zf += zk[ZP]; zg += zk[2 * ZP]; zo += zk[3 * ZP];
+                    const float4 zk = *reinterpret_cast<const float4*>(zpart + ((size_t)(k * 8 + gu[q]) * ZP + gn[q]) * 4);
+                    zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
                 }
                 c[q] = sigmoidf_(zf) * c[q] + sigmoidf_(zi) * tanhf_(zg);
                 hh[q] = __float2half_rn(sigmoidf_(zo) * tanhf_(c[q]));
@@ -810,18 +813,16 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         // ---- 3. publish
         if (tid < B) {
             const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
-            if (s + 1 < T) {
-                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
-                __threadfence();
-            }
+            if (s + 1 < T) a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
             if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)tid * a.y_bstride + u0) = v;
         }
         if (s + 1 == T) break;
         __syncthreads();
         if (tr && tid == 0) tr[3] = clock64();
         const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        // release: the flag writers fence after the barrier, which covers the record stores of the whole CTA
         if (tid < kBulkFlagCopies)
-            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
         // ---- 4. flags
         int timed_out = 0;
         if (tid < n_cta) {
@@ -836,7 +837,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
             }
             if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
             if (tr && tid == 0) tr[4] = clock64();
-            __threadfence();
+            {   // acquire: one acquire load of the flag just seen (cheaper than a full fence; the data is read by the
+                // bulk-copy engine after the barrier below)
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                if (v != tag) timed_out = 1;   // cannot happen: flags only move forward within a launch
+            }
             if (tr && tid == 0) tr[5] = clock64();
         }
         if (__syncthreads_or(timed_out)) return;
@@ -844,11 +850,11 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         // ---- 5. gather: the records of all CTAs are one contiguous block with the layout of hs, fetched by the bulk-copy
         //         engine (no cluster multicast).  Nobody else waits here: the next step's tensor-core loop waits piece
         //         by piece.
-        if (tid == 0) {
+        if (tid == kWideThreads - 32) {   // a thread that did not poll
             const unsigned char* src = reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP);
             const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(hs);
             const uint32_t total = (uint32_t)n_cta * BP * 16u;
-            asm volatile("fence.proxy.async;" ::: "memory");   // records were written through the generic proxy
+            asm volatile("fence.proxy.async.global;" ::: "memory");   // records were written through the generic proxy
             pimb200::tc::mbar_expect_tx(gbar_addr, total);
             for (uint32_t off = 0; off < total; off += 16384u) {
                 const uint32_t len = total - off < 16384u ? total - off : 16384u;
@@ -863,8 +869,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         for (int q = 0; q < PPT; ++q) {
             if (live[q]) {
                 const int tn = a.reverse ? t - 1 : t + 1;
-                gx[q] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)tn * a.g_tstride + (size_t)gn[q] * a.g_bstride +
-                                                               (size_t)(u0 + gu[q]) * 4));
+                // volatile: the load must issue here, a whole tensor-core phase ahead of its use (left to the
+                // scheduler it sinks towards the use to shorten the live range, and its latency lands in the gates)
+                const float* gp = a.G + (size_t)tn * a.g_tstride + (size_t)gn[q] * a.g_bstride + (size_t)(u0 + gu[q]) * 4;
+                asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(gx[q].x), "=f"(gx[q].y), "=f"(gx[q].z), "=f"(gx[q].w)
+                             : "l"(gp));
             }
         }
         if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status))) {
@@ -1327,7 +1337,7 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 
 static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
-    return (size_t)BP * H * 2 + (size_t)kWideKq * kPersistRows * (BP + 8) * 4 + (size_t)BP * 16 + 16;
+    return (size_t)BP * H * 2 + (size_t)kWideKq * 8 * (BP + 1) * 16 + (size_t)BP * 16 + 16;
 }
 static size_t tc_smem(int H, int BP) {
     return (size_t)(H / 64) * (kPersistRows * 128 + BP * 128) + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16 + 64 + 1024;
