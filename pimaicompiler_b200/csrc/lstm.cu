@@ -648,8 +648,8 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
 // shared memory the tensor-core phase was bound by shared-memory bandwidth, 512 KiB per step).  The four K-partials
 // of a tile meet in a padded fp32 buffer (the four gates of a unit side by side, so a gate thread fetches a partial
 // with one 128-bit load) that the gate threads sum.
-// The gather of the exchanged hidden states is one contiguous block, fetched by the bulk-copy engine in 16 KiB
-// copies that complete on one mbarrier.
+// The gather of the exchanged hidden states is one contiguous block, fetched by the bulk-copy engine: each warp
+// polls the flags of one group of CTAs and issues the copy of that group's records, all completing on one mbarrier.
 // ---------------------------------------------------------------------------------------------
 constexpr int kWideThreads = kPersistThreads;
 constexpr int kWideKq = 4;         // K-split of the tensor-core phase across warps
@@ -675,8 +675,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
     const int n_cta = gridDim.x, cta = blockIdx.x;
     const int u0 = cta * 8;
     const int ktiles = H >> 4;
+    const int cpw = (n_cta + kPersistWarps - 1) / kPersistWarps;   // CTAs whose flags and records one warp handles
     if (tid == 0) {
-        pimb200::tc::mbar_init(gbar_addr, 1);
+        pimb200::tc::mbar_init(gbar_addr, (uint32_t)((n_cta + cpw - 1) / cpw));   // one arrival per issuing warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     const int kq = warp & (kWideKq - 1), nh = (warp >> 2) & 1;
@@ -813,7 +814,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         // ---- 3. publish
         if (tid < B) {
             const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
-            if (s + 1 < T) a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+            if (s + 1 < T) {
+                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+                // the record is read by the other CTAs' bulk copies (async proxy): the cross-proxy fence sits on the
+                // writer side, where it overlaps the release of the flag, instead of in front of every CTA's gather
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+            }
             if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)tid * a.y_bstride + u0) = v;
         }
         if (s + 1 == T) break;
@@ -823,46 +829,46 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         // release: the flag writers fence after the barrier, which covers the record stores of the whole CTA
         if (tid < kBulkFlagCopies)
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
-        // ---- 4. flags
+        // ---- 4./5. flags and gather, one group of CTAs per warp: the lanes of warp w poll the flags of CTAs
+        //      [w*cpw, (w+1)*cpw); as soon as all of them are up, lane 0 hands the group's records (one contiguous
+        //      block with the layout of hs) to the bulk-copy engine (no cluster multicast).  A group's copy therefore
+        //      starts while slower CTAs are still being waited for, and no CTA-wide barrier sits between flag and copy.
         int timed_out = 0;
-        if (tid < n_cta) {
-            const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + tid) * 32;
-            int polls = 0;
-            while (true) {
-                uint32_t v;
-                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                if (v == tag) break;
-                if (++polls >= a.poll_limit) { timed_out = 1; break; }
-                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+        {
+            const int c0 = warp * cpw;
+            const int c1 = c0 + cpw < n_cta ? c0 + cpw : n_cta;
+            if (c0 < n_cta) {   // warp-uniform
+                const int j = c0 + lane;
+                if (j < c1) {
+                    const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + j) * 32;
+                    int polls = 0;
+                    while (true) {
+                        uint32_t v;
+                        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                        if (v == tag) break;
+                        if (++polls >= a.poll_limit) { timed_out = 1; break; }
+                        if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+                    }
+                    if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                    // acquire: one acquire load of the flag just seen (cheaper than a full fence)
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                }
+                if (tr && tid == 0) tr[4] = clock64();
+                const int lost = __any_sync(0xffffffffu, timed_out);   // also orders the lanes' acquires before the copy
+                if (lane == 0 && !lost) {
+                    const uint32_t off = (uint32_t)c0 * BP * 16u, len = (uint32_t)(c1 - c0) * BP * 16u;
+                    pimb200::tc::mbar_expect_tx(gbar_addr, len);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                 "r"((uint32_t)__cvta_generic_to_shared(hs) + off),
+                                 "l"(reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP) + off), "r"(len),
+                                 "r"(gbar_addr)
+                                 : "memory");
+                }
+                if (tr && tid == 0) tr[5] = clock64();
             }
-            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
-            if (tr && tid == 0) tr[4] = clock64();
-            {   // acquire: one acquire load of the flag just seen (cheaper than a full fence; the data is read by the
-                // bulk-copy engine after the barrier below)
-                uint32_t v;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                if (v != tag) timed_out = 1;   // cannot happen: flags only move forward within a launch
-            }
-            if (tr && tid == 0) tr[5] = clock64();
         }
-        if (__syncthreads_or(timed_out)) return;
         if (tr && tid == 0) tr[6] = clock64();
-        // ---- 5. gather: the records of all CTAs are one contiguous block with the layout of hs, fetched by the bulk-copy
-        //         engine (no cluster multicast).  Nobody else waits here: the next step's tensor-core loop waits piece
-        //         by piece.
-        if (tid == kWideThreads - 32) {   // a thread that did not poll
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP);
-            const uint32_t dst0 = (uint32_t)__cvta_generic_to_shared(hs);
-            const uint32_t total = (uint32_t)n_cta * BP * 16u;
-            asm volatile("fence.proxy.async.global;" ::: "memory");   // records were written through the generic proxy
-            pimb200::tc::mbar_expect_tx(gbar_addr, total);
-            for (uint32_t off = 0; off < total; off += 16384u) {
-                const uint32_t len = total - off < 16384u ? total - off : 16384u;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst0 + off),
-                             "l"(src + off), "r"(len), "r"(gbar_addr)
-                             : "memory");
-            }
-        }
         // next step's input-projection term: issued after the fences (a fence waits for loads in flight, and these may
         // come from HBM); consumed after the next tensor-core phase
 #pragma unroll
