@@ -612,6 +612,7 @@ __device__ __forceinline__ void stage_swizzled(__half* dst, const __half* src, i
     }
 }
 // acc += A[mt*16 .. +16, kt0*16 .. (kt0+nkt)*16) . B, A swizzled in shared memory, B = hb[n][k] with row pitch `bp`
+// (splitting the k-tiles over independent accumulators was measured and does not shorten these short chains)
 __device__ __forceinline__ void mma_rows_smem(float* acc, const __half* A, int K, int mt, int kt0, int nkt,
                                               const __half* hb, int bp, int lane) {
     const int a_row = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
@@ -689,7 +690,8 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
     const int part_floats = 2 * M * RG > 4 * M * 32 ? 2 * M * RG : 4 * M * 32;
     float* part = reinterpret_cast<float*>(carve((size_t)part_floats * 4));
     const int gl = RG, jl = 32;   // row pitches of the two uses
-    float* lg = reinterpret_cast<float*>(carve((size_t)M * 32 * 4));             // [M][32]
+    // staging of this CTA's new values before they go to the other CTAs as 8- / 16-byte stores
+    __half* stage = reinterpret_cast<__half*>(carve((size_t)M * 32 * 4));        // [M][UP] or [M][JP] halves
     float* b2s = reinterpret_cast<float*>(carve((size_t)32 * 4));
     float* bias1s = reinterpret_cast<float*>(carve((size_t)RG * 4));
     int* best_s = reinterpret_cast<int*>(carve((size_t)M * 4));
@@ -702,13 +704,36 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
     for (int i = tid; i < 32; i += nthr) b2s[i] = i < V ? a.b2[i] : -INFINITY;
     for (int i = tid; i < RG; i += nthr) bias1s[i] = a.bias1[(size_t)u0 * 4 + i];
 
-    // gate threads: pair p = (unit j, utterance n), replicated REP times; replica r serves CTAs r, r+REP, ...
+    // gate threads: thread p < UP*M owns (unit gj, utterance gn)
     const int NG = UP * M;
-    const int REP = min(C, nthr / NG);
-    const int gp = tid % NG, grep = tid / NG;
-    const bool gate_thread = grep < REP;
-    const int gj = gp / M, gn = gp - gj * M;
+    const bool gate_thread = tid < NG;
+    const int gj = gate_thread ? tid / M : 0, gn = gate_thread ? tid - gj * M : 0;
     float c_l0 = 0.f, c_l1 = 0.f;
+    // warp roles of the gate-phase products: role 0 / 1 = the two K halves, role 2 = the product with the state of the
+    // previous evaluation (independent of the exchange in flight)
+    const int mt_w = warp % MTG, role = warp / MTG;
+    const int k_half = KTP / 2;
+    // joint-phase roles: m-tile and K quarter
+    const int mtj_w = warp % MTJ, kqj = warp / MTJ;
+    const int perj = (KTP + 3) / 4;
+    // items of the two all-to-all copies, fixed per thread: (destination CTA d, utterance n, chunk c)
+    const int CH = UP / 4, CJ = JP / 8;                     // 8-byte chunks of a state row, 16-byte chunks of a joint row
+    const int n_hitems = C * M * CH, n_jitems = C * M * CJ;
+    int h_item[2], j_item;                                  // packed d << 16 | n << 8 | c, or -1
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int i = tid + q * nthr;
+        h_item[q] = -1;
+        if (i < n_hitems) {
+            const int d = i / (M * CH), r = i - d * (M * CH), n = r / CH, c = r - n * CH;
+            h_item[q] = (d << 16) | (n << 8) | c;
+        }
+    }
+    j_item = -1;
+    if (tid < n_jitems) {
+        const int d = tid / (M * CJ), r = tid - d * (M * CJ), n = r / CJ, c = r - n * CJ;
+        j_item = (d << 16) | (n << 8) | c;
+    }
 
     const int n_groups = (a.n_utts + M - 1) / M;
     for (int grp = cluster_id; grp < n_groups; grp += n_clusters) {
@@ -722,93 +747,121 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         }
         for (int i = tid; i < M * zp; i += nthr) zs[i] = __float2half_rn(0.f);
         for (int i = tid; i < M * JH; i += nthr) Pj[i] = __float2half_rn(0.f);
+        if (tid < M) best_s[tid] = a.blank;   // the start-of-sequence evaluation embeds the blank symbol
         c_l0 = 0.f;
         c_l1 = 0.f;
         cluster.sync();
         // all utterances of a group evaluate the prediction network the same number of times only if they emit in
         // the same frames; each keeps its own parity, packed one bit per utterance
         unsigned par = 0;          // bit n = parity of utterance n's next evaluation
-        int n_emit[M], tok[M];
+        int n_emit[M];
 #pragma unroll
-        for (int m = 0; m < M; ++m) { n_emit[m] = 0; tok[m] = a.blank; }
+        for (int m = 0; m < M; ++m) n_emit[m] = 0;
 
         // Because an m16n8k16 pass always covers all 8 columns, the B operand of an evaluation must hold, for every
         // column, the state that utterance will read: buffers are indexed [parity][n], and a column that sits the
         // evaluation out simply produces a value nobody stores.
         long long* trp = nullptr;
+        // new state values of this CTA (stage[n][0..UP)) -> plane (par>>n)&1 of `buf` in every CTA, 8 bytes a store
+        auto scatter_state = [&](__half* buf, unsigned mask) {
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int it = h_item[q];
+                if (it >= 0) {
+                    const int d = it >> 16, n = (it >> 8) & 0xff, c = it & 0xff;
+                    if (mask & (1u << n)) {
+                        const uint2 v = *reinterpret_cast<const uint2*>(stage + n * UP + c * 4);
+                        __half* dstl = buf + ((size_t)((par >> n) & 1u) * M + n) * hp + u0 + c * 4;
+                        *reinterpret_cast<uint2*>(cluster.map_shared_rank(dstl, d)) = v;
+                    }
+                }
+            }
+        };
         auto pred_eval = [&](unsigned mask) {
-            // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]); two K halves per m-tile
-            if (warp < 2 * MTG) {
-                const int mt = warp % MTG, kh = warp / MTG;
-                const int k_lo = kh ? KTP / 2 : 0, k_n = kh ? KTP - KTP / 2 : KTP / 2;
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                // column n reads parity ((par>>n)&1)^1: gather per-lane base (lane's column = lane>>2)
+            const bool mine = gate_thread && (mask & (1u << gn));
+            // input term of layer 0 for the symbol just emitted: fetched now, used after the first product
+            float4 p0v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine) p0v = __ldg(reinterpret_cast<const float4*>(a.P0 + (size_t)best_s[gn] * 4 * PH + (size_t)(u0 + gj) * 4));
+            // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]) in two K halves; meanwhile role 2 computes Whh1 . h1prev
+            float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+            {
                 const int n = lane >> 2;
-                const __half* hb = h0buf + ((size_t)((((par >> n) & 1u) ^ 1u) * M)) * hp;  // row n added inside
-                // mma_rows_smem indexes hb + (lane>>2)*bp: pass the parity-selected plane
-                mma_rows_smem(acc, Whh0, PH, mt, k_lo, k_n, hb, hp, lane);
-                store_acc(part + (size_t)kh * M * gl, gl, mt, acc, lane);
+                const unsigned pn = (par >> n) & 1u;   // column n reads the plane written by its previous evaluation
+                if (role < 2) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_rows_smem(acc, Whh0, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half,
+                                  h0buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
+                    store_acc(part + (size_t)role * M * gl, gl, mt_w, acc, lane);
+                } else if (role == 2) {
+                    mma_rows_smem(acc2, Whh1, PH, mt_w, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
+                }
             }
             __syncthreads();
             if (trp && tid == 0) trp[4] = clock64();
-            if (gate_thread && (mask & (1u << gn))) {
-                const float* p0 = a.P0 + (size_t)tok[gn] * 4 * PH + (size_t)(u0 + gj) * 4;
-                float z[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    z[g] = part[(size_t)gn * gl + gj * 4 + g] + part[(size_t)(M + gn) * gl + gj * 4 + g] + __ldg(p0 + g);
-                c_l0 = sigmoidf_(z[1]) * c_l0 + sigmoidf_(z[0]) * tanhf_(z[2]);
-                const __half hh = __float2half_rn(sigmoidf_(z[3]) * tanhf_(c_l0));
-                __half* dstl = h0buf + ((size_t)((par >> gn) & 1u) * M + gn) * hp + u0 + gj;
-                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
-            }
-            cluster.sync();
-            if (trp && tid == 0) trp[5] = clock64();
-            // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias; the two products go to two warp groups
-            if (warp < 2 * MTG) {
-                const int mt = warp % MTG, which = warp / MTG;
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                const int n = lane >> 2;
-                const unsigned pn = (par >> n) & 1u;
-                if (which == 0) mma_rows_smem(acc, Wih1, PH, mt, 0, KTP, h0buf + (size_t)(pn * M) * hp, hp, lane);
-                else mma_rows_smem(acc, Whh1, PH, mt, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
-                store_acc(part + (size_t)which * M * gl, gl, mt, acc, lane);
+            if (mine) {
+                const float4 za = *reinterpret_cast<const float4*>(part + (size_t)gn * gl + gj * 4);
+                const float4 zb = *reinterpret_cast<const float4*>(part + (size_t)(M + gn) * gl + gj * 4);
+                const float zi = za.x + zb.x + p0v.x, zf = za.y + zb.y + p0v.y, zg = za.z + zb.z + p0v.z,
+                            zo = za.w + zb.w + p0v.w;
+                c_l0 = sigmoidf_(zf) * c_l0 + sigmoidf_(zi) * tanhf_(zg);
+                stage[gn * UP + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
             }
             __syncthreads();
-            if (gate_thread && (mask & (1u << gn))) {
-                float z[4];
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    z[g] = part[(size_t)gn * gl + gj * 4 + g] + part[(size_t)(M + gn) * gl + gj * 4 + g] + bias1s[gj * 4 + g];
-                c_l1 = sigmoidf_(z[1]) * c_l1 + sigmoidf_(z[0]) * tanhf_(z[2]);
-                const __half hh = __float2half_rn(sigmoidf_(z[3]) * tanhf_(c_l1));
-                __half* dstl = h1buf + ((size_t)((par >> gn) & 1u) * M + gn) * hp + u0 + gj;
-                for (int d = grep; d < C; d += REP) *cluster.map_shared_rank(dstl, d) = hh;
+            scatter_state(h0buf, mask);
+            cluster.sync();
+            if (trp && tid == 0) trp[5] = clock64();
+            // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias: role 0 takes the first K half, role 2 adds the
+            //      second half to the product it already holds
+            {
+                const int n = lane >> 2;
+                const unsigned pn = (par >> n) & 1u;
+                const __half* hb = h0buf + (size_t)(pn * M) * hp;
+                if (role == 0) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_rows_smem(acc, Wih1, PH, mt_w, 0, k_half, hb, hp, lane);
+                    store_acc(part, gl, mt_w, acc, lane);
+                } else if (role == 2) {
+                    mma_rows_smem(acc2, Wih1, PH, mt_w, k_half, KTP - k_half, hb, hp, lane);
+                    store_acc(part + (size_t)M * gl, gl, mt_w, acc2, lane);
+                }
             }
+            __syncthreads();
+            if (mine) {
+                const float4 za = *reinterpret_cast<const float4*>(part + (size_t)gn * gl + gj * 4);
+                const float4 zb = *reinterpret_cast<const float4*>(part + (size_t)(M + gn) * gl + gj * 4);
+                const float4 bb = *reinterpret_cast<const float4*>(bias1s + gj * 4);
+                const float zi = za.x + zb.x + bb.x, zf = za.y + zb.y + bb.y, zg = za.z + zb.z + bb.z,
+                            zo = za.w + zb.w + bb.w;
+                c_l1 = sigmoidf_(zf) * c_l1 + sigmoidf_(zi) * tanhf_(zg);
+                stage[gn * UP + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
+            }
+            __syncthreads();
+            scatter_state(h1buf, mask);
             cluster.sync();
             if (trp && tid == 0) trp[6] = clock64();
             // ---- prediction half of the joint: Pj[n][j0 + q] = W1p[q,:] . h1new[n]; four K quarters per m-tile
             if (warp < 4 * MTJ) {
-                const int mt = warp % MTJ, kq = warp / MTJ;
-                const int per = (KTP + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTP - k_lo));
+                const int k_lo = kqj * perj, k_n = max(0, min(perj, KTP - k_lo));
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 const int n = lane >> 2;
-                mma_rows_gmem(acc, W1p, PH, mt, k_lo, k_n, h1buf + (size_t)(((par >> n) & 1u) * M) * hp, hp, lane);
-                store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
+                mma_rows_gmem(acc, W1p, PH, mtj_w, k_lo, k_n, h1buf + (size_t)(((par >> n) & 1u) * M) * hp, hp, lane);
+                store_acc(part + (size_t)kqj * M * jl, jl, mtj_w, acc, lane);
             }
             __syncthreads();
-            {
-                // value v = (n, q): JP*M values, each delivered to every CTA; threads split the destinations
-                const int NV = JP * M, reps = max(1, min(C, nthr / NV));
-                const int v = tid % NV, r = tid / NV;
-                if (r < reps) {
-                    const int n = v / JP, q = v - n * JP;
-                    if (mask & (1u << n)) {
-                        const float sum = (part[(size_t)n * jl + q] + part[(size_t)(M + n) * jl + q]) +
-                                          (part[(size_t)(2 * M + n) * jl + q] + part[(size_t)(3 * M + n) * jl + q]);
-                        const __half hv = __float2half_rn(sum);
-                        for (int d = r; d < C; d += reps) cluster.map_shared_rank(Pj + (size_t)n * JH, d)[j0 + q] = hv;
-                    }
+            if (tid < M * 32) {   // (utterance n, joint row q of this CTA's slice)
+                const int n = tid >> 5, q = tid & 31;
+                if (q < JP) {
+                    const float sum = (part[(size_t)n * jl + q] + part[(size_t)(M + n) * jl + q]) +
+                                      (part[(size_t)(2 * M + n) * jl + q] + part[(size_t)(3 * M + n) * jl + q]);
+                    stage[n * JP + q] = __float2half_rn(sum);
+                }
+            }
+            __syncthreads();
+            if (j_item >= 0) {
+                const int d = j_item >> 16, n = (j_item >> 8) & 0xff, c = j_item & 0xff;
+                if (mask & (1u << n)) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + n * JP + c * 8);
+                    *reinterpret_cast<uint4*>(cluster.map_shared_rank(Pj + (size_t)n * JH + j0 + c * 8, d)) = v;
                 }
             }
             cluster.sync();
@@ -819,33 +872,25 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         pred_eval(valid);  // start of sequence
         // E of the next frame is fetched one frame ahead (its L2 latency would otherwise open every frame)
         constexpr int EPF = 8;
-        const bool prefetch = M * JH <= EPF * nthr;
-        float e_next[EPF];
         // element q of a thread is (sequence n, column k) of the [M x JH] joint input; when JH equals the block size
-        // (the benchmark's 512) that is simply (q, tid) and no division is needed in the frame loop
+        // (the benchmark's 512) that is simply (q, tid) and the frame loop needs no division
         const bool square = (JH == nthr);
+        float e_next[EPF];
         auto load_E = [&](int t) {
 #pragma unroll
-            for (int q = 0; q < EPF; ++q) {
-                const int i = tid + q * nthr;
-                const int n = square ? q : i / JH, k = square ? tid : i - (i / JH) * JH;
-                e_next[q] = (i < M * JH && (valid & (1u << n)) && t < a.Tp)
-                                ? __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k) : 0.f;
-            }
+            for (int q = 0; q < EPF; ++q)
+                e_next[q] = ((valid & (1u << q)) && t < a.Tp) ? __ldcg(a.E + ((size_t)(utt0 + q) * a.Tp + t) * JH + tid) : 0.f;
         };
-        if (prefetch) load_E(0);
+        if (square) load_E(0);
         for (int t = 0; t < a.Tp; ++t) {
             trp = (a.trace && grp == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
             if (trp && tid == 0) trp[0] = clock64();
             // ---- joint input z[n] = relu(E[n][t] + Pj[n]) in fp16
-            if (prefetch) {
+            if (square) {
 #pragma unroll
-                for (int q = 0; q < EPF; ++q) {
-                    const int i = tid + q * nthr;
-                    const int n = square ? q : i / JH, k = square ? tid : i - (i / JH) * JH;
-                    if (i < M * JH && (valid & (1u << n)))
-                        zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e_next[q] + __half2float(Pj[i]), 0.f));
-                }
+                for (int q = 0; q < EPF; ++q)
+                    if (valid & (1u << q))
+                        zs[(size_t)q * zp + tid] = __float2half_rn(fmaxf(e_next[q] + __half2float(Pj[q * nthr + tid]), 0.f));
                 load_E(t + 1);
             } else {
                 for (int i = tid; i < M * JH; i += nthr) {
@@ -872,7 +917,6 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 const int n = tid >> 5, r = tid & 31;   // warp n handles utterance n, lane = vocabulary row
                 float v = (part[(size_t)n * jl + r] + part[(size_t)(M + n) * jl + r]) +
                           (part[(size_t)(2 * M + n) * jl + r] + part[(size_t)(3 * M + n) * jl + r]) + b2s[r];
-                lg[tid] = v;
                 float bv = v;
                 int best = r;
 #pragma unroll
@@ -894,7 +938,6 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 if ((valid & (1u << m)) && best != a.blank) {
                     if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
                     ++n_emit[m];
-                    tok[m] = best;
                     emit |= 1u << m;
                 }
             }
@@ -933,7 +976,8 @@ static bool greedy_mma_fits(const pimb200_rnnt_config& c, int C, int max_smem) {
     if (PH % C || JH % C || PH % 64 || JH % 64 || c.vocab > 32) return false;
     const int UP = PH / C, JP = JH / C;
     if ((4 * UP) % 16 || JP % 16) return false;
-    if (2 * (4 * UP / 16) > kGreedyWarps || 4 * (JP / 16) > kGreedyWarps) return false;
+    if (3 * (4 * UP / 16) > kGreedyWarps || 4 * (JP / 16) > kGreedyWarps) return false;
+    if (UP % 4 || JP % 8 || JP > 32 || UP > 32) return false;   // 8- / 16-byte chunks of the all-to-all copies; staging rows
     if (UP * kMmaUtts > kGreedyThreads || JP * kMmaUtts > kGreedyThreads) return false;
     return greedy_mma_smem(c, C) <= (size_t)max_smem;
 }
