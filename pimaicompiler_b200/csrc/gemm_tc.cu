@@ -171,23 +171,39 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (!ok || *abort_flag != 0) break;
             const float bv = (a.bias && m < a.N) ? __half2float(a.bias[m]) : 0.f;
+            const float lo = a.act == PIMB200_ACT_RELU ? 0.f : -INFINITY;   // v = max(v, lo): ReLU without a branch
+            const int j_end = a.J < j0 + a.bn ? a.J : j0 + a.bn;            // first activation row past this tile
+            // One warp per scheduler runs this loop with nothing to hide instruction latency behind, so the common case
+            // (all 32 columns of a chunk inside the matrix) carries no per-element checks or index arithmetic: a
+            // running pointer, one add, one max, one store.
+            float* yf = static_cast<float*>(a.Y) + (size_t)j0 * a.ldy + m;
+            __half* yh = static_cast<__half*>(a.Y) + (size_t)j0 * a.ldy + m;
             for (int c0 = 0; c0 < a.bn; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.bn + c0), r);
                 if (m < a.N) {
+                    if (j0 + c0 + 32 <= j_end) {
+                        if (a.y_is_f32) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int j = j0 + c0 + c;
-                        if (c0 + c < a.bn && j < a.J) {
-                            float v = __uint_as_float(r[c]) + bv;
-                            if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
-                            if (a.y_is_f32)
-                                static_cast<float*>(a.Y)[(size_t)j * a.ldy + m] = v;
-                            else
-                                static_cast<__half*>(a.Y)[(size_t)j * a.ldy + m] = __float2half_rn(v);
+                            for (int c = 0; c < 32; ++c) yf[(size_t)c * a.ldy] = fmaxf(__uint_as_float(r[c]) + bv, lo);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                yh[(size_t)c * a.ldy] = __float2half_rn(fmaxf(__uint_as_float(r[c]) + bv, lo));
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            if (j0 + c0 + c < j_end) {
+                                const float v = fmaxf(__uint_as_float(r[c]) + bv, lo);
+                                if (a.y_is_f32) yf[(size_t)c * a.ldy] = v;
+                                else yh[(size_t)c * a.ldy] = __float2half_rn(v);
+                            }
                         }
                     }
                 }
+                yf += (size_t)32 * a.ldy;
+                yh += (size_t)32 * a.ldy;
             }
             // this warp is done reading the stage: hand it back to the MMA issuer
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
