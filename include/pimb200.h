@@ -174,6 +174,11 @@ int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrenc
  * rows per CTA), so the default is 0.  No counterpart in the reference. */
 int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on);
 
+/* A/B switch between the two batched persistent recurrences (2..64 lock-step sequences): 1 (default) = the kernel
+ * that keeps its W_hh slice in registers (H <= 1024), 0 = the K-split kernel with W_hh in shared memory (up to 32
+ * sequences; also what H > 1024 falls back to).  Same results.  No counterpart in the reference. */
+int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on);
+
 /* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are
  * inside MIOpen. */

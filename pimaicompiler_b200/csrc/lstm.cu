@@ -655,12 +655,12 @@ constexpr int kWideThreads = kPersistThreads;
 constexpr int kWideKq = 4;         // K-split of the tensor-core phase across warps
 constexpr int kWideMaxKtw = 16;    // k-tiles per warp held in registers (H <= 1024)
 
-template <int NT>  // 4 or 8 tiles of 8 sequences
+template <int NT>  // 2, 4 or 8 tiles of 8 sequences
 __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(BulkArgs a) {
     constexpr int BP = NT * 8;
     constexpr int NH = NT / 2;                       // n-tiles per warp
     constexpr int ZP = BP + 1;                       // padded sequence pitch of the partial sums: [kq][unit][ZP][gate]
-    constexpr int PPT = (8 * BP) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
+    constexpr int PPT = (8 * BP + kPersistThreads - 1) / kPersistThreads;  // (unit, sequence) pairs per gate thread: 1 or 2
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, T = a.T, B = a.B;
     // hidden states in the layout of the exchange records: hs[j][n][8] = units 8j..8j+7 of sequence n.  The gather is
@@ -718,7 +718,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
         const int p_ = tid + q * kPersistThreads;
         gu[q] = p_ / BP;
         gn[q] = p_ - gu[q] * BP;
-        live[q] = gn[q] < B;
+        live[q] = p_ < 8 * BP && gn[q] < B;
+        if (p_ >= 8 * BP) gu[q] = gn[q] = 0;   // threads beyond the pairs (16 sequences) idle through the gate phase
         c[q] = 0.f;
         bias4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
         gx[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1154,7 +1155,7 @@ struct pimb200_lstm {
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
     int use_tc = 0;        // 1 = tcgen05 recurrence for 17..64 sequences (measured slower than mma.sync here: opt-in)
-    int bulk_wide = 1;     // 1 = tile-owning warps for 33..64 sequences, 2 = also for 17..32, 0 = K-split kernel only (up to 32)
+    int bulk_wide = 1;     // 1 = register-resident (wide) kernel for 2..64 sequences, 0 = K-split kernel only (up to 32)
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
@@ -1306,7 +1307,7 @@ extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
 // A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
-    h->bulk_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
+    h->bulk_wide = on > 0 ? 1 : 0;
     return PIMB200_OK;
 }
 extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
@@ -1390,12 +1391,14 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     PersistPlan pp = plan_persistent(h);
     const bool fits = pp.ok && B <= kPersistMaxB && !packed && (int)persist_smem(H, B) <= h->max_smem_optin;
     const int nt = B <= 8 ? 1 : (B <= 16 ? 2 : (B <= 32 ? 4 : 8));
-    // 33..64 sequences: warps own whole output tiles; up to 32 the K-split kernel keeps the tensor pipes busier
+    // 2..64 sequences: the register-resident kernel (2.8 / 3.4 / 4.7 us per step at 16 / 32 / 64 sequences against
+    // 4.3 / 5.8 for the K-split one at 16 / 32)
     // (the wide kernel keeps its W_hh slice in registers: H at most 1024)
     const bool wide_ok = (H % 16 == 0) && H <= 16 * kWideKq * kWideMaxKtw;
-    const bool wide = wide_ok && (nt >= 8 || (nt == 4 && h->bulk_wide == 2));
-    const size_t bsmem = wide ? wide_smem(H, nt) : bulk_smem(H, nt);
-    const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= 2 &&
+    const bool wide = wide_ok && h->bulk_wide >= 1;
+    const int wnt = nt < 2 ? 2 : nt;   // the wide kernel's smallest instance takes 16 sequences
+    const size_t bsmem = wide ? wide_smem(H, wnt) : bulk_smem(H, nt);
+    const bool bulk_fits = (H % 16 == 0) && (H / 8 <= h->sm_count) && (H / 8 <= kPersistThreads) && B >= (wide ? 1 : 2) &&
                            B <= (h->bulk_wide ? kBulkMaxB : 32) && (nt <= 4 || wide) && !packed && (int)bsmem <= h->max_smem_optin;
     // tensor-core (tcgen05) recurrence: 17..64 sequences, H a multiple of 64
     const int tc_bp = B <= 32 ? 32 : 64;   // accumulator columns; two warps read half of them each, 16 at a time
@@ -1446,11 +1449,12 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
         a.trace = h->trace;
         h->bulk_tag += (uint32_t)T + 1u;
-        const void* fn = nt == 1 ? (const void*)lstm_persistent_bulk_kernel<1>
-                       : nt == 2 ? (const void*)lstm_persistent_bulk_kernel<2>
-                       : !wide   ? (const void*)lstm_persistent_bulk_kernel<4>
-                       : nt == 4 ? (const void*)lstm_persistent_wide_kernel<4>
-                                 : (const void*)lstm_persistent_wide_kernel<8>;
+        const void* fn = wide ? (wnt == 2   ? (const void*)lstm_persistent_wide_kernel<2>
+                                 : wnt == 4 ? (const void*)lstm_persistent_wide_kernel<4>
+                                            : (const void*)lstm_persistent_wide_kernel<8>)
+                              : (nt == 1   ? (const void*)lstm_persistent_bulk_kernel<1>
+                                 : nt == 2 ? (const void*)lstm_persistent_bulk_kernel<2>
+                                           : (const void*)lstm_persistent_bulk_kernel<4>);
         const size_t smem = bsmem;
         PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         void* kargs[] = {&a};

@@ -24,11 +24,14 @@ def _ops():
     return ops
 
 
-def _run(ops, ps, x, h0, c0, L, bi, hb, bf, variant):
+def _run(ops, ps, x, h0, c0, L, bi, hb, bf, variant, bulk_wide=1):
     T = x.shape[1] if bf else x.shape[0]
     I, H = x.shape[2], ps[1].shape[1]
     m = ops.Lstm([to_dev(p) for p in ps], L, bi, I, H, hb)
     m.set_variant(variant)
+    if not bulk_wide:
+        from pimaicompiler_b200 import _lib
+        assert _lib.lib().pimb200_lstm_set_bulk_wide(m._h, 0) == 0
     y, hn, cn = m.forward(to_dev(x), None if h0 is None else to_dev(h0), None if c0 is None else to_dev(c0), bf)
     torch.cuda.synchronize()
     assert m.last_status() == 0
@@ -93,12 +96,14 @@ CASES = [
 
 
 @pytest.mark.parametrize("case", CASES)
-@pytest.mark.parametrize("variant", ["streamed", "persistent", "tagged"])
+@pytest.mark.parametrize("variant", ["streamed", "persistent", "ksplit", "tagged"])
 def test_lstm_matches_oracle(case, variant):
     ops = _ops()
     T, B, I, H, L, bi, hb, bf, nz = case
     if variant == "persistent" and (B > 64 or H % 16):
         pytest.skip("persistent variants take up to 64 sequences and H % 16 == 0")
+    if variant == "ksplit" and (B < 2 or B > 32 or H % 16):
+        pytest.skip("the K-split batched kernel takes 2..32 sequences and H % 16 == 0")
     if variant == "tagged" and (B > 8 or H % 16):
         pytest.skip("tagged-word exchange takes up to 8 sequences and H % 16 == 0")
     D = 2 if bi else 1
@@ -109,8 +114,9 @@ def test_lstm_matches_oracle(case, variant):
     c0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5) if nz else None
     ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, bi, hb, None if h0 is None else h0.numpy(),
                   None if c0 is None else c0.numpy(), bf)
-    vid = {"streamed": ops.LSTM_STREAMED, "persistent": ops.LSTM_PERSISTENT, "tagged": ops.LSTM_PERSISTENT_TAGGED}[variant]
-    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, vid)
+    vid = {"streamed": ops.LSTM_STREAMED, "persistent": ops.LSTM_PERSISTENT, "ksplit": ops.LSTM_PERSISTENT,
+           "tagged": ops.LSTM_PERSISTENT_TAGGED}[variant]
+    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, vid, bulk_wide=0 if variant == "ksplit" else 1)
     for name, a, b in zip(("y", "hn", "cn"), got, ref):
         assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"{variant} {name} {case}")
 
