@@ -135,8 +135,10 @@ int pimb200_lstm_create(const void* const* params, int n_params, int num_layers,
 int pimb200_lstm_destroy(pimb200_lstm* h);
 
 /* variant selection for A/B profiling: 0 = automatic, 1 = streamed per-step kernels,
- * 2 = persistent weight-stationary kernels (tagged-word exchange for one sequence, flag + bulk exchange for 2..64;
- * fails with UNSUPPORTED when the shape does not fit), 3 = persistent with the tagged-word exchange for up to 8. */
+ * 2 = persistent weight-stationary kernels (one cooperative launch per layer and direction; W_hh slice in registers,
+ * flag + bulk-copy exchange, 1..64 sequences, H a multiple of 16 up to 1024; larger H falls back to the variants with
+ * W_hh in shared memory; fails with UNSUPPORTED when the shape does not fit), 3 = persistent with the tagged-word
+ * exchange (W_hh in shared memory) for up to 8 sequences. */
 enum { PIMB200_LSTM_AUTO = 0, PIMB200_LSTM_STREAMED = 1, PIMB200_LSTM_PERSISTENT = 2,
        PIMB200_LSTM_PERSISTENT_TAGGED = 3 };
 int pimb200_lstm_set_variant(pimb200_lstm* h, int variant);

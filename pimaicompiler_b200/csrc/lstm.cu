@@ -865,6 +865,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
                                  "l"(reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP) + off), "r"(len),
                                  "r"(gbar_addr)
                                  : "memory");
+                } else if (lane == 0) {
+                    // a flag never came: arrive without a copy, so that the barrier still completes once the copies
+                    // the other warps did issue have landed (the CTA waits for them below before it leaves)
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gbar_addr) : "memory");
                 }
                 if (tr && tid == 0) tr[5] = clock64();
             }
@@ -885,7 +889,11 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
             }
         }
         if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status))) {
-            atomicExch(a.status, PIMB200_ERR_TIMEOUT);   // a bulk copy never completed within the wait limit
+            // gave up (a flag or a copy never came, here or in another CTA): before the CTA hands its shared memory
+            // back, give the bulk copies it has in flight a bounded chance to land
+            for (uint32_t i = 0; i < (1u << 20); ++i)
+                if (pimb200::tc::mbar_try_wait(gbar_addr, (uint32_t)(s & 1))) break;
+            atomicExch(a.status, PIMB200_ERR_TIMEOUT);
             timed_out = 1;
         }
         if (__syncthreads_or(timed_out)) return;

@@ -185,7 +185,7 @@ def test_lstm_outputs_alias_slices_of_caller_buffers():
     assert (cat_buf[..., 1024:] == 5).all() and (state_buf[:2] == 5).all() and (state_buf[4:] == 5).all()
 
 
-@pytest.mark.parametrize("B", [1, 4])
+@pytest.mark.parametrize("B", [1, 4, 40])
 def test_persistent_bounded_wait_reports_timeout_and_context_survives(B):
     # Fault handling without faulting anything: shrink the bounded wait to a single poll, so the hidden-state exchange
     # cannot complete in time; the kernel must give up, record ERR_TIMEOUT and return, and the next call (normal
