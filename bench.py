@@ -247,10 +247,10 @@ def run_gpu(args, rank, world, local):
     rec_s = prof["ms"] * 1e-3
     achieved = prof["bytes"] / rec_s / 1e9 if rec_s > 0 else 0.0
     share = prof["ms"] / sum(step_ms) if sum(step_ms) > 0 else 0.0
-    # per group of encoder-batch utterances: (projection GEMM + recurrence) per LSTM layer; then one joint GEMM and
-    # one greedy kernel
+    # per group of encoder-batch utterances: (projection GEMM + recurrence) per LSTM layer and the joint's encoder-half
+    # GEMM; then one greedy kernel for the whole call
     eb = args.encoder_batch or 64
-    launches_per_step = ((S + eb - 1) // eb) * 2 * (cfg.pre_layers + cfg.post_layers) + 2
+    launches_per_step = ((S + eb - 1) // eb) * (2 * (cfg.pre_layers + cfg.post_layers) + 1) + 1
 
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
