@@ -8,13 +8,17 @@
 //
 // Structure per (layer, direction):
 //   1. whole-sequence input projection  G[T*B, 4H] = X · Wp_ih^T  (one dense GEMM, fp32 result)
-//   2. the recurrence over T, in one of two variants:
+//   2. the recurrence over T:
 //        streamed   — one launch per timestep; W_hh is re-read (from L2/HBM) every step with
 //                     128-bit loads; any B, any H; the form used by seq_len==1 decoder calls
-//        persistent — one cooperative launch for all T steps; every CTA keeps its slice of W_hh in
-//                     shared memory for the whole sequence, hidden states travel between CTAs as
-//                     64-bit {value, step-tag} words polled from L2 (a data-carrying grid
-//                     barrier, one L2 round trip per step); B == 1
+//        persistent — one cooperative launch for all T steps; every CTA keeps its slice of W_hh on
+//                     chip for the whole sequence and the CTAs exchange the new hidden states through
+//                     L2 once per step.  Default: lstm_persistent_wide_kernel (1..64 sequences in
+//                     lock step, H <= 1024, slice in registers as mma fragments, 16-byte records +
+//                     per-CTA step flags + bulk-copy gather).  Kept beside it: the K-split kernel
+//                     with the slice in shared memory (2..32 sequences, any H that fits), the
+//                     tagged-word kernel (up to 8 sequences, data and flag in one 16-byte word) and
+//                     an opt-in tcgen05 variant (measured slower).
 // Weights are stored gate-interleaved (packed row u*4+g = original row g*H+u) so the four gate
 // rows of one hidden unit are contiguous and its four pre-activations are one float4 of G.
 #include <mutex>
@@ -902,7 +906,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 }
 
 // ---------------------------------------------------------------------------------------------
-// tcgen05 variant of the wide batched recurrence (17..64 sequences, H a multiple of 64).
+// tcgen05 variant of the batched recurrence (17..64 sequences, H a multiple of 64), opt-in.
 //
 // The per-step product Z[32 x BP] = W_slice[32 x H] . Hprev[H x BP] runs on the 5th-generation tensor cores: one
 // thread issues H/16 tcgen05.mma (kind::f16, M = 128, N = BP, K = 16) per step, the accumulator lives in tensor
@@ -911,7 +915,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 // straight to its swizzled place).  The instruction's M is 128 but a CTA owns 32 gate rows: the A descriptor of a
 // k-block simply runs on into the following shared memory, rows 32..127 of the accumulator are never read.
 // Exchange, gates and bounded waits are those of the wide kernel; every exit path frees the tensor memory.
-// Measured on B200 at H = 1024, 64 sequences: 14.9 us per step against 8.3 us for the mma.sync kernel.  With only 32
+// Measured on B200 at H = 1024, 64 sequences: 14.9 us per step against 8.3 us for the mma.sync kernel of the time
+// (4.7 us for today's register-resident one).  With only 32
 // useful rows per CTA the instruction is shared-memory-bandwidth bound (each of the 64 MMAs of a step streams the
 // full 128-row A window, 6 KB with B), and the swizzled scatter of the gather costs more than the contiguous copy.
 // The kernel is therefore opt-in (pimb200_lstm_set_use_tc) and kept as the measured alternative.
