@@ -122,6 +122,33 @@ int pimb200_cat(void* dst, const void* const* src, const size_t* inner_bytes, in
 
 /* ---- fused multi-layer LSTM ---------------------------------------------- */
 
+/* ---- row-wise glue of the decode path (fp16 storage, fp32 arithmetic), contiguous rows of `cols` elements ---- */
+
+/* y[r, :] = softmax(x[r, :]) or log_softmax(x[r, :]) over the last dimension.
+ * Replaces executeAtenSoftmax / executeAtenLogSoftmax -> at::softmax / at::log_softmax
+ * (runtime/source/executor/op_executor/aten_ops_executor.cpp:3402-3436, 2092-2133; aten_ops.cpp:492, 323) for
+ * dim = last. */
+int pimb200_softmax_rows(const void* x, void* y, long rows, long cols, int log_softmax, void* stream);
+
+/* idx[r] = index of the largest element of row r (the lowest index among equal maxima), int64.
+ * Replaces executeAtenArgmax -> at::argmax (aten_ops_executor.cpp:520-547, aten_ops.cpp:71) for dim = last. */
+int pimb200_argmax_rows(const void* x, long long* idx, long rows, long cols, void* stream);
+
+/* y[r, :] = (x[r, :] - mean) / sqrt(var + eps) * gamma + beta, biased variance, over the last dimension;
+ * gamma / beta [cols] fp16 or NULL.  Replaces executeAtenLayerNorm -> at::layer_norm
+ * (aten_ops_executor.cpp:1898-1942, aten_ops.cpp:277-290) for a one-dimensional normalized_shape. */
+int pimb200_layer_norm_rows(const void* x, const void* gamma, const void* beta, void* y, long rows, long cols, float eps,
+                            void* stream);
+
+/* y = tanh(x), n elements.  Replaces executeAtenTanh (aten_ops_executor.cpp:3555-3568). */
+int pimb200_tanh_f16(const void* x, void* y, size_t n, void* stream);
+
+/* y[i] = mask[i % mask_n] ? value : x[i]; mask holds one byte per element (bool), mask_n divides n (n = same shape,
+ * cols = one mask row broadcast over the rows).  Replaces executeAtenMaskedFill with a scalar value
+ * (aten_ops_executor.cpp:2432-2467, aten_ops.cpp:350-353). */
+int pimb200_masked_fill_f16(const void* x, const unsigned char* mask, float value, void* y, size_t n, size_t mask_n,
+                            void* stream);
+
 typedef struct pimb200_lstm pimb200_lstm;
 
 /* One-time weight layout step.  params = the flat list at::lstm takes:

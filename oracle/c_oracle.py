@@ -55,6 +55,46 @@ def add(A, B):
     return out
 
 
+def softmax(x, log=False):
+    x = _c(x)
+    cols = x.shape[-1]
+    y = np.empty_like(x)
+    lib().oracle_softmax(_f(x), _f(y), C.c_long(x.size // cols), C.c_long(cols), int(log))
+    return y
+
+
+def argmax(x):
+    x = _c(x)
+    cols = x.shape[-1]
+    idx = np.empty(x.shape[:-1], np.int64)
+    lib().oracle_argmax(_f(x), idx.ctypes.data_as(C.POINTER(C.c_longlong)), C.c_long(x.size // cols), C.c_long(cols))
+    return idx
+
+
+def layer_norm(x, gamma=None, beta=None, eps=1e-5):
+    x, gamma, beta = _c(x), _c(gamma), _c(beta)
+    cols = x.shape[-1]
+    y = np.empty_like(x)
+    lib().oracle_layer_norm(_f(x), _f(gamma), _f(beta), _f(y), C.c_long(x.size // cols), C.c_long(cols), C.c_float(eps))
+    return y
+
+
+def tanh(x):
+    x = _c(x)
+    y = np.empty_like(x)
+    lib().oracle_tanh(_f(x), _f(y), C.c_size_t(x.size))
+    return y
+
+
+def masked_fill(x, mask, value):
+    x = _c(x)
+    mask = np.ascontiguousarray(mask, dtype=np.uint8)
+    y = np.empty_like(x)
+    lib().oracle_masked_fill(_f(x), mask.ctypes.data_as(C.POINTER(C.c_ubyte)), C.c_float(value), _f(y),
+                             C.c_size_t(x.size), C.c_size_t(mask.size))
+    return y
+
+
 def cat(arrays, dim):
     arrays = [np.ascontiguousarray(a) for a in arrays if a.size > 0]
     ref = arrays[0]

@@ -1,0 +1,206 @@
+// Row-wise glue operators of the decode path, fp16 storage / fp32 arithmetic: softmax and log_softmax over the last
+// dimension, arg max over the last dimension, layer normalisation over the last dimension, tanh and masked_fill.
+//
+// They stand where the reference's executors forward to libtorch one tensor op at a time
+// (runtime/source/executor/op_executor/aten_ops_executor.cpp: executeAtenSoftmax 3402-3436, executeAtenLogSoftmax
+// 2092-2133, executeAtenArgmax 520-547, executeAtenLayerNorm 1898-1942, executeAtenTanh 3555-3568,
+// executeAtenMaskedFill 2432-2467).  All are small and latency-bound at decode sizes (a 29..32320-wide logit row, a
+// handful of attention scores, a 512-wide model vector): one CTA per row, the row is read with 128-bit loads when its
+// address and length allow, reductions run in fp32 through warp shuffles and one shared-memory hop.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+using namespace pimb200;
+
+namespace {
+
+constexpr int kRowThreads = 128;
+constexpr int kRowWarps = kRowThreads / 32;
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();   // red may still be read from the previous reduction
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int w = 1; w < kRowWarps; ++w) r = fmaxf(r, red[w]);
+    return r;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int w = 1; w < kRowWarps; ++w) r += red[w];   // fixed order: the result does not depend on timing
+    return r;
+}
+
+// element access: VEC = 8 halves per 16-byte load when the row allows it, else scalar
+template <bool VEC, typename F>
+__device__ __forceinline__ void for_each(const __half* row, long cols, F f) {
+    if (VEC) {
+        const uint4* r4 = reinterpret_cast<const uint4*>(row);
+        for (long c = threadIdx.x; c < (cols >> 3); c += kRowThreads) {
+            float xf[8];
+            widen8(r4[c], xf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f(c * 8 + j, xf[j]);
+        }
+    } else {
+        for (long c = threadIdx.x; c < cols; c += kRowThreads) f(c, __half2float(row[c]));
+    }
+}
+
+template <bool VEC, bool LOG>
+__global__ void __launch_bounds__(kRowThreads) softmax_rows_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+                                                                   long cols) {
+    __shared__ float red[kRowWarps];
+    const __half* row = x + (size_t)blockIdx.x * cols;
+    __half* out = y + (size_t)blockIdx.x * cols;
+    float m = -CUDART_INF_F;
+    for_each<VEC>(row, cols, [&](long, float v) { m = fmaxf(m, v); });
+    m = block_max(m, red);
+    float s = 0.f;
+    for_each<VEC>(row, cols, [&](long, float v) { s += expf(v - m); });
+    s = block_sum(s, red);
+    const float inv = 1.0f / s, ls = logf(s);
+    for_each<VEC>(row, cols, [&](long c, float v) {
+        out[c] = __float2half_rn(LOG ? (v - m) - ls : expf(v - m) * inv);
+    });
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kRowThreads) argmax_rows_kernel(const __half* __restrict__ x, long long* __restrict__ idx,
+                                                                  long cols) {
+    __shared__ float red_v[kRowWarps];
+    __shared__ long long red_i[kRowWarps];
+    const __half* row = x + (size_t)blockIdx.x * cols;
+    float bv = -CUDART_INF_F;
+    long long bi = cols;   // lowest index among equal maxima wins, as in at::argmax on a contiguous row
+    for_each<VEC>(row, cols, [&](long c, float v) {
+        if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kRowWarps; ++w)
+            if (red_v[w] > bv || (red_v[w] == bv && red_i[w] < bi)) { bv = red_v[w]; bi = red_i[w]; }
+        idx[blockIdx.x] = bi < cols ? bi : 0;   // a row of NaNs / -inf only: index 0
+    }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kRowThreads) layer_norm_rows_kernel(const __half* __restrict__ x,
+                                                                      const __half* __restrict__ gamma,
+                                                                      const __half* __restrict__ beta,
+                                                                      __half* __restrict__ y, long cols, float eps) {
+    __shared__ float red[kRowWarps];
+    const __half* row = x + (size_t)blockIdx.x * cols;
+    __half* out = y + (size_t)blockIdx.x * cols;
+    float s = 0.f;
+    for_each<VEC>(row, cols, [&](long, float v) { s += v; });
+    const float mean = block_sum(s, red) / (float)cols;
+    float q = 0.f;
+    for_each<VEC>(row, cols, [&](long, float v) { const float d = v - mean; q += d * d; });
+    const float rstd = rsqrtf(block_sum(q, red) / (float)cols + eps);   // biased variance, as at::layer_norm
+    for_each<VEC>(row, cols, [&](long c, float v) {
+        float r = (v - mean) * rstd;
+        if (gamma) r *= __half2float(gamma[c]);
+        if (beta) r += __half2float(beta[c]);
+        out[c] = __float2half_rn(r);
+    });
+}
+
+__global__ void tanh_f16_kernel(const __half* __restrict__ x, __half* __restrict__ y, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = __float2half_rn(tanhf(__half2float(x[i])));
+}
+
+__global__ void masked_fill_f16_kernel(const __half* __restrict__ x, const unsigned char* __restrict__ mask, __half value,
+                                       __half* __restrict__ y, size_t n, size_t mask_n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = mask[i % mask_n] ? value : x[i];
+}
+
+inline unsigned flat_grid(size_t n) {
+    const size_t g = (n + 255) / 256;
+    return (unsigned)(g > (size_t)kNumSmB200 * 8 ? (size_t)kNumSmB200 * 8 : (g ? g : 1));
+}
+inline bool rows_ok(long rows, long cols) { return rows > 0 && cols > 0 && rows <= 0x7fffffffL; }
+
+}  // namespace
+
+extern "C" int pimb200_softmax_rows(const void* x, void* y, long rows, long cols, int log_softmax, void* stream) {
+    if (rows == 0 || cols == 0) return PIMB200_OK;   // empty tensors carry no storage
+    if (!x || !y || !rows_ok(rows, cols)) return PIMB200_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xp = static_cast<const __half*>(x);
+    __half* yp = static_cast<__half*>(y);
+    const bool vec = cols % 8 == 0 && aligned16(x);
+    if (vec) {
+        if (log_softmax) softmax_rows_kernel<true, true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+        else softmax_rows_kernel<true, false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+    } else {
+        if (log_softmax) softmax_rows_kernel<false, true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+        else softmax_rows_kernel<false, false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+    }
+    return launch_status();
+}
+
+extern "C" int pimb200_argmax_rows(const void* x, long long* idx, long rows, long cols, void* stream) {
+    if (rows == 0) return PIMB200_OK;
+    if (!x || !idx || !rows_ok(rows, cols)) return PIMB200_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xp = static_cast<const __half*>(x);
+    if (cols % 8 == 0 && aligned16(x)) argmax_rows_kernel<true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, idx, cols);
+    else argmax_rows_kernel<false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, idx, cols);
+    return launch_status();
+}
+
+extern "C" int pimb200_layer_norm_rows(const void* x, const void* gamma, const void* beta, void* y, long rows, long cols,
+                                       float eps, void* stream) {
+    if (rows == 0 || cols == 0) return PIMB200_OK;
+    if (!x || !y || !rows_ok(rows, cols)) return PIMB200_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const __half* xp = static_cast<const __half*>(x);
+    const __half* g = static_cast<const __half*>(gamma);
+    const __half* b = static_cast<const __half*>(beta);
+    __half* yp = static_cast<__half*>(y);
+    if (cols % 8 == 0 && aligned16(x))
+        layer_norm_rows_kernel<true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, g, b, yp, cols, eps);
+    else
+        layer_norm_rows_kernel<false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, g, b, yp, cols, eps);
+    return launch_status();
+}
+
+extern "C" int pimb200_tanh_f16(const void* x, void* y, size_t n, void* stream) {
+    if (n == 0) return PIMB200_OK;
+    if (!x || !y) return PIMB200_ERR_BAD_ARG;
+    tanh_f16_kernel<<<flat_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(x),
+                                                                                 static_cast<__half*>(y), n);
+    return launch_status();
+}
+
+extern "C" int pimb200_masked_fill_f16(const void* x, const unsigned char* mask, float value, void* y, size_t n,
+                                       size_t mask_n, void* stream) {
+    if (n == 0) return PIMB200_OK;
+    if (!x || !y || !mask) return PIMB200_ERR_BAD_ARG;
+    if (mask_n == 0 || n % mask_n != 0) return PIMB200_ERR_BAD_ARG;
+    masked_fill_f16_kernel<<<flat_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), mask, __float2half_rn(value), static_cast<__half*>(y), n, mask_n);
+    return launch_status();
+}

@@ -63,6 +63,32 @@ struct GraphBuilder {
         return add(l, {a, b});
     }
     int64_t addBmm(int64_t a, int64_t b) { return add(std::make_shared<ir::AtenBmmLayer>("aten::bmm"), {a, b}); }
+    int64_t addSoftmax(int64_t x, int64_t dim, bool log) {
+        auto l = std::make_shared<ir::AtenSoftmaxLayer>(log ? "aten::log_softmax" : "aten::softmax", log);
+        l->dim = dim;
+        return add(l, {x});
+    }
+    int64_t addArgmax(int64_t x, int64_t dim, bool keepdim) {
+        auto l = std::make_shared<ir::AtenArgmaxLayer>("aten::argmax");
+        l->dim = dim;
+        l->keepdim = keepdim ? 1 : 0;
+        return add(l, {x});
+    }
+    int64_t addLayerNorm(int64_t x, std::vector<int64_t> shape, c10::optional<at::Tensor> w, c10::optional<at::Tensor> b,
+                         double eps) {
+        auto l = std::make_shared<ir::AtenLayerNormLayer>("aten::layer_norm");
+        l->normalized_shape = std::move(shape);
+        if (w.has_value()) l->weight = *w;
+        if (b.has_value()) l->bias = *b;
+        l->eps = eps;
+        return add(l, {x});
+    }
+    int64_t addTanh(int64_t x) { return add(std::make_shared<ir::AtenTanhLayer>("aten::tanh"), {x}); }
+    int64_t addMaskedFill(int64_t x, int64_t mask, double value) {
+        auto l = std::make_shared<ir::AtenMaskedFillLayer>("aten::masked_fill");
+        l->value = value;
+        return add(l, {x, mask});
+    }
     int64_t addCat(int64_t list_id, int64_t dim, int64_t mem_layer_id) {
         auto l = std::make_shared<ir::AtenCatLayer>("aten::cat");
         l->setDim(dim);
@@ -151,6 +177,12 @@ PYBIND11_MODULE(_pimb200_host, m) {
         .def("add_linear", &GraphBuilder::addLinear, py::arg("x"), py::arg("weight"), py::arg("bias") = py::none())
         .def("add_add", &GraphBuilder::addAdd, py::arg("a"), py::arg("b"), py::arg("alpha") = 1.0)
         .def("add_bmm", &GraphBuilder::addBmm)
+        .def("add_softmax", &GraphBuilder::addSoftmax, py::arg("x"), py::arg("dim") = -1, py::arg("log") = false)
+        .def("add_argmax", &GraphBuilder::addArgmax, py::arg("x"), py::arg("dim") = -1, py::arg("keepdim") = false)
+        .def("add_layer_norm", &GraphBuilder::addLayerNorm, py::arg("x"), py::arg("normalized_shape"),
+             py::arg("weight") = py::none(), py::arg("bias") = py::none(), py::arg("eps") = 1e-5)
+        .def("add_tanh", &GraphBuilder::addTanh)
+        .def("add_masked_fill", &GraphBuilder::addMaskedFill)
         .def("add_cat", &GraphBuilder::addCat, py::arg("list_id"), py::arg("dim"), py::arg("mem_layer_id") = -1)
         .def("add_copy", &GraphBuilder::addCopy)
         .def("add_lstm", &GraphBuilder::addLstm, py::arg("inputs"), py::arg("params"), py::arg("has_biases") = true,

@@ -23,6 +23,7 @@ enum class DataType { UNDEFINED, TENSOR, LIST, TUPLE, INT64, FLOAT64, BOOL, NONE
 
 enum class LayerType {
     ATENADD, ATENADDMM, ATENBMM, ATENCAT, ATENCOPY, ATENLINEAR, ATENLSTM1, ATENLSTM2, ATENMATMUL, MULTISTREAM,
+    ATENSOFTMAX, ATENLOGSOFTMAX, ATENARGMAX, ATENLAYERNORM, ATENTANH, ATENMASKEDFILL,
     PRIMINPUT, PRIMOUTPUT, PRIMCONSTANT, PRIMLISTCONSTRUCT
 };
 
@@ -38,6 +39,12 @@ inline const char* convertLayerTypeToString(LayerType t) {
         case LayerType::ATENLSTM2: return "aten::lstm2";
         case LayerType::ATENMATMUL: return "aten::matmul";
         case LayerType::MULTISTREAM: return "MultiStream";
+        case LayerType::ATENSOFTMAX: return "aten::softmax";
+        case LayerType::ATENLOGSOFTMAX: return "aten::log_softmax";
+        case LayerType::ATENARGMAX: return "aten::argmax";
+        case LayerType::ATENLAYERNORM: return "aten::layer_norm";
+        case LayerType::ATENTANH: return "aten::tanh";
+        case LayerType::ATENMASKEDFILL: return "aten::masked_fill";
         case LayerType::PRIMINPUT: return "prim::Input";
         case LayerType::PRIMOUTPUT: return "prim::Output";
         case LayerType::PRIMCONSTANT: return "prim::Constant";
@@ -164,6 +171,43 @@ class AtenCopyLayer : public NNLayer {
    public:
     explicit AtenCopyLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENCOPY) {}
     int non_blocking = 0;
+};
+
+// aten::softmax / aten::log_softmax(self, dim): the attribute the reference's layers carry (dim; dtype is not modelled)
+class AtenSoftmaxLayer : public NNLayer {
+   public:
+    AtenSoftmaxLayer(std::string name, bool log)
+        : NNLayer(std::move(name), log ? LayerType::ATENLOGSOFTMAX : LayerType::ATENSOFTMAX) {}
+    int64_t dim = -1;
+};
+
+// aten::argmax(self, dim, keepdim)
+class AtenArgmaxLayer : public NNLayer {
+   public:
+    explicit AtenArgmaxLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENARGMAX) {}
+    int64_t dim = -1;
+    int keepdim = 0;
+};
+
+// aten::layer_norm(input, normalized_shape, weight, bias, eps) with weight / bias preloaded on the layer
+class AtenLayerNormLayer : public NNLayer {
+   public:
+    explicit AtenLayerNormLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENLAYERNORM) {}
+    std::vector<int64_t> normalized_shape;
+    at::Tensor weight, bias;
+    double eps = 1e-5;
+};
+
+class AtenTanhLayer : public NNLayer {
+   public:
+    explicit AtenTanhLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENTANH) {}
+};
+
+// aten::masked_fill(self, mask, value) with a scalar value
+class AtenMaskedFillLayer : public NNLayer {
+   public:
+    explicit AtenMaskedFillLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENMASKEDFILL) {}
+    double value = 0.0;
 };
 
 class MultiStreamLayer : public NNLayer {

@@ -179,6 +179,100 @@ void executeAtenAdd(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
     ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
 }
 
+// ---- row-wise glue of the decode path: the device kernels take contiguous fp16 rows along the last dimension;
+//      any other dim / dtype keeps the libtorch call the reference makes ----
+static bool lastDim(const at::Tensor& t, int64_t dim) { return t.dim() >= 1 && (dim == -1 || dim == t.dim() - 1); }
+
+void executeAtenSoftmax(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    auto sm = std::static_pointer_cast<ir::AtenSoftmaxLayer>(layer);
+    const bool log = layer->getType() == ir::LayerType::ATENLOGSOFTMAX;
+    at::Tensor x = blobTensor(ex, layer->getInSTensorID()[0]);
+    at::Tensor out;
+    if (fastHalf(x) && lastDim(x, sm->dim) && x.numel() > 0) {
+        at::Tensor xc = x.contiguous();
+        out = at::empty_like(xc);
+        const long cols = (long)xc.size(-1), rows = (long)(xc.numel() / cols);
+        ex.setStatus(pimb200_softmax_rows(xc.data_ptr(), out.data_ptr(), rows, cols, log ? 1 : 0, ex.currentStream()));
+    } else {
+        out = log ? at::log_softmax(x, sm->dim) : at::softmax(x, sm->dim);
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
+void executeAtenArgmax(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    auto am = std::static_pointer_cast<ir::AtenArgmaxLayer>(layer);
+    at::Tensor x = blobTensor(ex, layer->getInSTensorID()[0]);
+    at::Tensor out;
+    if (fastHalf(x) && lastDim(x, am->dim) && x.numel() > 0) {
+        at::Tensor xc = x.contiguous();
+        auto sizes = xc.sizes().vec();
+        const long cols = (long)sizes.back(), rows = (long)(xc.numel() / cols);
+        if (am->keepdim) sizes.back() = 1;
+        else sizes.pop_back();
+        out = at::empty(sizes, xc.options().dtype(at::kLong));
+        ex.setStatus(pimb200_argmax_rows(xc.data_ptr(), reinterpret_cast<long long*>(out.data_ptr<int64_t>()), rows, cols,
+                                         ex.currentStream()));
+    } else {
+        out = at::argmax(x, am->dim, am->keepdim != 0);
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
+void executeAtenLayerNorm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    auto ln = std::static_pointer_cast<ir::AtenLayerNormLayer>(layer);
+    at::Tensor x = blobTensor(ex, layer->getInSTensorID()[0]);
+    at::Tensor out;
+    const bool one_dim = ln->normalized_shape.size() == 1 && x.dim() >= 1 && ln->normalized_shape[0] == x.size(-1);
+    if (fastHalf(x) && one_dim && x.numel() > 0 && (!ln->weight.defined() || fastHalf(ln->weight)) &&
+        (!ln->bias.defined() || fastHalf(ln->bias))) {
+        at::Tensor xc = x.contiguous();
+        out = at::empty_like(xc);
+        const long cols = (long)xc.size(-1), rows = (long)(xc.numel() / cols);
+        at::Tensor w = ln->weight.defined() ? ln->weight.contiguous() : at::Tensor();
+        at::Tensor b = ln->bias.defined() ? ln->bias.contiguous() : at::Tensor();
+        ex.setStatus(pimb200_layer_norm_rows(xc.data_ptr(), w.defined() ? w.data_ptr() : nullptr,
+                                             b.defined() ? b.data_ptr() : nullptr, out.data_ptr(), rows, cols,
+                                             (float)ln->eps, ex.currentStream()));
+    } else {
+        out = at::layer_norm(x, ln->normalized_shape,
+                             ln->weight.defined() ? c10::optional<at::Tensor>(ln->weight) : c10::nullopt,
+                             ln->bias.defined() ? c10::optional<at::Tensor>(ln->bias) : c10::nullopt, ln->eps);
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
+void executeAtenTanh(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    at::Tensor x = blobTensor(ex, layer->getInSTensorID()[0]);
+    at::Tensor out;
+    if (fastHalf(x) && x.numel() > 0) {
+        at::Tensor xc = x.contiguous();
+        out = at::empty_like(xc);
+        ex.setStatus(pimb200_tanh_f16(xc.data_ptr(), out.data_ptr(), (size_t)xc.numel(), ex.currentStream()));
+    } else {
+        out = at::tanh(x);
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
+void executeAtenMaskedFill(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    auto mf = std::static_pointer_cast<ir::AtenMaskedFillLayer>(layer);
+    const auto& in = layer->getInSTensorID();
+    at::Tensor x = blobTensor(ex, in[0]), mask = blobTensor(ex, in[1]);
+    at::Tensor out;
+    const bool same = mask.sizes() == x.sizes();
+    const bool row = !same && x.dim() >= 1 && mask.numel() == x.size(-1) && mask.dim() >= 1 && mask.size(-1) == x.size(-1);
+    if (fastHalf(x) && mask.is_cuda() && mask.scalar_type() == at::kBool && (same || row) && x.numel() > 0) {
+        at::Tensor xc = x.contiguous(), mc = mask.contiguous();
+        out = at::empty_like(xc);
+        ex.setStatus(pimb200_masked_fill_f16(xc.data_ptr(), reinterpret_cast<const unsigned char*>(mc.data_ptr<bool>()),
+                                             (float)mf->value, out.data_ptr(), (size_t)xc.numel(), (size_t)mc.numel(),
+                                             ex.currentStream()));
+    } else {
+        out = at::masked_fill(x, mask, mf->value);
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
 // x[1,1,k] . A[1,k,n] (the GNMT attention context) through the single-row kernel; anything else is at::bmm
 void executeAtenBmm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
     const auto& in = layer->getInSTensorID();

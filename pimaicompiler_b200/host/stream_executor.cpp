@@ -50,6 +50,12 @@ void StreamExecutor::registerOp() {
     reg(ir::LayerType::ATENLSTM2, executeAtenLSTM2);
     reg(ir::LayerType::ATENMATMUL, executeAtenMatmul);
     reg(ir::LayerType::MULTISTREAM, executeMultiStream);
+    reg(ir::LayerType::ATENSOFTMAX, executeAtenSoftmax);
+    reg(ir::LayerType::ATENLOGSOFTMAX, executeAtenSoftmax);
+    reg(ir::LayerType::ATENARGMAX, executeAtenArgmax);
+    reg(ir::LayerType::ATENLAYERNORM, executeAtenLayerNorm);
+    reg(ir::LayerType::ATENTANH, executeAtenTanh);
+    reg(ir::LayerType::ATENMASKEDFILL, executeAtenMaskedFill);
     // the one prim op graphs on this path cannot do without: gathers tensor blobs into a list blob
     reg(ir::LayerType::PRIMLISTCONSTRUCT, [](std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
         c10::List<at::Tensor> l;

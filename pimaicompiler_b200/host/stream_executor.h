@@ -84,6 +84,11 @@ void executeAtenAdd(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_
 void executeAtenAddmm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenAddmmWithStream(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor, void* stream);
 void executeAtenBmm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
+void executeAtenSoftmax(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);   // also log_softmax
+void executeAtenArgmax(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
+void executeAtenLayerNorm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
+void executeAtenTanh(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
+void executeAtenMaskedFill(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenCat(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenCopy(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenLinear(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);

@@ -151,6 +151,58 @@ def cat(tensors: Sequence[torch.Tensor], dim: int, out: Optional[torch.Tensor] =
     return out
 
 
+def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax / log_softmax over the last dimension of a contiguous CUDA fp16 tensor."""
+    _req_half_cuda(x)
+    cols = x.shape[-1] if x.dim() else 1
+    rows = x.numel() // max(cols, 1)
+    y = out if out is not None else torch.empty_like(x)
+    check(_lib.lib().pimb200_softmax_rows(_ptr(x), _ptr(y), rows, cols, 1 if log else 0, _stream()), "softmax_rows")
+    return y
+
+
+def argmax(x: torch.Tensor) -> torch.Tensor:
+    """Index of the largest element along the last dimension (lowest index on ties), int64."""
+    _req_half_cuda(x)
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    idx = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    check(_lib.lib().pimb200_argmax_rows(_ptr(x), idx.data_ptr(), rows, cols, _stream()), "argmax_rows")
+    return idx
+
+
+def layer_norm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
+               eps: float = 1e-5) -> torch.Tensor:
+    """Layer normalisation over the last dimension."""
+    _req_half_cuda(x, gamma, beta)
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    y = torch.empty_like(x)
+    check(_lib.lib().pimb200_layer_norm_rows(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), rows, cols, float(eps),
+                                             _stream()), "layer_norm_rows")
+    return y
+
+
+def tanh(x: torch.Tensor) -> torch.Tensor:
+    _req_half_cuda(x)
+    y = torch.empty_like(x)
+    check(_lib.lib().pimb200_tanh_f16(_ptr(x), _ptr(y), x.numel(), _stream()), "tanh_f16")
+    return y
+
+
+def masked_fill(x: torch.Tensor, mask: torch.Tensor, value: float) -> torch.Tensor:
+    """x with `value` where mask is set; mask (bool) has x's shape or is one row broadcast over the rows of x."""
+    _req_half_cuda(x)
+    if mask.dtype != torch.bool or not mask.is_cuda or not mask.is_contiguous():
+        raise TypeError("expected a contiguous CUDA bool mask")
+    if mask.numel() not in (x.numel(), x.shape[-1]):
+        raise ValueError("mask must match x or be one row of it")
+    y = torch.empty_like(x)
+    check(_lib.lib().pimb200_masked_fill_f16(_ptr(x), mask.data_ptr(), float(value), _ptr(y), x.numel(), mask.numel(),
+                                             _stream()), "masked_fill_f16")
+    return y
+
+
 class Lstm:
     """Packed-weight handle of one aten::lstm node (``pimb200_lstm_create`` ... ``_destroy``)."""
 

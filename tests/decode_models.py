@@ -4,7 +4,8 @@ model code runs on the libtorch-CPU oracle (fp32) and on the device ops of this 
 Random-init weights of the benchmark's architectures (C4: 4-layer LSTM decoder with normalised Bahdanau attention and a
 vocabulary projection; C5: Transformer decoder layers with a KV cache); the corpora and checkpoints are not available
 offline.  The hot ops (lstm with seq_len 1, batch-1 linear with fused ReLU, fp16 add, single-row bmm, cat / KV append)
-go through the backend; softmax, layer norm and tanh stay with torch on either side, as they do in the reference.
+and the row-wise glue around them (tanh, softmax, layer norm, arg max) go through the backend; only the per-head
+reshapes and the two small batched products of multi-head attention stay with torch on either side.
 """
 from __future__ import annotations
 
@@ -42,6 +43,18 @@ class CpuBackend:
     def cat(self, ts, dim):
         return torch.cat(ts, dim)
 
+    def tanh(self, x):
+        return torch.tanh(x)
+
+    def softmax(self, x):
+        return torch.softmax(x, -1)
+
+    def layer_norm(self, x):
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],))
+
+    def argmax(self, x):
+        return int(torch.argmax(x))
+
 
 class PimBackend:
     """fp16 device ops through libpimb200.so."""
@@ -77,6 +90,18 @@ class PimBackend:
     def cat(self, ts, dim):
         return self.ops.cat([t.contiguous() for t in ts], dim)
 
+    def tanh(self, x):
+        return self.ops.tanh(x.contiguous())
+
+    def softmax(self, x):
+        return self.ops.softmax(x.contiguous())
+
+    def layer_norm(self, x):
+        return self.ops.layer_norm(x.contiguous().view(1, -1)).view(x.shape)
+
+    def argmax(self, x):
+        return int(self.ops.argmax(x.contiguous().view(1, -1)).item())
+
 
 # ------------------------------------------------------------------------------------------------ GNMT-style decoder
 def make_gnmt(H, V, src_len, gen, gain=1.0):
@@ -97,7 +122,7 @@ def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
     residual adds -> vocabulary projection -> argmax; `forced[t]` overrides the fed-back token ("follow" mode)."""
     W = {k: ([be.put(t) for t in v] if isinstance(v, list) else be.put(v)) for k, v in w.items()}
     keys_proj = be.linear(W["keys"], W["Wk"])                               # [S, H], once per sentence
-    v_norm = W["att_v"].float() / W["att_v"].float().norm() * float(w["att_g"])
+    v_norm = be.put(w["att_v"] / w["att_v"].norm() * float(w["att_g"]))       # normalised Bahdanau score vector
     hs = [torch.zeros(1, 1, H, dtype=be.dtype, device=be.dev) for _ in range(4)]
     cs = [torch.zeros(1, 1, H, dtype=be.dtype, device=be.dev) for _ in range(4)]
     tok, toks, logits = bos, [], []
@@ -105,8 +130,9 @@ def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
         x = W["emb"][tok]
         y0, hs[0], cs[0] = be.lstm_cell_stack("l0", x, hs[0], cs[0], W["l0"], 1)
         q = be.linear(y0, W["Wq"])
-        e = torch.tanh((keys_proj.float() + q.float() + W["att_b"].float())) @ v_norm          # [S]
-        att = torch.softmax(e, 0).to(be.dtype)
+        scores = be.tanh(be.add(keys_proj, be.add(q, W["att_b"])))          # [S, H]: row broadcast add, tanh
+        e = be.linear(v_norm, scores)                                       # [S] = scores . v
+        att = be.softmax(e)
         ctx = be.bmm_row(att, W["keys"])                                    # [H]
         x1 = be.cat([y0.view(1, H), ctx.view(1, H)], 1).view(-1)            # the {1,1,2048} buffer of the reference
         y1, hs[1], cs[1] = be.lstm_cell_stack("l1", x1, hs[1], cs[1], W["l1"], 1)
@@ -116,9 +142,9 @@ def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
         x3 = be.cat([r2.view(1, H), ctx.view(1, H)], 1).view(-1)
         y3, hs[3], cs[3] = be.lstm_cell_stack("l3", x3, hs[3], cs[3], W["l3"], 1)
         r3 = be.add(y3, r2)
-        lg = be.linear(r3, W["Wc"], W["bc"]).float().cpu()
-        logits.append(lg)
-        best = int(torch.argmax(lg))
+        lgd = be.linear(r3, W["Wc"], W["bc"])
+        logits.append(lgd.float().cpu())
+        best = be.argmax(lgd)
         toks.append(best)
         tok = best if forced is None else int(forced[t])
     return toks, torch.stack(logits)
@@ -139,19 +165,20 @@ def make_transformer(d, heads, ffn, V, layers, src_len, gen, gain=1.0):
     return w
 
 
-def _attend(q, K, Vv, heads):
-    """q [d], K/V [t, d] -> [d]; per-head scaled dot-product attention (not a hot-path op: torch on either side)."""
+def _attend(be, q, K, Vv, heads):
+    """q [d], K/V [t, d] -> [d]; per-head scaled dot-product attention: the two small batched products stay with torch
+    on either side, the softmax over each head's scores goes through the backend."""
     d = q.numel()
     hd = d // heads
     qh = q.float().view(heads, 1, hd)
     Kh = K.float().view(-1, heads, hd).transpose(0, 1)
     Vh = Vv.float().view(-1, heads, hd).transpose(0, 1)
-    p = torch.softmax(qh @ Kh.transpose(1, 2) / math.sqrt(hd), -1)
+    p = be.softmax((qh @ Kh.transpose(1, 2) / math.sqrt(hd)).to(be.dtype)).float()
     return (p @ Vh).reshape(d)
 
 
 def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
-    ln = lambda x: torch.nn.functional.layer_norm(x.float(), (d,)).to(be.dtype)
+    ln = be.layer_norm
     P = lambda t: be.put(t)
     emb, Wo, mem = P(w["emb"]), P(w["Wo"]), P(w["mem"])
     Ls = [{k: P(v) for k, v in L.items()} for L in w["layers"]]
@@ -167,16 +194,16 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
             v = be.linear(x, L["sv"], L["sv_b"])
             kcache[i] = be.cat([kcache[i], k.view(1, d)], 0) if kcache[i].shape[0] else k.view(1, d).clone()  # KV append
             vcache[i] = be.cat([vcache[i], v.view(1, d)], 0) if vcache[i].shape[0] else v.view(1, d).clone()
-            a = _attend(q, kcache[i], vcache[i], heads).to(be.dtype)
+            a = _attend(be, q, kcache[i], vcache[i], heads).to(be.dtype)
             x = ln(be.add(x, be.linear(a, L["so"], L["so_b"])))
             cq = be.linear(x, L["cq"], L["cq_b"])
-            ca = _attend(cq, cross[i][0], cross[i][1], heads).to(be.dtype)
+            ca = _attend(be, cq, cross[i][0], cross[i][1], heads).to(be.dtype)
             x = ln(be.add(x, be.linear(ca, L["co"], L["co_b"])))
             f = be.linear(be.linear(x, L["f1"], L["f1_b"], relu=True), L["f2"], L["f2_b"])
             x = ln(be.add(x, f))
-        lg = be.linear(x, Wo).float().cpu()
-        logits.append(lg)
-        best = int(torch.argmax(lg))
+        lgd = be.linear(x, Wo)
+        logits.append(lgd.float().cpu())
+        best = be.argmax(lgd)
         toks.append(best)
         tok = best if forced is None else int(forced[t])
     return toks, torch.stack(logits)

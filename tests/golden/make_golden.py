@@ -99,7 +99,34 @@ def main():
                         add_sym=(A.half() + Bm.half()).numpy(), add_bcast=(A.half() + Br.half()).numpy(),
                         cat0=parts[0].numpy(), cat1=parts[1].numpy(), cat2=parts[2].numpy(),
                         cat_out=torch.cat(parts, 1).numpy(), **meta)
+    rowops(meta)
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
+
+
+def rowops(meta):
+    """softmax / log_softmax / argmax / layer_norm / tanh / masked_fill over the last dimension (its own generator,
+    so adding it left the older fixtures unchanged)."""
+    g = torch.Generator().manual_seed(4321)
+    out = dict(meta)
+    for name, shape in (("logits", (3, 29)), ("scores", (8, 1, 13)), ("model", (5, 512)), ("vocab", (2, 1000))):
+        x = h16(torch.randn(*shape, generator=g) * 3.0)
+        out[f"{name}_x"] = x.numpy().astype(np.float16)
+        out[f"{name}_softmax"] = torch.softmax(x, -1).numpy()
+        out[f"{name}_log_softmax"] = torch.log_softmax(x, -1).numpy()
+        out[f"{name}_argmax"] = torch.argmax(x, -1).numpy()
+        out[f"{name}_tanh"] = torch.tanh(x).numpy()
+    x = h16(torch.randn(5, 512, generator=g) * 2.0 + 0.5)
+    gamma = h16(torch.rand(512, generator=g) + 0.5)
+    beta = h16(torch.randn(512, generator=g) * 0.1)
+    out["ln_x"], out["ln_gamma"], out["ln_beta"] = (t.numpy().astype(np.float16) for t in (x, gamma, beta))
+    out["ln_y"] = torch.nn.functional.layer_norm(x, (512,), gamma, beta, 1e-5).numpy()
+    out["ln_y_plain"] = torch.nn.functional.layer_norm(x, (512,), None, None, 1e-6).numpy()
+    mask = torch.rand(4, 13, generator=g) < 0.3
+    mx = h16(torch.randn(4, 13, generator=g))
+    out["mf_x"], out["mf_mask"], out["mf_row_mask"] = mx.numpy().astype(np.float16), mask.numpy(), mask[0].numpy()
+    out["mf_y"] = mx.masked_fill(mask, -65504.0).numpy()
+    out["mf_y_row"] = mx.masked_fill(mask[0], 0.25).numpy()
+    np.savez_compressed(os.path.join(HERE, "rowops.npz"), **out)
 
 
 if __name__ == "__main__":

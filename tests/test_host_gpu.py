@@ -100,6 +100,40 @@ def test_add_bmm_cat_copy_executors():
     assert torch.equal(ocp.cpu(), a + b) and ocp.data_ptr() == dst.data_ptr()
 
 
+def test_decode_glue_executors_attention_and_classifier_tail():
+    # The tail of a GNMT / Transformer decode step as one graph: attention scores -> tanh -> masked_fill ->
+    # softmax; model vector -> layer_norm; logits -> log_softmax and argmax.  fp16 CUDA inputs take the device
+    # kernels, the fp32 CPU run of the same graph takes the executors' libtorch branch (the reference's calls).
+    h = _host()
+    g = torch.Generator().manual_seed(5)
+    scores = h16(torch.randn(8, 1, 13, generator=g) * 2.0)
+    mask = torch.rand(13, generator=g) < 0.3
+    vec = h16(torch.randn(1, 512, generator=g))
+    gamma, beta = h16(torch.rand(512, generator=g) + 0.5), h16(torch.randn(512, generator=g) * 0.1)
+    logits = h16(torch.randn(1, 32320, generator=g) * 3.0)
+
+    def build(dev):
+        gr = h.Graph()
+        i_s, i_m, i_v, i_l = gr.add_input(), gr.add_input(), gr.add_input(), gr.add_input()
+        t = gr.add_tanh(i_s)
+        f = gr.add_masked_fill(t, i_m, -65504.0)
+        gr.mark_output(gr.add_softmax(f, -1))
+        gr.mark_output(gr.add_layer_norm(i_v, [512], dev(gamma), dev(beta), 1e-5))
+        gr.mark_output(gr.add_softmax(i_l, -1, log=True))
+        gr.mark_output(gr.add_argmax(i_l, -1, keepdim=True))
+        return h.NNRuntime(gr)
+
+    got = build(to_dev).inferenceModel([to_dev(scores), mask.cuda(), to_dev(vec), to_dev(logits)])
+    ref = build(lambda t: t).inferenceModel([scores, mask, vec, logits])
+    assert got[0].dtype == torch.float16 and got[3].dtype == torch.int64 and got[3].shape == (1, 1)
+    assert_close(got[0], ref[0], 1e-3, 1e-3, "tanh -> masked_fill -> softmax")
+    assert_close(got[1], ref[1], 3e-3, 1e-3, "layer_norm")
+    assert_close(got[2], ref[2], 8e-3, 1e-3, "log_softmax")
+    assert torch.equal(got[3].cpu(), ref[3])
+    # masked positions carry no attention weight
+    assert float(got[0].float().cpu()[..., mask].abs().max()) == 0.0
+
+
 def test_custom_cat_returns_prefilled_buffer_without_copy():
     h = _host()
     gr = h.Graph()

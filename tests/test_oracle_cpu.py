@@ -93,3 +93,20 @@ def test_oracle_fp16_emulation_rounds_hidden_state():
     assert np.array_equal(y, y.astype(np.float16).astype(np.float32))
     y32, _, _ = co.lstm(x, ps, 1, False)
     assert np.abs(y - y32).max() < 2e-3
+
+
+def test_oracle_rowops_match_libtorch_golden():
+    # softmax / log_softmax / argmax / tanh / layer_norm / masked_fill over the last dimension against libtorch CPU
+    z = _load("rowops.npz")
+    for name in ("logits", "scores", "model", "vocab"):
+        x = z[f"{name}_x"].astype(np.float32)
+        np.testing.assert_allclose(co.softmax(x), z[f"{name}_softmax"], atol=1e-6, rtol=1e-5)
+        np.testing.assert_allclose(co.softmax(x, log=True), z[f"{name}_log_softmax"], atol=2e-6, rtol=1e-5)
+        assert np.array_equal(co.argmax(x), z[f"{name}_argmax"])
+        np.testing.assert_allclose(co.tanh(x), z[f"{name}_tanh"], atol=1e-6, rtol=1e-6)
+    x, gamma, beta = (z[k].astype(np.float32) for k in ("ln_x", "ln_gamma", "ln_beta"))
+    np.testing.assert_allclose(co.layer_norm(x, gamma, beta, 1e-5), z["ln_y"], atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(co.layer_norm(x, None, None, 1e-6), z["ln_y_plain"], atol=2e-6, rtol=1e-5)
+    mx = z["mf_x"].astype(np.float32)
+    assert np.array_equal(co.masked_fill(mx, z["mf_mask"], -65504.0), z["mf_y"])
+    assert np.array_equal(co.masked_fill(mx, z["mf_row_mask"], 0.25), z["mf_y_row"])
