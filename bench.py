@@ -360,6 +360,17 @@ def run_c2(args):
             results.append({"N": N, "K": K, "B": B, "bytes": bb, "gemm_us": usb, "gemm_gbs": bb / usb / 1e3,
                             "gemm_tflops": 2.0 * B * N * K / usb / 1e6})
         del Ws, As
+    # row-wise glue of a decode step at its benchmark sizes: the 32320-wide GNMT / 29-wide RNN-T logit rows, a 512-wide
+    # model vector, 8 heads x 40 attention scores (one launch each, 16 calls per graph)
+    rowops = []
+    for name, rows, cols in (("logits_gnmt", 1, 32320), ("logits_rnnt", 1, 29), ("model_vec", 1, 512), ("attn", 8, 40)):
+        xr = (torch.randn(rows, cols, generator=g) * 3).half().to(dev)
+        yr = torch.empty_like(xr)
+        t_sm = _graph_time_us([(lambda: ops.softmax(xr, out=yr)) for _ in range(16)], args.steps * 10)
+        t_am = _graph_time_us([(lambda: ops.argmax(xr)) for _ in range(16)], args.steps * 10)
+        t_ln = _graph_time_us([(lambda: ops.layer_norm(xr)) for _ in range(16)], args.steps * 10)
+        rowops.append({"case": name, "rows": rows, "cols": cols, "softmax_us": t_sm, "argmax_us": t_am,
+                       "layer_norm_us": t_ln})
     clocks = sampler.stop()
     big = next(r for r in results if r["N"] == 32320 and r["B"] == 1)
     line = {"metric": "gemv_mv_hbm_gbs", "value": big["mv_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -371,7 +382,7 @@ def run_c2(args):
             "roofline": {"bound": "hbm", "kernel": "gemv_mv_vec_kernel<4> (32320x1024)", "achieved": big["mv_gbs"],
                          "peak": peak, "unit": "GB/s", "frac": big["mv_gbs"] / peak, "peak_source": peak_src,
                          "traffic": None},
-            "results": results, "clocks": clocks, "gpu_launches": None}
+            "results": results, "rowops": rowops, "clocks": clocks, "gpu_launches": None}
     print(json.dumps(line), flush=True)
 
 

@@ -5,8 +5,9 @@
 // (runtime/source/executor/op_executor/aten_ops_executor.cpp: executeAtenSoftmax 3402-3436, executeAtenLogSoftmax
 // 2092-2133, executeAtenArgmax 520-547, executeAtenLayerNorm 1898-1942, executeAtenTanh 3555-3568,
 // executeAtenMaskedFill 2432-2467).  All are small and latency-bound at decode sizes (a 29..32320-wide logit row, a
-// handful of attention scores, a 512-wide model vector): one CTA per row, the row is read with 128-bit loads when its
-// address and length allow, reductions run in fp32 through warp shuffles and one shared-memory hop.
+// handful of attention scores, a 512-wide model vector): one CTA per row (128 threads, 1024 for rows of 4096 elements
+// or more), the row is read with 128-bit loads when its address and length allow, reductions run in fp32 through warp
+// shuffles and one shared-memory hop.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -15,9 +16,9 @@ using namespace pimb200;
 
 namespace {
 
-constexpr int kRowThreads = 128;
-constexpr int kRowWarps = kRowThreads / 32;
+constexpr int kWideRow = 4096;   // rows at least this long get a 1024-thread CTA
 
+template <int T>
 __device__ __forceinline__ float block_max(float v, float* red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -27,9 +28,10 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     __syncthreads();
     float r = red[0];
 #pragma unroll
-    for (int w = 1; w < kRowWarps; ++w) r = fmaxf(r, red[w]);
+    for (int w = 1; w < T / 32; ++w) r = fmaxf(r, red[w]);
     return r;
 }
+template <int T>
 __device__ __forceinline__ float block_sum(float v, float* red) {
     v = warp_sum(v);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -38,53 +40,75 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     __syncthreads();
     float r = red[0];
 #pragma unroll
-    for (int w = 1; w < kRowWarps; ++w) r += red[w];   // fixed order: the result does not depend on timing
+    for (int w = 1; w < T / 32; ++w) r += red[w];   // fixed order: the result does not depend on timing
     return r;
 }
 
 // element access: VEC = 8 halves per 16-byte load when the row allows it, else scalar
-template <bool VEC, typename F>
+template <int T, bool VEC, typename F>
 __device__ __forceinline__ void for_each(const __half* row, long cols, F f) {
     if (VEC) {
         const uint4* r4 = reinterpret_cast<const uint4*>(row);
-        for (long c = threadIdx.x; c < (cols >> 3); c += kRowThreads) {
+        for (long c = threadIdx.x; c < (cols >> 3); c += T) {
             float xf[8];
             widen8(r4[c], xf);
 #pragma unroll
             for (int j = 0; j < 8; ++j) f(c * 8 + j, xf[j]);
         }
     } else {
-        for (long c = threadIdx.x; c < cols; c += kRowThreads) f(c, __half2float(row[c]));
+        for (long c = threadIdx.x; c < cols; c += T) f(c, __half2float(row[c]));
     }
 }
 
-template <bool VEC, bool LOG>
-__global__ void __launch_bounds__(kRowThreads) softmax_rows_kernel(const __half* __restrict__ x, __half* __restrict__ y,
+// out[c] = g(c, row[c]) for the whole row; in the vector case eight results leave as one 16-byte store
+template <int T, bool VEC, typename G>
+__device__ __forceinline__ void map_store(const __half* row, __half* out, long cols, G g) {
+    if (VEC) {
+        const uint4* r4 = reinterpret_cast<const uint4*>(row);
+        uint4* o4 = reinterpret_cast<uint4*>(out);
+        for (long c = threadIdx.x; c < (cols >> 3); c += T) {
+            float xf[8];
+            widen8(r4[c], xf);
+            __half2 h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(g(c * 8 + 2 * j, xf[2 * j]), g(c * 8 + 2 * j + 1, xf[2 * j + 1]));
+            uint4 pk;
+            pk.x = *reinterpret_cast<uint32_t*>(&h[0]);
+            pk.y = *reinterpret_cast<uint32_t*>(&h[1]);
+            pk.z = *reinterpret_cast<uint32_t*>(&h[2]);
+            pk.w = *reinterpret_cast<uint32_t*>(&h[3]);
+            o4[c] = pk;
+        }
+    } else {
+        for (long c = threadIdx.x; c < cols; c += T) out[c] = __float2half_rn(g(c, __half2float(row[c])));
+    }
+}
+
+template <int T, bool VEC, bool LOG>
+__global__ void __launch_bounds__(T) softmax_rows_kernel(const __half* __restrict__ x, __half* __restrict__ y,
                                                                    long cols) {
-    __shared__ float red[kRowWarps];
+    __shared__ float red[T / 32];
     const __half* row = x + (size_t)blockIdx.x * cols;
     __half* out = y + (size_t)blockIdx.x * cols;
     float m = -CUDART_INF_F;
-    for_each<VEC>(row, cols, [&](long, float v) { m = fmaxf(m, v); });
-    m = block_max(m, red);
+    for_each<T, VEC>(row, cols, [&](long, float v) { m = fmaxf(m, v); });
+    m = block_max<T>(m, red);
     float s = 0.f;
-    for_each<VEC>(row, cols, [&](long, float v) { s += expf(v - m); });
-    s = block_sum(s, red);
+    for_each<T, VEC>(row, cols, [&](long, float v) { s += expf(v - m); });
+    s = block_sum<T>(s, red);
     const float inv = 1.0f / s, ls = logf(s);
-    for_each<VEC>(row, cols, [&](long c, float v) {
-        out[c] = __float2half_rn(LOG ? (v - m) - ls : expf(v - m) * inv);
-    });
+    map_store<T, VEC>(row, out, cols, [&](long, float v) { return LOG ? (v - m) - ls : expf(v - m) * inv; });
 }
 
-template <bool VEC>
-__global__ void __launch_bounds__(kRowThreads) argmax_rows_kernel(const __half* __restrict__ x, long long* __restrict__ idx,
+template <int T, bool VEC>
+__global__ void __launch_bounds__(T) argmax_rows_kernel(const __half* __restrict__ x, long long* __restrict__ idx,
                                                                   long cols) {
-    __shared__ float red_v[kRowWarps];
-    __shared__ long long red_i[kRowWarps];
+    __shared__ float red_v[T / 32];
+    __shared__ long long red_i[T / 32];
     const __half* row = x + (size_t)blockIdx.x * cols;
     float bv = -CUDART_INF_F;
     long long bi = cols;   // lowest index among equal maxima wins, as in at::argmax on a contiguous row
-    for_each<VEC>(row, cols, [&](long c, float v) {
+    for_each<T, VEC>(row, cols, [&](long c, float v) {
         if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
     });
 #pragma unroll
@@ -97,31 +121,31 @@ __global__ void __launch_bounds__(kRowThreads) argmax_rows_kernel(const __half* 
     if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int w = 1; w < kRowWarps; ++w)
+        for (int w = 1; w < T / 32; ++w)
             if (red_v[w] > bv || (red_v[w] == bv && red_i[w] < bi)) { bv = red_v[w]; bi = red_i[w]; }
         idx[blockIdx.x] = bi < cols ? bi : 0;   // a row of NaNs / -inf only: index 0
     }
 }
 
-template <bool VEC>
-__global__ void __launch_bounds__(kRowThreads) layer_norm_rows_kernel(const __half* __restrict__ x,
+template <int T, bool VEC>
+__global__ void __launch_bounds__(T) layer_norm_rows_kernel(const __half* __restrict__ x,
                                                                       const __half* __restrict__ gamma,
                                                                       const __half* __restrict__ beta,
                                                                       __half* __restrict__ y, long cols, float eps) {
-    __shared__ float red[kRowWarps];
+    __shared__ float red[T / 32];
     const __half* row = x + (size_t)blockIdx.x * cols;
     __half* out = y + (size_t)blockIdx.x * cols;
     float s = 0.f;
-    for_each<VEC>(row, cols, [&](long, float v) { s += v; });
-    const float mean = block_sum(s, red) / (float)cols;
+    for_each<T, VEC>(row, cols, [&](long, float v) { s += v; });
+    const float mean = block_sum<T>(s, red) / (float)cols;
     float q = 0.f;
-    for_each<VEC>(row, cols, [&](long, float v) { const float d = v - mean; q += d * d; });
-    const float rstd = rsqrtf(block_sum(q, red) / (float)cols + eps);   // biased variance, as at::layer_norm
-    for_each<VEC>(row, cols, [&](long c, float v) {
+    for_each<T, VEC>(row, cols, [&](long, float v) { const float d = v - mean; q += d * d; });
+    const float rstd = rsqrtf(block_sum<T>(q, red) / (float)cols + eps);   // biased variance, as at::layer_norm
+    map_store<T, VEC>(row, out, cols, [&](long c, float v) {
         float r = (v - mean) * rstd;
         if (gamma) r *= __half2float(gamma[c]);
         if (beta) r += __half2float(beta[c]);
-        out[c] = __float2half_rn(r);
+        return r;
     });
 }
 
@@ -150,13 +174,22 @@ extern "C" int pimb200_softmax_rows(const void* x, void* y, long rows, long cols
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __half* xp = static_cast<const __half*>(x);
     __half* yp = static_cast<__half*>(y);
-    const bool vec = cols % 8 == 0 && aligned16(x);
-    if (vec) {
-        if (log_softmax) softmax_rows_kernel<true, true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
-        else softmax_rows_kernel<true, false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+    const bool vec = cols % 8 == 0 && aligned16(x) && aligned16(y);
+    const unsigned grid = (unsigned)rows;
+    if (cols >= kWideRow) {
+        if (vec) {
+            if (log_softmax) softmax_rows_kernel<1024, true, true><<<grid, 1024, 0, st>>>(xp, yp, cols);
+            else softmax_rows_kernel<1024, true, false><<<grid, 1024, 0, st>>>(xp, yp, cols);
+        } else {
+            if (log_softmax) softmax_rows_kernel<1024, false, true><<<grid, 1024, 0, st>>>(xp, yp, cols);
+            else softmax_rows_kernel<1024, false, false><<<grid, 1024, 0, st>>>(xp, yp, cols);
+        }
+    } else if (vec) {
+        if (log_softmax) softmax_rows_kernel<128, true, true><<<grid, 128, 0, st>>>(xp, yp, cols);
+        else softmax_rows_kernel<128, true, false><<<grid, 128, 0, st>>>(xp, yp, cols);
     } else {
-        if (log_softmax) softmax_rows_kernel<false, true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
-        else softmax_rows_kernel<false, false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, yp, cols);
+        if (log_softmax) softmax_rows_kernel<128, false, true><<<grid, 128, 0, st>>>(xp, yp, cols);
+        else softmax_rows_kernel<128, false, false><<<grid, 128, 0, st>>>(xp, yp, cols);
     }
     return launch_status();
 }
@@ -166,8 +199,15 @@ extern "C" int pimb200_argmax_rows(const void* x, long long* idx, long rows, lon
     if (!x || !idx || !rows_ok(rows, cols)) return PIMB200_ERR_BAD_ARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const __half* xp = static_cast<const __half*>(x);
-    if (cols % 8 == 0 && aligned16(x)) argmax_rows_kernel<true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, idx, cols);
-    else argmax_rows_kernel<false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, idx, cols);
+    const bool vec = cols % 8 == 0 && aligned16(x);
+    const unsigned grid = (unsigned)rows;
+    if (cols >= kWideRow) {
+        if (vec) argmax_rows_kernel<1024, true><<<grid, 1024, 0, st>>>(xp, idx, cols);
+        else argmax_rows_kernel<1024, false><<<grid, 1024, 0, st>>>(xp, idx, cols);
+    } else {
+        if (vec) argmax_rows_kernel<128, true><<<grid, 128, 0, st>>>(xp, idx, cols);
+        else argmax_rows_kernel<128, false><<<grid, 128, 0, st>>>(xp, idx, cols);
+    }
     return launch_status();
 }
 
@@ -180,10 +220,15 @@ extern "C" int pimb200_layer_norm_rows(const void* x, const void* gamma, const v
     const __half* g = static_cast<const __half*>(gamma);
     const __half* b = static_cast<const __half*>(beta);
     __half* yp = static_cast<__half*>(y);
-    if (cols % 8 == 0 && aligned16(x))
-        layer_norm_rows_kernel<true><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, g, b, yp, cols, eps);
-    else
-        layer_norm_rows_kernel<false><<<(unsigned)rows, kRowThreads, 0, st>>>(xp, g, b, yp, cols, eps);
+    const bool vec = cols % 8 == 0 && aligned16(x) && aligned16(y);
+    const unsigned grid = (unsigned)rows;
+    if (cols >= kWideRow) {
+        if (vec) layer_norm_rows_kernel<1024, true><<<grid, 1024, 0, st>>>(xp, g, b, yp, cols, eps);
+        else layer_norm_rows_kernel<1024, false><<<grid, 1024, 0, st>>>(xp, g, b, yp, cols, eps);
+    } else {
+        if (vec) layer_norm_rows_kernel<128, true><<<grid, 128, 0, st>>>(xp, g, b, yp, cols, eps);
+        else layer_norm_rows_kernel<128, false><<<grid, 128, 0, st>>>(xp, g, b, yp, cols, eps);
+    }
     return launch_status();
 }
 

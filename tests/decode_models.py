@@ -43,6 +43,13 @@ class CpuBackend:
     def cat(self, ts, dim):
         return torch.cat(ts, dim)
 
+    def kv_new(self, steps, d):
+        return torch.zeros(0, d)
+
+    def kv_append(self, cache, t, row):
+        # the reference's form: the cache grows by an at::cat per step
+        return torch.cat([cache, row.view(1, -1)], 0) if cache.shape[0] else row.view(1, -1).clone()
+
     def tanh(self, x):
         return torch.tanh(x)
 
@@ -89,6 +96,22 @@ class PimBackend:
 
     def cat(self, ts, dim):
         return self.ops.cat([t.contiguous() for t in ts], dim)
+
+    def kv_new(self, steps, d):
+        # pre-allocated [S_max, d] buffer; entries are written in place, the live prefix is a view
+        self._kv_full = getattr(self, "_kv_full", {})
+        buf = torch.zeros(steps, d, dtype=torch.float16, device="cuda")
+        view = buf[:0]
+        self._kv_full[id(view)] = buf
+        return view
+
+    def kv_append(self, cache, t, row):
+        buf = self._kv_full.pop(id(cache))
+        d = buf.shape[1]
+        self.ops.copy_2d(buf, t * d * 2, d * 2, row.contiguous(), 0, d * 2, d * 2, 1)   # one row at offset t
+        view = buf[: t + 1]
+        self._kv_full[id(view)] = buf
+        return view
 
     def tanh(self, x):
         return self.ops.tanh(x.contiguous())
@@ -183,8 +206,8 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
     emb, Wo, mem = P(w["emb"]), P(w["Wo"]), P(w["mem"])
     Ls = [{k: P(v) for k, v in L.items()} for L in w["layers"]]
     cross = [(be.linear(mem, L["ck"], L["ck_b"]), be.linear(mem, L["cv"], L["cv_b"])) for L in Ls]
-    kcache = [torch.zeros(0, d, dtype=be.dtype, device=be.dev) for _ in Ls]
-    vcache = [torch.zeros(0, d, dtype=be.dtype, device=be.dev) for _ in Ls]
+    kcache = [be.kv_new(steps, d) for _ in Ls]
+    vcache = [be.kv_new(steps, d) for _ in Ls]
     tok, toks, logits = bos, [], []
     for t in range(steps):
         x = emb[tok]
@@ -192,8 +215,8 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
             q = be.linear(x, L["sq"], L["sq_b"])
             k = be.linear(x, L["sk"], L["sk_b"])
             v = be.linear(x, L["sv"], L["sv_b"])
-            kcache[i] = be.cat([kcache[i], k.view(1, d)], 0) if kcache[i].shape[0] else k.view(1, d).clone()  # KV append
-            vcache[i] = be.cat([vcache[i], v.view(1, d)], 0) if vcache[i].shape[0] else v.view(1, d).clone()
+            kcache[i] = be.kv_append(kcache[i], t, k)      # KV append
+            vcache[i] = be.kv_append(vcache[i], t, v)
             a = _attend(be, q, kcache[i], vcache[i], heads).to(be.dtype)
             x = ln(be.add(x, be.linear(a, L["so"], L["so_b"])))
             cq = be.linear(x, L["cq"], L["cq_b"])
