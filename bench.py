@@ -429,14 +429,53 @@ def run_c1(args):
     print(json.dumps(line), flush=True)
 
 
+def run_c4(args):
+    """C4 (decoder side): GNMT-style greedy decode, vocabulary 32320, hidden 1024, 4 decoder LSTM layers with normalised
+    Bahdanau attention over 37 encoder states, 80 steps, one sentence stream.  Compares the op-by-op decode (one host
+    read of the token per step, as the reference's interpreter does) with the step resident on the device (CUDA graph,
+    token fed back through device memory)."""
+    from pimaicompiler_b200 import build
+    build.build()
+    from tests import decode_models as dm
+    H, V, S, steps = 1024, 32320, 37, 80
+    w = dm.make_gnmt(H, V, S, torch.Generator().manual_seed(4), 2.0)
+    be = dm.PimBackend()
+    dm.gnmt_greedy(be, w, H, 4)                                   # warm-up: handles, workspaces
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    toks, _ = dm.gnmt_greedy(be, w, H, steps)
+    torch.cuda.synchronize()
+    eager_us = (time.perf_counter() - t0) * 1e6 / steps
+    best = None
+    for _ in range(max(1, args.steps)):
+        gtoks, _, us = dm.gnmt_greedy_graph(w, H, steps)
+        best = us if best is None else min(best, us)
+    assert gtoks == toks
+    peak, peak_src = load_peaks()
+    # bytes one token streams: 4 LSTM layers (w_ih + w_hh), query projection, classifier, attention keys
+    nbytes = 2 * (4 * H * H * 2 + 3 * (4 * H * 2 * H + 4 * H * H) + H * H + V * H + 2 * S * H)
+    us_tok = best / steps
+    line = {"metric": "gnmt_decode_us_per_token", "value": us_tok, "unit": "us", "n_gpus": 1, "steps": args.steps,
+            "warmup": 1, "ms_per_step": best / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "C4 decoder: GNMT-style greedy decode, V=32320 H=1024, 37 source states, 80 steps, 1 stream"},
+            "op_by_op_us_per_token": eager_us, "device_resident_us_per_token": us_tok,
+            "roofline": {"bound": "hbm", "kernel": "one decode step (about 40 launches in one CUDA graph)",
+                         "achieved": nbytes / us_tok / 1e3, "peak": peak, "unit": "GB/s",
+                         "frac": nbytes / us_tok / 1e3 / peak, "peak_source": peak_src, "traffic": None},
+            "gpu_launches": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1"],
-                    help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm")
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4"],
+                    help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm; "
+                         "c4 = GNMT-style decoder step, op by op against device-resident")
     ap.add_argument("--streams-per-gpu", type=int, default=128)
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -446,9 +485,9 @@ def main():
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed
         run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
-    if args.workload in ("c1", "c2"):
+    if args.workload in ("c1", "c2", "c4"):
         if int(os.environ.get("RANK", "0")) == 0:
-            (run_c2 if args.workload == "c2" else run_c1)(args)
+            {"c1": run_c1, "c2": run_c2, "c4": run_c4}[args.workload](args)
         return
     rank, world, local = dist_setup(args.gpus)
     try:

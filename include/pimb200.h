@@ -149,6 +149,13 @@ int pimb200_tanh_f16(const void* x, void* y, size_t n, void* stream);
 int pimb200_masked_fill_f16(const void* x, const unsigned char* mask, float value, void* y, size_t n, size_t mask_n,
                             void* stream);
 
+/* out[i, :] = table[idx[i], :] for n_idx int64 indices that live in DEVICE memory (rows of row_bytes bytes; an index
+ * outside [0, n_table) gives a zero row).  The embedding lookup of a decode step without the host round trip of
+ * executeAtenEmbedding, which reads the index with indices.item() (aten_ops_executor.cpp:1233-1300, the sync at
+ * 1276-1287): the token chosen by pimb200_argmax_rows feeds the next step on the device. */
+int pimb200_gather_rows(const void* table, const long long* idx, void* out, long n_idx, size_t row_bytes, long n_table,
+                        void* stream);
+
 typedef struct pimb200_lstm pimb200_lstm;
 
 /* One-time weight layout step.  params = the flat list at::lstm takes:

@@ -168,6 +168,95 @@ __global__ void __launch_bounds__(256) lstm_step_kernel(StepArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// decode form (seq_len == 1): one launch per layer and direction computes the whole cell,
+//     z = W_ih x + W_hh h0 + b,  c = sigma(z_f) c0 + sigma(z_i) tanh(z_g),  h = sigma(z_o) tanh(c),
+// a warp per hidden unit streaming its four rows of both matrices once (128-bit loads that bypass L1), x and h0
+// through L1.  Replaces the projection GEMM + state initialisation + step kernel of the general path, which cost
+// three launches per layer where an autoregressive decoder calls aten::lstm once per token.
+// ---------------------------------------------------------------------------------------------
+struct CellArgs {
+    const __half* Wih;   // packed [4H, I]
+    const __half* Whh;   // packed [4H, H]
+    const float* bias;   // packed [4H]
+    const __half* x;     // input of sequence b at x + b*x_bstride
+    long x_bstride;
+    const __half* h0;    // [B, H] or NULL
+    const __half* c0;    // [B, H] or NULL
+    __half* y;           // h of sequence b at y + b*y_bstride
+    long y_bstride;
+    __half* hn;          // optional [B, H]
+    __half* cn;          // optional [B, H]
+    int I, H, B;
+};
+
+template <int BT>
+__global__ void __launch_bounds__(256) lstm_cell_kernel(CellArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int u = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (u >= a.H) return;
+    const int H = a.H, I = a.I;
+    const __half* wi = a.Wih + (size_t)u * 4 * I;
+    const __half* wh = a.Whh + (size_t)u * 4 * H;
+    for (int b0 = 0; b0 < a.B; b0 += BT) {
+        float acc[4][BT];
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < BT; ++j) acc[g][j] = 0.f;
+        const int I8 = I >> 3, H8 = H >> 3;
+#pragma unroll 2
+        for (int c = lane; c < I8; c += 32) {
+            uint4 wv[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) wv[g] = ldg_stream_v4(reinterpret_cast<const uint4*>(wi + (size_t)g * I) + c);
+#pragma unroll
+            for (int j = 0; j < BT; ++j) {
+                const int b = min(b0 + j, a.B - 1);
+                float xf[8];
+                widen8(__ldg(reinterpret_cast<const uint4*>(a.x + (size_t)b * a.x_bstride) + c), xf);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) acc[g][j] = dot8f(wv[g], xf, acc[g][j]);
+            }
+        }
+        if (a.h0) {
+#pragma unroll 2
+            for (int c = lane; c < H8; c += 32) {
+                uint4 wv[4];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) wv[g] = ldg_stream_v4(reinterpret_cast<const uint4*>(wh + (size_t)g * H) + c);
+#pragma unroll
+                for (int j = 0; j < BT; ++j) {
+                    const int b = min(b0 + j, a.B - 1);
+                    float xf[8];
+                    widen8(__ldg(reinterpret_cast<const uint4*>(a.h0 + (size_t)b * H) + c), xf);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) acc[g][j] = dot8f(wv[g], xf, acc[g][j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int j = 0; j < BT; ++j) acc[g][j] = warp_sum(acc[g][j]);
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < BT; ++j) {
+                const int b = b0 + j;
+                if (b >= a.B) break;
+                const float zi = acc[0][j] + a.bias[u * 4 + 0], zf = acc[1][j] + a.bias[u * 4 + 1],
+                            zg = acc[2][j] + a.bias[u * 4 + 2], zo = acc[3][j] + a.bias[u * 4 + 3];
+                const float cprev = a.c0 ? __half2float(a.c0[(size_t)b * H + u]) : 0.f;
+                const float cnew = sigmoidf_(zf) * cprev + sigmoidf_(zi) * tanhf_(zg);
+                const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(cnew));
+                a.y[(size_t)b * a.y_bstride + u] = hh;
+                if (a.hn) a.hn[(size_t)b * H + u] = hh;
+                if (a.cn) a.cn[(size_t)b * H + u] = __float2half_rn(cnew);
+            }
+        }
+    }
+}
+
 __global__ void lstm_init_c_kernel(float* __restrict__ c, const __half* __restrict__ c0, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) c[i] = c0 ? __half2float(c0[i]) : 0.f;
@@ -1569,9 +1658,35 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
     if (packed) rows = sq.row0[T - 1] + (long)sq.batch_sizes[T - 1];
     else rows = (long)T * B;
     int rc;
-    if ((rc = grow(&h->G, &h->G_cap, (size_t)rows * 4 * H)) != PIMB200_OK) return rc;
+    // decode form: seq_len 1, every extent a multiple of 8 and 16-byte aligned -> one fused cell launch per layer
+    bool cell = !packed && T == 1 && h->variant != PIMB200_LSTM_PERSISTENT && h->variant != PIMB200_LSTM_PERSISTENT_TAGGED &&
+                H % 8 == 0 && h->I % 8 == 0 && aligned16(x) && aligned16(y) && (!h0 || aligned16(h0));
+    if (!cell && (rc = grow(&h->G, &h->G_cap, (size_t)rows * 4 * H)) != PIMB200_OK) return rc;
     if (L > 1 && (rc = grow(&h->ybuf[0], &h->y_cap[0], (size_t)rows * D * H)) != PIMB200_OK) return rc;
     if (L > 2 && (rc = grow(&h->ybuf[1], &h->y_cap[1], (size_t)rows * D * H)) != PIMB200_OK) return rc;
+    if (cell) {
+        for (int l = 0; l < L; ++l) {
+            const bool last = (l == L - 1);
+            const __half* X = l == 0 ? x : h->ybuf[(l - 1) & 1];
+            __half* Y = last ? y : h->ybuf[l & 1];
+            for (int d = 0; d < D; ++d) {
+                const int ld = l * D + d;
+                CellArgs a;
+                a.Wih = h->w_ih[ld]; a.Whh = h->w_hh[ld]; a.bias = h->bias[ld];
+                a.x = X; a.x_bstride = in_size(h, l);
+                a.h0 = h0 ? h0 + (size_t)ld * B * H : nullptr;
+                a.c0 = c0 ? c0 + (size_t)ld * B * H : nullptr;
+                a.y = Y + (size_t)d * H; a.y_bstride = (long)D * H;
+                a.hn = hn ? hn + (size_t)ld * B * H : nullptr;
+                a.cn = cn ? cn + (size_t)ld * B * H : nullptr;
+                a.I = in_size(h, l); a.H = H; a.B = B;
+                if (B == 1) lstm_cell_kernel<1><<<ceil_div(H, 8), 256, 0, st>>>(a);
+                else lstm_cell_kernel<4><<<ceil_div(H, 8), 256, 0, st>>>(a);
+                if ((rc = launch_status()) != PIMB200_OK) return rc;
+            }
+        }
+        return PIMB200_OK;
+    }
     for (int l = 0; l < L; ++l) {
         const int Il = in_size(h, l);
         const bool first = (l == 0), last = (l == L - 1);

@@ -160,6 +160,22 @@ __global__ void masked_fill_f16_kernel(const __half* __restrict__ x, const unsig
         y[i] = mask[i % mask_n] ? value : x[i];
 }
 
+// out[i, :] = table[idx[i], :], rows of row_bytes bytes; an index outside [0, n_table) yields a zero row
+__global__ void gather_rows_kernel(const unsigned char* __restrict__ table, const long long* __restrict__ idx,
+                                   unsigned char* __restrict__ out, size_t row_bytes, long n_table, int vec16) {
+    const long long r = idx[blockIdx.x];
+    const bool ok = r >= 0 && r < n_table;
+    const unsigned char* src = table + (size_t)(ok ? r : 0) * row_bytes;
+    unsigned char* dst = out + (size_t)blockIdx.x * row_bytes;
+    if (vec16) {
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+        for (size_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = ok ? reinterpret_cast<const uint4*>(src)[i] : zero;
+    } else {
+        for (size_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = ok ? src[i] : (unsigned char)0;
+    }
+}
+
 inline unsigned flat_grid(size_t n) {
     const size_t g = (n + 255) / 256;
     return (unsigned)(g > (size_t)kNumSmB200 * 8 ? (size_t)kNumSmB200 * 8 : (g ? g : 1));
@@ -247,5 +263,15 @@ extern "C" int pimb200_masked_fill_f16(const void* x, const unsigned char* mask,
     if (mask_n == 0 || n % mask_n != 0) return PIMB200_ERR_BAD_ARG;
     masked_fill_f16_kernel<<<flat_grid(n), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(x), mask, __float2half_rn(value), static_cast<__half*>(y), n, mask_n);
+    return launch_status();
+}
+
+extern "C" int pimb200_gather_rows(const void* table, const long long* idx, void* out, long n_idx, size_t row_bytes,
+                                   long n_table, void* stream) {
+    if (n_idx == 0 || row_bytes == 0) return PIMB200_OK;
+    if (!table || !idx || !out || n_idx < 0 || n_idx > 0x7fffffffL || n_table <= 0) return PIMB200_ERR_BAD_ARG;
+    const int vec16 = (row_bytes % 16 == 0 && aligned16(table) && aligned16(out)) ? 1 : 0;
+    gather_rows_kernel<<<(unsigned)n_idx, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned char*>(table), idx, static_cast<unsigned char*>(out), row_bytes, n_table, vec16);
     return launch_status();
 }

@@ -161,12 +161,14 @@ def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = No
     return y
 
 
-def argmax(x: torch.Tensor) -> torch.Tensor:
+def argmax(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Index of the largest element along the last dimension (lowest index on ties), int64."""
     _req_half_cuda(x)
     cols = x.shape[-1]
     rows = x.numel() // max(cols, 1)
-    idx = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    idx = out if out is not None else torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    if idx.dtype != torch.int64 or not idx.is_cuda or idx.numel() != rows:
+        raise TypeError("expected a CUDA int64 tensor with one element per row")
     check(_lib.lib().pimb200_argmax_rows(_ptr(x), idx.data_ptr(), rows, cols, _stream()), "argmax_rows")
     return idx
 
@@ -180,6 +182,19 @@ def layer_norm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, beta: Opti
     y = torch.empty_like(x)
     check(_lib.lib().pimb200_layer_norm_rows(_ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), rows, cols, float(eps),
                                              _stream()), "layer_norm_rows")
+    return y
+
+
+def gather_rows(table: torch.Tensor, idx: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """table[idx] for a device-resident int64 index tensor (embedding lookup without a host round trip)."""
+    if not table.is_cuda or not table.is_contiguous() or table.dim() != 2:
+        raise TypeError("expected a contiguous 2-D CUDA table")
+    if idx.dtype != torch.int64 or not idx.is_cuda or not idx.is_contiguous():
+        raise TypeError("expected a contiguous CUDA int64 index tensor")
+    y = out if out is not None else torch.empty(*idx.shape, table.shape[1], dtype=table.dtype, device=table.device)
+    check(_lib.lib().pimb200_gather_rows(table.data_ptr(), idx.data_ptr(), y.data_ptr(), idx.numel(),
+                                         table.shape[1] * table.element_size(), table.shape[0], _stream()),
+          "gather_rows")
     return y
 
 

@@ -173,6 +173,71 @@ def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
     return toks, torch.stack(logits)
 
 
+def gnmt_greedy_graph(w, H, steps, bos=2):
+    """The same decode with the whole step resident on the device: arg max writes the chosen token's int64 index into
+    device memory, the next step gathers its embedding row by that index, the recurrent states live in fixed buffers,
+    and the step (about 40 launches) is captured once in a CUDA graph and replayed.  Nothing is read back until the
+    sentence is done, where the reference's interpreter synchronises at least once per token
+    (aten_ops_executor.cpp:1276-1287).  Returns (token ids, logits [steps, V], the graph replays' device time in us)."""
+    be = PimBackend()
+    ops = be.ops
+    W = {k: ([be.put(t) for t in v] if isinstance(v, list) else be.put(v)) for k, v in w.items()}
+    keys_proj = be.linear(W["keys"], W["Wk"])
+    v_norm = be.put(w["att_v"] / w["att_v"].norm() * float(w["att_g"]))
+    V = W["Wc"].shape[0]
+    tok = torch.full((1,), bos, dtype=torch.int64, device="cuda")
+    hs = [torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)]
+    cs = [torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)]
+    lg_buf = torch.zeros(V, dtype=torch.float16, device="cuda")
+    toks_dev = torch.zeros(steps, dtype=torch.int64, device="cuda")
+    logits_dev = torch.zeros(steps, V, dtype=torch.float16, device="cuda")
+
+    def step():
+        x = ops.gather_rows(W["emb"], tok).view(-1)                         # embedding lookup by a device-side index
+        new = [None] * 4
+        y0, *new[0] = be.lstm_cell_stack("l0", x, hs[0], cs[0], W["l0"], 1)
+        q = be.linear(y0, W["Wq"])
+        scores = be.tanh(be.add(keys_proj, be.add(q, W["att_b"])))
+        att = be.softmax(be.linear(v_norm, scores))
+        ctx = be.bmm_row(att, W["keys"])
+        y1, *new[1] = be.lstm_cell_stack("l1", be.cat([y0.view(1, H), ctx.view(1, H)], 1).view(-1), hs[1], cs[1], W["l1"], 1)
+        y2, *new[2] = be.lstm_cell_stack("l2", be.cat([y1.view(1, H), ctx.view(1, H)], 1).view(-1), hs[2], cs[2], W["l2"], 1)
+        r2 = be.add(y2, y1)
+        y3, *new[3] = be.lstm_cell_stack("l3", be.cat([r2.view(1, H), ctx.view(1, H)], 1).view(-1), hs[3], cs[3], W["l3"], 1)
+        r3 = be.add(y3, r2)
+        lgd = be.linear(r3, W["Wc"], W["bc"])
+        lg_buf.copy_(lgd)
+        ops.argmax(lgd.view(1, -1), out=tok)                                # the token stays on the device
+        for i in range(4):
+            hs[i].copy_(new[i][0])
+            cs[i].copy_(new[i][1])
+
+    def reset():
+        tok.fill_(bos)
+        for t in hs + cs:
+            t.zero_()
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # one eager step: handle creation and workspace growth happen outside capture
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    reset()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(steps):
+        g.replay()
+        toks_dev[t:t + 1].copy_(tok)       # device-to-device; no host synchronisation inside the loop
+        logits_dev[t].copy_(lg_buf)
+    e1.record()
+    torch.cuda.synchronize()
+    return toks_dev.cpu().tolist(), logits_dev.float().cpu(), e0.elapsed_time(e1) * 1e3
+
+
 # ------------------------------------------------------------------------------------ Transformer-style decoder
 def make_transformer(d, heads, ffn, V, layers, src_len, gen, gain=1.0):
     w = {"emb": torch.randn(V, d, generator=gen).half().float() * 0.3, "Wo": u((V, d), d, gen, gain),
