@@ -83,6 +83,9 @@ struct GraphBuilder {
         l->eps = eps;
         return add(l, {x});
     }
+    int64_t addEmbedding(int64_t table, int64_t idx) {
+        return add(std::make_shared<ir::AtenEmbeddingLayer>("aten::embedding"), {table, idx});
+    }
     int64_t addTanh(int64_t x) { return add(std::make_shared<ir::AtenTanhLayer>("aten::tanh"), {x}); }
     int64_t addMaskedFill(int64_t x, int64_t mask, double value) {
         auto l = std::make_shared<ir::AtenMaskedFillLayer>("aten::masked_fill");
@@ -182,6 +185,7 @@ PYBIND11_MODULE(_pimb200_host, m) {
         .def("add_layer_norm", &GraphBuilder::addLayerNorm, py::arg("x"), py::arg("normalized_shape"),
              py::arg("weight") = py::none(), py::arg("bias") = py::none(), py::arg("eps") = 1e-5)
         .def("add_tanh", &GraphBuilder::addTanh)
+        .def("add_embedding", &GraphBuilder::addEmbedding)
         .def("add_masked_fill", &GraphBuilder::addMaskedFill)
         .def("add_cat", &GraphBuilder::addCat, py::arg("list_id"), py::arg("dim"), py::arg("mem_layer_id") = -1)
         .def("add_copy", &GraphBuilder::addCopy)

@@ -23,7 +23,7 @@ enum class DataType { UNDEFINED, TENSOR, LIST, TUPLE, INT64, FLOAT64, BOOL, NONE
 
 enum class LayerType {
     ATENADD, ATENADDMM, ATENBMM, ATENCAT, ATENCOPY, ATENLINEAR, ATENLSTM1, ATENLSTM2, ATENMATMUL, MULTISTREAM,
-    ATENSOFTMAX, ATENLOGSOFTMAX, ATENARGMAX, ATENLAYERNORM, ATENTANH, ATENMASKEDFILL,
+    ATENSOFTMAX, ATENLOGSOFTMAX, ATENARGMAX, ATENLAYERNORM, ATENTANH, ATENMASKEDFILL, ATENEMBEDDING,
     PRIMINPUT, PRIMOUTPUT, PRIMCONSTANT, PRIMLISTCONSTRUCT
 };
 
@@ -45,6 +45,7 @@ inline const char* convertLayerTypeToString(LayerType t) {
         case LayerType::ATENLAYERNORM: return "aten::layer_norm";
         case LayerType::ATENTANH: return "aten::tanh";
         case LayerType::ATENMASKEDFILL: return "aten::masked_fill";
+        case LayerType::ATENEMBEDDING: return "aten::embedding";
         case LayerType::PRIMINPUT: return "prim::Input";
         case LayerType::PRIMOUTPUT: return "prim::Output";
         case LayerType::PRIMCONSTANT: return "prim::Constant";
@@ -208,6 +209,14 @@ class AtenMaskedFillLayer : public NNLayer {
    public:
     explicit AtenMaskedFillLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENMASKEDFILL) {}
     double value = 0.0;
+};
+
+// aten::embedding(weight, indices): the table is an input blob, or preloaded on the layer as the reference's
+// AtenEmbeddingLayer::getWeights allows
+class AtenEmbeddingLayer : public NNLayer {
+   public:
+    explicit AtenEmbeddingLayer(std::string name) : NNLayer(std::move(name), LayerType::ATENEMBEDDING) {}
+    at::Tensor weights;
 };
 
 class MultiStreamLayer : public NNLayer {

@@ -273,6 +273,28 @@ void executeAtenMaskedFill(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& 
     ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
 }
 
+// aten::embedding.  Indices that already live on the device are used there (the reference reads them back with
+// indices.item(), one host synchronisation per decoded token); host indices keep the libtorch call.
+void executeAtenEmbedding(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
+    auto emb = std::static_pointer_cast<ir::AtenEmbeddingLayer>(layer);
+    const auto& in = layer->getInSTensorID();
+    at::Tensor table = emb->weights.defined() ? emb->weights : blobTensor(ex, in[0]);
+    at::Tensor idx = blobTensor(ex, in[emb->weights.defined() ? 0 : 1]);
+    at::Tensor out;
+    if (table.is_cuda() && table.dim() == 2 && idx.is_cuda() && idx.scalar_type() == at::kLong && idx.numel() > 0) {
+        at::Tensor tc = table.contiguous(), ic = idx.contiguous();
+        auto sizes = ic.sizes().vec();
+        sizes.push_back(tc.size(1));
+        out = at::empty(sizes, tc.options());
+        ex.setStatus(pimb200_gather_rows(tc.data_ptr(), reinterpret_cast<const long long*>(ic.data_ptr<int64_t>()),
+                                         out.data_ptr(), (long)ic.numel(), (size_t)tc.size(1) * tc.element_size(),
+                                         (long)tc.size(0), ex.currentStream()));
+    } else {
+        out = at::embedding(table, idx.to(table.device()));
+    }
+    ex.updateBlob(layer->getOutSTensorID()[0], ir::DataType::TENSOR, torch::jit::IValue(out));
+}
+
 // x[1,1,k] . A[1,k,n] (the GNMT attention context) through the single-row kernel; anything else is at::bmm
 void executeAtenBmm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
     const auto& in = layer->getInSTensorID();

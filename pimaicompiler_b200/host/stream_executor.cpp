@@ -56,6 +56,7 @@ void StreamExecutor::registerOp() {
     reg(ir::LayerType::ATENLAYERNORM, executeAtenLayerNorm);
     reg(ir::LayerType::ATENTANH, executeAtenTanh);
     reg(ir::LayerType::ATENMASKEDFILL, executeAtenMaskedFill);
+    reg(ir::LayerType::ATENEMBEDDING, executeAtenEmbedding);
     // the one prim op graphs on this path cannot do without: gathers tensor blobs into a list blob
     reg(ir::LayerType::PRIMLISTCONSTRUCT, [](std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
         c10::List<at::Tensor> l;

@@ -89,6 +89,7 @@ void executeAtenArgmax(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stre
 void executeAtenLayerNorm(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenTanh(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenMaskedFill(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
+void executeAtenEmbedding(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenCat(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenCopy(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);
 void executeAtenLinear(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& stream_executor);

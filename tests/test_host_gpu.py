@@ -111,21 +111,25 @@ def test_decode_glue_executors_attention_and_classifier_tail():
     vec = h16(torch.randn(1, 512, generator=g))
     gamma, beta = h16(torch.rand(512, generator=g) + 0.5), h16(torch.randn(512, generator=g) * 0.1)
     logits = h16(torch.randn(1, 32320, generator=g) * 3.0)
+    table = h16(torch.randn(32320, 64, generator=g))
 
     def build(dev):
         gr = h.Graph()
-        i_s, i_m, i_v, i_l = gr.add_input(), gr.add_input(), gr.add_input(), gr.add_input()
+        i_s, i_m, i_v, i_l, i_t = gr.add_input(), gr.add_input(), gr.add_input(), gr.add_input(), gr.add_input()
         t = gr.add_tanh(i_s)
         f = gr.add_masked_fill(t, i_m, -65504.0)
         gr.mark_output(gr.add_softmax(f, -1))
         gr.mark_output(gr.add_layer_norm(i_v, [512], dev(gamma), dev(beta), 1e-5))
         gr.mark_output(gr.add_softmax(i_l, -1, log=True))
         gr.mark_output(gr.add_argmax(i_l, -1, keepdim=True))
+        am = gr.add_argmax(i_l, -1, keepdim=False)
+        gr.mark_output(gr.add_embedding(i_t, am))          # the chosen token's embedding row; the index stays on the device
         return h.NNRuntime(gr)
 
-    got = build(to_dev).inferenceModel([to_dev(scores), mask.cuda(), to_dev(vec), to_dev(logits)])
-    ref = build(lambda t: t).inferenceModel([scores, mask, vec, logits])
+    got = build(to_dev).inferenceModel([to_dev(scores), mask.cuda(), to_dev(vec), to_dev(logits), to_dev(table)])
+    ref = build(lambda t: t).inferenceModel([scores, mask, vec, logits, table])
     assert got[0].dtype == torch.float16 and got[3].dtype == torch.int64 and got[3].shape == (1, 1)
+    assert got[4].shape == (1, 64) and torch.equal(got[4].float().cpu(), ref[4])
     assert_close(got[0], ref[0], 1e-3, 1e-3, "tanh -> masked_fill -> softmax")
     assert_close(got[1], ref[1], 3e-3, 1e-3, "layer_norm")
     assert_close(got[2], ref[2], 8e-3, 1e-3, "log_softmax")
