@@ -460,7 +460,7 @@ def run_c4(args):
             "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
             "config": {"workload": "C4 decoder: GNMT-style greedy decode, V=32320 H=1024, 37 source states, 80 steps, 1 stream"},
             "op_by_op_us_per_token": eager_us, "device_resident_us_per_token": us_tok,
-            "roofline": {"bound": "hbm", "kernel": "one decode step (about 40 launches in one CUDA graph)",
+            "roofline": {"bound": "hbm", "kernel": "one decode step (about 25 dependent launches in one CUDA graph)",
                          "achieved": nbytes / us_tok / 1e3, "peak": peak, "unit": "GB/s",
                          "frac": nbytes / us_tok / 1e3 / peak, "peak_source": peak_src, "traffic": None},
             "gpu_launches": None}

@@ -76,11 +76,11 @@ class PimBackend:
     def put(self, t):
         return t.to(torch.float16).cuda().contiguous()
 
-    def linear(self, x, W, b=None, relu=False):
+    def linear(self, x, W, b=None, relu=False, out=None):
         o = self.ops
         if x.dim() == 1:
-            return o.gemv_mv(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE)
-        return o.gemm_wx(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE)
+            return o.gemv_mv(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE, out=out)
+        return o.gemm_wx(W, x.contiguous(), b, o.ACT_RELU if relu else o.ACT_NONE, out=out)
 
     def lstm_cell_stack(self, key, x, h, c, params, layers):
         if key not in self._lstm:
@@ -175,8 +175,8 @@ def gnmt_greedy(be, w, H, steps, bos=2, forced=None):
 
 def gnmt_greedy_graph(w, H, steps, bos=2):
     """The same decode with the whole step resident on the device: arg max writes the chosen token's int64 index into
-    device memory, the next step gathers its embedding row by that index, the recurrent states live in fixed buffers,
-    and the step (about 40 launches) is captured once in a CUDA graph and replayed.  Nothing is read back until the
+    device memory, the next step gathers its embedding row by that index, the recurrent states ping-pong between two
+    sets of fixed buffers, and the step (about 25 launches) is captured in two CUDA graphs replayed alternately.  Nothing is read back until the
     sentence is done, where the reference's interpreter synchronises at least once per token
     (aten_ops_executor.cpp:1276-1287).  Returns (token ids, logits [steps, V], the graph replays' device time in us)."""
     be = PimBackend()
@@ -186,51 +186,56 @@ def gnmt_greedy_graph(w, H, steps, bos=2):
     v_norm = be.put(w["att_v"] / w["att_v"].norm() * float(w["att_g"]))
     V = W["Wc"].shape[0]
     tok = torch.full((1,), bos, dtype=torch.int64, device="cuda")
-    hs = [torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)]
-    cs = [torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)]
-    lg_buf = torch.zeros(V, dtype=torch.float16, device="cuda")
+    # recurrent states ping-pong between two sets of buffers (an LSTM call must not write the state it reads), so the
+    # step exists as two graphs, one per direction
+    hs = [[torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)] for _ in range(2)]
+    cs = [[torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)] for _ in range(2)]
+    ys = [torch.zeros(1, 1, H, dtype=torch.float16, device="cuda") for _ in range(4)]
     toks_dev = torch.zeros(steps, dtype=torch.int64, device="cuda")
     logits_dev = torch.zeros(steps, V, dtype=torch.float16, device="cuda")
 
-    def step():
+    def cell(key, x, i, src, dst):
+        if key not in be._lstm:
+            p = W[key]
+            be._lstm[key] = ops.Lstm(p, 1, False, p[0].shape[1], p[1].shape[1], True)
+        be._lstm[key].forward(x.view(1, 1, -1), hs[src][i], cs[src][i], out=(ys[i], hs[dst][i], cs[dst][i]))
+        return ys[i].view(-1)
+
+    def step(src, dst, t_out):
         x = ops.gather_rows(W["emb"], tok).view(-1)                         # embedding lookup by a device-side index
-        new = [None] * 4
-        y0, *new[0] = be.lstm_cell_stack("l0", x, hs[0], cs[0], W["l0"], 1)
+        y0 = cell("l0", x, 0, src, dst)
         q = be.linear(y0, W["Wq"])
         scores = be.tanh(be.add(keys_proj, be.add(q, W["att_b"])))
         att = be.softmax(be.linear(v_norm, scores))
         ctx = be.bmm_row(att, W["keys"])
-        y1, *new[1] = be.lstm_cell_stack("l1", be.cat([y0.view(1, H), ctx.view(1, H)], 1).view(-1), hs[1], cs[1], W["l1"], 1)
-        y2, *new[2] = be.lstm_cell_stack("l2", be.cat([y1.view(1, H), ctx.view(1, H)], 1).view(-1), hs[2], cs[2], W["l2"], 1)
+        y1 = cell("l1", be.cat([y0.view(1, H), ctx.view(1, H)], 1).view(-1), 1, src, dst)
+        y2 = cell("l2", be.cat([y1.view(1, H), ctx.view(1, H)], 1).view(-1), 2, src, dst)
         r2 = be.add(y2, y1)
-        y3, *new[3] = be.lstm_cell_stack("l3", be.cat([r2.view(1, H), ctx.view(1, H)], 1).view(-1), hs[3], cs[3], W["l3"], 1)
+        y3 = cell("l3", be.cat([r2.view(1, H), ctx.view(1, H)], 1).view(-1), 3, src, dst)
         r3 = be.add(y3, r2)
-        lgd = be.linear(r3, W["Wc"], W["bc"])
-        lg_buf.copy_(lgd)
+        lgd = be.linear(r3, W["Wc"], W["bc"], out=t_out)
         ops.argmax(lgd.view(1, -1), out=tok)                                # the token stays on the device
-        for i in range(4):
-            hs[i].copy_(new[i][0])
-            cs[i].copy_(new[i][1])
 
-    def reset():
-        tok.fill_(bos)
-        for t in hs + cs:
-            t.zero_()
-
+    lg_buf = torch.zeros(V, dtype=torch.float16, device="cuda")
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):          # one eager step: handle creation and workspace growth happen outside capture
-        step()
+        step(0, 1, lg_buf)
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-        step()
-    reset()
+    graphs = []
+    for src in (0, 1):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step(src, 1 - src, lg_buf)
+        graphs.append(g)
+    tok.fill_(bos)
+    for t in hs[0] + cs[0]:
+        t.zero_()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for t in range(steps):
-        g.replay()
+        graphs[t & 1].replay()
         toks_dev[t:t + 1].copy_(tok)       # device-to-device; no host synchronisation inside the loop
         logits_dev[t].copy_(lg_buf)
     e1.record()
