@@ -50,6 +50,8 @@ struct GemmArgs {
     int tmem_cols;        // power of two >= max(32, 2 * bn): two accumulator stages
     int m_tiles, j_tiles; // tiles along the weight rows and along the activation rows
     int* status;          // device status word
+    int x_batch;          // > 0: X is [x_batch sequences][T steps][K] (batch-first) but the activation rows are numbered
+                          //      time-major, row = t * x_batch + b; map_x is then a 3-D map (K, b, t) and bn % x_batch == 0
 };
 
 // Persistent: CTA b works on tiles b, b + gridDim.x, ...; consecutive tile numbers share the activation (j) block, so the
@@ -102,13 +104,17 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             int issued = 0;  // k-blocks issued so far = position in the shared-memory ring
             for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x) {
                 const int m0 = (tile % a.m_tiles) * BM, j0 = (tile / a.m_tiles) * a.bn;
+                const int t0 = a.x_batch > 0 ? j0 / a.x_batch : 0;   // first timestep of the tile (once per tile)
                 for (int kb = 0; kb < kblocks; ++kb, ++issued) {
                     const int s = issued % STAGES;
                     const uint32_t it = (uint32_t)(issued / STAGES);
                     if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag)) { failed = true; break; }
                     mbar_expect_tx(full0 + 8 * s, stage_bytes);
                     tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_w, full0 + 8 * s, kb * BK, m0);
-                    tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, j0);
+                    if (a.x_batch > 0)   // bn / x_batch whole timesteps of all sequences, sequence index fastest
+                        tma_load_3d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, 0, t0);
+                    else
+                        tma_load_2d(smem_u32(sB + (size_t)s * B_STAGE_BYTES), &map_x, full0 + 8 * s, kb * BK, j0);
                 }
             }
             if (failed) {
@@ -255,9 +261,22 @@ static bool encode_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// returns PIMB200_ERR_UNSUPPORTED when the shape must take the SIMT kernel
+// X as [batch][steps][K] (row (b, t) at (b*steps + t) * ldx), tiles of box_t timesteps x all `batch` sequences
+static bool encode_x_time_major(CUtensorMap* map, const void* base, uint64_t batch, uint64_t steps, uint64_t cols,
+                                uint64_t ldx_bytes, uint32_t box_t) {
+    const cuuint64_t dims[3] = {cols, batch, steps};
+    const cuuint64_t strides[2] = {steps * ldx_bytes, ldx_bytes};
+    const cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)batch, box_t};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// returns PIMB200_ERR_UNSUPPORTED when the shape must take the SIMT kernel.  x_batch > 0: X is batch-first
+// [x_batch][J / x_batch][K] and the output rows are numbered time-major (row = t * x_batch + b).
 static int launch(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx, int ldy,
-                  int act, int y_is_f32, cudaStream_t st) {
+                  int act, int y_is_f32, cudaStream_t st, int x_batch) {
     if (K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
     int dev = 0;
     PIMB200_CUDA_TRY(cudaGetDevice(&dev));
@@ -279,6 +298,11 @@ static int launch(const __half* W, const __half* X, const __half* bias, void* Y,
     GemmArgs a;
     a.bias = bias; a.Y = Y; a.N = N; a.K = K; a.J = J; a.ldy = ldy; a.act = act; a.y_is_f32 = y_is_f32;
     a.bn = J >= BN_MAX ? BN_MAX : ((J + 15) / 16) * 16;
+    a.x_batch = 0;
+    if (x_batch > 0) {
+        if (J % x_batch != 0 || a.bn % x_batch != 0 || x_batch > 256) return PIMB200_ERR_UNSUPPORTED;
+        a.x_batch = x_batch;
+    }
     // two stages of bn columns; the epilogue reads 32 columns at a time, so the second stage needs its length rounded up
     const int need_cols = a.bn + ((a.bn + 31) / 32) * 32;
     a.tmem_cols = need_cols <= 32 ? 32 : (need_cols <= 64 ? 64 : (need_cols <= 128 ? 128 : 256));
@@ -287,7 +311,13 @@ static int launch(const __half* W, const __half* X, const __half* bias, void* Y,
     a.status = status;
     CUtensorMap map_w, map_x;
     if (!encode_2d(&map_w, W, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return PIMB200_ERR_UNSUPPORTED;
-    if (!encode_2d(&map_x, X, (uint64_t)J, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)a.bn)) return PIMB200_ERR_UNSUPPORTED;
+    if (a.x_batch > 0) {
+        if (!encode_x_time_major(&map_x, X, (uint64_t)x_batch, (uint64_t)(J / x_batch), (uint64_t)K, (uint64_t)ldx * 2,
+                                 (uint32_t)(a.bn / x_batch)))
+            return PIMB200_ERR_UNSUPPORTED;
+    } else if (!encode_2d(&map_x, X, (uint64_t)J, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)a.bn)) {
+        return PIMB200_ERR_UNSUPPORTED;
+    }
     const long tiles = (long)a.m_tiles * a.j_tiles;
     int sms = kNumSmB200;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -303,10 +333,19 @@ static int g_force_simt = 0;
 int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                    int ldy, int act, int y_is_f32, cudaStream_t st) {
     if (!g_force_simt) {
-        const int rc = tc::launch(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st);
+        const int rc = tc::launch(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st, 0);
         if (rc != PIMB200_ERR_UNSUPPORTED) return rc;
     }
     return launch_gemm_wx_simt(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st);
+}
+
+// Y[t * batch + b, :] = X[b, t, :] . W^T for a batch-first X [batch][J / batch][K]: the projection of a batch-first
+// sequence tensor written in time-major row order.  Tensor-core path only; PIMB200_ERR_UNSUPPORTED when the shape does
+// not allow it (the caller then projects in the input's own row order).
+int launch_gemm_wx_time_major(const __half* W, const __half* X, void* Y, int N, int K, int J, int ldx, int ldy, int batch,
+                              cudaStream_t st) {
+    if (g_force_simt || batch <= 0) return PIMB200_ERR_UNSUPPORTED;
+    return tc::launch(W, X, nullptr, Y, N, K, J, ldx, ldy, PIMB200_ACT_NONE, 1, st, batch);
 }
 
 }  // namespace pimb200

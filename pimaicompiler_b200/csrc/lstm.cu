@@ -32,6 +32,8 @@ int launch_gemm_wx_simt(const __half* W, const __half* X, const __half* bias, vo
                         int ldy, int act, int y_is_f32, cudaStream_t st);
 int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                    int ldy, int act, int y_is_f32, cudaStream_t st);
+int launch_gemm_wx_time_major(const __half* W, const __half* X, void* Y, int N, int K, int J, int ldx, int ldy, int batch,
+                              cudaStream_t st);
 }  // namespace pimb200
 
 using namespace pimb200;
@@ -1701,14 +1703,24 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
         }
         for (int d = 0; d < D; ++d) {
             const int ld = l * D + d;
-            rc = launch_gemm_wx(h->w_ih[ld], X, nullptr, h->G, 4 * H, Il, (int)rows, Il, 4 * H, PIMB200_ACT_NONE, 1,
-                                st);
+            // A batch-first input is projected into time-major rows when the tensor-core path allows it: the terms
+            // the recurrence needs in one step then sit side by side (with the input's own order the 64 sequences of
+            // a step lie megabytes apart, one page each, and the per-step loads miss the TLB)
+            long g_t = in_t, g_b = in_b;
+            rc = PIMB200_ERR_UNSUPPORTED;
+            if (first && batch_first && !packed && B > 1 && T > 1) {
+                rc = launch_gemm_wx_time_major(h->w_ih[ld], X, h->G, 4 * H, Il, (int)rows, Il, 4 * H, B, st);
+                if (rc == PIMB200_OK) { g_t = B; g_b = 1; }
+            }
+            if (rc == PIMB200_ERR_UNSUPPORTED)
+                rc = launch_gemm_wx(h->w_ih[ld], X, nullptr, h->G, 4 * H, Il, (int)rows, Il, 4 * H, PIMB200_ACT_NONE, 1,
+                                    st);
             if (rc != PIMB200_OK) return rc;
             const __half* h0_ld = h0 ? h0 + (size_t)ld * B * H : nullptr;
             const __half* c0_ld = c0 ? c0 + (size_t)ld * B * H : nullptr;
             __half* hn_ld = hn ? hn + (size_t)ld * B * H : nullptr;
             __half* cn_ld = cn ? cn + (size_t)ld * B * H : nullptr;
-            rc = run_recurrence(h, ld, sq, d == 1, h->G, in_t * 4 * H, in_b * 4 * H, h0_ld, c0_ld,
+            rc = run_recurrence(h, ld, sq, d == 1, h->G, g_t * 4 * H, g_b * 4 * H, h0_ld, c0_ld,
                                 Y + (size_t)d * H, out_t * (long)D * H, out_b * (long)D * H, hn_ld, cn_ld, st);
             if (rc != PIMB200_OK) return rc;
         }
