@@ -178,7 +178,7 @@ enum { PIMB200_LSTM_AUTO = 0, PIMB200_LSTM_STREAMED = 1, PIMB200_LSTM_PERSISTENT
 int pimb200_lstm_set_variant(pimb200_lstm* h, int variant);
 
 /* Forward pass, padded input:  x [T,B,I] (or [B,T,I] when batch_first), h0/c0 [L*D,B,H]
- * (NULL = zeros), y [T,B,D*H] (or [B,T,D*H]), hn/cn [L*D,B,H] (may be NULL).
+ * (NULL = zeros), y [T,B,D*H] (or [B,T,D*H]), hn/cn [L*D,B,H] (may be NULL).  Outputs must not overlap h0/c0.
  * Replaces atenLstm1 -> at::lstm (aten_ops.cpp:328-335) and executeMIOpenLSTM1's
  * miopenRNNForwardInference call (runtime/source/executor/op_executor/miopen_ops_executor.cpp:22-241).
  * y / hn / cn may point into slices of larger caller buffers (the reference's in-place
