@@ -792,8 +792,6 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                     mma_rows_smem(acc, Whh0, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half,
                                   h0buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
                     store_acc(part + (size_t)role * M * gl, gl, mt_w, acc, lane);
-                } else if (role == 2) {
-                    mma_rows_smem(acc2, Whh1, PH, mt_w, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
                 }
             }
             __syncthreads();
@@ -808,7 +806,15 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             }
             __syncthreads();
             scatter_state(h0buf, mask);
-            cluster.sync();
+            // the state product of layer 1 does not depend on the exchange in flight: it runs between the arrive and the
+            // wait of the cluster barrier
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            if (role == 2) {
+                const int n = lane >> 2;
+                const unsigned pn = (par >> n) & 1u;
+                mma_rows_smem(acc2, Whh1, PH, mt_w, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
+            }
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
             if (trp && tid == 0) trp[5] = clock64();
             // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias: role 0 takes the first K half, role 2 adds the
             //      second half to the product it already holds
