@@ -467,15 +467,44 @@ def run_c4(args):
     print(json.dumps(line), flush=True)
 
 
+def run_c5(args):
+    """C5 (decoder side): Transformer-base greedy decode, 6 decoder layers, d_model 512, 8 heads, FFN 2048, vocabulary
+    32000, 40 memory states, 64 steps with a KV cache, one sequence stream; op by op against the step resident on the
+    device (CUDA graph, token and position in device memory, in-place KV append)."""
+    from pimaicompiler_b200 import build
+    build.build()
+    from tests import decode_models as dm
+    d, heads, ffn, V, layers, S, steps = 512, 8, 2048, 32000, 6, 40, 64
+    w = dm.make_transformer(d, heads, ffn, V, layers, S, torch.Generator().manual_seed(5), 2.0)
+    be = dm.PimBackend()
+    dm.transformer_greedy(be, w, d, heads, 4)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    dm.transformer_greedy(be, w, d, heads, steps)
+    torch.cuda.synchronize()
+    eager_us = (time.perf_counter() - t0) * 1e6 / steps
+    best = None
+    for _ in range(max(1, args.steps)):
+        _, _, us = dm.transformer_greedy_graph(w, d, heads, steps)
+        best = us if best is None else min(best, us)
+    us_tok = best / steps
+    line = {"metric": "transformer_decode_us_per_token", "value": us_tok, "unit": "us", "n_gpus": 1, "steps": args.steps,
+            "warmup": 1, "ms_per_step": best / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "C5 decoder: Transformer-base greedy decode with KV cache, 6 layers d=512 V=32000, 64 steps, 1 stream"},
+            "op_by_op_us_per_token": eager_us, "device_resident_us_per_token": us_tok, "gpu_launches": None}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4"],
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4", "c5"],
                     help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm; "
-                         "c4 = GNMT-style decoder step, op by op against device-resident")
+                         "c4 / c5 = GNMT-style / Transformer-style decoder step, op by op against device-resident")
     ap.add_argument("--streams-per-gpu", type=int, default=128)
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -485,9 +514,9 @@ def main():
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed
         run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
-    if args.workload in ("c1", "c2", "c4"):
+    if args.workload in ("c1", "c2", "c4", "c5"):
         if int(os.environ.get("RANK", "0")) == 0:
-            {"c1": run_c1, "c2": run_c2, "c4": run_c4}[args.workload](args)
+            {"c1": run_c1, "c2": run_c2, "c4": run_c4, "c5": run_c5}[args.workload](args)
         return
     rank, world, local = dist_setup(args.gpus)
     try:

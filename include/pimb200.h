@@ -156,6 +156,13 @@ int pimb200_masked_fill_f16(const void* x, const unsigned char* mask, float valu
 int pimb200_gather_rows(const void* table, const long long* idx, void* out, long n_idx, size_t row_bytes, long n_table,
                         void* stream);
 
+/* table[idx[i], :] = src[i, :] for n_idx int64 row indices in DEVICE memory (indices outside [0, n_table) are skipped;
+ * equal indices race).  The in-place KV-cache append of a decode step at a position kept on the device: where the
+ * reference grows the cache with an at::cat per token (atenCat, aten_ops.cpp:97), the row goes into a pre-allocated
+ * [S_max, d] buffer. */
+int pimb200_scatter_rows(void* table, const long long* idx, const void* src, long n_idx, size_t row_bytes, long n_table,
+                         void* stream);
+
 typedef struct pimb200_lstm pimb200_lstm;
 
 /* One-time weight layout step.  params = the flat list at::lstm takes:

@@ -176,6 +176,22 @@ __global__ void gather_rows_kernel(const unsigned char* __restrict__ table, cons
     }
 }
 
+// table[idx[i], :] = src[i, :]: the write-side twin of the gather (a KV-cache append at a position that lives on the
+// device); an index outside [0, n_table) is skipped
+__global__ void scatter_rows_kernel(unsigned char* __restrict__ table, const long long* __restrict__ idx,
+                                    const unsigned char* __restrict__ src, size_t row_bytes, long n_table, int vec16) {
+    const long long r = idx[blockIdx.x];
+    if (r < 0 || r >= n_table) return;
+    unsigned char* dst = table + (size_t)r * row_bytes;
+    const unsigned char* s = src + (size_t)blockIdx.x * row_bytes;
+    if (vec16) {
+        for (size_t i = threadIdx.x; i < row_bytes / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+        for (size_t i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = s[i];
+    }
+}
+
 inline unsigned flat_grid(size_t n) {
     const size_t g = (n + 255) / 256;
     return (unsigned)(g > (size_t)kNumSmB200 * 8 ? (size_t)kNumSmB200 * 8 : (g ? g : 1));
@@ -273,5 +289,15 @@ extern "C" int pimb200_gather_rows(const void* table, const long long* idx, void
     const int vec16 = (row_bytes % 16 == 0 && aligned16(table) && aligned16(out)) ? 1 : 0;
     gather_rows_kernel<<<(unsigned)n_idx, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const unsigned char*>(table), idx, static_cast<unsigned char*>(out), row_bytes, n_table, vec16);
+    return launch_status();
+}
+
+extern "C" int pimb200_scatter_rows(void* table, const long long* idx, const void* src, long n_idx, size_t row_bytes,
+                                    long n_table, void* stream) {
+    if (n_idx == 0 || row_bytes == 0) return PIMB200_OK;
+    if (!table || !idx || !src || n_idx < 0 || n_idx > 0x7fffffffL || n_table <= 0) return PIMB200_ERR_BAD_ARG;
+    const int vec16 = (row_bytes % 16 == 0 && aligned16(table) && aligned16(src)) ? 1 : 0;
+    scatter_rows_kernel<<<(unsigned)n_idx, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<unsigned char*>(table), idx, static_cast<const unsigned char*>(src), row_bytes, n_table, vec16);
     return launch_status();
 }

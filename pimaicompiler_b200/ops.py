@@ -198,6 +198,19 @@ def gather_rows(table: torch.Tensor, idx: torch.Tensor, out: Optional[torch.Tens
     return y
 
 
+def scatter_rows(table: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> None:
+    """table[idx] = src for a device-resident int64 index tensor (in-place KV-cache append at a device-side position)."""
+    if not table.is_cuda or not table.is_contiguous() or table.dim() != 2:
+        raise TypeError("expected a contiguous 2-D CUDA table")
+    if idx.dtype != torch.int64 or not idx.is_cuda or not idx.is_contiguous():
+        raise TypeError("expected a contiguous CUDA int64 index tensor")
+    if src.dtype != table.dtype or not src.is_cuda or not src.is_contiguous() or src.numel() != idx.numel() * table.shape[1]:
+        raise TypeError("src must hold one row of the table's width and dtype per index")
+    check(_lib.lib().pimb200_scatter_rows(table.data_ptr(), idx.data_ptr(), src.data_ptr(), idx.numel(),
+                                          table.shape[1] * table.element_size(), table.shape[0], _stream()),
+          "scatter_rows")
+
+
 def tanh(x: torch.Tensor) -> torch.Tensor:
     _req_half_cuda(x)
     y = torch.empty_like(x)

@@ -300,3 +300,74 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
         toks.append(best)
         tok = best if forced is None else int(forced[t])
     return toks, torch.stack(logits)
+
+
+def transformer_greedy_graph(w, d, heads, steps, bos=1):
+    """The Transformer decode step resident on the device: token and position live in device memory (arg max writes the
+    token, the embedding is gathered by it, keys and values are appended in place at the device-side position into
+    pre-allocated [S_max, d] caches), self-attention runs over the whole cache with the positions after the current
+    one masked out, and the step is one CUDA graph replayed `steps` times.  Returns (token ids, logits, device us)."""
+    be = PimBackend()
+    ops = be.ops
+    P = be.put
+    emb, Wo, mem = P(w["emb"]), P(w["Wo"]), P(w["mem"])
+    Ls = [{k: P(v) for k, v in L.items()} for L in w["layers"]]
+    cross = [(be.linear(mem, L["ck"], L["ck_b"]), be.linear(mem, L["cv"], L["cv_b"])) for L in Ls]
+    S_max, V, hd = steps, Wo.shape[0], d // heads
+    kc = [torch.zeros(S_max, d, dtype=torch.float16, device="cuda") for _ in Ls]
+    vc = [torch.zeros(S_max, d, dtype=torch.float16, device="cuda") for _ in Ls]
+    tok = torch.full((1,), bos, dtype=torch.int64, device="cuda")
+    pos = torch.zeros(1, dtype=torch.int64, device="cuda")
+    ar = torch.arange(S_max, device="cuda")
+    lg_buf = torch.zeros(V, dtype=torch.float16, device="cuda")
+    toks_dev = torch.zeros(steps, dtype=torch.int64, device="cuda")
+    logits_dev = torch.zeros(steps, V, dtype=torch.float16, device="cuda")
+
+    def attend_cache(q, K, Vv, later):
+        qh = q.float().view(heads, 1, hd)
+        Kh = K.float().view(S_max, heads, hd).transpose(0, 1)
+        Vh = Vv.float().view(S_max, heads, hd).transpose(0, 1)
+        sc = (qh @ Kh.transpose(1, 2) / math.sqrt(hd)).to(torch.float16).view(heads, S_max).contiguous()
+        p = ops.softmax(ops.masked_fill(sc, later, -65504.0)).float().view(heads, 1, S_max)   # later positions: weight 0
+        return (p @ Vh).reshape(d)
+
+    def step():
+        x = ops.gather_rows(emb, tok).view(-1)
+        later = (ar > pos).contiguous()
+        for i, L in enumerate(Ls):
+            q = be.linear(x, L["sq"], L["sq_b"])
+            ops.scatter_rows(kc[i], pos, be.linear(x, L["sk"], L["sk_b"]).view(1, d))      # KV append in place
+            ops.scatter_rows(vc[i], pos, be.linear(x, L["sv"], L["sv_b"]).view(1, d))
+            a = attend_cache(q, kc[i], vc[i], later).to(torch.float16)
+            x = be.layer_norm(be.add(x, be.linear(a, L["so"], L["so_b"])))
+            cq = be.linear(x, L["cq"], L["cq_b"])
+            ca = _attend(be, cq, cross[i][0], cross[i][1], heads).to(torch.float16)
+            x = be.layer_norm(be.add(x, be.linear(ca, L["co"], L["co_b"])))
+            f = be.linear(be.linear(x, L["f1"], L["f1_b"], relu=True), L["f2"], L["f2_b"])
+            x = be.layer_norm(be.add(x, f))
+        lgd = be.linear(x, Wo, out=lg_buf)
+        ops.argmax(lgd.view(1, -1), out=tok)
+        pos.add_(1)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                              # eager once: workspaces and the split-K scratch exist before capture
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    tok.fill_(bos)
+    pos.zero_()
+    for c in kc + vc:
+        c.zero_()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(steps):
+        g.replay()
+        toks_dev[t:t + 1].copy_(tok)
+        logits_dev[t].copy_(lg_buf)
+    e1.record()
+    torch.cuda.synchronize()
+    return toks_dev.cpu().tolist(), logits_dev.float().cpu(), e0.elapsed_time(e1) * 1e3
