@@ -163,6 +163,17 @@ int pimb200_gather_rows(const void* table, const long long* idx, void* out, long
 int pimb200_scatter_rows(void* table, const long long* idx, const void* src, long n_idx, size_t row_bytes, long n_table,
                          void* stream);
 
+/* Single-query multi-head attention of a decode step over a key / value cache:
+ *     out[h, :] = softmax(scale * q[h, :] . K[0..L, h, :]^T) . V[0..L, h, :]   for each of `heads` heads,
+ * q / out [heads * head_dim] fp16, K / V rows of kv_stride elements holding the heads side by side, attended length
+ * L = (len_dev ? *len_dev : 0) + len_add clamped to [0, max_len]: len_dev is an int64 in DEVICE memory, so a step
+ * captured in a CUDA graph attends to a cache that grows between replays.  max_len <= 8192.
+ * Stands for the matmul -> (masked) softmax -> matmul group that the reference's Transformer graph executes as three
+ * libtorch calls with per-head reshapes in between (executeAtenMatmul aten_ops_executor.cpp:2488-2505,
+ * executeAtenSoftmax 3402-3436). */
+int pimb200_attention_row(const void* q, const void* K, const void* V, const long long* len_dev, long len_add,
+                          long max_len, void* out, int heads, int head_dim, long kv_stride, float scale, void* stream);
+
 typedef struct pimb200_lstm pimb200_lstm;
 
 /* One-time weight layout step.  params = the flat list at::lstm takes:

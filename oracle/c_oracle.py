@@ -95,6 +95,17 @@ def masked_fill(x, mask, value):
     return y
 
 
+def attention_row(q, K, V, heads, length=None, scale=None):
+    q, K, V = _c(q), _c(K), _c(V)
+    d = q.size
+    hd = d // heads
+    L = K.shape[0] if length is None else int(length)
+    out = np.empty(d, np.float32)
+    lib().oracle_attention_row(_f(q), _f(K), _f(V), C.c_long(L), _f(out), heads, hd, C.c_long(K.shape[1]),
+                               C.c_float(hd ** -0.5 if scale is None else scale))
+    return out
+
+
 def cat(arrays, dim):
     arrays = [np.ascontiguousarray(a) for a in arrays if a.size > 0]
     ref = arrays[0]

@@ -192,6 +192,59 @@ __global__ void scatter_rows_kernel(unsigned char* __restrict__ table, const lon
     }
 }
 
+// Single-query (decode-step) multi-head attention over a key / value cache: one CTA per head,
+//     out[h] = softmax(scale * q[h] . K[0..L)[h]^T) . V[0..L)[h],   L = *len_dev + len_add (or len_add when len_dev is NULL).
+// Scores live in shared memory (fp32), so L is limited by kAttnMaxLen.  Rows of K / V are kv_stride elements apart.
+constexpr int kAttnThreads = 128;
+constexpr int kAttnMaxLen = 8192;
+
+__global__ void __launch_bounds__(kAttnThreads) attention_row_kernel(const __half* __restrict__ q, const __half* __restrict__ K,
+                                                                     const __half* __restrict__ V, const long long* len_dev,
+                                                                     long len_add, long max_len, __half* __restrict__ out,
+                                                                     int hd, long kv_stride, float scale) {
+    extern __shared__ float sc[];            // [L] scores, then [kAttnThreads / 32][hd] partial outputs
+    __shared__ float red[kAttnThreads / 32];
+    const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long L = (len_dev ? (long)*len_dev : 0) + len_add;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
+    const __half* qh = q + (size_t)h * hd;
+    // scores: a warp per cache row, lanes along the head dimension
+    for (long t = warp; t < L; t += kAttnThreads / 32) {
+        const __half* kr = K + (size_t)t * kv_stride + (size_t)h * hd;
+        float a = 0.f;
+        for (int j = lane; j < hd; j += 32) a = fmaf(__half2float(qh[j]), __half2float(kr[j]), a);
+        a = warp_sum(a);
+        if (lane == 0) sc[t] = a * scale;
+    }
+    __syncthreads();
+    float m = -CUDART_INF_F;
+    for (long t = threadIdx.x; t < L; t += kAttnThreads) m = fmaxf(m, sc[t]);
+    m = block_max<kAttnThreads>(m, red);
+    float s = 0.f;
+    for (long t = threadIdx.x; t < L; t += kAttnThreads) {
+        const float e = expf(sc[t] - m);
+        sc[t] = e;
+        s += e;
+    }
+    s = block_sum<kAttnThreads>(s, red);   // ends with a barrier: every sc[t] is final
+    const float inv = L > 0 ? 1.0f / s : 0.f;
+    // weighted sum: warp w takes rows w, w+4, ...; lanes along the head dimension; partials meet in shared memory
+    float* part = sc + max_len;
+    for (int j = lane; j < hd; j += 32) {
+        float a = 0.f;
+        for (long t = warp; t < L; t += kAttnThreads / 32)
+            a = fmaf(sc[t], __half2float(V[(size_t)t * kv_stride + (size_t)h * hd + j]), a);
+        part[warp * hd + j] = a;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < hd; j += kAttnThreads) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnThreads / 32; ++w) a += part[w * hd + j];
+        out[(size_t)h * hd + j] = __float2half_rn(a * inv);
+    }
+}
+
 inline unsigned flat_grid(size_t n) {
     const size_t g = (n + 255) / 256;
     return (unsigned)(g > (size_t)kNumSmB200 * 8 ? (size_t)kNumSmB200 * 8 : (g ? g : 1));
@@ -299,5 +352,18 @@ extern "C" int pimb200_scatter_rows(void* table, const long long* idx, const voi
     const int vec16 = (row_bytes % 16 == 0 && aligned16(table) && aligned16(src)) ? 1 : 0;
     scatter_rows_kernel<<<(unsigned)n_idx, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<unsigned char*>(table), idx, static_cast<const unsigned char*>(src), row_bytes, n_table, vec16);
+    return launch_status();
+}
+
+extern "C" int pimb200_attention_row(const void* q, const void* K, const void* V, const long long* len_dev, long len_add,
+                                     long max_len, void* out, int heads, int head_dim, long kv_stride, float scale,
+                                     void* stream) {
+    if (!q || !K || !V || !out || heads <= 0 || head_dim <= 0 || max_len <= 0 || kv_stride < (long)heads * head_dim)
+        return PIMB200_ERR_BAD_ARG;
+    if (max_len > kAttnMaxLen || head_dim > 1024) return PIMB200_ERR_UNSUPPORTED;
+    const size_t smem = ((size_t)max_len + (size_t)(kAttnThreads / 32) * head_dim) * sizeof(float);
+    attention_row_kernel<<<(unsigned)heads, kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_add,
+        max_len, static_cast<__half*>(out), head_dim, kv_stride, scale);
     return launch_status();
 }

@@ -211,6 +211,27 @@ def scatter_rows(table: torch.Tensor, idx: torch.Tensor, src: torch.Tensor) -> N
           "scatter_rows")
 
 
+def attention_row(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int, length: Optional[int] = None,
+                  length_dev: Optional[torch.Tensor] = None, length_add: int = 0, scale: Optional[float] = None,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-query multi-head attention over the first L rows of the caches K, V [S, d]: L = `length`, or
+    `length_dev` (int64 on the device) + `length_add`."""
+    _req_half_cuda(q, K, V)
+    d = q.numel()
+    hd = d // heads
+    if K.shape != V.shape or K.shape[1] != d:
+        raise ValueError("K and V must be [S, heads * head_dim]")
+    if length_dev is not None and (length_dev.dtype != torch.int64 or not length_dev.is_cuda):
+        raise TypeError("length_dev must be a CUDA int64 tensor")
+    y = out if out is not None else torch.empty(d, dtype=torch.float16, device=q.device)
+    add = length_add if length_dev is not None else (K.shape[0] if length is None else int(length))
+    check(_lib.lib().pimb200_attention_row(_ptr(q), _ptr(K), _ptr(V), None if length_dev is None else length_dev.data_ptr(),
+                                           add, K.shape[0], _ptr(y), heads, hd, K.stride(0),
+                                           float(scale if scale is not None else hd ** -0.5), _stream()),
+          "attention_row")
+    return y
+
+
 def tanh(x: torch.Tensor) -> torch.Tensor:
     _req_half_cuda(x)
     y = torch.empty_like(x)

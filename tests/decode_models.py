@@ -4,8 +4,8 @@ model code runs on the libtorch-CPU oracle (fp32) and on the device ops of this 
 Random-init weights of the benchmark's architectures (C4: 4-layer LSTM decoder with normalised Bahdanau attention and a
 vocabulary projection; C5: Transformer decoder layers with a KV cache); the corpora and checkpoints are not available
 offline.  The hot ops (lstm with seq_len 1, batch-1 linear with fused ReLU, fp16 add, single-row bmm, cat / KV append)
-and the row-wise glue around them (tanh, softmax, layer norm, arg max) go through the backend; only the per-head
-reshapes and the two small batched products of multi-head attention stay with torch on either side.
+and the glue around them (tanh, softmax, layer norm, arg max, single-query multi-head attention) go through the
+backend.
 """
 from __future__ import annotations
 
@@ -49,6 +49,15 @@ class CpuBackend:
     def kv_append(self, cache, t, row):
         # the reference's form: the cache grows by an at::cat per step
         return torch.cat([cache, row.view(1, -1)], 0) if cache.shape[0] else row.view(1, -1).clone()
+
+    def attend(self, q, K, Vv, heads):
+        # per-head scaled dot-product attention of one query over K / V [t, d]: matmul -> softmax -> matmul
+        d = q.numel()
+        hd = d // heads
+        qh = q.view(heads, 1, hd)
+        Kh = K.view(-1, heads, hd).transpose(0, 1)
+        Vh = Vv.view(-1, heads, hd).transpose(0, 1)
+        return (torch.softmax(qh @ Kh.transpose(1, 2) / math.sqrt(hd), -1) @ Vh).reshape(d)
 
     def tanh(self, x):
         return torch.tanh(x)
@@ -112,6 +121,9 @@ class PimBackend:
         view = buf[: t + 1]
         self._kv_full[id(view)] = buf
         return view
+
+    def attend(self, q, K, Vv, heads):
+        return self.ops.attention_row(q.contiguous(), K.contiguous(), Vv.contiguous(), heads)
 
     def tanh(self, x):
         return self.ops.tanh(x.contiguous())
@@ -258,18 +270,6 @@ def make_transformer(d, heads, ffn, V, layers, src_len, gen, gain=1.0):
     return w
 
 
-def _attend(be, q, K, Vv, heads):
-    """q [d], K/V [t, d] -> [d]; per-head scaled dot-product attention: the two small batched products stay with torch
-    on either side, the softmax over each head's scores goes through the backend."""
-    d = q.numel()
-    hd = d // heads
-    qh = q.float().view(heads, 1, hd)
-    Kh = K.float().view(-1, heads, hd).transpose(0, 1)
-    Vh = Vv.float().view(-1, heads, hd).transpose(0, 1)
-    p = be.softmax((qh @ Kh.transpose(1, 2) / math.sqrt(hd)).to(be.dtype)).float()
-    return (p @ Vh).reshape(d)
-
-
 def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
     ln = be.layer_norm
     P = lambda t: be.put(t)
@@ -287,10 +287,10 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
             v = be.linear(x, L["sv"], L["sv_b"])
             kcache[i] = be.kv_append(kcache[i], t, k)      # KV append
             vcache[i] = be.kv_append(vcache[i], t, v)
-            a = _attend(be, q, kcache[i], vcache[i], heads).to(be.dtype)
+            a = be.attend(q, kcache[i], vcache[i], heads)
             x = ln(be.add(x, be.linear(a, L["so"], L["so_b"])))
             cq = be.linear(x, L["cq"], L["cq_b"])
-            ca = _attend(be, cq, cross[i][0], cross[i][1], heads).to(be.dtype)
+            ca = be.attend(cq, cross[i][0], cross[i][1], heads)
             x = ln(be.add(x, be.linear(ca, L["co"], L["co_b"])))
             f = be.linear(be.linear(x, L["f1"], L["f1_b"], relu=True), L["f2"], L["f2_b"])
             x = ln(be.add(x, f))
@@ -305,43 +305,33 @@ def transformer_greedy(be, w, d, heads, steps, bos=1, forced=None):
 def transformer_greedy_graph(w, d, heads, steps, bos=1):
     """The Transformer decode step resident on the device: token and position live in device memory (arg max writes the
     token, the embedding is gathered by it, keys and values are appended in place at the device-side position into
-    pre-allocated [S_max, d] caches), self-attention runs over the whole cache with the positions after the current
-    one masked out, and the step is one CUDA graph replayed `steps` times.  Returns (token ids, logits, device us)."""
+    pre-allocated [S_max, d] caches), self-attention reads the attended length from the device-side position, and the
+    step is one CUDA graph replayed `steps` times.  Returns (token ids, logits, device us)."""
     be = PimBackend()
     ops = be.ops
     P = be.put
     emb, Wo, mem = P(w["emb"]), P(w["Wo"]), P(w["mem"])
     Ls = [{k: P(v) for k, v in L.items()} for L in w["layers"]]
     cross = [(be.linear(mem, L["ck"], L["ck_b"]), be.linear(mem, L["cv"], L["cv_b"])) for L in Ls]
-    S_max, V, hd = steps, Wo.shape[0], d // heads
+    S_max, V = steps, Wo.shape[0]
     kc = [torch.zeros(S_max, d, dtype=torch.float16, device="cuda") for _ in Ls]
     vc = [torch.zeros(S_max, d, dtype=torch.float16, device="cuda") for _ in Ls]
     tok = torch.full((1,), bos, dtype=torch.int64, device="cuda")
     pos = torch.zeros(1, dtype=torch.int64, device="cuda")
-    ar = torch.arange(S_max, device="cuda")
     lg_buf = torch.zeros(V, dtype=torch.float16, device="cuda")
     toks_dev = torch.zeros(steps, dtype=torch.int64, device="cuda")
     logits_dev = torch.zeros(steps, V, dtype=torch.float16, device="cuda")
 
-    def attend_cache(q, K, Vv, later):
-        qh = q.float().view(heads, 1, hd)
-        Kh = K.float().view(S_max, heads, hd).transpose(0, 1)
-        Vh = Vv.float().view(S_max, heads, hd).transpose(0, 1)
-        sc = (qh @ Kh.transpose(1, 2) / math.sqrt(hd)).to(torch.float16).view(heads, S_max).contiguous()
-        p = ops.softmax(ops.masked_fill(sc, later, -65504.0)).float().view(heads, 1, S_max)   # later positions: weight 0
-        return (p @ Vh).reshape(d)
-
     def step():
         x = ops.gather_rows(emb, tok).view(-1)
-        later = (ar > pos).contiguous()
         for i, L in enumerate(Ls):
             q = be.linear(x, L["sq"], L["sq_b"])
             ops.scatter_rows(kc[i], pos, be.linear(x, L["sk"], L["sk_b"]).view(1, d))      # KV append in place
             ops.scatter_rows(vc[i], pos, be.linear(x, L["sv"], L["sv_b"]).view(1, d))
-            a = attend_cache(q, kc[i], vc[i], later).to(torch.float16)
+            a = ops.attention_row(q, kc[i], vc[i], heads, length_dev=pos, length_add=1)   # entries 0..pos
             x = be.layer_norm(be.add(x, be.linear(a, L["so"], L["so_b"])))
             cq = be.linear(x, L["cq"], L["cq_b"])
-            ca = _attend(be, cq, cross[i][0], cross[i][1], heads).to(torch.float16)
+            ca = be.attend(cq, cross[i][0], cross[i][1], heads)
             x = be.layer_norm(be.add(x, be.linear(ca, L["co"], L["co_b"])))
             f = be.linear(be.linear(x, L["f1"], L["f1_b"], relu=True), L["f2"], L["f2_b"])
             x = be.layer_norm(be.add(x, f))

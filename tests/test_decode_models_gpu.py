@@ -71,9 +71,8 @@ def test_gather_rows_by_device_index():
 @pytest.mark.parametrize("d,heads,ffn,V,layers,S,steps", [(64, 4, 128, 300, 2, 9, 10), (512, 8, 2048, 32000, 6, 40, 8)])
 def test_transformer_device_resident_step_matches_eager(d, heads, ffn, V, layers, S, steps):
     # the step as one replayed CUDA graph: token and position stay on the device, keys / values are appended in place
-    # by a device-side index, self-attention runs over the whole pre-allocated cache with later positions masked.
-    # Same kernels as the op-by-op decode; only the softmax rows are longer (masked entries weigh exactly zero), so the
-    # logits agree to fp16 rounding and the tokens are equal
+    # by a device-side index, self-attention takes its length from the device-side position.  Same kernels, same
+    # inputs as the op-by-op decode
     gen = torch.Generator().manual_seed(d + S)
     w = dm.make_transformer(d, heads, ffn, V, layers, S, gen, 2.0)
     toks, logits = dm.transformer_greedy(dm.PimBackend(), w, d, heads, steps)

@@ -110,3 +110,15 @@ def test_oracle_rowops_match_libtorch_golden():
     mx = z["mf_x"].astype(np.float32)
     assert np.array_equal(co.masked_fill(mx, z["mf_mask"], -65504.0), z["mf_y"])
     assert np.array_equal(co.masked_fill(mx, z["mf_row_mask"], 0.25), z["mf_y_row"])
+
+
+@pytest.mark.parametrize("heads,hd,S,L", [(8, 64, 40, 40), (4, 16, 9, 5), (1, 32, 3, 1)])
+def test_oracle_attention_row_matches_libtorch(heads, hd, S, L):
+    g = torch.Generator().manual_seed(heads * 100 + S)
+    d = heads * hd
+    q, K, V = (torch.randn(*s, generator=g) for s in ((d,), (S, d), (S, d)))
+    qh = q.view(heads, 1, hd)
+    Kh = K[:L].view(L, heads, hd).transpose(0, 1)
+    Vh = V[:L].view(L, heads, hd).transpose(0, 1)
+    ref = (torch.softmax(qh @ Kh.transpose(1, 2) / hd ** 0.5, -1) @ Vh).reshape(d)
+    np.testing.assert_allclose(co.attention_row(q.numpy(), K.numpy(), V.numpy(), heads, L), ref.numpy(), atol=2e-6, rtol=1e-5)

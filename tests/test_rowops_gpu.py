@@ -119,3 +119,20 @@ def test_rowops_empty_and_bad_arguments():
     assert lib.pimb200_argmax_rows(x.data_ptr(), None, 4, 8, None) == _lib.ERR_BAD_ARG
     m = torch.zeros(5, dtype=torch.bool, device="cuda")
     assert lib.pimb200_masked_fill_f16(x.data_ptr(), m.data_ptr(), 0.0, x.data_ptr(), 32, 5, None) == _lib.ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("heads,hd,S,L", [(8, 64, 64, 64), (8, 64, 64, 1), (4, 16, 9, 5), (2, 40, 300, 257), (1, 8, 3, 0)])
+def test_attention_row_matches_oracle(heads, hd, S, L):
+    # decode-step attention over a key / value cache, host-side and device-side length
+    ops = _ops()
+    g = torch.Generator().manual_seed(heads * 1000 + S + L)
+    d = heads * hd
+    q = torch.randn(d, generator=g).to(torch.float16)
+    K = torch.randn(S, d, generator=g).to(torch.float16)
+    V = torch.randn(S, d, generator=g).to(torch.float16)
+    ref = co.attention_row(q.float().numpy(), K.float().numpy(), V.float().numpy(), heads, L)
+    got = ops.attention_row(q.cuda(), K.cuda(), V.cuda(), heads, length=L).float().cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=RTOL, atol=2e-3)
+    pos = torch.tensor([L - 1], dtype=torch.int64, device="cuda")     # entries 0..pos are valid
+    got_dev = ops.attention_row(q.cuda(), K.cuda(), V.cuda(), heads, length_dev=pos, length_add=1).float().cpu().numpy()
+    assert np.array_equal(got_dev, got)
