@@ -231,3 +231,32 @@ def test_tcgen05_recurrence_variant_matches_oracle(T, B, I, H):
     assert m.last_status() == 0
     for name, a, b in zip(("y", "hn", "cn"), got, ref):
         assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"tcgen05 recurrence {name}")
+
+
+def test_lstm_benchmark_shape_batched_properties():
+    # the benchmark's pre-net shape at full size: 64 sequences x 1000 steps, batch-first (the projection is then written
+    # time-major through the 3-D tensor map).  Size-independent properties instead of an oracle run:
+    #   * the persistent kernel agrees with the streamed one (different kernels, different summation order);
+    #   * a repeat is bit-identical;
+    #   * every sequence is computed independently of its batch: sequence n alone reproduces row n bit for bit
+    ops = _ops()
+    g = torch.Generator().manual_seed(64)
+    T, B, I, H, L = 1000, 64, 240, 1024, 2
+    ps = [to_dev(p) for p in lstm_params(L, 1, I, H, g, scale=1 / 32)]
+    x = to_dev(h16(torch.randn(B, T, I, generator=g)))
+    m = ops.Lstm(ps, L, False, I, H, True)
+    m.set_variant(ops.LSTM_PERSISTENT)
+    y, hn, cn = m.forward(x, batch_first=True)
+    y2, hn2, cn2 = m.forward(x, batch_first=True)
+    torch.cuda.synchronize()
+    assert m.last_status() == 0
+    assert torch.equal(y, y2) and torch.equal(hn, hn2) and torch.equal(cn, cn2)
+    assert torch.isfinite(y.float()).all()
+    m.set_variant(ops.LSTM_STREAMED)
+    ys, hns, cns = m.forward(x, batch_first=True)
+    assert_close(y, ys, LSTM_ATOL, LSTM_RTOL, "persistent vs streamed y at T=1000, B=64")
+    assert_close(cn, cns, LSTM_ATOL, LSTM_RTOL, "persistent vs streamed c_n")
+    m.set_variant(ops.LSTM_PERSISTENT)
+    for n in (0, 37, 63):
+        y1, hn1, cn1 = m.forward(x[n:n + 1].contiguous(), batch_first=True)
+        assert torch.equal(y1[0], y[n]) and torch.equal(hn1[:, 0], hn[:, n]) and torch.equal(cn1[:, 0], cn[:, n])
