@@ -2,12 +2,13 @@
 """Benchmark of the hot path: RNN-T greedy decode of synthetic 10 s utterances (1000 frames x 240
 features, batch 1 per stream, random-init weights of the benchmark architecture).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--streams-per-gpu S] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--streams-total S] [--impl reference]
 
-One "step" = every rank decodes S utterances (S = 128, so N = 8 is the 1024-stream configuration).
-Utterances are independent, so ranks share nothing on the data path ("weak" scaling, no collective);
-torch.distributed is used only for the barrier and the max-over-ranks of the device time.
-Prints ONE JSON line on rank 0.
+One "step" = the benchmark configuration's 1024 utterance streams, sharded over the N ranks (1024 / N per rank,
+decoded in calls of 128 utterances).  Utterances are independent, so ranks share nothing on the data path
+("strong" scaling: the total is fixed; no collective); torch.distributed is used only for the barrier and the
+max-over-ranks of the device time.  The same line carries the stand-alone LSTM (C1) and GEMV (C2) figures of the
+baseline metric under the keys `lstm_c1` and `gemv`.  Prints ONE JSON line on rank 0.
 """
 from __future__ import annotations
 
@@ -27,7 +28,29 @@ sys.path.insert(0, ROOT)
 
 T_FRAMES = 1000
 TRAFFIC_T1000 = 1.18e9   # bytes, lstm_persistent_wide_kernel<8>, T=1000, 64 sequences (ncu dram read+write)
-WORKLOAD = "C3: RNN-T greedy decode, 1000x240 frames per utterance, batch 1 per stream"
+WORKLOAD = "C3: RNN-T greedy decode, 1000x240 frames per utterance, batch 1 per stream, 1024 streams"
+STREAMS_TOTAL = 1024
+TENSOR_PIPE_ACTIVE_PCT_NCU = None   # sm__pipe_tensor_cycles_active of the recurrence kernel, from profiles/ (set below)
+
+
+def base_config(streams_total: int) -> dict:
+    """The workload description both arms print (identical keys and values)."""
+    return {"workload": WORKLOAD, "frames": T_FRAMES, "streams_total": streams_total,
+            "parallelism": "independent utterance streams sharded over the ranks, no collective",
+            "l2": "GPU arm: 256 MB flush write between timed steps; the per-step working set (90.6 MB weights + "
+                  "features + activations) also exceeds the 126 MB L2"}
+
+
+RECURRENCE_KERNEL = "lstm_persistent_wide_kernel<8> (W_hh recurrence, all T steps of 64 sequences per launch)"
+
+
+def load_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), "measured burst (MEASURED_PEAKS.json)"
+    return 1590.0, "fallback"
 
 
 def load_peaks():
@@ -141,9 +164,10 @@ def run_reference(args, rank, world):
     line = {
         "impl": "reference", "metric": "rnnt_greedy_utterances_per_s", "value": value, "unit": "utt/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": secs / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": secs / max(args.steps, 1) * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames": T_FRAMES, "streams_per_step": n},
+        "config": base_config(args.streams_total),
+        "sample_streams_per_step": n,
         "cpu_baseline": {"value": value, "unit": "utt/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "utt/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -170,11 +194,15 @@ def run_gpu(args, rank, world, local):
                       d(w.w1), d(w.b1), d(w.w2), d(w.b2))
     if args.encoder_batch:
         dec.set_encoder_batch(args.encoder_batch)
-    S = args.streams_per_gpu
+    # this rank's shard of the configuration's streams, decoded in calls of `chunk` utterances
+    streams_total = args.streams_per_gpu * world if args.streams_per_gpu else args.streams_total
+    S = (streams_total + world - 1) // world
+    chunk = min(args.streams_per_call, S)
     Tp = T_FRAMES // cfg.stack_factor
     g = torch.Generator().manual_seed(1000 + rank)
     feats_host = torch.randn(S, T_FRAMES, cfg.feat_dim, generator=g).to(torch.float16).pin_memory()
     feats = feats_host.to(dev)
+    feats_stage = torch.empty(chunk, T_FRAMES, cfg.feat_dim, dtype=torch.float16, device=dev)
     tokens = torch.zeros(S, Tp, dtype=torch.int32, device=dev)
     n_tokens = torch.zeros(S, dtype=torch.int32, device=dev)
     tokens_host = torch.zeros(S, Tp, dtype=torch.int32).pin_memory()
@@ -182,18 +210,25 @@ def run_gpu(args, rank, world, local):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
 
     def step_device():
-        dec.decode_into(feats, tokens, n_tokens, None)
+        for c in range(0, S, chunk):
+            e = min(c + chunk, S)
+            dec.decode_into(feats[c:e], tokens[c:e], n_tokens[c:e], None)
 
     def step_e2e():
-        f = feats_host.to(dev, non_blocking=True)
-        dec.decode_into(f, tokens, n_tokens, None)
-        tokens_host.copy_(tokens, non_blocking=True)
-        n_tokens_host.copy_(n_tokens, non_blocking=True)
+        # host features in, token ids out, per call of `chunk` utterances
+        for c in range(0, S, chunk):
+            e = min(c + chunk, S)
+            f = feats_stage[: e - c]
+            f.copy_(feats_host[c:e], non_blocking=True)
+            dec.decode_into(f, tokens[c:e], n_tokens[c:e], None)
+            tokens_host[c:e].copy_(tokens[c:e], non_blocking=True)
+            n_tokens_host[c:e].copy_(n_tokens[c:e], non_blocking=True)
         torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
         step_device()
     torch.cuda.synchronize()
+    dec.check_status("warm-up decode")
 
     # ---- device-resident throughput: K steps, each bracketed by CUDA events, L2 flushed between steps
     sampler = ClockSampler(local)
@@ -213,6 +248,7 @@ def run_gpu(args, rank, world, local):
     step_ms = [a.elapsed_time(b) for a, b in ev]
     prof = dec.profile_read()
     dec.profile(False)
+    dec.check_status("timed decode")
     total_ms = max_over_ranks(sum(step_ms), world)
     clocks = sampler.stop() if rank == 0 else {}
 
@@ -237,6 +273,7 @@ def run_gpu(args, rank, world, local):
         step_e2e()
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
+    dec.check_status("end-to-end decode")
 
     utts_total = S * world * args.steps
     value = utts_total / (total_ms * 1e-3)
@@ -244,38 +281,47 @@ def run_gpu(args, rank, world, local):
 
     # ---- roofline of the dominant kernel (the LSTM recurrence), timed live with CUDA events
     peak, peak_src = load_peaks()
+    tpeak, tpeak_src = load_tensor_peak()
     rec_s = prof["ms"] * 1e-3
     achieved = prof["bytes"] / rec_s / 1e9 if rec_s > 0 else 0.0
     share = prof["ms"] / sum(step_ms) if sum(step_ms) > 0 else 0.0
-    # per group of encoder-batch utterances: (projection GEMM + recurrence) per LSTM layer and the joint's encoder-half
-    # GEMM; then one greedy kernel for the whole call
-    eb = args.encoder_batch or 64
-    launches_per_step = ((S + eb - 1) // eb) * (2 * (cfg.pre_layers + cfg.post_layers) + 1) + 1
+    eb = min(args.encoder_batch or 64, chunk)
+    # the same launches as a contraction: 2 flop per weight element and sequence and timestep
+    flops = prof["bytes"] / 2.0 * 2.0 * eb
+    tflops = flops / rec_s / 1e12 if rec_s > 0 else 0.0
+    # per call of `chunk` utterances: per group of encoder-batch utterances (projection GEMM + recurrence) per LSTM
+    # layer and the joint's encoder-half GEMM; then one greedy kernel for the whole call
+    calls = (S + chunk - 1) // chunk
+    launches_per_step = calls * (((chunk + eb - 1) // eb) * (2 * (cfg.pre_layers + cfg.post_layers) + 1) + 1)
 
+    extras = {}
+    if rank == 0 and not args.no_extras:
+        del feats, flush
+        torch.cuda.empty_cache()
+        extras["lstm_c1"] = measure_c1(max(args.steps, 3))["persistent"]
+        extras["gemv"] = measure_c2(max(args.steps, 3), batches=(32,), shapes_batched=((4096, 1024),), rowops=False)["results"]
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
         v, dt, cores = cpu_rnnt_throughput(args.cpu_sample, 7000)
         cpu = {"value": v, "unit": "utt/s", "cores": cores, "kind": "port",
                "sample": f"{args.cpu_sample} of the same synthetic utterances, libtorch {torch.__version__} CPU fp32 "
                          f"(the at::lstm/at::linear calls of the reference's default executors), {dt:.1f} s"}
+    barrier(world)
     if rank != 0:
         return
     line = {
         "metric": "rnnt_greedy_utterances_per_s", "value": value, "unit": "utt/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "frames": T_FRAMES, "streams_per_gpu": S, "streams_total": S * world,
-                   "parallelism": f"replicas x{world}, no collective",
-                   "l2": "256 MB flush write between timed steps; per-step working set (90.6 MB weights + "
-                         f"{S * T_FRAMES * cfg.feat_dim * 2 / 1e6:.0f} MB features + activations) also exceeds L2",
-                   "greedy_kernel": dec.info()},
+        "config": base_config(S * world),
+        "streams_per_gpu": S, "streams_per_call": chunk, "greedy_kernel": dec.info(),
         "p50_ms_per_utt": p50_ms,
         "e2e": {"value": e2e_value, "unit": "utt/s",
                 "h2d_bytes_per_step": int(feats_host.numel() * 2),
                 "d2h_bytes_per_step": int(tokens_host.numel() * 4 + n_tokens_host.numel() * 4)},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "lstm_persistent_wide_kernel<8> (W_hh recurrence, all T steps of 64 sequences per launch)",
+        "roofline": {"bound": "hbm", "kernel": RECURRENCE_KERNEL,
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src,
                      # dram__bytes_read+write of one T=1000 launch from the committed ncu capture under profiles/
@@ -283,14 +329,21 @@ def run_gpu(args, rank, world, local):
                      # bytes are 8.39e9
                      "traffic": TRAFFIC_T1000,
                      "launches": prof["recurrences"], "avg_launch_ms": prof["ms"] / max(prof["recurrences"], 1),
-                     "sequences_per_launch": min(eb, S),
+                     "us_per_timestep": prof["ms"] * 1e3 / max(prof["bytes"] / (4.0 * cfg.enc_hidden * cfg.enc_hidden * 2.0), 1.0),
+                     "sequences_per_launch": eb,
                      # what batch-1-per-stream execution would have to stream: every sequence its own W_hh per step
-                     "per_stream_equivalent_gbs": achieved * min(eb, S),
+                     "per_stream_equivalent_gbs": achieved * eb,
                      "share_of_step_time": share,
+                     # the weight-stationary kernel's own bound is the tensor pipe (and the L2 exchange), not HBM:
+                     # the same launches as flops against the measured dense bf16 peak, and the pipe's active share
+                     # from the committed ncu capture
+                     "tensor": {"achieved_tflops": tflops, "peak_tflops": tpeak, "frac": tflops / tpeak,
+                                "peak_source": tpeak_src, "pipe_active_pct_ncu": TENSOR_PIPE_ACTIVE_PCT_NCU},
                      "note": "algorithmic bytes = T * 4H*H * 2 per launch (W_hh once per timestep, the streamed "
                              "formulation); the kernel keeps them in registers as mma fragments"},
         "clocks": clocks,
     }
+    line.update(extras)
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
@@ -323,19 +376,16 @@ def _graph_time_us(calls, reps):
     return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
 
 
-def run_c2(args):
+def measure_c2(reps_base, batches=(8, 32, 128), shapes_batched=None, rowops=True):
     """C2: y = Wx + b at batch 1 for the five (N,K) shapes (weights rotated over > 126 MB so every call streams from
-    HBM), and the same layers at batch 8/32/128 through the tensor-core GEMM."""
-    from pimaicompiler_b200 import build, ops
-    build.build()
+    HBM), and the same layers at batch 8/32/128 through the batched-stream GEMM."""
+    from pimaicompiler_b200 import ops
     ops.init()
     peak, peak_src = load_peaks()
-    dev = torch.device("cuda", 0)
+    dev = torch.device("cuda", torch.cuda.current_device())
     shapes = [(4096, 1024), (4096, 2048), (1024, 1024), (32320, 1024), (29, 512)]
     g = torch.Generator().manual_seed(1)
     results = []
-    sampler = ClockSampler(0)
-    sampler.start()
     for (N, K) in shapes:
         nb = max(2, min(96, int(400e6 // (N * K * 2)) + 1))       # > 126 MB of distinct weights where it matters
         k = 1.0 / K ** 0.5
@@ -343,34 +393,48 @@ def run_c2(args):
         b = ((torch.rand(N, generator=g) * 2 - 1) * k).half().to(dev)
         x = torch.randn(K, generator=g).half().to(dev)
         y = torch.empty(N, dtype=torch.float16, device=dev)
-        us = _graph_time_us([(lambda W=W: ops.gemv_mv(W, x, b, out=y)) for W in Ws], args.steps * 10)
-        us_l2 = _graph_time_us([(lambda: ops.gemv_mv(Ws[0], x, b, out=y)) for _ in range(nb)], args.steps * 10)
+        us = _graph_time_us([(lambda W=W: ops.gemv_mv(W, x, b, out=y)) for W in Ws], reps_base * 10)
+        us_l2 = _graph_time_us([(lambda: ops.gemv_mv(Ws[0], x, b, out=y)) for _ in range(nb)], reps_base * 10)
         As = [W.t().contiguous() for W in Ws[: min(nb, 24)]]
-        us_vm = _graph_time_us([(lambda A=A: ops.gemv_vm(x, A, b, out=y)) for A in As], args.steps * 10)
+        us_vm = _graph_time_us([(lambda A=A: ops.gemv_vm(x, A, b, out=y)) for A in As], reps_base * 10)
         nbytes = 2 * (N * K + K + 2 * N)
         row = {"N": N, "K": K, "B": 1, "bytes": nbytes, "mv_us": us, "mv_gbs": nbytes / us / 1e3,
                "mv_frac_of_measured_hbm": nbytes / us / 1e3 / peak, "mv_l2_resident_us": us_l2,
                "vm_us": us_vm, "vm_gbs": nbytes / us_vm / 1e3, "weights_rotated_mb": nb * N * K * 2 / 1e6}
         results.append(row)
-        for B in (8, 32, 128):
+        for B in batches:
+            if shapes_batched is not None and (N, K) not in shapes_batched:
+                continue
             X = torch.randn(B, K, generator=g).half().to(dev)
             Y = torch.empty(B, N, dtype=torch.float16, device=dev)
-            usb = _graph_time_us([(lambda W=W: ops.gemm_wx(W, X, b, out=Y)) for W in Ws], args.steps * 10)
+            usb = _graph_time_us([(lambda W=W: ops.gemm_wx(W, X, b, out=Y)) for W in Ws], reps_base * 10)
             bb = 2 * (N * K + B * K + N + B * N)
             results.append({"N": N, "K": K, "B": B, "bytes": bb, "gemm_us": usb, "gemm_gbs": bb / usb / 1e3,
+                            "gemm_frac_of_measured_hbm": bb / usb / 1e3 / peak,
                             "gemm_tflops": 2.0 * B * N * K / usb / 1e6})
         del Ws, As
     # row-wise glue of a decode step at its benchmark sizes: the 32320-wide GNMT / 29-wide RNN-T logit rows, a 512-wide
     # model vector, 8 heads x 40 attention scores (one launch each, 16 calls per graph)
-    rowops = []
-    for name, rows, cols in (("logits_gnmt", 1, 32320), ("logits_rnnt", 1, 29), ("model_vec", 1, 512), ("attn", 8, 40)):
-        xr = (torch.randn(rows, cols, generator=g) * 3).half().to(dev)
-        yr = torch.empty_like(xr)
-        t_sm = _graph_time_us([(lambda: ops.softmax(xr, out=yr)) for _ in range(16)], args.steps * 10)
-        t_am = _graph_time_us([(lambda: ops.argmax(xr)) for _ in range(16)], args.steps * 10)
-        t_ln = _graph_time_us([(lambda: ops.layer_norm(xr)) for _ in range(16)], args.steps * 10)
-        rowops.append({"case": name, "rows": rows, "cols": cols, "softmax_us": t_sm, "argmax_us": t_am,
-                       "layer_norm_us": t_ln})
+    rows_out = []
+    if rowops:
+        for name, rows, cols in (("logits_gnmt", 1, 32320), ("logits_rnnt", 1, 29), ("model_vec", 1, 512), ("attn", 8, 40)):
+            xr = (torch.randn(rows, cols, generator=g) * 3).half().to(dev)
+            yr = torch.empty_like(xr)
+            t_sm = _graph_time_us([(lambda: ops.softmax(xr, out=yr)) for _ in range(16)], reps_base * 10)
+            t_am = _graph_time_us([(lambda: ops.argmax(xr)) for _ in range(16)], reps_base * 10)
+            t_ln = _graph_time_us([(lambda: ops.layer_norm(xr)) for _ in range(16)], reps_base * 10)
+            rows_out.append({"case": name, "rows": rows, "cols": cols, "softmax_us": t_sm, "argmax_us": t_am,
+                             "layer_norm_us": t_ln})
+    return {"results": results, "rowops": rows_out, "peak": peak, "peak_src": peak_src}
+
+
+def run_c2(args):
+    from pimaicompiler_b200 import build
+    build.build()
+    sampler = ClockSampler(0)
+    sampler.start()
+    m = measure_c2(args.steps)
+    results, rowops, peak, peak_src = m["results"], m["rowops"], m["peak"], m["peak_src"]
     clocks = sampler.stop()
     big = next(r for r in results if r["N"] == 32320 and r["B"] == 1)
     line = {"metric": "gemv_mv_hbm_gbs", "value": big["mv_gbs"], "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -386,23 +450,24 @@ def run_c2(args):
     print(json.dumps(line), flush=True)
 
 
-def run_c1(args):
-    """C1: one aten::lstm, 2 layers, input 240, hidden 1024, T=200, batch 1 (seed 0), every recurrence variant."""
-    from pimaicompiler_b200 import build, ops
-    build.build()
-    dev = torch.device("cuda", 0)
-    torch.manual_seed(0)
+def measure_c1(reps_base):
+    """C1: one aten::lstm, 2 layers, input 240, hidden 1024, T=200, batch 1 (seed 0), streamed and persistent."""
+    from pimaicompiler_b200 import ops
+    dev = torch.device("cuda", torch.cuda.current_device())
+    gen = torch.Generator().manual_seed(0)
     T, I, H, L = 200, 240, 1024, 2
-    x = torch.randn(T, 1, I).half().to(dev)
+    x = torch.randn(T, 1, I, generator=gen).half().to(dev)
     ps = []
     for l in range(L):
         Il = I if l == 0 else H
-        ps += [((torch.rand(4 * H, Il) * 2 - 1) / 32).half().to(dev), ((torch.rand(4 * H, H) * 2 - 1) / 32).half().to(dev),
-               ((torch.rand(4 * H) * 2 - 1) / 32).half().to(dev), ((torch.rand(4 * H) * 2 - 1) / 32).half().to(dev)]
+        ps += [((torch.rand(4 * H, Il, generator=gen) * 2 - 1) / 32).half().to(dev),
+               ((torch.rand(4 * H, H, generator=gen) * 2 - 1) / 32).half().to(dev),
+               ((torch.rand(4 * H, generator=gen) * 2 - 1) / 32).half().to(dev),
+               ((torch.rand(4 * H, generator=gen) * 2 - 1) / 32).half().to(dev)]
     m = ops.Lstm(ps, L, False, I, H, True)
-    peak, peak_src = load_peaks()
+    peak, _ = load_peaks()
     res = {}
-    for name, v in (("streamed", ops.LSTM_STREAMED), ("persistent", ops.LSTM_PERSISTENT)):
+    for name, v in (("streamed", ops.LSTM_STREAMED), ("persistent", ops.LSTM_AUTO)):
         m.set_variant(v)
         out = m.forward(x)
         for _ in range(3):
@@ -410,19 +475,30 @@ def run_c1(args):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps * 5):
+        for _ in range(reps_base * 5):
             m.forward(x, out=out)
         e1.record()
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / (args.steps * 5)
-        res[name] = {"us_per_call": us, "us_per_layer_step": us / (T * L),
-                     "w_hh_stream_gbs": T * L * 4 * H * H * 2 / us / 1e3}
+        us = e0.elapsed_time(e1) * 1e3 / (reps_base * 5)
+        gbs = T * L * 4 * H * H * 2 / us / 1e3
+        res[name] = {"us_per_call": us, "us_per_layer_step": us / (T * L), "w_hh_stream_gbs": gbs,
+                     "frac_of_measured_hbm": gbs / peak,
+                     "config": "aten::lstm L=2 I=240 H=1024 T=200 B=1, whole call (projection GEMMs included)"}
+    assert m.last_status() == 0
+    return res
+
+
+def run_c1(args):
+    from pimaicompiler_b200 import build
+    build.build()
+    res = measure_c1(args.steps)
+    peak, peak_src = load_peaks()
     best = res["persistent"]
     line = {"metric": "lstm_c1_us_per_call", "value": best["us_per_call"], "unit": "us", "n_gpus": 1,
             "steps": args.steps, "warmup": 3, "ms_per_step": best["us_per_call"] / 1e3, "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
             "config": {"workload": "C1: aten::lstm L=2 I=240 H=1024 T=200 B=1"},
-            "roofline": {"bound": "hbm", "kernel": "lstm_persistent_kernel", "achieved": best["w_hh_stream_gbs"],
+            "roofline": {"bound": "hbm", "kernel": "persistent recurrence", "achieved": best["w_hh_stream_gbs"],
                          "peak": peak, "unit": "GB/s", "frac": best["w_hh_stream_gbs"] / peak, "peak_source": peak_src,
                          "traffic": None, "note": "whole call (projection GEMMs included); bytes = T*L*4H*H*2"},
             "results": res, "gpu_launches": None}
@@ -436,7 +512,7 @@ def run_c4(args):
     token fed back through device memory)."""
     from pimaicompiler_b200 import build
     build.build()
-    from tests import decode_models as dm
+    from pimaicompiler_b200 import decode_models as dm
     H, V, S, steps = 1024, 32320, 37, 80
     w = dm.make_gnmt(H, V, S, torch.Generator().manual_seed(4), 2.0)
     be = dm.PimBackend()
@@ -473,7 +549,7 @@ def run_c5(args):
     device (CUDA graph, token and position in device memory, in-place KV append)."""
     from pimaicompiler_b200 import build
     build.build()
-    from tests import decode_models as dm
+    from pimaicompiler_b200 import decode_models as dm
     d, heads, ffn, V, layers, S, steps = 512, 8, 2048, 32000, 6, 40, 64
     w = dm.make_transformer(d, heads, ffn, V, layers, S, torch.Generator().manual_seed(5), 2.0)
     be = dm.PimBackend()
@@ -505,7 +581,12 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4", "c5"],
                     help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm; "
                          "c4 / c5 = GNMT-style / Transformer-style decoder step, op by op against device-resident")
-    ap.add_argument("--streams-per-gpu", type=int, default=128)
+    ap.add_argument("--streams-total", type=int, default=STREAMS_TOTAL,
+                    help="utterance streams of one step, sharded over the ranks (the configuration's 1024)")
+    ap.add_argument("--streams-per-gpu", type=int, default=0,
+                    help="overrides --streams-total with a per-rank count (profiling runs on small cases)")
+    ap.add_argument("--streams-per-call", type=int, default=128, help="utterances per decode call")
+    ap.add_argument("--no-extras", action="store_true", help="skip the C1 / C2 figures of the default line")
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--encoder-batch", type=int, default=0, help="utterances per lock-step encoder group (0 = default)")

@@ -60,7 +60,9 @@ int pimb200_gemv_mv(const void* W, const void* x, const void* bias, void* y,
 /* VM:  y[N] = act(x[K] · A[K,N] + bias[N]);  A row-major K x N, bias may be NULL.
  * Replaces the I_X_W PimExecuteGemm call (aten_ops.cpp:626-661, 771-803) and
  * rocblas_gemv_template_xAy / addmv_kernel_xAy (custom_ops.h:66-139, 216-298).
- * Uses the per-device split-K scratch allocated by pimb200_init. */
+ * Uses the per-device split-K scratch allocated by pimb200_init; calls on different streams are ordered by the
+ * library, except launches captured into a CUDA graph: replays of such graphs must be ordered by the caller against
+ * every other VM call on the device. */
 int pimb200_gemv_vm(const void* x, const void* A, const void* bias, void* y,
                     int K, int N, int act, void* stream);
 
@@ -119,8 +121,6 @@ int pimb200_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pit
  * Replaces atenCat (aten_ops.cpp:97) for contiguous inputs. */
 int pimb200_cat(void* dst, const void* const* src, const size_t* inner_bytes, int n_src,
                 size_t outer, void* stream);
-
-/* ---- fused multi-layer LSTM ---------------------------------------------- */
 
 /* ---- row-wise glue of the decode path (fp16 storage, fp32 arithmetic), contiguous rows of `cols` elements ---- */
 
@@ -212,7 +212,8 @@ int pimb200_lstm_forward_packed(pimb200_lstm* h, const void* data, const int64_t
                                 const void* h0, const void* c0, void* y, void* hn, void* cn, void* stream);
 
 /* The last device-side status of a handle's asynchronous work: call after synchronising the
- * stream; returns PIMB200_ERR_TIMEOUT when a bounded wait inside the persistent kernel gave up. */
+ * stream; returns PIMB200_ERR_TIMEOUT when a bounded wait inside the persistent kernel gave up (the outputs of that
+ * call are then undefined); reading clears it.  A launch that gave up does not affect the launches after it. */
 int pimb200_lstm_last_status(pimb200_lstm* h);
 
 /* Timing hook: while enabled, every recurrence launch sequence (all T steps of one layer and direction)
@@ -237,6 +238,16 @@ int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on);
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are
  * inside MIOpen. */
 int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit);
+
+/* Tuning / diagnostics of the tagged-word persistent kernel (PIMB200_LSTM_PERSISTENT_TAGGED): how many replicas of the
+ * exchange buffer every CTA publishes into (1..16) and how far apart consecutive exchange words lie, in 16-byte units
+ * (1..8; 8 = one word per 128-byte line).  No counterpart in the reference. */
+int pimb200_lstm_set_exchange_copies(pimb200_lstm* h, int copies);
+int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16);
+
+/* Diagnostics: a device buffer of n_cta * T * 8 int64 that the persistent kernels fill with per-step clocks (NULL
+ * switches it off).  Not owned by the handle.  No counterpart in the reference. */
+int pimb200_lstm_set_trace(pimb200_lstm* h, long long* device_buffer);
 
 #ifdef __cplusplus
 }

@@ -72,6 +72,18 @@ int pimb200_rnnt_info(pimb200_rnnt* h, int* cluster_size, int* smem_mask, size_t
 int pimb200_rnnt_profile_enable(pimb200_rnnt* h, int enable);
 int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long* recurrences, double* bytes);
 
+/* First non-zero status among the kernels a decode launched since the last call (PIMB200_ERR_TIMEOUT when a bounded
+ * wait of a recurrence or of a tensor-core GEMM gave up: the outputs of that decode are then undefined); reading clears
+ * it.  Synchronises the device.  A timed-out launch does not affect later launches. */
+int pimb200_rnnt_last_status(pimb200_rnnt* h);
+
+/* ---- diagnostics and test hooks (no counterpart in the reference) ---- */
+/* Bounded waits of both encoder stacks, in polls (see pimb200_lstm_set_poll_limit): fault tests shrink it to 1. */
+int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit);
+/* Device buffer of (T / stack_factor) * 8 int64 that the greedy kernel fills with per-frame clocks of utterance 0
+ * (NULL switches it off).  Not owned by the handle. */
+int pimb200_rnnt_set_trace(pimb200_rnnt* h, long long* device_buffer);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,6 +63,12 @@ SIGNATURES = {
     "pimb200_rnnt_set_encoder_batch": (_i, [_vp, _i]),
     "pimb200_rnnt_set_greedy_multi": (_i, [_vp, _i]),
     "pimb200_rnnt_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_sz)]),
+    "pimb200_rnnt_last_status": (_i, [_vp]),
+    "pimb200_rnnt_set_poll_limit": (_i, [_vp, _i]),
+    "pimb200_rnnt_set_trace": (_i, [_vp, _vp]),
+    "pimb200_lstm_set_exchange_copies": (_i, [_vp, _i]),
+    "pimb200_lstm_set_exchange_stride": (_i, [_vp, _i]),
+    "pimb200_lstm_set_trace": (_i, [_vp, _vp]),
 }
 
 

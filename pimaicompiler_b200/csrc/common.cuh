@@ -50,6 +50,17 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
     return r;
 }
 
+// Device status block of the kernels with bounded waits: word 0 is the sticky error code that *_last_status reads and
+// clears; word 1 is the generation of the launch that gave up.  A launch aborts its waits only when word 1 carries its
+// own generation (never 0), so one timed-out launch does not make later launches skip their work.
+__device__ __forceinline__ bool status_aborted(const int* status, int gen) {
+    return reinterpret_cast<const volatile int*>(status)[1] == gen;
+}
+__device__ __forceinline__ void status_raise(int* status, int gen, int code) {
+    atomicExch(status, code);
+    atomicExch(status + 1, gen);
+}
+
 __device__ __forceinline__ float2 h2f2(uint32_t v) {
     __half2 h = *reinterpret_cast<__half2*>(&v);
     return __half22float2(h);

@@ -49,7 +49,8 @@ struct GemmArgs {
     int bn;               // activation rows per tile: multiple of 16 in [16, 128]
     int tmem_cols;        // power of two >= max(32, 2 * bn): two accumulator stages
     int m_tiles, j_tiles; // tiles along the weight rows and along the activation rows
-    int* status;          // device status word
+    int* status;          // device status block: [0] sticky error code, [1] generation of the launch that gave up
+    int gen;              // this launch's generation (never 0)
     int x_batch;          // > 0: X is [x_batch sequences][T steps][K] (batch-first) but the activation rows are numbered
                           //      time-major, row = t * x_batch + b; map_x is then a 3-D map (K, b, t) and bn % x_batch == 0
 };
@@ -72,7 +73,7 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (a.K + BK - 1) / BK;
     const int n_tiles = a.m_tiles * a.j_tiles;
-    const volatile int* abort_flag = a.status;
+    const volatile int* abort_flag = a.status + 1;   // generation of the launch that gave up
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -108,7 +109,7 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 for (int kb = 0; kb < kblocks; ++kb, ++issued) {
                     const int s = issued % STAGES;
                     const uint32_t it = (uint32_t)(issued / STAGES);
-                    if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag)) { failed = true; break; }
+                    if (!mbar_wait(empty0 + 8 * s, (it & 1) ^ 1, abort_flag, a.gen)) { failed = true; break; }
                     mbar_expect_tx(full0 + 8 * s, stage_bytes);
                     tma_load_2d(smem_u32(sA + (size_t)s * A_STAGE_BYTES), &map_w, full0 + 8 * s, kb * BK, m0);
                     if (a.x_batch > 0)   // bn / x_batch whole timesteps of all sequences, sequence index fastest
@@ -118,7 +119,7 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 }
             }
             if (failed) {
-                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
                 // let the copies already issued land before the CTA gives its shared memory back
                 const int first = issued > STAGES ? issued - STAGES : 0;
                 for (int q = first; q < issued; ++q) {
@@ -137,13 +138,13 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             for (int tile = blockIdx.x; tile < n_tiles && !failed; tile += gridDim.x, ++local) {
                 const int as = local & 1;                          // accumulator stage
                 const uint32_t ait = (uint32_t)(local >> 1);        // how often this stage has been used before
-                if (!mbar_wait(acce0 + 8 * as, (ait & 1) ^ 1, abort_flag)) { failed = true; break; }
+                if (!mbar_wait(acce0 + 8 * as, (ait & 1) ^ 1, abort_flag, a.gen)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * a.bn);
                 for (int kb = 0; kb < kblocks; ++kb, ++consumed) {
                     const int s = consumed % STAGES;
                     const uint32_t it = (uint32_t)(consumed / STAGES);
-                    if (!mbar_wait(full0 + 8 * s, it & 1, abort_flag)) { failed = true; break; }
+                    if (!mbar_wait(full0 + 8 * s, it & 1, abort_flag, a.gen)) { failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t adesc = make_smem_desc(smem_u32(sA + (size_t)s * A_STAGE_BYTES));
                     const uint64_t bdesc = make_smem_desc(smem_u32(sB + (size_t)s * B_STAGE_BYTES));
@@ -158,7 +159,7 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 umma_commit(accf0 + 8 * as);      // this tile's accumulator is complete once everything above retires
             }
             if (failed) {
-                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
                 umma_commit(accf0);               // wake epilogue warps; they see the status word and leave
                 umma_commit(accf0 + 8);
             }
@@ -172,10 +173,10 @@ gemm_wx_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             const uint32_t ait = (uint32_t)(local >> 1);
             const int m0 = (tile % a.m_tiles) * BM, j0 = (tile / a.m_tiles) * a.bn;
             const int m = m0 + q * 32 + lane;
-            bool ok = mbar_wait(accf0 + 8 * as, ait & 1, abort_flag);
-            if (!ok) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            bool ok = mbar_wait(accf0 + 8 * as, ait & 1, abort_flag, a.gen);
+            if (!ok) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (!ok || *abort_flag != 0) break;
+            if (!ok || *abort_flag == a.gen) break;
             const float bv = (a.bias && m < a.N) ? __half2float(a.bias[m]) : 0.f;
             const float lo = a.act == PIMB200_ACT_RELU ? 0.f : -INFINITY;   // v = max(v, lo): ReLU without a branch
             const int j_end = a.J < j0 + a.bn ? a.J : j0 + a.bn;            // first activation row past this tile
@@ -234,8 +235,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 static std::mutex g_mu;
 static EncodeTiledFn g_encode = nullptr;
 static bool g_encode_tried = false;
-static int* g_status[64];
-static bool g_attr_set = false;
+constexpr int kMaxDevices = 64;
+static int* g_status[kMaxDevices];       // per device: {sticky error code, generation of the launch that gave up}
+static bool g_attr_set[kMaxDevices];     // cudaFuncSetAttribute is per device
+static int g_gen = 0;                    // launch generation, never 0
 
 static EncodeTiledFn get_encode() {
     if (g_encode_tried) return g_encode;
@@ -280,22 +283,27 @@ static int launch(const __half* W, const __half* X, const __half* bias, void* Y,
     if (K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
     int dev = 0;
     PIMB200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return PIMB200_ERR_UNSUPPORTED;
     int* status = nullptr;
+    int gen = 0;
     {
         std::lock_guard<std::mutex> lk(g_mu);
         if (!get_encode()) return PIMB200_ERR_UNSUPPORTED;
         if (!g_status[dev]) {
-            PIMB200_CUDA_TRY(cudaMalloc(&g_status[dev], sizeof(int)));
-            PIMB200_CUDA_TRY(cudaMemset(g_status[dev], 0, sizeof(int)));
+            PIMB200_CUDA_TRY(cudaMalloc(&g_status[dev], 2 * sizeof(int)));
+            PIMB200_CUDA_TRY(cudaMemset(g_status[dev], 0, 2 * sizeof(int)));
         }
         status = g_status[dev];
-        if (!g_attr_set) {
+        if (!g_attr_set[dev]) {
             PIMB200_CUDA_TRY(cudaFuncSetAttribute(gemm_wx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                   (int)SMEM_BYTES));
-            g_attr_set = true;
+            g_attr_set[dev] = true;
         }
+        if (++g_gen == 0) g_gen = 1;
+        gen = g_gen;
     }
     GemmArgs a;
+    a.gen = gen;
     a.bias = bias; a.Y = Y; a.N = N; a.K = K; a.J = J; a.ldy = ldy; a.act = act; a.y_is_f32 = y_is_f32;
     a.bn = J >= BN_MAX ? BN_MAX : ((J + 15) / 16) * 16;
     a.x_batch = 0;
@@ -361,6 +369,7 @@ extern "C" int pimb200_gemm_force_simt(int on) {
 extern "C" int pimb200_gemm_last_status(void) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return PIMB200_ERR_LAUNCH;
+    if (dev < 0 || dev >= pimb200::tc::kMaxDevices) return PIMB200_OK;
     int* p = nullptr;
     {
         std::lock_guard<std::mutex> lk(pimb200::tc::g_mu);

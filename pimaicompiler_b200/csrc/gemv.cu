@@ -237,21 +237,31 @@ int launch_gemv_vm_with_scratch(const __half* x, const __half* A, const __half* 
 static std::mutex g_vm_mutex;
 static cudaStream_t g_vm_last_stream[64];
 static bool g_vm_used[64];
-static cudaEvent_t g_vm_event[64];
+static cudaEvent_t g_vm_event[64];   // recorded behind the last split-K user of the device's scratch
 
-// Calls on one device share the split-K scratch: when the caller switches streams, order the new
-// stream after the work already queued on the previous one.
+// Calls on one device share the split-K scratch.  Every split-K launch records an event behind itself on its own
+// stream (scratch_user_done); a later caller on a different stream waits for that event first.  Nothing is ever
+// recorded on a stream handle remembered from an earlier call (the caller may have destroyed it since).
+// While a stream is being captured into a CUDA graph neither side is possible: captured launches are not ordered
+// against other users of the scratch, so replays of graphs that contain split-K VM products must be ordered by
+// the caller against every other VM call on the device.
 static int order_scratch_users(int dev, cudaStream_t st) {
+    if (dev < 0 || dev >= 64) return PIMB200_ERR_UNSUPPORTED;
     std::lock_guard<std::mutex> lk(g_vm_mutex);
-    if (g_vm_used[dev] && g_vm_last_stream[dev] != st) {
-        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(st, &cs);
-        if (cs == cudaStreamCaptureStatusNone) {
-            if (!g_vm_event[dev]) PIMB200_CUDA_TRY(cudaEventCreateWithFlags(&g_vm_event[dev], cudaEventDisableTiming));
-            PIMB200_CUDA_TRY(cudaEventRecord(g_vm_event[dev], g_vm_last_stream[dev]));
-            PIMB200_CUDA_TRY(cudaStreamWaitEvent(st, g_vm_event[dev], 0));
-        }
-    }
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cs);
+    if (cs != cudaStreamCaptureStatusNone) return PIMB200_OK;
+    if (g_vm_used[dev] && g_vm_last_stream[dev] != st) PIMB200_CUDA_TRY(cudaStreamWaitEvent(st, g_vm_event[dev], 0));
+    return PIMB200_OK;
+}
+static int scratch_user_done(int dev, cudaStream_t st) {
+    if (dev < 0 || dev >= 64) return PIMB200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(g_vm_mutex);
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cs);
+    if (cs != cudaStreamCaptureStatusNone) return PIMB200_OK;
+    if (!g_vm_event[dev]) PIMB200_CUDA_TRY(cudaEventCreateWithFlags(&g_vm_event[dev], cudaEventDisableTiming));
+    PIMB200_CUDA_TRY(cudaEventRecord(g_vm_event[dev], st));
     g_vm_used[dev] = true;
     g_vm_last_stream[dev] = st;
     return PIMB200_OK;
@@ -267,12 +277,12 @@ static int launch_gemv_vm(const __half* x, const __half* A, const __half* bias, 
     float* partials = nullptr;
     unsigned int* tickets = nullptr;
     VmPlan p;
+    int dev = -1;
     if (allow_split) {
         DeviceCtx* ctx = current_ctx();
         if (!ctx) return PIMB200_ERR_NOT_INIT;
         p = plan_gemv_vm(K, N, kSplitKMaxFloats, kSplitKMaxTiles);
         if (p.splits > 1) {
-            int dev = 0;
             PIMB200_CUDA_TRY(cudaGetDevice(&dev));
             int rc = order_scratch_users(dev, st);
             if (rc != PIMB200_OK) return rc;
@@ -282,7 +292,9 @@ static int launch_gemv_vm(const __half* x, const __half* A, const __half* bias, 
     } else {
         p = plan_gemv_vm(K, N, 0, 0);  // forces a single split
     }
-    return launch_gemv_vm_with_scratch(x, A, bias, y, K, N, act, p, partials, tickets, st);
+    const int rc = launch_gemv_vm_with_scratch(x, A, bias, y, K, N, act, p, partials, tickets, st);
+    if (rc == PIMB200_OK && dev >= 0) return scratch_user_done(dev, st);
+    return rc;
 }
 
 // =============================================================================================

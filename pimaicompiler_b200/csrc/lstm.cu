@@ -315,7 +315,8 @@ struct PersistArgs {
     int copies;
     int wstride;            // spacing of consecutive exchange words in 16-byte units
     uint32_t tag_base;      // tag of step s output = (tag_base + s + 1) & 0xffff
-    int* status;            // device status word, set to PIMB200_ERR_TIMEOUT when a wait runs out
+    int* status;            // device status block: [0] sticky error code, [1] generation of the launch that gave up
+    int gen;                // this launch's generation (never 0)
     int H, T, U, B;         // U = hidden units per CTA
     int reverse;
     int poll_limit;
@@ -507,7 +508,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
                     timed_out = 1;
                     break;
                 }
-                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) {
+                if ((polls & 1023) == 0 && status_aborted(a.status, a.gen)) {
                     timed_out = 1;  // another CTA already gave up
                     break;
                 }
@@ -527,7 +528,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_kernel(Per
                     }
                 }
             } else {
-                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             }
         }
         if (tr && tid == 0) { tr[2] = clock64(); tr[3] = polls; }
@@ -563,7 +564,8 @@ struct BulkArgs {
     uint4* data;            // [2 parities][n_cta][BP] 16-byte records: the 8 hidden values of (cta, sequence)
     uint32_t* flags;        // [kBulkFlagCopies][2 parities][n_cta] step tags, one per 128-byte line
     uint32_t tag_base;      // flag value of step s = tag_base + s + 1
-    int* status;
+    int* status;            // as in PersistArgs
+    int gen;
     int H, T, B;
     int reverse;
     int poll_limit;
@@ -712,9 +714,9 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_bulk_kerne
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                 if (v == tag) break;
                 if (++polls >= a.poll_limit) { timed_out = 1; break; }
-                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+                if ((polls & 1023) == 0 && status_aborted(a.status, a.gen)) { timed_out = 1; break; }
             }
-            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            if (timed_out) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             if (tr && tid == 0) tr[4] = clock64();
             __threadfence();  // acquire side: loads below are ordered after the flag reads
             if (tr && tid == 0) tr[5] = clock64();
@@ -943,9 +945,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
                         asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                         if (v == tag) break;
                         if (++polls >= a.poll_limit) { timed_out = 1; break; }
-                        if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+                        if ((polls & 1023) == 0 && status_aborted(a.status, a.gen)) { timed_out = 1; break; }
                     }
-                    if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                    if (timed_out) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
                     // acquire: one acquire load of the flag just seen (cheaper than a full fence)
                     uint32_t v;
                     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
@@ -983,12 +985,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
                              : "l"(gp));
             }
         }
-        if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status))) {
+        if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status) + 1, a.gen)) {
             // gave up (a flag or a copy never came, here or in another CTA): before the CTA hands its shared memory
             // back, give the bulk copies it has in flight a bounded chance to land
             for (uint32_t i = 0; i < (1u << 20); ++i)
                 if (pimb200::tc::mbar_try_wait(gbar_addr, (uint32_t)(s & 1))) break;
-            atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             timed_out = 1;
         }
         if (__syncthreads_or(timed_out)) return;
@@ -1035,7 +1037,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_tc_kernel(
     const int n_cta = gridDim.x, cta = blockIdx.x;
     const int u0 = cta * 8;
     const int PPT = (8 * BP + kPersistThreads - 1) / kPersistThreads;  // (unit, sequence) pairs per thread: 1 or 2
-    const volatile int* abort_flag = a.status;
+    const volatile int* abort_flag = a.status + 1;   // generation of the launch that gave up
 
     // W_hh slice -> A operand tiles
     {
@@ -1119,7 +1121,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_tc_kernel(
         }
         // rows 0..31 of the accumulator -> zbuf: warps 0 and 4 own TMEM lanes 0..31, half of the columns each
         if ((warp & 3) == 0 && warp < 8) {
-            if (!mbar_wait(bar_addr, (uint32_t)(s & 1), abort_flag)) failed = 1;
+            if (!mbar_wait(bar_addr, (uint32_t)(s & 1), abort_flag, a.gen)) failed = 1;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (tr && tid == 0) tr[1] = clock64();
             if (!failed) {
@@ -1134,7 +1136,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_tc_kernel(
                                         __uint_as_float(r[q + 3]));
                 }
             } else {
-                atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+                status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         }
@@ -1191,9 +1193,9 @@ __global__ void __launch_bounds__(kPersistThreads, 1) lstm_persistent_tc_kernel(
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
                 if (v == tag) break;
                 if (++polls >= a.poll_limit) { timed_out = 1; break; }
-                if ((polls & 1023) == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) { timed_out = 1; break; }
+                if ((polls & 1023) == 0 && status_aborted(a.status, a.gen)) { timed_out = 1; break; }
             }
-            if (timed_out) atomicExch(a.status, PIMB200_ERR_TIMEOUT);
+            if (timed_out) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
             __threadfence();
         }
         if (__syncthreads_or(timed_out)) { failed = 1; break; }
@@ -1255,7 +1257,8 @@ struct pimb200_lstm {
     uint4* bulk_data = nullptr;      // batched variant: [2][n_cta][32] records
     uint32_t* bulk_flags = nullptr;  // [2][n_cta]
     uint32_t bulk_tag = 0;
-    int* d_status = nullptr;
+    int* d_status = nullptr;         // {sticky error code, generation of the launch that gave up}
+    int launch_gen = 0;              // generation handed to the last persistent launch (never 0)
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
     int use_tc = 0;        // 1 = tcgen05 recurrence for 17..64 sequences (measured slower than mma.sync here: opt-in)
@@ -1278,6 +1281,11 @@ static void prof_mark(pimb200_lstm* h, cudaStream_t st) {
         h->prof_ev.push_back(e);
     }
     cudaEventRecord(h->prof_ev[h->prof_used++], st);
+}
+
+static int next_gen(pimb200_lstm* h) {
+    if (++h->launch_gen == 0) h->launch_gen = 1;
+    return h->launch_gen;
 }
 
 static int in_size(const pimb200_lstm* h, int l) { return l == 0 ? h->I : h->D * h->H; }
@@ -1337,7 +1345,7 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
         }
     }
     if (cudaMalloc(&h->xchg, kXchgBytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
-    if (cudaMalloc(&h->d_status, 4) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+    if (cudaMalloc(&h->d_status, 8) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
     cudaMemset(h->xchg, 0, kXchgBytes);
     {
         const size_t ncta = (size_t)ceil_div(H, 8);
@@ -1346,7 +1354,7 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
         if (cudaMalloc(&h->bulk_flags, flag_bytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
         cudaMemset(h->bulk_flags, 0, flag_bytes);
     }
-    cudaMemset(h->d_status, 0, 4);
+    cudaMemset(h->d_status, 0, 8);
     if ((rc = cuda_status(cudaDeviceSynchronize())) != PIMB200_OK) return fail(rc);
     *out = h;
     return PIMB200_OK;
@@ -1515,7 +1523,7 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
         a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
         a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
-        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status;
+        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
         a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
         a.trace = h->trace;
         h->bulk_tag += (uint32_t)T + 1u;
@@ -1549,7 +1557,7 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
         a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
         a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
-        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status;
+        a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
         a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
         a.trace = h->trace;
         h->bulk_tag += (uint32_t)T + 1u;
@@ -1576,7 +1584,7 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
         a.B = B;
         pp.smem = persist_smem(H, B);
-        a.xchg = h->xchg; a.tag_base = h->tag_counter; a.status = h->d_status;
+        a.xchg = h->xchg; a.tag_base = h->tag_counter; a.status = h->d_status; a.gen = next_gen(h);
         a.H = H; a.T = T; a.U = pp.U; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
         a.trace = h->trace;
         a.copies = h->xchg_copies;

@@ -1033,6 +1033,9 @@ struct pimb200_rnnt {
     int greedy_multi = 1;   // 0 = always one utterance per cluster
     int enc_batch = 64;     // utterances the encoder advances in lock step
     int cluster = 0;        // CTAs per cluster
+    int resident = 1;       // clusters of each greedy kernel that are co-resident on the device (occupancy query)
+    int resident_mma = 1;
+    int resident_multi = 1;
     int smem_mask = 0;
     size_t smem_bytes = 0;
     std::mutex mu;
@@ -1162,6 +1165,7 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
         int n_clusters = 0;
         if (cudaOccupancyMaxActiveClusters(&n_clusters, fn, &lc) == cudaSuccess && n_clusters >= 1) {
             h->cluster = C;
+            h->resident = n_clusters;
             h->fn = fn;
             h->smem_mask = mask;
             h->smem_bytes = smem;
@@ -1172,6 +1176,7 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
                 int ncl = 0;
                 if (cudaOccupancyMaxActiveClusters(&ncl, rnnt_greedy_mma_kernel, &lc) == cudaSuccess && ncl >= 1) {
                     h->mma_ok = true;
+                    h->resident_mma = ncl;
                     h->smem_bytes_mma = lc.dynamicSmemBytes;
                 } else {
                     cudaGetLastError();
@@ -1187,6 +1192,7 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
                 int ncl = 0;
                 if (cudaOccupancyMaxActiveClusters(&ncl, fm, &lc) == cudaSuccess && ncl >= 1) {
                     h->fn_multi = fm;
+                    h->resident_multi = ncl;
                     h->smem_mask_multi = 31;
                     h->smem_bytes_multi = smem_m;
                 } else {
@@ -1235,6 +1241,27 @@ extern "C" int pimb200_rnnt_set_greedy_multi(pimb200_rnnt* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     h->greedy_multi = on < 0 ? 0 : (on > 2 ? 2 : on);
     return PIMB200_OK;
+}
+
+extern "C" int pimb200_lstm_last_status(pimb200_lstm* h);
+extern "C" int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit);
+extern "C" int pimb200_gemm_last_status(void);
+
+// First non-zero status word among the kernels a decode launches (both encoder stacks' recurrences, the tensor-core
+// GEMMs of this device); reading clears them.  Synchronises the device.
+extern "C" int pimb200_rnnt_last_status(pimb200_rnnt* h) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    const int s_pre = pimb200_lstm_last_status(h->pre);
+    const int s_post = pimb200_lstm_last_status(h->post);
+    const int s_gemm = pimb200_gemm_last_status();
+    return s_pre != PIMB200_OK ? s_pre : (s_post != PIMB200_OK ? s_post : s_gemm);
+}
+
+// Test hook: the bounded waits of both encoder stacks (see pimb200_lstm_set_poll_limit).
+extern "C" int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    const int rc = pimb200_lstm_set_poll_limit(h->pre, limit);
+    return rc != PIMB200_OK ? rc : pimb200_lstm_set_poll_limit(h->post, limit);
 }
 
 // Diagnostics: device buffer of (T/stack)*8 int64 filled with per-frame clocks of utterance 0.
@@ -1312,14 +1339,15 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     a.trace = h->trace;
     a.PH = c.pred_hidden; a.JH = JH; a.V = c.vocab; a.blank = c.blank; a.smem_mask = h->smem_mask;
     const int C = h->cluster;
-    int max_clusters = kNumSmB200 / C;
-    if (max_clusters < 1) max_clusters = 1;
     // more utterances than clusters: several utterances per cluster in lock step
     // greedy_multi: 0 = one utterance per cluster, 1 = best available, 2 = FMA lock-step variant (4 per cluster)
-    const bool crowded = n_utts > max_clusters;
+    const bool crowded = n_utts > h->resident;
     const bool use_mma = h->mma_ok && h->greedy_multi == 1 && crowded;
     const bool multi = !use_mma && h->fn_multi && h->greedy_multi >= 1 && crowded;
     const int groups = use_mma ? ceil_div(n_utts, kMmaUtts) : (multi ? ceil_div(n_utts, kGreedyMulti) : n_utts);
+    // the grid holds as many clusters as are co-resident at this kernel's shared-memory footprint (the occupancy
+    // query of create time), each working through groups cluster, cluster + n_clusters, ...
+    const int max_clusters = use_mma ? h->resident_mma : (multi ? h->resident_multi : h->resident);
     const int n_clusters = groups < max_clusters ? groups : max_clusters;
     if (multi) a.smem_mask = h->smem_mask_multi;
     cudaLaunchConfig_t lc = {};

@@ -362,6 +362,9 @@ extern "C" int pimb200_attention_row(const void* q, const void* K, const void* V
         return PIMB200_ERR_BAD_ARG;
     if (max_len > kAttnMaxLen || head_dim > 1024) return PIMB200_ERR_UNSUPPORTED;
     const size_t smem = ((size_t)max_len + (size_t)(kAttnThreads / 32) * head_dim) * sizeof(float);
+    // the kernel runs within the default 48 KB of shared memory per CTA (16 B of it static): larger score / partial
+    // buffers are refused here instead of failing at launch
+    if (smem + 16 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
     attention_row_kernel<<<(unsigned)heads, kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_add,
         max_len, static_cast<__half*>(out), head_dim, kv_stride, scale);

@@ -29,14 +29,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// bounded wait; false = gave up
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+// bounded wait; false = gave up.  abort_word holds the generation of the launch that gave up (status block word 1):
+// the wait ends early when that is this launch's generation `gen`.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* abort_word, int gen) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 0xff) == 0xff) {
-            if (*abort_flag != 0) return false;                    // another role already gave up
+            if (*abort_word == gen) return false;                  // another role of this launch already gave up
             if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
         }
     }

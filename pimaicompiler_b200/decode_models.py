@@ -1,5 +1,6 @@
-"""GNMT-style and Transformer-style greedy decode steps written once against a small backend interface, so the same
-model code runs on the libtorch-CPU oracle (fp32) and on the device ops of this library (fp16 through the C ABI).
+"""GNMT-style and Transformer-style greedy decode steps written once against a small backend interface: `PimBackend`
+runs every op on the device through the C ABI (fp16); the parity tests run the same model code on a libtorch-CPU fp32
+backend of their own (tests/cpu_backend.py).
 
 Random-init weights of the benchmark's architectures (C4: 4-layer LSTM decoder with normalised Bahdanau attention and a
 vocabulary projection; C5: Transformer decoder layers with a KV cache); the corpora and checkpoints are not available
@@ -17,59 +18,6 @@ import torch
 def u(shape, fan_in, gen, gain=1.0):
     k = gain / math.sqrt(fan_in)
     return ((torch.rand(*shape, generator=gen) * 2 - 1) * k).to(torch.float16).to(torch.float32)
-
-
-class CpuBackend:
-    """libtorch CPU fp32: the calls the reference's default executors make."""
-    dev, dtype = "cpu", torch.float32
-
-    def put(self, t):
-        return t.clone()
-
-    def linear(self, x, W, b=None, relu=False):
-        y = torch.nn.functional.linear(x, W, b)
-        return torch.relu(y) if relu else y
-
-    def lstm_cell_stack(self, key, x, h, c, params, layers):
-        y, hn, cn = torch.lstm(x.view(1, 1, -1), [h, c], params, True, layers, 0.0, False, False, False)
-        return y.view(-1), hn, cn
-
-    def add(self, a, b):
-        return a + b
-
-    def bmm_row(self, x, A):
-        return x @ A
-
-    def cat(self, ts, dim):
-        return torch.cat(ts, dim)
-
-    def kv_new(self, steps, d):
-        return torch.zeros(0, d)
-
-    def kv_append(self, cache, t, row):
-        # the reference's form: the cache grows by an at::cat per step
-        return torch.cat([cache, row.view(1, -1)], 0) if cache.shape[0] else row.view(1, -1).clone()
-
-    def attend(self, q, K, Vv, heads):
-        # per-head scaled dot-product attention of one query over K / V [t, d]: matmul -> softmax -> matmul
-        d = q.numel()
-        hd = d // heads
-        qh = q.view(heads, 1, hd)
-        Kh = K.view(-1, heads, hd).transpose(0, 1)
-        Vh = Vv.view(-1, heads, hd).transpose(0, 1)
-        return (torch.softmax(qh @ Kh.transpose(1, 2) / math.sqrt(hd), -1) @ Vh).reshape(d)
-
-    def tanh(self, x):
-        return torch.tanh(x)
-
-    def softmax(self, x):
-        return torch.softmax(x, -1)
-
-    def layer_norm(self, x):
-        return torch.nn.functional.layer_norm(x, (x.shape[-1],))
-
-    def argmax(self, x):
-        return int(torch.argmax(x))
 
 
 class PimBackend:

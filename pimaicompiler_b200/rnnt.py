@@ -70,6 +70,19 @@ class RnntDecoder:
               "rnnt_profile_read")
         return {"ms": ms.value, "recurrences": n.value, "bytes": by.value}
 
+    def last_status(self) -> int:
+        """Device-side status of the decodes since the last call (0, or ERR_TIMEOUT when a bounded wait gave up);
+        synchronises the device and clears the status."""
+        return int(_lib.lib().pimb200_rnnt_last_status(self._h))
+
+    def check_status(self, where: str = "rnnt") -> None:
+        """Raises when a kernel of an earlier decode gave up; call after synchronising ``decode_into``'s stream."""
+        check(self.last_status(), where)
+
+    def set_poll_limit(self, limit: int) -> None:
+        """Test hook: iteration limit of the encoder recurrences' bounded waits."""
+        check(_lib.lib().pimb200_rnnt_set_poll_limit(self._h, int(limit)), "rnnt_set_poll_limit")
+
     def decode_into(self, feats: torch.Tensor, tokens: torch.Tensor, n_tokens: torch.Tensor,
                     logits: Optional[torch.Tensor] = None) -> None:
         """Asynchronous decode of feats [n_utts, T, feat_dim] into preallocated device outputs."""
@@ -90,7 +103,8 @@ class RnntDecoder:
         logits = torch.empty(n_utts, Tp, self.cfg.vocab, dtype=torch.float32, device=feats.device) if want_logits \
             else None
         self.decode_into(feats, tokens, n_tokens, logits)
-        n = n_tokens.cpu().tolist()
+        n = n_tokens.cpu().tolist()   # synchronises the stream
+        self.check_status("rnnt_decode")
         tk = tokens.cpu()
         out = [tk[u, : n[u]].tolist() for u in range(n_utts)]
         return (out, logits) if want_logits else out

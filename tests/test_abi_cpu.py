@@ -34,3 +34,18 @@ def test_bad_arguments_are_rejected_before_any_launch(pimlib):
     assert pimlib.pimb200_lstm_forward(None, 16, 1, 1, None, None, 16, None, None, 0, None) == _lib.ERR_BAD_ARG
     assert pimlib.pimb200_lstm_destroy(None) == _lib.OK
     assert pimlib.pimb200_init(-1) == _lib.ERR_BAD_ARG
+
+
+def test_every_exported_entry_point_is_declared(pimlib):
+    # the reverse direction: no extern "C" pimb200_* symbol of the library is missing from include/*.h
+    import shutil
+    import subprocess
+    import pytest
+    nm = shutil.which("nm")
+    if nm is None:
+        pytest.skip("binutils nm not available")
+    out = subprocess.run([nm, "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = sorted({line.split()[-1] for line in out.splitlines() if line.split() and line.split()[-1].startswith("pimb200_")})
+    declared = set(_lib.declared_symbols())
+    undeclared = [s for s in exported if s not in declared]
+    assert not undeclared, f"exported but not declared in include/*.h: {undeclared}"

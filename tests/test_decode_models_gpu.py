@@ -6,7 +6,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests import decode_models as dm
+from pimaicompiler_b200 import decode_models as dm
+from tests.cpu_backend import CpuBackend
 from tests.util import CONTRACT_ATOL, CONTRACT_RTOL, assert_close
 
 pytestmark = pytest.mark.gpu
@@ -27,7 +28,7 @@ def test_gnmt_style_greedy_decode(H, V, S, steps, gain):
     gen = torch.Generator().manual_seed(H + S)
     w = dm.make_gnmt(H, V, S, gen, gain)
     toks, logits = dm.gnmt_greedy(dm.PimBackend(), w, H, steps)
-    _, ref_logits = dm.gnmt_greedy(dm.CpuBackend(), w, H, steps, forced=toks)
+    _, ref_logits = dm.gnmt_greedy(CpuBackend(), w, H, steps, forced=toks)
     n = _check(toks, logits, ref_logits)
     print(f"GNMT H={H} V={V}: {n}/{steps} decided steps")
 
@@ -38,7 +39,7 @@ def test_transformer_style_greedy_decode(d, heads, ffn, V, layers, S, steps, gai
     gen = torch.Generator().manual_seed(d + S)
     w = dm.make_transformer(d, heads, ffn, V, layers, S, gen, gain)
     toks, logits = dm.transformer_greedy(dm.PimBackend(), w, d, heads, steps)
-    _, ref_logits = dm.transformer_greedy(dm.CpuBackend(), w, d, heads, steps, forced=toks)
+    _, ref_logits = dm.transformer_greedy(CpuBackend(), w, d, heads, steps, forced=toks)
     n = _check(toks, logits, ref_logits)
     print(f"Transformer d={d} V={V}: {n}/{steps} decided steps")
 

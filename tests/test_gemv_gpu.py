@@ -139,7 +139,7 @@ def test_dot_vv_and_bmm_row():
 
 
 @pytest.mark.parametrize("B", [8, 32, 128])
-@pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 1024), (29, 512)])
+@pytest.mark.parametrize("N,K", [(4096, 1024), (4096, 2048), (1024, 1024), (32320, 1024), (29, 512)])
 def test_batched_stream_gemm(N, K, B):
     ops = _ops()
     W, b, X = _c2_inputs(N, K, B)

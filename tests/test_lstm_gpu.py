@@ -210,6 +210,15 @@ def test_persistent_bounded_wait_reports_timeout_and_context_survives(B):
     assert m.last_status() == 0
     ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, False)
     assert_close(y, ref[0], LSTM_ATOL, LSTM_RTOL, "after a timed-out launch")
+    # a timed-out launch must not poison the launches behind it: nobody reads (and thereby clears) the status between
+    # the two calls here, the second call must be correct all the same, and the time-out is still reported afterwards
+    assert lib.pimb200_lstm_set_poll_limit(m._h, 1) == 0
+    m.forward(to_dev(x))
+    assert lib.pimb200_lstm_set_poll_limit(m._h, 1 << 21) == 0
+    y2, _, _ = m.forward(to_dev(x))
+    torch.cuda.synchronize()
+    assert_close(y2, ref[0], LSTM_ATOL, LSTM_RTOL, "directly behind a timed-out launch, status unread")
+    assert m.last_status() == _lib.ERR_TIMEOUT
 
 
 @pytest.mark.parametrize("T,B,I,H", [(6, 64, 64, 1024), (9, 23, 32, 256), (5, 40, 16, 128)])
@@ -260,3 +269,27 @@ def test_lstm_benchmark_shape_batched_properties():
     for n in (0, 37, 63):
         y1, hn1, cn1 = m.forward(x[n:n + 1].contiguous(), batch_first=True)
         assert torch.equal(y1[0], y[n]) and torch.equal(hn1[:, 0], hn[:, n]) and torch.equal(cn1[:, 0], cn[:, n])
+
+
+def test_lstm_benchmark_shape_batched_vs_libtorch():
+    # the benchmark's pre-net recurrence at full size (2 layers, 240 -> 1024, 1000 steps, 64 sequences in lock step,
+    # batch-first) against live libtorch CPU fp32 for three of the 64 sequences: the whole output sequence, h_n and c_n.
+    # fp16 hidden states feed back through 1000 steps here; the error at the last step is printed.
+    ops = _ops()
+    g = torch.Generator().manual_seed(65)
+    T, B, I, H, L = 1000, 64, 240, 1024, 2
+    ps = lstm_params(L, 1, I, H, g, scale=1 / 32)
+    x = h16(torch.randn(B, T, I, generator=g))
+    m = ops.Lstm([to_dev(p) for p in ps], L, False, I, H, True)
+    y, hn, cn = m.forward(to_dev(x), batch_first=True)
+    torch.cuda.synchronize()
+    assert m.last_status() == 0
+    z = torch.zeros(L, 1, H)
+    for n in (0, 21, 63):
+        with torch.no_grad():
+            yr, hr, cr = torch.lstm(x[n:n + 1], [z, z], ps, True, L, 0.0, False, False, True)
+        e = assert_close(y[n], yr[0], CONTRACT_ATOL, CONTRACT_RTOL, f"y of sequence {n} at T=1000, B=64")
+        e_last = float((y[n, -1].float().cpu() - yr[0, -1]).abs().max())
+        assert_close(hn[:, n], hr[:, 0], CONTRACT_ATOL, CONTRACT_RTOL, f"h_n of sequence {n}")
+        assert_close(cn[:, n], cr[:, 0], CONTRACT_ATOL, CONTRACT_RTOL, f"c_n of sequence {n}")
+        print(f"sequence {n}: max err over 1000 steps {e:.2e}, at the last step {e_last:.2e}")

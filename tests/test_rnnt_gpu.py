@@ -63,8 +63,26 @@ def test_rnnt_baseline_config_vs_libtorch():
     # free-running oracle: identical transcript when every frame is decided
     ref_tokens, ref_logits, _ = to.rnnt_greedy(w, feats, cfg)
     srt = np.sort(ref_logits.numpy(), axis=1)
-    if ((srt[:, -1] - srt[:, -2]) > MARGIN).all():
+    all_decided = bool(((srt[:, -1] - srt[:, -2]) > MARGIN).all())
+    print(f"free-running transcript compared: {all_decided}")
+    if all_decided:
         assert toks[0] == ref_tokens
+    # the free-running comparison must not be vacuous: a model with sharper logits (every frame decided) is decoded
+    # freely on both sides and the transcripts must be identical
+    w2 = to.make_rnnt_weights(cfg, seed=3, gain=2.0, logit_gain=30.0)
+    dec2 = _decoder(cfg, w2)
+    compared = 0
+    for s in range(6):
+        f2 = to.make_features(120, cfg, 40 + s)
+        ref_t, ref_l, _ = to.rnnt_greedy(w2, f2, cfg)
+        srt2 = np.sort(ref_l.numpy(), axis=1)
+        if not ((srt2[:, -1] - srt2[:, -2]) > MARGIN).all():
+            continue
+        t2, _ = dec2.decode(f2.to(torch.float16).cuda(), want_logits=True)
+        assert t2[0] == ref_t, "free-running transcript differs although every frame is decided"
+        compared += 1
+    print(f"free-running transcripts compared on the sharper model: {compared} of 6")
+    assert compared >= 2
 
 
 def test_rnnt_baseline_config_blank_mix():
@@ -169,3 +187,64 @@ def test_rnnt_benchmark_scale_is_independent_of_batching():
     assert torch.equal(logits16, logits[:16])
     lens = [len(t) for t in toks]
     assert 0 < min(lens) and max(lens) <= 500 and len(set(lens)) > 1   # transcripts differ, none empty
+
+
+def test_rnnt_benchmark_configuration_vs_libtorch_full_length():
+    # The configuration the benchmark times: 1000 frames per utterance, 64 utterances advanced in lock step (the
+    # 64-sequence recurrence kernel, the batched joint GEMM and the tensor-core greedy kernel).  Three utterances taken
+    # out of that call, and the same three decoded alone (the one-sequence recurrence and the one-utterance greedy
+    # kernel), are compared with libtorch CPU fp32 over all 500 joint frames: logits within the contract, token ids
+    # equal to the oracle's arg max wherever its top-2 margin exceeds MARGIN.  fp16 hidden states feed back through
+    # 1000 steps of five layers here, which shorter utterances do not exercise.
+    cfg = to.RnntConfig()
+    w = to.make_rnnt_weights(cfg, seed=9, gain=2.0, logit_gain=8.0)
+    w.b2[cfg.blank] += 1.5
+    w.b2 = w.b2.to(torch.float16).to(torch.float32)
+    dec = _decoder(cfg, w)
+    g = torch.Generator().manual_seed(64)
+    feats = torch.randn(64, 1000, cfg.feat_dim, generator=g).to(torch.float16)
+    toks, logits = dec.decode(feats.cuda(), want_logits=True)
+    assert logits.shape == (64, 500, cfg.vocab)
+    for i in (0, 37, 63):
+        f32 = feats[i].float()
+        nd, Tp, err = _check_utterance(cfg, w, f32, toks[i], logits[i].cpu().numpy(), to.rnnt_greedy)
+        ref = np.asarray(to.rnnt_greedy(w, f32, cfg, logits[i].argmax(1).tolist())[1])
+        err_last = float(np.abs(logits[i, Tp - 1].cpu().numpy() - ref[Tp - 1]).max())
+        print(f"utterance {i} in a 64-utterance call: decided frames {nd}/{Tp}, max logit err {err:.2e}, "
+              f"at frame {Tp - 1}: {err_last:.2e}, {len(toks[i])} tokens")
+        assert nd > Tp // 2
+        t1, l1 = dec.decode(feats[i].cuda(), want_logits=True)
+        nd1, _, err1 = _check_utterance(cfg, w, f32, t1[0], l1[0].cpu().numpy(), to.rnnt_greedy)
+        print(f"utterance {i} decoded alone: decided frames {nd1}/{Tp}, max logit err {err1:.2e}")
+
+
+def test_rnnt_timeout_is_reported_and_does_not_poison_later_decodes():
+    # Fault handling without faulting anything: the encoder recurrences' bounded waits are shrunk to one poll, so the
+    # first decode gives up; decode() must raise ERR_TIMEOUT.  A second timed-out decode is then issued through the
+    # asynchronous entry point and nobody reads the status; the decode behind it (normal limit) must still be correct,
+    # and the time-out must still be on record afterwards.
+    from pimaicompiler_b200 import _lib
+    cfg = to.RnntConfig(feat_dim=24, enc_hidden=256, pred_hidden=32, joint_hidden=48, vocab=11, blank=10)
+    w = to.make_rnnt_weights(cfg, seed=11, gain=2.0, logit_gain=6.0)
+    dec = _decoder(cfg, w)
+    feats = to.make_features(64, cfg, 77)
+    dev = feats.to(torch.float16).cuda().unsqueeze(0).contiguous()
+    good_tokens, good_logits = dec.decode(dev, want_logits=True)
+    _check_utterance(cfg, w, feats, good_tokens[0], good_logits[0].cpu().numpy(), co.rnnt_greedy)
+    dec.set_poll_limit(1)
+    with pytest.raises(_lib.Pimb200Error) as e:
+        dec.decode(dev)
+    assert e.value.status == _lib.ERR_TIMEOUT
+    assert dec.last_status() == 0                      # reading cleared it
+    Tp = 32
+    tokens = torch.zeros(1, Tp, dtype=torch.int32, device="cuda")
+    n_tokens = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dec.decode_into(dev, tokens, n_tokens)             # gives up again; status left unread
+    dec.set_poll_limit(1 << 21)
+    logits = torch.empty(1, Tp, cfg.vocab, dtype=torch.float32, device="cuda")
+    dec.decode_into(dev, tokens, n_tokens, logits)
+    torch.cuda.synchronize()
+    assert torch.equal(logits, good_logits)
+    assert tokens[0, : int(n_tokens[0])].tolist() == good_tokens[0]
+    assert dec.last_status() == _lib.ERR_TIMEOUT       # the earlier time-out is still reported
+    assert dec.last_status() == 0
