@@ -229,10 +229,17 @@ int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrenc
  * rows per CTA), so the default is 0.  No counterpart in the reference. */
 int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on);
 
-/* A/B switch between the two batched persistent recurrences (2..64 lock-step sequences): 1 (default) = the kernel
- * that keeps its W_hh slice in registers (H <= 1024), 0 = the K-split kernel with W_hh in shared memory (up to 32
- * sequences; also what H > 1024 falls back to).  Same results.  No counterpart in the reference. */
+/* A/B switch between the batched persistent recurrences (1..64 lock-step sequences, H <= 1024): 2 (default) = the
+ * pipelined kernel (W_hh slice in registers; the sequences advance as independent groups, so one group's hidden-state
+ * exchange runs under the other groups' arithmetic), 1 = the same arithmetic with the exchange on the compute warps,
+ * 0 = the K-split kernel with W_hh in shared memory (up to 32 sequences; also what H > 1024 falls back to).  Results
+ * agree within the LSTM tolerance; within one setting they do not depend on the batch size.  No counterpart in the
+ * reference. */
 int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on);
+
+/* Tuning switch of the pipelined kernel for 33..64 sequences: 2 (or 0, the default) = two groups of 32 sequences,
+ * 4 = four groups of 16.  Same results.  No counterpart in the reference. */
+int pimb200_lstm_set_pipe_groups(pimb200_lstm* h, int groups);
 
 /* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are

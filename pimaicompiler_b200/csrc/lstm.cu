@@ -999,6 +999,381 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 }
 
 // ---------------------------------------------------------------------------------------------
+// pipelined variant of the register-resident recurrence (the default for 1..64 sequences, H <= 1024)
+//
+// Same ownership as the wide kernel (CTA c owns hidden units 8c..8c+7 = 32 gate rows, H/8 CTAs, W_hh slice in registers
+// as mma A fragments) and the same exchange protocol (16-byte records + per-CTA step flags + bulk-copy gather), but the
+// sequences of a launch are split into NG groups of BPG = 8*NTG that advance independently, and the exchange is taken off
+// the compute warps:
+//   * warps 0..7 (compute) split K eight ways (warp w owns k-tiles w, w+8, ...; no duplication of A fragments: 64
+//     registers per thread) and run, for one group after the other: wait for the group's gathered hidden states ->
+//     tensor-core partial products -> one CTA barrier -> gates -> arrive on the group's "done" mbarrier.  While group g
+//     is exchanged, the other groups compute, so the two L2 round trips of the exchange no longer sit on the critical
+//     path of a step.  The K-partials of consecutive group phases alternate between two buffers, so no second barrier
+//     is needed between the gate reads of one phase and the partial-sum writes of the next.
+//   * warp 8 (publisher) waits for "done", stores the group's records (and the y rows) and raises the step flags.
+//   * warp 9 (gatherer) polls the flags of all CTAs for (step, group), 32 CTAs per lane round, and hands each chunk of
+//     32 CTAs' records to the bulk-copy engine as soon as its flags are up (no cluster multicast); the copies complete
+//     on the group's "full" mbarrier, which the compute warps wait on.
+// Per-sequence arithmetic (k-tile order inside a warp's accumulator, order of the eight partial sums) is the same for
+// every NTG / NG, so a sequence's result does not depend on how many sequences share the launch.
+// Every wait is bounded and ends early once the launch's generation appears in the status block.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPipeComputeWarps = 8;
+constexpr int kPipeComputeThreads = kPipeComputeWarps * 32;
+constexpr int kPipeThreads = kPipeComputeThreads + 64;   // + publisher warp + gatherer warp
+constexpr int kPipeKtw = 8;          // k-tiles per compute warp held in registers (H <= 1024)
+constexpr int kPipeMaxGroups = 4;
+constexpr int kPipeChunk = 32;       // CTAs per gather chunk (one flag per lane)
+constexpr int kPipeMaxChunks = 4;    // H <= 1024: at most 128 CTAs
+
+struct PipeArgs {
+    const __half* Whh;
+    const float* bias;
+    const float* G;
+    long g_tstride, g_bstride;
+    const __half* h0;
+    const __half* c0;
+    __half* y;
+    long y_tstride, y_bstride;
+    int y_vec;
+    __half* hn;
+    __half* cn;
+    uint4* data;            // [2 parities][NG][n_cta][BPG] 16-byte records
+    uint32_t* flags;        // [kBulkFlagCopies][2 parities][kPipeMaxGroups][n_cta] step tags, one per 128-byte line
+    uint32_t tag_base;
+    int* status;
+    int gen;
+    int H, T, B;
+    int reverse;
+    int poll_limit;
+    long long* trace;       // optional: 8 clocks per CTA and step (compute thread 0)
+};
+
+__device__ __forceinline__ void bar_sync_named(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// named-barrier OR reduction: true when `pred` holds in any participating thread
+__device__ __forceinline__ bool bar_red_or_named(int id, int count, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %3, 0;\n\t"
+        "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"(id), "r"(count), "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded mbarrier wait in polls (not clocks); false = gave up or the launch was aborted
+__device__ __forceinline__ bool mbar_wait_polls(uint32_t bar, uint32_t parity, const int* status, int gen, int limit) {
+    for (int i = 0; i < limit; ++i) {
+        if (pimb200::tc::mbar_try_wait(bar, parity)) return true;
+        if ((i & 255) == 255 && status_aborted(status, gen)) return false;
+    }
+    return false;
+}
+
+template <int NTG, int NG>
+__global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(PipeArgs a) {
+    constexpr int BPG = NTG * 8;                      // sequences per group (padded to whole mma tiles)
+    static_assert(BPG <= 32 && NG <= kPipeMaxGroups, "one publisher lane per sequence of a group");
+    constexpr int ZP = BPG + 1;                       // padded sequence pitch of the partial sums
+    constexpr int ZBUF = kPipeComputeWarps * 8 * ZP * 4;   // floats per partial-sum buffer: [k-eighth][unit][ZP][gate]
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, T = a.T, B = a.B;
+    __half* hs = reinterpret_cast<__half*>(smem_raw);                                  // [NG][H/8][BPG][8]
+    float* zpart = reinterpret_cast<float*>(hs + (size_t)NG * BPG * H);                // [2][ZBUF]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + 2 * ZBUF);        // [NG][BPG][8]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(hpub + (size_t)NG * BPG * 8);         // full[NG], done[NG]
+    const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(bars);
+    const uint32_t done0 = full0 + 8u * NG;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x, cta = blockIdx.x;
+    const int u0 = cta * 8;
+    const int ktiles = H >> 4;
+    const int nchunks = (n_cta + kPipeChunk - 1) / kPipeChunk;
+    // a wait on an mbarrier may take as long as the slowest CTA's flag: same budget as the gatherer's polls
+    const int wait_limit = a.poll_limit < (1 << 27) ? a.poll_limit * 8 : a.poll_limit;
+    if (tid == 0) {
+        for (int g = 0; g < NG; ++g) {
+            pimb200::tc::mbar_init(full0 + 8u * g, (uint32_t)nchunks);          // one arrival (+ bytes) per chunk
+            pimb200::tc::mbar_init(done0 + 8u * g, (uint32_t)kPipeComputeThreads);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // initial hidden states, in the layout of the exchange records: hs[g][j][n][8] = units 8j..8j+7 of sequence g*BPG+n
+    for (int i = tid; i < NG * BPG * H; i += kPipeThreads) {
+        const int n = i / H, k = i - n * H;
+        const int g = n / BPG, nl = n - g * BPG;
+        hs[(size_t)g * BPG * H + ((size_t)(k >> 3) * BPG + nl) * 8 + (k & 7)] =
+            (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
+    }
+    for (int i = tid; i < NG * BPG * 8; i += kPipeThreads) hpub[i] = 0;
+    __syncthreads();
+
+    if (warp < kPipeComputeWarps) {
+        // ================================ compute warps ================================
+        const int b_n = lane >> 2, b_k = (lane & 3) * 2;
+        uint32_t afrag[kPipeKtw][2][4];   // afrag[i][m] = rows 16m..16m+15 of the slice, k-tile 8i + warp
+        {
+            const __half* wbase = a.Whh + (size_t)u0 * 4 * H;
+#pragma unroll
+            for (int i = 0; i < kPipeKtw; ++i)
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        afrag[i][m][r] = 0u;
+                        if (kPipeComputeWarps * i + warp < ktiles) {
+                            const int row = m * 16 + b_n + (r & 1) * 8;
+                            const int k = (kPipeComputeWarps * i + warp) * 16 + b_k + (r >> 1) * 8;
+                            afrag[i][m][r] = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)row * H + k));
+                        }
+                    }
+        }
+        // gate cell of this thread in every group: unit gu, local sequence gn
+        const int gu = tid / BPG, gn = tid - gu * BPG;
+        const bool cell = tid < 8 * BPG;
+        float c[NG];
+        float4 gx[NG];
+        bool live[NG];
+        float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (cell) bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)(u0 + gu) * 4);
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+            const int n = g * BPG + gn;
+            live[g] = cell && n < B;
+            c[g] = 0.f;
+            gx[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live[g]) {
+                c[g] = a.c0 ? __half2float(a.c0[(size_t)n * H + u0 + gu]) : 0.f;
+                const int t0 = a.reverse ? T - 1 : 0;
+                gx[g] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)n * a.g_bstride +
+                                                               (size_t)(u0 + gu) * 4));
+            }
+        }
+        int phase = 0;      // group phases executed so far: selects the partial-sum buffer
+        bool dead = false;
+        for (int s = 0; s < T && !dead; ++s) {
+            const int t = a.reverse ? T - 1 - s : s;
+            long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                if (g * BPG >= B) break;   // uniform: groups beyond the batch do not exist
+                if (tr && tid == 0 && g < 2) tr[g * 4 + 0] = clock64();
+                bool ok = true;
+                if (s > 0) ok = mbar_wait_polls(full0 + 8u * g, (uint32_t)((s - 1) & 1), a.status, a.gen, wait_limit);
+                if (tr && tid == 0 && g < 2) tr[g * 4 + 1] = clock64();
+                // ---- K-partial products of this warp for group g
+                float* zq = zpart + (size_t)(phase & 1) * ZBUF + (size_t)warp * 8 * ZP * 4;
+                {
+                    float acc[2][NTG][4];
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+#pragma unroll
+                        for (int j = 0; j < NTG; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+                    const __half* brow = hs + (size_t)g * BPG * H + (size_t)b_n * 8 + b_k;
+#pragma unroll
+                    for (int i = 0; i < kPipeKtw; ++i) {
+                        if (kPipeComputeWarps * i + warp < ktiles) {   // warp-uniform
+                            const int kt = kPipeComputeWarps * i + warp;
+                            const __half* hp = brow + (size_t)(2 * kt) * BPG * 8;
+                            uint32_t b0[NTG], b1[NTG];
+#pragma unroll
+                            for (int j = 0; j < NTG; ++j) {
+                                b0[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64);
+                                b1[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64 + (size_t)BPG * 8);
+                            }
+#pragma unroll
+                            for (int j = 0; j < NTG; ++j) {
+                                mma_16816(acc[0][j], afrag[i][0], b0[j], b1[j]);
+                                mma_16816(acc[1][j], afrag[i][1], b0[j], b1[j]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+#pragma unroll
+                        for (int j = 0; j < NTG; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int r = m * 16 + b_n + (i >> 1) * 8, n = j * 8 + b_k + (i & 1);
+                                zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][j][i];
+                            }
+                }
+                // the one CTA barrier of a group phase; it also carries whether any thread's wait gave up
+                if (bar_red_or_named(1, kPipeComputeThreads, !ok)) {
+                    if (tid == 0) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+                    dead = true;
+                    break;
+                }
+                if (tr && tid == 0 && g < 2) tr[g * 4 + 2] = clock64();
+                // ---- gates of cell (gu, gn) of group g
+                if (cell) {
+                    const float* zb = zpart + (size_t)(phase & 1) * ZBUF + ((size_t)gu * ZP + gn) * 4;
+                    float zi = gx[g].x + bias4.x, zf = gx[g].y + bias4.y, zg = gx[g].z + bias4.z, zo = gx[g].w + bias4.w;
+#pragma unroll
+                    for (int k = 0; k < kPipeComputeWarps; ++k) {
+                        const float4 zk = *reinterpret_cast<const float4*>(zb + (size_t)k * 8 * ZP * 4);
+                        zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
+                    }
+                    c[g] = sigmoidf_(zf) * c[g] + sigmoidf_(zi) * tanhf_(zg);
+                    const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c[g]));
+                    if (live[g]) {
+                        const int n = g * BPG + gn, u = u0 + gu;
+                        hpub[((size_t)g * BPG + gn) * 8 + gu] = __half_as_ushort(hh);
+                        if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh;
+                        if (s == T - 1) {
+                            if (a.hn) a.hn[(size_t)n * H + u] = hh;
+                            if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[g]);
+                        }
+                    }
+                }
+                mbar_arrive(done0 + 8u * g);   // release: the publisher reads hpub after this phase completes
+                // next step's input-projection term of this cell, a whole step ahead of its use
+                if (live[g] && s + 1 < T) {
+                    const int tn = a.reverse ? t - 1 : t + 1;
+                    const float* gp = a.G + (size_t)tn * a.g_tstride + (size_t)(g * BPG + gn) * a.g_bstride +
+                                      (size_t)(u0 + gu) * 4;
+                    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(gx[g].x), "=f"(gx[g].y), "=f"(gx[g].z), "=f"(gx[g].w)
+                                 : "l"(gp));
+                }
+                if (tr && tid == 0 && g < 2) tr[g * 4 + 3] = clock64();
+                ++phase;
+            }
+        }
+    } else if (warp == kPipeComputeWarps) {
+        // ================================ publisher warp ================================
+        for (int s = 0; s < T; ++s) {
+            const int t = a.reverse ? T - 1 - s : s;
+            const int par = s & 1;
+            const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+            bool dead = false;
+            for (int g = 0; g < NG; ++g) {
+                if (g * BPG >= B) break;
+                if (!mbar_wait_polls(done0 + 8u * g, (uint32_t)(s & 1), a.status, a.gen, wait_limit)) { dead = true; break; }
+                const int n = g * BPG + lane;
+                if (lane < BPG && n < B) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(hpub + ((size_t)g * BPG + lane) * 8);
+                    if (s + 1 < T) {
+                        a.data[(((size_t)par * NG + g) * n_cta + cta) * BPG + lane] = v;
+                        // the record is read by the other CTAs' bulk copies (async proxy): cross-proxy fence on the
+                        // writer side, in front of the flag's release
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
+                    if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u0) = v;
+                }
+                __syncwarp();
+                if (s + 1 < T && lane < kBulkFlagCopies)
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(
+                                     a.flags + ((((size_t)lane * 2 + par) * kPipeMaxGroups + g) * n_cta + cta) * 32),
+                                 "r"(tag)
+                                 : "memory");
+            }
+            if (dead) break;
+        }
+    } else {
+        // ================================ gatherer warp ================================
+        const int rep = cta % kBulkFlagCopies;
+        bool dead = false;
+        for (int s = 0; s + 1 < T && !dead; ++s) {
+            const int par = s & 1;
+            const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+            for (int g = 0; g < NG && !dead; ++g) {
+                if (g * BPG >= B) break;
+                const uint32_t* fbase = a.flags + ((((size_t)rep * 2 + par) * kPipeMaxGroups + g) * n_cta) * 32;
+                const unsigned char* src = reinterpret_cast<const unsigned char*>(a.data + ((size_t)par * NG + g) * n_cta * BPG);
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(hs + (size_t)g * BPG * H);
+                const uint32_t fbar = full0 + 8u * g;
+                // lane l watches CTA 32i + l of every chunk i; a chunk's copy is issued as soon as its 32 flags are up
+                uint32_t seen = 0;      // bit i: this lane's flag of chunk i carries the tag (or there is no such CTA)
+                uint32_t issued = 0;    // bit i: chunk i's copy has been handed to the copy engine (warp-uniform)
+#pragma unroll
+                for (int i = 0; i < kPipeMaxChunks; ++i)
+                    if (i >= nchunks || i * kPipeChunk + lane >= n_cta) seen |= 1u << i;
+                for (int i = nchunks; i < kPipeMaxChunks; ++i) issued |= 1u << i;
+                constexpr uint32_t all_chunks = (1u << kPipeMaxChunks) - 1u;
+                int polls = 0;
+                while (issued != all_chunks) {
+                    // all of this lane's outstanding flags are loaded before any is looked at: up to four loads in flight
+                    uint32_t v[kPipeMaxChunks];
+#pragma unroll
+                    for (int i = 0; i < kPipeMaxChunks; ++i) {
+                        v[i] = tag;
+                        if (!(seen >> i & 1u))
+                            asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];"
+                                         : "=r"(v[i])
+                                         : "l"(fbase + (size_t)(i * kPipeChunk + lane) * 32)
+                                         : "memory");
+                    }
+#pragma unroll
+                    for (int i = 0; i < kPipeMaxChunks; ++i)
+                        if (v[i] == tag) seen |= 1u << i;
+#pragma unroll
+                    for (int i = 0; i < kPipeMaxChunks; ++i) {
+                        if ((issued >> i & 1u) || !__all_sync(0xffffffffu, seen >> i & 1u)) continue;
+                        // acquire: one acquire load of the flag just seen, then the warp-wide sync orders every
+                        // lane's acquire before lane 0's copy
+                        if (i * kPipeChunk + lane < n_cta) {
+                            uint32_t w;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
+                                         : "=r"(w)
+                                         : "l"(fbase + (size_t)(i * kPipeChunk + lane) * 32)
+                                         : "memory");
+                        }
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int c0 = i * kPipeChunk, c1 = c0 + kPipeChunk < n_cta ? c0 + kPipeChunk : n_cta;
+                            const uint32_t off = (uint32_t)c0 * BPG * 16u, len = (uint32_t)(c1 - c0) * BPG * 16u;
+                            pimb200::tc::mbar_expect_tx(fbar, len);
+                            asm volatile(
+                                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + off),
+                                "l"(src + off), "r"(len), "r"(fbar)
+                                : "memory");
+                        }
+                        issued |= 1u << i;
+                    }
+                    if (issued == all_chunks) break;
+                    ++polls;
+                    bool lost = polls >= a.poll_limit;
+                    if ((polls & 255) == 0 && status_aborted(a.status, a.gen)) lost = true;
+                    if (__any_sync(0xffffffffu, lost)) {
+                        // a flag never came: arrive without bytes for the chunks not issued, so that the barrier still
+                        // completes once the copies that were issued have landed; then leave
+                        if (lane == 0) {
+                            status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+                            for (int i = 0; i < nchunks; ++i)
+                                if (!(issued >> i & 1u)) mbar_arrive(fbar);
+                        }
+                        dead = true;
+                        break;
+                    }
+                }
+                if (dead) {
+                    // before the CTA hands its shared memory back, give the copies in flight (this group's and the ones
+                    // issued for the other groups just before) a bounded chance to land
+                    for (int gg = 0; gg < NG; ++gg) {
+                        const int last_s = gg <= g ? s : s - 1;
+                        if (last_s < 0 || gg * BPG >= B) continue;
+                        for (uint32_t i = 0; i < (1u << 20); ++i)
+                            if (pimb200::tc::mbar_try_wait(full0 + 8u * gg, (uint32_t)(last_s & 1))) break;
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();   // no warp leaves (and no shared memory is handed back) before all roles are done
+}
+
+// ---------------------------------------------------------------------------------------------
 // tcgen05 variant of the batched recurrence (17..64 sequences, H a multiple of 64), opt-in.
 //
 // The per-step product Z[32 x BP] = W_slice[32 x H] . Hprev[H x BP] runs on the 5th-generation tensor cores: one
@@ -1262,7 +1637,9 @@ struct pimb200_lstm {
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
     int use_tc = 0;        // 1 = tcgen05 recurrence for 17..64 sequences (measured slower than mma.sync here: opt-in)
-    int bulk_wide = 1;     // 1 = register-resident (wide) kernel for 2..64 sequences, 0 = K-split kernel only (up to 32)
+    int bulk_wide = 2;     // 2 = pipelined register-resident kernel (default), 1 = wide kernel (exchange on the compute warps),
+                           // 0 = K-split kernel with W_hh in shared memory (up to 32 sequences)
+    int pipe_groups = 0;   // groups of the pipelined kernel for 33..64 sequences: 0 / 2 = two of 32, 4 = four of 16
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
@@ -1350,7 +1727,7 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
     {
         const size_t ncta = (size_t)ceil_div(H, 8);
         if (cudaMalloc(&h->bulk_data, 2 * ncta * kBulkMaxB * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
-        const size_t flag_bytes = (size_t)kBulkFlagCopies * 2 * ncta * 128;
+        const size_t flag_bytes = (size_t)kBulkFlagCopies * 2 * kPipeMaxGroups * ncta * 128;   // the pipelined kernel's layout is the largest
         if (cudaMalloc(&h->bulk_flags, flag_bytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
         cudaMemset(h->bulk_flags, 0, flag_bytes);
     }
@@ -1419,7 +1796,13 @@ extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
 // A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
-    h->bulk_wide = on > 0 ? 1 : 0;
+    h->bulk_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
+    return PIMB200_OK;
+}
+// A/B switch of the pipelined kernel for 33..64 sequences: 2 = two groups of 32 (default), 4 = four groups of 16.
+extern "C" int pimb200_lstm_set_pipe_groups(pimb200_lstm* h, int groups) {
+    if (!h || (groups != 0 && groups != 2 && groups != 4)) return PIMB200_ERR_BAD_ARG;
+    h->pipe_groups = groups;
     return PIMB200_OK;
 }
 extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
@@ -1457,6 +1840,11 @@ static int grow(T** p, size_t* cap, size_t need_elems) {
 static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
     return (size_t)BP * H * 2 + (size_t)kWideKq * 8 * (BP + 1) * 16 + (size_t)BP * 16 + 16;
+}
+static size_t pipe_smem(int H, int ntg, int ng) {
+    const int BPG = ntg * 8;
+    return (size_t)ng * BPG * H * 2 + (size_t)2 * kPipeComputeWarps * 8 * (BPG + 1) * 16 + (size_t)ng * BPG * 16 +
+           (size_t)2 * ng * 8 + 16;
 }
 static size_t tc_smem(int H, int BP) {
     return (size_t)(H / 64) * (kPersistRows * 128 + BP * 128) + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16 + 64 + 1024;
@@ -1539,6 +1927,39 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
             h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
         }
         return PIMB200_OK;
+    }
+    // pipelined register-resident recurrence: the default wherever the wide kernel applies
+    if (wide && h->bulk_wide >= 2 && bulk_fits && !tc_fits &&
+        (h->variant == PIMB200_LSTM_PERSISTENT || (h->variant == PIMB200_LSTM_AUTO && T >= 8))) {
+        int ntg, ng;
+        if (B <= 16) { ntg = 2; ng = 1; }
+        else if (B <= 32) { ntg = 2; ng = 2; }
+        else if (h->pipe_groups == 4) { ntg = 2; ng = 4; }
+        else { ntg = 4; ng = 2; }
+        const size_t smem = pipe_smem(H, ntg, ng);
+        if ((int)smem <= h->max_smem_optin) {
+            PipeArgs a;
+            a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
+            a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
+            a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
+            a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
+            a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+            a.trace = h->trace;
+            h->bulk_tag += (uint32_t)T + 1u;
+            const void* fn = ng == 1   ? (const void*)lstm_persistent_pipe_kernel<2, 1>
+                             : ntg == 4 ? (const void*)lstm_persistent_pipe_kernel<4, 2>
+                             : ng == 2  ? (const void*)lstm_persistent_pipe_kernel<2, 2>
+                                        : (const void*)lstm_persistent_pipe_kernel<2, 4>;
+            PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            void* kargs[] = {&a};
+            if (h->prof) prof_mark(h, st);
+            PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(kPipeThreads), kargs, smem, st));
+            if (h->prof) {
+                prof_mark(h, st);
+                h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
+            }
+            return PIMB200_OK;
+        }
     }
     bool use_bulk = false;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
