@@ -5,7 +5,7 @@ features, batch 1 per stream, random-init weights of the benchmark architecture)
     python bench.py [--gpus N] [--steps K] [--warmup W] [--streams-total S] [--impl reference]
 
 One "step" = the benchmark configuration's 1024 utterance streams, sharded over the N ranks (1024 / N per rank,
-decoded in calls of 128 utterances).  Utterances are independent, so ranks share nothing on the data path
+decoded in one call per rank: encoder groups of 128 utterances, one greedy launch).  Utterances are independent, so ranks share nothing on the data path
 ("strong" scaling: the total is fixed; no collective); torch.distributed is used only for the barrier and the
 max-over-ranks of the device time.  The same line carries the stand-alone LSTM (C1) and GEMV (C2) figures of the
 baseline metric under the keys `lstm_c1` and `gemv`.  Prints ONE JSON line on rank 0.
@@ -41,7 +41,7 @@ def base_config(streams_total: int) -> dict:
                   "features + activations) also exceeds the 126 MB L2"}
 
 
-RECURRENCE_KERNEL = "lstm_persistent_wide_kernel<8> (W_hh recurrence, all T steps of 64 sequences per launch)"
+RECURRENCE_KERNEL = "lstm_persistent_pipe_kernel<16,2,4> (W_hh recurrence, all T steps of 128 sequences per launch)"
 
 
 def load_tensor_peak():
@@ -197,7 +197,7 @@ def run_gpu(args, rank, world, local):
     # this rank's shard of the configuration's streams, decoded in calls of `chunk` utterances
     streams_total = args.streams_per_gpu * world if args.streams_per_gpu else args.streams_total
     S = (streams_total + world - 1) // world
-    chunk = min(args.streams_per_call, S)
+    chunk = min(args.streams_per_call, S) if args.streams_per_call > 0 else S
     Tp = T_FRAMES // cfg.stack_factor
     g = torch.Generator().manual_seed(1000 + rank)
     feats_host = torch.randn(S, T_FRAMES, cfg.feat_dim, generator=g).to(torch.float16).pin_memory()
@@ -285,14 +285,14 @@ def run_gpu(args, rank, world, local):
     rec_s = prof["ms"] * 1e-3
     achieved = prof["bytes"] / rec_s / 1e9 if rec_s > 0 else 0.0
     share = prof["ms"] / sum(step_ms) if sum(step_ms) > 0 else 0.0
-    eb = min(args.encoder_batch or 64, chunk)
+    eb = min(args.encoder_batch or 128, chunk)
     # the same launches as a contraction: 2 flop per weight element and sequence and timestep
     flops = prof["bytes"] / 2.0 * 2.0 * eb
     tflops = flops / rec_s / 1e12 if rec_s > 0 else 0.0
     # per call of `chunk` utterances: per group of encoder-batch utterances (projection GEMM + recurrence) per LSTM
-    # layer and the joint's encoder-half GEMM; then one greedy kernel for the whole call
+    # layer; then the joint's encoder-half GEMM and one greedy kernel for the whole call
     calls = (S + chunk - 1) // chunk
-    launches_per_step = calls * (((chunk + eb - 1) // eb) * (2 * (cfg.pre_layers + cfg.post_layers) + 1) + 1)
+    launches_per_step = calls * (((chunk + eb - 1) // eb) * 2 * (cfg.pre_layers + cfg.post_layers) + 2)
 
     extras = {}
     if rank == 0 and not args.no_extras:
@@ -585,7 +585,9 @@ def main():
                     help="utterance streams of one step, sharded over the ranks (the configuration's 1024)")
     ap.add_argument("--streams-per-gpu", type=int, default=0,
                     help="overrides --streams-total with a per-rank count (profiling runs on small cases)")
-    ap.add_argument("--streams-per-call", type=int, default=128, help="utterances per decode call")
+    ap.add_argument("--streams-per-call", type=int, default=0,
+                    help="utterances per decode call (0 = the rank's whole shard in one call: the encoder still advances "
+                         "groups of up to 128 utterances, the greedy kernel takes all of them at once)")
     ap.add_argument("--no-extras", action="store_true", help="skip the C1 / C2 figures of the default line")
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -219,7 +219,9 @@ int pimb200_lstm_last_status(pimb200_lstm* h);
 /* Timing hook: while enabled, every recurrence launch sequence (all T steps of one layer and direction)
  * is bracketed by CUDA events on the launching stream.  profile_read waits for those events and returns
  * their summed device time, how many recurrences ran and their algorithmic W_hh bytes
- * (T * 4H*H * 2 each), then clears the record.  Stands where the reference wraps each op in
+ * (T * 4H*H * 2 each: W_hh once per timestep; a launch of 65..128 sequences runs as two batch halves on separate
+ * CTAs, each half a recurrence of its own with its own resident copy of W_hh, and counts twice), then clears the
+ * record.  Stands where the reference wraps each op in
  * PROFILE_SCOPE + a device-wide sync (runtime/source/executor/stream_executor.cpp:204-258). */
 int pimb200_lstm_profile_enable(pimb200_lstm* h, int enable);
 int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrences, double* bytes);
@@ -229,17 +231,19 @@ int pimb200_lstm_profile_read(pimb200_lstm* h, double* total_ms, long* recurrenc
  * rows per CTA), so the default is 0.  No counterpart in the reference. */
 int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on);
 
-/* A/B switch between the batched persistent recurrences (1..64 lock-step sequences, H <= 1024): 2 (default) = the
- * pipelined kernel (W_hh slice in registers; the sequences advance as independent groups, so one group's hidden-state
- * exchange runs under the other groups' arithmetic), 1 = the same arithmetic with the exchange on the compute warps,
- * 0 = the K-split kernel with W_hh in shared memory (up to 32 sequences; also what H > 1024 falls back to).  Results
- * agree within the LSTM tolerance; within one setting they do not depend on the batch size.  No counterpart in the
- * reference. */
+/* A/B switch between the batched persistent recurrences (lock-step sequences, H <= 1024): 2 (default) = the
+ * pipelined kernel for 33..128 sequences (W_hh slice in registers; the sequences advance as independent groups, so
+ * one group's hidden-state exchange runs under the other groups' arithmetic; 65..128 sequences as two batch halves)
+ * and, for 1..32 sequences, the kernel with the exchange on the compute warps (shorter critical path when there is
+ * nothing to overlap); 3 = the pipelined kernel for every batch size; 1 = the exchange-on-compute-warps kernel for
+ * 1..64 sequences; 0 = the K-split kernel with W_hh in shared memory (up to 32 sequences; also what H > 1024 falls
+ * back to).  Results agree within the LSTM tolerance; within one kernel they do not depend on the batch size.  No
+ * counterpart in the reference. */
 int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on);
 
-/* Tuning switch of the pipelined kernel for 33..64 sequences: 2 (or 0, the default) = two groups of 32 sequences,
- * 4 = four groups of 16.  Same results.  No counterpart in the reference. */
-int pimb200_lstm_set_pipe_groups(pimb200_lstm* h, int groups);
+/* Tuning switch of the pipelined kernel: how many sequences form one independently advancing group (8, 16 or 32;
+ * 0 = chosen by batch size, the default).  Same results.  No counterpart in the reference. */
+int pimb200_lstm_set_pipe_group_size(pimb200_lstm* h, int seqs);
 
 /* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are

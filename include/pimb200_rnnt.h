@@ -55,7 +55,7 @@ int pimb200_rnnt_destroy(pimb200_rnnt* h);
 int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, int n_utts, int32_t* tokens,
                         int32_t* n_tokens, float* logits, void* stream);
 
-/* How many utterances the encoder advances in lock step (1..64, default 64); each is one column of the
+/* How many utterances the encoder advances in lock step (1..128, default 128); each is one column of the
  * recurrence's tensor-core tiles.  1 reproduces strict batch-1 execution. */
 int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n);
 

@@ -55,7 +55,7 @@ SIGNATURES = {
     "pimb200_lstm_set_poll_limit": (_i, [_vp, _i]),
     "pimb200_lstm_set_use_tc": (_i, [_vp, _i]),
     "pimb200_lstm_set_bulk_wide": (_i, [_vp, _i]),
-    "pimb200_lstm_set_pipe_groups": (_i, [_vp, _i]),
+    "pimb200_lstm_set_pipe_group_size": (_i, [_vp, _i]),
     "pimb200_rnnt_profile_enable": (_i, [_vp, _i]),
     "pimb200_rnnt_profile_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_long), C.POINTER(C.c_double)]),
     "pimb200_rnnt_create": (_i, [_vp, _vp, C.POINTER(_vp)]),

@@ -15,7 +15,7 @@ ROOT = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libpimb200.so")
 
-CUDA_SOURCES = ["gemv.cu", "gemm_tc.cu", "lstm.cu", "rnnt.cu", "capi.cu", "noalloc.cu", "rowops.cu"]
+CUDA_SOURCES = ["gemv.cu", "gemm_tc.cu", "gemm_skinny.cu", "lstm.cu", "rnnt.cu", "capi.cu", "noalloc.cu", "rowops.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -338,9 +338,16 @@ static int launch(const __half* W, const __half* X, const __half* bias, void* Y,
 
 static int g_force_simt = 0;
 
+int launch_gemm_wx_skinny(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
+                          int ldy, int act, int y_is_f32, cudaStream_t st);
+
+// Router of the dense contraction: up to 32 activation rows stream W on every SM (HBM-bound, like the GEMV); more rows
+// go to the tcgen05 kernel; shapes neither takes (unaligned operands, K not a multiple of 8) to the SIMT kernel.
 int launch_gemm_wx(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                    int ldy, int act, int y_is_f32, cudaStream_t st) {
     if (!g_force_simt) {
+        const int rs = launch_gemm_wx_skinny(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st);
+        if (rs != PIMB200_ERR_UNSUPPORTED) return rs;
         const int rc = tc::launch(W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32, st, 0);
         if (rc != PIMB200_ERR_UNSUPPORTED) return rc;
     }

@@ -13,14 +13,19 @@
 //                     128-bit loads; any B, any H; the form used by seq_len==1 decoder calls
 //        persistent — one cooperative launch for all T steps; every CTA keeps its slice of W_hh on
 //                     chip for the whole sequence and the CTAs exchange the new hidden states through
-//                     L2 once per step.  Default: lstm_persistent_wide_kernel (1..64 sequences in
-//                     lock step, H <= 1024, slice in registers as mma fragments, 16-byte records +
-//                     per-CTA step flags + bulk-copy gather).  Kept beside it: the K-split kernel
-//                     with the slice in shared memory (2..32 sequences, any H that fits), the
-//                     tagged-word kernel (up to 8 sequences, data and flag in one 16-byte word) and
-//                     an opt-in tcgen05 variant (measured slower).
+//                     L2 once per step (16-byte records + per-CTA step flags + bulk-copy gather).
+//                     Defaults (H <= 1024, slice in registers as mma fragments): 1..32 lock-step
+//                     sequences run lstm_persistent_wide_kernel (exchange on the compute warps: the
+//                     shortest critical path when there is little to overlap), 33..128 run
+//                     lstm_persistent_pipe_kernel (warp-specialised; independent sequence groups,
+//                     so one group's exchange runs under the others' arithmetic; 65..128 as two
+//                     batch halves on CTAs of 16 units).  Kept beside them: the K-split kernel with
+//                     the slice in shared memory (2..32 sequences, any H that fits), the tagged-word
+//                     kernel (up to 8 sequences, data and flag in one 16-byte word) and an opt-in
+//                     tcgen05 variant (measured slower).
 // Weights are stored gate-interleaved (packed row u*4+g = original row g*H+u) so the four gate
 // rows of one hidden unit are contiguous and its four pre-activations are one float4 of G.
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -999,33 +1004,44 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 }
 
 // ---------------------------------------------------------------------------------------------
-// pipelined variant of the register-resident recurrence (the default for 1..64 sequences, H <= 1024)
+// pipelined, warp-specialised variant of the register-resident recurrence (1..128 sequences, H <= 1024)
 //
-// Same ownership as the wide kernel (CTA c owns hidden units 8c..8c+7 = 32 gate rows, H/8 CTAs, W_hh slice in registers
-// as mma A fragments) and the same exchange protocol (16-byte records + per-CTA step flags + bulk-copy gather), but the
-// sequences of a launch are split into NG groups of BPG = 8*NTG that advance independently, and the exchange is taken off
-// the compute warps:
-//   * warps 0..7 (compute) split K eight ways (warp w owns k-tiles w, w+8, ...; no duplication of A fragments: 64
-//     registers per thread) and run, for one group after the other: wait for the group's gathered hidden states ->
-//     tensor-core partial products -> one CTA barrier -> gates -> arrive on the group's "done" mbarrier.  While group g
-//     is exchanged, the other groups compute, so the two L2 round trips of the exchange no longer sit on the critical
-//     path of a step.  The K-partials of consecutive group phases alternate between two buffers, so no second barrier
-//     is needed between the gate reads of one phase and the partial-sum writes of the next.
-//   * warp 8 (publisher) waits for "done", stores the group's records (and the y rows) and raises the step flags.
-//   * warp 9 (gatherer) polls the flags of all CTAs for (step, group), 32 CTAs per lane round, and hands each chunk of
-//     32 CTAs' records to the bulk-copy engine as soon as its flags are up (no cluster multicast); the copies complete
-//     on the group's "full" mbarrier, which the compute warps wait on.
-// Per-sequence arithmetic (k-tile order inside a warp's accumulator, order of the eight partial sums) is the same for
-// every NTG / NG, so a sequence's result does not depend on how many sequences share the launch.
-// Every wait is bounded and ends early once the launch's generation appears in the status block.
+// Ownership: CTA (slice c, half b) owns hidden units UPC*c .. UPC*c + UPC - 1 (4*UPC gate rows of W_hh, kept in
+// registers as mma A fragments for the whole launch) for the sequences of batch half b.  UPC = 8 gives H/8 CTAs that
+// each see every sequence (up to 64, bounded by the shared memory the hidden states of all sequences need); UPC = 16
+// with two batch halves gives 2 * H/16 CTAs, each seeing one half of up to 128 sequences: the same number of SMs, half
+// as many participants in each half's exchange, twice the sequences per launch.  The halves never interact.
+// Within a CTA the sequences are split into NG groups of BPG = 8*NTG that advance independently, and every stage of a
+// step has warps of its own, handing over through mbarriers, so that the stages of different groups overlap:
+//   * warps 0..7 (tensor) split K eight ways (warp w owns k-tiles w, w+8, ...): wait for the group's gathered hidden
+//     states ("full") and for a free partial-sum buffer ("zfree"), multiply, store the K-partials, arrive on "zready".
+//     They never wait for the gates: the tensor pipe stays busy with the next group.
+//   * warps 8..11 (gates) wait for "zready", sum the eight partials, free the buffer, run the cell update (c stays in
+//     fp32 registers for the whole sequence), assemble each sequence's 16-byte records (eight units each) with shuffles,
+//     store them (and the y row) and arrive on "done".  The input-projection terms of the next step are fetched into
+//     shared memory with cp.async a whole step ahead (they stream from HBM).
+//   * warps 12..15 (exchange), one per group: wait for "done", raise this CTA's step flag (release, cumulative over the
+//     gate warps' record stores), then poll the flags of the half's CTAs, one flag per lane and chunk of 32 CTAs, and
+//     hand each chunk's records to the bulk-copy engine as soon as its flags are up (no cluster multicast); the copies
+//     complete on "full".
+// The exchange of one group (two L2 round trips plus the skew of the slowest CTA, ~4-5 thousand cycles) runs under the
+// arithmetic of the other groups; a step of all groups takes about as long as one group's chain.
+// The tensor warpgroups take registers from the others at start-up (setmaxnreg).  Per-sequence arithmetic (k-tile order
+// inside a warp's accumulator, order of the eight partial sums) is the same for every UPC / NTG / NG, so a sequence's
+// result does not depend on how many sequences share the launch.  Every wait is bounded and ends early once the
+// launch's generation appears in the status block.
 // ---------------------------------------------------------------------------------------------
-constexpr int kPipeComputeWarps = 8;
-constexpr int kPipeComputeThreads = kPipeComputeWarps * 32;
-constexpr int kPipeThreads = kPipeComputeThreads + 64;   // + publisher warp + gatherer warp
-constexpr int kPipeKtw = 8;          // k-tiles per compute warp held in registers (H <= 1024)
-constexpr int kPipeMaxGroups = 4;
+constexpr int kPipeTensorWarps = 8;
+constexpr int kPipeTensorThreads = kPipeTensorWarps * 32;
+constexpr int kPipeGateWarps = 4;
+constexpr int kPipeGateThreads = kPipeGateWarps * 32;
+constexpr int kPipeThreads = 512;    // 4 warpgroups: 2 tensor, 1 gates, 1 exchange (one warp per group)
+constexpr int kPipeKtw = 8;          // k-tiles per tensor warp held in registers (H <= 1024)
+constexpr int kPipeMaxGroups = 4;    // one exchange warp per group
+constexpr int kPipeMaxHalves = 2;
+constexpr int kPipeMaxB = 128;       // sequences per launch: 2 halves x 4 groups x 16
 constexpr int kPipeChunk = 32;       // CTAs per gather chunk (one flag per lane)
-constexpr int kPipeMaxChunks = 4;    // H <= 1024: at most 128 CTAs
+constexpr int kPipeMaxChunks = 4;    // H <= 1024: at most 128 CTAs per half
 
 struct PipeArgs {
     const __half* Whh;
@@ -1039,33 +1055,18 @@ struct PipeArgs {
     int y_vec;
     __half* hn;
     __half* cn;
-    uint4* data;            // [2 parities][NG][n_cta][BPG] 16-byte records
-    uint32_t* flags;        // [kBulkFlagCopies][2 parities][kPipeMaxGroups][n_cta] step tags, one per 128-byte line
+    uint4* data;            // [2 parities][halves][NG][H/8 octets][BPG] 16-byte records (the image of a group's hs)
+    uint32_t* flags;        // [kBulkFlagCopies][2 parities][kPipeMaxHalves][kPipeMaxGroups][slices] step tags, one per 128-byte line
     uint32_t tag_base;
     int* status;
     int gen;
     int H, T, B;
+    int halves;             // batch halves (1 or 2): grid = halves * H / UPC
     int reverse;
     int poll_limit;
-    long long* trace;       // optional: 8 clocks per CTA and step (compute thread 0)
+    long long* trace;       // optional: 8 clocks per CTA and step
 };
 
-__device__ __forceinline__ void bar_sync_named(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-// named-barrier OR reduction: true when `pred` holds in any participating thread
-__device__ __forceinline__ bool bar_red_or_named(int id, int count, bool pred) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %3, 0;\n\t"
-        "barrier.cta.red.or.pred p, %1, %2, q;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(r)
-        : "r"(id), "r"(count), "r"((uint32_t)pred)
-        : "memory");
-    return r != 0;
-}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -1078,31 +1079,45 @@ __device__ __forceinline__ bool mbar_wait_polls(uint32_t bar, uint32_t parity, c
     return false;
 }
 
-template <int NTG, int NG>
+template <int UPC, int NTG, int NG>
 __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(PipeArgs a) {
     constexpr int BPG = NTG * 8;                      // sequences per group (padded to whole mma tiles)
-    static_assert(BPG <= 32 && NG <= kPipeMaxGroups, "one publisher lane per sequence of a group");
+    constexpr int MT = UPC / 4;                       // 16-row m-tiles of the CTA's gate rows
+    constexpr int OCT = UPC / 8;                      // 16-byte records (unit octets) per sequence and CTA
+    static_assert((UPC == 8 || UPC == 16) && BPG <= 32 && NG <= kPipeMaxGroups, "supported shapes");
     constexpr int ZP = BPG + 1;                       // padded sequence pitch of the partial sums
-    constexpr int ZBUF = kPipeComputeWarps * 8 * ZP * 4;   // floats per partial-sum buffer: [k-eighth][unit][ZP][gate]
+    constexpr int ZBUF = kPipeTensorWarps * UPC * ZP * 4;  // floats per partial-sum buffer: [k-eighth][unit][ZP][gate]
+    constexpr int SB = (BPG + 15) / 16;               // sequence blocks of 16 per gate thread
+    constexpr int CPT = SB * OCT;                     // cells per gate thread and group
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int H = a.H, T = a.T, B = a.B;
+    const int H = a.H, T = a.T;
     __half* hs = reinterpret_cast<__half*>(smem_raw);                                  // [NG][H/8][BPG][8]
     float* zpart = reinterpret_cast<float*>(hs + (size_t)NG * BPG * H);                // [2][ZBUF]
-    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + 2 * ZBUF);        // [NG][BPG][8]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(hpub + (size_t)NG * BPG * 8);         // full[NG], done[NG]
+    float4* gxs = reinterpret_cast<float4*>(zpart + 2 * ZBUF);                         // [NG][CPT][128 gate threads]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(gxs + (size_t)NG * CPT * kPipeGateThreads);   // full[NG], done[NG], zready[2], zfree[2]
     const uint32_t full0 = (uint32_t)__cvta_generic_to_shared(bars);
     const uint32_t done0 = full0 + 8u * NG;
+    const uint32_t zready0 = done0 + 8u * NG;
+    const uint32_t zfree0 = zready0 + 16u;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_cta = gridDim.x, cta = blockIdx.x;
-    const int u0 = cta * 8;
+    const int n_slices = H / UPC;                     // CTAs per batch half
+    const int slice = blockIdx.x % n_slices, half = blockIdx.x / n_slices;
+    const int u0 = slice * UPC;
+    const int seq0 = half * NG * BPG;                 // first sequence of this half
+    const int B = a.B - seq0 < 0 ? 0 : (a.B - seq0 < NG * BPG ? a.B - seq0 : NG * BPG);   // sequences of this half
     const int ktiles = H >> 4;
-    const int nchunks = (n_cta + kPipeChunk - 1) / kPipeChunk;
-    // a wait on an mbarrier may take as long as the slowest CTA's flag: same budget as the gatherer's polls
+    const int nchunks = (n_slices + kPipeChunk - 1) / kPipeChunk;
+    const int ng_live = (B + BPG - 1) / BPG;          // groups that hold sequences
+    // a wait on an mbarrier may take as long as the slowest CTA's flag: same budget as the exchange warps' polls
     const int wait_limit = a.poll_limit < (1 << 27) ? a.poll_limit * 8 : a.poll_limit;
     if (tid == 0) {
         for (int g = 0; g < NG; ++g) {
             pimb200::tc::mbar_init(full0 + 8u * g, (uint32_t)nchunks);          // one arrival (+ bytes) per chunk
-            pimb200::tc::mbar_init(done0 + 8u * g, (uint32_t)kPipeComputeThreads);
+            pimb200::tc::mbar_init(done0 + 8u * g, (uint32_t)kPipeGateThreads);
+        }
+        for (int b = 0; b < 2; ++b) {
+            pimb200::tc::mbar_init(zready0 + 8u * b, (uint32_t)kPipeTensorThreads);
+            pimb200::tc::mbar_init(zfree0 + 8u * b, (uint32_t)kPipeGateThreads);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1111,194 +1126,251 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
         const int n = i / H, k = i - n * H;
         const int g = n / BPG, nl = n - g * BPG;
         hs[(size_t)g * BPG * H + ((size_t)(k >> 3) * BPG + nl) * 8 + (k & 7)] =
-            (n < B && a.h0) ? a.h0[(size_t)n * H + k] : __float2half_rn(0.f);
+            (n < B && a.h0) ? a.h0[(size_t)(seq0 + n) * H + k] : __float2half_rn(0.f);
     }
-    for (int i = tid; i < NG * BPG * 8; i += kPipeThreads) hpub[i] = 0;
     __syncthreads();
 
-    if (warp < kPipeComputeWarps) {
-        // ================================ compute warps ================================
+    if (warp < kPipeTensorWarps) {
+        // ================================ tensor warps ================================
+        if (UPC == 16) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 136;" ::: "memory");
         const int b_n = lane >> 2, b_k = (lane & 3) * 2;
-        uint32_t afrag[kPipeKtw][2][4];   // afrag[i][m] = rows 16m..16m+15 of the slice, k-tile 8i + warp
+        uint32_t afrag[kPipeKtw][MT][4];   // afrag[i][m] = rows 16m..16m+15 of the slice, k-tile 8i + warp
         {
             const __half* wbase = a.Whh + (size_t)u0 * 4 * H;
 #pragma unroll
             for (int i = 0; i < kPipeKtw; ++i)
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
+                for (int m = 0; m < MT; ++m)
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         afrag[i][m][r] = 0u;
-                        if (kPipeComputeWarps * i + warp < ktiles) {
+                        if (kPipeTensorWarps * i + warp < ktiles) {
                             const int row = m * 16 + b_n + (r & 1) * 8;
-                            const int k = (kPipeComputeWarps * i + warp) * 16 + b_k + (r >> 1) * 8;
+                            const int k = (kPipeTensorWarps * i + warp) * 16 + b_k + (r >> 1) * 8;
                             afrag[i][m][r] = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)row * H + k));
                         }
                     }
         }
-        // gate cell of this thread in every group: unit gu, local sequence gn
-        const int gu = tid / BPG, gn = tid - gu * BPG;
-        const bool cell = tid < 8 * BPG;
-        float c[NG];
-        float4 gx[NG];
-        bool live[NG];
-        float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cell) bias4 = *reinterpret_cast<const float4*>(a.bias + (size_t)(u0 + gu) * 4);
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-            const int n = g * BPG + gn;
-            live[g] = cell && n < B;
-            c[g] = 0.f;
-            gx[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live[g]) {
-                c[g] = a.c0 ? __half2float(a.c0[(size_t)n * H + u0 + gu]) : 0.f;
-                const int t0 = a.reverse ? T - 1 : 0;
-                gx[g] = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)t0 * a.g_tstride + (size_t)n * a.g_bstride +
-                                                               (size_t)(u0 + gu) * 4));
-            }
-        }
         int phase = 0;      // group phases executed so far: selects the partial-sum buffer
         bool dead = false;
         for (int s = 0; s < T && !dead; ++s) {
+            long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+            for (int g = 0; g < ng_live; ++g, ++phase) {
+                const int zb = phase & 1;
+                if (tr && tid == 0 && g == 0) tr[0] = clock64();
+                bool ok = true;
+                if (s > 0) ok = mbar_wait_polls(full0 + 8u * g, (uint32_t)((s - 1) & 1), a.status, a.gen, wait_limit);
+                if (tr && tid == 0 && g == 0) tr[1] = clock64();
+                // the partial-sum buffer must have been read by the gate warps (its use two phases ago)
+                if (ok && phase >= 2)
+                    ok = mbar_wait_polls(zfree0 + 8u * zb, (uint32_t)(((phase >> 1) - 1) & 1), a.status, a.gen, wait_limit);
+                if (!ok) { dead = true; break; }
+                if (tr && tid == 0 && g == 0) tr[2] = clock64();
+                float* zq = zpart + (size_t)zb * ZBUF + (size_t)warp * UPC * ZP * 4;
+                float acc[MT][NTG][4];
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int j = 0; j < NTG; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+                const __half* brow = hs + (size_t)g * BPG * H + (size_t)b_n * 8 + b_k;
+                auto ktile = [&](int i) {
+                    const int kt = kPipeTensorWarps * i + warp;
+                    const __half* hp = brow + (size_t)(2 * kt) * BPG * 8;
+                    uint32_t b0[NTG], b1[NTG];
+#pragma unroll
+                    for (int j = 0; j < NTG; ++j) {
+                        b0[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64);
+                        b1[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64 + (size_t)BPG * 8);
+                    }
+#pragma unroll
+                    for (int j = 0; j < NTG; ++j)
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) mma_16816(acc[m][j], afrag[i][m], b0[j], b1[j]);
+                };
+                if (ktiles == kPipeKtw * kPipeTensorWarps) {
+                    // H = 1024: every warp owns eight k-tiles; no conditions in the way of scheduling the operand loads
+                    // of later k-tiles above the products of earlier ones
+#pragma unroll
+                    for (int i = 0; i < kPipeKtw; ++i) ktile(i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kPipeKtw; ++i)
+                        if (kPipeTensorWarps * i + warp < ktiles) ktile(i);   // warp-uniform
+                }
+#pragma unroll
+                for (int m = 0; m < MT; ++m)
+#pragma unroll
+                    for (int j = 0; j < NTG; ++j)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int r = m * 16 + b_n + (i >> 1) * 8, n = j * 8 + b_k + (i & 1);
+                            zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][j][i];
+                        }
+                mbar_arrive(zready0 + 8u * zb);
+                if (tr && tid == 0 && g == 0) tr[3] = clock64();
+            }
+        }
+        if (dead && lane == 0) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+    } else {
+    // the other two warpgroups hand registers over (one instruction per warpgroup, before the roles split up)
+    if (UPC == 16) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 120;" ::: "memory");
+    if (warp < kPipeTensorWarps + kPipeGateWarps) {
+        // ================================ gate warps ================================
+        // Eight consecutive lanes hold the eight units of one octet of one sequence, so a 16-byte record is assembled
+        // with four shuffles and stored by its first lane.  Cell q = (sequence block sb, octet o) of thread gt:
+        // unit 8*o + (gt & 7), local sequence gt/8 + 16*sb.
+        const int gt = tid - kPipeTensorThreads;          // 0..127
+        const int gl = gt & 7;
+        float4 bias4[OCT];
+#pragma unroll
+        for (int o = 0; o < OCT; ++o) bias4[o] = *reinterpret_cast<const float4*>(a.bias + (size_t)(u0 + 8 * o + gl) * 4);
+        float c[NG][CPT];
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+            for (int q = 0; q < CPT; ++q) {
+                const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT), n = g * BPG + gn;
+                c[g][q] = (gn < BPG && n < B && a.c0) ? __half2float(a.c0[(size_t)(seq0 + n) * H + u0 + 8 * o + gl]) : 0.f;
+            }
+        // input-projection terms: fetched with cp.async into this thread's own slots a whole step ahead; one commit
+        // group per group phase, so "all but the newest NG - 1 groups" is exactly the phase about to be consumed
+        auto prefetch_gx = [&](int g, int t) {
+#pragma unroll
+            for (int q = 0; q < CPT; ++q) {
+                const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT), n = g * BPG + gn;
+                if (gn < BPG && n < B) {
+                    const float* gp = a.G + (size_t)t * a.g_tstride + (size_t)(seq0 + n) * a.g_bstride + (size_t)(u0 + 8 * o + gl) * 4;
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(gxs + ((size_t)g * CPT + q) * kPipeGateThreads + gt);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gp) : "memory");
+                }
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+#pragma unroll
+        for (int g = 0; g < NG; ++g) prefetch_gx(g, a.reverse ? T - 1 : 0);   // (empty commit groups for absent sequences)
+        int phase = 0;
+        bool dead = false;
+        for (int s = 0; s < T && !dead; ++s) {
             const int t = a.reverse ? T - 1 - s : s;
+            const int par = s & 1;
             long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
 #pragma unroll
             for (int g = 0; g < NG; ++g) {
-                if (g * BPG >= B) break;   // uniform: groups beyond the batch do not exist
-                if (tr && tid == 0 && g < 2) tr[g * 4 + 0] = clock64();
-                bool ok = true;
-                if (s > 0) ok = mbar_wait_polls(full0 + 8u * g, (uint32_t)((s - 1) & 1), a.status, a.gen, wait_limit);
-                if (tr && tid == 0 && g < 2) tr[g * 4 + 1] = clock64();
-                // ---- K-partial products of this warp for group g
-                float* zq = zpart + (size_t)(phase & 1) * ZBUF + (size_t)warp * 8 * ZP * 4;
-                {
-                    float acc[2][NTG][4];
-#pragma unroll
-                    for (int m = 0; m < 2; ++m)
-#pragma unroll
-                        for (int j = 0; j < NTG; ++j)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
-                    const __half* brow = hs + (size_t)g * BPG * H + (size_t)b_n * 8 + b_k;
-#pragma unroll
-                    for (int i = 0; i < kPipeKtw; ++i) {
-                        if (kPipeComputeWarps * i + warp < ktiles) {   // warp-uniform
-                            const int kt = kPipeComputeWarps * i + warp;
-                            const __half* hp = brow + (size_t)(2 * kt) * BPG * 8;
-                            uint32_t b0[NTG], b1[NTG];
-#pragma unroll
-                            for (int j = 0; j < NTG; ++j) {
-                                b0[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64);
-                                b1[j] = *reinterpret_cast<const uint32_t*>(hp + j * 64 + (size_t)BPG * 8);
-                            }
-#pragma unroll
-                            for (int j = 0; j < NTG; ++j) {
-                                mma_16816(acc[0][j], afrag[i][0], b0[j], b1[j]);
-                                mma_16816(acc[1][j], afrag[i][1], b0[j], b1[j]);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int m = 0; m < 2; ++m)
-#pragma unroll
-                        for (int j = 0; j < NTG; ++j)
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int r = m * 16 + b_n + (i >> 1) * 8, n = j * 8 + b_k + (i & 1);
-                                zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][j][i];
-                            }
+                if (g >= ng_live) {   // keep one commit group per group slot, so the wait below stays exact
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    continue;
                 }
-                // the one CTA barrier of a group phase; it also carries whether any thread's wait gave up
-                if (bar_red_or_named(1, kPipeComputeThreads, !ok)) {
-                    if (tid == 0) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+                const int zb = phase & 1;
+                if (!mbar_wait_polls(zready0 + 8u * zb, (uint32_t)((phase >> 1) & 1), a.status, a.gen, wait_limit)) {
                     dead = true;
                     break;
                 }
-                if (tr && tid == 0 && g < 2) tr[g * 4 + 2] = clock64();
-                // ---- gates of cell (gu, gn) of group g
-                if (cell) {
-                    const float* zb = zpart + (size_t)(phase & 1) * ZBUF + ((size_t)gu * ZP + gn) * 4;
-                    float zi = gx[g].x + bias4.x, zf = gx[g].y + bias4.y, zg = gx[g].z + bias4.z, zo = gx[g].w + bias4.w;
+                if (tr && gt == 0 && g == 0) tr[4] = clock64();
+                // the cells of a thread are worked side by side (independent chains): partial sums, gate math, then
+                // the shuffles and stores
+                float z[CPT][4];
+                const float* zbp[CPT];
 #pragma unroll
-                    for (int k = 0; k < kPipeComputeWarps; ++k) {
-                        const float4 zk = *reinterpret_cast<const float4*>(zb + (size_t)k * 8 * ZP * 4);
-                        zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
+                for (int q = 0; q < CPT; ++q) {
+                    const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT);
+                    zbp[q] = zpart + (size_t)zb * ZBUF + ((size_t)(8 * o + gl) * ZP + (gn < BPG ? gn : 0)) * 4;
+                    z[q][0] = 0.f; z[q][1] = 0.f; z[q][2] = 0.f; z[q][3] = 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < kPipeTensorWarps; ++k)
+#pragma unroll
+                    for (int q = 0; q < CPT; ++q) {
+                        const float4 zk = *reinterpret_cast<const float4*>(zbp[q] + (size_t)k * UPC * ZP * 4);
+                        z[q][0] += zk.x; z[q][1] += zk.y; z[q][2] += zk.z; z[q][3] += zk.w;
                     }
-                    c[g] = sigmoidf_(zf) * c[g] + sigmoidf_(zi) * tanhf_(zg);
-                    const __half hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c[g]));
-                    if (live[g]) {
-                        const int n = g * BPG + gn, u = u0 + gu;
-                        hpub[((size_t)g * BPG + gn) * 8 + gu] = __half_as_ushort(hh);
-                        if (!a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u] = hh;
+                mbar_arrive(zfree0 + 8u * zb);   // the buffer may be overwritten: its sums are in registers
+                asm volatile("cp.async.wait_group %0;" ::"n"(NG - 1) : "memory");   // this phase's input terms have landed
+                __half hh[CPT];
+#pragma unroll
+                for (int q = 0; q < CPT; ++q) {
+                    const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT), n = g * BPG + gn;
+                    float4 gx = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (gn < BPG && n < B) gx = gxs[((size_t)g * CPT + q) * kPipeGateThreads + gt];
+                    // order of the additions: input term + bias first, then the sum of the eight partials
+                    const float zi = (gx.x + bias4[o].x) + z[q][0], zf = (gx.y + bias4[o].y) + z[q][1],
+                                zg = (gx.z + bias4[o].z) + z[q][2], zo = (gx.w + bias4[o].w) + z[q][3];
+                    c[g][q] = sigmoidf_(zf) * c[g][q] + sigmoidf_(zi) * tanhf_(zg);
+                    hh[q] = __float2half_rn(sigmoidf_(zo) * tanhf_(c[g][q]));
+                }
+#pragma unroll
+                for (int q = 0; q < CPT; ++q) {
+                    const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT), n = g * BPG + gn, u = u0 + 8 * o + gl;
+                    const bool live = gn < BPG && n < B;
+                    // the octet's record {units 0..7} lands in the lane of unit 0
+                    const uint32_t v = (uint32_t)__half_as_ushort(hh[q]);
+                    const uint32_t p1 = v | (__shfl_down_sync(0xffffffffu, v, 1, 8) << 16);
+                    const uint32_t p2 = __shfl_down_sync(0xffffffffu, p1, 2, 8);
+                    const uint32_t q1 = __shfl_down_sync(0xffffffffu, p1, 4, 8);
+                    const uint32_t q2 = __shfl_down_sync(0xffffffffu, p2, 4, 8);
+                    if (live) {
+                        const size_t nn = (size_t)(seq0 + n);
+                        if (gl == 0) {
+                            const uint4 rec = make_uint4(p1, p2, q1, q2);
+                            if (s + 1 < T)
+                                a.data[((((size_t)par * a.halves + half) * NG + g) * (H >> 3) + (size_t)slice * OCT + o) * BPG + gn] = rec;
+                            if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + nn * a.y_bstride + u0 + 8 * o) = rec;
+                        }
+                        if (!a.y_vec) a.y[(size_t)t * a.y_tstride + nn * a.y_bstride + u] = hh[q];
                         if (s == T - 1) {
-                            if (a.hn) a.hn[(size_t)n * H + u] = hh;
-                            if (a.cn) a.cn[(size_t)n * H + u] = __float2half_rn(c[g]);
+                            if (a.hn) a.hn[nn * H + u] = hh[q];
+                            if (a.cn) a.cn[nn * H + u] = __float2half_rn(c[g][q]);
                         }
                     }
                 }
-                mbar_arrive(done0 + 8u * g);   // release: the publisher reads hpub after this phase completes
-                // next step's input-projection term of this cell, a whole step ahead of its use
-                if (live[g] && s + 1 < T) {
-                    const int tn = a.reverse ? t - 1 : t + 1;
-                    const float* gp = a.G + (size_t)tn * a.g_tstride + (size_t)(g * BPG + gn) * a.g_bstride +
-                                      (size_t)(u0 + gu) * 4;
-                    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];"
-                                 : "=f"(gx[g].x), "=f"(gx[g].y), "=f"(gx[g].z), "=f"(gx[g].w)
-                                 : "l"(gp));
-                }
-                if (tr && tid == 0 && g < 2) tr[g * 4 + 3] = clock64();
+                // release (CTA scope): the group's exchange warp raises the step flag after this phase completes; its
+                // cross-proxy fence and gpu-scope release are cumulative over the record stores above
+                mbar_arrive(done0 + 8u * g);
+                if (s + 1 < T) prefetch_gx(g, a.reverse ? t - 1 : t + 1);
+                else asm volatile("cp.async.commit_group;" ::: "memory");
+                if (tr && gt == 0 && g == 0) tr[5] = clock64();
                 ++phase;
             }
         }
-    } else if (warp == kPipeComputeWarps) {
-        // ================================ publisher warp ================================
-        for (int s = 0; s < T; ++s) {
-            const int t = a.reverse ? T - 1 - s : s;
-            const int par = s & 1;
-            const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        if (dead && lane == 0) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+    } else {
+        // ================================ exchange warps: warp 12 + g serves group g ================================
+        const int g = warp - (kPipeTensorWarps + kPipeGateWarps);
+        if (g < ng_live) {
+            const int rep = blockIdx.x % kBulkFlagCopies;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(hs + (size_t)g * BPG * H);
+            const uint32_t fbar = full0 + 8u * g;
             bool dead = false;
-            for (int g = 0; g < NG; ++g) {
-                if (g * BPG >= B) break;
-                if (!mbar_wait_polls(done0 + 8u * g, (uint32_t)(s & 1), a.status, a.gen, wait_limit)) { dead = true; break; }
-                const int n = g * BPG + lane;
-                if (lane < BPG && n < B) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(hpub + ((size_t)g * BPG + lane) * 8);
-                    if (s + 1 < T) {
-                        a.data[(((size_t)par * NG + g) * n_cta + cta) * BPG + lane] = v;
-                        // the record is read by the other CTAs' bulk copies (async proxy): cross-proxy fence on the
-                        // writer side, in front of the flag's release
-                        asm volatile("fence.proxy.async.global;" ::: "memory");
-                    }
-                    if (a.y_vec) *reinterpret_cast<uint4*>(a.y + (size_t)t * a.y_tstride + (size_t)n * a.y_bstride + u0) = v;
-                }
-                __syncwarp();
-                if (s + 1 < T && lane < kBulkFlagCopies)
+            for (int s = 0; s + 1 < T && !dead; ++s) {
+                const int par = s & 1;
+                const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+                long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * T + s) * 8 : nullptr;
+                if (!mbar_wait_polls(done0 + 8u * g, (uint32_t)(s & 1), a.status, a.gen, wait_limit)) break;
+                // ---- publish: the gate warps' records are out; raise this CTA's step flag in every replica.  The records
+                //      are read by the other CTAs' bulk copies (async proxy): the cross-proxy fence sits on the writer
+                //      side, here, where its wait for the record stores is the wait the release needs anyway (on the
+                //      reader side, in front of the copy, it was measured to cost several thousand cycles per step)
+                if (lane < kBulkFlagCopies) asm volatile("fence.proxy.async.global;" ::: "memory");
+                if (lane < kBulkFlagCopies)
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(
-                                     a.flags + ((((size_t)lane * 2 + par) * kPipeMaxGroups + g) * n_cta + cta) * 32),
+                                     a.flags + ((((((size_t)lane * 2 + par) * kPipeMaxHalves + half) * kPipeMaxGroups + g) * n_slices + slice) * 32)),
                                  "r"(tag)
                                  : "memory");
-            }
-            if (dead) break;
-        }
-    } else {
-        // ================================ gatherer warp ================================
-        const int rep = cta % kBulkFlagCopies;
-        bool dead = false;
-        for (int s = 0; s + 1 < T && !dead; ++s) {
-            const int par = s & 1;
-            const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
-            for (int g = 0; g < NG && !dead; ++g) {
-                if (g * BPG >= B) break;
-                const uint32_t* fbase = a.flags + ((((size_t)rep * 2 + par) * kPipeMaxGroups + g) * n_cta) * 32;
-                const unsigned char* src = reinterpret_cast<const unsigned char*>(a.data + ((size_t)par * NG + g) * n_cta * BPG);
-                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(hs + (size_t)g * BPG * H);
-                const uint32_t fbar = full0 + 8u * g;
-                // lane l watches CTA 32i + l of every chunk i; a chunk's copy is issued as soon as its 32 flags are up
+                if (tr && lane == 0 && g == 0) tr[6] = clock64();
+                // ---- gather: lane l watches slice 32i + l of every chunk i; a chunk's records go to the bulk-copy
+                //      engine as soon as its 32 flags are up
+                const uint32_t* fbase = a.flags + (((((size_t)rep * 2 + par) * kPipeMaxHalves + half) * kPipeMaxGroups + g) * n_slices) * 32;
+                const unsigned char* src =
+                    reinterpret_cast<const unsigned char*>(a.data + (((size_t)par * a.halves + half) * NG + g) * (H >> 3) * BPG);
                 uint32_t seen = 0;      // bit i: this lane's flag of chunk i carries the tag (or there is no such CTA)
                 uint32_t issued = 0;    // bit i: chunk i's copy has been handed to the copy engine (warp-uniform)
 #pragma unroll
                 for (int i = 0; i < kPipeMaxChunks; ++i)
-                    if (i >= nchunks || i * kPipeChunk + lane >= n_cta) seen |= 1u << i;
+                    if (i >= nchunks || i * kPipeChunk + lane >= n_slices) seen |= 1u << i;
                 for (int i = nchunks; i < kPipeMaxChunks; ++i) issued |= 1u << i;
                 constexpr uint32_t all_chunks = (1u << kPipeMaxChunks) - 1u;
                 int polls = 0;
@@ -1320,9 +1392,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
 #pragma unroll
                     for (int i = 0; i < kPipeMaxChunks; ++i) {
                         if ((issued >> i & 1u) || !__all_sync(0xffffffffu, seen >> i & 1u)) continue;
-                        // acquire: one acquire load of the flag just seen, then the warp-wide sync orders every
-                        // lane's acquire before lane 0's copy
-                        if (i * kPipeChunk + lane < n_cta) {
+                        // acquire: one acquire load of the flag just seen (polling with acquire loads was measured far
+                        // slower); the warp-wide sync orders every lane's acquire before lane 0's copy
+                        if (i * kPipeChunk + lane < n_slices) {
                             uint32_t w;
                             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];"
                                          : "=r"(w)
@@ -1331,8 +1403,8 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
                         }
                         __syncwarp();
                         if (lane == 0) {
-                            const int c0 = i * kPipeChunk, c1 = c0 + kPipeChunk < n_cta ? c0 + kPipeChunk : n_cta;
-                            const uint32_t off = (uint32_t)c0 * BPG * 16u, len = (uint32_t)(c1 - c0) * BPG * 16u;
+                            const int c0 = i * kPipeChunk, c1 = c0 + kPipeChunk < n_slices ? c0 + kPipeChunk : n_slices;
+                            const uint32_t off = (uint32_t)c0 * OCT * BPG * 16u, len = (uint32_t)(c1 - c0) * OCT * BPG * 16u;
                             pimb200::tc::mbar_expect_tx(fbar, len);
                             asm volatile(
                                 "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst + off),
@@ -1357,18 +1429,15 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
                         break;
                     }
                 }
+                if (tr && lane == 0 && g == 0) tr[7] = clock64();
                 if (dead) {
-                    // before the CTA hands its shared memory back, give the copies in flight (this group's and the ones
-                    // issued for the other groups just before) a bounded chance to land
-                    for (int gg = 0; gg < NG; ++gg) {
-                        const int last_s = gg <= g ? s : s - 1;
-                        if (last_s < 0 || gg * BPG >= B) continue;
-                        for (uint32_t i = 0; i < (1u << 20); ++i)
-                            if (pimb200::tc::mbar_try_wait(full0 + 8u * gg, (uint32_t)(last_s & 1))) break;
-                    }
+                    // before the CTA hands its shared memory back, give the copies in flight a bounded chance to land
+                    for (uint32_t i = 0; i < (1u << 20); ++i)
+                        if (pimb200::tc::mbar_try_wait(fbar, (uint32_t)(s & 1))) break;
                 }
             }
         }
+    }
     }
     __syncthreads();   // no warp leaves (and no shared memory is handed back) before all roles are done
 }
@@ -1637,9 +1706,10 @@ struct pimb200_lstm {
     uint32_t tag_counter = 0;
     int poll_limit = kPersistPollLimit;
     int use_tc = 0;        // 1 = tcgen05 recurrence for 17..64 sequences (measured slower than mma.sync here: opt-in)
-    int bulk_wide = 2;     // 2 = pipelined register-resident kernel (default), 1 = wide kernel (exchange on the compute warps),
+    int bulk_wide = 2;     // 2 = pipelined kernel for 33..128 sequences, wide kernel below (default), 3 = pipelined kernel
+                           // for every batch size, 1 = wide kernel (exchange on the compute warps, up to 64 sequences),
                            // 0 = K-split kernel with W_hh in shared memory (up to 32 sequences)
-    int pipe_groups = 0;   // groups of the pipelined kernel for 33..64 sequences: 0 / 2 = two of 32, 4 = four of 16
+    int pipe_group_size = 0;   // sequences per group of the pipelined kernel: 0 = choose by batch size, else 8, 16 or 32
     int xchg_copies = 4;   // measured: 4 replicas, words 128 B apart (one sequence) or 32 B apart (several)
     int xchg_stride = 0;   // 0 = choose by batch size
     long long* trace = nullptr;  // diagnostics buffer supplied through pimb200_lstm_set_trace (not owned)
@@ -1726,8 +1796,9 @@ extern "C" int pimb200_lstm_create(const void* const* params, int n_params, int 
     cudaMemset(h->xchg, 0, kXchgBytes);
     {
         const size_t ncta = (size_t)ceil_div(H, 8);
-        if (cudaMalloc(&h->bulk_data, 2 * ncta * kBulkMaxB * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
-        const size_t flag_bytes = (size_t)kBulkFlagCopies * 2 * kPipeMaxGroups * ncta * 128;   // the pipelined kernel's layout is the largest
+        // records of both parities: the pipelined kernel's layout (up to kPipeMaxB sequences) is the largest
+        if (cudaMalloc(&h->bulk_data, 2 * ncta * kPipeMaxB * 16) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
+        const size_t flag_bytes = (size_t)kBulkFlagCopies * 2 * kPipeMaxHalves * kPipeMaxGroups * ncta * 128;   // the pipelined kernel's layout is the largest
         if (cudaMalloc(&h->bulk_flags, flag_bytes) != cudaSuccess) return fail(PIMB200_ERR_NO_MEMORY);
         cudaMemset(h->bulk_flags, 0, flag_bytes);
     }
@@ -1796,13 +1867,13 @@ extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
 // A/B switch between the two batched kernels for 17..32 sequences (the wide one also takes 33..64).
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
-    h->bulk_wide = on < 0 ? 0 : (on > 2 ? 2 : on);
+    h->bulk_wide = on < 0 ? 0 : (on > 3 ? 3 : on);
     return PIMB200_OK;
 }
-// A/B switch of the pipelined kernel for 33..64 sequences: 2 = two groups of 32 (default), 4 = four groups of 16.
-extern "C" int pimb200_lstm_set_pipe_groups(pimb200_lstm* h, int groups) {
-    if (!h || (groups != 0 && groups != 2 && groups != 4)) return PIMB200_ERR_BAD_ARG;
-    h->pipe_groups = groups;
+// Tuning switch of the pipelined kernel: sequences per independently advancing group (8, 16 or 32; 0 = by batch size).
+extern "C" int pimb200_lstm_set_pipe_group_size(pimb200_lstm* h, int seqs) {
+    if (!h || (seqs != 0 && seqs != 8 && seqs != 16 && seqs != 32)) return PIMB200_ERR_BAD_ARG;
+    h->pipe_group_size = seqs;
     return PIMB200_OK;
 }
 extern "C" int pimb200_lstm_set_exchange_stride(pimb200_lstm* h, int stride16) {
@@ -1841,10 +1912,10 @@ static size_t wide_smem(int H, int nt) {
     const int BP = nt * 8;
     return (size_t)BP * H * 2 + (size_t)kWideKq * 8 * (BP + 1) * 16 + (size_t)BP * 16 + 16;
 }
-static size_t pipe_smem(int H, int ntg, int ng) {
-    const int BPG = ntg * 8;
-    return (size_t)ng * BPG * H * 2 + (size_t)2 * kPipeComputeWarps * 8 * (BPG + 1) * 16 + (size_t)ng * BPG * 16 +
-           (size_t)2 * ng * 8 + 16;
+static size_t pipe_smem(int H, int upc, int ntg, int ng) {
+    const int BPG = ntg * 8, cpt = ((BPG + 15) / 16) * (upc / 8);
+    return (size_t)ng * BPG * H * 2 + (size_t)2 * kPipeTensorWarps * upc * (BPG + 1) * 16 +
+           (size_t)ng * cpt * kPipeGateThreads * 16 + (size_t)(2 * ng + 4) * 8 + 16;
 }
 static size_t tc_smem(int H, int BP) {
     return (size_t)(H / 64) * (kPersistRows * 128 + BP * 128) + (size_t)kPersistRows * BP * 4 + (size_t)BP * 16 + 64 + 1024;
@@ -1928,39 +1999,62 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
         }
         return PIMB200_OK;
     }
-    // pipelined register-resident recurrence: the default wherever the wide kernel applies
-    if (wide && h->bulk_wide >= 2 && bulk_fits && !tc_fits &&
+    // pipelined register-resident recurrence: the default for 33..128 lock-step sequences (below that a step is mostly
+    // exchange latency with little to overlap it with, and the wide kernel's shorter chain wins); 65..128 sequences run
+    // as two batch halves on CTAs of 16 hidden units each
+    const bool pipe_shape = wide_ok && !packed && B <= kPipeMaxB && (H / 8 <= h->sm_count) && (B <= 64 || H % 16 == 0);
+    const bool pipe_wanted = h->bulk_wide >= 2 && (B > 32 || h->bulk_wide >= 3);
+    if (pipe_shape && pipe_wanted && !tc_fits &&
         (h->variant == PIMB200_LSTM_PERSISTENT || (h->variant == PIMB200_LSTM_AUTO && T >= 8))) {
-        int ntg, ng;
-        if (B <= 16) { ntg = 2; ng = 1; }
-        else if (B <= 32) { ntg = 2; ng = 2; }
-        else if (h->pipe_groups == 4) { ntg = 2; ng = 4; }
-        else { ntg = 4; ng = 2; }
-        const size_t smem = pipe_smem(H, ntg, ng);
+        const int upc = B > 64 ? 16 : 8, halves = B > 64 ? 2 : 1;
+        const int b_half = halves == 2 ? 64 : B;   // sequences the first half holds
+        // sequences per group (8, 16 or 32) and the smallest instantiated group count (at most 4) that holds a half
+        int bpg = h->pipe_group_size;
+        if (bpg == 0) bpg = 16;
+        if (bpg * kPipeMaxGroups < b_half) bpg = 16;
+        if (upc == 16) bpg = 16;
+        const int need = ceil_div(b_half, bpg);
+        const int ng = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+        const int ntg = bpg / 8;
+        const size_t smem = pipe_smem(H, upc, ntg, ng);
         if ((int)smem <= h->max_smem_optin) {
             PipeArgs a;
             a.Whh = h->w_hh[ld]; a.bias = h->bias[ld]; a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
             a.h0 = h0; a.c0 = c0; a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride; a.hn = hn; a.cn = cn;
             a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
             a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
-            a.H = H; a.T = T; a.B = B; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
+            a.H = H; a.T = T; a.B = B; a.halves = halves; a.reverse = reverse ? 1 : 0; a.poll_limit = h->poll_limit;
             a.trace = h->trace;
             h->bulk_tag += (uint32_t)T + 1u;
-            const void* fn = ng == 1   ? (const void*)lstm_persistent_pipe_kernel<2, 1>
-                             : ntg == 4 ? (const void*)lstm_persistent_pipe_kernel<4, 2>
-                             : ng == 2  ? (const void*)lstm_persistent_pipe_kernel<2, 2>
-                                        : (const void*)lstm_persistent_pipe_kernel<2, 4>;
+            const void* fn = nullptr;
+            if (upc == 16) {
+                fn = (const void*)lstm_persistent_pipe_kernel<16, 2, 4>;
+            } else {
+                switch (ntg * 16 + ng) {
+                    case 1 * 16 + 1: fn = (const void*)lstm_persistent_pipe_kernel<8, 1, 1>; break;
+                    case 1 * 16 + 2: fn = (const void*)lstm_persistent_pipe_kernel<8, 1, 2>; break;
+                    case 1 * 16 + 4: fn = (const void*)lstm_persistent_pipe_kernel<8, 1, 4>; break;
+                    case 2 * 16 + 1: fn = (const void*)lstm_persistent_pipe_kernel<8, 2, 1>; break;
+                    case 2 * 16 + 2: fn = (const void*)lstm_persistent_pipe_kernel<8, 2, 2>; break;
+                    case 2 * 16 + 4: fn = (const void*)lstm_persistent_pipe_kernel<8, 2, 4>; break;
+                    case 4 * 16 + 1: fn = (const void*)lstm_persistent_pipe_kernel<8, 4, 1>; break;
+                    default: fn = (const void*)lstm_persistent_pipe_kernel<8, 4, 2>; break;
+                }
+            }
             PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             void* kargs[] = {&a};
             if (h->prof) prof_mark(h, st);
-            PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(kPipeThreads), kargs, smem, st));
+            PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(halves * H / upc), dim3(kPipeThreads), kargs, smem, st));
             if (h->prof) {
                 prof_mark(h, st);
-                h->prof_bytes += (double)T * 4.0 * H * H * 2.0;
+                // each batch half is a recurrence of its own on its own CTAs, with its own register-resident copy of W_hh
+                h->prof_bytes += (double)halves * T * 4.0 * H * H * 2.0;
             }
             return PIMB200_OK;
         }
     }
+    if (B > kBulkMaxB && !packed && h->variant != PIMB200_LSTM_STREAMED && h->variant != PIMB200_LSTM_AUTO)
+        return PIMB200_ERR_UNSUPPORTED;   // a persistent variant was requested for a batch only the pipelined kernel takes
     bool use_bulk = false;
     if (h->variant == PIMB200_LSTM_PERSISTENT) {
         if (!fits && !bulk_fits) return PIMB200_ERR_UNSUPPORTED;

@@ -1031,7 +1031,7 @@ struct pimb200_rnnt {
     int smem_mask_multi = 0;
     size_t smem_bytes_multi = 0;
     int greedy_multi = 1;   // 0 = always one utterance per cluster
-    int enc_batch = 64;     // utterances the encoder advances in lock step
+    int enc_batch = 128;    // utterances the encoder advances in lock step
     int cluster = 0;        // CTAs per cluster
     int resident = 1;       // clusters of each greedy kernel that are co-resident on the device (occupancy query)
     int resident_mma = 1;
@@ -1231,7 +1231,7 @@ extern "C" int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long
 }
 
 extern "C" int pimb200_rnnt_set_encoder_batch(pimb200_rnnt* h, int n) {
-    if (!h || n < 1 || n > 64) return PIMB200_ERR_BAD_ARG;
+    if (!h || n < 1 || n > 128) return PIMB200_ERR_BAD_ARG;
     h->enc_batch = n;
     return PIMB200_OK;
 }

@@ -146,9 +146,10 @@ struct RuntimeHandle {
         : rt(std::make_unique<runtime::NNRuntime>(g.graph, model_type)) {
         if (rt->lastResult() != RetVal::SUCCESS) throw std::runtime_error("NNRuntime: preProcess failed");
     }
-    std::vector<at::Tensor> inferenceModel(std::vector<at::Tensor> inputs) {
+    std::vector<at::Tensor> inferenceModel(std::vector<at::Tensor> inputs, bool profiling, const std::string& profile_path) {
         std::vector<at::Tensor> out;
-        rt->inferenceModel(inputs, out, false);
+        if (!profile_path.empty()) rt->setProfilePath(profile_path);
+        rt->inferenceModel(inputs, out, profiling);
         if (rt->lastResult() != RetVal::SUCCESS) throw std::runtime_error("NNRuntime::inferenceModel returned FAILURE");
         return out;
     }
@@ -195,5 +196,9 @@ PYBIND11_MODULE(_pimb200_host, m) {
         .def("add_multistream", &GraphBuilder::addMultiStream);
     py::class_<RuntimeHandle>(m, "NNRuntime")
         .def(py::init<GraphBuilder&, const std::string&>(), py::arg("graph"), py::arg("model_type") = "")
-        .def("inferenceModel", &RuntimeHandle::inferenceModel);
+        .def("inferenceModel", &RuntimeHandle::inferenceModel, py::arg("input_tensors"), py::arg("profiling") = false,
+             py::arg("profile_path") = "");
+    m.def("fallback_count", &runtime::tensor_ops::fallbackCount,
+          "how often an operator took the libtorch call instead of a device kernel of this library since the last reset");
+    m.def("reset_fallback_count", &runtime::tensor_ops::resetFallbackCount);
 }

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 ROOT = os.path.dirname(PKG)
 OUT = os.path.join(PKG, "_pimb200_host.so")
-SOURCES = ["stream_executor.cpp", "op_executors.cpp", "bindings.cpp"]
+SOURCES = ["tensor_ops.cpp", "stream_executor.cpp", "op_executors.cpp", "bindings.cpp"]
 
 
 def needs_build() -> bool:
@@ -47,7 +47,7 @@ def build(force: bool = False) -> str:
             raise RuntimeError(f"g++ failed on {src}:\n{res.stdout}{res.stderr}")
         return obj
 
-    with ThreadPoolExecutor(max_workers=3) as ex:
+    with ThreadPoolExecutor(max_workers=4) as ex:
         objs = list(ex.map(cc, SOURCES))
     link = ["g++", "-shared", "-o", OUT, *objs, f"-L{tlib}", "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda",
             "-ltorch_python", f"-L{PKG}", "-lpimb200", f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN"]

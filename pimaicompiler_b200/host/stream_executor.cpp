@@ -3,6 +3,8 @@
 
 #include <ATen/cuda/CUDAContext.h>
 
+#include <cstdio>
+
 #include "pimb200.h"
 
 namespace nn_compiler {
@@ -14,28 +16,12 @@ AtenLSTM1Layer::~AtenLSTM1Layer() {
 
 namespace runtime {
 
-// Same classes as the reference's router (runtime/source/executor/utils/utils.cpp:373-396) on shapes already
-// padded to rank 4: vector classes need both leading dims to be 1; an operand is a vector when exactly one of its
-// last two extents differs from 1, a matrix when both do.
-GEMM_TYPE getGemmType(const std::vector<int64_t>& a, const std::vector<int64_t>& b) {
-    if (a.size() != 4 || b.size() != 4) return GEMM_TYPE::UNKNOW;
-    const bool lead_one = a[0] == 1 && a[1] == 1 && b[0] == 1 && b[1] == 1;
-    if (!lead_one) return GEMM_TYPE::MM;
-    const int na = (a[2] != 1) + (a[3] != 1), nb = (b[2] != 1) + (b[3] != 1);
-    if (na == 1 && nb == 1) return GEMM_TYPE::VV;
-    if (na == 1 && nb == 2) return GEMM_TYPE::VM;
-    if (na == 2 && nb == 1) return GEMM_TYPE::MV;
-    return GEMM_TYPE::MM;
-}
-
 StreamExecutor::StreamExecutor(std::shared_ptr<ir::NNGraph> graph, std::string model_type)
     : graph_(std::move(graph)), model_type_(std::move(model_type)) {
     registerOp();
 }
 
-StreamExecutor::~StreamExecutor() {
-    for (auto s : streams_) cudaStreamDestroy(s);
-}
+StreamExecutor::~StreamExecutor() = default;
 
 void StreamExecutor::registerOp() {
     using namespace op_executor;
@@ -84,18 +70,10 @@ RetVal StreamExecutor::preProcess() {
         if (layer->getType() == ir::LayerType::ATENLSTM1 || layer->getType() == ir::LayerType::ATENLSTM2) {
             auto lstm = std::static_pointer_cast<ir::AtenLSTM1Layer>(layer);
             if (lstm->getPackedHandle()) continue;
-            const auto& pv = lstm->getParamVector();
-            if (pv.size() < 2) return RetVal::FAILURE;
-            std::vector<const void*> ptrs;
-            for (auto& p : pv) {
-                if (!p.is_cuda() || p.scalar_type() != at::kHalf || !p.is_contiguous()) return RetVal::FAILURE;
-                ptrs.push_back(p.data_ptr());
-            }
-            const int H = (int)pv[1].size(1), I = (int)pv[0].size(1);
-            pimb200_lstm* h = nullptr;
-            const int rc = pimb200_lstm_create(ptrs.data(), (int)ptrs.size(), (int)lstm->getNumLayers(),
-                                               lstm->getBidirectional(), I, H, lstm->getHasBiases(), &h);
-            if (rc != PIMB200_OK) return RetVal::FAILURE;
+            tensor_ops::OpContext cx;
+            pimb200_lstm* h = tensor_ops::lstmPack(cx, lstm->getParamVector(), lstm->getNumLayers(), lstm->getBidirectional() != 0,
+                                                   lstm->getHasBiases() != 0);
+            if (!h || cx.status != PIMB200_OK) return RetVal::FAILURE;
             lstm->setPackedHandle(h);
         }
     }
@@ -116,18 +94,45 @@ bool StreamExecutor::checkValidBlobID(int64_t blob_id) { return global_blobs_.fi
 
 cudaStream_t StreamExecutor::currentStream() const { return at::cuda::getCurrentCUDAStream().stream(); }
 
-const std::vector<cudaStream_t>& StreamExecutor::streamPool() {
-    if (streams_.empty()) {
-        for (int i = 0; i < 4; ++i) {
-            cudaStream_t s = nullptr;
-            if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) == cudaSuccess) streams_.push_back(s);
-        }
-    }
-    return streams_;
+c10::cuda::CUDAStream StreamExecutor::sideStream(size_t i) {
+    while (streams_.size() < 4) streams_.push_back(c10::cuda::getStreamFromPool());
+    return streams_[i % streams_.size()];
+}
+
+at::cuda::CUDAEvent& StreamExecutor::event(size_t i) {
+    while (events_.size() <= i) events_.push_back(std::make_unique<at::cuda::CUDAEvent>(cudaEventDefault));   // timing enabled: the profiler reads them
+    return *events_[i];
 }
 
 RetVal StreamExecutor::inferenceModel(const std::vector<torch::Tensor>& input_tensors,
                                       std::vector<torch::Tensor>& output_tensors) {
+    return run(input_tensors, output_tensors, false);
+}
+
+RetVal StreamExecutor::inferenceModelwithProfiling(const std::vector<torch::Tensor>& input_tensors,
+                                                   std::vector<torch::Tensor>& output_tensors) {
+    return run(input_tensors, output_tensors, true);
+}
+
+// A kernel whose bounded wait gave up leaves PIMB200_ERR_TIMEOUT in a device status word; outputs of such a run are
+// undefined, so the run is reported as failed.
+RetVal StreamExecutor::checkDeviceStatus() {
+    if (cudaStreamSynchronize(currentStream()) != cudaSuccess) return RetVal::FAILURE;
+    int rc = pimb200_gemm_last_status();
+    for (auto& layer : graph_->getLayers()) {
+        if (layer->getType() != ir::LayerType::ATENLSTM1 && layer->getType() != ir::LayerType::ATENLSTM2) continue;
+        auto lstm = std::static_pointer_cast<ir::AtenLSTM1Layer>(layer);
+        if (lstm->getPackedHandle()) {
+            const int s = pimb200_lstm_last_status(lstm->getPackedHandle());
+            if (rc == PIMB200_OK) rc = s;
+        }
+    }
+    setStatus(rc);
+    return rc == PIMB200_OK ? RetVal::SUCCESS : RetVal::FAILURE;
+}
+
+RetVal StreamExecutor::run(const std::vector<torch::Tensor>& input_tensors, std::vector<torch::Tensor>& output_tensors,
+                           bool profiling) {
     if (input_tensors.size() != graph_->input_ids.size()) return RetVal::FAILURE;
     if (op_executor_.size() != graph_->getLayers().size() && preProcess() != RetVal::SUCCESS) return RetVal::FAILURE;
     status_ = 0;
@@ -136,12 +141,43 @@ RetVal StreamExecutor::inferenceModel(const std::vector<torch::Tensor>& input_te
     for (size_t i = 0; i < input_tensors.size(); ++i)
         updateBlob(graph_->input_ids[i], ir::DataType::TENSOR, torch::jit::IValue(input_tensors[i]));
     const auto& layers = graph_->getLayers();
+    struct Span { std::string name; size_t e0, e1; };
+    std::vector<Span> spans;
+    size_t next_event = 16;   // events 0..15 belong to MULTISTREAM
     for (cursor_ = 0; cursor_ < (int64_t)layers.size();) {
         auto layer = layers[cursor_];
         const int64_t before = cursor_;
-        op_executor_[cursor_](layer, *this);
+        if (profiling) {
+            event(next_event).record(c10::cuda::getCurrentCUDAStream());
+            op_executor_[cursor_](layer, *this);
+            event(next_event + 1).record(c10::cuda::getCurrentCUDAStream());
+            spans.push_back({layer->getName(), next_event, next_event + 1});
+            next_event += 2;
+        } else {
+            op_executor_[cursor_](layer, *this);
+        }
         if (status_ != 0) return RetVal::FAILURE;
         if (cursor_ == before) ++cursor_;  // executors that jump (MULTISTREAM) set the cursor themselves
+    }
+    if (checkDeviceStatus() != RetVal::SUCCESS) return RetVal::FAILURE;
+    if (profiling) {
+        // Chrome trace ("traceEvents" of complete events, microseconds): one span per op, laid end to end on the
+        // device timeline of the launching stream
+        FILE* f = std::fopen(profile_path_.c_str(), "w");
+        if (f) {
+            std::fprintf(f, "{\"otherData\": {}, \"traceEvents\": [");
+            double t0 = 0.0;
+            for (size_t i = 0; i < spans.size(); ++i) {
+                const double start_us = i == 0 ? 0.0 : 1e3 * event(spans[0].e0).elapsed_time(event(spans[i].e0));
+                const double dur_us = 1e3 * event(spans[i].e0).elapsed_time(event(spans[i].e1));
+                (void)t0;
+                std::fprintf(f, "%s{\"cat\": \"function\", \"dur\": %.3f, \"name\": \"%s\", \"ph\": \"X\", \"pid\": 0, "
+                                "\"tid\": 0, \"ts\": %.3f}",
+                             i ? ", " : "", dur_us, spans[i].name.c_str(), start_us);
+            }
+            std::fprintf(f, "]}\n");
+            std::fclose(f);
+        }
     }
     for (auto id : graph_->output_ids) {
         auto& iv = findBlob(id).second;
@@ -169,9 +205,20 @@ NNRuntime::NNRuntime(std::shared_ptr<ir::NNGraph> graph, std::string model_type)
 NNRuntime::~NNRuntime() = default;
 
 void NNRuntime::inferenceModel(const std::vector<torch::Tensor>& input_tensors,
-                               std::vector<torch::Tensor>& output_tensors, bool /*profiling*/) {
-    last_ = executor_->inferenceModel(input_tensors, output_tensors);
+                               std::vector<torch::Tensor>& output_tensors, bool profiling) {
+    if (!profiling) {
+        last_ = executor_->inferenceModel(input_tensors, output_tensors);
+        return;
+    }
+    // as the reference does (runtime/source/nn_runtime.cpp:44-53): a few untimed runs first, then the profiled one
+    for (int i = 0; i < 3 && last_ == RetVal::SUCCESS; ++i) {
+        std::vector<torch::Tensor> scratch;
+        last_ = executor_->inferenceModel(input_tensors, scratch);
+    }
+    last_ = executor_->inferenceModelwithProfiling(input_tensors, output_tensors);
 }
+
+void NNRuntime::setProfilePath(const std::string& path) { executor_->setProfilePath(path); }
 
 }  // namespace runtime
 }  // namespace nn_compiler

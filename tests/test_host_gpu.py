@@ -256,3 +256,82 @@ def test_pipeline_manager_rnnt_from_torchscript():
     _, ref_logits, ref_choice = to.rnnt_greedy(w, feats, cfg, forced)
     assert_close(logits, ref_logits, 2e-2, 1e-2, "PipelineManager logits")
     assert transcript.tolist() == [k for k in forced if k != cfg.blank] and int(n) == len(transcript)
+
+
+def test_multistream_with_matrix_branches_and_transposed_views():
+    # MULTISTREAM branches whose operands need temporaries (an MM-class product, a transposed view of a row-major
+    # weight, a non-contiguous activation): the copies must be made on the branch's own stream.  Repeated, so that a
+    # race between the preparation and the kernel, or a recycled temporary, shows as a wrong result.
+    h = _host()
+    g = torch.Generator().manual_seed(17)
+    K, N, J = 256, 384, 24
+    X = h16(torch.randn(J, K, generator=g))
+    Wt = h16(torch.randn(K, N, generator=g) * 0.05)          # used as Wt.t(): a transposed view, K-major rows
+    W2 = h16(torch.randn(N, K, generator=g) * 0.05)
+    xs = h16(torch.randn(K, 2, generator=g))                  # column 0 of a [K, 2] tensor: non-contiguous vector
+    b = h16(torch.randn(N, generator=g))
+    gr = h.Graph()
+    iX, iWt, iW2, ixs, ib = (gr.add_input() for _ in range(5))
+    outs = gr.add_multistream([("matmul", [iX, iWt], ""), ("matmul", [iW2, ixs], ""),
+                               ("addmm", [ib, iW2, ixs], "aten::relu"), ("matmul", [iX, iWt], "")])
+    for o in outs:
+        gr.mark_output(o)
+    rt = h.NNRuntime(gr, "SwitchTransformer")
+    Xd, Wtd, W2d, bd = to_dev(X), to_dev(Wt), to_dev(W2), to_dev(b)
+    xsd = xs.to(torch.float16).cuda()[:, :1]                  # [K, 1] view with stride 2
+    refs = [X @ Wt, W2 @ xs[:, :1], torch.relu(W2 @ xs[:, :1] + b.view(-1, 1)), X @ Wt]
+    for _ in range(20):
+        res = rt.inferenceModel([Xd, Wtd, W2d, xsd, bd])
+        for r, ref in zip(res, refs):
+            assert_close(r.reshape(ref.shape), ref, 4e-3, 2e-3, "multistream branch with temporaries")
+
+
+def test_profiling_writes_a_chrome_trace_with_one_span_per_op():
+    import json
+    h = _host()
+    g = torch.Generator().manual_seed(3)
+    N, K = 256, 512
+    W, b, x = h16(torch.randn(N, K, generator=g) * 0.05), h16(torch.randn(N, generator=g)), h16(torch.randn(K, generator=g))
+    gr = h.Graph()
+    i_b, i_W, i_x = gr.add_input(), gr.add_input(), gr.add_input()
+    y = gr.add_addmm(i_b, i_W, i_x, act="aten::relu")
+    gr.mark_output(gr.add_tanh(y))
+    rt = h.NNRuntime(gr)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "trace.json")
+        (out,) = rt.inferenceModel([to_dev(b), to_dev(W), to_dev(x).view(K, 1)], profiling=True, profile_path=path)
+        with open(path) as f:
+            trace = json.load(f)
+    ev = trace["traceEvents"]
+    assert [e["name"] for e in ev] == ["aten::addmm", "aten::tanh"]
+    assert all(e["ph"] == "X" and e["dur"] > 0 for e in ev) and ev[1]["ts"] >= ev[0]["ts"]
+    assert_close(out.view(-1), torch.tanh(torch.relu(W @ x + b)), ATOL, RTOL, "profiled run result")
+
+
+def test_hot_shapes_never_fall_back_to_the_library_call():
+    # the shapes of the benchmark configurations (batch-1 linear layers in the swapped addmm form, the RNN-T joint pair,
+    # decoder-style add / softmax / argmax / layer_norm / cat rows) must all run on this library's kernels
+    h = _host()
+    g = torch.Generator().manual_seed(5)
+    h.reset_fallback_count()
+    for (N, K) in ((4096, 1024), (1024, 1024), (29, 512), (512, 1024), (512, 320), (2048, 512), (512, 2048)):
+        W, b, x = h16(torch.randn(N, K, generator=g) * 0.03), h16(torch.randn(N, generator=g)), h16(torch.randn(K, generator=g))
+        gr = h.Graph()
+        i_b, i_W, i_x = gr.add_input(), gr.add_input(), gr.add_input()
+        y = gr.add_addmm(i_b, i_W, i_x, act="aten::relu")
+        gr.mark_output(y)
+        gr.mark_output(gr.add_matmul(i_W, i_x))
+        rt = h.NNRuntime(gr)
+        o1, o2 = rt.inferenceModel([to_dev(b), to_dev(W), to_dev(x).view(1, 1, K, 1)])
+        assert_close(o1.view(-1), torch.relu(W @ x + b), 4e-3, 2e-3, f"addmm {N}x{K}")
+    gr = h.Graph()
+    ia, ib2 = gr.add_input(), gr.add_input()
+    s = gr.add_add(ia, ib2)
+    gr.mark_output(gr.add_softmax(s))
+    gr.mark_output(gr.add_argmax(s))
+    gr.mark_output(gr.add_layer_norm(s, [512]))
+    gr.mark_output(gr.add_cat(gr.add_list([s, s]), 1))
+    rt = h.NNRuntime(gr)
+    a = to_dev(h16(torch.randn(1, 512, generator=g)))
+    rt.inferenceModel([a, a])
+    assert h.fallback_count() == 0

@@ -24,14 +24,14 @@ def _ops():
     return ops
 
 
-def _run(ops, ps, x, h0, c0, L, bi, hb, bf, variant, bulk_wide=1):
+def _run(ops, ps, x, h0, c0, L, bi, hb, bf, variant, bulk_wide=None):
     T = x.shape[1] if bf else x.shape[0]
     I, H = x.shape[2], ps[1].shape[1]
     m = ops.Lstm([to_dev(p) for p in ps], L, bi, I, H, hb)
     m.set_variant(variant)
-    if not bulk_wide:
+    if bulk_wide is not None:   # None = the library's default choice of persistent kernel by batch size
         from pimaicompiler_b200 import _lib
-        assert _lib.lib().pimb200_lstm_set_bulk_wide(m._h, 0) == 0
+        assert _lib.lib().pimb200_lstm_set_bulk_wide(m._h, bulk_wide) == 0
     y, hn, cn = m.forward(to_dev(x), None if h0 is None else to_dev(h0), None if c0 is None else to_dev(c0), bf)
     torch.cuda.synchronize()
     assert m.last_status() == 0
@@ -90,18 +90,23 @@ CASES = [
     (3, 40, 16, 32, 1, False, True, False, True),        # eight tiles, the last ones ragged
     (5, 64, 240, 1024, 1, False, True, True, False),     # 64 utterances at the encoder width, batch_first
     (4, 57, 32, 128, 2, True, True, False, True),        # ragged eighth tile, bidirectional, two layers
-    (2, 70, 16, 32, 1, False, True, False, True),        # B > 64: streamed only
+    (2, 70, 16, 32, 1, False, True, False, True),        # 65..128 sequences: two batch halves, the second ragged
+    (4, 128, 32, 1024, 1, False, True, True, False),     # the largest lock-step batch at the encoder width, batch_first
+    (3, 97, 24, 256, 2, True, True, False, True),        # ragged second half, bidirectional, two layers
+    (5, 33, 16, 1024, 1, False, True, False, True),      # smallest batch the pipelined kernel takes by default
     (3, 2, 7, 5, 2, False, True, False, True),           # odd sizes: scalar path
 ]
 
 
 @pytest.mark.parametrize("case", CASES)
-@pytest.mark.parametrize("variant", ["streamed", "persistent", "ksplit", "tagged"])
+@pytest.mark.parametrize("variant", ["streamed", "persistent", "pipe", "wide", "ksplit", "tagged"])
 def test_lstm_matches_oracle(case, variant):
     ops = _ops()
     T, B, I, H, L, bi, hb, bf, nz = case
-    if variant == "persistent" and (B > 64 or H % 16):
-        pytest.skip("persistent variants take up to 64 sequences and H % 16 == 0")
+    if variant in ("persistent", "pipe") and (B > 128 or H % 16):
+        pytest.skip("the persistent kernels take up to 128 sequences and H % 16 == 0")
+    if variant == "wide" and (B > 64 or H % 16):
+        pytest.skip("the exchange-on-compute-warps kernel takes up to 64 sequences and H % 16 == 0")
     if variant == "ksplit" and (B < 2 or B > 32 or H % 16):
         pytest.skip("the K-split batched kernel takes 2..32 sequences and H % 16 == 0")
     if variant == "tagged" and (B > 8 or H % 16):
@@ -114,9 +119,9 @@ def test_lstm_matches_oracle(case, variant):
     c0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5) if nz else None
     ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, bi, hb, None if h0 is None else h0.numpy(),
                   None if c0 is None else c0.numpy(), bf)
-    vid = {"streamed": ops.LSTM_STREAMED, "persistent": ops.LSTM_PERSISTENT, "ksplit": ops.LSTM_PERSISTENT,
-           "tagged": ops.LSTM_PERSISTENT_TAGGED}[variant]
-    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, vid, bulk_wide=0 if variant == "ksplit" else 1)
+    vid = {"streamed": ops.LSTM_STREAMED, "persistent": ops.LSTM_PERSISTENT, "pipe": ops.LSTM_PERSISTENT,
+           "wide": ops.LSTM_PERSISTENT, "ksplit": ops.LSTM_PERSISTENT, "tagged": ops.LSTM_PERSISTENT_TAGGED}[variant]
+    got = _run(ops, ps, x, h0, c0, L, bi, hb, bf, vid, bulk_wide={"ksplit": 0, "wide": 1, "pipe": 3}.get(variant))
     for name, a, b in zip(("y", "hn", "cn"), got, ref):
         assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"{variant} {name} {case}")
 
@@ -247,7 +252,7 @@ def test_lstm_benchmark_shape_batched_properties():
     # time-major through the 3-D tensor map).  Size-independent properties instead of an oracle run:
     #   * the persistent kernel agrees with the streamed one (different kernels, different summation order);
     #   * a repeat is bit-identical;
-    #   * every sequence is computed independently of its batch: sequence n alone reproduces row n bit for bit
+    #   * every sequence is computed independently of its batch: a sub-batch reproduces its rows bit for bit
     ops = _ops()
     g = torch.Generator().manual_seed(64)
     T, B, I, H, L = 1000, 64, 240, 1024, 2
@@ -266,9 +271,14 @@ def test_lstm_benchmark_shape_batched_properties():
     assert_close(y, ys, LSTM_ATOL, LSTM_RTOL, "persistent vs streamed y at T=1000, B=64")
     assert_close(cn, cns, LSTM_ATOL, LSTM_RTOL, "persistent vs streamed c_n")
     m.set_variant(ops.LSTM_PERSISTENT)
+    # a smaller lock-step batch of the same kernel family (17..128 sequences) reproduces its rows bit for bit
+    yb, hnb, cnb = m.forward(x[20:44].contiguous(), batch_first=True)
+    assert torch.equal(yb, y[20:44]) and torch.equal(hnb, hn[:, 20:44]) and torch.equal(cnb, cn[:, 20:44])
+    # a single sequence runs on the low-latency kernel (another summation order): equal within the LSTM tolerance
     for n in (0, 37, 63):
         y1, hn1, cn1 = m.forward(x[n:n + 1].contiguous(), batch_first=True)
-        assert torch.equal(y1[0], y[n]) and torch.equal(hn1[:, 0], hn[:, n]) and torch.equal(cn1[:, 0], cn[:, n])
+        assert_close(y1[0], y[n], LSTM_ATOL, LSTM_RTOL, f"sequence {n} alone vs in the batch")
+        assert_close(cn1[:, 0], cn[:, n], LSTM_ATOL, LSTM_RTOL, f"c_n of sequence {n} alone vs in the batch")
 
 
 def test_lstm_benchmark_shape_batched_vs_libtorch():

@@ -168,9 +168,9 @@ def test_rnnt_ragged_group_sizes_and_odd_frame_count():
 
 
 def test_rnnt_benchmark_scale_is_independent_of_batching():
-    # The benchmark's configuration at full length (1000 frames): 72 utterances in one call (two encoder groups, nine
-    # greedy groups over two rounds of clusters) against the first 16 of them in a call of their own (one narrower
-    # encoder group, two greedy groups).  Every utterance is a column of the same lock-step arithmetic whatever the
+    # The benchmark's configuration at full length (1000 frames): 72 utterances in one call (one encoder group of two
+    # batch halves, nine greedy groups over two rounds of clusters) against the first 24 of them in a call of their own
+    # (one narrower encoder group, three greedy groups).  Every utterance is a column of the same lock-step arithmetic whatever the
     # batch, so transcripts and logits must be bit-identical; a repeat of the large call as well.
     cfg = to.RnntConfig()
     w = to.make_rnnt_weights(cfg, seed=9, gain=2.0, logit_gain=8.0)
@@ -182,9 +182,9 @@ def test_rnnt_benchmark_scale_is_independent_of_batching():
     toks, logits = dec.decode(feats, want_logits=True)
     toks_again, logits_again = dec.decode(feats, want_logits=True)
     assert toks_again == toks and torch.equal(logits_again, logits)
-    toks16, logits16 = dec.decode(feats[:16].contiguous(), want_logits=True)
-    assert toks16 == toks[:16]
-    assert torch.equal(logits16, logits[:16])
+    toks24, logits24 = dec.decode(feats[:24].contiguous(), want_logits=True)
+    assert toks24 == toks[:24]
+    assert torch.equal(logits24, logits[:24])
     lens = [len(t) for t in toks]
     assert 0 < min(lens) and max(lens) <= 500 and len(set(lens)) > 1   # transcripts differ, none empty
 
