@@ -12,7 +12,7 @@
 //     a thread holds (k0 + 8t .. k0 + 8t + 7 of rows g and g + 8) are fed as the fragment's "2t, 2t+1, 2t+8, 2t+9"
 //     slots of two products, and the B fragment (X, read through L1: it is small and shared by all CTAs) is taken
 //     from the same k positions.  No shared-memory staging, no shuffles;
-//   * the 8 K-partials meet in shared memory; 16 x J outputs get bias, activation and the fp16 (or fp32) store.
+//   * the K-partials meet in shared memory; the CTA's rows x J outputs get bias, activation and the fp16 (or fp32) store.
 #include "common.cuh"
 
 namespace pimb200 {

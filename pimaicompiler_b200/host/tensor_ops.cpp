@@ -33,11 +33,25 @@ at::Tensor fusedMatmul(OpContext& cx, at::Tensor L, at::Tensor R, const at::Tens
     const int64_t rowsL = L.numel() / K;                       // every leading extent of L is a row
     const int64_t colsR = R.dim() == 1 ? 1 : R.size(-1);
     const int64_t Kr = R.dim() == 1 ? R.size(0) : R.size(-2);
-    if (Kr != K || R.numel() != Kr * colsR) return {};         // a batched right operand is not a hot-path shape
+    if (Kr != K) return {};
     const at::Tensor b = bias.defined() ? bias.contiguous() : bias;
     const void* bp = b.defined() ? b.data_ptr() : nullptr;
     at::Tensor out;
     int rc = PIMB200_OK;
+    if (R.numel() != Kr * colsR) {
+        // a batched right operand: only the stack of column vectors [J, K, 1] under a weight matrix [N, K], which is
+        // what SwapAddmmInputs makes of a linear layer over a sequence of J rows (transpose, addmm, transpose back)
+        if (L.dim() != 2 || R.dim() != 3 || colsR != 1 || (b.defined() && b.numel() != rowsL)) return {};
+        at::Tensor W = L.contiguous();
+        at::Tensor X = R.squeeze(-1).contiguous();              // [J, K]; the transposed view of a contiguous [J, 1, K]
+        const int64_t J = X.size(0);
+        out = at::empty({J, rowsL}, L.options());
+        rc = pimb200_gemm_wx(W.data_ptr(), X.data_ptr(), bp, out.data_ptr(), (int)rowsL, (int)K, (int)J, (int)K, (int)rowsL,
+                             act, 0, cx.stream);
+        cx.note(rc);
+        if (rc != PIMB200_OK) return {};
+        return out.reshape(out_sizes);
+    }
     const GEMM_TYPE type = getGemmType(pad4({rowsL, K}), pad4({K, colsR}));
     if (type == GEMM_TYPE::VV) {
         L = L.contiguous(); R = R.contiguous();
@@ -113,7 +127,14 @@ at::Tensor addmm(OpContext& cx, const at::Tensor& self, const at::Tensor& mat1, 
     at::Tensor s = self;
     if (self.dim() == 1 && mat2.dim() >= 2 && self.size(0) == mat1.size(-2) && self.size(0) != mat2.size(-1))
         s = self.unsqueeze(1);  // per-row bias of the swapped form
-    out = at::addmm(s, mat1.dim() > 2 ? mat1.squeeze(0) : mat1, mat2.dim() > 2 ? mat2.squeeze(0) : mat2, beta, alpha);
+    if (mat1.dim() > 2 || mat2.dim() > 2) {
+        // operands with leading extents (a sequence of rows behind SwapAddmmInputs' transposes): matmul's shape rule
+        out = at::matmul(mat1, mat2);
+        if (alpha != 1.0) out = out * alpha;
+        out = out + (beta == 1.0 ? s : s * beta);
+    } else {
+        out = at::addmm(s, mat1, mat2, beta, alpha);
+    }
     return relu ? at::relu(out) : out;
 }
 
@@ -155,7 +176,9 @@ at::Tensor add(OpContext& cx, const at::Tensor& a, const at::Tensor& b, double a
         return out;
     }
     fellBack();
-    return at::add(a, b, alpha);
+    // libtorch rejects a floating-point alpha on integral operands
+    const bool integral = c10::isIntegralType(a.scalar_type(), true) && c10::isIntegralType(b.scalar_type(), true);
+    return integral ? at::add(a, b, c10::Scalar((int64_t)alpha)) : at::add(a, b, c10::Scalar(alpha));
 }
 
 at::Tensor softmax(OpContext& cx, const at::Tensor& x, int64_t dim, bool log) {

@@ -153,7 +153,11 @@ def test_lstm_and_linear_model_through_the_reference_compiler(T):
     mod.reset_fallback_count()
     logits, hn, cn = pm.inferenceModel(_dev([x, h0, c0]))
     assert mod.fallback_count() == 0, "a hot-path op fell back to the library call"
-    ref = m.float()(x.float(), h0.float(), c0.float())
+    m = m.float()
+    for name in ("w_ih0", "w_hh0", "b_ih0", "b_hh0", "w_ih1", "w_hh1", "b_ih1", "b_hh1"):   # plain attributes, not parameters
+        setattr(m, name, getattr(m, name).float())
+    with torch.backends.mkldnn.flags(enabled=False):   # oneDNN has no LSTM primitive for every shape on every host
+        ref = m(x.float(), h0.float(), c0.float())
     assert logits.shape == ref[0].shape
     assert_close(logits, ref[0], 2e-2, 1e-2, "logits")
     assert_close(hn, ref[1], 4e-3, 4e-3, "h_n")

@@ -98,7 +98,10 @@ def test_rnnt_batch_of_utterances_matches_single():
     cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=32, joint_hidden=48, vocab=11, blank=10)
     w = to.make_rnnt_weights(cfg, seed=4, gain=2.0, logit_gain=6.0)
     dec = _decoder(cfg, w)
-    n, T = 13, 30   # more utterances than clusters fit on the device
+    # more utterances than clusters fit on the device; 80 frames (40 after the time reduction), so that every
+    # projection has more than 32 rows at any batch and takes the same GEMM kernel (the few-row streaming kernel
+    # sums in another order)
+    n, T = 13, 80
     feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
     dec.set_greedy_multi(2)   # FMA lock-step kernel: same summation order as the one-utterance kernel
     toks, logits = dec.decode(feats, want_logits=True)
@@ -169,8 +172,8 @@ def test_rnnt_ragged_group_sizes_and_odd_frame_count():
 
 def test_rnnt_benchmark_scale_is_independent_of_batching():
     # The benchmark's configuration at full length (1000 frames): 72 utterances in one call (one encoder group of two
-    # batch halves, nine greedy groups over two rounds of clusters) against the first 24 of them in a call of their own
-    # (one narrower encoder group, three greedy groups).  Every utterance is a column of the same lock-step arithmetic whatever the
+    # batch halves, nine greedy groups over two rounds of clusters) against the first 40 of them in a call of their own
+    # (one narrower encoder group of the same kernel family, five greedy groups).  Every utterance is a column of the same lock-step arithmetic whatever the
     # batch, so transcripts and logits must be bit-identical; a repeat of the large call as well.
     cfg = to.RnntConfig()
     w = to.make_rnnt_weights(cfg, seed=9, gain=2.0, logit_gain=8.0)
@@ -182,9 +185,9 @@ def test_rnnt_benchmark_scale_is_independent_of_batching():
     toks, logits = dec.decode(feats, want_logits=True)
     toks_again, logits_again = dec.decode(feats, want_logits=True)
     assert toks_again == toks and torch.equal(logits_again, logits)
-    toks24, logits24 = dec.decode(feats[:24].contiguous(), want_logits=True)
-    assert toks24 == toks[:24]
-    assert torch.equal(logits24, logits[:24])
+    toks40, logits40 = dec.decode(feats[:40].contiguous(), want_logits=True)
+    assert toks40 == toks[:40]
+    assert torch.equal(logits40, logits[:40])
     lens = [len(t) for t in toks]
     assert 0 < min(lens) and max(lens) <= 500 and len(set(lens)) > 1   # transcripts differ, none empty
 
