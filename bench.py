@@ -376,14 +376,14 @@ def _graph_time_us(calls, reps):
     return e0.elapsed_time(e1) * 1e3 / (reps * len(calls))
 
 
-def measure_c2(reps_base, batches=(8, 32, 128), shapes_batched=None, rowops=True):
+def measure_c2(reps_base, batches=(8, 32, 128), shapes_batched=None, rowops=True, shapes=None):
     """C2: y = Wx + b at batch 1 for the five (N,K) shapes (weights rotated over > 126 MB so every call streams from
     HBM), and the same layers at batch 8/32/128 through the batched-stream GEMM."""
     from pimaicompiler_b200 import ops
     ops.init()
     peak, peak_src = load_peaks()
     dev = torch.device("cuda", torch.cuda.current_device())
-    shapes = [(4096, 1024), (4096, 2048), (1024, 1024), (32320, 1024), (29, 512)]
+    shapes = shapes or [(4096, 1024), (4096, 2048), (1024, 1024), (32320, 1024), (29, 512)]
     g = torch.Generator().manual_seed(1)
     results = []
     for (N, K) in shapes:
@@ -433,7 +433,13 @@ def run_c2(args):
     build.build()
     sampler = ClockSampler(0)
     sampler.start()
-    m = measure_c2(args.steps)
+    if args.c2_shape:   # a restricted sweep (one shape, chosen batches, no row ops): the small case a profiler capture uses
+        n, k = (int(v) for v in args.c2_shape.lower().split("x"))
+        batches = tuple(int(v) for v in args.c2_batches.split(",")) if args.c2_batches else ()
+        m = measure_c2(args.steps, batches=batches, rowops=False, shapes=[(32320, 1024), (n, k)] if (n, k) != (32320, 1024) else [(n, k)],
+                       shapes_batched=[(n, k)])
+    else:
+        m = measure_c2(args.steps)
     results, rowops, peak, peak_src = m["results"], m["rowops"], m["peak"], m["peak_src"]
     clocks = sampler.stop()
     big = next(r for r in results if r["N"] == 32320 and r["B"] == 1)
@@ -589,6 +595,8 @@ def main():
                     help="utterances per decode call (0 = the rank's whole shard in one call: the encoder still advances "
                          "groups of up to 128 utterances, the greedy kernel takes all of them at once)")
     ap.add_argument("--no-extras", action="store_true", help="skip the C1 / C2 figures of the default line")
+    ap.add_argument("--c2-shape", default="", help="with --workload c2: only this NxK shape (plus the headline shape), e.g. 4096x1024")
+    ap.add_argument("--c2-batches", default="", help="with --c2-shape: the batched-stream sizes to time, e.g. 8,32")
     ap.add_argument("--cpu-sample", type=int, default=64, help="utterances decoded on the CPU per baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--encoder-batch", type=int, default=0, help="utterances per lock-step encoder group (0 = default)")

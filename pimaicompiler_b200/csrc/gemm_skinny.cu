@@ -4,9 +4,9 @@
 // branches of a MULTISTREAM node): the arithmetic intensity is J flop per weight byte, far below the ridge, so the
 // bound is the one pass over W from HBM, exactly as for the GEMV.  A 128-row tcgen05 tile per CTA leaves most SMs
 // without work at N = 4096 (32 CTAs) and costs a fixed pipeline set-up; here every SM streams W instead:
-//   * a CTA owns 16 or 32 weight rows (one or two 16-row tiles), its 8 warps split the tiles and K between them
-//     (32 rows x 4 K-quarters for N >= 2048: one CTA per SM at N = 4096, 64 KB of W per SM in flight, and the two
-//     tiles of a K-quarter share their X loads through L1; 16 rows x 8 K-eighths below that, for more CTAs);
+//   * a CTA owns 16 or 32 weight rows (one or two 16-row tiles) and its 8 warps split K between them; with 32 rows
+//     (N >= 2048: one CTA per SM at N = 4096) a warp multiplies both tiles by the same X fragments; every load of a
+//     group of K blocks is issued before the previous group's products, so 8 KB per warp are in flight;
 //   * a warp reads its W rows with 128-bit loads that bypass L1, 8 consecutive k per thread and row, and uses them
 //     directly as mma.sync m16n8k16 A fragments: the contraction index is only a summation order, so the k positions
 //     a thread holds (k0 + 8t .. k0 + 8t + 7 of rows g and g + 8) are fed as the fragment's "2t, 2t+1, 2t+8, 2t+9"
@@ -23,10 +23,17 @@ constexpr int kSkinnyThreads = kSkinnyWarps * 32;
 constexpr int kSkinnyRows = 16;
 constexpr int kSkinnyMaxJ = 32;
 
+// not volatile: the compiler may move these loads and products freely (volatile asm statements keep their order, which
+// would put every block's loads behind the previous block's products and serialise the HBM round trips)
 __device__ __forceinline__ void mma16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 ldg_w(const __half* p) {
+    uint4 r;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
 }
 
 struct SkinnyArgs {
@@ -37,59 +44,91 @@ struct SkinnyArgs {
     int N, K, J, ldx, ldy, act, y_is_f32;
 };
 
-template <int NT, int MTC>   // n-tiles of 8 activation rows; 16-row weight tiles per CTA (1 or 2)
+// NT: n-tiles of 8 activation rows; MTW: 16-row weight tiles per warp (1 or 2; they share the warp's X fragments).
+// The 8 warps of a CTA split K; a warp walks its K range in groups of UB 32-wide blocks, the loads of the next group
+// in flight while the current one is multiplied.
+template <int NT, int MTW>
 __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs a) {
-    constexpr int KS = kSkinnyWarps / MTC;   // K splits
-    constexpr int ROWS = MTC * kSkinnyRows;
+    constexpr int KS = kSkinnyWarps;
+    constexpr int ROWS = MTW * kSkinnyRows;
+    constexpr int UB = 4 / MTW;
     __shared__ float part[KS][ROWS][NT * 8 + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int mt = warp % MTC, ks = warp / MTC;
-    const int n0 = blockIdx.x * ROWS + mt * kSkinnyRows;
+    const int n0 = blockIdx.x * ROWS;
     const int K = a.K;
     // this warp's K range, in blocks of 32 (whole blocks; the ragged tail is zero-filled)
     const int blocks = (K + 31) >> 5;
     const int per = (blocks + KS - 1) / KS;
-    const int b_lo = ks * per, b_hi = min(blocks, b_lo + per);
-    const int r_lo = min(n0 + g, a.N - 1), r_hi = min(n0 + g + 8, a.N - 1);   // rows past N repeat the last one (never stored)
-    const __half* w_lo = a.W + (size_t)r_lo * K + 8 * t;
-    const __half* w_hi = a.W + (size_t)r_hi * K + 8 * t;
+    const int b_lo = warp * per, b_hi = min(blocks, b_lo + per);
+    const __half* wrow[MTW][2];   // rows past N repeat the last one (never stored)
+#pragma unroll
+    for (int m = 0; m < MTW; ++m) {
+        wrow[m][0] = a.W + (size_t)min(n0 + m * 16 + g, a.N - 1) * K + 8 * t;
+        wrow[m][1] = a.W + (size_t)min(n0 + m * 16 + g + 8, a.N - 1) * K + 8 * t;
+    }
     const __half* xrow[NT];
 #pragma unroll
     for (int j = 0; j < NT; ++j) xrow[j] = a.X + (size_t)min(j * 8 + g, a.J - 1) * a.ldx + 8 * t;
-    float acc[NT][4];
+    float acc[MTW][NT][4];
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
+    for (int m = 0; m < MTW; ++m)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 8
-    for (int b = b_lo; b < b_hi; ++b) {
-        const int k = b * 32 + 8 * t;          // first of this thread's 8 consecutive k
-        const bool in = k < K;                 // K % 8 == 0: a thread's 8 positions are all inside or all outside
-        const uint4 wl = in ? ldg_stream_v4(w_lo + (size_t)b * 32) : zero;
-        const uint4 wh = in ? ldg_stream_v4(w_hi + (size_t)b * 32) : zero;
+    uint4 wc[UB][MTW][2], xc[UB][NT], wn[UB][MTW][2], xn[UB][NT];
+    auto load_group = [&](uint4 (&w)[UB][MTW][2], uint4 (&x)[UB][NT], int b0) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const uint4 xv = in ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + (size_t)b * 32)) : zero;
-            // two products per 32-wide block: k positions {0,1 | 2,3} and {4,5 | 6,7} of the thread's eight
-            mma16816(acc[j], wl.x, wh.x, wl.y, wh.y, xv.x, xv.y);
-            mma16816(acc[j], wl.z, wh.z, wl.w, wh.w, xv.z, xv.w);
+        for (int u = 0; u < UB; ++u) {
+            const int b = b0 + u;
+            // K % 8 == 0: a thread's 8 consecutive k are all inside or all outside
+            const bool in = b < b_hi && b * 32 + 8 * t < K;
+#pragma unroll
+            for (int m = 0; m < MTW; ++m) {
+                w[u][m][0] = in ? ldg_w(wrow[m][0] + (size_t)b * 32) : zero;
+                w[u][m][1] = in ? ldg_w(wrow[m][1] + (size_t)b * 32) : zero;
+            }
+#pragma unroll
+            for (int j = 0; j < NT; ++j) x[u][j] = in ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + (size_t)b * 32)) : zero;
         }
+    };
+    auto multiply = [&](const uint4 (&w)[UB][MTW][2], const uint4 (&x)[UB][NT]) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int m = 0; m < MTW; ++m) {
+                    // two products per 32-wide block: k positions {0,1 | 2,3} and {4,5 | 6,7} of the thread's eight
+                    mma16816(acc[m][j], w[u][m][0].x, w[u][m][1].x, w[u][m][0].y, w[u][m][1].y, x[u][j].x, x[u][j].y);
+                    mma16816(acc[m][j], w[u][m][0].z, w[u][m][1].z, w[u][m][0].w, w[u][m][1].w, x[u][j].z, x[u][j].w);
+                }
+    };
+    // two register buffers used alternately (no copies between them: a move would wait for the load it moves)
+    load_group(wc, xc, b_lo);
+    for (int b0 = b_lo; b0 < b_hi; b0 += 2 * UB) {
+        load_group(wn, xn, b0 + UB);
+        multiply(wc, xc);
+        load_group(wc, xc, b0 + 2 * UB);
+        multiply(wn, xn);
     }
     // accumulator layout: (row g, cols 2t, 2t+1), (row g+8, same cols) of each n-tile
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        part[ks][mt * 16 + g][j * 8 + 2 * t] = acc[j][0];
-        part[ks][mt * 16 + g][j * 8 + 2 * t + 1] = acc[j][1];
-        part[ks][mt * 16 + g + 8][j * 8 + 2 * t] = acc[j][2];
-        part[ks][mt * 16 + g + 8][j * 8 + 2 * t + 1] = acc[j][3];
-    }
+    for (int m = 0; m < MTW; ++m)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            part[warp][m * 16 + g][j * 8 + 2 * t] = acc[m][j][0];
+            part[warp][m * 16 + g][j * 8 + 2 * t + 1] = acc[m][j][1];
+            part[warp][m * 16 + g + 8][j * 8 + 2 * t] = acc[m][j][2];
+            part[warp][m * 16 + g + 8][j * 8 + 2 * t + 1] = acc[m][j][3];
+        }
     __syncthreads();
     // output (activation row j, weight row r): consecutive threads take consecutive weight rows
     for (int i = threadIdx.x; i < ROWS * NT * 8; i += kSkinnyThreads) {
         const int r = i % ROWS, j = i / ROWS;
-        const int n = blockIdx.x * ROWS + r;
+        const int n = n0 + r;
         if (n >= a.N || j >= a.J) continue;
         float v = 0.f;
 #pragma unroll
@@ -100,6 +139,121 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
         else static_cast<__half*>(a.Y)[(size_t)j * a.ldy + n] = __float2half_rn(v);
     }
 }
+
+// Many weight rows (N >= 16384: the vocabulary projection of a batched decode step) and 9..32 activation rows: one
+// warp per 16-row tile over the whole of K, no K split, so nothing is folded through shared memory and no barrier
+// follows the start.  Read straight from global memory the X fragments would cost as many load slots and registers as
+// W itself; here the CTA copies X into shared memory once (cp.async; odd rows stored with their 16-byte chunks swapped
+// across 64 bytes, so a quarter-warp's 128-bit reads - two rows x 64 bytes - fall in distinct banks) and its 8 warps
+// walk tiles of a persistent grid, two register buffers of W loads in flight per warp.
+template <int NT>
+__global__ void __launch_bounds__(kSkinnyThreads, 2) gemm_skinny_rows_kernel(SkinnyArgs a, int tiles) {
+    constexpr int UB = 4;                                            // 32-wide K blocks per register buffer
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int K = a.K;                                               // K % 64 == 0 (checked by the launcher)
+    const int xs = K * 2;                                            // bytes per X row, a multiple of 128
+    const int blocks = K >> 5;
+    {
+        const int chunks = K >> 3;                                   // 16-byte chunks per row
+        for (int i = threadIdx.x; i < NT * 8 * chunks; i += kSkinnyThreads) {
+            const int row = i / chunks, c = i % chunks;
+            unsigned char* dst = sk_smem + (size_t)row * xs + (c ^ ((row & 1) << 2)) * 16;
+            const __half* src = a.X + (size_t)min(row, a.J - 1) * a.ldx + c * 8;   // rows past J repeat the last one
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    uint4 w0[UB][2], w1[UB][2];
+    const __half *p_lo = a.W, *p_hi = a.W;
+    auto load_group = [&](uint4 (&w)[UB][2], int b0) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+            if (b0 + u < blocks) {                                   // warp-uniform
+                w[u][0] = ldg_w(p_lo + (size_t)(b0 + u) * 32);
+                w[u][1] = ldg_w(p_hi + (size_t)(b0 + u) * 32);
+            }
+    };
+    float acc[NT][4];
+    const unsigned char* xg = sk_smem + (size_t)g * xs;
+    const int sw = (g & 1) << 2;
+    auto multiply = [&](const uint4 (&w)[UB][2], int b0) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+            if (b0 + u < blocks) {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xg + (size_t)j * 8 * xs + ((((b0 + u) << 2) + t) ^ sw) * 16);
+                    mma16816(acc[j], w[u][0].x, w[u][1].x, w[u][0].y, w[u][1].y, xv.x, xv.y);
+                    mma16816(acc[j], w[u][0].z, w[u][1].z, w[u][0].w, w[u][1].w, xv.z, xv.w);
+                }
+            }
+    };
+    auto start_tile = [&](int tile) {
+        const int n0 = tile * kSkinnyRows;
+        p_lo = a.W + (size_t)min(n0 + g, a.N - 1) * K + 8 * t;       // rows past N repeat the last one (never stored)
+        p_hi = a.W + (size_t)min(n0 + g + 8, a.N - 1) * K + 8 * t;
+        load_group(w0, 0);
+    };
+    // tile i of the launch belongs to CTA i % gridDim.x, warp (i / gridDim.x) % 8.  The first tile's loads are issued
+    // before the wait for X; the barrier is reached by every warp, with or without a tile.
+    int tile = blockIdx.x + warp * gridDim.x;
+    if (tile < tiles) start_tile(tile);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    for (bool first = true; tile < tiles; tile += kSkinnyWarps * gridDim.x, first = false) {
+        const int n0 = tile * kSkinnyRows;
+        if (!first) start_tile(tile);
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        for (int b0 = 0; b0 < blocks; b0 += 2 * UB) {
+            load_group(w1, b0 + UB);
+            multiply(w0, b0);
+            load_group(w0, b0 + 2 * UB);
+            multiply(w1, b0 + UB);
+        }
+        // accumulator layout: (row g, cols 2t, 2t+1), (row g+8, same cols) of each n-tile
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int n = n0 + g + 8 * h;
+            if (n >= a.N) continue;
+            const float bv = a.bias ? __half2float(a.bias[n]) : 0.f;
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int col = j * 8 + 2 * t + e;
+                    if (col >= a.J) continue;
+                    float v = acc[j][2 * h + e] + bv;
+                    if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
+                    if (a.y_is_f32) static_cast<float*>(a.Y)[(size_t)col * a.ldy + n] = v;
+                    else static_cast<__half*>(a.Y)[(size_t)col * a.ldy + n] = __float2half_rn(v);
+                }
+        }
+    }
+}
+
+template <int NT>
+int launch_skinny_rows(const SkinnyArgs& a, cudaStream_t st) {
+    const size_t smem = (size_t)NT * 8 * a.K * 2;
+    if (a.K % 64 != 0 || smem > 200 * 1024) return PIMB200_ERR_UNSUPPORTED;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return PIMB200_ERR_UNSUPPORTED;
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(gemm_skinny_rows_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return PIMB200_ERR_LAUNCH;
+        attr_set[dev] = true;
+    }
+    const int tiles = ceil_div(a.N, kSkinnyRows);
+    const int per_sm = smem <= 110 * 1024 ? 2 : 1;
+    DeviceCtx* ctx = current_ctx();
+    const int grid = min(ceil_div(tiles, kSkinnyWarps), (ctx ? ctx->sm_count : kNumSmB200) * per_sm);
+    gemm_skinny_rows_kernel<NT><<<grid, kSkinnyThreads, smem, st>>>(a, tiles);
+    return launch_status();
+}
 }  // namespace
 
 // PIMB200_ERR_UNSUPPORTED when the shape is not this kernel's (the caller then takes the tensor-core or SIMT path)
@@ -108,6 +262,11 @@ int launch_gemm_wx_skinny(const __half* W, const __half* X, const __half* bias, 
     if (J < 1 || J > kSkinnyMaxJ || K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
     SkinnyArgs a{W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32};
     const int nt = ceil_div(J, 8);
+    if (nt >= 2 && N >= 16384) {
+        // a warp per row tile with X in shared memory, when the CTA's copy of X fits
+        const int rc = nt == 2 ? launch_skinny_rows<2>(a, st) : nt == 3 ? launch_skinny_rows<3>(a, st) : launch_skinny_rows<4>(a, st);
+        if (rc != PIMB200_ERR_UNSUPPORTED) return rc;
+    }
     if (N >= 2048) {
         const int grid = ceil_div(N, 2 * kSkinnyRows);
         switch (nt) {

@@ -152,6 +152,22 @@ def test_batched_stream_gemm(N, K, B):
     assert _lib.lib().pimb200_gemm_last_status() == 0
 
 
+@pytest.mark.parametrize("N,K,J", [(16400, 192, 19), (20001, 64, 9), (32320, 1024, 24), (16390, 2048, 17), (4100, 40, 5),
+                                   (37, 72, 31), (2049, 264, 12), (16384, 96, 32)])
+def test_few_row_gemm_ragged_shapes(N, K, J):
+    # the streaming kernels for 1..32 activation rows: ragged row tiles, K tails, row counts between the 8-row tiles,
+    # both the K-split form and the warp-per-tile form of the large vocabulary projections
+    ops = _ops()
+    W, b, X = _c2_inputs(N, K, J, seed=33)
+    ref = co.linear(W.numpy(), X.numpy(), b.numpy())
+    Yf = ops.gemm_wx(to_dev(W), to_dev(X), to_dev(b), ops.ACT_NONE, out_f32=True)
+    assert_close(Yf, ref, 1e-3, 1e-4, f"few-row gemm f32 {N}x{K}x{J}")
+    Yh = ops.gemm_wx(to_dev(W), to_dev(X), to_dev(b), ops.ACT_RELU)
+    assert_close(Yh, np.maximum(ref, 0), GEMV_ATOL, GEMV_RTOL, f"few-row gemm f16 {N}x{K}x{J}")
+    from pimaicompiler_b200 import _lib
+    assert _lib.lib().pimb200_gemm_last_status() == 0
+
+
 @pytest.mark.parametrize("N,K,J", [(4096, 240, 200), (512, 1024, 500), (4096, 2048, 130), (130, 72, 17), (128, 64, 16),
                                    (256, 8, 3), (1280, 320, 29)])
 def test_dense_gemm_tensor_core_and_simt_agree_with_oracle(N, K, J):
