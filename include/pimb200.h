@@ -174,6 +174,29 @@ int pimb200_scatter_rows(void* table, const long long* idx, const void* src, lon
 int pimb200_attention_row(const void* q, const void* K, const void* V, const long long* len_dev, long len_add,
                           long max_len, void* out, int heads, int head_dim, long kv_stride, float scale, void* stream);
 
+/* Batched form of pimb200_attention_row for n_seq sequences decoded in lock step: q / out are [n_seq, heads * head_dim],
+ * sequence j attends to its own cache at K + j * seq_stride (V likewise) with its own length
+ * L_j = (len_dev ? len_dev[j * len_inc] : 0) + len_add (len_inc 0: one shared device-side position, the self-attention
+ * of a lock-step decode; len_inc 1: per-sequence source lengths, the cross-attention).  One launch, a CTA per
+ * (head, sequence).  The reference runs one sequence at a time (its matmul -> softmax -> matmul group, see above);
+ * batching sentences is how one GPU serves many streams here. */
+int pimb200_attention_rows(const void* q, const void* K, const void* V, const long long* len_dev, long len_inc,
+                           long len_add, long max_len, void* out, int n_seq, int heads, int head_dim, long kv_stride,
+                           long seq_stride, float scale, void* stream);
+
+/* Additive (normalised Bahdanau) attention of a GNMT decode step for n_seq sentences, one CTA per sentence:
+ *     e[s] = sum_h v[h] * tanh(keys_proj[s, h] + q[h] + bias[h]),  s < lengths[j]  (int64 in DEVICE memory; NULL = max_len)
+ *     ctx[j, :] = sum_s softmax(e)[s] * values[s, :]
+ * q [n_seq, H]; row s of sentence j at j * seq_stride + s * row_stride elements of keys_proj / values (a time-major
+ * encoder output [S, n_seq, H] has row_stride = n_seq * H, seq_stride = H); ctx rows ctx_stride elements apart, so the
+ * context can be written straight into the second half of the decoder's [n_seq, 2H] concatenation buffer.
+ * Stands for the add -> tanh -> matmul -> softmax -> bmm chain of the reference's GNMT graph (executeAtenAdd
+ * aten_ops_executor.cpp:110-166, executeAtenTanh, executeAtenMatmul 2488-2505, executeAtenSoftmax 3402-3436,
+ * executeAtenBmm), five interpreter dispatches per token there. */
+int pimb200_additive_attention(const void* q, const void* keys_proj, const void* values, const long long* lengths,
+                               const void* v, const void* bias, void* ctx, int n_seq, long max_len, int H,
+                               long row_stride, long seq_stride, long ctx_stride, void* stream);
+
 typedef struct pimb200_lstm pimb200_lstm;
 
 /* One-time weight layout step.  params = the flat list at::lstm takes:

@@ -12,7 +12,8 @@ from typing import List, Optional
 import torch
 
 
-from pimaicompiler_b200.synthetic import RnntConfig, RnntWeights, make_features, make_rnnt_weights  # noqa: F401,E402
+from pimaicompiler_b200.synthetic import (GnmtConfig, RnntConfig, RnntWeights, make_features,  # noqa: F401,E402
+                                          make_gnmt_weights, make_rnnt_weights, make_sentences)
 
 
 def rnnt_encoder(w: RnntWeights, feats: torch.Tensor, cfg: RnntConfig) -> torch.Tensor:
@@ -55,3 +56,51 @@ def rnnt_greedy(w: RnntWeights, feats: torch.Tensor, cfg: RnntConfig, forced: Op
                 label, h, c = k, hp, cp
                 g, hp, cp = pred(label, h, c)
         return tokens, logits, choice
+
+
+# ------------------------------------------------------------------------------------------------ GNMT (configuration C4)
+def gnmt_encode(w: dict, src: torch.Tensor, cfg) -> torch.Tensor:
+    """Encoder states [S, H] of one sentence: at::lstm per layer (aten_ops.cpp:328-344), bidirectional first layer,
+    residual adds from the third layer."""
+    H = cfg.hidden
+    S = src.shape[0]
+    x = w["emb_src"][src].view(S, 1, H)
+    z2, z1 = torch.zeros(2, 1, H), torch.zeros(1, 1, H)
+    y0, _, _ = torch.lstm(x, [z2, z2], w["enc0_f"] + w["enc0_r"], True, 1, 0.0, False, True, False)
+    y1, _, _ = torch.lstm(y0, [z1, z1], w["enc1"], True, 1, 0.0, False, False, False)
+    y2, _, _ = torch.lstm(y1, [z1, z1], w["enc2"], True, 1, 0.0, False, False, False)
+    y2 = y2 + y1
+    y3, _, _ = torch.lstm(y2, [z1, z1], w["enc3"], True, 1, 0.0, False, False, False)
+    return (y3 + y2).view(S, H)
+
+
+def gnmt_translate(w: dict, src: torch.Tensor, cfg, steps: Optional[int] = None, forced: Optional[List[int]] = None):
+    """Greedy decode of one sentence for `steps` steps (no stop at the end-of-sentence token: the caller truncates).
+    Returns (tokens, logits [steps, V]); `forced[t]` overrides the token fed back after step t."""
+    H = cfg.hidden
+    steps = cfg.max_steps if steps is None else steps
+    keys = gnmt_encode(w, src, cfg)
+    keys_proj = torch.nn.functional.linear(keys, w["Wk"])
+    v_norm = w["att_v"] / w["att_v"].norm() * float(w["att_g"])
+    hs = [torch.zeros(1, 1, H) for _ in range(4)]
+    cs = [torch.zeros(1, 1, H) for _ in range(4)]
+
+    def cell(name, x, i):
+        y, hs[i], cs[i] = torch.lstm(x.view(1, 1, -1), [hs[i], cs[i]], w[name], True, 1, 0.0, False, False, False)
+        return y.view(-1)
+
+    tok, toks, logits = cfg.bos, [], []
+    for t in range(steps):
+        y0 = cell("dec0", w["emb_tgt"][tok], 0)
+        q = torch.nn.functional.linear(y0, w["Wq"])
+        e = torch.tanh(keys_proj + q + w["att_b"]) @ v_norm
+        ctx = torch.softmax(e, 0) @ keys
+        y1 = cell("dec1", torch.cat([y0, ctx]), 1)
+        r2 = cell("dec2", torch.cat([y1, ctx]), 2) + y1
+        r3 = cell("dec3", torch.cat([r2, ctx]), 3) + r2
+        lg = torch.nn.functional.linear(r3, w["Wc"], w["bc"])
+        logits.append(lg)
+        best = int(torch.argmax(lg))
+        toks.append(best)
+        tok = best if forced is None else int(forced[t])
+    return toks, torch.stack(logits)

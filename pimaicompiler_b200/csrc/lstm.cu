@@ -264,6 +264,41 @@ __global__ void __launch_bounds__(256) lstm_cell_kernel(CellArgs a) {
     }
 }
 
+// Decode form for 8 or more sequences in lock step (a batched decode step: one token for each of B sentences): the
+// cell kernel above would stream both matrices once per four sequences, so the two products run as GEMMs over the B
+// rows (one pass over each matrix whatever B is) into fp32 gate terms, and this kernel applies bias and gate math:
+// a thread per (sequence, hidden unit), the unit's four gate terms one 16-byte load from each product.
+constexpr int kCellGemmMinB = 8;
+struct CellPointArgs {
+    const float* Gx;     // [B, 4H]  W_ih x, packed gate order (unit-major)
+    const float* Gh;     // [B, 4H]  W_hh h0, or NULL when h0 is zero
+    const float* bias;   // packed [4H]
+    const __half* c0;    // [B, H] or NULL
+    __half* y;           // h of sequence b at y + b*y_bstride
+    long y_bstride;
+    __half* hn;          // optional [B, H]
+    __half* cn;          // optional [B, H]
+    int H, B;
+};
+
+__global__ void __launch_bounds__(256) lstm_cell_point_kernel(CellPointArgs a) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)a.B * a.H) return;
+    const int b = (int)(idx / a.H), u = (int)(idx % a.H);
+    float4 z = *reinterpret_cast<const float4*>(a.Gx + ((size_t)b * a.H + u) * 4);
+    if (a.Gh) {
+        const float4 zh = *reinterpret_cast<const float4*>(a.Gh + ((size_t)b * a.H + u) * 4);
+        z.x += zh.x; z.y += zh.y; z.z += zh.z; z.w += zh.w;
+    }
+    const float4 bb = *reinterpret_cast<const float4*>(a.bias + (size_t)u * 4);
+    const float cprev = a.c0 ? __half2float(a.c0[(size_t)b * a.H + u]) : 0.f;
+    const float cnew = sigmoidf_(z.y + bb.y) * cprev + sigmoidf_(z.x + bb.x) * tanhf_(z.z + bb.z);
+    const __half hh = __float2half_rn(sigmoidf_(z.w + bb.w) * tanhf_(cnew));
+    a.y[(size_t)b * a.y_bstride + u] = hh;
+    if (a.hn) a.hn[(size_t)b * a.H + u] = hh;
+    if (a.cn) a.cn[(size_t)b * a.H + u] = __float2half_rn(cnew);
+}
+
 __global__ void lstm_init_c_kernel(float* __restrict__ c, const __half* __restrict__ c0, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) c[i] = c0 ? __half2float(c0[i]) : 0.f;
@@ -2186,6 +2221,8 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
     // decode form: seq_len 1, every extent a multiple of 8 and 16-byte aligned -> one fused cell launch per layer
     bool cell = !packed && T == 1 && h->variant != PIMB200_LSTM_PERSISTENT && h->variant != PIMB200_LSTM_PERSISTENT_TAGGED &&
                 H % 8 == 0 && h->I % 8 == 0 && aligned16(x) && aligned16(y) && (!h0 || aligned16(h0));
+    const bool cell_gemm = cell && B >= kCellGemmMinB;   // lock-step decode of many sequences: products as GEMMs
+    if (cell_gemm && (rc = grow(&h->G, &h->G_cap, (size_t)2 * B * 4 * H)) != PIMB200_OK) return rc;
     if (!cell && (rc = grow(&h->G, &h->G_cap, (size_t)rows * 4 * H)) != PIMB200_OK) return rc;
     if (L > 1 && (rc = grow(&h->ybuf[0], &h->y_cap[0], (size_t)rows * D * H)) != PIMB200_OK) return rc;
     if (L > 2 && (rc = grow(&h->ybuf[1], &h->y_cap[1], (size_t)rows * D * H)) != PIMB200_OK) return rc;
@@ -2205,6 +2242,20 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
                 a.hn = hn ? hn + (size_t)ld * B * H : nullptr;
                 a.cn = cn ? cn + (size_t)ld * B * H : nullptr;
                 a.I = in_size(h, l); a.H = H; a.B = B;
+                if (cell_gemm) {
+                    float* Gx = h->G;
+                    float* Gh = a.h0 ? h->G + (size_t)B * 4 * H : nullptr;
+                    if ((rc = launch_gemm_wx(a.Wih, a.x, nullptr, Gx, 4 * H, a.I, B, (int)a.x_bstride, 4 * H, PIMB200_ACT_NONE, 1,
+                                             st)) != PIMB200_OK)
+                        return rc;
+                    if (Gh && (rc = launch_gemm_wx(a.Whh, a.h0, nullptr, Gh, 4 * H, H, B, H, 4 * H, PIMB200_ACT_NONE, 1, st)) !=
+                                  PIMB200_OK)
+                        return rc;
+                    CellPointArgs pa{Gx, Gh, a.bias, a.c0, a.y, a.y_bstride, a.hn, a.cn, H, B};
+                    lstm_cell_point_kernel<<<ceil_div(B * H, 256), 256, 0, st>>>(pa);
+                    if ((rc = launch_status()) != PIMB200_OK) return rc;
+                    continue;
+                }
                 if (B == 1) lstm_cell_kernel<1><<<ceil_div(H, 8), 256, 0, st>>>(a);
                 else lstm_cell_kernel<4><<<ceil_div(H, 8), 256, 0, st>>>(a);
                 if ((rc = launch_status()) != PIMB200_OK) return rc;

@@ -245,6 +245,132 @@ __global__ void __launch_bounds__(kAttnThreads) attention_row_kernel(const __hal
     }
 }
 
+// Batched form of attention_row_kernel: blockIdx.y is the sequence; every sequence has its own cache (seq_stride
+// elements after the previous one) and its own length (len_dev[seq * len_inc]).
+__global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const __half* __restrict__ q, const __half* __restrict__ K,
+                                                                      const __half* __restrict__ V, const long long* len_dev,
+                                                                      long len_inc, long len_add, long max_len,
+                                                                      __half* __restrict__ out, int hd, long kv_stride,
+                                                                      long seq_stride, float scale) {
+    extern __shared__ float sc[];            // [max_len] scores, then [kAttnThreads / 32][hd] partial outputs
+    __shared__ float red[kAttnThreads / 32];
+    const int h = blockIdx.x, seq = blockIdx.y, heads = gridDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long L = (len_dev ? (long)len_dev[(size_t)seq * len_inc] : 0) + len_add;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
+    const __half* qh = q + ((size_t)seq * heads + h) * hd;
+    const __half* Ks = K + (size_t)seq * seq_stride + (size_t)h * hd;
+    const __half* Vs = V + (size_t)seq * seq_stride + (size_t)h * hd;
+    for (long t = warp; t < L; t += kAttnThreads / 32) {
+        const __half* kr = Ks + (size_t)t * kv_stride;
+        float a = 0.f;
+        for (int j = lane; j < hd; j += 32) a = fmaf(__half2float(qh[j]), __half2float(kr[j]), a);
+        a = warp_sum(a);
+        if (lane == 0) sc[t] = a * scale;
+    }
+    __syncthreads();
+    float m = -CUDART_INF_F;
+    for (long t = threadIdx.x; t < L; t += kAttnThreads) m = fmaxf(m, sc[t]);
+    m = block_max<kAttnThreads>(m, red);
+    float s = 0.f;
+    for (long t = threadIdx.x; t < L; t += kAttnThreads) {
+        const float e = expf(sc[t] - m);
+        sc[t] = e;
+        s += e;
+    }
+    s = block_sum<kAttnThreads>(s, red);   // ends with a barrier: every sc[t] is final
+    const float inv = L > 0 ? 1.0f / s : 0.f;
+    float* part = sc + max_len;
+    for (int j = lane; j < hd; j += 32) {
+        float a = 0.f;
+        for (long t = warp; t < L; t += kAttnThreads / 32) a = fmaf(sc[t], __half2float(Vs[(size_t)t * kv_stride + j]), a);
+        part[warp * hd + j] = a;
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < hd; j += kAttnThreads) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAttnThreads / 32; ++w) a += part[w * hd + j];
+        out[((size_t)seq * heads + h) * hd + j] = __float2half_rn(a * inv);
+    }
+}
+
+// Additive (normalised Bahdanau) attention of a decode step, one CTA per sentence:
+//     e[s]   = sum_h v[h] * tanh(keys_proj[s, h] + q[h] + bias[h]),  s < length
+//     ctx[h] = sum_s softmax(e)[s] * values[s, h]
+// Row s of sentence j lies at j * seq_stride + s * row_stride elements (time-major encoder output: row_stride =
+// sentences * H, seq_stride = H).  Scores and the query vector live in shared memory.
+constexpr int kAddAttnThreads = 256;
+
+__global__ void __launch_bounds__(kAddAttnThreads) additive_attention_kernel(
+    const __half* __restrict__ q, const __half* __restrict__ keys_proj, const __half* __restrict__ values,
+    const long long* __restrict__ lengths, const __half* __restrict__ v, const __half* __restrict__ bias,
+    __half* __restrict__ ctx, long max_len, int H, long row_stride, long seq_stride, long ctx_stride) {
+    extern __shared__ float sm[];            // [max_len] scores, [H] q + bias, [H] v
+    __shared__ float red[kAddAttnThreads / 32];
+    float* sc = sm;
+    float* qb = sm + max_len;
+    float* vs = qb + H;
+    const int seq = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    long L = lengths ? (long)lengths[seq] : max_len;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
+    for (int h = threadIdx.x; h < H; h += kAddAttnThreads) {
+        qb[h] = __half2float(q[(size_t)seq * H + h]) + (bias ? __half2float(bias[h]) : 0.f);
+        vs[h] = __half2float(v[h]);
+    }
+    __syncthreads();
+    const __half* kp = keys_proj + (size_t)seq * seq_stride;
+    const __half* vals = values + (size_t)seq * seq_stride;
+    const bool vec = (H % 8 == 0) && (row_stride % 8 == 0) && (seq_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(keys_proj) & 15u) == 0);
+    for (long s = warp; s < L; s += kAddAttnThreads / 32) {
+        const __half* kr = kp + (size_t)s * row_stride;
+        float a = 0.f;
+        if (vec) {
+            for (int c = lane; c < (H >> 3); c += 32) {
+                float kf[8];
+                widen8(__ldg(reinterpret_cast<const uint4*>(kr) + c), kf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) a = fmaf(vs[c * 8 + i], tanhf_(kf[i] + qb[c * 8 + i]), a);
+            }
+        } else {
+            for (int h = lane; h < H; h += 32) a = fmaf(vs[h], tanhf_(__half2float(kr[h]) + qb[h]), a);
+        }
+        a = warp_sum(a);
+        if (lane == 0) sc[s] = a;
+    }
+    __syncthreads();
+    float m = -CUDART_INF_F;
+    for (long s = threadIdx.x; s < L; s += kAddAttnThreads) m = fmaxf(m, sc[s]);
+    m = block_max<kAddAttnThreads>(m, red);
+    float sum = 0.f;
+    for (long s = threadIdx.x; s < L; s += kAddAttnThreads) {
+        const float e = expf(sc[s] - m);
+        sc[s] = e;
+        sum += e;
+    }
+    sum = block_sum<kAddAttnThreads>(sum, red);   // ends with a barrier: every sc[s] is final
+    const float inv = L > 0 ? 1.0f / sum : 0.f;
+    // context: threads along H (two halves per thread and pass), rows in sequence; a warp reads 128 contiguous bytes
+    for (int h = threadIdx.x * 2; h < H; h += kAddAttnThreads * 2) {
+        float a0 = 0.f, a1 = 0.f;
+        if (h + 1 < H && (row_stride % 2 == 0) && (seq_stride % 2 == 0)) {
+            for (long s = 0; s < L; ++s) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(vals + (size_t)s * row_stride + h));
+                a0 = fmaf(sc[s], f.x, a0);
+                a1 = fmaf(sc[s], f.y, a1);
+            }
+            ctx[(size_t)seq * ctx_stride + h] = __float2half_rn(a0 * inv);
+            ctx[(size_t)seq * ctx_stride + h + 1] = __float2half_rn(a1 * inv);
+        } else {
+            for (int hh = h; hh < min(h + 2, H); ++hh) {
+                float a = 0.f;
+                for (long s = 0; s < L; ++s) a = fmaf(sc[s], __half2float(vals[(size_t)s * row_stride + hh]), a);
+                ctx[(size_t)seq * ctx_stride + hh] = __float2half_rn(a * inv);
+            }
+        }
+    }
+}
+
 inline unsigned flat_grid(size_t n) {
     const size_t g = (n + 255) / 256;
     return (unsigned)(g > (size_t)kNumSmB200 * 8 ? (size_t)kNumSmB200 * 8 : (g ? g : 1));
@@ -368,5 +494,37 @@ extern "C" int pimb200_attention_row(const void* q, const void* K, const void* V
     attention_row_kernel<<<(unsigned)heads, kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_add,
         max_len, static_cast<__half*>(out), head_dim, kv_stride, scale);
+    return launch_status();
+}
+
+extern "C" int pimb200_attention_rows(const void* q, const void* K, const void* V, const long long* len_dev, long len_inc,
+                                      long len_add, long max_len, void* out, int n_seq, int heads, int head_dim,
+                                      long kv_stride, long seq_stride, float scale, void* stream) {
+    if (n_seq == 0) return PIMB200_OK;
+    if (!q || !K || !V || !out || n_seq < 0 || n_seq > 65535 || heads <= 0 || head_dim <= 0 || max_len <= 0 ||
+        kv_stride < (long)heads * head_dim || seq_stride < 0 || len_inc < 0)
+        return PIMB200_ERR_BAD_ARG;
+    if (max_len > kAttnMaxLen || head_dim > 1024) return PIMB200_ERR_UNSUPPORTED;
+    const size_t smem = ((size_t)max_len + (size_t)(kAttnThreads / 32) * head_dim) * sizeof(float);
+    if (smem + 16 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
+    attention_rows_kernel<<<dim3((unsigned)heads, (unsigned)n_seq), kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_inc, len_add,
+        max_len, static_cast<__half*>(out), head_dim, kv_stride, seq_stride, scale);
+    return launch_status();
+}
+
+extern "C" int pimb200_additive_attention(const void* q, const void* keys_proj, const void* values, const long long* lengths,
+                                          const void* v, const void* bias, void* ctx, int n_seq, long max_len, int H,
+                                          long row_stride, long seq_stride, long ctx_stride, void* stream) {
+    if (n_seq == 0) return PIMB200_OK;
+    if (!q || !keys_proj || !values || !v || !ctx || n_seq < 0 || max_len <= 0 || H <= 0 || row_stride < H || seq_stride < 0 ||
+        ctx_stride < H)
+        return PIMB200_ERR_BAD_ARG;
+    const size_t smem = ((size_t)max_len + 2 * (size_t)H) * sizeof(float);
+    if (smem + 64 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
+    additive_attention_kernel<<<(unsigned)n_seq, kAddAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(keys_proj), static_cast<const __half*>(values), lengths,
+        static_cast<const __half*>(v), static_cast<const __half*>(bias), static_cast<__half*>(ctx), max_len, H, row_stride,
+        seq_stride, ctx_stride);
     return launch_status();
 }

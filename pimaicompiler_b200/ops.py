@@ -7,6 +7,7 @@ nothing falls back to a PyTorch op.
 from __future__ import annotations
 
 import ctypes as C
+import math
 from typing import Optional, Sequence
 
 import torch
@@ -98,10 +99,10 @@ def gemm_wx(W: torch.Tensor, X: torch.Tensor, bias: Optional[torch.Tensor] = Non
     _req_half_cuda(W, X, bias)
     N, K = W.shape
     J = X.shape[0]
-    assert X.shape[1] == K
+    assert X.shape[1] == K and X.stride(1) == 1
     if out is None:
         out = torch.empty(J, N, dtype=torch.float32 if out_f32 else torch.float16, device=W.device)
-    check(_lib.lib().pimb200_gemm_wx(_ptr(W), _ptr(X), _ptr(bias), _ptr(out), N, K, J, K, out.stride(0), act,
+    check(_lib.lib().pimb200_gemm_wx(_ptr(W), _ptr(X), _ptr(bias), _ptr(out), N, K, J, X.stride(0), out.stride(0), act,
                                      1 if out.dtype == torch.float32 else 0, _stream()), "gemm_wx")
     return out
 
@@ -230,6 +231,37 @@ def attention_row(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int,
                                            float(scale if scale is not None else hd ** -0.5), _stream()),
           "attention_row")
     return y
+
+
+def attention_rows(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int, len_dev: Optional[torch.Tensor] = None,
+                   len_inc: int = 0, len_add: int = 0, max_len: Optional[int] = None, scale: Optional[float] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Single-query multi-head attention for n sequences in lock step: q [n, heads*hd]; K, V [n, S_max, heads*hd] (one
+    cache per sequence); lengths from the int64 device tensor `len_dev` (element j*len_inc for sequence j) plus len_add."""
+    _req_half_cuda(q, K, V)
+    n, d = q.shape
+    hd = d // heads
+    S = K.shape[1] if max_len is None else max_len
+    if out is None:
+        out = torch.empty_like(q)
+    check(_lib.lib().pimb200_attention_rows(_ptr(q), _ptr(K), _ptr(V), _ptr(len_dev), len_inc, len_add, S, _ptr(out), n,
+                                            heads, hd, K.stride(1), K.stride(0),
+                                            scale if scale is not None else 1.0 / math.sqrt(hd), _stream()), "attention_rows")
+    return out
+
+
+def additive_attention(q: torch.Tensor, keys_proj: torch.Tensor, values: torch.Tensor, lengths: Optional[torch.Tensor],
+                       v: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Normalised Bahdanau attention for n sentences: q [n, H]; keys_proj / values time-major [S, n, H] (contiguous);
+    lengths int64 [n] on the device; v, bias [H].  `out` may be a column slice of a wider [n, *] buffer."""
+    _req_half_cuda(q, keys_proj, values, v, bias)
+    S, n, H = keys_proj.shape
+    if out is None:
+        out = torch.empty(n, H, dtype=torch.float16, device=q.device)
+    check(_lib.lib().pimb200_additive_attention(_ptr(q), _ptr(keys_proj), _ptr(values), _ptr(lengths), _ptr(v), _ptr(bias),
+                                                _ptr(out), n, S, H, keys_proj.stride(0), keys_proj.stride(1),
+                                                out.stride(0), _stream()), "additive_attention")
+    return out
 
 
 def tanh(x: torch.Tensor) -> torch.Tensor:

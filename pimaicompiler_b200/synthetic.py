@@ -114,3 +114,42 @@ def save_rnnt_torchscript(path: str, cfg: RnntConfig, w: RnntWeights) -> None:
     sd["joint2.weight"], sd["joint2.bias"] = w.w2, w.b2
     m.load_state_dict(sd)
     torch.jit.script(m).save(path)
+
+
+# ------------------------------------------------------------------------------------------------ GNMT (configuration C4)
+@dataclass
+class GnmtConfig:
+    """4-layer LSTM encoder (first layer bidirectional, residual connections from the third layer), 4-layer LSTM
+    decoder with normalised Bahdanau attention fed by the first decoder layer, vocabulary projection; greedy search."""
+    vocab: int = 32320
+    hidden: int = 1024
+    max_steps: int = 80
+    min_len: int = 20
+    max_len: int = 50
+    bos: int = 2
+    eos: int = 3
+
+
+def make_gnmt_weights(cfg: GnmtConfig, seed: int = 0, gain: float = 1.0, logit_gain: float = 1.0) -> dict:
+    """fp32 CPU tensors with fp16-representable values: U(-1/sqrt(fan_in), 1/sqrt(fan_in)) matrices, N(0, 0.5) embeddings."""
+    g = torch.Generator().manual_seed(seed)
+    H, V = cfg.hidden, cfg.vocab
+
+    def lstm(I):
+        return [_u((4 * H, I), H, g, gain), _u((4 * H, H), H, g, gain), _u((4 * H,), H, g, gain), _u((4 * H,), H, g, gain)]
+
+    w = {"emb_src": (torch.randn(V, H, generator=g) * 0.5).half().float(),
+         "emb_tgt": (torch.randn(V, H, generator=g) * 0.5).half().float(),
+         "enc0_f": lstm(H), "enc0_r": lstm(H), "enc1": lstm(2 * H), "enc2": lstm(H), "enc3": lstm(H),
+         "dec0": lstm(H), "dec1": lstm(2 * H), "dec2": lstm(2 * H), "dec3": lstm(2 * H),
+         "Wq": _u((H, H), H, g, gain), "Wk": _u((H, H), H, g, gain), "att_b": _u((H,), H, g, gain),
+         "att_v": _u((H,), H, g, gain), "att_g": torch.tensor(1.0),
+         "Wc": _u((V, H), H, g, logit_gain), "bc": _u((V,), H, g, logit_gain)}
+    return w
+
+
+def make_sentences(n: int, cfg: GnmtConfig, seed: int) -> List[torch.Tensor]:
+    """n source sentences: lengths U[min_len, max_len], token ids U[4, vocab)."""
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(cfg.min_len, cfg.max_len + 1, (n,), generator=g)
+    return [torch.randint(4, cfg.vocab, (int(L),), generator=g) for L in lens]

@@ -95,6 +95,10 @@ CASES = [
     (3, 97, 24, 256, 2, True, True, False, True),        # ragged second half, bidirectional, two layers
     (5, 33, 16, 1024, 1, False, True, False, True),      # smallest batch the pipelined kernel takes by default
     (3, 2, 7, 5, 2, False, True, False, True),           # odd sizes: scalar path
+    (1, 8, 16, 32, 1, False, True, False, True),         # decode form, 8+ sequences: products as GEMMs + gate kernel
+    (1, 33, 64, 128, 2, False, True, False, True),       # ... two layers, ragged row tiles
+    (1, 128, 2048, 1024, 1, False, True, True, True),    # ... a GNMT decoder layer for 128 sentences
+    (1, 20, 24, 48, 2, True, False, False, False),       # ... bidirectional, no biases, zero state
 ]
 
 
