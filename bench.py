@@ -511,41 +511,159 @@ def run_c1(args):
     print(json.dumps(line), flush=True)
 
 
-def run_c4(args):
-    """C4 (decoder side): GNMT-style greedy decode, vocabulary 32320, hidden 1024, 4 decoder LSTM layers with normalised
-    Bahdanau attention over 37 encoder states, 80 steps, one sentence stream.  Compares the op-by-op decode (one host
-    read of the token per step, as the reference's interpreter does) with the step resident on the device (CUDA graph,
-    token fed back through device memory)."""
-    from pimaicompiler_b200 import build
-    build.build()
-    from pimaicompiler_b200 import decode_models as dm
-    H, V, S, steps = 1024, 32320, 37, 80
-    w = dm.make_gnmt(H, V, S, torch.Generator().manual_seed(4), 2.0)
-    be = dm.PimBackend()
-    dm.gnmt_greedy(be, w, H, 4)                                   # warm-up: handles, workspaces
-    torch.cuda.synchronize()
+C4_SENTENCES = 512   # BASELINE.json configs[3]: 512 sentences of 20..50 tokens, at most 80 decode steps
+
+
+def c4_config(total: int, group: int) -> dict:
+    return {"workload": "C4: GNMT greedy translation (4+4 LSTM layers, hidden 1024, vocabulary 32320, normalised Bahdanau "
+                        "attention), sentences of 20..50 tokens, 80 decode steps",
+            "sentences_total": total, "lockstep_group": group, "max_steps": 80,
+            "sharding": "sentences round-robin over the ranks, no collective on the data path",
+            "l2": "one step touches 160 MB of weights, more than the 126 MB L2"}
+
+
+def cpu_gnmt_throughput(n: int, seed: int):
+    """Translates n synthetic sentences on the host cores with the libtorch oracle; (sentences/s, seconds, cores)."""
+    from oracle import torch_oracle as to
+    cfg = to.GnmtConfig()
+    w = to.make_gnmt_weights(cfg, seed=0)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sents = to.make_sentences(n, cfg, seed)
+    to.gnmt_translate(w, sents[0], cfg, 4)
     t0 = time.perf_counter()
-    toks, _ = dm.gnmt_greedy(be, w, H, steps)
+    for s_ in sents:
+        to.gnmt_translate(w, s_, cfg)
+    dt = time.perf_counter() - t0
+    return n / dt, dt, cores
+
+
+def run_reference_c4(args, rank, world):
+    if rank != 0:
+        return
+    n = max(1, min(args.cpu_sample, 8))
+    vals, secs, cores = [], 0.0, 1
+    for k in range(args.steps):
+        v, dt, cores = cpu_gnmt_throughput(n, 9000 + k)
+        vals.append(v)
+        secs += dt
+    value = statistics.median(vals)
+    total = args.streams_total or C4_SENTENCES
+    line = {"impl": "reference", "metric": "gnmt_greedy_sentences_per_s", "value": value, "unit": "sentences/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / max(args.steps, 1) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": c4_config(total, min(args.group or 128, (total + args.gpus - 1) // args.gpus)), "sample_sentences_per_step": n,
+            "cpu_baseline": {"value": value, "unit": "sentences/s", "cores": cores, "kind": "port",
+                             "sample": f"{n} sentences per step, libtorch {torch.__version__} CPU fp32, {cores} threads"},
+            "e2e": {"value": value, "unit": "sentences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_c4(args, rank, world, local):
+    """C4: the configuration's 512 sentences sharded over the ranks; each rank translates its shard in lock-step groups
+    (encoder over the padded group, 80 greedy steps from a CUDA graph).  `value` has the staged token ids resident in
+    HBM; `e2e` goes through GnmtTranslator.translate with host token lists in and out."""
+    from pimaicompiler_b200 import build
+    from pimaicompiler_b200 import synthetic as syn
+    from pimaicompiler_b200.gnmt import GnmtTranslator
+    build.build()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cfg = syn.GnmtConfig()
+    w = syn.make_gnmt_weights(cfg, seed=0)
+    total = args.streams_total or C4_SENTENCES
+    sentences_all = syn.make_sentences(total, cfg, seed=11)
+    mine = sentences_all[rank::world]
+    S = len(mine)
+    group = min(args.group or 128, S)
+    tr = GnmtTranslator(cfg, w, group=group, device=dev)
+    staged = tr.stage(mine)
+    dev_groups = [(ids.to(dev), lens.to(dev)) for _, ids, lens in staged]
+    out_tokens = torch.zeros(len(staged), cfg.max_steps, group, dtype=torch.int64, device=dev)
+
+    def step_device(events=None):
+        for gi, (ids_d, lens_d) in enumerate(dev_groups):
+            tr.encode(ids_d, lens_d)
+            if events is not None:
+                events[gi][0].record()
+            toks, _ = tr.decode(cfg.max_steps)
+            if events is not None:
+                events[gi][1].record()
+            out_tokens[gi].copy_(toks)
+
+    for _ in range(max(args.warmup, 3)):
+        step_device()
     torch.cuda.synchronize()
-    eager_us = (time.perf_counter() - t0) * 1e6 / steps
-    best = None
-    for _ in range(max(1, args.steps)):
-        gtoks, _, us = dm.gnmt_greedy_graph(w, H, steps)
-        best = us if best is None else min(best, us)
-    assert gtoks == toks
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier(world)
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    dec_ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in dev_groups]
+              for _ in range(args.steps)]
+    for k in range(args.steps):
+        ev[k][0].record()
+        step_device(dec_ev[k])
+        ev[k][1].record()
+    torch.cuda.synchronize()
+    barrier(world)
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    decode_ms = sum(a.elapsed_time(b) for row in dec_ev for a, b in row)
+    total_ms = max_over_ranks(sum(step_ms), world)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    for _ in range(2):
+        tr.translate(mine)
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        res = tr.translate(mine)
+    e2e_s = max_over_ranks(time.perf_counter() - t0, world)
+    barrier(world)
+
+    n_sent = S * world * args.steps
+    value = n_sent / (total_ms * 1e-3)
+    e2e_value = n_sent / e2e_s
     peak, peak_src = load_peaks()
-    # bytes one token streams: 4 LSTM layers (w_ih + w_hh), query projection, classifier, attention keys
-    nbytes = 2 * (4 * H * H * 2 + 3 * (4 * H * 2 * H + 4 * H * H) + H * H + V * H + 2 * S * H)
-    us_tok = best / steps
-    line = {"metric": "gnmt_decode_us_per_token", "value": us_tok, "unit": "us", "n_gpus": 1, "steps": args.steps,
-            "warmup": 1, "ms_per_step": best / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": "C4 decoder: GNMT-style greedy decode, V=32320 H=1024, 37 source states, 80 steps, 1 stream"},
-            "op_by_op_us_per_token": eager_us, "device_resident_us_per_token": us_tok,
-            "roofline": {"bound": "hbm", "kernel": "one decode step (about 25 dependent launches in one CUDA graph)",
-                         "achieved": nbytes / us_tok / 1e3, "peak": peak, "unit": "GB/s",
-                         "frac": nbytes / us_tok / 1e3 / peak, "peak_source": peak_src, "traffic": None},
-            "gpu_launches": None}
+    H, V = cfg.hidden, cfg.vocab
+    mean_len = sum(int(x.shape[0]) for x in mine) / max(S, 1)
+    # bytes one decode step of one group has to stream: the four layers' matrices, the query projection, the vocabulary
+    # projection (each once per step whatever the group size) and every sentence's attention keys and values
+    step_bytes = 2.0 * (2 * 4 * H * H + 3 * (4 * H * 2 * H + 4 * H * H) + H * H + V * H) + group * 2 * mean_len * H * 2
+    n_steps = len(dev_groups) * cfg.max_steps * args.steps
+    achieved = step_bytes * n_steps / (decode_ms * 1e-3) / 1e9 if decode_ms > 0 else 0.0
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        n_cpu = max(1, min(args.cpu_sample, 8))
+        v, dt, cores = cpu_gnmt_throughput(n_cpu, 9100)
+        cpu = {"value": v, "unit": "sentences/s", "cores": cores, "kind": "port",
+               "sample": f"{n_cpu} synthetic sentences of the same distribution, libtorch {torch.__version__} CPU fp32 "
+                         f"(at::lstm / at::linear per token, one sentence at a time), {dt:.1f} s"}
+    barrier(world)
+    if rank != 0:
+        return
+    h2d = sum(int(ids.numel() + lens.numel()) * 8 for _, ids, lens in staged)
+    line = {"metric": "gnmt_greedy_sentences_per_s", "value": value, "unit": "sentences/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate",
+            "data": "synthetic", "config": c4_config(S * world, group), "sentences_per_gpu": S,
+            "us_per_decode_step": decode_ms * 1e3 / max(n_steps, 1), "decode_share_of_step_time": decode_ms / max(sum(step_ms), 1e-9),
+            "tokens_checksum": int(sum(sum(t) for t in res) % 1000003),
+            "e2e": {"value": e2e_value, "unit": "sentences/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": len(staged) * cfg.max_steps * group * 8},
+            "gpu_launches": (len(dev_groups) * (cfg.max_steps * tr.launches_per_step + 24)) * args.steps,
+            "roofline": {"bound": "hbm", "kernel": f"one decode step of {group} sentences ({tr.launches_per_step} launches in a "
+                                                    "CUDA graph: 8 gate GEMMs, 4 gate kernels, attention, vocabulary GEMM, arg max, copies)",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+                         "traffic": None, "bytes_per_step": step_bytes,
+                         "per_sentence_equivalent_gbs": achieved * group,
+                         "note": "algorithmic bytes = every decoder matrix once per step plus each sentence's keys and "
+                                 "values; one sentence at a time would stream the same matrices per sentence"},
+            "clocks": clocks}
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
 
 
@@ -587,8 +705,10 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4", "c5"],
                     help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm; "
                          "c4 / c5 = GNMT-style / Transformer-style decoder step, op by op against device-resident")
-    ap.add_argument("--streams-total", type=int, default=STREAMS_TOTAL,
-                    help="utterance streams of one step, sharded over the ranks (the configuration's 1024)")
+    ap.add_argument("--streams-total", type=int, default=0,
+                    help="streams of one step, sharded over the ranks (0 = the configuration's own: 1024 utterances for "
+                         "c3, 512 sentences for c4, 2048 sequences for c5)")
+    ap.add_argument("--group", type=int, default=0, help="c4 / c5: sentences decoded in lock step per group (0 = 128)")
     ap.add_argument("--streams-per-gpu", type=int, default=0,
                     help="overrides --streams-total with a per-rank count (profiling runs on small cases)")
     ap.add_argument("--streams-per-call", type=int, default=0,
@@ -601,17 +721,20 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--encoder-batch", type=int, default=0, help="utterances per lock-step encoder group (0 = default)")
     args = ap.parse_args()
+    if args.workload == "c3" and not args.streams_total:
+        args.streams_total = STREAMS_TOTAL
     if args.impl == "reference":
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed
-        run_reference(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
+        ref = {"c4": run_reference_c4}.get(args.workload, run_reference)
+        ref(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
-    if args.workload in ("c1", "c2", "c4", "c5"):
+    if args.workload in ("c1", "c2", "c5"):
         if int(os.environ.get("RANK", "0")) == 0:
-            {"c1": run_c1, "c2": run_c2, "c4": run_c4, "c5": run_c5}[args.workload](args)
+            {"c1": run_c1, "c2": run_c2, "c5": run_c5}[args.workload](args)
         return
     rank, world, local = dist_setup(args.gpus)
     try:
-        run_gpu(args, rank, world, local)
+        {"c3": run_gpu, "c4": run_c4}[args.workload](args, rank, world, local)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -189,12 +189,13 @@ int pimb200_attention_rows(const void* q, const void* K, const void* V, const lo
  *     ctx[j, :] = sum_s softmax(e)[s] * values[s, :]
  * q [n_seq, H]; row s of sentence j at j * seq_stride + s * row_stride elements of keys_proj / values (a time-major
  * encoder output [S, n_seq, H] has row_stride = n_seq * H, seq_stride = H); ctx rows ctx_stride elements apart, so the
- * context can be written straight into the second half of the decoder's [n_seq, 2H] concatenation buffer.
+ * context can be written straight into the second half of the decoder's [n_seq, 2H] concatenation buffer; `scores` is
+ * caller-provided device scratch of n_seq * max_len floats (the raw scores e, left there).  Two launches.
  * Stands for the add -> tanh -> matmul -> softmax -> bmm chain of the reference's GNMT graph (executeAtenAdd
  * aten_ops_executor.cpp:110-166, executeAtenTanh, executeAtenMatmul 2488-2505, executeAtenSoftmax 3402-3436,
  * executeAtenBmm), five interpreter dispatches per token there. */
 int pimb200_additive_attention(const void* q, const void* keys_proj, const void* values, const long long* lengths,
-                               const void* v, const void* bias, void* ctx, int n_seq, long max_len, int H,
+                               const void* v, const void* bias, void* ctx, float* scores, int n_seq, long max_len, int H,
                                long row_stride, long seq_stride, long ctx_stride, void* stream);
 
 typedef struct pimb200_lstm pimb200_lstm;

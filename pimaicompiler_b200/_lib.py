@@ -43,8 +43,8 @@ SIGNATURES = {
     "pimb200_attention_row": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, _vp, _i, _i, C.c_long, C.c_float, _vp]),
     "pimb200_attention_rows": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, C.c_long, _vp, _i, _i, _i, C.c_long, C.c_long,
                                     C.c_float, _vp]),
-    "pimb200_additive_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, C.c_long, _i, C.c_long, C.c_long, C.c_long,
-                                        _vp]),
+    "pimb200_additive_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, C.c_long, _i, C.c_long, C.c_long,
+                                        C.c_long, _vp]),
     "pimb200_gather_rows": (_i, [_vp, _vp, _vp, C.c_long, _sz, C.c_long, _vp]),
     "pimb200_scatter_rows": (_i, [_vp, _vp, _vp, C.c_long, _sz, C.c_long, _vp]),
     "pimb200_masked_fill_f16": (_i, [_vp, _vp, C.c_float, _vp, _sz, _sz, _vp]),

@@ -295,78 +295,104 @@ __global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const __ha
     }
 }
 
-// Additive (normalised Bahdanau) attention of a decode step, one CTA per sentence:
+// Additive (normalised Bahdanau) attention of a decode step:
 //     e[s]   = sum_h v[h] * tanh(keys_proj[s, h] + q[h] + bias[h]),  s < length
 //     ctx[h] = sum_s softmax(e)[s] * values[s, h]
 // Row s of sentence j lies at j * seq_stride + s * row_stride elements (time-major encoder output: row_stride =
-// sentences * H, seq_stride = H).  Scores and the query vector live in shared memory.
+// sentences * H, seq_stride = H).  Two launches, both with far more CTAs than SMs, because one CTA per sentence walks
+// its 50 rows one dependent load after the other: (1) a warp per (sentence, source position) computes the score,
+// (2) a CTA per (sentence, slice of H) turns the sentence's scores into weights and accumulates its slice of the
+// context, eight rows of loads in flight per thread.
 constexpr int kAddAttnThreads = 256;
+constexpr int kAddAttnSlice = 256;       // context elements per CTA of the second launch (two per thread, 128 threads)
 
-__global__ void __launch_bounds__(kAddAttnThreads) additive_attention_kernel(
-    const __half* __restrict__ q, const __half* __restrict__ keys_proj, const __half* __restrict__ values,
-    const long long* __restrict__ lengths, const __half* __restrict__ v, const __half* __restrict__ bias,
-    __half* __restrict__ ctx, long max_len, int H, long row_stride, long seq_stride, long ctx_stride) {
-    extern __shared__ float sm[];            // [max_len] scores, [H] q + bias, [H] v
-    __shared__ float red[kAddAttnThreads / 32];
-    float* sc = sm;
-    float* qb = sm + max_len;
-    float* vs = qb + H;
-    const int seq = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(kAddAttnThreads) additive_scores_kernel(
+    const __half* __restrict__ q, const __half* __restrict__ keys_proj, const long long* __restrict__ lengths,
+    const __half* __restrict__ v, const __half* __restrict__ bias, float* __restrict__ scores, int n_seq, long max_len,
+    int H, long row_stride, long seq_stride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long row = (long)blockIdx.x * (kAddAttnThreads / 32) + warp;     // (sentence, position), position fastest
+    if (row >= (long)n_seq * max_len) return;
+    const int seq = (int)(row / max_len);
+    const long s = row % max_len;
     long L = lengths ? (long)lengths[seq] : max_len;
     L = L < 0 ? 0 : (L > max_len ? max_len : L);
-    for (int h = threadIdx.x; h < H; h += kAddAttnThreads) {
-        qb[h] = __half2float(q[(size_t)seq * H + h]) + (bias ? __half2float(bias[h]) : 0.f);
-        vs[h] = __half2float(v[h]);
-    }
-    __syncthreads();
-    const __half* kp = keys_proj + (size_t)seq * seq_stride;
-    const __half* vals = values + (size_t)seq * seq_stride;
-    const bool vec = (H % 8 == 0) && (row_stride % 8 == 0) && (seq_stride % 8 == 0) && ((reinterpret_cast<uintptr_t>(keys_proj) & 15u) == 0);
-    for (long s = warp; s < L; s += kAddAttnThreads / 32) {
-        const __half* kr = kp + (size_t)s * row_stride;
-        float a = 0.f;
-        if (vec) {
-            for (int c = lane; c < (H >> 3); c += 32) {
-                float kf[8];
-                widen8(__ldg(reinterpret_cast<const uint4*>(kr) + c), kf);
+    if (s >= L) return;
+    const __half* kr = keys_proj + (size_t)seq * seq_stride + (size_t)s * row_stride;
+    const __half* qr = q + (size_t)seq * H;
+    float a = 0.f;
+    const bool vec = (H % 8 == 0) && (row_stride % 8 == 0) && (seq_stride % 8 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(keys_proj) & 15u) == 0) && ((reinterpret_cast<uintptr_t>(q) & 15u) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(v) & 15u) == 0) && (!bias || (reinterpret_cast<uintptr_t>(bias) & 15u) == 0);
+    if (vec) {
+        for (int c = lane; c < (H >> 3); c += 32) {
+            float kf[8], qf[8], vf[8], bf[8];
+            widen8(__ldg(reinterpret_cast<const uint4*>(kr) + c), kf);
+            widen8(__ldg(reinterpret_cast<const uint4*>(qr) + c), qf);
+            widen8(__ldg(reinterpret_cast<const uint4*>(v) + c), vf);
+            if (bias) widen8(__ldg(reinterpret_cast<const uint4*>(bias) + c), bf);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) a = fmaf(vs[c * 8 + i], tanhf_(kf[i] + qb[c * 8 + i]), a);
-            }
-        } else {
-            for (int h = lane; h < H; h += 32) a = fmaf(vs[h], tanhf_(__half2float(kr[h]) + qb[h]), a);
+            for (int i = 0; i < 8; ++i) a = fmaf(vf[i], tanhf_(kf[i] + (qf[i] + (bias ? bf[i] : 0.f))), a);
         }
-        a = warp_sum(a);
-        if (lane == 0) sc[s] = a;
+    } else {
+        for (int h = lane; h < H; h += 32)
+            a = fmaf(__half2float(v[h]),
+                     tanhf_(__half2float(kr[h]) + (__half2float(qr[h]) + (bias ? __half2float(bias[h]) : 0.f))), a);
     }
-    __syncthreads();
+    a = warp_sum(a);
+    if (lane == 0) scores[row] = a;
+}
+
+__global__ void __launch_bounds__(kAddAttnSlice / 2) additive_context_kernel(
+    const float* __restrict__ scores, const __half* __restrict__ values, const long long* __restrict__ lengths,
+    __half* __restrict__ ctx, long max_len, int H, long row_stride, long seq_stride, long ctx_stride) {
+    extern __shared__ float sc[];            // [max_len] softmax weights of this sentence
+    __shared__ float red[kAddAttnSlice / 64];
+    constexpr int T = kAddAttnSlice / 2;
+    const int seq = blockIdx.y;
+    long L = lengths ? (long)lengths[seq] : max_len;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
     float m = -CUDART_INF_F;
-    for (long s = threadIdx.x; s < L; s += kAddAttnThreads) m = fmaxf(m, sc[s]);
-    m = block_max<kAddAttnThreads>(m, red);
+    for (long s = threadIdx.x; s < L; s += T) m = fmaxf(m, scores[(size_t)seq * max_len + s]);
+    m = block_max<T>(m, red);
     float sum = 0.f;
-    for (long s = threadIdx.x; s < L; s += kAddAttnThreads) {
-        const float e = expf(sc[s] - m);
+    for (long s = threadIdx.x; s < L; s += T) {
+        const float e = expf(scores[(size_t)seq * max_len + s] - m);
         sc[s] = e;
         sum += e;
     }
-    sum = block_sum<kAddAttnThreads>(sum, red);   // ends with a barrier: every sc[s] is final
+    sum = block_sum<T>(sum, red);             // ends with a barrier: every sc[s] is final
     const float inv = L > 0 ? 1.0f / sum : 0.f;
-    // context: threads along H (two halves per thread and pass), rows in sequence; a warp reads 128 contiguous bytes
-    for (int h = threadIdx.x * 2; h < H; h += kAddAttnThreads * 2) {
+    const int h = blockIdx.x * kAddAttnSlice + threadIdx.x * 2;
+    if (h >= H) return;
+    const __half* vals = values + (size_t)seq * seq_stride + h;
+    __half* out = ctx + (size_t)seq * ctx_stride + h;
+    if (h + 1 < H && (row_stride % 2 == 0) && (seq_stride % 2 == 0) && (ctx_stride % 2 == 0) &&
+        ((reinterpret_cast<uintptr_t>(values) & 3u) == 0) && ((reinterpret_cast<uintptr_t>(ctx) & 3u) == 0)) {
         float a0 = 0.f, a1 = 0.f;
-        if (h + 1 < H && (row_stride % 2 == 0) && (seq_stride % 2 == 0)) {
-            for (long s = 0; s < L; ++s) {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(vals + (size_t)s * row_stride + h));
-                a0 = fmaf(sc[s], f.x, a0);
-                a1 = fmaf(sc[s], f.y, a1);
+        long s = 0;
+        for (; s + 8 <= L; s += 8) {
+            __half2 x[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = *reinterpret_cast<const __half2*>(vals + (size_t)(s + i) * row_stride);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = __half22float2(x[i]);
+                a0 = fmaf(sc[s + i], f.x, a0);
+                a1 = fmaf(sc[s + i], f.y, a1);
             }
-            ctx[(size_t)seq * ctx_stride + h] = __float2half_rn(a0 * inv);
-            ctx[(size_t)seq * ctx_stride + h + 1] = __float2half_rn(a1 * inv);
-        } else {
-            for (int hh = h; hh < min(h + 2, H); ++hh) {
-                float a = 0.f;
-                for (long s = 0; s < L; ++s) a = fmaf(sc[s], __half2float(vals[(size_t)s * row_stride + hh]), a);
-                ctx[(size_t)seq * ctx_stride + hh] = __float2half_rn(a * inv);
-            }
+        }
+        for (; s < L; ++s) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(vals + (size_t)s * row_stride));
+            a0 = fmaf(sc[s], f.x, a0);
+            a1 = fmaf(sc[s], f.y, a1);
+        }
+        *reinterpret_cast<__half2*>(out) = __floats2half2_rn(a0 * inv, a1 * inv);
+    } else {
+        for (int e = 0; e < 2 && h + e < H; ++e) {
+            float a = 0.f;
+            for (long s = 0; s < L; ++s) a = fmaf(sc[s], __half2float(vals[(size_t)s * row_stride + e]), a);
+            out[e] = __float2half_rn(a * inv);
         }
     }
 }
@@ -514,17 +540,22 @@ extern "C" int pimb200_attention_rows(const void* q, const void* K, const void* 
 }
 
 extern "C" int pimb200_additive_attention(const void* q, const void* keys_proj, const void* values, const long long* lengths,
-                                          const void* v, const void* bias, void* ctx, int n_seq, long max_len, int H,
-                                          long row_stride, long seq_stride, long ctx_stride, void* stream) {
+                                          const void* v, const void* bias, void* ctx, float* scores, int n_seq,
+                                          long max_len, int H, long row_stride, long seq_stride, long ctx_stride,
+                                          void* stream) {
     if (n_seq == 0) return PIMB200_OK;
-    if (!q || !keys_proj || !values || !v || !ctx || n_seq < 0 || max_len <= 0 || H <= 0 || row_stride < H || seq_stride < 0 ||
-        ctx_stride < H)
+    if (!q || !keys_proj || !values || !v || !ctx || !scores || n_seq < 0 || n_seq > 65535 || max_len <= 0 || H <= 0 ||
+        row_stride < H || seq_stride < 0 || ctx_stride < H)
         return PIMB200_ERR_BAD_ARG;
-    const size_t smem = ((size_t)max_len + 2 * (size_t)H) * sizeof(float);
-    if (smem + 64 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
-    additive_attention_kernel<<<(unsigned)n_seq, kAddAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(q), static_cast<const __half*>(keys_proj), static_cast<const __half*>(values), lengths,
-        static_cast<const __half*>(v), static_cast<const __half*>(bias), static_cast<__half*>(ctx), max_len, H, row_stride,
-        seq_stride, ctx_stride);
+    if ((size_t)max_len * sizeof(float) + 64 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const long rows = (long)n_seq * max_len;
+    additive_scores_kernel<<<(unsigned)((rows + kAddAttnThreads / 32 - 1) / (kAddAttnThreads / 32)), kAddAttnThreads, 0, st>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(keys_proj), lengths, static_cast<const __half*>(v),
+        static_cast<const __half*>(bias), scores, n_seq, max_len, H, row_stride, seq_stride);
+    additive_context_kernel<<<dim3((unsigned)((H + kAddAttnSlice - 1) / kAddAttnSlice), (unsigned)n_seq), kAddAttnSlice / 2,
+                              (size_t)max_len * sizeof(float), st>>>(
+        scores, static_cast<const __half*>(values), lengths, static_cast<__half*>(ctx), max_len, H, row_stride, seq_stride,
+        ctx_stride);
     return launch_status();
 }

@@ -55,6 +55,7 @@ class GnmtTranslator:
         self.step_idx = torch.zeros(1, **i64)
         self.x = torch.zeros(G, H, **f16)
         self.q = torch.zeros(G, H, **f16)
+        self.scores = torch.zeros(G, S, dtype=torch.float32, device=self.dev)
         self.y = [torch.zeros(1, G, H, **f16) for _ in range(4)]
         self.r2 = torch.zeros(G, H, **f16)
         self.r3 = torch.zeros(G, H, **f16)
@@ -106,7 +107,7 @@ class GnmtTranslator:
         y0 = self.y[0].view(G, H)
         ops.gemm_wx(w["Wq"], y0, out=self.q); n += 1
         ops.additive_attention(self.q, self.keys_proj, self.enc_out, self.lengths, self.v_norm, w["att_b"],
-                               out=self.cat[0][:, H:]); n += 1
+                               out=self.cat[0][:, H:], scores=self.scores); n += 2
         ops.copy_2d(self.cat[0], 0, row, y0, 0, half, half, G); n += 1
         for i in (1, 2):          # the context is the second half of every layer's input
             ops.copy_2d(self.cat[i], half, row, self.cat[0], half, row, half, G); n += 1
@@ -186,6 +187,32 @@ class GnmtTranslator:
         return (toks, self.logits_out[:steps]) if want_logits else (toks, None)
 
     # ------------------------------------------------------------------------------------------------ user call
+    def stage(self, sentences: Sequence[torch.Tensor]):
+        """Sorts the sentences by length and packs them into lock-step groups: a list of (sentence indices, padded ids
+        [S_g, G] int64, lengths [G] int64), the tensors in pinned host memory.  A ragged last group is filled with
+        one-token dummies."""
+        G = self.G
+        order = sorted(range(len(sentences)), key=lambda i: -int(sentences[i].shape[0]))
+        groups = []
+        for g0 in range(0, len(order), G):
+            idx = order[g0:g0 + G]
+            lens = [int(sentences[i].shape[0]) for i in idx]
+            if max(lens) > self.S or min(lens) < 1:
+                raise ValueError("sentence length outside 1..max_len")
+            ids = torch.full((max(lens), G), 4, dtype=torch.int64)
+            for j, i in enumerate(idx):
+                ids[:lens[j], j] = sentences[i]
+            lens_t = torch.ones(G, dtype=torch.int64)
+            lens_t[:len(idx)] = torch.tensor(lens, dtype=torch.int64)
+            groups.append((idx, ids.pin_memory(), lens_t.pin_memory()))
+        return groups
+
+    def run_group(self, ids_dev: torch.Tensor, lens_dev: torch.Tensor, steps: int, forced: Optional[torch.Tensor] = None,
+                  want_logits: bool = False):
+        """Encoder + greedy decode of one staged group whose ids / lengths are already on the device."""
+        self.encode(ids_dev, lens_dev)
+        return self.decode(steps, forced, want_logits)
+
     def translate(self, sentences: Sequence[torch.Tensor], steps: Optional[int] = None,
                   forced: Optional[Sequence[Sequence[int]]] = None, want_logits: bool = False):
         """sentences: 1-D int64 CPU tensors of source token ids.  Returns one token list per sentence (cut behind the
@@ -194,30 +221,18 @@ class GnmtTranslator:
         cfg, G = self.cfg, self.G
         n = len(sentences)
         run_steps = cfg.max_steps if steps is None else steps
-        order = sorted(range(n), key=lambda i: -int(sentences[i].shape[0]))
         out_toks: List[Optional[List[int]]] = [None] * n
         out_logits: List[Optional[torch.Tensor]] = [None] * n
         pending = []
-        for g0 in range(0, n, G):
-            idx = order[g0:g0 + G]
-            lens = [int(sentences[i].shape[0]) for i in idx]
-            if max(lens) > self.S or min(lens) < 1:
-                raise ValueError("sentence length outside 1..max_len")
-            Sg = max(lens)
-            ids = torch.full((Sg, G), 4, dtype=torch.int64)
-            for j, i in enumerate(idx):
-                ids[:lens[j], j] = sentences[i]
-            lens_t = torch.ones(G, dtype=torch.int64)
-            lens_t[:len(idx)] = torch.tensor(lens, dtype=torch.int64)
-            ids_d = ids.pin_memory().to(self.dev, non_blocking=True)
-            lens_d = lens_t.pin_memory().to(self.dev, non_blocking=True)
-            self.encode(ids_d, lens_d)
+        for idx, ids, lens in self.stage(sentences):
+            ids_d = ids.to(self.dev, non_blocking=True)
+            lens_d = lens.to(self.dev, non_blocking=True)
             f = None
             if forced is not None:
                 f = torch.zeros(run_steps, G, dtype=torch.int64)
                 for j, i in enumerate(idx):
                     f[:, j] = torch.tensor(list(forced[i])[:run_steps], dtype=torch.int64)
-            toks, logits = self.decode(run_steps, f, want_logits)
+            toks, logits = self.run_group(ids_d, lens_d, run_steps, f, want_logits)
             host = torch.empty(toks.shape, dtype=torch.int64).pin_memory()
             host.copy_(toks, non_blocking=True)
             pending.append((idx, host, logits.float().cpu() if want_logits else None))

@@ -251,15 +251,18 @@ def attention_rows(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int
 
 
 def additive_attention(q: torch.Tensor, keys_proj: torch.Tensor, values: torch.Tensor, lengths: Optional[torch.Tensor],
-                       v: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       v: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+                       scores: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Normalised Bahdanau attention for n sentences: q [n, H]; keys_proj / values time-major [S, n, H] (contiguous);
     lengths int64 [n] on the device; v, bias [H].  `out` may be a column slice of a wider [n, *] buffer."""
     _req_half_cuda(q, keys_proj, values, v, bias)
     S, n, H = keys_proj.shape
     if out is None:
         out = torch.empty(n, H, dtype=torch.float16, device=q.device)
+    if scores is None:
+        scores = torch.empty(n, S, dtype=torch.float32, device=q.device)
     check(_lib.lib().pimb200_additive_attention(_ptr(q), _ptr(keys_proj), _ptr(values), _ptr(lengths), _ptr(v), _ptr(bias),
-                                                _ptr(out), n, S, H, keys_proj.stride(0), keys_proj.stride(1),
+                                                _ptr(out), _ptr(scores), n, S, H, keys_proj.stride(0), keys_proj.stride(1),
                                                 out.stride(0), _stream()), "additive_attention")
     return out
 

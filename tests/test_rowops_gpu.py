@@ -136,3 +136,55 @@ def test_attention_row_matches_oracle(heads, hd, S, L):
     pos = torch.tensor([L - 1], dtype=torch.int64, device="cuda")     # entries 0..pos are valid
     got_dev = ops.attention_row(q.cuda(), K.cuda(), V.cuda(), heads, length_dev=pos, length_add=1).float().cpu().numpy()
     assert np.array_equal(got_dev, got)
+
+
+@pytest.mark.parametrize("n,heads,hd,S", [(5, 8, 64, 64), (3, 4, 16, 9), (33, 2, 40, 70)])
+def test_attention_rows_batched_matches_oracle(n, heads, hd, S):
+    # lock-step decode of n sequences: one cache and one length per sequence (cross-attention over ragged sources), and a
+    # shared device-side position (self-attention at step t)
+    ops = _ops()
+    g = torch.Generator().manual_seed(n * 100 + S)
+    d = heads * hd
+    q = torch.randn(n, d, generator=g).to(torch.float16)
+    K = torch.randn(n, S, d, generator=g).to(torch.float16)
+    V = torch.randn(n, S, d, generator=g).to(torch.float16)
+    lens = torch.randint(0, S + 1, (n,), generator=g)
+    lens[0] = S
+    got = ops.attention_rows(q.cuda(), K.cuda(), V.cuda(), heads, len_dev=lens.cuda(), len_inc=1).float().cpu().numpy()
+    for j in range(n):
+        ref = co.attention_row(q[j].float().numpy(), K[j].float().numpy(), V[j].float().numpy(), heads, int(lens[j]))
+        np.testing.assert_allclose(got[j], ref, rtol=RTOL, atol=2e-3)
+    pos = torch.tensor([S // 2], dtype=torch.int64, device="cuda")
+    got2 = ops.attention_rows(q.cuda(), K.cuda(), V.cuda(), heads, len_dev=pos, len_inc=0, len_add=1).float().cpu().numpy()
+    for j in range(n):
+        ref = co.attention_row(q[j].float().numpy(), K[j].float().numpy(), V[j].float().numpy(), heads, S // 2 + 1)
+        np.testing.assert_allclose(got2[j], ref, rtol=RTOL, atol=2e-3)
+
+
+@pytest.mark.parametrize("n,S,H", [(7, 50, 1024), (3, 9, 64), (4, 11, 70), (130, 5, 16)])
+def test_additive_attention_matches_libtorch(n, S, H):
+    # normalised Bahdanau attention for n sentences of ragged length over a time-major [S, n, H] encoder output, the
+    # context written into the second half of a [n, 2H] buffer
+    ops = _ops()
+    g = torch.Generator().manual_seed(n + S + H)
+    q = torch.randn(n, H, generator=g).half()
+    kp = torch.randn(S, n, H, generator=g).half()
+    vals = torch.tanh(torch.randn(S, n, H, generator=g)).half()
+    v = (torch.randn(H, generator=g) / H ** 0.5).half()
+    b = (torch.randn(H, generator=g) * 0.1).half()
+    lens = torch.randint(1, S + 1, (n,), generator=g)
+    lens[0] = S
+    buf = torch.zeros(n, 2 * H, dtype=torch.float16, device="cuda")
+    ops.additive_attention(q.cuda(), kp.cuda(), vals.cuda(), lens.cuda(), v.cuda(), b.cuda(), out=buf[:, H:])
+    got = buf[:, H:].float().cpu()
+    assert float(buf[:, :H].abs().max()) == 0.0
+    for j in range(n):
+        L = int(lens[j])
+        e = torch.tanh(kp[:L, j].float() + q[j].float() + b.float()) @ v.float()
+        ref = torch.softmax(e, 0) @ vals[:L, j].float()
+        np.testing.assert_allclose(got[j].numpy(), ref.numpy(), rtol=2e-3, atol=2e-3)
+    # no bias, full lengths
+    out = ops.additive_attention(q.cuda(), kp.cuda(), vals.cuda(), None, v.cuda(), None).float().cpu()
+    e = torch.einsum("snh,h->sn", torch.tanh(kp.float() + q.float().unsqueeze(0)), v.float())
+    ref = torch.einsum("sn,snh->nh", torch.softmax(e, 0), vals.float())
+    np.testing.assert_allclose(out.numpy(), ref.numpy(), rtol=2e-3, atol=2e-3)
