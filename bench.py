@@ -511,76 +511,113 @@ def run_c1(args):
     print(json.dumps(line), flush=True)
 
 
-C4_SENTENCES = 512   # BASELINE.json configs[3]: 512 sentences of 20..50 tokens, at most 80 decode steps
+# ------------------------------------------------------------------------------------------------
+# C4 / C5: translation workloads, stream-sharded like C3 (sentences round-robin over the ranks, no collective)
+# ------------------------------------------------------------------------------------------------
+class _Translate:
+    """What differs between the GNMT (C4) and the Transformer (C5) workload."""
+
+    def __init__(self, kind: str):
+        from pimaicompiler_b200 import synthetic as syn
+        self.kind = kind
+        if kind == "c4":
+            self.total, self.metric, self.unit = 512, "gnmt_greedy_sentences_per_s", "sentences/s"
+            self.cfg = syn.GnmtConfig()
+            self.make_weights = syn.make_gnmt_weights
+            self.desc = ("C4: GNMT greedy translation (4+4 LSTM layers, hidden 1024, vocabulary 32320, normalised Bahdanau "
+                         "attention), sentences of 20..50 tokens, 80 decode steps")
+            self.l2 = "one step touches 160 MB of weights, more than the 126 MB L2"
+        else:
+            self.total, self.metric, self.unit = 2048, "transformer_greedy_sequences_per_s", "sequences/s"
+            self.cfg = syn.TransformerConfig()
+            self.make_weights = syn.make_transformer_weights
+            self.desc = ("C5: Transformer-base greedy translation (6+6 layers, width 512, 8 heads, feed-forward 2048, "
+                         "vocabulary 32000, key / value cache), sources of 16..64 tokens, 64 decode steps")
+            self.l2 = "a 256 MB buffer is rewritten between timed steps (one step's weights, 84 MB, would fit the L2)"
+
+    def config(self, total: int, group: int) -> dict:
+        return {"workload": self.desc, "streams_total": total, "lockstep_group": group, "max_steps": self.cfg.max_steps,
+                "sharding": "streams round-robin over the ranks, no collective on the data path", "l2": self.l2}
+
+    def translator(self, w, group, dev):
+        if self.kind == "c4":
+            from pimaicompiler_b200.gnmt import GnmtTranslator
+            return GnmtTranslator(self.cfg, w, group=group, device=dev)
+        from pimaicompiler_b200.transformer import TransformerTranslator
+        return TransformerTranslator(self.cfg, w, group=group, device=dev)
+
+    def step_bytes(self, group: int, mean_len: float) -> float:
+        """Bytes one decode step of one group has to stream: every decoder matrix once (whatever the group size) plus each
+        stream's attention keys and values."""
+        c = self.cfg
+        if self.kind == "c4":
+            H, V = c.hidden, c.vocab
+            return 2.0 * (2 * 4 * H * H + 3 * (4 * H * 2 * H + 4 * H * H) + H * H + V * H) + group * 2 * mean_len * H * 2
+        d, f, V, nl = c.d_model, c.ffn, c.vocab, c.layers
+        weights = 2.0 * (nl * (3 * d * d + d * d + d * d + d * d + 2 * d * f) + V * d)
+        kv = group * nl * 2.0 * (mean_len + c.max_steps / 2.0) * d * 2      # cross keys/values + half-full self cache
+        return weights + kv
+
+    def cpu_throughput(self, n: int, seed: int):
+        """Translates n synthetic streams on the host cores with the libtorch oracle; (streams/s, seconds, cores)."""
+        from oracle import torch_oracle as to
+        w = self.make_weights(self.cfg, seed=0)
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        seqs = to.make_sentences(n, self.cfg, seed)
+        fn = to.gnmt_translate if self.kind == "c4" else to.transformer_translate
+        fn(w, seqs[0], self.cfg, 4)
+        t0 = time.perf_counter()
+        for s_ in seqs:
+            fn(w, s_, self.cfg)
+        dt = time.perf_counter() - t0
+        return n / dt, dt, cores
 
 
-def c4_config(total: int, group: int) -> dict:
-    return {"workload": "C4: GNMT greedy translation (4+4 LSTM layers, hidden 1024, vocabulary 32320, normalised Bahdanau "
-                        "attention), sentences of 20..50 tokens, 80 decode steps",
-            "sentences_total": total, "lockstep_group": group, "max_steps": 80,
-            "sharding": "sentences round-robin over the ranks, no collective on the data path",
-            "l2": "one step touches 160 MB of weights, more than the 126 MB L2"}
-
-
-def cpu_gnmt_throughput(n: int, seed: int):
-    """Translates n synthetic sentences on the host cores with the libtorch oracle; (sentences/s, seconds, cores)."""
-    from oracle import torch_oracle as to
-    cfg = to.GnmtConfig()
-    w = to.make_gnmt_weights(cfg, seed=0)
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    sents = to.make_sentences(n, cfg, seed)
-    to.gnmt_translate(w, sents[0], cfg, 4)
-    t0 = time.perf_counter()
-    for s_ in sents:
-        to.gnmt_translate(w, s_, cfg)
-    dt = time.perf_counter() - t0
-    return n / dt, dt, cores
-
-
-def run_reference_c4(args, rank, world):
+def run_reference_translate(args, rank, world):
     if rank != 0:
         return
+    wl = _Translate(args.workload)
     n = max(1, min(args.cpu_sample, 8))
     vals, secs, cores = [], 0.0, 1
     for k in range(args.steps):
-        v, dt, cores = cpu_gnmt_throughput(n, 9000 + k)
+        v, dt, cores = wl.cpu_throughput(n, 9000 + k)
         vals.append(v)
         secs += dt
     value = statistics.median(vals)
-    total = args.streams_total or C4_SENTENCES
-    line = {"impl": "reference", "metric": "gnmt_greedy_sentences_per_s", "value": value, "unit": "sentences/s",
+    total = args.streams_total or wl.total
+    line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit,
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / max(args.steps, 1) * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": c4_config(total, min(args.group or 128, (total + args.gpus - 1) // args.gpus)), "sample_sentences_per_step": n,
-            "cpu_baseline": {"value": value, "unit": "sentences/s", "cores": cores, "kind": "port",
-                             "sample": f"{n} sentences per step, libtorch {torch.__version__} CPU fp32, {cores} threads"},
-            "e2e": {"value": value, "unit": "sentences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "config": wl.config(total, min(args.group or 128, (total + args.gpus - 1) // args.gpus)), "sample_streams_per_step": n,
+            "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": "port",
+                             "sample": f"{n} streams per step, libtorch {torch.__version__} CPU fp32, {cores} threads"},
+            "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
 
-def run_c4(args, rank, world, local):
-    """C4: the configuration's 512 sentences sharded over the ranks; each rank translates its shard in lock-step groups
-    (encoder over the padded group, 80 greedy steps from a CUDA graph).  `value` has the staged token ids resident in
-    HBM; `e2e` goes through GnmtTranslator.translate with host token lists in and out."""
+def run_translate(args, rank, world, local):
+    """C4 / C5: the configuration's streams sharded over the ranks; each rank translates its shard in lock-step groups
+    (encoder over the padded group, then every greedy step from a CUDA graph).  `value` has the staged token ids resident
+    in HBM; `e2e` goes through the translator's translate() with host token lists in and out."""
     from pimaicompiler_b200 import build
     from pimaicompiler_b200 import synthetic as syn
-    from pimaicompiler_b200.gnmt import GnmtTranslator
     build.build()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    cfg = syn.GnmtConfig()
-    w = syn.make_gnmt_weights(cfg, seed=0)
-    total = args.streams_total or C4_SENTENCES
-    sentences_all = syn.make_sentences(total, cfg, seed=11)
-    mine = sentences_all[rank::world]
+    wl = _Translate(args.workload)
+    cfg = wl.cfg
+    w = wl.make_weights(cfg, seed=0)
+    total = args.streams_total or wl.total
+    mine = syn.make_sentences(total, cfg, seed=11)[rank::world]
     S = len(mine)
     group = min(args.group or 128, S)
-    tr = GnmtTranslator(cfg, w, group=group, device=dev)
+    tr = wl.translator(w, group, dev)
     staged = tr.stage(mine)
     dev_groups = [(ids.to(dev), lens.to(dev)) for _, ids, lens in staged]
     out_tokens = torch.zeros(len(staged), cfg.max_steps, group, dtype=torch.int64, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
 
     def step_device(events=None):
         for gi, (ids_d, lens_d) in enumerate(dev_groups):
@@ -604,6 +641,7 @@ def run_c4(args, rank, world, local):
     dec_ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in dev_groups]
               for _ in range(args.steps)]
     for k in range(args.steps):
+        flush.fill_(k & 0xff)
         ev[k][0].record()
         step_device(dec_ev[k])
         ev[k][1].record()
@@ -623,76 +661,44 @@ def run_c4(args, rank, world, local):
     e2e_s = max_over_ranks(time.perf_counter() - t0, world)
     barrier(world)
 
-    n_sent = S * world * args.steps
-    value = n_sent / (total_ms * 1e-3)
-    e2e_value = n_sent / e2e_s
+    n_streams = S * world * args.steps
+    value = n_streams / (total_ms * 1e-3)
+    e2e_value = n_streams / e2e_s
     peak, peak_src = load_peaks()
-    H, V = cfg.hidden, cfg.vocab
     mean_len = sum(int(x.shape[0]) for x in mine) / max(S, 1)
-    # bytes one decode step of one group has to stream: the four layers' matrices, the query projection, the vocabulary
-    # projection (each once per step whatever the group size) and every sentence's attention keys and values
-    step_bytes = 2.0 * (2 * 4 * H * H + 3 * (4 * H * 2 * H + 4 * H * H) + H * H + V * H) + group * 2 * mean_len * H * 2
+    step_bytes = wl.step_bytes(group, mean_len)
     n_steps = len(dev_groups) * cfg.max_steps * args.steps
     achieved = step_bytes * n_steps / (decode_ms * 1e-3) / 1e9 if decode_ms > 0 else 0.0
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
         n_cpu = max(1, min(args.cpu_sample, 8))
-        v, dt, cores = cpu_gnmt_throughput(n_cpu, 9100)
-        cpu = {"value": v, "unit": "sentences/s", "cores": cores, "kind": "port",
-               "sample": f"{n_cpu} synthetic sentences of the same distribution, libtorch {torch.__version__} CPU fp32 "
-                         f"(at::lstm / at::linear per token, one sentence at a time), {dt:.1f} s"}
+        v, dt, cores = wl.cpu_throughput(n_cpu, 9100)
+        cpu = {"value": v, "unit": wl.unit, "cores": cores, "kind": "port",
+               "sample": f"{n_cpu} synthetic streams of the same distribution, libtorch {torch.__version__} CPU fp32 "
+                         f"(the at:: calls of the reference's default executors, one stream at a time), {dt:.1f} s"}
     barrier(world)
     if rank != 0:
         return
     h2d = sum(int(ids.numel() + lens.numel()) * 8 for _, ids, lens in staged)
-    line = {"metric": "gnmt_greedy_sentences_per_s", "value": value, "unit": "sentences/s", "n_gpus": world,
+    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate",
-            "data": "synthetic", "config": c4_config(S * world, group), "sentences_per_gpu": S,
+            "data": "synthetic", "config": wl.config(S * world, group), "streams_per_gpu": S,
             "us_per_decode_step": decode_ms * 1e3 / max(n_steps, 1), "decode_share_of_step_time": decode_ms / max(sum(step_ms), 1e-9),
             "tokens_checksum": int(sum(sum(t) for t in res) % 1000003),
-            "e2e": {"value": e2e_value, "unit": "sentences/s", "h2d_bytes_per_step": h2d,
+            "e2e": {"value": e2e_value, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": len(staged) * cfg.max_steps * group * 8},
             "gpu_launches": (len(dev_groups) * (cfg.max_steps * tr.launches_per_step + 24)) * args.steps,
-            "roofline": {"bound": "hbm", "kernel": f"one decode step of {group} sentences ({tr.launches_per_step} launches in a "
-                                                    "CUDA graph: 8 gate GEMMs, 4 gate kernels, attention, vocabulary GEMM, arg max, copies)",
+            "roofline": {"bound": "hbm", "kernel": f"one decode step of {group} streams ({tr.launches_per_step} launches inside a "
+                                                    "CUDA graph: projection GEMMs, attention, vocabulary GEMM, arg max)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
                          "traffic": None, "bytes_per_step": step_bytes,
-                         "per_sentence_equivalent_gbs": achieved * group,
-                         "note": "algorithmic bytes = every decoder matrix once per step plus each sentence's keys and "
-                                 "values; one sentence at a time would stream the same matrices per sentence"},
+                         "per_stream_equivalent_gbs": achieved * group,
+                         "note": "algorithmic bytes = every decoder matrix once per step plus each stream's keys and "
+                                 "values; one stream at a time would read the same matrices once per stream"},
             "clocks": clocks}
     if cpu is not None:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
-
-
-def run_c5(args):
-    """C5 (decoder side): Transformer-base greedy decode, 6 decoder layers, d_model 512, 8 heads, FFN 2048, vocabulary
-    32000, 40 memory states, 64 steps with a KV cache, one sequence stream; op by op against the step resident on the
-    device (CUDA graph, token and position in device memory, in-place KV append)."""
-    from pimaicompiler_b200 import build
-    build.build()
-    from pimaicompiler_b200 import decode_models as dm
-    d, heads, ffn, V, layers, S, steps = 512, 8, 2048, 32000, 6, 40, 64
-    w = dm.make_transformer(d, heads, ffn, V, layers, S, torch.Generator().manual_seed(5), 2.0)
-    be = dm.PimBackend()
-    dm.transformer_greedy(be, w, d, heads, 4)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    dm.transformer_greedy(be, w, d, heads, steps)
-    torch.cuda.synchronize()
-    eager_us = (time.perf_counter() - t0) * 1e6 / steps
-    best = None
-    for _ in range(max(1, args.steps)):
-        _, _, us = dm.transformer_greedy_graph(w, d, heads, steps)
-        best = us if best is None else min(best, us)
-    us_tok = best / steps
-    line = {"metric": "transformer_decode_us_per_token", "value": us_tok, "unit": "us", "n_gpus": 1, "steps": args.steps,
-            "warmup": 1, "ms_per_step": best / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 storage / f32 accumulate", "data": "synthetic",
-            "config": {"workload": "C5 decoder: Transformer-base greedy decode with KV cache, 6 layers d=512 V=32000, 64 steps, 1 stream"},
-            "op_by_op_us_per_token": eager_us, "device_resident_us_per_token": us_tok, "gpu_launches": None}
     print(json.dumps(line), flush=True)
 
 
@@ -704,7 +710,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c3", choices=["c3", "c2", "c1", "c4", "c5"],
                     help="c3 = RNN-T greedy decode (the headline); c2 = GEMV/GEMM sweep; c1 = single aten::lstm; "
-                         "c4 / c5 = GNMT-style / Transformer-style decoder step, op by op against device-resident")
+                         "c4 / c5 = GNMT / Transformer greedy translation of 512 / 2048 streams in lock-step groups")
     ap.add_argument("--streams-total", type=int, default=0,
                     help="streams of one step, sharded over the ranks (0 = the configuration's own: 1024 utterances for "
                          "c3, 512 sentences for c4, 2048 sequences for c5)")
@@ -725,16 +731,16 @@ def main():
         args.streams_total = STREAMS_TOTAL
     if args.impl == "reference":
         # CPU arm: rank 0 alone works, the others leave at once; no process group is needed
-        ref = {"c4": run_reference_c4}.get(args.workload, run_reference)
+        ref = {"c4": run_reference_translate, "c5": run_reference_translate}.get(args.workload, run_reference)
         ref(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
-    if args.workload in ("c1", "c2", "c5"):
+    if args.workload in ("c1", "c2"):
         if int(os.environ.get("RANK", "0")) == 0:
-            {"c1": run_c1, "c2": run_c2, "c5": run_c5}[args.workload](args)
+            {"c1": run_c1, "c2": run_c2}[args.workload](args)
         return
     rank, world, local = dist_setup(args.gpus)
     try:
-        {"c3": run_gpu, "c4": run_c4}[args.workload](args, rank, world, local)
+        {"c3": run_gpu, "c4": run_translate, "c5": run_translate}[args.workload](args, rank, world, local)
     finally:
         if world > 1:
             import torch.distributed as dist

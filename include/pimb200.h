@@ -178,11 +178,29 @@ int pimb200_attention_row(const void* q, const void* K, const void* V, const lon
  * sequence j attends to its own cache at K + j * seq_stride (V likewise) with its own length
  * L_j = (len_dev ? len_dev[j * len_inc] : 0) + len_add (len_inc 0: one shared device-side position, the self-attention
  * of a lock-step decode; len_inc 1: per-sequence source lengths, the cross-attention).  One launch, a CTA per
- * (head, sequence).  The reference runs one sequence at a time (its matmul -> softmax -> matmul group, see above);
+ * (head, sequence); rows of q / out are q_stride / out_stride elements apart.  The reference runs one sequence at a time (its matmul -> softmax -> matmul group, see above);
  * batching sentences is how one GPU serves many streams here. */
 int pimb200_attention_rows(const void* q, const void* K, const void* V, const long long* len_dev, long len_inc,
                            long len_add, long max_len, void* out, int n_seq, int heads, int head_dim, long kv_stride,
-                           long seq_stride, float scale, void* stream);
+                           long seq_stride, long q_stride, long out_stride, float scale, void* stream);
+
+/* Multi-head self-attention over every position of n_seq padded sequences (a Transformer encoder layer):
+ *     out[j, i, h, :] = softmax_s(scale * q[j, i, h, :] . k[j, s, h, :]) . v[j, s, h, :],   s < lengths[j] (int64, DEVICE;
+ * NULL = max_len), for every query position i < lengths[j]; positions past the length give zero rows.  Row (j, i) of
+ * q / k / v lies at j * seq_stride + i * row_stride elements (so the three may be column slices of one fused [.., 3d]
+ * projection), of out at j * out_seq_stride + i * out_row_stride.  One launch, a CTA per (head, sequence), keys and
+ * values of the head in shared memory (max_len * head_dim limited by 48 KB).  Stands for the per-head
+ * matmul -> masked softmax -> matmul group of the reference's Transformer graph (executeAtenMatmul
+ * aten_ops_executor.cpp:2488-2505, executeAtenMaskedFill, executeAtenSoftmax 3402-3436). */
+int pimb200_attention_block(const void* q, const void* k, const void* v, const long long* lengths, void* out, int n_seq,
+                            long max_len, int heads, int head_dim, long row_stride, long seq_stride, long out_row_stride,
+                            long out_seq_stride, float scale, void* stream);
+
+/* y = layer_norm(x + r) over the last dimension (gamma / beta optional): the residual add and the normalisation that
+ * follow every Transformer sub-layer, two interpreter nodes in the reference (executeAtenAdd aten_ops_executor.cpp:110-166,
+ * executeAtenLayerNorm).  cols * 4 bytes of shared memory per row. */
+int pimb200_add_layer_norm_rows(const void* x, const void* r, const void* gamma, const void* beta, void* y, long rows,
+                                long cols, float eps, void* stream);
 
 /* Additive (normalised Bahdanau) attention of a GNMT decode step for n_seq sentences, one CTA per sentence:
  *     e[s] = sum_h v[h] * tanh(keys_proj[s, h] + q[h] + bias[h]),  s < lengths[j]  (int64 in DEVICE memory; NULL = max_len)

@@ -12,7 +12,8 @@ from typing import List, Optional
 import torch
 
 
-from pimaicompiler_b200.synthetic import (GnmtConfig, RnntConfig, RnntWeights, make_features,  # noqa: F401,E402
+from pimaicompiler_b200.synthetic import (GnmtConfig, RnntConfig, RnntWeights, TransformerConfig,  # noqa: F401,E402
+                                          make_features, make_transformer_weights,
                                           make_gnmt_weights, make_rnnt_weights, make_sentences)
 
 
@@ -99,6 +100,60 @@ def gnmt_translate(w: dict, src: torch.Tensor, cfg, steps: Optional[int] = None,
         r2 = cell("dec2", torch.cat([y1, ctx]), 2) + y1
         r3 = cell("dec3", torch.cat([r2, ctx]), 3) + r2
         lg = torch.nn.functional.linear(r3, w["Wc"], w["bc"])
+        logits.append(lg)
+        best = int(torch.argmax(lg))
+        toks.append(best)
+        tok = best if forced is None else int(forced[t])
+    return toks, torch.stack(logits)
+
+
+# ------------------------------------------------------------------------------------------------ Transformer (configuration C5)
+def _mha(q, k, v, heads):
+    """q [Tq, d], k / v [Tk, d] -> [Tq, d]: at::matmul -> softmax -> matmul per head."""
+    Tq, d = q.shape
+    hd = d // heads
+    qh = q.view(Tq, heads, hd).transpose(0, 1)
+    kh = k.view(-1, heads, hd).transpose(0, 1)
+    vh = v.view(-1, heads, hd).transpose(0, 1)
+    p = torch.softmax(qh @ kh.transpose(1, 2) / hd ** 0.5, -1)
+    return (p @ vh).transpose(0, 1).reshape(Tq, d)
+
+
+def _ln(x):
+    return torch.nn.functional.layer_norm(x, x.shape[-1:])
+
+
+def transformer_encode(w: dict, src: torch.Tensor, cfg) -> torch.Tensor:
+    lin = torch.nn.functional.linear
+    S = src.shape[0]
+    x = w["emb_src"][src] + w["pe"][:S]
+    for L in w["enc"]:
+        a = _mha(lin(x, L["sq"], L["sq_b"]), lin(x, L["sk"], L["sk_b"]), lin(x, L["sv"], L["sv_b"]), cfg.heads)
+        x = _ln(x + lin(a, L["so"], L["so_b"]))
+        x = _ln(x + lin(torch.relu(lin(x, L["f1"], L["f1_b"])), L["f2"], L["f2_b"]))
+    return x
+
+
+def transformer_translate(w: dict, src: torch.Tensor, cfg, steps: Optional[int] = None, forced: Optional[List[int]] = None):
+    """Greedy decode of one sequence with a key / value cache; returns (tokens, logits [steps, V])."""
+    lin = torch.nn.functional.linear
+    steps = cfg.max_steps if steps is None else steps
+    mem = transformer_encode(w, src, cfg)
+    cross = [(lin(mem, L["ck"], L["ck_b"]), lin(mem, L["cv"], L["cv_b"])) for L in w["dec"]]
+    kc = [[] for _ in w["dec"]]
+    vc = [[] for _ in w["dec"]]
+    tok, toks, logits = cfg.bos, [], []
+    for t in range(steps):
+        x = (w["emb_tgt"][tok] + w["pe"][t]).view(1, -1)
+        for i, L in enumerate(w["dec"]):
+            kc[i].append(lin(x, L["sk"], L["sk_b"]))
+            vc[i].append(lin(x, L["sv"], L["sv_b"]))
+            a = _mha(lin(x, L["sq"], L["sq_b"]), torch.cat(kc[i]), torch.cat(vc[i]), cfg.heads)
+            x = _ln(x + lin(a, L["so"], L["so_b"]))
+            ca = _mha(lin(x, L["cq"], L["cq_b"]), cross[i][0], cross[i][1], cfg.heads)
+            x = _ln(x + lin(ca, L["co"], L["co_b"]))
+            x = _ln(x + lin(torch.relu(lin(x, L["f1"], L["f1_b"])), L["f2"], L["f2_b"]))
+        lg = lin(x, w["Wo"]).view(-1)
         logits.append(lg)
         best = int(torch.argmax(lg))
         toks.append(best)

@@ -42,7 +42,10 @@ SIGNATURES = {
     "pimb200_tanh_f16": (_i, [_vp, _vp, _sz, _vp]),
     "pimb200_attention_row": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, _vp, _i, _i, C.c_long, C.c_float, _vp]),
     "pimb200_attention_rows": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, C.c_long, _vp, _i, _i, _i, C.c_long, C.c_long,
-                                    C.c_float, _vp]),
+                                    C.c_long, C.c_long, C.c_float, _vp]),
+    "pimb200_attention_block": (_i, [_vp, _vp, _vp, _vp, _vp, _i, C.c_long, _i, _i, C.c_long, C.c_long, C.c_long, C.c_long,
+                                     C.c_float, _vp]),
+    "pimb200_add_layer_norm_rows": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_long, C.c_long, C.c_float, _vp]),
     "pimb200_additive_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, C.c_long, _i, C.c_long, C.c_long,
                                         C.c_long, _vp]),
     "pimb200_gather_rows": (_i, [_vp, _vp, _vp, C.c_long, _sz, C.c_long, _vp]),

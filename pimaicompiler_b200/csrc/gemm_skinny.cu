@@ -22,6 +22,9 @@ constexpr int kSkinnyWarps = 8;
 constexpr int kSkinnyThreads = kSkinnyWarps * 32;
 constexpr int kSkinnyRows = 16;
 constexpr int kSkinnyMaxJ = 32;
+constexpr int kSkinnyMaxBlockedJ = 256;                     // column-blocked form: at most 8 blocks of 32 rows ...
+constexpr int kSkinnyMaxBlockedN = 2048;                    // ... of a matrix of at most 16 tcgen05 row tiles ...
+constexpr size_t kSkinnyMaxBlockedNK = (size_t)8 << 20;     // ... and 16 MB
 
 // not volatile: the compiler may move these loads and products freely (volatile asm statements keep their order, which
 // would put every block's loads behind the previous block's products and serialise the HBM round trips)
@@ -69,7 +72,9 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
     }
     const __half* xrow[NT];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) xrow[j] = a.X + (size_t)min(j * 8 + g, a.J - 1) * a.ldx + 8 * t;
+    const int j_base = blockIdx.y * kSkinnyMaxJ;               // this CTA's block of up to 32 activation rows
+    const int j_rem = a.J - j_base;
+    for (int j = 0; j < NT; ++j) xrow[j] = a.X + (size_t)(j_base + min(j * 8 + g, j_rem - 1)) * a.ldx + 8 * t;
     float acc[MTW][NT][4];
 #pragma unroll
     for (int m = 0; m < MTW; ++m)
@@ -129,14 +134,14 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
     for (int i = threadIdx.x; i < ROWS * NT * 8; i += kSkinnyThreads) {
         const int r = i % ROWS, j = i / ROWS;
         const int n = n0 + r;
-        if (n >= a.N || j >= a.J) continue;
+        if (n >= a.N || j >= j_rem) continue;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < KS; ++w) v += part[w][r][j];
         if (a.bias) v += __half2float(a.bias[n]);
         if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
-        if (a.y_is_f32) static_cast<float*>(a.Y)[(size_t)j * a.ldy + n] = v;
-        else static_cast<__half*>(a.Y)[(size_t)j * a.ldy + n] = __float2half_rn(v);
+        if (a.y_is_f32) static_cast<float*>(a.Y)[(size_t)(j_base + j) * a.ldy + n] = v;
+        else static_cast<__half*>(a.Y)[(size_t)(j_base + j) * a.ldy + n] = __float2half_rn(v);
     }
 }
 
@@ -259,16 +264,22 @@ int launch_skinny_rows(const SkinnyArgs& a, cudaStream_t st) {
 // PIMB200_ERR_UNSUPPORTED when the shape is not this kernel's (the caller then takes the tensor-core or SIMT path)
 int launch_gemm_wx_skinny(const __half* W, const __half* X, const __half* bias, void* Y, int N, int K, int J, int ldx,
                           int ldy, int act, int y_is_f32, cudaStream_t st) {
-    if (J < 1 || J > kSkinnyMaxJ || K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
+    if (J < 1 || K % 8 != 0 || ldx % 8 != 0 || !aligned16(W) || !aligned16(X)) return PIMB200_ERR_UNSUPPORTED;
+    // More than 32 activation rows run as column blocks of 32 (grid.y) when the weight matrix is small: W then comes
+    // from L2 for all but the first block, and a matrix of a few 128-row tiles would leave most SMs of the tcgen05
+    // kernel's grid without work (a Transformer layer's 512 x 512 projections for 128 sequences: 4 tiles).
+    if (J > kSkinnyMaxJ && (J > kSkinnyMaxBlockedJ || N > kSkinnyMaxBlockedN || (size_t)N * K > kSkinnyMaxBlockedNK))
+        return PIMB200_ERR_UNSUPPORTED;
     SkinnyArgs a{W, X, bias, Y, N, K, J, ldx, ldy, act, y_is_f32};
-    const int nt = ceil_div(J, 8);
-    if (nt >= 2 && N >= 16384) {
+    const int nt = J > kSkinnyMaxJ ? 4 : ceil_div(J, 8);
+    const int jblocks = ceil_div(J, kSkinnyMaxJ);
+    if (nt >= 2 && N >= 16384 && jblocks == 1) {
         // a warp per row tile with X in shared memory, when the CTA's copy of X fits
         const int rc = nt == 2 ? launch_skinny_rows<2>(a, st) : nt == 3 ? launch_skinny_rows<3>(a, st) : launch_skinny_rows<4>(a, st);
         if (rc != PIMB200_ERR_UNSUPPORTED) return rc;
     }
     if (N >= 2048) {
-        const int grid = ceil_div(N, 2 * kSkinnyRows);
+        const dim3 grid(ceil_div(N, 2 * kSkinnyRows), jblocks);
         switch (nt) {
             case 1: gemm_skinny_kernel<1, 2><<<grid, kSkinnyThreads, 0, st>>>(a); break;
             case 2: gemm_skinny_kernel<2, 2><<<grid, kSkinnyThreads, 0, st>>>(a); break;
@@ -276,7 +287,7 @@ int launch_gemm_wx_skinny(const __half* W, const __half* X, const __half* bias, 
             default: gemm_skinny_kernel<4, 2><<<grid, kSkinnyThreads, 0, st>>>(a); break;
         }
     } else {
-        const int grid = ceil_div(N, kSkinnyRows);
+        const dim3 grid(ceil_div(N, kSkinnyRows), jblocks);
         switch (nt) {
             case 1: gemm_skinny_kernel<1, 1><<<grid, kSkinnyThreads, 0, st>>>(a); break;
             case 2: gemm_skinny_kernel<2, 1><<<grid, kSkinnyThreads, 0, st>>>(a); break;

@@ -251,14 +251,16 @@ __global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const __ha
                                                                       const __half* __restrict__ V, const long long* len_dev,
                                                                       long len_inc, long len_add, long max_len,
                                                                       __half* __restrict__ out, int hd, long kv_stride,
-                                                                      long seq_stride, float scale) {
+                                                                      long seq_stride, long q_stride, long out_stride,
+                                                                      float scale) {
     extern __shared__ float sc[];            // [max_len] scores, then [kAttnThreads / 32][hd] partial outputs
     __shared__ float red[kAttnThreads / 32];
     const int h = blockIdx.x, seq = blockIdx.y, heads = gridDim.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     long L = (len_dev ? (long)len_dev[(size_t)seq * len_inc] : 0) + len_add;
     L = L < 0 ? 0 : (L > max_len ? max_len : L);
-    const __half* qh = q + ((size_t)seq * heads + h) * hd;
+    (void)heads;
+    const __half* qh = q + (size_t)seq * q_stride + (size_t)h * hd;
     const __half* Ks = K + (size_t)seq * seq_stride + (size_t)h * hd;
     const __half* Vs = V + (size_t)seq * seq_stride + (size_t)h * hd;
     for (long t = warp; t < L; t += kAttnThreads / 32) {
@@ -291,7 +293,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const __ha
         float a = 0.f;
 #pragma unroll
         for (int w = 0; w < kAttnThreads / 32; ++w) a += part[w * hd + j];
-        out[((size_t)seq * heads + h) * hd + j] = __float2half_rn(a * inv);
+        out[(size_t)seq * out_stride + (size_t)h * hd + j] = __float2half_rn(a * inv);
     }
 }
 
@@ -394,6 +396,99 @@ __global__ void __launch_bounds__(kAddAttnSlice / 2) additive_context_kernel(
             for (long s = 0; s < L; ++s) a = fmaf(sc[s], __half2float(vals[(size_t)s * row_stride + e]), a);
             out[e] = __float2half_rn(a * inv);
         }
+    }
+}
+
+// y = layer_norm(x + r) per row: the residual connection and the normalisation behind every Transformer sub-layer in one
+// pass (the sum lives in shared memory as fp32; each thread re-reads only the entries it wrote).
+template <int T>
+__global__ void __launch_bounds__(T) add_layer_norm_rows_kernel(const __half* __restrict__ x, const __half* __restrict__ r,
+                                                                const __half* __restrict__ gamma, const __half* __restrict__ beta,
+                                                                __half* __restrict__ y, long cols, float eps) {
+    extern __shared__ float sum_row[];
+    __shared__ float red[T / 32];
+    const __half* xr = x + (size_t)blockIdx.x * cols;
+    const __half* rr = r + (size_t)blockIdx.x * cols;
+    __half* out = y + (size_t)blockIdx.x * cols;
+    float s = 0.f;
+    for (long c = threadIdx.x; c < cols; c += T) {
+        const float v = __half2float(xr[c]) + __half2float(rr[c]);
+        sum_row[c] = v;
+        s += v;
+    }
+    const float mean = block_sum<T>(s, red) / (float)cols;
+    float q = 0.f;
+    for (long c = threadIdx.x; c < cols; c += T) { const float d = sum_row[c] - mean; q += d * d; }
+    const float rstd = rsqrtf(block_sum<T>(q, red) / (float)cols + eps);
+    for (long c = threadIdx.x; c < cols; c += T) {
+        float v = (sum_row[c] - mean) * rstd;
+        if (gamma) v *= __half2float(gamma[c]);
+        if (beta) v += __half2float(beta[c]);
+        out[c] = __float2half_rn(v);
+    }
+}
+
+// Multi-head self-attention over every position of a batch of padded sequences (the encoder side of a Transformer):
+// one CTA per (head, sequence) holds the sequence's keys and values of that head in shared memory; a warp per query row
+// computes its scores (lanes along the keys), the softmax over the sequence's own length, and the weighted sum (lanes
+// along the head dimension).  Query rows past the length give zeros.
+constexpr int kBlockAttnThreads = 128;
+
+__global__ void __launch_bounds__(kBlockAttnThreads) attention_block_kernel(
+    const __half* __restrict__ Q, const __half* __restrict__ K, const __half* __restrict__ V,
+    const long long* __restrict__ lengths, __half* __restrict__ out, long max_len, int hd, long row_stride, long seq_stride,
+    long out_row_stride, long out_seq_stride, float scale) {
+    extern __shared__ __align__(16) unsigned char blk_smem[];
+    const int h = blockIdx.x, seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kp = hd + 2;                                   // padded key row (halves): lanes on different rows, different banks
+    __half* Ks = reinterpret_cast<__half*>(blk_smem);         // [max_len][kp]
+    __half* Vs = Ks + (size_t)max_len * kp;                   // [max_len][hd]
+    float* qs = reinterpret_cast<float*>(Vs + (size_t)max_len * hd);   // [warps][hd]
+    float* ps = qs + (kBlockAttnThreads / 32) * hd;           // [warps][max_len]
+    long L = lengths ? (long)lengths[seq] : max_len;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
+    const size_t base = (size_t)seq * seq_stride + (size_t)h * hd;
+    for (long i = threadIdx.x; i < L * hd; i += kBlockAttnThreads) {
+        const long s_ = i / hd;
+        const int c = (int)(i % hd);
+        Ks[s_ * kp + c] = K[base + (size_t)s_ * row_stride + c];
+        Vs[s_ * hd + c] = V[base + (size_t)s_ * row_stride + c];
+    }
+    __syncthreads();
+    float* qw = qs + warp * hd;
+    float* pw = ps + (size_t)warp * max_len;
+    for (long qi = warp; qi < max_len; qi += kBlockAttnThreads / 32) {
+        __half* o = out + (size_t)seq * out_seq_stride + (size_t)qi * out_row_stride + (size_t)h * hd;
+        if (qi >= L) {
+            for (int c = lane; c < hd; c += 32) o[c] = __float2half_rn(0.f);
+            continue;
+        }
+        for (int c = lane; c < hd; c += 32) qw[c] = __half2float(Q[base + (size_t)qi * row_stride + c]) * scale;
+        __syncwarp();
+        float m = -CUDART_INF_F;
+        for (long s_ = lane; s_ < L; s_ += 32) {
+            float a = 0.f;
+            for (int c = 0; c < hd; ++c) a = fmaf(qw[c], __half2float(Ks[s_ * kp + c]), a);
+            pw[s_] = a;
+            m = fmaxf(m, a);
+        }
+#pragma unroll
+        for (int o2 = 16; o2 > 0; o2 >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o2));
+        float sum = 0.f;
+        for (long s_ = lane; s_ < L; s_ += 32) {
+            const float e = expf(pw[s_] - m);
+            pw[s_] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        __syncwarp();
+        const float inv = 1.0f / sum;
+        for (int c = lane; c < hd; c += 32) {
+            float a = 0.f;
+            for (long s_ = 0; s_ < L; ++s_) a = fmaf(pw[s_], __half2float(Vs[s_ * hd + c]), a);
+            o[c] = __float2half_rn(a * inv);
+        }
+        __syncwarp();
     }
 }
 
@@ -525,17 +620,19 @@ extern "C" int pimb200_attention_row(const void* q, const void* K, const void* V
 
 extern "C" int pimb200_attention_rows(const void* q, const void* K, const void* V, const long long* len_dev, long len_inc,
                                       long len_add, long max_len, void* out, int n_seq, int heads, int head_dim,
-                                      long kv_stride, long seq_stride, float scale, void* stream) {
+                                      long kv_stride, long seq_stride, long q_stride, long out_stride, float scale,
+                                      void* stream) {
     if (n_seq == 0) return PIMB200_OK;
     if (!q || !K || !V || !out || n_seq < 0 || n_seq > 65535 || heads <= 0 || head_dim <= 0 || max_len <= 0 ||
-        kv_stride < (long)heads * head_dim || seq_stride < 0 || len_inc < 0)
+        kv_stride < (long)heads * head_dim || seq_stride < 0 || len_inc < 0 || q_stride < (long)heads * head_dim ||
+        out_stride < (long)heads * head_dim)
         return PIMB200_ERR_BAD_ARG;
     if (max_len > kAttnMaxLen || head_dim > 1024) return PIMB200_ERR_UNSUPPORTED;
     const size_t smem = ((size_t)max_len + (size_t)(kAttnThreads / 32) * head_dim) * sizeof(float);
     if (smem + 16 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
     attention_rows_kernel<<<dim3((unsigned)heads, (unsigned)n_seq), kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_inc, len_add,
-        max_len, static_cast<__half*>(out), head_dim, kv_stride, seq_stride, scale);
+        max_len, static_cast<__half*>(out), head_dim, kv_stride, seq_stride, q_stride, out_stride, scale);
     return launch_status();
 }
 
@@ -557,5 +654,32 @@ extern "C" int pimb200_additive_attention(const void* q, const void* keys_proj, 
                               (size_t)max_len * sizeof(float), st>>>(
         scores, static_cast<const __half*>(values), lengths, static_cast<__half*>(ctx), max_len, H, row_stride, seq_stride,
         ctx_stride);
+    return launch_status();
+}
+
+extern "C" int pimb200_add_layer_norm_rows(const void* x, const void* r, const void* gamma, const void* beta, void* y,
+                                           long rows, long cols, float eps, void* stream) {
+    if (rows == 0 || cols == 0) return PIMB200_OK;
+    if (!x || !r || !y || !rows_ok(rows, cols)) return PIMB200_ERR_BAD_ARG;
+    if ((size_t)cols * sizeof(float) + 64 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
+    add_layer_norm_rows_kernel<128><<<(unsigned)rows, 128, (size_t)cols * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<const __half*>(r), static_cast<const __half*>(gamma),
+        static_cast<const __half*>(beta), static_cast<__half*>(y), cols, eps);
+    return launch_status();
+}
+
+extern "C" int pimb200_attention_block(const void* q, const void* k, const void* v, const long long* lengths, void* out,
+                                       int n_seq, long max_len, int heads, int head_dim, long row_stride, long seq_stride,
+                                       long out_row_stride, long out_seq_stride, float scale, void* stream) {
+    if (n_seq == 0) return PIMB200_OK;
+    if (!q || !k || !v || !out || n_seq < 0 || n_seq > 65535 || heads <= 0 || head_dim <= 0 || max_len <= 0 ||
+        row_stride < (long)heads * head_dim || out_row_stride < (long)heads * head_dim || seq_stride < 0 || out_seq_stride < 0)
+        return PIMB200_ERR_BAD_ARG;
+    const size_t smem = (size_t)max_len * (head_dim + 2) * 2 + (size_t)max_len * head_dim * 2 +
+                        (size_t)(kBlockAttnThreads / 32) * (head_dim + max_len) * sizeof(float);
+    if (smem > 48 * 1024 || head_dim % 2 != 0) return PIMB200_ERR_UNSUPPORTED;
+    attention_block_kernel<<<dim3((unsigned)heads, (unsigned)n_seq), kBlockAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(q), static_cast<const __half*>(k), static_cast<const __half*>(v), lengths,
+        static_cast<__half*>(out), max_len, head_dim, row_stride, seq_stride, out_row_stride, out_seq_stride, scale);
     return launch_status();
 }

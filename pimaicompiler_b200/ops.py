@@ -37,6 +37,17 @@ def _req_half_cuda(*ts: Optional[torch.Tensor]) -> None:
             raise ValueError("expected a contiguous tensor")
 
 
+def _req_half_cuda_rows(*ts: Optional[torch.Tensor]) -> None:
+    """fp16 CUDA views whose last dimension is contiguous (rows may be strided: slices of a wider buffer)."""
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda or t.dtype != torch.float16:
+            raise TypeError("expected a CUDA fp16 tensor")
+        if t.dim() and t.stride(-1) != 1:
+            raise ValueError("expected a contiguous last dimension")
+
+
 def init(device: Optional[int] = None) -> None:
     """pimb200_init for ``device`` (default: the current device); idempotent."""
     dev = torch.cuda.current_device() if device is None else int(device)
@@ -95,8 +106,9 @@ def bmm_row(x: torch.Tensor, A: torch.Tensor, out: Optional[torch.Tensor] = None
 
 def gemm_wx(W: torch.Tensor, X: torch.Tensor, bias: Optional[torch.Tensor] = None, act: int = ACT_NONE,
             out_f32: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Y[J,N] = act(X[J,K] @ W[N,K]^T + bias)."""
-    _req_half_cuda(W, X, bias)
+    """Y[J,N] = act(X[J,K] @ W[N,K]^T + bias).  Rows of X and of `out` may be strided (column slices of wider buffers)."""
+    _req_half_cuda(W, bias)
+    _req_half_cuda_rows(X)
     N, K = W.shape
     J = X.shape[0]
     assert X.shape[1] == K and X.stride(1) == 1
@@ -235,19 +247,52 @@ def attention_row(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int,
 
 def attention_rows(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, heads: int, len_dev: Optional[torch.Tensor] = None,
                    len_inc: int = 0, len_add: int = 0, max_len: Optional[int] = None, scale: Optional[float] = None,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Single-query multi-head attention for n sequences in lock step: q [n, heads*hd]; K, V [n, S_max, heads*hd] (one
-    cache per sequence); lengths from the int64 device tensor `len_dev` (element j*len_inc for sequence j) plus len_add."""
-    _req_half_cuda(q, K, V)
+                   out: Optional[torch.Tensor] = None, time_major: bool = False) -> torch.Tensor:
+    """Single-query multi-head attention for n sequences in lock step: q [n, heads*hd] (rows may be strided); K, V
+    [n, S_max, heads*hd] views (one cache per sequence; [S_max, n, heads*hd] with time_major), last dimension contiguous;
+    lengths from the int64 device tensor `len_dev` (element j*len_inc for sequence j) plus len_add."""
+    _req_half_cuda_rows(q, K, V)
     n, d = q.shape
     hd = d // heads
-    S = K.shape[1] if max_len is None else max_len
+    seq_dim, t_dim = (1, 0) if time_major else (0, 1)
+    S = K.shape[t_dim] if max_len is None else max_len
+    if K.stride() != V.stride() or K.stride(2) != 1 or q.stride(1) != 1:
+        raise ValueError("K and V must share their strides; the last dimension must be contiguous")
     if out is None:
-        out = torch.empty_like(q)
+        out = torch.empty(n, d, dtype=torch.float16, device=q.device)
     check(_lib.lib().pimb200_attention_rows(_ptr(q), _ptr(K), _ptr(V), _ptr(len_dev), len_inc, len_add, S, _ptr(out), n,
-                                            heads, hd, K.stride(1), K.stride(0),
+                                            heads, hd, K.stride(t_dim), K.stride(seq_dim), q.stride(0), out.stride(0),
                                             scale if scale is not None else 1.0 / math.sqrt(hd), _stream()), "attention_rows")
     return out
+
+
+def attention_block(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, lengths: Optional[torch.Tensor],
+                    out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Self-attention over all positions of n padded sequences: q, k, v [n, S, heads*hd] views with equal strides (e.g.
+    column slices of one fused projection), lengths int64 [n] on the device."""
+    _req_half_cuda_rows(q, k, v)
+    n, S, d = q.shape
+    hd = d // heads
+    if not (q.stride() == k.stride() == v.stride()) or q.stride(2) != 1:
+        raise ValueError("q, k, v must share their strides; the last dimension must be contiguous")
+    if out is None:
+        out = torch.empty(n, S, d, dtype=torch.float16, device=q.device)
+    check(_lib.lib().pimb200_attention_block(_ptr(q), _ptr(k), _ptr(v), _ptr(lengths), _ptr(out), n, S, heads, hd,
+                                             q.stride(1), q.stride(0), out.stride(1), out.stride(0),
+                                             scale if scale is not None else 1.0 / math.sqrt(hd), _stream()), "attention_block")
+    return out
+
+
+def add_layer_norm(x: torch.Tensor, r: torch.Tensor, gamma: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
+                   eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """layer_norm(x + r) over the last dimension."""
+    _req_half_cuda(x, r, gamma, beta)
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    y = out if out is not None else torch.empty_like(x)
+    check(_lib.lib().pimb200_add_layer_norm_rows(_ptr(x), _ptr(r), _ptr(gamma), _ptr(beta), _ptr(y), rows, cols, float(eps),
+                                                 _stream()), "add_layer_norm_rows")
+    return y
 
 
 def additive_attention(q: torch.Tensor, keys_proj: torch.Tensor, values: torch.Tensor, lengths: Optional[torch.Tensor],
@@ -255,7 +300,8 @@ def additive_attention(q: torch.Tensor, keys_proj: torch.Tensor, values: torch.T
                        scores: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Normalised Bahdanau attention for n sentences: q [n, H]; keys_proj / values time-major [S, n, H] (contiguous);
     lengths int64 [n] on the device; v, bias [H].  `out` may be a column slice of a wider [n, *] buffer."""
-    _req_half_cuda(q, keys_proj, values, v, bias)
+    _req_half_cuda(q, v, bias)
+    _req_half_cuda_rows(keys_proj, values)
     S, n, H = keys_proj.shape
     if out is None:
         out = torch.empty(n, H, dtype=torch.float16, device=q.device)

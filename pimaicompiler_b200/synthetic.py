@@ -7,6 +7,7 @@ fp16-representable values, so the fp16 device path and the fp32 CPU oracle consu
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -153,3 +154,53 @@ def make_sentences(n: int, cfg: GnmtConfig, seed: int) -> List[torch.Tensor]:
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(cfg.min_len, cfg.max_len + 1, (n,), generator=g)
     return [torch.randint(4, cfg.vocab, (int(L),), generator=g) for L in lens]
+
+
+# ------------------------------------------------------------------------------------------------ Transformer (configuration C5)
+@dataclass
+class TransformerConfig:
+    """Transformer-base: 6 encoder + 6 decoder layers (post-norm, no affine parameters in the layer norms), model width
+    512, 8 heads, feed-forward width 2048, sinusoidal positions, greedy search with a key / value cache."""
+    vocab: int = 32000
+    d_model: int = 512
+    heads: int = 8
+    ffn: int = 2048
+    layers: int = 6
+    max_steps: int = 64
+    min_len: int = 16
+    max_len: int = 64
+    bos: int = 1
+    eos: int = 2
+
+
+def positional_table(n: int, d: int) -> torch.Tensor:
+    """Sinusoidal position encodings [n, d], fp16-representable."""
+    pos = torch.arange(n, dtype=torch.float32).unsqueeze(1)
+    inv = torch.exp(torch.arange(0, d, 2, dtype=torch.float32) * (-math.log(10000.0) / d))
+    pe = torch.zeros(n, d)
+    pe[:, 0::2] = torch.sin(pos * inv)
+    pe[:, 1::2] = torch.cos(pos * inv)
+    return pe.to(torch.float16).to(torch.float32)
+
+
+def make_transformer_weights(cfg: TransformerConfig, seed: int = 0, gain: float = 1.0, logit_gain: float = 1.0) -> dict:
+    g = torch.Generator().manual_seed(seed)
+    d, f, V = cfg.d_model, cfg.ffn, cfg.vocab
+
+    def lin(n_out, n_in, gn=gain):
+        return _u((n_out, n_in), n_in, g, gn), _u((n_out,), n_in, g, gn)
+
+    def layer(cross: bool):
+        L = {}
+        names = ("sq", "sk", "sv", "so") + (("cq", "ck", "cv", "co") if cross else ())
+        for name in names:
+            L[name], L[name + "_b"] = lin(d, d)
+        L["f1"], L["f1_b"] = lin(f, d)
+        L["f2"], L["f2_b"] = lin(d, f)
+        return L
+
+    return {"emb_src": (torch.randn(V, d, generator=g) * 0.3).half().float(),
+            "emb_tgt": (torch.randn(V, d, generator=g) * 0.3).half().float(),
+            "pe": positional_table(max(cfg.max_len, cfg.max_steps), d),
+            "enc": [layer(False) for _ in range(cfg.layers)], "dec": [layer(True) for _ in range(cfg.layers)],
+            "Wo": _u((V, d), d, g, logit_gain)}

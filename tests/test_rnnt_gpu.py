@@ -98,10 +98,10 @@ def test_rnnt_batch_of_utterances_matches_single():
     cfg = to.RnntConfig(feat_dim=24, enc_hidden=64, pred_hidden=32, joint_hidden=48, vocab=11, blank=10)
     w = to.make_rnnt_weights(cfg, seed=4, gain=2.0, logit_gain=6.0)
     dec = _decoder(cfg, w)
-    # more utterances than clusters fit on the device; 80 frames (40 after the time reduction), so that every
-    # projection has more than 32 rows at any batch and takes the same GEMM kernel (the few-row streaming kernel
-    # sums in another order)
-    n, T = 13, 80
+    # more utterances than clusters fit on the device; 600 frames (300 after the time reduction), so that every
+    # projection has more than 256 rows at any batch and takes the same GEMM kernel (the streaming kernels for few rows
+    # sum in another order)
+    n, T = 13, 600
     feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
     dec.set_greedy_multi(2)   # FMA lock-step kernel: same summation order as the one-utterance kernel
     toks, logits = dec.decode(feats, want_logits=True)
