@@ -521,14 +521,14 @@ class _Translate:
         from pimaicompiler_b200 import synthetic as syn
         self.kind = kind
         if kind == "c4":
-            self.total, self.metric, self.unit = 512, "gnmt_greedy_sentences_per_s", "sentences/s"
+            self.total, self.metric, self.unit, self.group = 512, "gnmt_greedy_sentences_per_s", "sentences/s", 512
             self.cfg = syn.GnmtConfig()
             self.make_weights = syn.make_gnmt_weights
             self.desc = ("C4: GNMT greedy translation (4+4 LSTM layers, hidden 1024, vocabulary 32320, normalised Bahdanau "
                          "attention), sentences of 20..50 tokens, 80 decode steps")
             self.l2 = "one step touches 160 MB of weights, more than the 126 MB L2"
         else:
-            self.total, self.metric, self.unit = 2048, "transformer_greedy_sequences_per_s", "sequences/s"
+            self.total, self.metric, self.unit, self.group = 2048, "transformer_greedy_sequences_per_s", "sequences/s", 2048
             self.cfg = syn.TransformerConfig()
             self.make_weights = syn.make_transformer_weights
             self.desc = ("C5: Transformer-base greedy translation (6+6 layers, width 512, 8 heads, feed-forward 2048, "
@@ -578,7 +578,7 @@ def run_reference_translate(args, rank, world):
     if rank != 0:
         return
     wl = _Translate(args.workload)
-    n = max(1, min(args.cpu_sample, 8))
+    n = max(1, min(args.cpu_sample, 8 if wl.kind == "c4" else 128))
     vals, secs, cores = [], 0.0, 1
     for k in range(args.steps):
         v, dt, cores = wl.cpu_throughput(n, 9000 + k)
@@ -589,7 +589,7 @@ def run_reference_translate(args, rank, world):
     line = {"impl": "reference", "metric": wl.metric, "value": value, "unit": wl.unit,
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": secs / max(args.steps, 1) * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": wl.config(total, min(args.group or 128, (total + args.gpus - 1) // args.gpus)), "sample_streams_per_step": n,
+            "config": wl.config(total, min(args.group or wl.group, (total + args.gpus - 1) // args.gpus)), "sample_streams_per_step": n,
             "cpu_baseline": {"value": value, "unit": wl.unit, "cores": cores, "kind": "port",
                              "sample": f"{n} streams per step, libtorch {torch.__version__} CPU fp32, {cores} threads"},
             "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -612,7 +612,7 @@ def run_translate(args, rank, world, local):
     total = args.streams_total or wl.total
     mine = syn.make_sentences(total, cfg, seed=11)[rank::world]
     S = len(mine)
-    group = min(args.group or 128, S)
+    group = min(args.group or wl.group, S)
     tr = wl.translator(w, group, dev)
     staged = tr.stage(mine)
     dev_groups = [(ids.to(dev), lens.to(dev)) for _, ids, lens in staged]
@@ -671,7 +671,7 @@ def run_translate(args, rank, world, local):
     achieved = step_bytes * n_steps / (decode_ms * 1e-3) / 1e9 if decode_ms > 0 else 0.0
     cpu = None
     if rank == 0 and not args.no_cpu_baseline:
-        n_cpu = max(1, min(args.cpu_sample, 8))
+        n_cpu = max(1, min(args.cpu_sample, 8 if wl.kind == "c4" else 128))
         v, dt, cores = wl.cpu_throughput(n_cpu, 9100)
         cpu = {"value": v, "unit": wl.unit, "cores": cores, "kind": "port",
                "sample": f"{n_cpu} synthetic streams of the same distribution, libtorch {torch.__version__} CPU fp32 "
@@ -714,7 +714,8 @@ def main():
     ap.add_argument("--streams-total", type=int, default=0,
                     help="streams of one step, sharded over the ranks (0 = the configuration's own: 1024 utterances for "
                          "c3, 512 sentences for c4, 2048 sequences for c5)")
-    ap.add_argument("--group", type=int, default=0, help="c4 / c5: sentences decoded in lock step per group (0 = 128)")
+    ap.add_argument("--group", type=int, default=0,
+                    help="c4 / c5: streams decoded in lock step per group (0 = the rank's whole shard, at most 512 / 2048)")
     ap.add_argument("--streams-per-gpu", type=int, default=0,
                     help="overrides --streams-total with a per-rank count (profiling runs on small cases)")
     ap.add_argument("--streams-per-call", type=int, default=0,

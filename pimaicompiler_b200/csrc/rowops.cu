@@ -297,6 +297,102 @@ __global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const __ha
     }
 }
 
+// The same batched single-query attention with a WARP per (head, sequence), for head widths of 64 or 128 and up to 128
+// cache rows: lanes along the cache rows for the scores (each lane reads whole 128- or 256-byte key rows, the query comes
+// from shared memory as a broadcast), warp shuffles for the softmax, lanes along the head dimension for the weighted sum
+// (one coalesced row of V per cache row, eight rows of loads in flight).  No block-wide barrier, nothing serial per row.
+constexpr int kWarpAttnWarps = 8;
+constexpr int kWarpAttnMaxLen = 128;
+
+template <int EPL>   // elements of the head dimension per lane: 2 (head_dim 64) or 4 (head_dim 128)
+__global__ void __launch_bounds__(kWarpAttnWarps * 32) attention_rows_warp_kernel(
+    const __half* __restrict__ q, const __half* __restrict__ K, const __half* __restrict__ V, const long long* len_dev,
+    long len_inc, long len_add, long max_len, __half* __restrict__ out, int heads, int n_seq, long kv_stride, long seq_stride,
+    long q_stride, long out_stride, float scale) {
+    constexpr int HD = EPL * 32;
+    constexpr int KPL = kWarpAttnMaxLen / 32;     // cache rows per lane
+    __shared__ __align__(16) float qs[kWarpAttnWarps][HD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long task = (long)blockIdx.x * kWarpAttnWarps + warp;   // head fastest: the heads of a sequence share cache lines
+    if (task >= (long)heads * n_seq) return;
+    const int h = (int)(task % heads), seq = (int)(task / heads);
+    long L = (len_dev ? (long)len_dev[(size_t)seq * len_inc] : 0) + len_add;
+    L = L < 0 ? 0 : (L > max_len ? max_len : L);
+    const __half* qh = q + (size_t)seq * q_stride + (size_t)h * HD;
+    const __half* Ks = K + (size_t)seq * seq_stride + (size_t)h * HD;
+    const __half* Vs = V + (size_t)seq * seq_stride + (size_t)h * HD;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qs[warp][lane * EPL + e] = __half2float(qh[lane * EPL + e]) * scale;
+    __syncwarp();
+    float sc[KPL];
+    float m = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+        const long t = lane + 32 * i;
+        sc[i] = -CUDART_INF_F;
+        if (t < L) {
+            const uint4* kr = reinterpret_cast<const uint4*>(Ks + (size_t)t * kv_stride);
+            float a = 0.f;
+#pragma unroll
+            for (int c = 0; c < HD / 8; ++c) {
+                float kf[8];
+                widen8(__ldg(kr + c), kf);
+                const float4 q0 = *reinterpret_cast<const float4*>(&qs[warp][c * 8]);
+                const float4 q1 = *reinterpret_cast<const float4*>(&qs[warp][c * 8 + 4]);
+                a = fmaf(q0.x, kf[0], a); a = fmaf(q0.y, kf[1], a); a = fmaf(q0.z, kf[2], a); a = fmaf(q0.w, kf[3], a);
+                a = fmaf(q1.x, kf[4], a); a = fmaf(q1.y, kf[5], a); a = fmaf(q1.z, kf[6], a); a = fmaf(q1.w, kf[7], a);
+            }
+            sc[i] = a;
+            m = fmaxf(m, a);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+        sc[i] = (lane + 32 * i < L) ? expf(sc[i] - m) : 0.f;
+        sum += sc[i];
+    }
+    sum = warp_sum(sum);
+    float acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+    const __half* vcol = Vs + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < KPL; ++i) {
+        if ((long)32 * i >= L) break;
+        const int rows = (int)min((long)32, L - 32 * i);
+        for (int t0 = 0; t0 < rows; t0 += 8) {
+            float vf[8][EPL];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const long t = 32 * i + min(t0 + u, rows - 1);       // the tail repeats the last row with weight 0
+                if (EPL == 2) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(vcol + (size_t)t * kv_stride));
+                    vf[u][0] = f.x; vf[u][1] = f.y;
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(vcol + (size_t)t * kv_stride);
+                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    vf[u][0] = f0.x; vf[u][1] = f0.y; vf[u][EPL - 2] = f1.x; vf[u][EPL - 1] = f1.y;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float p = __shfl_sync(0xffffffffu, sc[i], (t0 + u) & 31);
+                if (t0 + u >= rows) p = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[e] = fmaf(p, vf[u][e], acc[e]);
+            }
+        }
+    }
+    const float inv = L > 0 ? 1.0f / sum : 0.f;
+    __half* o = out + (size_t)seq * out_stride + (size_t)h * HD + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o[e] = __float2half_rn(acc[e] * inv);
+}
+
 // Additive (normalised Bahdanau) attention of a decode step:
 //     e[s]   = sum_h v[h] * tanh(keys_proj[s, h] + q[h] + bias[h]),  s < length
 //     ctx[h] = sum_s softmax(e)[s] * values[s, h]
@@ -628,6 +724,22 @@ extern "C" int pimb200_attention_rows(const void* q, const void* K, const void* 
         out_stride < (long)heads * head_dim)
         return PIMB200_ERR_BAD_ARG;
     if (max_len > kAttnMaxLen || head_dim > 1024) return PIMB200_ERR_UNSUPPORTED;
+    // a warp per (head, sequence) when the head width and the cache length allow it and every row is 16-byte aligned
+    const bool rows16 = aligned16(q) && aligned16(K) && aligned16(V) && kv_stride % 8 == 0 && seq_stride % 8 == 0 && q_stride % 8 == 0;
+    if ((head_dim == 64 || head_dim == 128) && max_len <= kWarpAttnMaxLen && rows16) {
+        const long tasks = (long)heads * n_seq;
+        const unsigned grid = (unsigned)((tasks + kWarpAttnWarps - 1) / kWarpAttnWarps);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (head_dim == 64)
+            attention_rows_warp_kernel<2><<<grid, kWarpAttnWarps * 32, 0, st>>>(
+                static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_inc,
+                len_add, max_len, static_cast<__half*>(out), heads, n_seq, kv_stride, seq_stride, q_stride, out_stride, scale);
+        else
+            attention_rows_warp_kernel<4><<<grid, kWarpAttnWarps * 32, 0, st>>>(
+                static_cast<const __half*>(q), static_cast<const __half*>(K), static_cast<const __half*>(V), len_dev, len_inc,
+                len_add, max_len, static_cast<__half*>(out), heads, n_seq, kv_stride, seq_stride, q_stride, out_stride, scale);
+        return launch_status();
+    }
     const size_t smem = ((size_t)max_len + (size_t)(kAttnThreads / 32) * head_dim) * sizeof(float);
     if (smem + 16 > 48 * 1024) return PIMB200_ERR_UNSUPPORTED;
     attention_rows_kernel<<<dim3((unsigned)heads, (unsigned)n_seq), kAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(

@@ -70,30 +70,47 @@ class GnmtTranslator:
 
     # ------------------------------------------------------------------------------------------------ encoder
     def encode(self, ids: torch.Tensor, lengths: torch.Tensor) -> int:
-        """ids [S_g, G] int64 (padded with any valid id), lengths [G] int64, both on the device.  Fills enc_out and
-        keys_proj; returns S_g."""
+        """ids [S_g, G] int64 (padded with any valid id), lengths [G] int64 in descending order, both on the device.
+        Fills enc_out and keys_proj; returns S_g.  The recurrences take up to 128 sequences in lock step, so a larger
+        group goes through the encoder in slices of 128 sentences (each padded to its own longest sentence only)."""
         H, G = self.H, self.G
         Sg = ids.shape[0]
-        n = Sg * G
         self.lengths.copy_(lengths)
-        x = ops.gather_rows(self.w["emb_src"], ids.reshape(-1)).view(Sg, G, H)
+        if G <= self.ENC_BATCH:
+            self._encode_slice(ids, lengths, self.enc_out[:Sg], Sg)
+        else:
+            host_len = lengths.tolist()
+            for j0 in range(0, G, self.ENC_BATCH):
+                j1 = min(j0 + self.ENC_BATCH, G)
+                Ss = max(1, int(host_len[j0]))                       # sorted: the slice's first sentence is its longest
+                tmp = torch.empty(Ss, j1 - j0, H, dtype=torch.float16, device=self.dev)
+                self._encode_slice(ids[:Ss, j0:j1].contiguous(), lengths[j0:j1].contiguous(), tmp, Ss)
+                self.enc_out[:Ss, j0:j1].copy_(tmp)
+        n = Sg * G
+        ops.gemm_wx(self.w["Wk"], self.enc_out[:Sg].view(n, H), out=self.keys_proj[:Sg].view(n, H))
+        return Sg
+
+    ENC_BATCH = 128
+
+    def _encode_slice(self, ids: torch.Tensor, lengths: torch.Tensor, out: torch.Tensor, Sg: int) -> None:
+        H = self.H
+        B = ids.shape[1]
+        n = Sg * B
+        x = ops.gather_rows(self.w["emb_src"], ids.reshape(-1)).view(Sg, B, H)
         # per-sentence reversal: row (t, j) <- row (len_j - 1 - t, j); past the sentence an out-of-range index (zero row)
         t = torch.arange(Sg, device=self.dev).view(Sg, 1)
-        src_t = lengths.view(1, G) - 1 - t
-        rev = torch.where(src_t >= 0, src_t * G + torch.arange(G, device=self.dev).view(1, G), torch.full_like(src_t, n)).reshape(-1)
-        x_rev = ops.gather_rows(x.view(n, H), rev).view(Sg, G, H)
+        src_t = lengths.view(1, B) - 1 - t
+        rev = torch.where(src_t >= 0, src_t * B + torch.arange(B, device=self.dev).view(1, B), torch.full_like(src_t, n)).reshape(-1)
+        x_rev = ops.gather_rows(x.view(n, H), rev).view(Sg, B, H)
         yf, _, _ = self.lstm["enc0_f"].forward(x)
         yr, _, _ = self.lstm["enc0_r"].forward(x_rev)
-        yb = ops.gather_rows(yr.view(n, H), rev).view(Sg, G, H)
+        yb = ops.gather_rows(yr.view(n, H), rev).view(Sg, B, H)
         y0 = ops.cat([yf, yb], 2)
         y1, _, _ = self.lstm["enc1"].forward(y0)
         y2, _, _ = self.lstm["enc2"].forward(y1)
         y2 = ops.add_f16(y2, y1)
         y3, _, _ = self.lstm["enc3"].forward(y2)
-        out = self.enc_out[:Sg]
         ops.add_f16(y3, y2, out=out)
-        ops.gemm_wx(self.w["Wk"], out.view(n, H), out=self.keys_proj[:Sg].view(n, H))
-        return Sg
 
     # ------------------------------------------------------------------------------------------------ decoder
     def _step(self, src: List[torch.Tensor], dst: List[torch.Tensor]) -> int:

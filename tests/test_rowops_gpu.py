@@ -138,7 +138,8 @@ def test_attention_row_matches_oracle(heads, hd, S, L):
     assert np.array_equal(got_dev, got)
 
 
-@pytest.mark.parametrize("n,heads,hd,S", [(5, 8, 64, 64), (3, 4, 16, 9), (33, 2, 40, 70)])
+@pytest.mark.parametrize("n,heads,hd,S", [(5, 8, 64, 64), (3, 4, 16, 9), (33, 2, 40, 70), (6, 4, 128, 100), (4, 8, 64, 128),
+                                         (130, 8, 64, 37)])
 def test_attention_rows_batched_matches_oracle(n, heads, hd, S):
     # lock-step decode of n sequences: one cache and one length per sequence (cross-attention over ragged sources), and a
     # shared device-side position (self-attention at step t)
