@@ -27,10 +27,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 T_FRAMES = 1000
-TRAFFIC_T1000 = 1.18e9   # bytes, lstm_persistent_wide_kernel<8>, T=1000, 64 sequences (ncu dram read+write)
+# dram__bytes_read.sum + dram__bytes_write.sum of one lstm_persistent_pipe_kernel<16,2,4> launch of 500 timesteps x 128
+# sequences (1.058 GB + 0.126 GB, the capture summarised under profiles/), per timestep: the fp32 gate pre-activations
+# read once and the fp16 outputs written once; traffic grows in proportion to the timesteps of a launch
+TRAFFIC_PER_TIMESTEP_128 = (1.058490e9 + 0.125801e9) / 500.0
 WORKLOAD = "C3: RNN-T greedy decode, 1000x240 frames per utterance, batch 1 per stream, 1024 streams"
 STREAMS_TOTAL = 1024
-TENSOR_PIPE_ACTIVE_PCT_NCU = None   # sm__pipe_tensor_cycles_active of the recurrence kernel, from profiles/ (set below)
+TENSOR_PIPE_ACTIVE_PCT_NCU = 43.3   # sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active, same capture
 
 
 def base_config(streams_total: int) -> dict:
@@ -324,10 +327,10 @@ def run_gpu(args, rank, world, local):
         "roofline": {"bound": "hbm", "kernel": RECURRENCE_KERNEL,
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src,
-                     # dram__bytes_read+write of one T=1000 launch from the committed ncu capture under profiles/
-                     # (fp32 gate pre-activations read once + fp16 outputs + one cold W_hh); that launch's algorithmic
-                     # bytes are 8.39e9
-                     "traffic": TRAFFIC_T1000,
+                     # DRAM bytes of an average launch, scaled from the committed ncu capture by its timesteps (a launch of
+                     # fewer than 128 sequences moves proportionally less; the capture is the 128-sequence case)
+                     "traffic": TRAFFIC_PER_TIMESTEP_128 * (eb / 128.0) * prof["bytes"] / max(prof["recurrences"], 1) /
+                                (4.0 * cfg.enc_hidden * cfg.enc_hidden * 2.0 * (2 if eb > 64 else 1)),
                      "launches": prof["recurrences"], "avg_launch_ms": prof["ms"] / max(prof["recurrences"], 1),
                      "us_per_timestep": prof["ms"] * 1e3 / max(prof["bytes"] / (4.0 * cfg.enc_hidden * cfg.enc_hidden * 2.0), 1.0),
                      "sequences_per_launch": eb,

@@ -71,9 +71,9 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
         wrow[m][1] = a.W + (size_t)min(n0 + m * 16 + g + 8, a.N - 1) * K + 8 * t;
     }
     const __half* xrow[NT];
-#pragma unroll
     const int j_base = blockIdx.y * kSkinnyMaxJ;               // this CTA's block of up to 32 activation rows
     const int j_rem = a.J - j_base;
+#pragma unroll
     for (int j = 0; j < NT; ++j) xrow[j] = a.X + (size_t)(j_base + min(j * 8 + g, j_rem - 1)) * a.ldx + 8 * t;
     float acc[MTW][NT][4];
 #pragma unroll
@@ -151,7 +151,13 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
 // W itself; here the CTA copies X into shared memory once (cp.async; odd rows stored with their 16-byte chunks swapped
 // across 64 bytes, so a quarter-warp's 128-bit reads - two rows x 64 bytes - fall in distinct banks) and its 8 warps
 // walk tiles of a persistent grid, two register buffers of W loads in flight per warp.
-template <int NT>
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+    uint4 r;
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+    return r;
+}
+
+template <int NT, bool FULL>   // FULL: K a multiple of 128 (no partial group of K blocks)
 __global__ void __launch_bounds__(kSkinnyThreads, 2) gemm_skinny_rows_kernel(SkinnyArgs a, int tiles) {
     constexpr int UB = 4;                                            // 32-wide K blocks per register buffer
     extern __shared__ __align__(16) unsigned char sk_smem[];
@@ -160,82 +166,87 @@ __global__ void __launch_bounds__(kSkinnyThreads, 2) gemm_skinny_rows_kernel(Ski
     const int K = a.K;                                               // K % 64 == 0 (checked by the launcher)
     const int xs = K * 2;                                            // bytes per X row, a multiple of 128
     const int blocks = K >> 5;
+    const int gpt = (blocks + UB - 1) / UB;                          // groups of K blocks per tile
     {
         const int chunks = K >> 3;                                   // 16-byte chunks per row
-        for (int i = threadIdx.x; i < NT * 8 * chunks; i += kSkinnyThreads) {
-            const int row = i / chunks, c = i % chunks;
-            unsigned char* dst = sk_smem + (size_t)row * xs + (c ^ ((row & 1) << 2)) * 16;
-            const __half* src = a.X + (size_t)min(row, a.J - 1) * a.ldx + c * 8;   // rows past J repeat the last one
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+        for (int row = warp; row < NT * 8; row += kSkinnyWarps) {
+            const __half* src = a.X + (size_t)min(row, a.J - 1) * a.ldx;   // rows past J repeat the last one
+            unsigned char* dst = sk_smem + (size_t)row * xs;
+            const int flip = (row & 1) << 2;
+            for (int c = lane; c < chunks; c += 32)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst + ((c ^ flip) << 4))),
+                             "l"(src + c * 8) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    // tile i of the launch belongs to CTA i % gridDim.x, warp (i / gridDim.x) % 8; a warp walks its tiles as one stream of
+    // (tile, group) pairs, so the loads of a tile's first group are in flight during the previous tile's last products
+    const int stride = kSkinnyWarps * gridDim.x;
     uint4 w0[UB][2], w1[UB][2];
-    const __half *p_lo = a.W, *p_hi = a.W;
-    auto load_group = [&](uint4 (&w)[UB][2], int b0) {
+    auto load_group = [&](uint4 (&w)[UB][2], int tile, int grp) {
+        if (tile >= tiles) return;                                   // warp-uniform
+        const int n0 = tile * kSkinnyRows;
+        const __half* p_lo = a.W + (size_t)min(n0 + g, a.N - 1) * K + 8 * t + grp * (UB * 32);   // rows past N repeat the last
+        const __half* p_hi = a.W + (size_t)min(n0 + g + 8, a.N - 1) * K + 8 * t + grp * (UB * 32);
 #pragma unroll
         for (int u = 0; u < UB; ++u)
-            if (b0 + u < blocks) {                                   // warp-uniform
-                w[u][0] = ldg_w(p_lo + (size_t)(b0 + u) * 32);
-                w[u][1] = ldg_w(p_hi + (size_t)(b0 + u) * 32);
+            if (FULL || grp * UB + u < blocks) {
+                w[u][0] = ldg_w(p_lo + u * 32);
+                w[u][1] = ldg_w(p_hi + u * 32);
             }
     };
     float acc[NT][4];
-    const unsigned char* xg = sk_smem + (size_t)g * xs;
-    const int sw = (g & 1) << 2;
-    auto multiply = [&](const uint4 (&w)[UB][2], int b0) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const uint32_t xaddr = (uint32_t)__cvta_generic_to_shared(sk_smem) + (uint32_t)(g * xs + t * 16);
+    const int s1 = g & 1;                                            // odd rows: 64-byte halves of a 128-byte pair swapped
+    auto step = [&](const uint4 (&w)[UB][2], int tile, int grp) {
 #pragma unroll
         for (int u = 0; u < UB; ++u)
-            if (b0 + u < blocks) {
+            if (FULL || grp * UB + u < blocks) {
+                const uint32_t xb = xaddr + (uint32_t)(((grp * UB + u) ^ s1) << 6);
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(xg + (size_t)j * 8 * xs + ((((b0 + u) << 2) + t) ^ sw) * 16);
+                    const uint4 xv = lds_v4(xb + (uint32_t)(j * 8 * xs));
                     mma16816(acc[j], w[u][0].x, w[u][1].x, w[u][0].y, w[u][1].y, xv.x, xv.y);
                     mma16816(acc[j], w[u][0].z, w[u][1].z, w[u][0].w, w[u][1].w, xv.z, xv.w);
                 }
             }
-    };
-    auto start_tile = [&](int tile) {
+        if (grp != gpt - 1) return;
+        // the tile is complete.  Accumulator layout: (row g, cols 2t, 2t+1), (row g+8, same cols) of each n-tile
         const int n0 = tile * kSkinnyRows;
-        p_lo = a.W + (size_t)min(n0 + g, a.N - 1) * K + 8 * t;       // rows past N repeat the last one (never stored)
-        p_hi = a.W + (size_t)min(n0 + g + 8, a.N - 1) * K + 8 * t;
-        load_group(w0, 0);
-    };
-    // tile i of the launch belongs to CTA i % gridDim.x, warp (i / gridDim.x) % 8.  The first tile's loads are issued
-    // before the wait for X; the barrier is reached by every warp, with or without a tile.
-    int tile = blockIdx.x + warp * gridDim.x;
-    if (tile < tiles) start_tile(tile);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    for (bool first = true; tile < tiles; tile += kSkinnyWarps * gridDim.x, first = false) {
-        const int n0 = tile * kSkinnyRows;
-        if (!first) start_tile(tile);
-#pragma unroll
-        for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-        for (int b0 = 0; b0 < blocks; b0 += 2 * UB) {
-            load_group(w1, b0 + UB);
-            multiply(w0, b0);
-            load_group(w0, b0 + 2 * UB);
-            multiply(w1, b0 + UB);
-        }
-        // accumulator layout: (row g, cols 2t, 2t+1), (row g+8, same cols) of each n-tile
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int n = n0 + g + 8 * h;
-            if (n >= a.N) continue;
-            const float bv = a.bias ? __half2float(a.bias[n]) : 0.f;
+            const float bv = (a.bias && n < a.N) ? __half2float(a.bias[n]) : 0.f;
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int col = j * 8 + 2 * t + e;
-                    if (col >= a.J) continue;
                     float v = acc[j][2 * h + e] + bv;
+                    acc[j][2 * h + e] = 0.f;
+                    if (n >= a.N || col >= a.J) continue;
                     if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
                     if (a.y_is_f32) static_cast<float*>(a.Y)[(size_t)col * a.ldy + n] = v;
                     else static_cast<__half*>(a.Y)[(size_t)col * a.ldy + n] = __float2half_rn(v);
                 }
         }
+    };
+    auto advance = [&](int& tile, int& grp) {
+        if (++grp == gpt) { grp = 0; tile += stride; }
+    };
+    int lt = blockIdx.x + warp * gridDim.x, lg = 0;                  // load cursor
+    int ct = lt, cg = 0;                                             // compute cursor
+    load_group(w0, lt, lg); advance(lt, lg);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                                 // reached by every warp, with or without a tile
+    while (ct < tiles) {
+        load_group(w1, lt, lg); advance(lt, lg);
+        step(w0, ct, cg); advance(ct, cg);
+        if (ct >= tiles) break;
+        load_group(w0, lt, lg); advance(lt, lg);
+        step(w1, ct, cg); advance(ct, cg);
     }
 }
 
@@ -248,7 +259,8 @@ int launch_skinny_rows(const SkinnyArgs& a, cudaStream_t st) {
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return PIMB200_ERR_UNSUPPORTED;
     if (!attr_set[dev]) {
-        if (cudaFuncSetAttribute(gemm_skinny_rows_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_skinny_rows_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_skinny_rows_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
             return PIMB200_ERR_LAUNCH;
         attr_set[dev] = true;
     }
@@ -256,7 +268,8 @@ int launch_skinny_rows(const SkinnyArgs& a, cudaStream_t st) {
     const int per_sm = smem <= 110 * 1024 ? 2 : 1;
     DeviceCtx* ctx = current_ctx();
     const int grid = min(ceil_div(tiles, kSkinnyWarps), (ctx ? ctx->sm_count : kNumSmB200) * per_sm);
-    gemm_skinny_rows_kernel<NT><<<grid, kSkinnyThreads, smem, st>>>(a, tiles);
+    if (a.K % 128 == 0) gemm_skinny_rows_kernel<NT, true><<<grid, kSkinnyThreads, smem, st>>>(a, tiles);
+    else gemm_skinny_rows_kernel<NT, false><<<grid, kSkinnyThreads, smem, st>>>(a, tiles);
     return launch_status();
 }
 }  // namespace
