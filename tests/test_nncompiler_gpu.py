@@ -184,3 +184,51 @@ def test_profiling_flag_writes_a_chrome_trace():
     names = [e["name"] for e in ev]
     assert any("lstm" in n for n in names) and sum("addmm" in n for n in names) == 2
     assert all(e["ph"] == "X" and e["dur"] >= 0 for e in ev)
+
+
+class MlpNet(torch.nn.Module):
+    """Row-wise independent: linear (tensor-core GEMM at 64 rows x 4096 outputs) + relu + linear."""
+
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(3)
+        self.fc = torch.nn.Linear(256, 4096)
+        self.fc2 = torch.nn.Linear(4096, 64)
+
+    def forward(self, x):
+        return self.fc2(torch.relu(self.fc(x)))
+
+
+def test_two_gpu_replicas_match_one_gpu():
+    # PipelineManager(..., gpu_num=2): one runtime per device on its own thread (the reference's thread-per-GPU replicas,
+    # examples/runtime/source/pipeline_manager.cpp:27-53), inputs chunked along dimension 0.  Every device sets its own
+    # kernel attributes and packs its own weights; the result must equal the one-GPU run bit for bit.
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mod = _module()
+    sm = torch.jit.freeze(torch.jit.script(MlpNet().half().eval()))
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(128, 256, generator=g).half()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "net.torchscript")
+        sm.save(path)
+        one = mod.PipelineManager(path, "", 1)
+        two = mod.PipelineManager(path, "", 2)
+        (ref,) = one.inferenceModel([x.cuda()])
+        mod.reset_fallback_count()
+        for _ in range(3):
+            (out,) = two.inferenceModel([x.cuda()])
+            assert out.shape == ref.shape
+            assert torch.equal(out.cpu(), ref.cpu())
+        assert mod.fallback_count() == 0
+        del one, two
+    add = AddNet()
+    pm2, sm_add = _compile(add)
+    a = torch.arange(12, dtype=torch.int64).view(4, 3)
+    b = torch.ones(4, 3, dtype=torch.int64)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "add.torchscript")
+        torch.jit.freeze(torch.jit.script(add.eval())).save(path)
+        two = mod.PipelineManager(path, "", 2)
+        (out,) = two.inferenceModel([a.cuda(), b.cuda()])
+        assert torch.equal(out.cpu(), sm_add(a, b))
