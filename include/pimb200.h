@@ -97,6 +97,20 @@ int pimb200_bmm_row(const void* x, const void* A, void* y, int k, int n, void* s
 int pimb200_gemm_wx(const void* W, const void* X, const void* bias, void* Y,
                     int N, int K, int J, int ldx, int ldy, int act, int y_is_f32, void* stream);
 
+/* n independent products of the form above in ONE launch when their shapes allow it (each with at most 32 activation
+ * rows, or at most 256 against a matrix of at most 2048 rows; up to 8 per launch, more are issued in launches of 8); any
+ * other mix is issued product by product on the same stream, so the call is always complete.  The fan-out of a
+ * MULTISTREAM node (runtime/source/executor/op_executor/stream_ops_executor.cpp:27-50: N addmm / matmul layers, one host
+ * thread and one stream each) as one grid: blockIdx.z is the branch. */
+typedef struct pimb200_gemm_problem {
+    const void* W;     /* [N, K] row-major */
+    const void* X;     /* [J, ldx >= K] */
+    const void* bias;  /* [N] or NULL */
+    void* Y;           /* [J, ldy >= N] fp16, or fp32 when y_is_f32 */
+    int N, K, J, ldx, ldy, act, y_is_f32;
+} pimb200_gemm_problem;
+int pimb200_gemm_wx_grouped(const pimb200_gemm_problem* problems, int n, void* stream);
+
 /* Status of the tensor-core GEMM's bounded waits on the current device (0, or PIMB200_ERR_TIMEOUT if one gave up
  * since the last call); synchronises the device.  pimb200_gemm_force_simt(1) routes every pimb200_gemm_wx call
  * (and the LSTM input projections) to the SIMT kernel, for A/B profiling.  No counterpart in the reference. */

@@ -21,6 +21,12 @@ LSTM_AUTO, LSTM_STREAMED, LSTM_PERSISTENT, LSTM_PERSISTENT_TAGGED = 0, 1, 2, 3
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 
 # name -> (restype, argtypes); must list every function declared in include/pimb200.h
+class GemmProblem(C.Structure):
+    """pimb200_gemm_problem of include/pimb200.h."""
+    _fields_ = [("W", C.c_void_p), ("X", C.c_void_p), ("bias", C.c_void_p), ("Y", C.c_void_p), ("N", C.c_int), ("K", C.c_int),
+                ("J", C.c_int), ("ldx", C.c_int), ("ldy", C.c_int), ("act", C.c_int), ("y_is_f32", C.c_int)]
+
+
 SIGNATURES = {
     "pimb200_status_string": (C.c_char_p, [_i]),
     "pimb200_init": (_i, [_i]),
@@ -41,6 +47,7 @@ SIGNATURES = {
     "pimb200_layer_norm_rows": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, C.c_float, _vp]),
     "pimb200_tanh_f16": (_i, [_vp, _vp, _sz, _vp]),
     "pimb200_attention_row": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, _vp, _i, _i, C.c_long, C.c_float, _vp]),
+    "pimb200_gemm_wx_grouped": (_i, [_vp, _i, _vp]),
     "pimb200_attention_rows": (_i, [_vp, _vp, _vp, _vp, C.c_long, C.c_long, C.c_long, _vp, _i, _i, _i, C.c_long, C.c_long,
                                     C.c_long, C.c_long, C.c_float, _vp]),
     "pimb200_attention_block": (_i, [_vp, _vp, _vp, _vp, _vp, _i, C.c_long, _i, _i, C.c_long, C.c_long, C.c_long, C.c_long,

@@ -88,3 +88,39 @@ extern "C" int pimb200_gemm_wx(const void* W, const void* X, const void* bias, v
                           static_cast<const __half*>(bias), Y, N, K, J, ldx, ldy, act, y_is_f32,
                           static_cast<cudaStream_t>(stream));
 }
+
+namespace pimb200 {
+int launch_gemm_wx_grouped(const GemmProblem* pr, int n, cudaStream_t st);
+}
+
+extern "C" int pimb200_gemm_wx_grouped(const pimb200_gemm_problem* problems, int n, void* stream) {
+    if (n == 0) return PIMB200_OK;
+    if (!problems || n < 0) return PIMB200_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int i = 0; i < n; ++i) {
+        const pimb200_gemm_problem& q = problems[i];
+        if (!q.W || !q.X || !q.Y || q.N <= 0 || q.K <= 0 || q.J <= 0 || q.ldx < q.K || q.ldy < q.N) return PIMB200_ERR_BAD_ARG;
+        if (q.act != PIMB200_ACT_NONE && q.act != PIMB200_ACT_RELU) return PIMB200_ERR_BAD_ARG;
+    }
+    // groups of up to 8 problems per launch; a group with a shape the few-row kernel does not take runs one by one
+    for (int i0 = 0; i0 < n; i0 += 8) {
+        const int m = n - i0 < 8 ? n - i0 : 8;
+        GemmProblem g[8];
+        for (int i = 0; i < m; ++i) {
+            const pimb200_gemm_problem& q = problems[i0 + i];
+            g[i] = GemmProblem{static_cast<const __half*>(q.W), static_cast<const __half*>(q.X), static_cast<const __half*>(q.bias),
+                               q.Y, q.N, q.K, q.J, q.ldx, q.ldy, q.act, q.y_is_f32};
+        }
+        int rc = launch_gemm_wx_grouped(g, m, st);
+        if (rc == PIMB200_ERR_UNSUPPORTED) {
+            for (int i = 0; i < m; ++i) {
+                rc = launch_gemm_wx(g[i].W, g[i].X, g[i].bias, g[i].Y, g[i].N, g[i].K, g[i].J, g[i].ldx, g[i].ldy, g[i].act,
+                                    g[i].y_is_f32, st);
+                if (rc != PIMB200_OK) return rc;
+            }
+        } else if (rc != PIMB200_OK) {
+            return rc;
+        }
+    }
+    return PIMB200_OK;
+}

@@ -29,6 +29,15 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// One product of a grouped launch: Y[J, N] = act(X[J, K] . W[N, K]^T + bias)
+struct GemmProblem {
+    const __half* W;
+    const __half* X;
+    const __half* bias;
+    void* Y;
+    int N, K, J, ldx, ldy, act, y_is_f32;
+};
+
 // Per-device scratch used by kernels that split one reduction across CTAs.
 struct DeviceCtx {
     bool ready = false;

@@ -151,6 +151,89 @@ __global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_kernel(SkinnyArgs 
 // W itself; here the CTA copies X into shared memory once (cp.async; odd rows stored with their 16-byte chunks swapped
 // across 64 bytes, so a quarter-warp's 128-bit reads - two rows x 64 bytes - fall in distinct banks) and its 8 warps
 // walk tiles of a persistent grid, two register buffers of W loads in flight per warp.
+// Several independent products in ONE launch (the branches of a MULTISTREAM node: a few activation rows against
+// different weight matrices): blockIdx.z selects the problem, blockIdx.y its block of 32 activation rows, blockIdx.x its
+// 16-row weight tile; CTAs past a problem's extent leave at once.  Same arithmetic as gemm_skinny_kernel<NT, 1>.
+constexpr int kGroupedMax = 8;
+struct GroupedArgs {
+    SkinnyArgs p[kGroupedMax];
+};
+
+template <int NT>
+__global__ void __launch_bounds__(kSkinnyThreads) gemm_skinny_grouped_kernel(const __grid_constant__ GroupedArgs ga) {
+    constexpr int KS = kSkinnyWarps;
+    constexpr int UB = 4;
+    __shared__ float part[KS][kSkinnyRows][NT * 8 + 1];
+    const SkinnyArgs& a = ga.p[blockIdx.z];
+    const int n0 = blockIdx.x * kSkinnyRows;
+    const int j_base = blockIdx.y * kSkinnyMaxJ;
+    if (n0 >= a.N || j_base >= a.J) return;                    // CTA-uniform
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int K = a.K;
+    const int blocks = (K + 31) >> 5;
+    const int per = (blocks + KS - 1) / KS;
+    const int b_lo = warp * per, b_hi = min(blocks, b_lo + per);
+    const __half* w_lo = a.W + (size_t)min(n0 + g, a.N - 1) * K + 8 * t;
+    const __half* w_hi = a.W + (size_t)min(n0 + g + 8, a.N - 1) * K + 8 * t;
+    const int j_rem = a.J - j_base;
+    const __half* xrow[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) xrow[j] = a.X + (size_t)(j_base + min(j * 8 + g, j_rem - 1)) * a.ldx + 8 * t;
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 wc[UB][2], xc[UB][NT], wn[UB][2], xn[UB][NT];
+    auto load_group = [&](uint4 (&w)[UB][2], uint4 (&x)[UB][NT], int b0) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+            const int b = b0 + u;
+            const bool in = b < b_hi && b * 32 + 8 * t < K;
+            w[u][0] = in ? ldg_w(w_lo + (size_t)b * 32) : zero;
+            w[u][1] = in ? ldg_w(w_hi + (size_t)b * 32) : zero;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) x[u][j] = in ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + (size_t)b * 32)) : zero;
+        }
+    };
+    auto multiply = [&](const uint4 (&w)[UB][2], const uint4 (&x)[UB][NT]) {
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                mma16816(acc[j], w[u][0].x, w[u][1].x, w[u][0].y, w[u][1].y, x[u][j].x, x[u][j].y);
+                mma16816(acc[j], w[u][0].z, w[u][1].z, w[u][0].w, w[u][1].w, x[u][j].z, x[u][j].w);
+            }
+    };
+    load_group(wc, xc, b_lo);
+    for (int b0 = b_lo; b0 < b_hi; b0 += 2 * UB) {
+        load_group(wn, xn, b0 + UB);
+        multiply(wc, xc);
+        load_group(wc, xc, b0 + 2 * UB);
+        multiply(wn, xn);
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        part[warp][g][j * 8 + 2 * t] = acc[j][0];
+        part[warp][g][j * 8 + 2 * t + 1] = acc[j][1];
+        part[warp][g + 8][j * 8 + 2 * t] = acc[j][2];
+        part[warp][g + 8][j * 8 + 2 * t + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kSkinnyRows * NT * 8; i += kSkinnyThreads) {
+        const int r = i % kSkinnyRows, j = i / kSkinnyRows;
+        const int n = n0 + r;
+        if (n >= a.N || j >= j_rem) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < KS; ++w) v += part[w][r][j];
+        if (a.bias) v += __half2float(a.bias[n]);
+        if (a.act == PIMB200_ACT_RELU) v = fmaxf(v, 0.f);
+        if (a.y_is_f32) static_cast<float*>(a.Y)[(size_t)(j_base + j) * a.ldy + n] = v;
+        else static_cast<__half*>(a.Y)[(size_t)(j_base + j) * a.ldy + n] = __float2half_rn(v);
+    }
+}
+
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
     uint4 r;
     asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
@@ -307,6 +390,33 @@ int launch_gemm_wx_skinny(const __half* W, const __half* X, const __half* bias, 
             case 3: gemm_skinny_kernel<3, 1><<<grid, kSkinnyThreads, 0, st>>>(a); break;
             default: gemm_skinny_kernel<4, 1><<<grid, kSkinnyThreads, 0, st>>>(a); break;
         }
+    }
+    return launch_status();
+}
+
+// Up to 8 problems in one launch; PIMB200_ERR_UNSUPPORTED when one of them is not a shape of the few-row kernels (the
+// caller then launches them one by one)
+int launch_gemm_wx_grouped(const GemmProblem* pr, int n, cudaStream_t st) {
+    if (n < 1 || n > kGroupedMax) return PIMB200_ERR_UNSUPPORTED;
+    GroupedArgs ga;
+    int max_tiles = 0, max_jb = 0, max_j = 0;
+    for (int i = 0; i < n; ++i) {
+        const GemmProblem& q = pr[i];
+        if (q.J < 1 || q.J > kSkinnyMaxBlockedJ || q.K % 8 != 0 || q.ldx % 8 != 0 || !aligned16(q.W) || !aligned16(q.X))
+            return PIMB200_ERR_UNSUPPORTED;
+        if (q.J > kSkinnyMaxJ && (q.N > kSkinnyMaxBlockedN || (size_t)q.N * q.K > kSkinnyMaxBlockedNK)) return PIMB200_ERR_UNSUPPORTED;
+        ga.p[i] = SkinnyArgs{q.W, q.X, q.bias, q.Y, q.N, q.K, q.J, q.ldx, q.ldy, q.act, q.y_is_f32};
+        max_tiles = max(max_tiles, ceil_div(q.N, kSkinnyRows));
+        max_jb = max(max_jb, ceil_div(q.J, kSkinnyMaxJ));
+        max_j = max(max_j, min(q.J, kSkinnyMaxJ));
+    }
+    for (int i = n; i < kGroupedMax; ++i) ga.p[i] = SkinnyArgs{nullptr, nullptr, nullptr, nullptr, 0, 0, 0, 0, 0, 0, 0};
+    const dim3 grid(max_tiles, max_jb, n);
+    switch (ceil_div(max_j, 8)) {
+        case 1: gemm_skinny_grouped_kernel<1><<<grid, kSkinnyThreads, 0, st>>>(ga); break;
+        case 2: gemm_skinny_grouped_kernel<2><<<grid, kSkinnyThreads, 0, st>>>(ga); break;
+        case 3: gemm_skinny_grouped_kernel<3><<<grid, kSkinnyThreads, 0, st>>>(ga); break;
+        default: gemm_skinny_grouped_kernel<4><<<grid, kSkinnyThreads, 0, st>>>(ga); break;
     }
     return launch_status();
 }

@@ -201,4 +201,6 @@ PYBIND11_MODULE(_pimb200_host, m) {
     m.def("fallback_count", &runtime::tensor_ops::fallbackCount,
           "how often an operator took the libtorch call instead of a device kernel of this library since the last reset");
     m.def("reset_fallback_count", &runtime::tensor_ops::resetFallbackCount);
+    m.def("grouped_launch_count", &runtime::tensor_ops::groupedLaunchCount,
+          "MULTISTREAM nodes issued as one grouped launch since the process started");
 }

@@ -222,8 +222,44 @@ void executeAtenLSTM2(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
 // queued on the main stream, the main stream waits for all of them, and the outputs are marked as used by the main
 // stream for the caching allocator.  The cursor then skips the copies of those layers that follow the node in the
 // flat list.  Events are kept by the executor and reused across calls.
+// When every branch is a matrix-class fp16 product (alpha = beta = 1) the node is ONE grouped launch on the main stream.
+static bool multiStreamGrouped(std::shared_ptr<ir::MultiStreamLayer>& ms, StreamExecutor& ex) {
+    std::vector<tensor_ops::MatmulBranch> branches;
+    for (auto sub : ms->getLayers()) {
+        const auto& in = sub->getInSTensorID();
+        tensor_ops::MatmulBranch br;
+        if (sub->getType() == ir::LayerType::ATENADDMM) {
+            auto addmm = std::static_pointer_cast<ir::AtenAddmmLayer>(sub);
+            if (addmm->beta != 1.0 || addmm->alpha != 1.0) return false;
+            br.relu = addmm->getActType() == "aten::relu";
+            br.bias = blobTensor(ex, in[0]);
+            br.mat1 = blobTensor(ex, in[1]);
+            br.mat2 = blobTensor(ex, in[2]);
+        } else if (sub->getType() == ir::LayerType::ATENMATMUL) {
+            br.mat1 = blobTensor(ex, in[0]);
+            br.mat2 = blobTensor(ex, in[1]);
+        } else {
+            return false;
+        }
+        branches.push_back(br);
+    }
+    auto cx = context(ex, ex.currentStream());
+    auto outs = tensor_ops::groupedMatmul(cx, branches);
+    if (outs.empty()) {
+        if (cx.status != 0) ex.setStatus(cx.status);
+        return false;
+    }
+    size_t i = 0;
+    for (auto sub : ms->getLayers()) publish(ex, cx, sub, outs[i++]);
+    return true;
+}
+
 void executeMultiStream(std::shared_ptr<ir::NNLayer>& layer, StreamExecutor& ex) {
     auto ms = std::static_pointer_cast<ir::MultiStreamLayer>(layer);
+    if (multiStreamGrouped(ms, ex)) {
+        ex.setCursor(ex.getCursor() + 1 + ms->getLayerNum());
+        return;
+    }
     const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
     at::cuda::CUDAEvent& fork = ex.event(0);
     fork.record(main);

@@ -96,6 +96,8 @@ at::Tensor fusedMatmul(OpContext& cx, at::Tensor L, at::Tensor R, const at::Tens
 }  // namespace
 
 long fallbackCount() { return g_fallbacks.load(std::memory_order_relaxed); }
+static std::atomic<long> g_grouped{0};
+long groupedLaunchCount() { return g_grouped.load(std::memory_order_relaxed); }
 void resetFallbackCount() { g_fallbacks.store(0, std::memory_order_relaxed); }
 
 std::vector<int64_t> pad4(at::IntArrayRef s) {
@@ -143,6 +145,56 @@ at::Tensor matmul(OpContext& cx, const at::Tensor& a, const at::Tensor& b) {
     if (out.defined() || cx.status != 0) return out;
     fellBack();
     return at::matmul(a, b);
+}
+
+std::vector<at::Tensor> groupedMatmul(OpContext& cx, const std::vector<MatmulBranch>& branches) {
+    const size_t n = branches.size();
+    if (n < 2) return {};
+    std::vector<pimb200_gemm_problem> pr(n);
+    std::vector<at::Tensor> keep, outs(n);          // operands made contiguous live until the launch is queued
+    std::vector<std::vector<int64_t>> shapes(n);
+    std::vector<bool> transposed(n, false);
+    const bool any_relu = branches[0].relu;
+    for (size_t i = 0; i < n; ++i) {
+        const MatmulBranch& br = branches[i];
+        const at::Tensor& L = br.mat1;
+        const at::Tensor& R = br.mat2;
+        if (br.relu != any_relu || !fastHalf(L) || !fastHalf(R) || L.dim() < 2 || R.dim() != 2) return {};
+        if (br.bias.defined() && (!fastHalf(br.bias) || br.bias.dim() != 1)) return {};
+        const int64_t K = L.size(-1), rowsL = L.numel() / K, colsR = R.size(1);
+        if (R.size(0) != K || rowsL < 2 || colsR < 2) return {};      // vector classes keep their own kernels
+        at::Tensor Lm = L.reshape({rowsL, K}).contiguous();
+        at::Tensor Rt = isTransposedKMajor(R) ? R.t() : R.t().contiguous();      // [colsR, K], K-major
+        keep.push_back(Lm);
+        keep.push_back(Rt);
+        auto sizes = L.sizes().vec();
+        sizes.back() = colsR;
+        shapes[i] = sizes;
+        pimb200_gemm_problem& q = pr[i];
+        q.act = br.relu ? PIMB200_ACT_RELU : PIMB200_ACT_NONE;
+        q.y_is_f32 = 0;
+        q.K = (int)K;
+        q.ldx = (int)K;
+        if (br.bias.defined()) {
+            if (br.bias.numel() != rowsL) return {};
+            at::Tensor b = br.bias.contiguous();
+            keep.push_back(b);
+            outs[i] = at::empty({colsR, rowsL}, L.options());         // Y^T[c, r]
+            transposed[i] = true;
+            q.W = Lm.data_ptr(); q.X = Rt.data_ptr(); q.bias = b.data_ptr(); q.Y = outs[i].data_ptr();
+            q.N = (int)rowsL; q.J = (int)colsR; q.ldy = (int)rowsL;
+        } else {
+            outs[i] = at::empty({rowsL, colsR}, L.options());
+            q.W = Rt.data_ptr(); q.X = Lm.data_ptr(); q.bias = nullptr; q.Y = outs[i].data_ptr();
+            q.N = (int)colsR; q.J = (int)rowsL; q.ldy = (int)colsR;
+        }
+    }
+    const int rc = pimb200_gemm_wx_grouped(pr.data(), (int)n, cx.stream);
+    cx.note(rc);
+    if (rc != PIMB200_OK) return {};
+    g_grouped.fetch_add(1, std::memory_order_relaxed);
+    for (size_t i = 0; i < n; ++i) outs[i] = (transposed[i] ? outs[i].t() : outs[i]).reshape(shapes[i]);
+    return outs;
 }
 
 at::Tensor linear(OpContext& cx, const at::Tensor& x, const at::Tensor& W, const at::Tensor& b) {

@@ -28,6 +28,8 @@ struct OpContext {
 // How often an operator fell back to the libtorch call since the last reset (process-wide).  Tests of hot shapes
 // assert that it stays zero.
 long fallbackCount();
+// MULTISTREAM nodes issued as one grouped launch since the process started (tests assert the path taken)
+long groupedLaunchCount();
 void resetFallbackCount();
 
 // shape classes of the reference's GEMM router (runtime/include/executor/utils/utils.h:30-36,
@@ -41,6 +43,15 @@ at::Tensor addmm(OpContext& cx, const at::Tensor& self, const at::Tensor& mat1, 
                  double alpha, bool relu);
 // out = a @ b   (customAtenMatmul, aten_ops.cpp:760-932)
 at::Tensor matmul(OpContext& cx, const at::Tensor& a, const at::Tensor& b);
+// The branches of a MULTISTREAM node (stream_ops_executor.cpp:27-50): independent addmm / matmul products.  All of them
+// in one grouped launch when every branch is a matrix-class fp16 product (bias indexed by the row of mat1, as in the
+// reference's MM branch); an empty vector otherwise (the caller then runs branch by branch on side streams).
+struct MatmulBranch {
+    at::Tensor bias;   // 1-D or undefined
+    at::Tensor mat1, mat2;
+    bool relu = false;
+};
+std::vector<at::Tensor> groupedMatmul(OpContext& cx, const std::vector<MatmulBranch>& branches);
 // out = x @ W^T + b   (atenLinear, aten_ops.cpp:304-307)
 at::Tensor linear(OpContext& cx, const at::Tensor& x, const at::Tensor& W, const at::Tensor& b);
 // out = a + alpha * b   (custom_add for fp16 same-shape / row-broadcast operands, aten_ops_executor.cpp:43-179)

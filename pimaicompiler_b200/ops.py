@@ -119,6 +119,24 @@ def gemm_wx(W: torch.Tensor, X: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
+def gemm_wx_grouped(problems: Sequence[tuple], act: int = ACT_NONE) -> list:
+    """[(W [N,K], X [J,K], bias or None), ...] -> [Y [J,N], ...]: independent products in one launch when their shapes allow
+    it (the branches of a MULTISTREAM node), else one launch each."""
+    n = len(problems)
+    arr = (_lib.GemmProblem * n)()
+    outs = []
+    for i, (W, X, b) in enumerate(problems):
+        _req_half_cuda(W, b)
+        _req_half_cuda_rows(X)
+        N, K = W.shape
+        J = X.shape[0]
+        Y = torch.empty(J, N, dtype=torch.float16, device=W.device)
+        outs.append(Y)
+        arr[i] = _lib.GemmProblem(W.data_ptr(), X.data_ptr(), _ptr(b), Y.data_ptr(), N, K, J, X.stride(0), N, act, 0)
+    check(_lib.lib().pimb200_gemm_wx_grouped(C.cast(arr, C.c_void_p), n, _stream()), "gemm_wx_grouped")
+    return outs
+
+
 def add_f16(A: torch.Tensor, B: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A + B, same shape, or B a single row broadcast over the rows of A."""
     _req_half_cuda(A, B)

@@ -297,10 +297,50 @@ void executeAtenLSTM2(Layer& layer, StreamExecutor& ex) {
 
 // MULTISTREAM (runtime/source/executor/op_executor/stream_ops_executor.cpp:27-50): the node's addmm / matmul layers
 // are independent; each runs with a side stream of libtorch's pool as the current stream (so its temporaries are
-// made on that stream), after the work already queued on the main stream; the main stream waits for all of them.  The
+// made on that stream), after the work already queued on the main stream; the main stream waits for all of them.  When
+// every branch is a matrix-class fp16 product the whole node is ONE grouped launch on the main stream instead.  The
 // cursor then skips the copies of those layers that follow the node in the flat list.
+// The branches as one grouped launch on the main stream when all of them are matrix-class fp16 products with alpha = beta
+// = 1; false when they are not (nothing has been launched then).
+static bool multiStreamGrouped(std::shared_ptr<ir::MultiStreamLayer>& ms, StreamExecutor& ex) {
+    std::vector<tensor_ops::MatmulBranch> branches;
+    for (auto sub : ms->getLayers()) {
+        auto in = sub->getInSTensorID();
+        tensor_ops::MatmulBranch br;
+        if (sub->getType() == ir::LayerType::ATENADDMM) {
+            auto addmm_layer = std::static_pointer_cast<ir::AtenAddmmLayer>(sub);
+            if (in.size() == 5 && (blob(ex, in[3]).toInt() != 1 || blob(ex, in[4]).toInt() != 1)) return false;
+            const std::string act = addmm_layer->get_act_type();
+            br.relu = act == "aten::relu" || act == "aten::max";
+            IValue self = blob(ex, in[0]);
+            if (!self.isNone()) br.bias = self.toTensor();
+            br.mat1 = blobTensor(ex, in[1]);
+            br.mat2 = blobTensor(ex, in[2]);
+        } else if (sub->getType() == ir::LayerType::ATENMATMUL) {
+            br.mat1 = blobTensor(ex, in[0]);
+            br.mat2 = blobTensor(ex, in[1]);
+        } else {
+            return false;
+        }
+        branches.push_back(br);
+    }
+    auto cx = context(ex);
+    auto outs = tensor_ops::groupedMatmul(cx, branches);
+    if (outs.empty()) {
+        if (cx.status != 0) ex.setStatus(cx.status);
+        return false;
+    }
+    size_t i = 0;
+    for (auto sub : ms->getLayers()) publish(ex, cx, sub, outs[i++]);
+    return true;
+}
+
 void executeMultiStream(Layer& layer, StreamExecutor& ex) {
     auto ms = std::static_pointer_cast<ir::MultiStreamLayer>(layer);
+    if (multiStreamGrouped(ms, ex)) {
+        ex.setCursor(layer->getID() + ms->getLayerNum() + 1);
+        return;
+    }
     const c10::cuda::CUDAStream main = c10::cuda::getCurrentCUDAStream();
     at::cuda::CUDAEvent& fork = ex.event(0);
     fork.record(main);

@@ -18,4 +18,5 @@ PYBIND11_MODULE(NNCompiler, m) {
         .def("setProfilePath", &PipelineManager::setProfilePath);
     m.def("fallback_count", &nn_compiler::runtime::tensor_ops::fallbackCount);
     m.def("reset_fallback_count", &nn_compiler::runtime::tensor_ops::resetFallbackCount);
+    m.def("grouped_launch_count", &nn_compiler::runtime::tensor_ops::groupedLaunchCount);
 }

@@ -202,3 +202,22 @@ def test_gemv_linearity_at_full_size():
     y2b = ops.gemv_mv(Wd, to_dev(resid)).float()
     assert_close(y12, (y1 + y2b).cpu(), 4e-3, 2e-3, "linearity")
     assert y2.shape == y1.shape
+
+
+def test_grouped_gemm_one_launch_for_independent_products():
+    # the branches of a MULTISTREAM node: four expert projections of 26 token rows (one launch), a mix with ragged sizes
+    # and a batch-1 product, and a group with a shape outside the few-row kernels (issued one by one by the same call)
+    ops = _ops()
+    cases = [[(1024, 512, 26)] * 4, [(37, 72, 5), (4096, 1024, 1), (300, 264, 31), (2048, 512, 130), (16, 8, 2)],
+             [(512, 256, 8), (4096, 2048, 400), (64, 64, 64)], [(256, 128, 3)] * 11]
+    for ci, shapes in enumerate(cases):
+        probs, refs = [], []
+        for k, (N, K, J) in enumerate(shapes):
+            W, b, X = _c2_inputs(N, K, J, seed=100 * ci + k)
+            probs.append((to_dev(W), to_dev(X), to_dev(b) if k % 2 == 0 else None))
+            refs.append(co.linear(W.numpy(), X.numpy(), b.numpy() if k % 2 == 0 else None, True))
+        outs = ops.gemm_wx_grouped(probs, ops.ACT_RELU)
+        for k, (Y, ref) in enumerate(zip(outs, refs)):
+            assert_close(Y, ref, GEMV_ATOL, GEMV_RTOL, f"grouped case {ci} problem {k} {shapes[k]}")
+    from pimaicompiler_b200 import _lib
+    assert _lib.lib().pimb200_gemm_last_status() == 0

@@ -286,6 +286,34 @@ def test_multistream_with_matrix_branches_and_transposed_views():
             assert_close(r.reshape(ref.shape), ref, 4e-3, 2e-3, "multistream branch with temporaries")
 
 
+def test_multistream_of_matrix_branches_is_one_grouped_launch():
+    # four expert projections of 26 token rows (the SwitchTransformer pattern the reference runs on four streams): every
+    # branch is a matrix-class product, so the node is one grouped launch; a biased branch indexes its bias by the row of
+    # mat1, as the reference's MM branch does
+    h = _host()
+    g = torch.Generator().manual_seed(23)
+    J, K, N = 26, 512, 1024
+    X = h16(torch.randn(J, K, generator=g))
+    Wts = [h16(torch.randn(K, N, generator=g) * 0.05) for _ in range(3)]
+    W4 = h16(torch.randn(N, K, generator=g) * 0.05)
+    b = h16(torch.randn(J, generator=g))
+    gr = h.Graph()
+    iX, ib, iW4 = gr.add_input(), gr.add_input(), gr.add_input()
+    iW = [gr.add_input() for _ in range(3)]
+    outs = gr.add_multistream([("matmul", [iX, iW[0]], ""), ("matmul", [iX, iW[1]], ""), ("addmm", [ib, iX, iW[2]], "none"),
+                               ("matmul", [iX, iW4], "")])
+    for o in outs:
+        gr.mark_output(o)
+    rt = h.NNRuntime(gr, "SwitchTransformer")
+    before = h.grouped_launch_count()
+    res = rt.inferenceModel([to_dev(X), to_dev(b), to_dev(W4).t()] + [to_dev(W) for W in Wts])
+    assert h.grouped_launch_count() == before + 1
+    refs = [X @ Wts[0], X @ Wts[1], X @ Wts[2] + b.view(-1, 1), X @ W4.t()]
+    for r, ref in zip(res, refs):
+        assert r.shape == ref.shape
+        assert_close(r, ref, 4e-3, 2e-3, "grouped multistream branch")
+
+
 def test_profiling_writes_a_chrome_trace_with_one_span_per_op():
     import json
     h = _host()
