@@ -618,13 +618,13 @@ def run_translate(args, rank, world, local):
     group = min(args.group or wl.group, S)
     tr = wl.translator(w, group, dev)
     staged = tr.stage(mine)
-    dev_groups = [(ids.to(dev), lens.to(dev)) for _, ids, lens in staged]
+    dev_groups = [tr.to_device(g_) for g_ in staged]
     out_tokens = torch.zeros(len(staged), cfg.max_steps, group, dtype=torch.int64, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
 
     def step_device(events=None):
-        for gi, (ids_d, lens_d) in enumerate(dev_groups):
-            tr.encode(ids_d, lens_d)
+        for gi, grp in enumerate(dev_groups):
+            tr.encode(grp)
             if events is not None:
                 events[gi][0].record()
             toks, _ = tr.decode(cfg.max_steps)
@@ -682,7 +682,7 @@ def run_translate(args, rank, world, local):
     barrier(world)
     if rank != 0:
         return
-    h2d = sum(int(ids.numel() + lens.numel()) * 8 for _, ids, lens in staged)
+    h2d = sum(tr.h2d_bytes(g_) for g_ in staged)
     line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 storage / f32 accumulate",

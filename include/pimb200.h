@@ -301,6 +301,12 @@ int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on);
  * 0 = chosen by batch size, the default).  Same results.  No counterpart in the reference. */
 int pimb200_lstm_set_pipe_group_size(pimb200_lstm* h, int seqs);
 
+/* Packed input (pimb200_lstm_forward_packed) of up to 128 sequences and H % 16 == 0 runs as a padded lock-step batch on
+ * the persistent recurrences (default, on = 1): the sequences are scattered into padded rows (the backward direction
+ * reversed sequence by sequence), the gate terms behind a sequence's end freeze its cell state, outputs are gathered
+ * back into packed rows.  on = 0 keeps the timestep-by-timestep streamed kernels (A/B and parity tests). */
+int pimb200_lstm_set_packed_lockstep(pimb200_lstm* h, int on);
+
 /* Shrinks (or restores) the iteration limit of the persistent kernel's bounded waits; used by the
  * fault-handling tests to see ERR_TIMEOUT quickly.  No counterpart in the reference, whose waits are
  * inside MIOpen. */

@@ -1732,6 +1732,16 @@ struct pimb200_lstm {
     size_t y_cap[2] = {0, 0};
     float* cstate = nullptr;
     size_t c_cap = 0;
+    // packed input on the lock-step kernels: lengths, packed row offsets, padded input copy, one direction's run output
+    int* pk_lens = nullptr;
+    size_t pk_lens_cap = 0;
+    long* pk_row0 = nullptr;
+    size_t pk_row0_cap = 0;
+    __half* pk_x = nullptr;
+    size_t pk_x_cap = 0;
+    __half* pk_run = nullptr;
+    size_t pk_run_cap = 0;
+    int packed_lockstep = 1;   // 0: packed input runs timestep by timestep on the streamed kernels
     uint4* xchg = nullptr;  // [kXchgCopies][2][kXchgWords]
     uint4* bulk_data = nullptr;      // batched variant: [2][n_cta][32] records
     uint32_t* bulk_flags = nullptr;  // [2][n_cta]
@@ -1779,6 +1789,10 @@ extern "C" int pimb200_lstm_destroy(pimb200_lstm* h) {
     for (auto p : h->w_hh) cudaFree(p);
     for (auto p : h->bias) cudaFree(p);
     cudaFree(h->G);
+    cudaFree(h->pk_lens);
+    cudaFree(h->pk_row0);
+    cudaFree(h->pk_x);
+    cudaFree(h->pk_run);
     cudaFree(h->ybuf[0]);
     cudaFree(h->ybuf[1]);
     cudaFree(h->cstate);
@@ -1903,6 +1917,12 @@ extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     h->bulk_wide = on < 0 ? 0 : (on > 3 ? 3 : on);
+    return PIMB200_OK;
+}
+// A/B switch: 0 runs packed input timestep by timestep on the streamed kernels, 1 (default) as a padded lock-step batch.
+extern "C" int pimb200_lstm_set_packed_lockstep(pimb200_lstm* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->packed_lockstep = on ? 1 : 0;
     return PIMB200_OK;
 }
 // Tuning switch of the pipelined kernel: sequences per independently advancing group (8, 16 or 32; 0 = by batch size).
@@ -2208,6 +2228,133 @@ static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool rev
     return launch_status();
 }
 
+// ---------------------------------------------------------------------------------------------
+// packed sequences on the lock-step recurrences
+//
+// A packed batch (sequences sorted by decreasing length, timestep t holds its first batch_sizes[t] sequences) runs as a
+// padded [T, B] batch through the same persistent kernels as padded input:
+//   * the input is scattered into padded time-major rows (zeros behind each sequence); the backward direction gets
+//     every sequence reversed on its own, so it too is a forward recurrence that starts at the sequence's first step
+//     with the caller's initial state, and its outputs are reversed back when they are stored;
+//   * behind a sequence's end the gate terms of its input and forget gates are set to -1e4 / +1e4: sigmoid gives exactly
+//     0 and 1, the cell state stays frozen, so the kernel's c_n is the state after the sequence's own last step;
+//     h_n is the output row of that step, picked up when the outputs are stored.
+// ---------------------------------------------------------------------------------------------
+struct PackedMeta {
+    const int* lens;       // [B] device
+    const long* row0;      // [T] device: first packed row of timestep t
+};
+
+// dst[t, b, :] (padded, row t*B+b, `w` halves) <- row (ts, b) of src, ts = reverse ? len_b-1-t : t; zeros for t >= len_b.
+// src is packed (row0[ts] + b) when src_packed, else padded (ts*B + b), rows src_ld halves apart.
+__global__ void lstm_to_padded_kernel(const __half* __restrict__ src, long src_ld, int src_packed, __half* __restrict__ dst,
+                                      PackedMeta m, int T, int B, int w, int reverse) {
+    const long row = blockIdx.x;
+    const int t = (int)(row / B), b = (int)(row % B);
+    const int len = m.lens[b];
+    __half* d = dst + row * (long)w;
+    if (t >= len) {
+        for (int c = threadIdx.x; c < w; c += blockDim.x) d[c] = __float2half_rn(0.f);
+        return;
+    }
+    const int ts = reverse ? len - 1 - t : t;
+    const __half* sp = src + (src_packed ? (m.row0[ts] + b) : ((long)ts * B + b)) * src_ld;
+    for (int c = threadIdx.x; c < w; c += blockDim.x) d[c] = sp[c];
+}
+
+// Behind each sequence's end: input gate off, forget gate on, the other two terms zero (packed gate order i, f, g, o).
+__global__ void lstm_freeze_gates_kernel(float* __restrict__ G, PackedMeta m, int T, int B, int H) {
+    const long row = blockIdx.x;
+    const int t = (int)(row / B), b = (int)(row % B);
+    if (t < m.lens[b]) return;
+    float4* g = reinterpret_cast<float4*>(G + row * 4L * H);
+    for (int u = threadIdx.x; u < H; u += blockDim.x) g[u] = make_float4(-1.0e4f, 1.0e4f, 0.f, 0.f);
+}
+
+// Stores the outputs of one direction's padded run (src [T, B, H], contiguous): row (t, b) of the run is timestep
+// ts = reverse ? len_b-1-t : t of sequence b.  Destination: packed rows (row0[ts] + b) or padded rows (ts*B + b), dst_ld
+// halves apart, at column offset col; padded destinations get zeros behind the sequence.  The run's row len_b-1 is h_n.
+__global__ void lstm_from_padded_kernel(const __half* __restrict__ src, __half* __restrict__ dst, long dst_ld, int dst_packed,
+                                        int col, __half* __restrict__ hn, PackedMeta m, int T, int B, int H, int reverse) {
+    const long row = blockIdx.x;
+    const int t = (int)(row / B), b = (int)(row % B);
+    const int len = m.lens[b];
+    if (t >= len) {
+        if (!dst_packed) {
+            __half* d = dst + ((long)t * B + b) * dst_ld + col;
+            for (int c = threadIdx.x; c < H; c += blockDim.x) d[c] = __float2half_rn(0.f);
+        }
+        return;
+    }
+    const int ts = reverse ? len - 1 - t : t;
+    const __half* sp = src + row * (long)H;
+    __half* d = dst + (dst_packed ? (m.row0[ts] + b) : ((long)ts * B + b)) * dst_ld + col;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) d[c] = sp[c];
+    if (hn && t == len - 1) {
+        __half* hp = hn + (long)b * H;
+        for (int c = threadIdx.x; c < H; c += blockDim.x) hp[c] = sp[c];
+    }
+}
+
+static int run_recurrence(pimb200_lstm* h, int ld, const SeqLayout& sq, bool reverse, const float* G, long g_tstride,
+                          long g_bstride, const __half* h0, const __half* c0, __half* y, long y_tstride,
+                          long y_bstride, __half* hn, __half* cn, cudaStream_t st);
+
+static int lstm_forward_packed_lockstep(pimb200_lstm* h, const __half* data, const SeqLayout& sq, const __half* h0,
+                                        const __half* c0, __half* y, __half* hn, __half* cn, cudaStream_t st) {
+    const int H = h->H, D = h->D, L = h->L, T = sq.T, B = sq.B;
+    const long prow = (long)T * B;
+    int rc;
+    // sequence lengths and packed row offsets, uploaded once per call
+    std::vector<int> lens(B, 0);
+    for (int t = 0; t < T; ++t)
+        for (int b = 0; b < (int)sq.batch_sizes[t]; ++b) lens[b] = t + 1;
+    if ((rc = grow(&h->pk_lens, &h->pk_lens_cap, (size_t)B)) != PIMB200_OK) return rc;
+    if ((rc = grow(&h->pk_row0, &h->pk_row0_cap, (size_t)T)) != PIMB200_OK) return rc;
+    PIMB200_CUDA_TRY(cudaMemcpyAsync(h->pk_lens, lens.data(), sizeof(int) * B, cudaMemcpyHostToDevice, st));
+    PIMB200_CUDA_TRY(cudaMemcpyAsync(h->pk_row0, sq.row0.data(), sizeof(long) * T, cudaMemcpyHostToDevice, st));
+    // (a copy from pageable host memory returns once the source has been staged, so the vectors may go out of scope)
+    const PackedMeta meta{h->pk_lens, h->pk_row0};
+    int max_in = h->I;
+    if (L > 1 && D * H > max_in) max_in = D * H;
+    if ((rc = grow(&h->pk_x, &h->pk_x_cap, (size_t)prow * max_in)) != PIMB200_OK) return rc;
+    if ((rc = grow(&h->pk_run, &h->pk_run_cap, (size_t)prow * H)) != PIMB200_OK) return rc;
+    if ((rc = grow(&h->G, &h->G_cap, (size_t)prow * 4 * H)) != PIMB200_OK) return rc;
+    if (L > 1 && (rc = grow(&h->ybuf[0], &h->y_cap[0], (size_t)prow * D * H)) != PIMB200_OK) return rc;
+    if (L > 2 && (rc = grow(&h->ybuf[1], &h->y_cap[1], (size_t)prow * D * H)) != PIMB200_OK) return rc;
+    SeqLayout padded;
+    padded.T = T; padded.B = B; padded.batch_sizes = nullptr;
+    const unsigned grid = (unsigned)prow;
+    for (int l = 0; l < L; ++l) {
+        const int Il = in_size(h, l);
+        const bool first = (l == 0), last = (l == L - 1);
+        const __half* Xin = first ? data : h->ybuf[(l - 1) & 1];      // packed rows (layer 0) or padded rows
+        __half* Yout = last ? y : h->ybuf[l & 1];
+        for (int d = 0; d < D; ++d) {
+            const int ld = l * D + d;
+            const __half* X = Xin;
+            if (first || d == 1) {   // padded (and, for the backward direction, per-sequence reversed) copy of the input
+                lstm_to_padded_kernel<<<grid, 128, 0, st>>>(Xin, Il, first ? 1 : 0, h->pk_x, meta, T, B, Il, d);
+                X = h->pk_x;
+            }
+            if ((rc = launch_gemm_wx(h->w_ih[ld], X, nullptr, h->G, 4 * H, Il, (int)prow, Il, 4 * H, PIMB200_ACT_NONE, 1, st)) !=
+                PIMB200_OK)
+                return rc;
+            lstm_freeze_gates_kernel<<<grid, 128, 0, st>>>(h->G, meta, T, B, H);
+            const __half* h0_ld = h0 ? h0 + (size_t)ld * B * H : nullptr;
+            const __half* c0_ld = c0 ? c0 + (size_t)ld * B * H : nullptr;
+            __half* cn_ld = cn ? cn + (size_t)ld * B * H : nullptr;
+            if ((rc = run_recurrence(h, ld, padded, false, h->G, (long)B * 4 * H, 4L * H, h0_ld, c0_ld, h->pk_run, (long)B * H,
+                                     (long)H, nullptr, cn_ld, st)) != PIMB200_OK)
+                return rc;
+            lstm_from_padded_kernel<<<grid, 128, 0, st>>>(h->pk_run, Yout, (long)D * H, last ? 1 : 0, d * H,
+                                                          hn ? hn + (size_t)ld * B * H : nullptr, meta, T, B, H, d);
+            if ((rc = launch_status()) != PIMB200_OK) return rc;
+        }
+    }
+    return PIMB200_OK;
+}
+
 static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& sq, const __half* h0,
                              const __half* c0, __half* y, __half* hn, __half* cn, int batch_first,
                              cudaStream_t st) {
@@ -2218,6 +2365,10 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
     if (packed) rows = sq.row0[T - 1] + (long)sq.batch_sizes[T - 1];
     else rows = (long)T * B;
     int rc;
+    // packed input of several steps: as a padded lock-step batch on the persistent recurrences (needs the 128-bit GEMM
+    // path for the padded rows; the streamed kernels below take every other case)
+    if (packed && h->packed_lockstep && h->variant != PIMB200_LSTM_STREAMED && T > 1 && H % 16 == 0 && B <= kPipeMaxB)
+        return lstm_forward_packed_lockstep(h, x, sq, h0, c0, y, hn, cn, st);
     // decode form: seq_len 1, every extent a multiple of 8 and 16-byte aligned -> one fused cell launch per layer
     bool cell = !packed && T == 1 && h->variant != PIMB200_LSTM_PERSISTENT && h->variant != PIMB200_LSTM_PERSISTENT_TAGGED &&
                 H % 8 == 0 && h->I % 8 == 0 && aligned16(x) && aligned16(y) && (!h0 || aligned16(h0));

@@ -6,10 +6,9 @@ projection a batch-1 addmm (runtime/source/executor/op_executor/aten_ops_executo
 inputs examples/runtime/source/pipeline_manager.cpp:143-151).  Sentences are independent, so a GPU that has to serve
 hundreds of them runs `group` sentences in lock step instead:
 
-  * encoder: the group's sentences, sorted by length and padded to the longest, go through each layer as ONE
-    [S, group, *] sequence on the persistent weight-stationary recurrence (the padding lies behind every sentence's last
-    token, so it never reaches a valid output); the backward direction of the first layer runs the same kernel on the
-    sentences reversed one by one (a row gather with per-sentence indices) and its outputs are gathered back;
+  * encoder: the group's sentences, sorted by length, go through each layer as packed batches of up to 128 sentences
+    (aten::lstm's packed overload, which the library runs as a padded lock-step batch on the persistent weight-stationary
+    recurrence, the backward direction of the first layer on the sentences reversed one by one);
   * decoder: one step for the whole group is 4 x (two streaming GEMMs over the group's rows + the gate kernel), one
     attention launch (a CTA per sentence, own source length), the vocabulary projection as a GEMM (the 66 MB matrix is
     read once per step for all sentences) and a row-wise arg max; two steps (state buffers alternate) are captured into
@@ -40,8 +39,8 @@ class GnmtTranslator:
 
         self.w = {k: ([put(t) for t in v] if isinstance(v, list) else put(v)) for k, v in weights.items()}
         self.v_norm = put(weights["att_v"] / weights["att_v"].norm() * float(weights["att_g"]))
-        self.lstm = {}
-        for name in ("enc0_f", "enc0_r", "enc1", "enc2", "enc3", "dec0", "dec1", "dec2", "dec3"):
+        self.lstm = {"enc0": ops.Lstm(self.w["enc0_f"] + self.w["enc0_r"], 1, True, H, H, True)}   # bidirectional first layer
+        for name in ("enc1", "enc2", "enc3", "dec0", "dec1", "dec2", "dec3"):
             p = self.w[name]
             self.lstm[name] = ops.Lstm(p, 1, False, p[0].shape[1], H, True)
         f16 = dict(dtype=torch.float16, device=self.dev)
@@ -69,48 +68,28 @@ class GnmtTranslator:
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------------------------------------ encoder
-    def encode(self, ids: torch.Tensor, lengths: torch.Tensor) -> int:
-        """ids [S_g, G] int64 (padded with any valid id), lengths [G] int64 in descending order, both on the device.
-        Fills enc_out and keys_proj; returns S_g.  The recurrences take up to 128 sequences in lock step, so a larger
-        group goes through the encoder in slices of 128 sentences (each padded to its own longest sentence only)."""
+    ENC_BATCH = 128          # sequences per packed aten::lstm call (the lock-step recurrences take up to 128)
+
+    def encode(self, group: dict) -> int:
+        """One staged group (see stage(); tensors on the device).  Every slice of up to 128 sentences goes through the
+        encoder as a PACKED batch (the aten::lstm overload the reference's GNMT graph uses for its encoder): rows of
+        padding never reach a GEMM or an add, and the library runs the packed batch on the lock-step recurrences.  The
+        encoder states are scattered into the padded time-major buffer the attention kernel reads.  Returns S_g."""
         H, G = self.H, self.G
-        Sg = ids.shape[0]
-        self.lengths.copy_(lengths)
-        if G <= self.ENC_BATCH:
-            self._encode_slice(ids, lengths, self.enc_out[:Sg], Sg)
-        else:
-            host_len = lengths.tolist()
-            for j0 in range(0, G, self.ENC_BATCH):
-                j1 = min(j0 + self.ENC_BATCH, G)
-                Ss = max(1, int(host_len[j0]))                       # sorted: the slice's first sentence is its longest
-                tmp = torch.empty(Ss, j1 - j0, H, dtype=torch.float16, device=self.dev)
-                self._encode_slice(ids[:Ss, j0:j1].contiguous(), lengths[j0:j1].contiguous(), tmp, Ss)
-                self.enc_out[:Ss, j0:j1].copy_(tmp)
+        Sg = group["S"]
+        self.lengths.copy_(group["lengths"])
+        flat = self.enc_out.view(-1, H)
+        for sl in group["slices"]:
+            x = ops.gather_rows(self.w["emb_src"], sl["ids"])                       # packed rows [sum of lengths, H]
+            y0, _, _ = self.lstm["enc0"].forward_packed(x, sl["batch_sizes"])       # [rows, 2H]
+            y1, _, _ = self.lstm["enc1"].forward_packed(y0, sl["batch_sizes"])
+            y2, _, _ = self.lstm["enc2"].forward_packed(y1, sl["batch_sizes"])
+            y2 = ops.add_f16(y2, y1)
+            y3, _, _ = self.lstm["enc3"].forward_packed(y2, sl["batch_sizes"])
+            ops.scatter_rows(flat, sl["dst"], ops.add_f16(y3, y2))                  # row (t, j) of the padded buffer
         n = Sg * G
         ops.gemm_wx(self.w["Wk"], self.enc_out[:Sg].view(n, H), out=self.keys_proj[:Sg].view(n, H))
         return Sg
-
-    ENC_BATCH = 128
-
-    def _encode_slice(self, ids: torch.Tensor, lengths: torch.Tensor, out: torch.Tensor, Sg: int) -> None:
-        H = self.H
-        B = ids.shape[1]
-        n = Sg * B
-        x = ops.gather_rows(self.w["emb_src"], ids.reshape(-1)).view(Sg, B, H)
-        # per-sentence reversal: row (t, j) <- row (len_j - 1 - t, j); past the sentence an out-of-range index (zero row)
-        t = torch.arange(Sg, device=self.dev).view(Sg, 1)
-        src_t = lengths.view(1, B) - 1 - t
-        rev = torch.where(src_t >= 0, src_t * B + torch.arange(B, device=self.dev).view(1, B), torch.full_like(src_t, n)).reshape(-1)
-        x_rev = ops.gather_rows(x.view(n, H), rev).view(Sg, B, H)
-        yf, _, _ = self.lstm["enc0_f"].forward(x)
-        yr, _, _ = self.lstm["enc0_r"].forward(x_rev)
-        yb = ops.gather_rows(yr.view(n, H), rev).view(Sg, B, H)
-        y0 = ops.cat([yf, yb], 2)
-        y1, _, _ = self.lstm["enc1"].forward(y0)
-        y2, _, _ = self.lstm["enc2"].forward(y1)
-        y2 = ops.add_f16(y2, y1)
-        y3, _, _ = self.lstm["enc3"].forward(y2)
-        ops.add_f16(y3, y2, out=out)
 
     # ------------------------------------------------------------------------------------------------ decoder
     def _step(self, src: List[torch.Tensor], dst: List[torch.Tensor]) -> int:
@@ -205,9 +184,11 @@ class GnmtTranslator:
 
     # ------------------------------------------------------------------------------------------------ user call
     def stage(self, sentences: Sequence[torch.Tensor]):
-        """Sorts the sentences by length and packs them into lock-step groups: a list of (sentence indices, padded ids
-        [S_g, G] int64, lengths [G] int64), the tensors in pinned host memory.  A ragged last group is filled with
-        one-token dummies."""
+        """Sorts the sentences by length and packs them into lock-step groups.  A group is a dict: `idx` (sentence
+        indices), `S` (longest sentence), `lengths` [G] int64, and `slices`: per 128 sentences the packed token ids
+        [sum of lengths] (timestep-major, as pack_padded_sequence orders them), `batch_sizes` (CPU int64, one per
+        timestep) and `dst`, the row t * G + j of the padded [S, G] buffer each packed row belongs to.  Tensors are in
+        pinned host memory; a ragged last group is filled with one-token dummies."""
         G = self.G
         order = sorted(range(len(sentences)), key=lambda i: -int(sentences[i].shape[0]))
         groups = []
@@ -216,18 +197,36 @@ class GnmtTranslator:
             lens = [int(sentences[i].shape[0]) for i in idx]
             if max(lens) > self.S or min(lens) < 1:
                 raise ValueError("sentence length outside 1..max_len")
-            ids = torch.full((max(lens), G), 4, dtype=torch.int64)
-            for j, i in enumerate(idx):
-                ids[:lens[j], j] = sentences[i]
-            lens_t = torch.ones(G, dtype=torch.int64)
-            lens_t[:len(idx)] = torch.tensor(lens, dtype=torch.int64)
-            groups.append((idx, ids.pin_memory(), lens_t.pin_memory()))
+            lens_all = lens + [1] * (G - len(idx))
+            toks = [sentences[i] for i in idx] + [torch.full((1,), 4, dtype=torch.int64)] * (G - len(idx))
+            slices = []
+            for j0 in range(0, G, self.ENC_BATCH):
+                j1 = min(j0 + self.ENC_BATCH, G)
+                sl_lens = lens_all[j0:j1]
+                nb, Ss = j1 - j0, sl_lens[0]
+                pad = torch.full((Ss, nb), 4, dtype=torch.int64)
+                for b in range(nb):
+                    pad[:sl_lens[b], b] = toks[j0 + b]
+                steps_col = torch.arange(Ss, dtype=torch.int64).view(Ss, 1)
+                mask = steps_col < torch.tensor(sl_lens, dtype=torch.int64).view(1, nb)      # [t, b]: sentence b has a step t
+                dst = (steps_col * G + j0 + torch.arange(nb, dtype=torch.int64).view(1, nb))[mask]
+                slices.append({"ids": pad[mask].pin_memory(), "dst": dst.pin_memory(), "batch_sizes": mask.sum(1)})
+            groups.append({"idx": idx, "S": max(lens_all), "lengths": torch.tensor(lens_all, dtype=torch.int64).pin_memory(),
+                           "slices": slices})
         return groups
 
-    def run_group(self, ids_dev: torch.Tensor, lens_dev: torch.Tensor, steps: int, forced: Optional[torch.Tensor] = None,
-                  want_logits: bool = False):
-        """Encoder + greedy decode of one staged group whose ids / lengths are already on the device."""
-        self.encode(ids_dev, lens_dev)
+    def to_device(self, group: dict) -> dict:
+        """The group's tensors copied to the device (batch_sizes stays on the host, as aten::lstm takes it)."""
+        mv = lambda t: t.to(self.dev, non_blocking=True)
+        return {"idx": group["idx"], "S": group["S"], "lengths": mv(group["lengths"]),
+                "slices": [{"ids": mv(sl["ids"]), "dst": mv(sl["dst"]), "batch_sizes": sl["batch_sizes"]} for sl in group["slices"]]}
+
+    def h2d_bytes(self, group: dict) -> int:
+        return 8 * (group["lengths"].numel() + sum(sl["ids"].numel() + sl["dst"].numel() for sl in group["slices"]))
+
+    def run_group(self, group_dev: dict, steps: int, forced: Optional[torch.Tensor] = None, want_logits: bool = False):
+        """Encoder + greedy decode of one staged group whose tensors are already on the device."""
+        self.encode(group_dev)
         return self.decode(steps, forced, want_logits)
 
     def translate(self, sentences: Sequence[torch.Tensor], steps: Optional[int] = None,
@@ -241,15 +240,14 @@ class GnmtTranslator:
         out_toks: List[Optional[List[int]]] = [None] * n
         out_logits: List[Optional[torch.Tensor]] = [None] * n
         pending = []
-        for idx, ids, lens in self.stage(sentences):
-            ids_d = ids.to(self.dev, non_blocking=True)
-            lens_d = lens.to(self.dev, non_blocking=True)
+        for group in self.stage(sentences):
+            idx = group["idx"]
             f = None
             if forced is not None:
                 f = torch.zeros(run_steps, G, dtype=torch.int64)
                 for j, i in enumerate(idx):
                     f[:, j] = torch.tensor(list(forced[i])[:run_steps], dtype=torch.int64)
-            toks, logits = self.run_group(ids_d, lens_d, run_steps, f, want_logits)
+            toks, logits = self.run_group(self.to_device(group), run_steps, f, want_logits)
             host = torch.empty(toks.shape, dtype=torch.int64).pin_memory()
             host.copy_(toks, non_blocking=True)
             pending.append((idx, host, logits.float().cpu() if want_logits else None))

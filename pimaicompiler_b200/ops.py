@@ -384,6 +384,9 @@ class Lstm:
     def last_status(self) -> int:
         return _lib.lib().pimb200_lstm_last_status(self._h)
 
+    def set_packed_lockstep(self, on: bool) -> None:
+        check(_lib.lib().pimb200_lstm_set_packed_lockstep(self._h, 1 if on else 0), "lstm_set_packed_lockstep")
+
     def forward(self, x: torch.Tensor, h0: Optional[torch.Tensor] = None, c0: Optional[torch.Tensor] = None,
                 batch_first: bool = False, out=None):
         _req_half_cuda(x, h0, c0)

@@ -70,13 +70,14 @@ class TransformerTranslator:
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------------------------------------ encoder
-    def encode(self, ids: torch.Tensor, lengths: torch.Tensor) -> None:
-        """ids [G, S_g] int64 (padded with any valid id), lengths [G] int64, on the device.  Fills the cross-attention
-        keys / values of every decoder layer."""
+    def encode(self, group: dict) -> None:
+        """One staged group (see stage(); tensors on the device): `ids` [G, S_g] int64 (padded with any valid id) and
+        `lengths` [G] int64.  Fills the cross-attention keys / values of every decoder layer."""
         cfg, d, G = self.cfg, self.d, self.G
+        ids = group["ids"]
         Sg = ids.shape[1]
         n = G * Sg
-        self.lengths.copy_(lengths)
+        self.lengths.copy_(group["lengths"])
         x = ops.gather_rows(self.emb_src, ids.reshape(-1))                       # [n, d]
         x = ops.add_f16(x.view(G, Sg * d), self.pe[:Sg].reshape(1, Sg * d)).view(n, d)   # positions: one row per sequence
         for L in self.enc:
@@ -149,7 +150,8 @@ class TransformerTranslator:
 
     # ------------------------------------------------------------------------------------------------ user call
     def stage(self, sequences: Sequence[torch.Tensor]):
-        """Sorts by length and packs lock-step groups: (indices, padded ids [G, S_g], lengths [G]) in pinned host memory."""
+        """Sorts by length and packs lock-step groups: dicts of `idx` (sequence indices), `ids` (padded [G, S_g]) and
+        `lengths` [G], the tensors in pinned host memory."""
         G = self.G
         order = sorted(range(len(sequences)), key=lambda i: -int(sequences[i].shape[0]))
         groups = []
@@ -163,8 +165,15 @@ class TransformerTranslator:
                 ids[j, :lens[j]] = sequences[i]
             lens_t = torch.ones(G, dtype=torch.int64)
             lens_t[:len(idx)] = torch.tensor(lens, dtype=torch.int64)
-            groups.append((idx, ids.pin_memory(), lens_t.pin_memory()))
+            groups.append({"idx": idx, "ids": ids.pin_memory(), "lengths": lens_t.pin_memory()})
         return groups
+
+    def to_device(self, group: dict) -> dict:
+        return {"idx": group["idx"], "ids": group["ids"].to(self.dev, non_blocking=True),
+                "lengths": group["lengths"].to(self.dev, non_blocking=True)}
+
+    def h2d_bytes(self, group: dict) -> int:
+        return 8 * (group["ids"].numel() + group["lengths"].numel())
 
     def translate(self, sequences: Sequence[torch.Tensor], steps: Optional[int] = None,
                   forced: Optional[Sequence[Sequence[int]]] = None, want_logits: bool = False):
@@ -176,8 +185,9 @@ class TransformerTranslator:
         out_toks: List[Optional[List[int]]] = [None] * n
         out_logits: List[Optional[torch.Tensor]] = [None] * n
         pending = []
-        for idx, ids, lens in self.stage(sequences):
-            self.encode(ids.to(self.dev, non_blocking=True), lens.to(self.dev, non_blocking=True))
+        for group in self.stage(sequences):
+            idx = group["idx"]
+            self.encode(self.to_device(group))
             f = None
             if forced is not None:
                 f = torch.zeros(run_steps, G, dtype=torch.int64)

@@ -310,3 +310,33 @@ def test_lstm_benchmark_shape_batched_vs_libtorch():
         assert_close(hn[:, n], hr[:, 0], CONTRACT_ATOL, CONTRACT_RTOL, f"h_n of sequence {n}")
         assert_close(cn[:, n], cr[:, 0], CONTRACT_ATOL, CONTRACT_RTOL, f"c_n of sequence {n}")
         print(f"sequence {n}: max err over 1000 steps {e:.2e}, at the last step {e_last:.2e}")
+
+
+@pytest.mark.parametrize("B,I,H,L,bi,lo,hi", [(7, 24, 64, 2, True, 1, 9), (40, 1024, 1024, 1, True, 20, 50), (128, 48, 128, 2, False, 3, 30),
+                                             (33, 40, 256, 3, True, 2, 12), (5, 16, 48, 1, False, 4, 4)])
+def test_lstm_packed_sequences_on_the_lockstep_kernels_vs_libtorch(B, I, H, L, bi, lo, hi):
+    # packed input (sequences of ragged length, sorted) runs as a padded lock-step batch on the persistent recurrences:
+    # outputs, h_n and c_n against libtorch's packed overload, and against the timestep-by-timestep streamed path
+    ops = _ops()
+    g = torch.Generator().manual_seed(B * 7 + H)
+    D = 2 if bi else 1
+    lens = sorted((int(v) for v in torch.randint(lo, hi + 1, (B,), generator=g)), reverse=True)
+    T = lens[0]
+    ps = lstm_params(L, D, I, H, g)
+    x = h16(torch.randn(T, B, I, generator=g))
+    h0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5)
+    c0 = h16(torch.randn(L * D, B, H, generator=g) * 0.5)
+    packed = torch.nn.utils.rnn.pack_padded_sequence(x, torch.tensor(lens), enforce_sorted=True)
+    with torch.backends.mkldnn.flags(enabled=False):
+        ry, rhn, rcn = torch.lstm(packed.data, packed.batch_sizes, [h0, c0], ps, True, L, 0.0, False, bi)
+    m = ops.Lstm([to_dev(p) for p in ps], L, bi, I, H, True)
+    y, hn, cn = m.forward_packed(to_dev(packed.data), packed.batch_sizes, to_dev(h0), to_dev(c0))
+    assert m.last_status() == 0
+    assert_close(y, ry, LSTM_ATOL, LSTM_RTOL, "packed y on the lock-step kernels")
+    assert_close(hn, rhn, LSTM_ATOL, LSTM_RTOL, "packed h_n")
+    assert_close(cn, rcn, LSTM_ATOL, LSTM_RTOL, "packed c_n")
+    m.set_packed_lockstep(False)
+    ys, hns, cns = m.forward_packed(to_dev(packed.data), packed.batch_sizes, to_dev(h0), to_dev(c0))
+    assert_close(ys, ry, LSTM_ATOL, LSTM_RTOL, "packed y, streamed")
+    assert_close(y, ys, LSTM_ATOL, LSTM_RTOL, "lock-step vs streamed")
+    assert_close(cn, cns, LSTM_ATOL, LSTM_RTOL, "lock-step vs streamed c_n")
