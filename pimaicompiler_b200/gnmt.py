@@ -229,6 +229,15 @@ class GnmtTranslator:
         self.encode(group_dev)
         return self.decode(steps, forced, want_logits)
 
+    def check_status(self) -> None:
+        """Raises if a bounded device-side wait of a recurrence or of the tensor-core GEMM gave up since the last check
+        (the launches that followed have run, but the results of the one that gave up are not valid)."""
+        from . import _lib
+        bad = [name for name, h in self.lstm.items() if h.last_status() != 0]
+        rc = _lib.lib().pimb200_gemm_last_status()
+        if bad or rc != 0:
+            raise RuntimeError(f"device-side wait timed out (recurrences: {bad}, gemm status {rc})")
+
     def translate(self, sentences: Sequence[torch.Tensor], steps: Optional[int] = None,
                   forced: Optional[Sequence[Sequence[int]]] = None, want_logits: bool = False):
         """sentences: 1-D int64 CPU tensors of source token ids.  Returns one token list per sentence (cut behind the
@@ -252,6 +261,7 @@ class GnmtTranslator:
             host.copy_(toks, non_blocking=True)
             pending.append((idx, host, logits.float().cpu() if want_logits else None))
             torch.cuda.current_stream(self.dev).synchronize()   # the next group reuses the token table
+            self.check_status()
         for idx, host, logits in pending:
             for j, i in enumerate(idx):
                 seq = host[:, j].tolist()

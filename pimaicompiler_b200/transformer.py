@@ -175,6 +175,13 @@ class TransformerTranslator:
     def h2d_bytes(self, group: dict) -> int:
         return 8 * (group["ids"].numel() + group["lengths"].numel())
 
+    def check_status(self) -> None:
+        """Raises if a bounded wait of the tensor-core GEMM gave up since the last check."""
+        from . import _lib
+        rc = _lib.lib().pimb200_gemm_last_status()
+        if rc != 0:
+            raise RuntimeError(f"device-side wait timed out (gemm status {rc})")
+
     def translate(self, sequences: Sequence[torch.Tensor], steps: Optional[int] = None,
                   forced: Optional[Sequence[Sequence[int]]] = None, want_logits: bool = False):
         """sequences: 1-D int64 CPU tensors of source token ids.  Returns one token list per sequence (cut behind the first
@@ -198,6 +205,7 @@ class TransformerTranslator:
             host.copy_(toks, non_blocking=True)
             pending.append((idx, host, logits.float().cpu() if want_logits else None))
             torch.cuda.current_stream(self.dev).synchronize()   # the next group reuses the token table
+            self.check_status()
         for idx, host, logits in pending:
             for j, i in enumerate(idx):
                 seq = host[:, j].tolist()
