@@ -28,7 +28,7 @@ using nn_compiler::ir::DataType;
 
 class ModelBuilder {
    public:
-    typedef std::unordered_map<int64_t, std::pair<DataType, torch::jit::IValue>> data_store_type;
+    using data_store_type = std::unordered_map<int64_t, std::pair<DataType, torch::jit::IValue>>;   // blob id -> (type, value)
 
     ModelBuilder() = default;
     ~ModelBuilder();
@@ -36,21 +36,22 @@ class ModelBuilder {
     RetVal preProcess(std::unique_ptr<nn_compiler::ir::NNModel>& model);
     RetVal preloadModel(std::unique_ptr<nn_compiler::ir::NNModel>& model);
 
-    std::pair<std::vector<int64_t>, std::vector<int64_t>> loadWeightAndBias(std::vector<at::Tensor> weight_data,
-                                                                            std::vector<at::Tensor> bias_data);
+    // moves the constants to the device, registers them as blobs; returns (weight blob ids, bias blob ids)
+    std::pair<std::vector<int64_t>, std::vector<int64_t>> loadWeightAndBias(const std::vector<at::Tensor>& weights,
+                                                                            const std::vector<at::Tensor>& biases);
     bool feasibleForLstmWeightProcess(std::shared_ptr<nn_compiler::ir::NNLayer>& layer);
     RetVal buildLstmParameterVector(std::shared_ptr<nn_compiler::ir::NNLayer>& layer);
     // the B200 counterpart of reArangeLstmWeights: one packed-weight handle per LSTM layer
     RetVal reArangeLstmWeights(std::shared_ptr<nn_compiler::ir::NNLayer>& layer);
 
-    data_store_type getPreLoadedData() { return preloaded_data_container_; }
+    data_store_type getPreLoadedData() { return preloaded_; }
     // packed-weight handle of an LSTM layer (NULL when the layer was not packed)
     pimb200_lstm* getLstmHandle(uint32_t layer_id) const;
     const std::map<uint32_t, pimb200_lstm*>& getLstmHandles() const { return lstm_handles_; }
 
    private:
-    int64_t preload_id_ = 0;
-    data_store_type preloaded_data_container_;
+    int64_t next_preload_id_ = 0;
+    data_store_type preloaded_;
     std::map<uint32_t, pimb200_lstm*> lstm_handles_;
 };
 

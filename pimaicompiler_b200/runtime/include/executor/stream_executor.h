@@ -54,18 +54,15 @@ class StreamExecutor {
     const std::shared_ptr<ir::NNGraph> getGraph();
     std::vector<torch::Tensor> iValueParser(torch::jit::IValue& iv);
 
-    void setCursor(int64_t cursor) { cursor_ = cursor; }
-    int64_t getCursor() const { return cursor_; }
+    void setCursor(int64_t cursor) { pc_ = cursor; }
+    int64_t getCursor() const { return pc_; }
 
-    void pushInLoopConditionStack(int64_t id) { loop_condition_stack_.push(id); }
-    int64_t getTopOfLoopConditionStack() { return loop_condition_stack_.top(); }
-    void popOfLoopConditionStack() { loop_condition_stack_.pop(); }
+    void pushInLoopConditionStack(int64_t id) { loop_conditions_.push(id); }
+    int64_t getTopOfLoopConditionStack() { return loop_conditions_.top(); }
+    void popOfLoopConditionStack() { loop_conditions_.pop(); }
 
-    void insertInRelationBlobIDsMap(int key, int value1, int value2) { releation_blob_ids_map_.insert({key, {value1, value2}}); }
-    std::pair<int, int> findInRelationBlobIDsMap(int key) { return releation_blob_ids_map_.at(key); }
-
-    void setModelType(const std::string& model_type) { model_type_ = model_type; }
-    const std::string& getModelType() const { return model_type_; }
+    void setModelType(const std::string& model_type) { family_ = model_type; }
+    const std::string& getModelType() const { return family_; }
 
     // ---- what replaces the reference's device-library members ----
     cudaStream_t currentStream() const;             // libtorch's current stream: every executor launches there
@@ -82,22 +79,21 @@ class StreamExecutor {
     RetVal run(const std::vector<torch::Tensor>& input_tensors, std::vector<torch::Tensor>& output_tensors, bool profiling);
     RetVal checkDeviceStatus();
 
-    std::shared_ptr<ir::NNGraph> graph_;
-    std::unordered_map<uint32_t, OpExecutorFn> op_executor_;
-    std::unordered_map<int, OpExecutorFn> aten_executor_map_;   // keyed by ir::LayerType
-    int64_t cursor_ = 0;  // the program counter
-    blob_store_type global_blobs_;
-    std::vector<int64_t> input_blob_ids_;
-    std::vector<int64_t> output_blob_ids_;
-    std::stack<int64_t> loop_condition_stack_;
-    std::unordered_map<int, std::pair<int, int>> releation_blob_ids_map_;
-    std::string model_type_ = "";
+    std::shared_ptr<ir::NNGraph> program_;
+    std::unordered_map<uint32_t, OpExecutorFn> dispatch_;
+    std::unordered_map<int, OpExecutorFn> by_type_;   // keyed by ir::LayerType
+    int64_t pc_ = 0;                                            // position of the layer being interpreted (control ops move it)
+    blob_store_type blobs_;
+    std::vector<int64_t> graph_inputs_;
+    std::vector<int64_t> graph_outputs_;
+    std::stack<int64_t> loop_conditions_;
+    std::string family_ = "";
     std::vector<c10::cuda::CUDAStream> streams_;
     std::vector<std::unique_ptr<at::cuda::CUDAEvent>> events_;
     std::map<uint32_t, pimb200_lstm*> lstm_handles_;
     int status_ = 0;
     std::string profile_path_ = "pimb200_profile.json";
-    static std::mutex stream_exec_mutex_;   // multi-GPU replicas: guards the copy of results to cuda:0
+    static std::mutex gather_mutex_;   // multi-GPU replicas: guards the copy of results to cuda:0
 };
 
 }  // namespace runtime

@@ -24,9 +24,9 @@ class NNRuntime {
     void setProfilePath(const std::string& path);
 
    private:
-    std::shared_ptr<ModelBuilder> mbuilder_ = nullptr;
-    std::shared_ptr<StreamExecutor> executor_ = nullptr;
-    std::string model_type_ = "";
+    std::shared_ptr<ModelBuilder> builder_ = nullptr;
+    std::shared_ptr<StreamExecutor> interpreter_ = nullptr;
+    std::string family_ = "";
     RetVal last_ = RetVal::SUCCESS;
 };
 

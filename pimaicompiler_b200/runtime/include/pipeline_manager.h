@@ -38,7 +38,7 @@ class PipelineManager {
     };
     void worker(Replica* r);
 
-    std::string input_file_path_, model_type_;
+    std::string input_file_path_, family_;
     bool is_profiling_ = false;
     std::shared_ptr<nn_compiler::ir::NNModel> compiled_;                 // shared, read-only after compile
     std::shared_ptr<nn_compiler::runtime::NNRuntime> runtime_;           // gpu_num == 1

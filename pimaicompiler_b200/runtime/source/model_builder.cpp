@@ -45,18 +45,18 @@ RetVal ModelBuilder::preProcess(std::unique_ptr<nn_compiler::ir::NNModel>& model
     // preloaded constants get blob ids above every STensor id of the graph
     auto graph = model->getGraphs()[0];
     for (auto layer : graph->getLayers())
-        for (auto id : layer->getOutSTensorID()) preload_id_ = std::max<int64_t>(preload_id_, id);
-    ++preload_id_;
+        for (auto id : layer->getOutSTensorID()) next_preload_id_ = std::max<int64_t>(next_preload_id_, id);
+    ++next_preload_id_;
     return RetVal::SUCCESS;
 }
 
-std::pair<std::vector<int64_t>, std::vector<int64_t>> ModelBuilder::loadWeightAndBias(std::vector<at::Tensor> weight_data,
-                                                                                      std::vector<at::Tensor> bias_data) {
+std::pair<std::vector<int64_t>, std::vector<int64_t>> ModelBuilder::loadWeightAndBias(const std::vector<at::Tensor>& weight_data,
+                                                                                      const std::vector<at::Tensor>& bias_data) {
     auto load = [&](const std::vector<at::Tensor>& src) {
         std::vector<int64_t> ids;
         for (const auto& t : src) {
-            const int64_t id = preload_id_++;
-            preloaded_data_container_.insert({id, {DataType::TENSOR, torch::jit::IValue(t.cuda())}});
+            const int64_t id = next_preload_id_++;
+            preloaded_.insert({id, {DataType::TENSOR, torch::jit::IValue(t.cuda())}});
             ids.push_back(id);
         }
         return ids;
@@ -148,7 +148,7 @@ RetVal ModelBuilder::buildLstmParameterVector(std::shared_ptr<nn_compiler::ir::N
         return RetVal::FAILURE;
     }
     std::vector<at::Tensor> params;
-    auto blob = [&](int64_t id) { return preloaded_data_container_.at(id).second.toTensor(); };
+    auto blob = [&](int64_t id) { return preloaded_.at(id).second.toTensor(); };
     for (int64_t i = 0; i < cells; ++i) {
         params.push_back(blob(v.weight_ids[2 * i]));
         params.push_back(blob(v.weight_ids[2 * i + 1]));

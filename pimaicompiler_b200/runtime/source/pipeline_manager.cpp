@@ -28,13 +28,13 @@ std::mutex g_build_mutex;   // replicas prepare their runtimes one at a time
 }  // namespace
 
 PipelineManager::PipelineManager(const std::string& input_file_path, std::string model_type, int gpu_num, bool profiling)
-    : input_file_path_(input_file_path), model_type_(std::move(model_type)), is_profiling_(profiling) {
+    : input_file_path_(input_file_path), family_(std::move(model_type)), is_profiling_(profiling) {
     auto model = std::make_unique<nn_compiler::ir::NNModel>();
     NNCompiler compiler;
-    compiler.initialize(input_file_path_, model_type_);
+    compiler.initialize(input_file_path_, family_);
     compiler.compile(model);
     if (gpu_num <= 1) {
-        runtime_ = std::make_shared<NNRuntime>(model, model_type_);
+        runtime_ = std::make_shared<NNRuntime>(model, family_);
         if (runtime_->lastResult() != RetVal::SUCCESS) throw std::runtime_error("NNRuntime: the model could not be prepared");
         compiled_ = std::move(model);
         return;
@@ -76,7 +76,7 @@ void PipelineManager::worker(Replica* r) {
         c10::cuda::CUDAGuard guard(r->device);
         std::lock_guard<std::mutex> build_lock(g_build_mutex);
         auto model = cloneForReplica(compiled_);
-        rt = std::make_shared<NNRuntime>(model, model_type_);
+        rt = std::make_shared<NNRuntime>(model, family_);
         if (rt->lastResult() != RetVal::SUCCESS) throw std::runtime_error("the model could not be prepared");
     } catch (const std::exception& e) {
         std::lock_guard<std::mutex> lk(r->mu);

@@ -12,10 +12,10 @@
 namespace nn_compiler {
 namespace runtime {
 
-std::mutex StreamExecutor::stream_exec_mutex_;
+std::mutex StreamExecutor::gather_mutex_;
 
 StreamExecutor::StreamExecutor(std::pair<std::shared_ptr<ir::NNGraph>, blob_store_type> model, std::string model_type)
-    : graph_(model.first), global_blobs_(std::move(model.second)), model_type_(std::move(model_type)) {
+    : program_(model.first), blobs_(std::move(model.second)), family_(std::move(model_type)) {
     registerOp();
 }
 
@@ -23,7 +23,7 @@ StreamExecutor::~StreamExecutor() = default;
 
 void StreamExecutor::registerOp() {
     using namespace op_executor;
-    auto reg = [&](ir::LayerType t, OpExecutorFn fn) { aten_executor_map_[(int)t] = std::move(fn); };
+    auto reg = [&](ir::LayerType t, OpExecutorFn fn) { by_type_[(int)t] = std::move(fn); };
     // hot path
     reg(ir::LayerType::ATENADD, executeAtenAdd);
     reg(ir::LayerType::ATENADDMM, executeAtenAddmm);
@@ -68,21 +68,21 @@ void StreamExecutor::registerOp() {
 }
 
 OpExecutorFn StreamExecutor::findAtenExecutorByType(ir::LayerType& op_type) {
-    auto it = aten_executor_map_.find((int)op_type);
-    return it == aten_executor_map_.end() ? OpExecutorFn() : it->second;
+    auto it = by_type_.find((int)op_type);
+    return it == by_type_.end() ? OpExecutorFn() : it->second;
 }
 
 OpExecutorFn StreamExecutor::getOpExecutor(uint32_t& id) {
-    auto it = op_executor_.find(id);
-    return it == op_executor_.end() ? OpExecutorFn() : it->second;
+    auto it = dispatch_.find(id);
+    return it == dispatch_.end() ? OpExecutorFn() : it->second;
 }
 
 RetVal StreamExecutor::preProcess() {
-    input_blob_ids_.clear();
-    output_blob_ids_.clear();
-    op_executor_.clear();
+    graph_inputs_.clear();
+    graph_outputs_.clear();
+    dispatch_.clear();
     // 1. one executor per layer id
-    for (auto layer : graph_->getLayers()) {
+    for (auto layer : program_->getLayers()) {
         auto type = layer->getType();
         if (type == ir::LayerType::PRIMINPUT || type == ir::LayerType::PRIMOUTPUT) continue;
         auto fn = findAtenExecutorByType(type);
@@ -91,37 +91,37 @@ RetVal StreamExecutor::preProcess() {
                        << "): this runtime covers the recurrent / decode hot path and the control ops around it";
             return RetVal::FAILURE;
         }
-        op_executor_.insert({layer->getID(), fn});
+        dispatch_.insert({layer->getID(), fn});
     }
     // 2. graph inputs / outputs, constants (materialised once and reused by every run), GNMT's pre-allocated cat buffers
     //    (stream_executor.cpp:80-92 of the reference; sizes follow the labelled layers' operands instead of constants)
     int custom_cat_mem_id = 0;
-    for (auto layer : graph_->getLayers()) {
+    for (auto layer : program_->getLayers()) {
         const auto type = layer->getType();
-        if (model_type_ == "GNMT" && type == ir::LayerType::ATENLSTM1)
+        if (family_ == "GNMT" && type == ir::LayerType::ATENLSTM1)
             custom_cat_mem_id = std::static_pointer_cast<ir::AtenLSTM1Layer>(layer)->getCustomCatMemId();
-        if (model_type_ == "GNMT" && type == ir::LayerType::ATENCAT) {
+        if (family_ == "GNMT" && type == ir::LayerType::ATENCAT) {
             auto cat_layer = std::static_pointer_cast<ir::AtenCatLayer>(layer);
             auto options = at::TensorOptions().dtype(at::kHalf).device(at::kCUDA);
             const int64_t mem_blob_id = cat_layer->getMemLayerId();
             if (mem_blob_id != -1) {
-                global_blobs_.insert({mem_blob_id, {ir::DataType::TENSOR, torch::jit::IValue(at::zeros({1, 1, 2048}, options))}});
+                blobs_.insert({mem_blob_id, {ir::DataType::TENSOR, torch::jit::IValue(at::zeros({1, 1, 2048}, options))}});
             } else {
                 cat_layer->setMemLayerId(custom_cat_mem_id);
-                global_blobs_.insert({custom_cat_mem_id, {ir::DataType::TENSOR, torch::jit::IValue(at::zeros({8, 1, 1024}, options))}});
+                blobs_.insert({custom_cat_mem_id, {ir::DataType::TENSOR, torch::jit::IValue(at::zeros({8, 1, 1024}, options))}});
             }
         }
         if (type == ir::LayerType::PRIMINPUT) {
-            input_blob_ids_.push_back(layer->getOutSTensorID()[0]);
+            graph_inputs_.push_back(layer->getOutSTensorID()[0]);
         } else if (type == ir::LayerType::PRIMOUTPUT) {
-            output_blob_ids_.push_back(layer->getInSTensorID()[0]);
+            graph_outputs_.push_back(layer->getInSTensorID()[0]);
         } else if (type == ir::LayerType::PRIMCONSTANT) {
             op_executor::executePrimConstant(layer, *this);
         } else if (type == ir::LayerType::PRIMVARIABLE) {
             if (std::static_pointer_cast<ir::PrimVariableLayer>(layer)->getIsConstant()) op_executor::executePrimVariable(layer, *this);
         }
     }
-    if (input_blob_ids_.empty() || output_blob_ids_.empty()) {
+    if (graph_inputs_.empty() || graph_outputs_.empty()) {
         LOG(ERROR) << "the graph needs at least one input and one output";
         return RetVal::FAILURE;
     }
@@ -129,18 +129,18 @@ RetVal StreamExecutor::preProcess() {
 }
 
 void StreamExecutor::updateBlob(int64_t blob_id, ir::DataType dtype, const torch::jit::IValue& iv) {
-    global_blobs_[blob_id] = std::make_pair(dtype, iv);
+    blobs_[blob_id] = std::make_pair(dtype, iv);
 }
 
 std::pair<ir::DataType, torch::jit::IValue>& StreamExecutor::findBlob(int64_t blob_id) {
-    auto it = global_blobs_.find(blob_id);
-    TORCH_CHECK(it != global_blobs_.end(), "blob ", blob_id, " has not been produced");
+    auto it = blobs_.find(blob_id);
+    TORCH_CHECK(it != blobs_.end(), "blob ", blob_id, " has not been produced");
     return it->second;
 }
 
-bool StreamExecutor::checkValidBlobID(int64_t blob_id) { return global_blobs_.find(blob_id) != global_blobs_.end(); }
+bool StreamExecutor::checkValidBlobID(int64_t blob_id) { return blobs_.find(blob_id) != blobs_.end(); }
 
-const std::shared_ptr<ir::NNGraph> StreamExecutor::getGraph() { return graph_; }
+const std::shared_ptr<ir::NNGraph> StreamExecutor::getGraph() { return program_; }
 
 cudaStream_t StreamExecutor::currentStream() const { return at::cuda::getCurrentCUDAStream().stream(); }
 
@@ -160,9 +160,9 @@ pimb200_lstm* StreamExecutor::lstmHandle(uint32_t layer_id) const {
 }
 
 void StreamExecutor::setInputTensors(const std::vector<torch::Tensor>& input_tensors) {
-    TORCH_CHECK(input_tensors.size() == input_blob_ids_.size(), "the graph takes ", input_blob_ids_.size(), " inputs, ",
+    TORCH_CHECK(input_tensors.size() == graph_inputs_.size(), "the graph takes ", graph_inputs_.size(), " inputs, ",
                 input_tensors.size(), " were given");
-    for (size_t k = 0; k < input_tensors.size(); ++k) updateBlob(input_blob_ids_[k], ir::DataType::TENSOR, torch::jit::IValue(input_tensors[k]));
+    for (size_t k = 0; k < input_tensors.size(); ++k) updateBlob(graph_inputs_[k], ir::DataType::TENSOR, torch::jit::IValue(input_tensors[k]));
 }
 
 // tensors of an output value, depth first: tensors as they are, runs of ints as one int64 row, tuples / lists unpacked
@@ -199,10 +199,10 @@ std::vector<torch::Tensor> StreamExecutor::iValueParser(torch::jit::IValue& iv) 
 }
 
 void StreamExecutor::getOutputTensors(std::vector<torch::Tensor>& output_tensors) {
-    for (auto id : output_blob_ids_) {
+    for (auto id : graph_outputs_) {
         auto iv = findBlob(id).second;
         for (auto& t : iValueParser(iv)) {
-            std::lock_guard<std::mutex> lock(stream_exec_mutex_);
+            std::lock_guard<std::mutex> lock(gather_mutex_);
             output_tensors.push_back(t.to("cuda:0"));   // every result ends up on cuda:0, as the reference's does
         }
     }
@@ -232,23 +232,23 @@ RetVal StreamExecutor::inferenceModelwithProfiling(const std::vector<torch::Tens
 RetVal StreamExecutor::run(const std::vector<torch::Tensor>& input_tensors, std::vector<torch::Tensor>& output_tensors, bool profiling) {
     status_ = 0;
     setInputTensors(input_tensors);
-    auto& layers = graph_->getLayers();
+    auto& layers = program_->getLayers();
     const int64_t n_layers = (int64_t)layers.size();
     struct Span { std::string name; size_t e0, e1; };
     std::vector<Span> spans;
     size_t next_event = 16;   // events 0..15 belong to MULTISTREAM
     // layers are ordered inputs, body, outputs; the cursor is the position (= id after UpdateLayerId) of the next layer
-    for (cursor_ = (int64_t)input_blob_ids_.size(); cursor_ < n_layers - (int64_t)output_blob_ids_.size();) {
-        auto layer = layers[cursor_];
+    for (pc_ = (int64_t)graph_inputs_.size(); pc_ < n_layers - (int64_t)graph_outputs_.size();) {
+        auto layer = layers[pc_];
         const auto type = layer->getType();
         if (type == ir::LayerType::PRIMCONSTANT || type == ir::LayerType::PRIMINPUT || type == ir::LayerType::PRIMOUTPUT) {
-            ++cursor_;   // constants were materialised by preProcess
+            ++pc_;   // constants were materialised by preProcess
             continue;
         }
         uint32_t id = layer->getID();
         auto fn = getOpExecutor(id);
         if (!fn) return RetVal::FAILURE;
-        const int64_t before = cursor_;
+        const int64_t before = pc_;
         if (profiling) {
             event(next_event).record(c10::cuda::getCurrentCUDAStream());
             fn(layer, *this);
@@ -263,7 +263,7 @@ RetVal StreamExecutor::run(const std::vector<torch::Tensor>& input_tensors, std:
             return RetVal::FAILURE;
         }
         // control ops (and MULTISTREAM) move the cursor themselves
-        if (!ir::isControlOp(type) && cursor_ == before) ++cursor_;
+        if (!ir::isControlOp(type) && pc_ == before) ++pc_;
     }
     if (checkDeviceStatus() != RetVal::SUCCESS) return RetVal::FAILURE;
     if (profiling && !spans.empty()) {
