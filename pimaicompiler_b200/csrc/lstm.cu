@@ -1071,7 +1071,9 @@ constexpr int kPipeTensorThreads = kPipeTensorWarps * 32;
 constexpr int kPipeGateWarps = 4;
 constexpr int kPipeGateThreads = kPipeGateWarps * 32;
 constexpr int kPipeThreads = 512;    // 4 warpgroups: 2 tensor, 1 gates, 1 exchange (one warp per group)
-constexpr int kPipeKtw = 8;          // k-tiles per tensor warp held in registers (H <= 1024)
+constexpr int kPipeKq = 4;           // tensor warp = (K quarter, half of the CTA's gate rows): four partial sums per gate
+constexpr int kPipeMh = kPipeTensorWarps / kPipeKq;
+constexpr int kPipeKtw = 16;         // k-tiles per tensor warp held in registers (H <= 1024)
 constexpr int kPipeMaxGroups = 4;    // one exchange warp per group
 constexpr int kPipeMaxHalves = 2;
 constexpr int kPipeMaxB = 128;       // sequences per launch: 2 halves x 4 groups x 16
@@ -1121,7 +1123,9 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
     constexpr int OCT = UPC / 8;                      // 16-byte records (unit octets) per sequence and CTA
     static_assert((UPC == 8 || UPC == 16) && BPG <= 32 && NG <= kPipeMaxGroups, "supported shapes");
     constexpr int ZP = BPG + 1;                       // padded sequence pitch of the partial sums
-    constexpr int ZBUF = kPipeTensorWarps * UPC * ZP * 4;  // floats per partial-sum buffer: [k-eighth][unit][ZP][gate]
+    constexpr int ZBUF = kPipeKq * UPC * ZP * 4;      // floats per partial-sum buffer: [k-quarter][unit][ZP][gate]
+    constexpr int MTW = MT / kPipeMh;                 // m-tiles per tensor warp
+    static_assert(MT % kPipeMh == 0, "the CTA's gate rows split evenly over the row halves");
     constexpr int SB = (BPG + 15) / 16;               // sequence blocks of 16 per gate thread
     constexpr int CPT = SB * OCT;                     // cells per gate thread and group
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -1170,19 +1174,23 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
         if (UPC == 16) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
         else asm volatile("setmaxnreg.inc.sync.aligned.u32 136;" ::: "memory");
         const int b_n = lane >> 2, b_k = (lane & 3) * 2;
-        uint32_t afrag[kPipeKtw][MT][4];   // afrag[i][m] = rows 16m..16m+15 of the slice, k-tile 8i + warp
+        // warp = (K quarter kq, row half mh): m-tiles mh*MTW .. of the slice, k-tiles 4i + kq.  Eight K-eighths over all
+        // rows would hold the same 128 fragment registers, but then every gate is the sum of eight partials, and the
+        // gate warps (one per scheduler, the step's critical resource) spent a third of their phase adding them up
+        const int kq = warp % kPipeKq, mh = warp / kPipeKq;
+        uint32_t afrag[kPipeKtw][MTW][4];
         {
             const __half* wbase = a.Whh + (size_t)u0 * 4 * H;
 #pragma unroll
             for (int i = 0; i < kPipeKtw; ++i)
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
+                for (int m = 0; m < MTW; ++m)
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         afrag[i][m][r] = 0u;
-                        if (kPipeTensorWarps * i + warp < ktiles) {
-                            const int row = m * 16 + b_n + (r & 1) * 8;
-                            const int k = (kPipeTensorWarps * i + warp) * 16 + b_k + (r >> 1) * 8;
+                        if (kPipeKq * i + kq < ktiles) {
+                            const int row = (mh * MTW + m) * 16 + b_n + (r & 1) * 8;
+                            const int k = (kPipeKq * i + kq) * 16 + b_k + (r >> 1) * 8;
                             afrag[i][m][r] = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)row * H + k));
                         }
                     }
@@ -1202,17 +1210,17 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
                     ok = mbar_wait_polls(zfree0 + 8u * zb, (uint32_t)(((phase >> 1) - 1) & 1), a.status, a.gen, wait_limit);
                 if (!ok) { dead = true; break; }
                 if (tr && tid == 0 && g == 0) tr[2] = clock64();
-                float* zq = zpart + (size_t)zb * ZBUF + (size_t)warp * UPC * ZP * 4;
-                float acc[MT][NTG][4];
+                float* zq = zpart + (size_t)zb * ZBUF + (size_t)kq * UPC * ZP * 4;
+                float acc[MTW][NTG][4];
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
+                for (int m = 0; m < MTW; ++m)
 #pragma unroll
                     for (int j = 0; j < NTG; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
                 const __half* brow = hs + (size_t)g * BPG * H + (size_t)b_n * 8 + b_k;
                 auto ktile = [&](int i) {
-                    const int kt = kPipeTensorWarps * i + warp;
+                    const int kt = kPipeKq * i + kq;
                     const __half* hp = brow + (size_t)(2 * kt) * BPG * 8;
                     uint32_t b0[NTG], b1[NTG];
 #pragma unroll
@@ -1223,25 +1231,25 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
 #pragma unroll
                     for (int j = 0; j < NTG; ++j)
 #pragma unroll
-                        for (int m = 0; m < MT; ++m) mma_16816(acc[m][j], afrag[i][m], b0[j], b1[j]);
+                        for (int m = 0; m < MTW; ++m) mma_16816(acc[m][j], afrag[i][m], b0[j], b1[j]);
                 };
-                if (ktiles == kPipeKtw * kPipeTensorWarps) {
-                    // H = 1024: every warp owns eight k-tiles; no conditions in the way of scheduling the operand loads
+                if (ktiles == kPipeKtw * kPipeKq) {
+                    // H = 1024: every warp owns sixteen k-tiles; no conditions in the way of scheduling the operand loads
                     // of later k-tiles above the products of earlier ones
 #pragma unroll
                     for (int i = 0; i < kPipeKtw; ++i) ktile(i);
                 } else {
 #pragma unroll
                     for (int i = 0; i < kPipeKtw; ++i)
-                        if (kPipeTensorWarps * i + warp < ktiles) ktile(i);   // warp-uniform
+                        if (kPipeKq * i + kq < ktiles) ktile(i);   // warp-uniform
                 }
 #pragma unroll
-                for (int m = 0; m < MT; ++m)
+                for (int m = 0; m < MTW; ++m)
 #pragma unroll
                     for (int j = 0; j < NTG; ++j)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int r = m * 16 + b_n + (i >> 1) * 8, n = j * 8 + b_k + (i & 1);
+                            const int r = (mh * MTW + m) * 16 + b_n + (i >> 1) * 8, n = j * 8 + b_k + (i & 1);
                             zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][j][i];
                         }
                 mbar_arrive(zready0 + 8u * zb);
@@ -1316,7 +1324,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
                     z[q][0] = 0.f; z[q][1] = 0.f; z[q][2] = 0.f; z[q][3] = 0.f;
                 }
 #pragma unroll
-                for (int k = 0; k < kPipeTensorWarps; ++k)
+                for (int k = 0; k < kPipeKq; ++k)
 #pragma unroll
                     for (int q = 0; q < CPT; ++q) {
                         const float4 zk = *reinterpret_cast<const float4*>(zbp[q] + (size_t)k * UPC * ZP * 4);
@@ -1330,7 +1338,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) lstm_persistent_pipe_kernel(P
                     const int o = q % OCT, gn = (gt >> 3) + 16 * (q / OCT), n = g * BPG + gn;
                     float4 gx = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (gn < BPG && n < B) gx = gxs[((size_t)g * CPT + q) * kPipeGateThreads + gt];
-                    // order of the additions: input term + bias first, then the sum of the eight partials
+                    // order of the additions: input term + bias first, then the sum of the four partials
                     const float zi = (gx.x + bias4[o].x) + z[q][0], zf = (gx.y + bias4[o].y) + z[q][1],
                                 zg = (gx.z + bias4[o].z) + z[q][2], zo = (gx.w + bias4[o].w) + z[q][3];
                     c[g][q] = sigmoidf_(zf) * c[g][q] + sigmoidf_(zi) * tanhf_(zg);
@@ -1969,7 +1977,7 @@ static size_t wide_smem(int H, int nt) {
 }
 static size_t pipe_smem(int H, int upc, int ntg, int ng) {
     const int BPG = ntg * 8, cpt = ((BPG + 15) / 16) * (upc / 8);
-    return (size_t)ng * BPG * H * 2 + (size_t)2 * kPipeTensorWarps * upc * (BPG + 1) * 16 +
+    return (size_t)ng * BPG * H * 2 + (size_t)2 * kPipeKq * upc * (BPG + 1) * 16 +
            (size_t)ng * cpt * kPipeGateThreads * 16 + (size_t)(2 * ng + 4) * 8 + 16;
 }
 static size_t tc_smem(int H, int BP) {
