@@ -75,6 +75,8 @@ int pimb200_gemv_vm(const void* x, const void* A, const void* bias, void* y,
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that first call
  * outside any stream capture.  All calls on a device share the one array: calls that may overlap on the GPU (different
  * streams without ordering between them) race; order them, or use pimb200_gemv_vm. */
+/* N bounds the scratch (partial sums and tickets are sized by the columns); K is only an argument sanity bound (row
+ * indices are ints), no part of the scratch depends on it. */
 #define PIMB200_VM_STATIC_MAX_N 32768
 #define PIMB200_VM_STATIC_MAX_K 1048576
 int pimb200_gemv_vm_static(const void* x, const void* A, const void* bias, void* y,

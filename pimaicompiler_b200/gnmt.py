@@ -25,6 +25,39 @@ import torch
 from . import ops
 
 
+def stage_groups(sentences: Sequence[torch.Tensor], G: int, enc_batch: int, max_len: int, pin: bool = False):
+    """Host-side packing of sentences into lock-step groups of G.  A group is a dict: `idx` (sentence indices, longest
+    first), `S` (longest sentence), `lengths` [G] int64, and `slices`: per `enc_batch` sentences the packed token ids
+    [sum of lengths] (timestep-major, the order of torch's pack_padded_sequence), `batch_sizes` (CPU int64, one per
+    timestep) and `dst`, the row t * G + j of the padded [S, G] buffer each packed row belongs to.  A ragged last group
+    is filled with one-token dummies.  With `pin` the tensors that travel to the device are in pinned host memory."""
+    keep = (lambda t: t.pin_memory()) if pin else (lambda t: t)
+    order = sorted(range(len(sentences)), key=lambda i: -int(sentences[i].shape[0]))
+    groups = []
+    for g0 in range(0, len(order), G):
+        idx = order[g0:g0 + G]
+        lens = [int(sentences[i].shape[0]) for i in idx]
+        if max(lens) > max_len or min(lens) < 1:
+            raise ValueError("sentence length outside 1..max_len")
+        lens_all = lens + [1] * (G - len(idx))
+        toks = [sentences[i] for i in idx] + [torch.full((1,), 4, dtype=torch.int64)] * (G - len(idx))
+        slices = []
+        for j0 in range(0, G, enc_batch):
+            j1 = min(j0 + enc_batch, G)
+            sl_lens = lens_all[j0:j1]
+            nb, Ss = j1 - j0, sl_lens[0]
+            pad = torch.full((Ss, nb), 4, dtype=torch.int64)
+            for b in range(nb):
+                pad[:sl_lens[b], b] = toks[j0 + b]
+            steps_col = torch.arange(Ss, dtype=torch.int64).view(Ss, 1)
+            mask = steps_col < torch.tensor(sl_lens, dtype=torch.int64).view(1, nb)      # [t, b]: sentence b has a step t
+            dst = (steps_col * G + j0 + torch.arange(nb, dtype=torch.int64).view(1, nb))[mask]
+            slices.append({"ids": keep(pad[mask]), "dst": keep(dst), "batch_sizes": mask.sum(1)})
+        groups.append({"idx": idx, "S": max(lens_all), "lengths": keep(torch.tensor(lens_all, dtype=torch.int64)),
+                       "slices": slices})
+    return groups
+
+
 class GnmtTranslator:
     def __init__(self, cfg, weights: dict, group: int = 128, device: Optional[torch.device] = None):
         ops.init()
@@ -184,36 +217,8 @@ class GnmtTranslator:
 
     # ------------------------------------------------------------------------------------------------ user call
     def stage(self, sentences: Sequence[torch.Tensor]):
-        """Sorts the sentences by length and packs them into lock-step groups.  A group is a dict: `idx` (sentence
-        indices), `S` (longest sentence), `lengths` [G] int64, and `slices`: per 128 sentences the packed token ids
-        [sum of lengths] (timestep-major, as pack_padded_sequence orders them), `batch_sizes` (CPU int64, one per
-        timestep) and `dst`, the row t * G + j of the padded [S, G] buffer each packed row belongs to.  Tensors are in
-        pinned host memory; a ragged last group is filled with one-token dummies."""
-        G = self.G
-        order = sorted(range(len(sentences)), key=lambda i: -int(sentences[i].shape[0]))
-        groups = []
-        for g0 in range(0, len(order), G):
-            idx = order[g0:g0 + G]
-            lens = [int(sentences[i].shape[0]) for i in idx]
-            if max(lens) > self.S or min(lens) < 1:
-                raise ValueError("sentence length outside 1..max_len")
-            lens_all = lens + [1] * (G - len(idx))
-            toks = [sentences[i] for i in idx] + [torch.full((1,), 4, dtype=torch.int64)] * (G - len(idx))
-            slices = []
-            for j0 in range(0, G, self.ENC_BATCH):
-                j1 = min(j0 + self.ENC_BATCH, G)
-                sl_lens = lens_all[j0:j1]
-                nb, Ss = j1 - j0, sl_lens[0]
-                pad = torch.full((Ss, nb), 4, dtype=torch.int64)
-                for b in range(nb):
-                    pad[:sl_lens[b], b] = toks[j0 + b]
-                steps_col = torch.arange(Ss, dtype=torch.int64).view(Ss, 1)
-                mask = steps_col < torch.tensor(sl_lens, dtype=torch.int64).view(1, nb)      # [t, b]: sentence b has a step t
-                dst = (steps_col * G + j0 + torch.arange(nb, dtype=torch.int64).view(1, nb))[mask]
-                slices.append({"ids": pad[mask].pin_memory(), "dst": dst.pin_memory(), "batch_sizes": mask.sum(1)})
-            groups.append({"idx": idx, "S": max(lens_all), "lengths": torch.tensor(lens_all, dtype=torch.int64).pin_memory(),
-                           "slices": slices})
-        return groups
+        """Sorts the sentences by length and packs them into lock-step groups (see stage_groups)."""
+        return stage_groups(sentences, self.G, self.ENC_BATCH, self.S, pin=True)
 
     def to_device(self, group: dict) -> dict:
         """The group's tensors copied to the device (batch_sizes stays on the host, as aten::lstm takes it)."""

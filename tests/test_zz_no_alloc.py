@@ -19,7 +19,7 @@ def _lib():
     return _lib.lib(), _lib
 
 
-@pytest.mark.parametrize("K,N", [(1024, 4096), (320, 1280), (2048, 1024), (64, 32768)])
+@pytest.mark.parametrize("K,N", [(1024, 4096), (320, 1280), (2048, 1024), (64, 32768), (2048, 32768), (1024, 16384)])
 def test_static_scratch_vm_matches_regular_entry_point_twice_in_a_row(K, N):
     lib, L = _lib()
     st = torch.cuda.current_stream().cuda_stream
@@ -37,6 +37,11 @@ def test_static_scratch_vm_matches_regular_entry_point_twice_in_a_row(K, N):
         torch.cuda.synchronize()
         # same kernel; only the K split (hence the fp32 summation order) may differ: the GEMV tolerance of the suite
         assert_close(y_new, y_ref.float().cpu(), 2e-3, 1e-3, f"static VM call {call} {K}x{N}")
+        # and directly against the C oracle (the largest widths run the widest K splits the scratch is sized for:
+        # 5 partial rows of 32768 columns, 10 of 16384)
+        from oracle import c_oracle as co
+        ref = co.vm(x.float().cpu().numpy(), A.float().cpu().numpy(), b.float().cpu().numpy(), call == 0)
+        assert_close(y_new, ref, 2e-3, 1e-3, f"static VM vs oracle, call {call} {K}x{N}")
 
 
 def test_static_scratch_vm_refuses_what_does_not_fit():
