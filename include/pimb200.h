@@ -165,6 +165,11 @@ int pimb200_tanh_f16(const void* x, void* y, size_t n, void* stream);
 int pimb200_masked_fill_f16(const void* x, const unsigned char* mask, float value, void* y, size_t n, size_t mask_n,
                             void* stream);
 
+/* The k largest (largest != 0) or smallest elements of every row of x [rows, cols] fp16, in order, and their int64
+ * indices (equal values: lower index first): values [rows, k], idx [rows, k].  k <= 64.  The aten::topk of a decode
+ * step over the last dimension (executeAtenTopk aten_ops_executor.cpp:3838, one at::topk call there). */
+int pimb200_topk_rows(const void* x, void* values, long long* idx, long rows, long cols, int k, int largest, void* stream);
+
 /* out[i, :] = table[idx[i], :] for n_idx int64 indices that live in DEVICE memory (rows of row_bytes bytes; an index
  * outside [0, n_table) gives a zero row).  The embedding lookup of a decode step without the host round trip of
  * executeAtenEmbedding, which reads the index with indices.item() (aten_ops_executor.cpp:1233-1300, the sync at
@@ -173,7 +178,8 @@ int pimb200_gather_rows(const void* table, const long long* idx, void* out, long
                         void* stream);
 
 /* table[idx[i], :] = src[i, :] for n_idx int64 row indices in DEVICE memory (indices outside [0, n_table) are skipped;
- * equal indices race).  The in-place KV-cache append of a decode step at a position kept on the device: where the
+ * equal indices race).  This is aten::index_put_ along dimension 0 with whole rows as values and accumulate = false
+ * (executeAtenIndexPut aten_ops_executor.cpp:1720), and the in-place KV-cache append of a decode step at a position kept on the device: where the
  * reference grows the cache with an at::cat per token (atenCat, aten_ops.cpp:97), the row goes into a pre-allocated
  * [S_max, d] buffer. */
 int pimb200_scatter_rows(void* table, const long long* idx, const void* src, long n_idx, size_t row_bytes, long n_table,

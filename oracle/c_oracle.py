@@ -71,6 +71,16 @@ def argmax(x):
     return idx
 
 
+def topk(x, k, largest=True):
+    x = _c(x)
+    cols = x.shape[-1]
+    vals = np.empty(x.shape[:-1] + (k,), np.float32)
+    idx = np.empty(x.shape[:-1] + (k,), np.int64)
+    lib().oracle_topk(_f(x), _f(vals), idx.ctypes.data_as(C.POINTER(C.c_longlong)), C.c_long(x.size // cols), C.c_long(cols),
+                      int(k), int(largest))
+    return vals, idx
+
+
 def layer_norm(x, gamma=None, beta=None, eps=1e-5):
     x, gamma, beta = _c(x), _c(gamma), _c(beta)
     cols = x.shape[-1]

@@ -58,6 +58,7 @@ SIGNATURES = {
     "pimb200_gather_rows": (_i, [_vp, _vp, _vp, C.c_long, _sz, C.c_long, _vp]),
     "pimb200_scatter_rows": (_i, [_vp, _vp, _vp, C.c_long, _sz, C.c_long, _vp]),
     "pimb200_masked_fill_f16": (_i, [_vp, _vp, C.c_float, _vp, _sz, _sz, _vp]),
+    "pimb200_topk_rows": (_i, [_vp, _vp, _vp, C.c_long, C.c_long, _i, _i, _vp]),
     "pimb200_lstm_create": (_i, [C.POINTER(_vp), _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
     "pimb200_lstm_destroy": (_i, [_vp]),
     "pimb200_lstm_set_variant": (_i, [_vp, _i]),

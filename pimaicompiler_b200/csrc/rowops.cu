@@ -127,6 +127,52 @@ __global__ void __launch_bounds__(T) argmax_rows_kernel(const __half* __restrict
     }
 }
 
+// The k largest (or smallest) elements of every row, in order, with their indices: k rounds over the row (it stays in
+// L1 / L2), each round the block-wide best element that comes after the previous pick in the total order
+// (value, then lower index first), so no set of taken indices has to be kept.  One CTA per row.
+template <int T>
+__global__ void __launch_bounds__(T) topk_rows_kernel(const __half* __restrict__ x, __half* __restrict__ values,
+                                                      long long* __restrict__ idx, long cols, int k, int largest) {
+    __shared__ float red_v[T / 32];
+    __shared__ long long red_i[T / 32];
+    __shared__ float pick_v;
+    __shared__ long long pick_i;
+    const __half* row = x + (size_t)blockIdx.x * cols;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float sgn = largest ? 1.f : -1.f;          // smallest-first is largest-first of the negated row
+    float prev_v = CUDART_INF_F;
+    long long prev_i = -1;
+    for (int r = 0; r < k; ++r) {
+        float bv = -CUDART_INF_F;
+        long long bi = cols;
+        for (long c = threadIdx.x; c < cols; c += T) {
+            const float v = sgn * __half2float(row[c]);
+            const bool after_prev = v < prev_v || (v == prev_v && c > prev_i);
+            if (after_prev && (v > bv || (v == bv && c < bi))) { bv = v; bi = c; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const long long oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < T / 32; ++w)
+                if (red_v[w] > bv || (red_v[w] == bv && red_i[w] < bi)) { bv = red_v[w]; bi = red_i[w]; }
+            pick_v = bv;
+            pick_i = bi;
+            const long long out_i = bi < cols ? bi : 0;          // fewer than k comparable elements (NaNs): index 0
+            values[(size_t)blockIdx.x * k + r] = row[out_i];
+            idx[(size_t)blockIdx.x * k + r] = out_i;
+        }
+        __syncthreads();
+        prev_v = pick_v;
+        prev_i = pick_i;
+    }
+}
+
 template <int T, bool VEC>
 __global__ void __launch_bounds__(T) layer_norm_rows_kernel(const __half* __restrict__ x,
                                                                       const __half* __restrict__ gamma,
@@ -793,5 +839,21 @@ extern "C" int pimb200_attention_block(const void* q, const void* k, const void*
     attention_block_kernel<<<dim3((unsigned)heads, (unsigned)n_seq), kBlockAttnThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(q), static_cast<const __half*>(k), static_cast<const __half*>(v), lengths,
         static_cast<__half*>(out), max_len, head_dim, row_stride, seq_stride, out_row_stride, out_seq_stride, scale);
+    return launch_status();
+}
+
+extern "C" int pimb200_topk_rows(const void* x, void* values, long long* idx, long rows, long cols, int k, int largest,
+                                 void* stream) {
+    if (rows == 0 || k == 0) return PIMB200_OK;
+    if (!x || !values || !idx || !rows_ok(rows, cols) || k < 0) return PIMB200_ERR_BAD_ARG;
+    if (k > cols) return PIMB200_ERR_BAD_ARG;
+    if (k > 64) return PIMB200_ERR_UNSUPPORTED;      // k passes over the row: meant for beam widths, not for sorting
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cols >= kWideRow)
+        topk_rows_kernel<1024><<<(unsigned)rows, 1024, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(values), idx,
+                                                               cols, k, largest ? 1 : 0);
+    else
+        topk_rows_kernel<128><<<(unsigned)rows, 128, 0, st>>>(static_cast<const __half*>(x), static_cast<__half*>(values), idx,
+                                                             cols, k, largest ? 1 : 0);
     return launch_status();
 }

@@ -260,6 +260,22 @@ at::Tensor argmax(OpContext& cx, const at::Tensor& x, int64_t dim, bool keepdim)
     return at::argmax(x, dim, keepdim);
 }
 
+std::tuple<at::Tensor, at::Tensor> topk(OpContext& cx, const at::Tensor& x, int64_t k, int64_t dim, bool largest, bool sorted) {
+    if (fastHalf(x) && lastDim(x, dim) && x.numel() > 0 && k >= 1 && k <= 64 && k <= x.size(-1)) {
+        at::Tensor xc = x.contiguous();
+        auto sizes = xc.sizes().vec();
+        const long cols = (long)sizes.back(), rows = (long)(xc.numel() / cols);
+        sizes.back() = k;
+        at::Tensor vals = at::empty(sizes, xc.options());
+        at::Tensor idx = at::empty(sizes, xc.options().dtype(at::kLong));
+        cx.note(pimb200_topk_rows(xc.data_ptr(), vals.data_ptr(), reinterpret_cast<long long*>(idx.data_ptr<int64_t>()), rows, cols,
+                                  (int)k, largest ? 1 : 0, cx.stream));
+        return {vals, idx};
+    }
+    fellBack();
+    return at::topk(x, k, dim, largest, sorted);
+}
+
 at::Tensor layerNorm(OpContext& cx, const at::Tensor& x, const std::vector<int64_t>& normalized_shape, const at::Tensor& weight,
                      const at::Tensor& bias, double eps) {
     const bool one_dim = normalized_shape.size() == 1 && x.dim() >= 1 && normalized_shape[0] == x.size(-1);

@@ -8,6 +8,7 @@
 #include <cuda_runtime_api.h>
 #include <torch/torch.h>
 
+#include <tuple>
 #include <vector>
 
 struct pimb200_lstm;
@@ -58,6 +59,8 @@ at::Tensor linear(OpContext& cx, const at::Tensor& x, const at::Tensor& W, const
 at::Tensor add(OpContext& cx, const at::Tensor& a, const at::Tensor& b, double alpha);
 at::Tensor softmax(OpContext& cx, const at::Tensor& x, int64_t dim, bool log);
 at::Tensor argmax(OpContext& cx, const at::Tensor& x, int64_t dim, bool keepdim);
+// (values, indices) = topk(x, k, dim, largest, sorted)   (atenTopk; the device kernel returns the picks in order)
+std::tuple<at::Tensor, at::Tensor> topk(OpContext& cx, const at::Tensor& x, int64_t k, int64_t dim, bool largest, bool sorted);
 at::Tensor layerNorm(OpContext& cx, const at::Tensor& x, const std::vector<int64_t>& normalized_shape, const at::Tensor& weight,
                      const at::Tensor& bias, double eps);
 at::Tensor tanh(OpContext& cx, const at::Tensor& x);

@@ -204,6 +204,18 @@ def argmax(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return idx
 
 
+def topk(x: torch.Tensor, k: int, largest: bool = True):
+    """(values, int64 indices) of the k largest / smallest elements along the last dimension, in order."""
+    _req_half_cuda(x)
+    cols = x.shape[-1]
+    rows = x.numel() // max(cols, 1)
+    vals = torch.empty(*x.shape[:-1], k, dtype=torch.float16, device=x.device)
+    idx = torch.empty(*x.shape[:-1], k, dtype=torch.int64, device=x.device)
+    check(_lib.lib().pimb200_topk_rows(_ptr(x), _ptr(vals), idx.data_ptr(), rows, cols, k, 1 if largest else 0, _stream()),
+          "topk_rows")
+    return vals, idx
+
+
 def layer_norm(x: torch.Tensor, gamma: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
                eps: float = 1e-5) -> torch.Tensor:
     """Layer normalisation over the last dimension."""

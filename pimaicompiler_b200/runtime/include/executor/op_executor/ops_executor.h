@@ -23,6 +23,7 @@ void executeAtenMatmul(Layer& layer, StreamExecutor& stream_executor);
 void executeAtenSoftmax(Layer& layer, StreamExecutor& stream_executor);
 void executeAtenLogSoftmax(Layer& layer, StreamExecutor& stream_executor);
 void executeAtenArgmax(Layer& layer, StreamExecutor& stream_executor);
+void executeAtenTopk(Layer& layer, StreamExecutor& stream_executor);
 void executeAtenTanh(Layer& layer, StreamExecutor& stream_executor);
 void executeMultiStream(Layer& layer, StreamExecutor& stream_executor);
 

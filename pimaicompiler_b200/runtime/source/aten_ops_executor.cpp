@@ -206,6 +206,24 @@ void executeAtenArgmax(Layer& layer, StreamExecutor& ex) {
     publish(ex, cx, layer, tensor_ops::argmax(cx, blobTensor(ex, in[0]), dim, keep != 0));
 }
 
+// aten::topk(self, k, dim, largest, sorted) -> (values, indices)
+void executeAtenTopk(Layer& layer, StreamExecutor& ex) {
+    auto tk = std::static_pointer_cast<ir::AtenTopkLayer>(layer);
+    auto in = layer->getInSTensorID();
+    auto outs = uniqueOuts(layer);
+    TORCH_CHECK(outs.size() == 2, "aten::topk publishes values and indices");
+    int in_id = 1;
+    const int k = attrOrInput(ex, tk->getK(), in, in_id);
+    const int dim = attrOrInput(ex, tk->getDim(), in, in_id);
+    const int largest = attrOrInput(ex, tk->getLargest(), in, in_id);
+    const int sorted = attrOrInput(ex, tk->getSorted(), in, in_id);
+    auto cx = context(ex);
+    auto r = tensor_ops::topk(cx, blobTensor(ex, in[0]), k, dim, largest != 0, sorted != 0);
+    ex.setStatus(cx.status);
+    ex.updateBlob(outs[0], DataType::TENSOR, IValue(std::get<0>(r)));
+    ex.updateBlob(outs[1], DataType::TENSOR, IValue(std::get<1>(r)));
+}
+
 void executeAtenTanh(Layer& layer, StreamExecutor& ex) {
     auto cx = context(ex);
     publish(ex, cx, layer, tensor_ops::tanh(cx, blobTensor(ex, layer->getInSTensorID()[0])));

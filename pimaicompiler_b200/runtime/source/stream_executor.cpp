@@ -38,6 +38,7 @@ void StreamExecutor::registerOp() {
     reg(ir::LayerType::ATENSOFTMAX, executeAtenSoftmax);
     reg(ir::LayerType::ATENLOGSOFTMAX, executeAtenLogSoftmax);
     reg(ir::LayerType::ATENARGMAX, executeAtenArgmax);
+    reg(ir::LayerType::ATENTOPK, executeAtenTopk);
     reg(ir::LayerType::ATENTANH, executeAtenTanh);
     reg(ir::LayerType::MULTISTREAM, executeMultiStream);
     // pass-through adapters

@@ -232,3 +232,21 @@ def test_two_gpu_replicas_match_one_gpu():
         two = mod.PipelineManager(path, "", 2)
         (out,) = two.inferenceModel([a.cuda(), b.cuda()])
         assert torch.equal(out.cpu(), sm_add(a, b))
+
+
+class TopkNet(torch.nn.Module):
+    def forward(self, x):
+        v, i = torch.topk(x, 3)
+        return v, i
+
+
+def test_topk_through_the_compiler_uses_the_device_kernel():
+    mod = _module()
+    pm, sm = _compile(TopkNet())
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(2, 300, generator=g).half()
+    mod.reset_fallback_count()
+    v, i = pm.inferenceModel(_dev([x]))
+    assert mod.fallback_count() == 0
+    rv, ri = sm(x.float())
+    assert torch.equal(v.float().cpu(), rv) and torch.equal(i.cpu(), ri)

@@ -189,3 +189,19 @@ def test_additive_attention_matches_libtorch(n, S, H):
     e = torch.einsum("snh,h->sn", torch.tanh(kp.float() + q.float().unsqueeze(0)), v.float())
     ref = torch.einsum("sn,snh->nh", torch.softmax(e, 0), vals.float())
     np.testing.assert_allclose(out.numpy(), ref.numpy(), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,cols,k", [(1, 32320, 4), (3, 29, 5), (5, 512, 1), (2, 4100, 8), (4, 37, 37)])
+def test_topk_rows_match_oracle(rows, cols, k):
+    # values bit-exact; indices equal to the oracle's (equal values: lower index first), largest and smallest
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows * 1000 + cols + k)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(torch.float16)
+    x[0, cols // 2] = x[0, 0]                       # a tie
+    for largest in (True, False):
+        rv, ri = co.topk(x.float().numpy(), k, largest)
+        v, i = ops.topk(x.cuda(), k, largest)
+        assert np.array_equal(v.float().cpu().numpy(), rv)
+        assert np.array_equal(i.cpu().numpy(), ri)
+        tv, _ = torch.topk(x.float(), k, largest=largest)
+        assert np.array_equal(rv, tv.numpy())       # the oracle itself against libtorch
