@@ -135,20 +135,44 @@ def dist_setup(n_gpus: int):
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the libtorch CPU implementation of the same ops (what the reference's default executors call)
 # ------------------------------------------------------------------------------------------------
+CPU_SAMPLE_SECONDS = 20.0   # the CPU arm stops taking new streams after this many seconds of work
+
+
+def host_threads() -> int:
+    """Threads the CPU arm uses: the cores this process may run on (affinity mask, cgroup CPU quota), at most 32.  More
+    threads than cores make the libtorch calls of a batch-1 decode crawl (spinning barriers on tiny products), and under
+    torchrun the other ranks' processes are busy waiting at the same time."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            n = min(n, max(1, int(int(quota) / int(period))))
+    except (OSError, ValueError):
+        pass
+    return max(1, min(n, 32))
+
+
 def cpu_rnnt_throughput(n_utts: int, seed0: int):
     """Decodes n_utts synthetic utterances on the host cores; returns (utt/s, seconds, cores)."""
     from oracle import torch_oracle as to
     cfg = to.RnntConfig()
     w = to.make_rnnt_weights(cfg, seed=0)
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     torch.set_num_threads(cores)
     feats = [to.make_features(T_FRAMES, cfg, seed0 + i) for i in range(n_utts)]
     to.rnnt_greedy(w, feats[0][:100], cfg)  # warm the thread pool
     t0 = time.perf_counter()
+    done = 0
     for f in feats:
         to.rnnt_greedy(w, f, cfg)
+        done += 1
+        if time.perf_counter() - t0 > CPU_SAMPLE_SECONDS:
+            break
     dt = time.perf_counter() - t0
-    return n_utts / dt, dt, cores
+    return done / dt, dt, cores
 
 
 def run_reference(args, rank, world):
@@ -163,7 +187,8 @@ def run_reference(args, rank, world):
         vals.append(v)
         secs += dt
     value = statistics.median(vals)
-    sample = f"{n} utterances per step, libtorch {torch.__version__} CPU fp32 (at::lstm/at::linear), {cores} threads"
+    sample = (f"up to {n} utterances per step (no new one after {CPU_SAMPLE_SECONDS:.0f} s), libtorch {torch.__version__} CPU fp32 "
+              f"(at::lstm/at::linear), {cores} threads")
     line = {
         "impl": "reference", "metric": "rnnt_greedy_utterances_per_s", "value": value, "unit": "utt/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -298,16 +323,16 @@ def run_gpu(args, rank, world, local):
     launches_per_step = calls * (((chunk + eb - 1) // eb) * 2 * (cfg.pre_layers + cfg.post_layers) + 2)
 
     extras = {}
-    if rank == 0 and not args.no_extras:
+    if rank == 0 and world == 1 and not args.no_extras:        # the op sweeps ride on the one-GPU line only
         del feats, flush
         torch.cuda.empty_cache()
         extras["lstm_c1"] = measure_c1(max(args.steps, 3))["persistent"]
         extras["gemv"] = measure_c2(max(args.steps, 3), batches=(32,), shapes_batched=((4096, 1024),), rowops=False)["results"]
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:   # timed on rank 0 at N = 1 only: the other ranks would wait
         v, dt, cores = cpu_rnnt_throughput(args.cpu_sample, 7000)
         cpu = {"value": v, "unit": "utt/s", "cores": cores, "kind": "port",
-               "sample": f"{args.cpu_sample} of the same synthetic utterances, libtorch {torch.__version__} CPU fp32 "
+               "sample": f"up to {args.cpu_sample} of the same synthetic utterances (no new one after {CPU_SAMPLE_SECONDS:.0f} s), libtorch {torch.__version__} CPU fp32 "
                          f"(the at::lstm/at::linear calls of the reference's default executors), {dt:.1f} s"}
     barrier(world)
     if rank != 0:
@@ -565,16 +590,20 @@ class _Translate:
         """Translates n synthetic streams on the host cores with the libtorch oracle; (streams/s, seconds, cores)."""
         from oracle import torch_oracle as to
         w = self.make_weights(self.cfg, seed=0)
-        cores = os.cpu_count() or 1
+        cores = host_threads()
         torch.set_num_threads(cores)
         seqs = to.make_sentences(n, self.cfg, seed)
         fn = to.gnmt_translate if self.kind == "c4" else to.transformer_translate
         fn(w, seqs[0], self.cfg, 4)
         t0 = time.perf_counter()
+        done = 0
         for s_ in seqs:
             fn(w, s_, self.cfg)
+            done += 1
+            if time.perf_counter() - t0 > CPU_SAMPLE_SECONDS:
+                break
         dt = time.perf_counter() - t0
-        return n / dt, dt, cores
+        return done / dt, dt, cores
 
 
 def run_reference_translate(args, rank, world):
@@ -673,7 +702,7 @@ def run_translate(args, rank, world, local):
     n_steps = len(dev_groups) * cfg.max_steps * args.steps
     achieved = step_bytes * n_steps / (decode_ms * 1e-3) / 1e9 if decode_ms > 0 else 0.0
     cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:   # timed on rank 0 at N = 1 only: the other ranks would wait
         n_cpu = max(1, min(args.cpu_sample, 8 if wl.kind == "c4" else 128))
         v, dt, cores = wl.cpu_throughput(n_cpu, 9100)
         cpu = {"value": v, "unit": wl.unit, "cores": cores, "kind": "port",
