@@ -268,6 +268,18 @@ int pimb200_lstm_set_variant(pimb200_lstm* h, int variant);
 int pimb200_lstm_forward(pimb200_lstm* h, const void* x, int T, int B, const void* h0, const void* c0,
                          void* y, void* hn, void* cn, int batch_first, void* stream);
 
+/* One decode step (seq_len 1) of a one-layer, one-direction handle for B >= 8 sequences in lock step, with row strides:
+ * x rows x_ld elements apart (a [B, x_ld] buffer whose first I columns are the input), the output written to rows y_ld
+ * elements apart, optionally as y = h + residual (residual rows residual_ld apart; the fp16 add a separate aten::add of
+ * the rounded h would make).  hn [B, H] receives h itself, cn [B, H] the cell state.  This is how the reference's GNMT
+ * graph is wired after LstmLabeling / CatLabeling: a decoder cell writes its output straight into one half of the
+ * pre-allocated buffer of the aten::cat that feeds the next cell (miopen_ops_executor.cpp:193-228) and the residual
+ * aten::add works in place on it (aten_ops_executor.cpp:131-146); here both happen in the cell's gate kernel.  Shapes
+ * outside the decode form (B < 8, more layers or directions, unaligned rows) return PIMB200_ERR_UNSUPPORTED: use
+ * pimb200_lstm_forward. */
+int pimb200_lstm_forward_step(pimb200_lstm* h, const void* x, long x_ld, int B, const void* h0, const void* c0, void* y,
+                              long y_ld, void* hn, void* cn, const void* residual, long residual_ld, void* stream);
+
 /* Forward pass, packed sequence:  data [sum(batch_sizes), I], batch_sizes = T host int64 values,
  * non-increasing; y [sum(batch_sizes), D*H]; h0/c0/hn/cn [L*D, batch_sizes[0], H].
  * Replaces atenLstm2 -> at::lstm(data, batch_sizes, ...) (aten_ops.cpp:337-344) and

@@ -279,6 +279,8 @@ struct CellPointArgs {
     __half* hn;          // optional [B, H]
     __half* cn;          // optional [B, H]
     int H, B;
+    const __half* res;   // optional residual rows: y = h + res (fp16 add of the rounded h, as a separate add would do)
+    long res_bstride;
 };
 
 __global__ void __launch_bounds__(256) lstm_cell_point_kernel(CellPointArgs a) {
@@ -294,7 +296,8 @@ __global__ void __launch_bounds__(256) lstm_cell_point_kernel(CellPointArgs a) {
     const float cprev = a.c0 ? __half2float(a.c0[(size_t)b * a.H + u]) : 0.f;
     const float cnew = sigmoidf_(z.y + bb.y) * cprev + sigmoidf_(z.x + bb.x) * tanhf_(z.z + bb.z);
     const __half hh = __float2half_rn(sigmoidf_(z.w + bb.w) * tanhf_(cnew));
-    a.y[(size_t)b * a.y_bstride + u] = hh;
+    a.y[(size_t)b * a.y_bstride + u] =
+        a.res ? __float2half_rn(__half2float(hh) + __half2float(a.res[(size_t)b * a.res_bstride + u])) : hh;
     if (a.hn) a.hn[(size_t)b * a.H + u] = hh;
     if (a.cn) a.cn[(size_t)b * a.H + u] = __float2half_rn(cnew);
 }
@@ -2410,7 +2413,7 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
                     if (Gh && (rc = launch_gemm_wx(a.Whh, a.h0, nullptr, Gh, 4 * H, H, B, H, 4 * H, PIMB200_ACT_NONE, 1, st)) !=
                                   PIMB200_OK)
                         return rc;
-                    CellPointArgs pa{Gx, Gh, a.bias, a.c0, a.y, a.y_bstride, a.hn, a.cn, H, B};
+                    CellPointArgs pa{Gx, Gh, a.bias, a.c0, a.y, a.y_bstride, a.hn, a.cn, H, B, nullptr, 0};
                     lstm_cell_point_kernel<<<ceil_div(B * H, 256), 256, 0, st>>>(pa);
                     if ((rc = launch_status()) != PIMB200_OK) return rc;
                     continue;
@@ -2469,6 +2472,36 @@ extern "C" int pimb200_lstm_forward(pimb200_lstm* h, const void* x, int T, int B
     return lstm_forward_impl(h, static_cast<const __half*>(x), sq, static_cast<const __half*>(h0),
                              static_cast<const __half*>(c0), static_cast<__half*>(y), static_cast<__half*>(hn),
                              static_cast<__half*>(cn), batch_first ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+// Decode step of a one-layer, one-direction handle for B >= 8 sequences with strided rows: x rows x_ld halves apart, the
+// output (optionally h + residual) written to rows y_ld halves apart, e.g. straight into one half of the next layer's
+// concatenated input.
+extern "C" int pimb200_lstm_forward_step(pimb200_lstm* h, const void* x, long x_ld, int B, const void* h0, const void* c0,
+                                         void* y, long y_ld, void* hn, void* cn, const void* residual, long residual_ld,
+                                         void* stream) {
+    if (!h || !x || !y || B <= 0) return PIMB200_ERR_BAD_ARG;
+    const int H = h->H, I = h->I;
+    if (x_ld < I || y_ld < H || (residual && residual_ld < H)) return PIMB200_ERR_BAD_ARG;
+    if (h->L != 1 || h->D != 1 || B < kCellGemmMinB || H % 8 != 0 || I % 8 != 0 || x_ld % 8 != 0 || !aligned16(x) ||
+        (h0 && !aligned16(h0)))
+        return PIMB200_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(h->mu);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc;
+    if ((rc = grow(&h->G, &h->G_cap, (size_t)2 * B * 4 * H)) != PIMB200_OK) return rc;
+    float* Gx = h->G;
+    float* Gh = h0 ? h->G + (size_t)B * 4 * H : nullptr;
+    if ((rc = launch_gemm_wx(h->w_ih[0], static_cast<const __half*>(x), nullptr, Gx, 4 * H, I, B, (int)x_ld, 4 * H,
+                             PIMB200_ACT_NONE, 1, st)) != PIMB200_OK)
+        return rc;
+    if (Gh && (rc = launch_gemm_wx(h->w_hh[0], static_cast<const __half*>(h0), nullptr, Gh, 4 * H, H, B, H, 4 * H,
+                                   PIMB200_ACT_NONE, 1, st)) != PIMB200_OK)
+        return rc;
+    CellPointArgs pa{Gx, Gh, h->bias[0], static_cast<const __half*>(c0), static_cast<__half*>(y), y_ld,
+                     static_cast<__half*>(hn), static_cast<__half*>(cn), H, B, static_cast<const __half*>(residual), residual_ld};
+    lstm_cell_point_kernel<<<ceil_div(B * H, 256), 256, 0, st>>>(pa);
+    return launch_status();
 }
 
 extern "C" int pimb200_lstm_forward_packed(pimb200_lstm* h, const void* data, const int64_t* batch_sizes, int T,

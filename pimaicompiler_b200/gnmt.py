@@ -9,7 +9,8 @@ hundreds of them runs `group` sentences in lock step instead:
   * encoder: the group's sentences, sorted by length, go through each layer as packed batches of up to 128 sentences
     (aten::lstm's packed overload, which the library runs as a padded lock-step batch on the persistent weight-stationary
     recurrence, the backward direction of the first layer on the sentences reversed one by one);
-  * decoder: one step for the whole group is 4 x (two streaming GEMMs over the group's rows + the gate kernel), one
+  * decoder: one step for the whole group is 4 x (two GEMMs over the group's rows + the gate kernel, which writes the
+    cell's output, for the last two cells with the residual added, straight into the next cell's concatenated input), one
     attention launch (a CTA per sentence, own source length), the vocabulary projection as a GEMM (the 66 MB matrix is
     read once per step for all sentences) and a row-wise arg max; two steps (state buffers alternate) are captured into
     one CUDA graph and replayed, the chosen tokens staying on the device until the group is done.
@@ -131,23 +132,38 @@ class GnmtTranslator:
         row = 2 * H * 2          # bytes per row of a concatenation buffer
         half = H * 2
         n = 0
+        cat = self.cat
         ops.gather_rows(w["emb_tgt"], self.tok, out=self.x); n += 1
-        self.lstm["dec0"].forward(self.x.view(1, G, H), src[0], src[4], out=(self.y[0], dst[0], dst[4])); n += 3
-        y0 = self.y[0].view(G, H)
+        # groups of 8 or more sentences: every cell writes its output (the last two with their residual added) straight
+        # into the first half of the next cell's concatenated input, as the reference's labelled GNMT graph does
+        fused = self.lstm["dec0"].forward_step(self.x, src[0][0], src[4][0], cat[0][:, :H], dst[0][0], dst[4][0])
+        if fused:
+            n += 3
+            y0 = cat[0][:, :H]
+        else:
+            self.lstm["dec0"].forward(self.x.view(1, G, H), src[0], src[4], out=(self.y[0], dst[0], dst[4])); n += 1
+            y0 = self.y[0].view(G, H)
+            ops.copy_2d(cat[0], 0, row, y0, 0, half, half, G); n += 1
         ops.gemm_wx(w["Wq"], y0, out=self.q); n += 1
         ops.additive_attention(self.q, self.keys_proj, self.enc_out, self.lengths, self.v_norm, w["att_b"],
-                               out=self.cat[0][:, H:], scores=self.scores); n += 2
-        ops.copy_2d(self.cat[0], 0, row, y0, 0, half, half, G); n += 1
+                               out=cat[0][:, H:], scores=self.scores); n += 2
         for i in (1, 2):          # the context is the second half of every layer's input
-            ops.copy_2d(self.cat[i], half, row, self.cat[0], half, row, half, G); n += 1
-        self.lstm["dec1"].forward(self.cat[0].view(1, G, 2 * H), src[1], src[5], out=(self.y[1], dst[1], dst[5])); n += 3
-        y1 = self.y[1].view(G, H)
-        ops.copy_2d(self.cat[1], 0, row, y1, 0, half, half, G); n += 1
-        self.lstm["dec2"].forward(self.cat[1].view(1, G, 2 * H), src[2], src[6], out=(self.y[2], dst[2], dst[6])); n += 3
-        ops.add_f16(self.y[2].view(G, H), y1, out=self.r2); n += 1
-        ops.copy_2d(self.cat[2], 0, row, self.r2, 0, half, half, G); n += 1
-        self.lstm["dec3"].forward(self.cat[2].view(1, G, 2 * H), src[3], src[7], out=(self.y[3], dst[3], dst[7])); n += 3
-        ops.add_f16(self.y[3].view(G, H), self.r2, out=self.r3); n += 1
+            ops.copy_2d(cat[i], half, row, cat[0], half, row, half, G); n += 1
+        if fused:
+            self.lstm["dec1"].forward_step(cat[0], src[1][0], src[5][0], cat[1][:, :H], dst[1][0], dst[5][0]); n += 3
+            self.lstm["dec2"].forward_step(cat[1], src[2][0], src[6][0], cat[2][:, :H], dst[2][0], dst[6][0],
+                                           residual=cat[1][:, :H]); n += 3
+            self.lstm["dec3"].forward_step(cat[2], src[3][0], src[7][0], self.r3, dst[3][0], dst[7][0],
+                                           residual=cat[2][:, :H]); n += 3
+        else:
+            self.lstm["dec1"].forward(cat[0].view(1, G, 2 * H), src[1], src[5], out=(self.y[1], dst[1], dst[5])); n += 1
+            y1 = self.y[1].view(G, H)
+            ops.copy_2d(cat[1], 0, row, y1, 0, half, half, G); n += 1
+            self.lstm["dec2"].forward(cat[1].view(1, G, 2 * H), src[2], src[6], out=(self.y[2], dst[2], dst[6])); n += 1
+            ops.add_f16(self.y[2].view(G, H), y1, out=self.r2); n += 1
+            ops.copy_2d(cat[2], 0, row, self.r2, 0, half, half, G); n += 1
+            self.lstm["dec3"].forward(cat[2].view(1, G, 2 * H), src[3], src[7], out=(self.y[3], dst[3], dst[7])); n += 1
+            ops.add_f16(self.y[3].view(G, H), self.r2, out=self.r3); n += 1
         ops.gemm_wx(w["Wc"], self.r3, w["bc"], out=self.logits); n += 1
         ops.argmax(self.logits, out=self.tok); n += 1
         # record the chosen tokens (and, for the parity tests, the logits) in row step_idx of the output tables

@@ -417,6 +417,21 @@ class Lstm:
                                               _ptr(cn), 1 if batch_first else 0, _stream()), "lstm_forward")
         return y, hn, cn
 
+    def forward_step(self, x: torch.Tensor, h0: Optional[torch.Tensor], c0: Optional[torch.Tensor], y: torch.Tensor,
+                     hn: torch.Tensor, cn: torch.Tensor, residual: Optional[torch.Tensor] = None) -> bool:
+        """Decode step for B >= 8 sequences with strided rows: x [B, >= I] and y [B, >= H] may be column slices of wider
+        buffers, y = h (+ residual).  Returns False when the shape is not the decode form (use forward())."""
+        _req_half_cuda(h0, c0, hn, cn)
+        _req_half_cuda_rows(x, y, residual)
+        B = x.shape[0]
+        rc = _lib.lib().pimb200_lstm_forward_step(self._h, _ptr(x), x.stride(0), B, _ptr(h0), _ptr(c0), _ptr(y), y.stride(0),
+                                                  _ptr(hn), _ptr(cn), _ptr(residual),
+                                                  residual.stride(0) if residual is not None else 0, _stream())
+        if rc == _lib.ERR_UNSUPPORTED:
+            return False
+        check(rc, "lstm_forward_step")
+        return True
+
     def forward_packed(self, data: torch.Tensor, batch_sizes: torch.Tensor, h0: Optional[torch.Tensor] = None,
                        c0: Optional[torch.Tensor] = None):
         _req_half_cuda(data, h0, c0)

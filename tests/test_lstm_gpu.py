@@ -340,3 +340,28 @@ def test_lstm_packed_sequences_on_the_lockstep_kernels_vs_libtorch(B, I, H, L, b
     assert_close(ys, ry, LSTM_ATOL, LSTM_RTOL, "packed y, streamed")
     assert_close(y, ys, LSTM_ATOL, LSTM_RTOL, "lock-step vs streamed")
     assert_close(cn, cns, LSTM_ATOL, LSTM_RTOL, "lock-step vs streamed c_n")
+
+
+@pytest.mark.parametrize("B,I,H", [(8, 64, 32), (33, 256, 128), (128, 2048, 1024)])
+def test_lstm_decode_step_with_strided_rows_and_residual(B, I, H):
+    # the decode step that writes into one half of the next cell's concatenated input: equal to forward() with T = 1 bit
+    # for bit, and to the fp16 add of a residual row
+    ops = _ops()
+    g = torch.Generator().manual_seed(B + I + H)
+    ps = [to_dev(p) for p in lstm_params(1, 1, I, H, g)]
+    m = ops.Lstm(ps, 1, False, I, H, True)
+    xbuf = to_dev(h16(torch.randn(B, I + 24, generator=g)))          # the input is the first I columns of wider rows
+    h0 = to_dev(h16(torch.randn(1, B, H, generator=g) * 0.5))
+    c0 = to_dev(h16(torch.randn(1, B, H, generator=g) * 0.5))
+    res = to_dev(h16(torch.randn(B, 2 * H, generator=g)))
+    y_ref, hn_ref, cn_ref = m.forward(xbuf[:, :I].contiguous().view(1, B, I), h0, c0)
+    out = torch.zeros(B, 2 * H, dtype=torch.float16, device="cuda")
+    hn, cn = torch.empty(B, H, dtype=torch.float16, device="cuda"), torch.empty(B, H, dtype=torch.float16, device="cuda")
+    assert m.forward_step(xbuf[:, :I], h0[0], c0[0], out[:, H:], hn, cn)
+    assert torch.equal(out[:, H:], y_ref[0]) and torch.equal(hn, hn_ref[0]) and torch.equal(cn, cn_ref[0])
+    assert float(out[:, :H].abs().max()) == 0.0
+    assert m.forward_step(xbuf[:, :I], h0[0], c0[0], out[:, :H], hn, cn, residual=res[:, H:])
+    assert torch.equal(out[:, :H], ops.add_f16(y_ref[0].contiguous(), res[:, H:].contiguous()))
+    assert torch.equal(hn, hn_ref[0])
+    small = ops.Lstm(ps, 1, False, I, H, True)
+    assert not small.forward_step(xbuf[:4, :I], h0[0, :4].contiguous(), c0[0, :4].contiguous(), out[:4, :H], hn[:4], cn[:4])
