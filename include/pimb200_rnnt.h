@@ -80,6 +80,9 @@ int pimb200_rnnt_last_status(pimb200_rnnt* h);
 /* ---- diagnostics and test hooks (no counterpart in the reference) ---- */
 /* Bounded waits of both encoder stacks, in polls (see pimb200_lstm_set_poll_limit): fault tests shrink it to 1. */
 int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit);
+
+/* pimb200_lstm_set_wavefront for both encoder stacks (default on). */
+int pimb200_rnnt_set_wavefront(pimb200_rnnt* h, int on);
 /* Device buffer of (T / stack_factor) * 8 int64 that the greedy kernel fills with per-frame clocks of utterance 0
  * (NULL switches it off).  Not owned by the handle. */
 int pimb200_rnnt_set_trace(pimb200_rnnt* h, long long* device_buffer);

@@ -63,6 +63,8 @@ SIGNATURES = {
     "pimb200_lstm_destroy": (_i, [_vp]),
     "pimb200_lstm_set_variant": (_i, [_vp, _i]),
     "pimb200_lstm_set_packed_lockstep": (_i, [_vp, _i]),
+    "pimb200_lstm_set_wavefront": (_i, [_vp, _i]),
+    "pimb200_rnnt_set_wavefront": (_i, [_vp, _i]),
     "pimb200_lstm_forward_step": (_i, [_vp, _vp, C.c_long, _i, _vp, _vp, _vp, C.c_long, _vp, _vp, _vp, C.c_long, _vp]),
     "pimb200_lstm_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "pimb200_lstm_forward_packed": (_i, [_vp, _vp, C.POINTER(C.c_int64), _i, _vp, _vp, _vp, _vp, _vp, _vp]),

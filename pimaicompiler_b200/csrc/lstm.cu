@@ -1042,6 +1042,253 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 }
 
 // ---------------------------------------------------------------------------------------------
+// two stacked layers as a wavefront (up to 8 sequences, H a multiple of 16 up to 1024): layer A at timestep s and layer
+// B at timestep s - 1 in the same step of ONE launch, so a pair of layers costs T + 1 dependent steps instead of 2T.
+// It is the wide kernel with its two sequence tiles given to the two layers: slots 0..7 of the exchange records and of
+// the hidden-state buffer hold layer A's sequences, slots 8..15 layer B's; the warps of tile half 0 keep layer A's
+// W_hh slice in registers, those of tile half 1 layer B's, and the exchange moves both layers' states in the same
+// records, flags and bulk copies.  Layer B's input is layer A's output of the previous step, which every CTA already
+// holds after the gather: the warps of tile half 1 add W_ih(B) . h_A(s - 1) into the same accumulators as
+// W_hh(B) . h_B(s - 2), with their 32 rows of W_ih(B) kept in shared memory (read as mma A fragments, rows padded by
+// 16 bytes: conflict-free).  Layer A's input projection stays hoisted (G); layer B has none.
+// ---------------------------------------------------------------------------------------------
+struct WaveArgs {
+    const __half* Whh[2];      // packed [4H, H] of layer A, layer B
+    const __half* WihB;        // packed [4H, H]: layer B's input matrix
+    const float* bias[2];
+    const float* G;            // layer A's input-projection terms (fp32)
+    long g_tstride, g_bstride;
+    const __half* h0[2];
+    const __half* c0[2];
+    __half* y;                 // layer B's output
+    long y_tstride, y_bstride;
+    int y_vec;
+    __half* hn[2];
+    __half* cn[2];
+    uint4* data;
+    uint32_t* flags;
+    uint32_t tag_base;
+    int* status;
+    int gen;
+    int H, T, B;
+    int poll_limit;
+};
+
+__global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(WaveArgs a) {
+    constexpr int BP = 16;                           // slots: 8 per layer
+    constexpr int ZP = BP + 1;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, T = a.T, B = a.B;
+    const int wp = H + 8;                            // row pitch of the W_ih(B) slice (halves)
+    __half* hs = reinterpret_cast<__half*>(smem_raw);                         // [H/8][BP][8]
+    float* zpart = reinterpret_cast<float*>(hs + (size_t)BP * H);             // [kWideKq][8 units][ZP][4 gates]
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + (size_t)kWideKq * 8 * ZP * 4);  // [BP][8]
+    __half* wib = reinterpret_cast<__half*>(hpub + (size_t)BP * 8);           // [32 rows][wp]
+    uint64_t* gbar = reinterpret_cast<uint64_t*>(wib + (size_t)32 * wp);
+    const uint32_t gbar_addr = (uint32_t)__cvta_generic_to_shared(gbar);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_cta = gridDim.x, cta = blockIdx.x;
+    const int u0 = cta * 8;
+    const int ktiles = H >> 4;
+    const int cpw = (n_cta + kPersistWarps - 1) / kPersistWarps;
+    if (tid == 0) {
+        pimb200::tc::mbar_init(gbar_addr, (uint32_t)((n_cta + cpw - 1) / cpw));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int kq = warp & (kWideKq - 1), nh = (warp >> 2) & 1;   // nh: the layer whose tile this warp multiplies
+    const int b_n = lane >> 2, b_k = (lane & 3) * 2;
+    uint32_t afrag[kWideMaxKtw][2][4];
+    {
+        const __half* wbase = a.Whh[nh] + (size_t)u0 * 4 * H;
+#pragma unroll
+        for (int i = 0; i < kWideMaxKtw; ++i)
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    afrag[i][m][r] = 0u;
+                    if (kWideKq * i + kq < ktiles) {
+                        const int row = m * 16 + b_n + (r & 1) * 8;
+                        const int k = (kWideKq * i + kq) * 16 + b_k + (r >> 1) * 8;
+                        afrag[i][m][r] = __ldg(reinterpret_cast<const uint32_t*>(wbase + (size_t)row * H + k));
+                    }
+                }
+    }
+    {
+        const int H8 = H >> 3;
+        const uint4* src = reinterpret_cast<const uint4*>(a.WihB + (size_t)u0 * 4 * H);
+        for (int i = tid; i < 32 * H8; i += kWideThreads) {
+            const int r = i / H8, c8 = i - r * H8;
+            *reinterpret_cast<uint4*>(wib + (size_t)r * wp + c8 * 8) = __ldg(src + (size_t)r * H8 + c8);
+        }
+    }
+    for (int i = tid; i < BP * H; i += kWideThreads) {
+        const int slot = i / H, k = i - slot * H, n = slot & 7;
+        const __half* h0 = a.h0[slot >> 3];
+        hs[((size_t)(k >> 3) * BP + slot) * 8 + (k & 7)] = (n < B && h0) ? h0[(size_t)n * H + k] : __float2half_rn(0.f);
+    }
+    for (int i = tid; i < BP * 8; i += kWideThreads) hpub[i] = 0;
+
+    // gate pair of this thread: unit tid / 16, slot tid % 16 (threads 128..255 have none)
+    const int gu = tid < 8 * BP ? tid / BP : 0, slot = tid < 8 * BP ? tid % BP : 0;
+    const int layer = slot >> 3, gn = slot & 7;
+    const bool live = tid < 8 * BP && gn < B;
+    float c = 0.f;
+    __half hh = __float2half_rn(0.f);
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f), gx = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+        const int u = u0 + gu;
+        c = a.c0[layer] ? __half2float(a.c0[layer][(size_t)gn * H + u]) : 0.f;
+        hh = a.h0[layer] ? a.h0[layer][(size_t)gn * H + u] : __float2half_rn(0.f);
+        bias4 = *reinterpret_cast<const float4*>(a.bias[layer] + (size_t)u * 4);
+        if (layer == 0) gx = __ldcg(reinterpret_cast<const float4*>(a.G + (size_t)gn * a.g_bstride + (size_t)u * 4));
+    }
+    __syncthreads();
+
+    for (int s = 0; s <= T; ++s) {
+        const int par = s & 1;
+        const bool act = layer == 0 ? (s < T) : (s >= 1);      // this thread's layer has a timestep in this step
+        const int t = layer == 0 ? s : s - 1;
+        // ---- 1. K-partial Z tiles: W_hh . h of the warp's layer, plus W_ih(B) . h_A for layer B
+        {
+            float acc[2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[m][i] = 0.f;
+            const __half* brow = hs + ((size_t)(nh * 8 + b_n)) * 8 + b_k;
+#pragma unroll
+            for (int i = 0; i < kWideMaxKtw; ++i) {
+                if (kWideKq * i + kq < ktiles) {   // warp-uniform
+                    const int kt = kWideKq * i + kq;
+                    const __half* hp = brow + (size_t)(2 * kt) * BP * 8;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
+                    mma_16816(acc[0], afrag[i][0], b0, b1);
+                    mma_16816(acc[1], afrag[i][1], b0, b1);
+                }
+            }
+            if (nh == 1) {
+                const __half* xrow = hs + (size_t)b_n * 8 + b_k;      // layer A's slots: tile 0
+#pragma unroll 4
+                for (int i = 0; i < kWideMaxKtw; ++i) {
+                    if (kWideKq * i + kq < ktiles) {
+                        const int kt = kWideKq * i + kq;
+                        const __half* hp = xrow + (size_t)(2 * kt) * BP * 8;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
+#pragma unroll
+                        for (int m = 0; m < 2; ++m) {
+                            const __half* ap = wib + (size_t)(m * 16 + b_n) * wp + kt * 16 + b_k;
+                            uint32_t af[4];
+                            af[0] = *reinterpret_cast<const uint32_t*>(ap);
+                            af[1] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp);
+                            af[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+                            af[3] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp + 8);
+                            mma_16816(acc[m], af, b0, b1);
+                        }
+                    }
+                }
+            }
+            float* zq = zpart + (size_t)kq * 8 * ZP * 4;
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = m * 16 + b_n + (i >> 1) * 8, n = nh * 8 + b_k + (i & 1);
+                    zq[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc[m][i];
+                }
+        }
+        __syncthreads();
+        // ---- 2. gates (a layer without a timestep in this step keeps its state)
+        if (live) {
+            if (act) {
+                float zi = gx.x + bias4.x, zf = gx.y + bias4.y, zg = gx.z + bias4.z, zo = gx.w + bias4.w;
+#pragma unroll
+                for (int k = 0; k < kWideKq; ++k) {
+                    const float4 zk = *reinterpret_cast<const float4*>(zpart + ((size_t)(k * 8 + gu) * ZP + slot) * 4);
+                    zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
+                }
+                c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
+                hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
+            }
+            const int u = u0 + gu;
+            hpub[slot * 8 + gu] = __half_as_ushort(hh);
+            if (act) {
+                if (layer == 1 && !a.y_vec) a.y[(size_t)t * a.y_tstride + (size_t)gn * a.y_bstride + u] = hh;
+                if (t == T - 1) {
+                    if (a.hn[layer]) a.hn[layer][(size_t)gn * H + u] = hh;
+                    if (a.cn[layer]) a.cn[layer][(size_t)gn * H + u] = __float2half_rn(c);
+                }
+            }
+        }
+        __syncthreads();
+        // ---- 3. publish both layers' records
+        if (tid < BP && (tid & 7) < B) {
+            const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
+            if (s < T) {
+                a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+            }
+            if (tid >= 8 && s >= 1 && a.y_vec)
+                *reinterpret_cast<uint4*>(a.y + (size_t)(s - 1) * a.y_tstride + (size_t)(tid & 7) * a.y_bstride + u0) = v;
+        }
+        if (s == T) break;
+        __syncthreads();
+        const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
+        if (tid < kBulkFlagCopies)
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+        // ---- 4./5. flags and gather, one group of CTAs per warp (as in the wide kernel)
+        int timed_out = 0;
+        {
+            const int c0 = warp * cpw;
+            const int c1 = c0 + cpw < n_cta ? c0 + cpw : n_cta;
+            if (c0 < n_cta) {   // warp-uniform
+                const int j = c0 + lane;
+                if (j < c1) {
+                    const uint32_t* f = a.flags + (((size_t)(cta % kBulkFlagCopies) * 2 + par) * n_cta + j) * 32;
+                    int polls = 0;
+                    while (true) {
+                        uint32_t v;
+                        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                        if (v == tag) break;
+                        if (++polls >= a.poll_limit) { timed_out = 1; break; }
+                        if ((polls & 1023) == 0 && status_aborted(a.status, a.gen)) { timed_out = 1; break; }
+                    }
+                    if (timed_out) status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+                    uint32_t v;
+                    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                }
+                const int lost = __any_sync(0xffffffffu, timed_out);
+                if (lane == 0 && !lost) {
+                    const uint32_t off = (uint32_t)c0 * BP * 16u, len = (uint32_t)(c1 - c0) * BP * 16u;
+                    pimb200::tc::mbar_expect_tx(gbar_addr, len);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                 "r"((uint32_t)__cvta_generic_to_shared(hs) + off),
+                                 "l"(reinterpret_cast<const unsigned char*>(a.data + (size_t)par * n_cta * BP) + off), "r"(len),
+                                 "r"(gbar_addr)
+                                 : "memory");
+                } else if (lane == 0) {
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(gbar_addr) : "memory");
+                }
+            }
+        }
+        // layer A's input-projection term of the next step
+        if (live && layer == 0 && s + 1 < T) {
+            const float* gp = a.G + (size_t)(s + 1) * a.g_tstride + (size_t)gn * a.g_bstride + (size_t)(u0 + gu) * 4;
+            asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(gx.x), "=f"(gx.y), "=f"(gx.z), "=f"(gx.w) : "l"(gp));
+        }
+        if (!pimb200::tc::mbar_wait(gbar_addr, (uint32_t)(s & 1), reinterpret_cast<const volatile int*>(a.status) + 1, a.gen)) {
+            for (uint32_t i = 0; i < (1u << 20); ++i)
+                if (pimb200::tc::mbar_try_wait(gbar_addr, (uint32_t)(s & 1))) break;
+            status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+            timed_out = 1;
+        }
+        if (__syncthreads_or(timed_out)) return;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // pipelined, warp-specialised variant of the register-resident recurrence (1..128 sequences, H <= 1024)
 //
 // Ownership: CTA (slice c, half b) owns hidden units UPC*c .. UPC*c + UPC - 1 (4*UPC gate rows of W_hh, kept in
@@ -1753,6 +2000,7 @@ struct pimb200_lstm {
     __half* pk_run = nullptr;
     size_t pk_run_cap = 0;
     int packed_lockstep = 1;   // 0: packed input runs timestep by timestep on the streamed kernels
+    int wavefront = 1;         // 1: stacked layers of up to 8 sequences run in pairs, one step apart, in one launch
     uint4* xchg = nullptr;  // [kXchgCopies][2][kXchgWords]
     uint4* bulk_data = nullptr;      // batched variant: [2][n_cta][32] records
     uint32_t* bulk_flags = nullptr;  // [2][n_cta]
@@ -1928,6 +2176,12 @@ extern "C" int pimb200_lstm_set_use_tc(pimb200_lstm* h, int on) {
 extern "C" int pimb200_lstm_set_bulk_wide(pimb200_lstm* h, int on) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     h->bulk_wide = on < 0 ? 0 : (on > 3 ? 3 : on);
+    return PIMB200_OK;
+}
+// A/B switch: 0 runs stacked layers one after the other, 1 (default) pairs of layers as a wavefront (up to 8 sequences).
+extern "C" int pimb200_lstm_set_wavefront(pimb200_lstm* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    h->wavefront = on ? 1 : 0;
     return PIMB200_OK;
 }
 // A/B switch: 0 runs packed input timestep by timestep on the streamed kernels, 1 (default) as a padded lock-step batch.
@@ -2366,6 +2620,49 @@ static int lstm_forward_packed_lockstep(pimb200_lstm* h, const __half* data, con
     return PIMB200_OK;
 }
 
+static size_t wave_smem(int H) {
+    return (size_t)16 * H * 2 + (size_t)kWideKq * 8 * 17 * 16 + (size_t)16 * 16 + (size_t)32 * (H + 8) * 2 + 16;
+}
+// Layers l and l + 1 (one direction) as a wavefront: true when the shape is the wave kernel's
+static bool wave_fits(const pimb200_lstm* h, int l, int T, int B, bool packed) {
+    const int H = h->H;
+    return h->wavefront && !packed && h->D == 1 && l + 1 < h->L && T >= 8 && B >= 1 && B <= 8 && H % 16 == 0 &&
+           H <= 16 * kWideKq * kWideMaxKtw && H / 8 <= h->sm_count && H / 8 <= kPersistThreads && h->bulk_wide >= 1 &&
+           (h->variant == PIMB200_LSTM_AUTO || h->variant == PIMB200_LSTM_PERSISTENT) && (int)wave_smem(H) <= h->max_smem_optin;
+}
+static int run_wave(pimb200_lstm* h, int l, int T, int B, const float* G, long g_tstride, long g_bstride, const __half* h0,
+                    const __half* c0, __half* y, long y_tstride, long y_bstride, __half* hn, __half* cn, cudaStream_t st) {
+    const int H = h->H;
+    WaveArgs a;
+    for (int k = 0; k < 2; ++k) {
+        const size_t off = (size_t)(l + k) * B * H;
+        a.Whh[k] = h->w_hh[l + k];
+        a.bias[k] = h->bias[l + k];
+        a.h0[k] = h0 ? h0 + off : nullptr;
+        a.c0[k] = c0 ? c0 + off : nullptr;
+        a.hn[k] = hn ? hn + off : nullptr;
+        a.cn[k] = cn ? cn + off : nullptr;
+    }
+    a.WihB = h->w_ih[l + 1];
+    a.G = G; a.g_tstride = g_tstride; a.g_bstride = g_bstride;
+    a.y = y; a.y_tstride = y_tstride; a.y_bstride = y_bstride;
+    a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
+    a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
+    a.H = H; a.T = T; a.B = B; a.poll_limit = h->poll_limit;
+    h->bulk_tag += (uint32_t)T + 2u;
+    const size_t smem = wave_smem(H);
+    const void* fn = (const void*)lstm_persistent_wave_kernel;
+    PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    void* kargs[] = {&a};
+    if (h->prof) prof_mark(h, st);
+    PIMB200_CUDA_TRY(cudaLaunchCooperativeKernel(fn, dim3(H / 8), dim3(kWideThreads), kargs, smem, st));
+    if (h->prof) {
+        prof_mark(h, st);
+        h->prof_bytes += 2.0 * T * 4.0 * H * H * 2.0;   // two layers' W_hh per timestep
+    }
+    return PIMB200_OK;
+}
+
 static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& sq, const __half* h0,
                              const __half* c0, __half* y, __half* hn, __half* cn, int batch_first,
                              cudaStream_t st) {
@@ -2452,6 +2749,16 @@ static int lstm_forward_impl(pimb200_lstm* h, const __half* x, const SeqLayout& 
                 rc = launch_gemm_wx(h->w_ih[ld], X, nullptr, h->G, 4 * H, Il, (int)rows, Il, 4 * H, PIMB200_ACT_NONE, 1,
                                     st);
             if (rc != PIMB200_OK) return rc;
+            if (wave_fits(h, l, T, B, packed)) {
+                // layers l and l + 1 in one launch, one step apart; the pair's output is layer l + 1's
+                const bool last2 = (l + 1 == L - 1);
+                __half* Y2 = last2 ? y : h->ybuf[(l + 1) & 1];
+                const long o_t = (last2 && batch_first) ? 1 : B, o_b = (last2 && batch_first) ? T : 1;
+                rc = run_wave(h, l, T, B, h->G, g_t * 4 * H, g_b * 4 * H, h0, c0, Y2, o_t * (long)H, o_b * (long)H, hn, cn, st);
+                if (rc != PIMB200_OK) return rc;
+                ++l;   // the second layer of the pair is done
+                break;
+            }
             const __half* h0_ld = h0 ? h0 + (size_t)ld * B * H : nullptr;
             const __half* c0_ld = c0 ? c0 + (size_t)ld * B * H : nullptr;
             __half* hn_ld = hn ? hn + (size_t)ld * B * H : nullptr;

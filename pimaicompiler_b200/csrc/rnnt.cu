@@ -1245,6 +1245,7 @@ extern "C" int pimb200_rnnt_set_greedy_multi(pimb200_rnnt* h, int on) {
 
 extern "C" int pimb200_lstm_last_status(pimb200_lstm* h);
 extern "C" int pimb200_lstm_set_poll_limit(pimb200_lstm* h, int limit);
+extern "C" int pimb200_lstm_set_wavefront(pimb200_lstm* h, int on);
 extern "C" int pimb200_gemm_last_status(void);
 
 // First non-zero status word among the kernels a decode launches (both encoder stacks' recurrences, the tensor-core
@@ -1262,6 +1263,13 @@ extern "C" int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     const int rc = pimb200_lstm_set_poll_limit(h->pre, limit);
     return rc != PIMB200_OK ? rc : pimb200_lstm_set_poll_limit(h->post, limit);
+}
+
+// A/B switch of both encoder stacks: layers in pairs as a wavefront for up to 8 utterances (see pimb200_lstm_set_wavefront).
+extern "C" int pimb200_rnnt_set_wavefront(pimb200_rnnt* h, int on) {
+    if (!h) return PIMB200_ERR_BAD_ARG;
+    const int rc = pimb200_lstm_set_wavefront(h->pre, on);
+    return rc != PIMB200_OK ? rc : pimb200_lstm_set_wavefront(h->post, on);
 }
 
 // Diagnostics: device buffer of (T/stack)*8 int64 filled with per-frame clocks of utterance 0.

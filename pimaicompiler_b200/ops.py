@@ -396,6 +396,9 @@ class Lstm:
     def last_status(self) -> int:
         return _lib.lib().pimb200_lstm_last_status(self._h)
 
+    def set_wavefront(self, on: bool) -> None:
+        check(_lib.lib().pimb200_lstm_set_wavefront(self._h, 1 if on else 0), "lstm_set_wavefront")
+
     def set_packed_lockstep(self, on: bool) -> None:
         check(_lib.lib().pimb200_lstm_set_packed_lockstep(self._h, 1 if on else 0), "lstm_set_packed_lockstep")
 

@@ -79,6 +79,10 @@ class RnntDecoder:
         """Raises when a kernel of an earlier decode gave up; call after synchronising ``decode_into``'s stream."""
         check(self.last_status(), where)
 
+    def set_wavefront(self, on: bool) -> None:
+        """Encoder layers in pairs, one step apart, for calls of up to 8 utterances (default on)."""
+        check(_lib.lib().pimb200_rnnt_set_wavefront(self._h, 1 if on else 0), "rnnt_set_wavefront")
+
     def set_poll_limit(self, limit: int) -> None:
         """Test hook: iteration limit of the encoder recurrences' bounded waits."""
         check(_lib.lib().pimb200_rnnt_set_poll_limit(self._h, int(limit)), "rnnt_set_poll_limit")

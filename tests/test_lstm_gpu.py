@@ -365,3 +365,29 @@ def test_lstm_decode_step_with_strided_rows_and_residual(B, I, H):
     assert torch.equal(hn, hn_ref[0])
     small = ops.Lstm(ps, 1, False, I, H, True)
     assert not small.forward_step(xbuf[:4, :I], h0[0, :4].contiguous(), c0[0, :4].contiguous(), out[:4, :H], hn[:4], cn[:4])
+
+
+@pytest.mark.parametrize("T,B,I,H,L,bf", [(20, 1, 240, 128, 2, False), (9, 3, 24, 64, 3, True), (12, 8, 40, 256, 4, False),
+                                          (1000, 1, 240, 1024, 2, False), (33, 2, 2048, 1024, 3, False)])
+def test_lstm_layer_wavefront_matches_oracle_and_sequential_layers(T, B, I, H, L, bf):
+    # stacked layers of up to 8 sequences run in pairs, one step apart, in one launch (the batch-1 latency path): against
+    # the C oracle, and against the same handle with the layers run one after the other
+    ops = _ops()
+    g = torch.Generator().manual_seed(T * 7 + H + L)
+    ps = lstm_params(L, 1, I, H, g, scale=1 / 32 if H >= 1024 else None)
+    x = h16(torch.randn((B, T, I) if bf else (T, B, I), generator=g))
+    h0 = h16(torch.randn(L, B, H, generator=g) * 0.5)
+    c0 = h16(torch.randn(L, B, H, generator=g) * 0.5)
+    m = ops.Lstm([to_dev(p) for p in ps], L, False, I, H, True)
+    y, hn, cn = m.forward(to_dev(x), to_dev(h0), to_dev(c0), batch_first=bf)
+    y_again, _, _ = m.forward(to_dev(x), to_dev(h0), to_dev(c0), batch_first=bf)
+    assert m.last_status() == 0 and torch.equal(y, y_again)
+    m.set_wavefront(False)
+    ys, hns, cns = m.forward(to_dev(x), to_dev(h0), to_dev(c0), batch_first=bf)
+    assert_close(y, ys, LSTM_ATOL, LSTM_RTOL, "wavefront vs layer after layer: y")
+    assert_close(hn, hns, LSTM_ATOL, LSTM_RTOL, "wavefront vs layer after layer: h_n")
+    assert_close(cn, cns, LSTM_ATOL, LSTM_RTOL, "wavefront vs layer after layer: c_n")
+    if T <= 40:
+        ref = co.lstm(x.numpy(), [p.numpy() for p in ps], L, False, True, h0.numpy(), c0.numpy(), bf)
+        for name, a, b in zip(("y", "hn", "cn"), (y, hn, cn), ref):
+            assert_close(a, b, LSTM_ATOL, LSTM_RTOL, f"wavefront {name}")

@@ -104,6 +104,7 @@ def test_rnnt_batch_of_utterances_matches_single():
     n, T = 13, 600
     feats = torch.stack([to.make_features(T, cfg, 200 + i) for i in range(n)]).to(torch.float16).cuda()
     dec.set_greedy_multi(2)   # FMA lock-step kernel: same summation order as the one-utterance kernel
+    dec.set_wavefront(False)  # calls of up to 8 utterances would otherwise pair the encoder layers (another summation order)
     toks, logits = dec.decode(feats, want_logits=True)
     # lock-step encoding of several utterances must not change any utterance's result: the per-sequence
     # arithmetic (tensor-core tile column, fp32 accumulation order) is the same at every batch size
