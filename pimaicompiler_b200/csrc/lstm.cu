@@ -1048,9 +1048,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 // the hidden-state buffer hold layer A's sequences, slots 8..15 layer B's; the warps of tile half 0 keep layer A's
 // W_hh slice in registers, those of tile half 1 layer B's, and the exchange moves both layers' states in the same
 // records, flags and bulk copies.  Layer B's input is layer A's output of the previous step, which every CTA already
-// holds after the gather: the warps of tile half 1 add W_ih(B) . h_A(s - 1) into the same accumulators as
-// W_hh(B) . h_B(s - 2), with their 32 rows of W_ih(B) kept in shared memory (read as mma A fragments, rows padded by
-// 16 bytes: conflict-free).  Layer A's input projection stays hoisted (G); layer B has none.
+// holds after the gather: W_ih(B) . h_A(s - 1) is one more product per step, shared by all eight warps (a K quarter of one
+// m-tile each), with the CTA's 32 rows of W_ih(B) kept in shared memory (read as mma A fragments, rows padded by 16
+// bytes: conflict-free); its partials are summed by layer B's gate threads next to those of W_hh(B) . h_B(s - 2).
+// Layer A's input projection stays hoisted (G); layer B has none.
 // ---------------------------------------------------------------------------------------------
 struct WaveArgs {
     const __half* Whh[2];      // packed [4H, H] of layer A, layer B
@@ -1082,7 +1083,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
     const int wp = H + 8;                            // row pitch of the W_ih(B) slice (halves)
     __half* hs = reinterpret_cast<__half*>(smem_raw);                         // [H/8][BP][8]
     float* zpart = reinterpret_cast<float*>(hs + (size_t)BP * H);             // [kWideKq][8 units][ZP][4 gates]
-    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart + (size_t)kWideKq * 8 * ZP * 4);  // [BP][8]
+    float* zpart2 = zpart + (size_t)kWideKq * 8 * ZP * 4;                     // same shape: partials of W_ih(B) . h_A
+    unsigned short* hpub = reinterpret_cast<unsigned short*>(zpart2 + (size_t)kWideKq * 8 * ZP * 4);  // [BP][8]
     __half* wib = reinterpret_cast<__half*>(hpub + (size_t)BP * 8);           // [32 rows][wp]
     uint64_t* gbar = reinterpret_cast<uint64_t*>(wib + (size_t)32 * wp);
     const uint32_t gbar_addr = (uint32_t)__cvta_generic_to_shared(gbar);
@@ -1168,8 +1170,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
                     mma_16816(acc[1], afrag[i][1], b0, b1);
                 }
             }
-            if (nh == 1) {
+            // layer B's input product W_ih(B) . h_A, shared by all eight warps: warp (kq, nh) takes its K quarter of m-tile
+            // nh (with only the tile-half-1 warps doing it, they had twice the products of the others on the step's
+            // critical path); these partials go to a buffer of their own
+            {
+                float acc2[4] = {0.f, 0.f, 0.f, 0.f};
                 const __half* xrow = hs + (size_t)b_n * 8 + b_k;      // layer A's slots: tile 0
+                const __half* arow = wib + (size_t)(nh * 16 + b_n) * wp + b_k;
 #pragma unroll 4
                 for (int i = 0; i < kWideMaxKtw; ++i) {
                     if (kWideKq * i + kq < ktiles) {
@@ -1177,17 +1184,20 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
                         const __half* hp = xrow + (size_t)(2 * kt) * BP * 8;
                         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
                         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
-#pragma unroll
-                        for (int m = 0; m < 2; ++m) {
-                            const __half* ap = wib + (size_t)(m * 16 + b_n) * wp + kt * 16 + b_k;
-                            uint32_t af[4];
-                            af[0] = *reinterpret_cast<const uint32_t*>(ap);
-                            af[1] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp);
-                            af[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
-                            af[3] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp + 8);
-                            mma_16816(acc[m], af, b0, b1);
-                        }
+                        const __half* ap = arow + kt * 16;
+                        uint32_t af[4];
+                        af[0] = *reinterpret_cast<const uint32_t*>(ap);
+                        af[1] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp);
+                        af[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+                        af[3] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp + 8);
+                        mma_16816(acc2, af, b0, b1);
                     }
+                }
+                float* zq2 = zpart2 + (size_t)kq * 8 * ZP * 4;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = nh * 16 + b_n + (i >> 1) * 8, n = 8 + b_k + (i & 1);
+                    zq2[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc2[i];
                 }
             }
             float* zq = zpart + (size_t)kq * 8 * ZP * 4;
@@ -1208,6 +1218,13 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
                 for (int k = 0; k < kWideKq; ++k) {
                     const float4 zk = *reinterpret_cast<const float4*>(zpart + ((size_t)(k * 8 + gu) * ZP + slot) * 4);
                     zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
+                }
+                if (layer == 1) {
+#pragma unroll
+                    for (int k = 0; k < kWideKq; ++k) {
+                        const float4 zk = *reinterpret_cast<const float4*>(zpart2 + ((size_t)(k * 8 + gu) * ZP + slot) * 4);
+                        zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
+                    }
                 }
                 c = sigmoidf_(zf) * c + sigmoidf_(zi) * tanhf_(zg);
                 hh = __float2half_rn(sigmoidf_(zo) * tanhf_(c));
@@ -2621,7 +2638,7 @@ static int lstm_forward_packed_lockstep(pimb200_lstm* h, const __half* data, con
 }
 
 static size_t wave_smem(int H) {
-    return (size_t)16 * H * 2 + (size_t)kWideKq * 8 * 17 * 16 + (size_t)16 * 16 + (size_t)32 * (H + 8) * 2 + 16;
+    return (size_t)16 * H * 2 + (size_t)2 * kWideKq * 8 * 17 * 16 + (size_t)16 * 16 + (size_t)32 * (H + 8) * 2 + 16;
 }
 // Layers l and l + 1 (one direction) as a wavefront: true when the shape is the wave kernel's
 static bool wave_fits(const pimb200_lstm* h, int l, int T, int B, bool packed) {
