@@ -1043,15 +1043,15 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wide_kernel(B
 
 // ---------------------------------------------------------------------------------------------
 // two stacked layers as a wavefront (up to 8 sequences, H a multiple of 16 up to 1024): layer A at timestep s and layer
-// B at timestep s - 1 in the same step of ONE launch, so a pair of layers costs T + 1 dependent steps instead of 2T.
+// B at timestep s - 2 in the same step of ONE launch, so a pair of layers costs T + 2 dependent steps instead of 2T.
 // It is the wide kernel with its two sequence tiles given to the two layers: slots 0..7 of the exchange records and of
 // the hidden-state buffer hold layer A's sequences, slots 8..15 layer B's; the warps of tile half 0 keep layer A's
 // W_hh slice in registers, those of tile half 1 layer B's, and the exchange moves both layers' states in the same
-// records, flags and bulk copies.  Layer B's input is layer A's output of the previous step, which every CTA already
-// holds after the gather: W_ih(B) . h_A(s - 1) is one more product per step, shared by all eight warps (a K quarter of one
-// m-tile each), with the CTA's 32 rows of W_ih(B) kept in shared memory (read as mma A fragments, rows padded by 16
-// bytes: conflict-free); its partials are summed by layer B's gate threads next to those of W_hh(B) . h_B(s - 2).
-// Layer A's input projection stays hoisted (G); layer B has none.
+// records, flags and bulk copies.  Layer B's input is layer A's output, which every CTA holds after the gather:
+// W_ih(B) . h_A is one more product per step, shared by all eight warps (a K quarter of one m-tile each), with the CTA's
+// 32 rows of W_ih(B) kept in shared memory (read as mma A fragments, rows padded by 16 bytes: conflict-free); it is made
+// a step ahead of its use, under the exchange (see the step loop), and summed by layer B's gate threads next to the
+// partials of W_hh(B) . h_B.  Layer A's input projection stays hoisted (G); layer B has none.
 // ---------------------------------------------------------------------------------------------
 struct WaveArgs {
     const __half* Whh[2];      // packed [4H, H] of layer A, layer B
@@ -1147,11 +1147,15 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
     }
     __syncthreads();
 
-    for (int s = 0; s <= T; ++s) {
+    // Layer B runs TWO steps behind layer A: its input product W_ih(B) . h_A(t) is then computed from the states already in
+    // shared memory right after this CTA has released its flag, while the other CTAs' flags are still on their way (a
+    // stretch in which the warps would only spin), and lies ready in zpart2 when layer B's gates need it a step later.
+    // One step behind, that product sat between the gather and the gates, on the step's critical path (3.4 us per step).
+    for (int s = 0; s <= T + 1; ++s) {
         const int par = s & 1;
-        const bool act = layer == 0 ? (s < T) : (s >= 1);      // this thread's layer has a timestep in this step
-        const int t = layer == 0 ? s : s - 1;
-        // ---- 1. K-partial Z tiles: W_hh . h of the warp's layer, plus W_ih(B) . h_A for layer B
+        const bool act = layer == 0 ? (s < T) : (s >= 2);      // this thread's layer has a timestep in this step
+        const int t = layer == 0 ? s : s - 2;
+        // ---- 1. K-partial Z tiles: W_hh . h of the warp's layer
         {
             float acc[2][4];
 #pragma unroll
@@ -1168,36 +1172,6 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
                     const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
                     mma_16816(acc[0], afrag[i][0], b0, b1);
                     mma_16816(acc[1], afrag[i][1], b0, b1);
-                }
-            }
-            // layer B's input product W_ih(B) . h_A, shared by all eight warps: warp (kq, nh) takes its K quarter of m-tile
-            // nh (with only the tile-half-1 warps doing it, they had twice the products of the others on the step's
-            // critical path); these partials go to a buffer of their own
-            {
-                float acc2[4] = {0.f, 0.f, 0.f, 0.f};
-                const __half* xrow = hs + (size_t)b_n * 8 + b_k;      // layer A's slots: tile 0
-                const __half* arow = wib + (size_t)(nh * 16 + b_n) * wp + b_k;
-#pragma unroll 4
-                for (int i = 0; i < kWideMaxKtw; ++i) {
-                    if (kWideKq * i + kq < ktiles) {
-                        const int kt = kWideKq * i + kq;
-                        const __half* hp = xrow + (size_t)(2 * kt) * BP * 8;
-                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
-                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
-                        const __half* ap = arow + kt * 16;
-                        uint32_t af[4];
-                        af[0] = *reinterpret_cast<const uint32_t*>(ap);
-                        af[1] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp);
-                        af[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
-                        af[3] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp + 8);
-                        mma_16816(acc2, af, b0, b1);
-                    }
-                }
-                float* zq2 = zpart2 + (size_t)kq * 8 * ZP * 4;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int r = nh * 16 + b_n + (i >> 1) * 8, n = 8 + b_k + (i & 1);
-                    zq2[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc2[i];
                 }
             }
             float* zq = zpart + (size_t)kq * 8 * ZP * 4;
@@ -1219,7 +1193,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
                     const float4 zk = *reinterpret_cast<const float4*>(zpart + ((size_t)(k * 8 + gu) * ZP + slot) * 4);
                     zi += zk.x; zf += zk.y; zg += zk.z; zo += zk.w;
                 }
-                if (layer == 1) {
+                if (layer == 1) {   // the input product made during the previous step's exchange
 #pragma unroll
                     for (int k = 0; k < kWideKq; ++k) {
                         const float4 zk = *reinterpret_cast<const float4*>(zpart2 + ((size_t)(k * 8 + gu) * ZP + slot) * 4);
@@ -1243,18 +1217,49 @@ __global__ void __launch_bounds__(kWideThreads, 1) lstm_persistent_wave_kernel(W
         // ---- 3. publish both layers' records
         if (tid < BP && (tid & 7) < B) {
             const uint4 v = *reinterpret_cast<const uint4*>(hpub + tid * 8);
-            if (s < T) {
+            if (s <= T) {
                 a.data[((size_t)par * n_cta + cta) * BP + tid] = v;
                 asm volatile("fence.proxy.async.global;" ::: "memory");
             }
-            if (tid >= 8 && s >= 1 && a.y_vec)
-                *reinterpret_cast<uint4*>(a.y + (size_t)(s - 1) * a.y_tstride + (size_t)(tid & 7) * a.y_bstride + u0) = v;
+            if (tid >= 8 && s >= 2 && a.y_vec)
+                *reinterpret_cast<uint4*>(a.y + (size_t)(s - 2) * a.y_tstride + (size_t)(tid & 7) * a.y_bstride + u0) = v;
         }
-        if (s == T) break;
+        if (s == T + 1) break;
         __syncthreads();
         const uint32_t tag = a.tag_base + (uint32_t)s + 1u;
         if (tid < kBulkFlagCopies)
             asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + (((size_t)tid * 2 + par) * n_cta + cta) * 32), "r"(tag) : "memory");
+        // ---- 3b. layer B's input product for the NEXT step, from layer A's states still in shared memory (the output of
+        //      A's timestep s - 1, which B reaches at step s + 1): warp (kq, nh) takes its K quarter of m-tile nh.  The
+        //      barrier behind it keeps every warp's reads of hs ahead of the bulk copies issued below.
+        {
+            float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+            const __half* xrow = hs + (size_t)b_n * 8 + b_k;      // layer A's slots: tile 0
+            const __half* arow = wib + (size_t)(nh * 16 + b_n) * wp + b_k;
+#pragma unroll 4
+            for (int i = 0; i < kWideMaxKtw; ++i) {
+                if (kWideKq * i + kq < ktiles) {
+                    const int kt = kWideKq * i + kq;
+                    const __half* hp = xrow + (size_t)(2 * kt) * BP * 8;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(hp);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(hp + (size_t)BP * 8);
+                    const __half* ap = arow + kt * 16;
+                    uint32_t af[4];
+                    af[0] = *reinterpret_cast<const uint32_t*>(ap);
+                    af[1] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp);
+                    af[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+                    af[3] = *reinterpret_cast<const uint32_t*>(ap + (size_t)8 * wp + 8);
+                    mma_16816(acc2, af, b0, b1);
+                }
+            }
+            float* zq2 = zpart2 + (size_t)kq * 8 * ZP * 4;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = nh * 16 + b_n + (i >> 1) * 8, n = 8 + b_k + (i & 1);
+                zq2[((size_t)(r >> 2) * ZP + n) * 4 + (r & 3)] = acc2[i];
+            }
+        }
+        __syncthreads();
         // ---- 4./5. flags and gather, one group of CTAs per warp (as in the wide kernel)
         int timed_out = 0;
         {
@@ -2666,7 +2671,7 @@ static int run_wave(pimb200_lstm* h, int l, int T, int B, const float* G, long g
     a.y_vec = (aligned16(y) && y_tstride % 8 == 0 && y_bstride % 8 == 0) ? 1 : 0;
     a.data = h->bulk_data; a.flags = h->bulk_flags; a.tag_base = h->bulk_tag; a.status = h->d_status; a.gen = next_gen(h);
     a.H = H; a.T = T; a.B = B; a.poll_limit = h->poll_limit;
-    h->bulk_tag += (uint32_t)T + 2u;
+    h->bulk_tag += (uint32_t)T + 3u;
     const size_t smem = wave_smem(H);
     const void* fn = (const void*)lstm_persistent_wave_kernel;
     PIMB200_CUDA_TRY(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
