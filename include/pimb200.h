@@ -328,8 +328,8 @@ int pimb200_lstm_set_pipe_group_size(pimb200_lstm* h, int seqs);
 int pimb200_lstm_set_packed_lockstep(pimb200_lstm* h, int on);
 
 /* Stacked layers of a one-direction handle with up to 8 sequences (the batch-1 latency case) run in pairs as a wavefront
- * (default, on = 1): one cooperative launch advances layer l at timestep s and layer l + 1 at timestep s - 1 in the same
- * step, so a pair costs T + 1 dependent steps instead of 2T (H a multiple of 16 up to 1024, T >= 8).  Layer l + 1's
+ * (default, on = 1): one cooperative launch advances layer l at timestep s and layer l + 1 at timestep s - 2 in the same
+ * step, so a pair costs T + 2 dependent steps instead of 2T (H a multiple of 16 up to 1024, T >= 8).  Layer l + 1's
  * input product is then summed inside the recurrence instead of a hoisted GEMM: results agree with on = 0 within the
  * LSTM tolerance, not bit for bit. */
 int pimb200_lstm_set_wavefront(pimb200_lstm* h, int on);
