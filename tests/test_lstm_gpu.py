@@ -194,15 +194,15 @@ def test_lstm_outputs_alias_slices_of_caller_buffers():
     assert (cat_buf[..., 1024:] == 5).all() and (state_buf[:2] == 5).all() and (state_buf[4:] == 5).all()
 
 
-@pytest.mark.parametrize("B", [1, 4, 40])
-def test_persistent_bounded_wait_reports_timeout_and_context_survives(B):
+@pytest.mark.parametrize("B,L", [(1, 1), (4, 1), (40, 1), (2, 2)])
+def test_persistent_bounded_wait_reports_timeout_and_context_survives(B, L):
     # Fault handling without faulting anything: shrink the bounded wait to a single poll, so the hidden-state exchange
     # cannot complete in time; the kernel must give up, record ERR_TIMEOUT and return, and the next call (normal
-    # limit) must still be correct.
+    # limit) must still be correct.  L = 2 with two sequences is the layer-wavefront kernel.
     ops = _ops()
     from pimaicompiler_b200 import _lib
     g = torch.Generator().manual_seed(17)
-    T, I, H, L = 64, 32, 256, 1
+    T, I, H = 64, 32, 256
     ps = lstm_params(L, 1, I, H, g)
     x = h16(torch.randn(T, B, I, generator=g))
     m = ops.Lstm([to_dev(p) for p in ps], L, False, I, H, True)
