@@ -64,7 +64,67 @@ struct GreedyArgs {
     int PH, JH, V, blank;
     int smem_mask;         // bit i set = matrix i (Whh0, Wih1, Whh1, W1p, W2) is staged in shared memory
     long long* trace;      // optional diagnostics: 8 clocks per frame of utterance 0 (cluster 0, CTA 0)
+    int* status;           // device status block: [0] sticky error code, [1] generation of the launch that gave up
+    int gen;               // generation of this launch (never 0)
+    int poll_limit;        // bound of every wait on an exchange barrier, in polls
 };
+
+// ---- all-to-all exchange inside a cluster without cluster-wide barriers ------------------------------------
+// A cluster barrier after remote stores costs the sender a release of those stores (a round trip to every peer)
+// before it may even arrive.  Here every value travels as st.async: the store itself reports its bytes to an mbarrier
+// in the RECEIVING CTA, which therefore learns of the arrival one way, and the sender never waits.  Each exchange
+// has two mbarriers used alternately: a peer can be at most one exchange ahead (it needs this CTA's contribution to
+// pass its own wait), so bytes of use k+1 never meet a barrier still counting use k.
+constexpr long long kGreedyWaitCycles = 4000000000ll;   // about two seconds
+constexpr int kGreedyPollLimit = 1 << 26;
+__device__ __forceinline__ uint32_t g_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t g_mapa(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void g_st_async_b32(uint32_t dst, uint32_t v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(dst), "r"(v),
+                 "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void g_st_async_v2(uint32_t dst, const uint2& v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(dst),
+                 "r"(v.x), "r"(v.y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void g_st_async_v4(uint32_t dst, const uint4& v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst),
+                 "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void g_xbar_init(uint32_t bar) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void g_xbar_expect(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool g_xbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded: false = gave up (poll or time limit), or another CTA of this launch already did
+__device__ __forceinline__ bool g_xbar_wait(uint32_t bar, uint32_t parity, const int* status, int gen, int limit) {
+    if (g_xbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 1; i < limit; ++i) {
+        if (g_xbar_try(bar, parity)) return true;
+        if ((i & 255) == 0 && (status_aborted(status, gen) || clock64() - t0 > kGreedyWaitCycles)) return false;
+    }
+    return false;
+}
 
 constexpr int kGreedyThreads = 512;
 constexpr int kGreedyWarps = kGreedyThreads / 32;
@@ -95,7 +155,10 @@ __device__ __forceinline__ void rows_reduce(float* z) {
         for (int i = 0; i < NR; ++i) z[i] += __shfl_xor_sync(0xffffffffu, z[i], o);
 }
 
-template <int NRG, int NRJ, int NRV>  // rows per warp of the gate phases, the joint slice and the vocabulary
+// NRG / NRJ / NRV = rows per warp of the gate phases, the joint slice and the vocabulary.  XB = the three exchanges of
+// an evaluation travel as st.async with one mbarrier per receiver (needs PH % C == 0 and an even number of units per
+// CTA: the state moves in 32-bit words); otherwise plain remote stores and cluster barriers.
+template <int NRG, int NRJ, int NRV, bool XB>
 __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.num_blocks();
@@ -123,6 +186,8 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
     float* b2s = reinterpret_cast<float*>(carve((size_t)V * 4));            // output bias
     float* bias1s = reinterpret_cast<float*>(carve((size_t)4 * UP * 4));    // layer-1 bias of my rows
     float* P0s = reinterpret_cast<float*>(carve((size_t)V * 4 * UP * 4));   // [V][4UP] layer-0 input term of my rows
+    __half* hst = reinterpret_cast<__half*>(carve((size_t)UP * 2));         // new hidden values of my units, before they travel
+    const uint32_t xbar0 = g_smem_u32(carve(6 * 8));                        // exchange barriers [exchange 0..2][use & 1]
     const size_t slice = (size_t)4 * UP * PH * 2;
     // weight slices: staged in shared memory when they fit, else read in place (L2)
     const __half* Whh0 = a.Whh0 + (size_t)u0 * 4 * PH;
@@ -149,25 +214,52 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
         P0s[k * 4 * UP + r] = a.P0[(size_t)k * 4 * PH + (size_t)u0 * 4 + r];
     }
 
-    // Gate threads: thread (j, d) = (tid / C, tid % C) keeps the cell state of unit u0+j and writes the new hidden
-    // value into CTA d, so the C copies of a unit are produced by C threads in parallel (same inputs, same result).
-    const int gj = tid / C, gd = tid - gj * C;
+    // Gate threads.  With cluster barriers: thread (j, d) = (tid / C, tid % C) keeps the cell state of unit u0+j and
+    // writes the new hidden value into CTA d, so the C copies of a unit are produced by C threads in parallel (same
+    // inputs, same result).  With st.async: thread j < nu owns unit u0+j; the values are staged and sent as words.
+    const int gj = XB ? tid : tid / C, gd = XB ? 0 : tid - gj * C;
     const bool gate_thread = gj < nu;
     float c_l0 = 0.f, c_l1 = 0.f;  // fp32 cell states for the whole utterance
     long long* trp = nullptr;
+    uint32_t n_eval = 0;    // evaluations of this launch: use n_eval of an exchange takes barrier n_eval & 1, phase n_eval >> 1
+    bool dead = false;      // a wait of this thread ran out: no more waits, no more sends
+    if (XB && tid == 0) {
+        for (int i = 0; i < 6; ++i) g_xbar_init(xbar0 + 8u * i);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    auto xwait = [&](int x) {
+        if (dead) return;
+        if (!g_xbar_wait(xbar0 + 8u * (2 * x + (n_eval & 1u)), (n_eval >> 1) & 1u, a.status, a.gen, a.poll_limit)) {
+            dead = true;
+            status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+        }
+    };
+    // my units' staged values -> the same place of `dst_local` in every CTA, one 32-bit word a thread
+    auto send_state = [&](__half* dst_local, int x) {
+        const int W = nu >> 1;
+        if (tid < C * W && !dead) {
+            const int d = tid / W, w = tid - d * W;
+            g_st_async_b32(g_mapa(g_smem_u32(dst_local + u0) + 4u * w, d), reinterpret_cast<const uint32_t*>(hst)[w],
+                           g_mapa(xbar0 + 8u * (2 * x + (n_eval & 1u)), d));
+        }
+    };
 
     // One evaluation of the prediction network for input token `tok`, from the state left by the previous
     // evaluation (buffers of parity (e+1)&1), into buffers of parity e&1; then the pred half of the joint.
+    float zp0[NRG], zp1[NRG];  // Whh0 . h0 and Whh1 . h1 of the coming evaluation, per-lane partial sums
     auto pred_eval = [&](int tok, int e) {
-        const __half* h0prev = h0buf + (size_t)((e + 1) & 1) * PH;
         __half* h0new_local = h0buf + (size_t)(e & 1) * PH;
-        const __half* h1prev = h1buf + (size_t)((e + 1) & 1) * PH;
         __half* h1new_local = h1buf + (size_t)(e & 1) * PH;
+        if (XB && tid == 0) {   // what this CTA receives in the three exchanges of this evaluation
+            const uint32_t b = n_eval & 1u;
+            g_xbar_expect(xbar0 + 8u * b, PH * 2);
+            g_xbar_expect(xbar0 + 8u * (2 + b), PH * 2);
+            g_xbar_expect(xbar0 + 8u * (4 + b), JH * 4);
+        }
         float z[NRG];
-        // layer 0
+        // layer 0: the state product was made at the end of the previous evaluation
 #pragma unroll
-        for (int i = 0; i < NRG; ++i) z[i] = 0.f;
-        rows_dot<NRG>(Whh0, 4 * nu, PH, h0prev, warp, lane, z);
+        for (int i = 0; i < NRG; ++i) z[i] = zp0[i];
         rows_reduce<NRG>(z);
         if (lane == 0) {
 #pragma unroll
@@ -181,15 +273,22 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
         if (gate_thread) {
             const float zi = zrow[gj * 4], zf = zrow[gj * 4 + 1], zg = zrow[gj * 4 + 2], zo = zrow[gj * 4 + 3];
             c_l0 = sigmoidf_(zf) * c_l0 + sigmoidf_(zi) * tanhf_(zg);
-            cluster.map_shared_rank(h0new_local, gd)[u0 + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
+            const __half hv = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
+            if (XB) hst[gj] = hv;
+            else cluster.map_shared_rank(h0new_local, gd)[u0 + gj] = hv;
         }
-        cluster.sync();
+        if (XB) {
+            __syncthreads();
+            send_state(h0new_local, 0);
+            xwait(0);
+        } else {
+            cluster.sync();
+        }
         if (trp && tid == 0) trp[4] = clock64();
-        // layer 1
+        // layer 1: the input product continues the sums of the state product made ahead
 #pragma unroll
-        for (int i = 0; i < NRG; ++i) z[i] = 0.f;
+        for (int i = 0; i < NRG; ++i) z[i] = zp1[i];
         rows_dot<NRG>(Wih1, 4 * nu, PH, h0new_local, warp, lane, z);
-        rows_dot<NRG>(Whh1, 4 * nu, PH, h1prev, warp, lane, z);
         rows_reduce<NRG>(z);
         if (lane == 0) {
 #pragma unroll
@@ -202,9 +301,17 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
         if (gate_thread) {
             const float zi = zrow[gj * 4], zf = zrow[gj * 4 + 1], zg = zrow[gj * 4 + 2], zo = zrow[gj * 4 + 3];
             c_l1 = sigmoidf_(zf) * c_l1 + sigmoidf_(zi) * tanhf_(zg);
-            cluster.map_shared_rank(h1new_local, gd)[u0 + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
+            const __half hv = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
+            if (XB) hst[gj] = hv;
+            else cluster.map_shared_rank(h1new_local, gd)[u0 + gj] = hv;
         }
-        cluster.sync();
+        if (XB) {
+            __syncthreads();
+            send_state(h1new_local, 1);
+            xwait(1);
+        } else {
+            cluster.sync();
+        }
         if (trp && tid == 0) trp[5] = clock64();
         // prediction half of the joint: Pj[j] = W1p[j,:] . h1 ; lane d delivers the value to CTA d
         float zj[NRJ];
@@ -212,15 +319,31 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
         for (int i = 0; i < NRJ; ++i) zj[i] = 0.f;
         rows_dot<NRJ>(W1p, nj, PH, h1new_local, warp, lane, zj);
         rows_reduce<NRJ>(zj);
-        if (lane < C) {
+        if (lane < C && !(XB && dead)) {
 #pragma unroll
             for (int i = 0; i < NRJ; ++i) {
                 const int q = warp + kGreedyWarps * i;
-                if (q < nj) cluster.map_shared_rank(Pj, lane)[j0 + q] = zj[i];
+                if (q < nj) {
+                    if (XB)
+                        g_st_async_b32(g_mapa(g_smem_u32(Pj + j0 + q), lane), __float_as_uint(zj[i]),
+                                       g_mapa(xbar0 + 8u * (4 + (n_eval & 1u)), lane));
+                    else
+                        cluster.map_shared_rank(Pj, lane)[j0 + q] = zj[i];
+                }
             }
         }
         if (trp && tid == 0) trp[6] = clock64();
-        cluster.sync();
+        // The state products of the NEXT evaluation depend on no token: they run while the joint values travel (between
+        // the arrive and the wait of the cluster barrier in the other variant), and stay in registers, as per-lane
+        // partial sums, until that evaluation comes.
+        if (!XB) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+#pragma unroll
+        for (int i = 0; i < NRG; ++i) zp0[i] = zp1[i] = 0.f;
+        rows_dot<NRG>(Whh0, 4 * nu, PH, h0new_local, warp, lane, zp0);
+        rows_dot<NRG>(Whh1, 4 * nu, PH, h1new_local, warp, lane, zp1);
+        if (XB) xwait(2);
+        else asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        ++n_eval;
         if (trp && tid == 0) trp[7] = clock64();
     };
 
@@ -234,63 +357,72 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
         }
         c_l0 = 0.f;
         c_l1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NRG; ++i) zp0[i] = zp1[i] = 0.f;  // products with the zero state
         cluster.sync();  // staged weights and zeroed states visible; nobody still writes into my buffers
         int e = 0, n_emit = 0;
-        trp = nullptr;
-        pred_eval(a.blank, e++);  // start of sequence: the blank row of the embedding, zero state
         float e_next[2] = {0.f, 0.f};  // E[t+1] for z elements tid and tid+nthr
         if (a.Tp > 0) {
             if (tid < JH) e_next[0] = __ldcg(E + tid);
             if (tid + nthr < JH) e_next[1] = __ldcg(E + tid + nthr);
         }
-        for (int t = 0; t < a.Tp; ++t) {
-            trp = (a.trace && utt == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
-            if (trp && tid == 0) trp[0] = clock64();
-            const float e_cur0 = e_next[0], e_cur1 = e_next[1];
-            if (t + 1 < a.Tp) {
-                if (tid < JH) e_next[0] = __ldcg(E + (size_t)(t + 1) * JH + tid);
-                if (tid + nthr < JH) e_next[1] = __ldcg(E + (size_t)(t + 1) * JH + tid + nthr);
-            }
-            if (tid < JH) zs[tid] = __float2half_rn(fmaxf(e_cur0 + Pj[tid], 0.f));
-            if (tid + nthr < JH) zs[tid + nthr] = __float2half_rn(fmaxf(e_cur1 + Pj[tid + nthr], 0.f));
-            __syncthreads();
-            float zv[NRV];
-#pragma unroll
-            for (int i = 0; i < NRV; ++i) zv[i] = 0.f;
-            rows_dot<NRV>(W2, V, JH, zs, warp, lane, zv);
-            rows_reduce<NRV>(zv);
-            if (lane == 0) {
-#pragma unroll
-                for (int i = 0; i < NRV; ++i) {
-                    const int r = warp + kGreedyWarps * i;
-                    if (r < V) lg[r] = zv[i] + b2s[r];
+        // iteration -1 is the start of sequence: the blank row of the embedding, zero state (one inlined copy of the
+        // evaluation serves both: the loop body is the kernel's instruction footprint)
+        for (int t = -1; t < a.Tp; ++t) {
+            int tok = a.blank;
+            trp = nullptr;
+            if (t >= 0) {
+                trp = (a.trace && utt == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
+                if (trp && tid == 0) trp[0] = clock64();
+                const float e_cur0 = e_next[0], e_cur1 = e_next[1];
+                if (t + 1 < a.Tp) {
+                    if (tid < JH) e_next[0] = __ldcg(E + (size_t)(t + 1) * JH + tid);
+                    if (tid + nthr < JH) e_next[1] = __ldcg(E + (size_t)(t + 1) * JH + tid + nthr);
                 }
-            }
-            __syncthreads();
-            if (trp && tid == 0) trp[1] = clock64();
-            // argmax, first maximum wins; every warp repeats it, so no broadcast is needed
-            float bv = -INFINITY;
-            int best = 0x7fffffff;
-            for (int r = lane; r < V; r += 32) {
-                const float v = lg[r];
-                if (v > bv) { bv = v; best = r; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, best, o);
-                if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
-            }
-            if (rank == 0 && logits && tid < V) logits[(size_t)t * V + tid] = lg[tid];
-            if (trp && tid == 0) trp[2] = clock64();
-            if (best != a.blank) {
+                if (tid < JH) zs[tid] = __float2half_rn(fmaxf(e_cur0 + Pj[tid], 0.f));
+                if (tid + nthr < JH) zs[tid + nthr] = __float2half_rn(fmaxf(e_cur1 + Pj[tid + nthr], 0.f));
+                __syncthreads();
+                float zv[NRV];
+    #pragma unroll
+                for (int i = 0; i < NRV; ++i) zv[i] = 0.f;
+                rows_dot<NRV>(W2, V, JH, zs, warp, lane, zv);
+                rows_reduce<NRV>(zv);
+                if (lane == 0) {
+    #pragma unroll
+                    for (int i = 0; i < NRV; ++i) {
+                        const int r = warp + kGreedyWarps * i;
+                        if (r < V) lg[r] = zv[i] + b2s[r];
+                    }
+                }
+                __syncthreads();
+                if (trp && tid == 0) trp[1] = clock64();
+                // argmax, first maximum wins; every warp repeats it, so no broadcast is needed
+                float bv = -INFINITY;
+                int best = 0x7fffffff;
+                for (int r = lane; r < V; r += 32) {
+                    const float v = lg[r];
+                    if (v > bv) { bv = v; best = r; }
+                }
+    #pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, best, o);
+                    if (ov > bv || (ov == bv && oi < best)) { bv = ov; best = oi; }
+                }
+                if (rank == 0 && logits && tid < V) logits[(size_t)t * V + tid] = lg[tid];
+                if (trp && tid == 0) trp[2] = clock64();
+                if (best == a.blank) continue;
                 if (rank == 0 && tid == 0) tokens[n_emit] = best;
                 ++n_emit;
-                pred_eval(best, e++);  // commits the pending state and evaluates the new label
+                tok = best;
             }
+            pred_eval(tok, e++);  // commits the pending state and evaluates the new label
         }
         if (rank == 0 && tid == 0) a.n_tokens[utt] = n_emit;
     }
+    // after a wait that ran out, a peer's stores may still be on their way to this CTA: let them land
+    if (XB && (dead || status_aborted(a.status, a.gen)))
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
     cluster.sync();  // no CTA leaves while a peer may still address its shared memory
 }
 
@@ -440,11 +572,12 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_multi_kernel(Gr
 #pragma unroll
                 for (int m = 0; m < M; ++m) z[i][m] = 0.f;
 #pragma unroll
-            for (int m = 0; m < M; ++m) hp[m] = h0buf + ((size_t)m * 2 + (e[m] & 1)) * PH;
-            rows_dot_multi<NRG, M>(Wih1, 4 * nu, PH, hp, mask, warp, lane, z);
-#pragma unroll
+            // state product first, input product second: the summation order of the one-utterance kernel
             for (int m = 0; m < M; ++m) hp[m] = h1buf + ((size_t)m * 2 + ((e[m] + 1) & 1)) * PH;
             rows_dot_multi<NRG, M>(Whh1, 4 * nu, PH, hp, mask, warp, lane, z);
+#pragma unroll
+            for (int m = 0; m < M; ++m) hp[m] = h0buf + ((size_t)m * 2 + (e[m] & 1)) * PH;
+            rows_dot_multi<NRG, M>(Wih1, 4 * nu, PH, hp, mask, warp, lane, z);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
@@ -695,7 +828,22 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
     float* b2s = reinterpret_cast<float*>(carve((size_t)32 * 4));
     float* bias1s = reinterpret_cast<float*>(carve((size_t)RG * 4));
     int* best_s = reinterpret_cast<int*>(carve((size_t)M * 4));
+    // exchange barriers [exchange 0..2 = layer-0 state, layer-1 state, joint half][use & 1]
+    const uint32_t xbar0 = g_smem_u32(carve(6 * 8));
     const __half* W1p = a.W1p + (size_t)j0 * PH;  // read through L1: no room left in shared memory
+    if (tid == 0) {
+        for (int i = 0; i < 6; ++i) g_xbar_init(xbar0 + 8u * i);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    uint32_t n_eval = 0;    // evaluations so far: use n_eval of every exchange takes barrier n_eval & 1, phase n_eval >> 1
+    bool dead = false;      // a wait of this thread ran out: no more waits, no more sends
+    auto xwait = [&](int x) {
+        if (dead) return;
+        if (!g_xbar_wait(xbar0 + 8u * (2 * x + (n_eval & 1u)), (n_eval >> 1) & 1u, a.status, a.gen, a.poll_limit)) {
+            dead = true;
+            status_raise(a.status, a.gen, PIMB200_ERR_TIMEOUT);
+        }
+    };
 
     stage_swizzled(Whh0, a.Whh0 + (size_t)u0 * 4 * PH, RG, RG, PH, tid, nthr);
     stage_swizzled(Wih1, a.Wih1 + (size_t)u0 * 4 * PH, RG, RG, PH, tid, nthr);
@@ -763,22 +911,29 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         // evaluation out simply produces a value nobody stores.
         long long* trp = nullptr;
         // new state values of this CTA (stage[n][0..UP)) -> plane (par>>n)&1 of `buf` in every CTA, 8 bytes a store
-        auto scatter_state = [&](__half* buf, unsigned mask) {
+        auto scatter_state = [&](__half* buf, unsigned mask, int x) {
+            const uint32_t bar = xbar0 + 8u * (2 * x + (n_eval & 1u));
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int it = h_item[q];
-                if (it >= 0) {
+                if (it >= 0 && !dead) {
                     const int d = it >> 16, n = (it >> 8) & 0xff, c = it & 0xff;
                     if (mask & (1u << n)) {
                         const uint2 v = *reinterpret_cast<const uint2*>(stage + n * UP + c * 4);
                         __half* dstl = buf + ((size_t)((par >> n) & 1u) * M + n) * hp + u0 + c * 4;
-                        *reinterpret_cast<uint2*>(cluster.map_shared_rank(dstl, d)) = v;
+                        g_st_async_v2(g_mapa(g_smem_u32(dstl), d), v, g_mapa(bar, d));
                     }
                 }
             }
         };
         auto pred_eval = [&](unsigned mask) {
             const bool mine = gate_thread && (mask & (1u << gn));
+            if (tid == 0) {   // what this CTA will receive in the three exchanges of this evaluation
+                const uint32_t nm = (uint32_t)__popc(mask), b = n_eval & 1u;
+                g_xbar_expect(xbar0 + 8u * b, nm * PH * 2);
+                g_xbar_expect(xbar0 + 8u * (2 + b), nm * PH * 2);
+                g_xbar_expect(xbar0 + 8u * (4 + b), nm * JH * 2);
+            }
             // input term of layer 0 for the symbol just emitted: fetched now, used after the first product
             float4 p0v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (mine) p0v = __ldg(reinterpret_cast<const float4*>(a.P0 + (size_t)best_s[gn] * 4 * PH + (size_t)(u0 + gj) * 4));
@@ -805,16 +960,14 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 stage[gn * UP + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l0));
             }
             __syncthreads();
-            scatter_state(h0buf, mask);
-            // the state product of layer 1 does not depend on the exchange in flight: it runs between the arrive and the
-            // wait of the cluster barrier
-            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            scatter_state(h0buf, mask, 0);
+            // the state product of layer 1 does not depend on the exchange in flight: it runs while the values travel
             if (role == 2) {
                 const int n = lane >> 2;
                 const unsigned pn = (par >> n) & 1u;
                 mma_rows_smem(acc2, Whh1, PH, mt_w, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
             }
-            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            xwait(0);
             if (trp && tid == 0) trp[5] = clock64();
             // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias: role 0 takes the first K half, role 2 adds the
             //      second half to the product it already holds
@@ -842,8 +995,8 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 stage[gn * UP + gj] = __float2half_rn(sigmoidf_(zo) * tanhf_(c_l1));
             }
             __syncthreads();
-            scatter_state(h1buf, mask);
-            cluster.sync();
+            scatter_state(h1buf, mask, 1);
+            xwait(1);
             if (trp && tid == 0) trp[6] = clock64();
             // ---- prediction half of the joint: Pj[n][j0 + q] = W1p[q,:] . h1new[n]; four K quarters per m-tile
             if (warp < 4 * MTJ) {
@@ -865,17 +1018,18 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             __syncthreads();
             if (j_item >= 0) {
                 const int d = j_item >> 16, n = (j_item >> 8) & 0xff, c = j_item & 0xff;
-                if (mask & (1u << n)) {
+                if ((mask & (1u << n)) && !dead) {
                     const uint4 v = *reinterpret_cast<const uint4*>(stage + n * JP + c * 8);
-                    *reinterpret_cast<uint4*>(cluster.map_shared_rank(Pj + (size_t)n * JH + j0 + c * 8, d)) = v;
+                    g_st_async_v4(g_mapa(g_smem_u32(Pj + (size_t)n * JH + j0 + c * 8), d), v,
+                                  g_mapa(xbar0 + 8u * (4 + (n_eval & 1u)), d));
                 }
             }
-            cluster.sync();
+            xwait(2);
             if (trp && tid == 0) trp[7] = clock64();
             par ^= mask;
+            ++n_eval;
         };
 
-        pred_eval(valid);  // start of sequence
         // E of the next frame is fetched one frame ahead (its L2 latency would otherwise open every frame)
         // When JH equals the block size (the benchmark's 512) a thread owns 8 consecutive columns of one utterance: two
         // 16-byte loads of E, one of Pj and one 16-byte store of z per frame, and no division in the frame loop.
@@ -895,68 +1049,74 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             }
         };
         if (square) load_E(0);
-        for (int t = 0; t < a.Tp; ++t) {
-            trp = (a.trace && grp == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
-            if (trp && tid == 0) trp[0] = clock64();
-            // ---- joint input z[n] = relu(E[n][t] + Pj[n]) in fp16
-            if (square) {
-                if (zlive) {
-                    const uint4 pj = *reinterpret_cast<const uint4*>(Pj + (size_t)zn * JH + zk);
-                    const float2 p0 = h2f2(pj.x), p1 = h2f2(pj.y), p2 = h2f2(pj.z), p3 = h2f2(pj.w);
-                    uint4 out;
-                    __half2 h;
-                    h = __floats2half2_rn(fmaxf(e_lo.x + p0.x, 0.f), fmaxf(e_lo.y + p0.y, 0.f)); out.x = *reinterpret_cast<uint32_t*>(&h);
-                    h = __floats2half2_rn(fmaxf(e_lo.z + p1.x, 0.f), fmaxf(e_lo.w + p1.y, 0.f)); out.y = *reinterpret_cast<uint32_t*>(&h);
-                    h = __floats2half2_rn(fmaxf(e_hi.x + p2.x, 0.f), fmaxf(e_hi.y + p2.y, 0.f)); out.z = *reinterpret_cast<uint32_t*>(&h);
-                    h = __floats2half2_rn(fmaxf(e_hi.z + p3.x, 0.f), fmaxf(e_hi.w + p3.y, 0.f)); out.w = *reinterpret_cast<uint32_t*>(&h);
-                    *reinterpret_cast<uint4*>(zs + (size_t)zn * zp + zk) = out;
-                }
-                load_E(t + 1);
-            } else {
-                for (int i = tid; i < M * JH; i += nthr) {
-                    const int n = i / JH, k = i - n * JH;
-                    if (valid & (1u << n)) {
-                        const float e = __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k);
-                        zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e + __half2float(Pj[i]), 0.f));
+        // iteration -1 is the start of sequence: every utterance evaluates the blank symbol from the zero state (one
+        // inlined copy of the evaluation serves both: the loop body is the kernel's instruction footprint)
+        for (int t = -1; t < a.Tp; ++t) {
+            unsigned emit = valid;
+            trp = nullptr;
+            if (t >= 0) {
+                trp = (a.trace && grp == 0 && rank == 0) ? a.trace + (size_t)t * 8 : nullptr;
+                if (trp && tid == 0) trp[0] = clock64();
+                // ---- joint input z[n] = relu(E[n][t] + Pj[n]) in fp16
+                if (square) {
+                    if (zlive) {
+                        const uint4 pj = *reinterpret_cast<const uint4*>(Pj + (size_t)zn * JH + zk);
+                        const float2 p0 = h2f2(pj.x), p1 = h2f2(pj.y), p2 = h2f2(pj.z), p3 = h2f2(pj.w);
+                        uint4 out;
+                        __half2 h;
+                        h = __floats2half2_rn(fmaxf(e_lo.x + p0.x, 0.f), fmaxf(e_lo.y + p0.y, 0.f)); out.x = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(fmaxf(e_lo.z + p1.x, 0.f), fmaxf(e_lo.w + p1.y, 0.f)); out.y = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(fmaxf(e_hi.x + p2.x, 0.f), fmaxf(e_hi.y + p2.y, 0.f)); out.z = *reinterpret_cast<uint32_t*>(&h);
+                        h = __floats2half2_rn(fmaxf(e_hi.z + p3.x, 0.f), fmaxf(e_hi.w + p3.y, 0.f)); out.w = *reinterpret_cast<uint32_t*>(&h);
+                        *reinterpret_cast<uint4*>(zs + (size_t)zn * zp + zk) = out;
+                    }
+                    load_E(t + 1);
+                } else {
+                    for (int i = tid; i < M * JH; i += nthr) {
+                        const int n = i / JH, k = i - n * JH;
+                        if (valid & (1u << n)) {
+                            const float e = __ldcg(a.E + ((size_t)(utt0 + n) * a.Tp + t) * JH + k);
+                            zs[(size_t)n * zp + k] = __float2half_rn(fmaxf(e + __half2float(Pj[i]), 0.f));
+                        }
                     }
                 }
-            }
-            __syncthreads();
-            if (trp && tid == 0) trp[1] = clock64();
-            // ---- logits[n][r] = W2[r,:] . z[n] + b2[r]: 2 m-tiles x 4 K quarters
-            if (warp < 8) {
-                const int mt = warp & 1, kq = warp >> 1;
-                const int per = (KTJ + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTJ - k_lo));
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                mma_rows_smem(acc, W2s, JH, mt, k_lo, k_n, zs, zp, lane);
-                store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
-            }
-            __syncthreads();
-            if (trp && tid == 0) trp[2] = clock64();
-            if (tid < M * 32) {
-                const int n = tid >> 5, r = tid & 31;   // warp n handles utterance n, lane = vocabulary row
-                float v = (part[(size_t)n * jl + r] + part[(size_t)(M + n) * jl + r]) +
-                          (part[(size_t)(2 * M + n) * jl + r] + part[(size_t)(3 * M + n) * jl + r]) + b2s[r];
-                // arg max over the 32 lanes, lowest index on ties: two warp reductions on an order-preserving integer
-                // image of the value (ten dependent shuffles measured ~2.6 k cycles here)
-                uint32_t key = __float_as_uint(v);
-                key = (key & 0x80000000u) ? ~key : (key | 0x80000000u);
-                const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
-                const int best = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (uint32_t)r : 0xffffffffu);
-                if (r == 0) best_s[n] = best;
-                if (rank == 0 && a.logits && r < V && (valid & (1u << n)))
-                    a.logits[((size_t)(utt0 + n) * a.Tp + t) * V + r] = v;
-            }
-            __syncthreads();
-            if (trp && tid == 0) trp[3] = clock64();
-            unsigned emit = 0;
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                const int best = best_s[m];
-                if ((valid & (1u << m)) && best != a.blank) {
-                    if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
-                    ++n_emit[m];
-                    emit |= 1u << m;
+                __syncthreads();
+                if (trp && tid == 0) trp[1] = clock64();
+                // ---- logits[n][r] = W2[r,:] . z[n] + b2[r]: 2 m-tiles x 4 K quarters
+                if (warp < 8) {
+                    const int mt = warp & 1, kq = warp >> 1;
+                    const int per = (KTJ + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTJ - k_lo));
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_rows_smem(acc, W2s, JH, mt, k_lo, k_n, zs, zp, lane);
+                    store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
+                }
+                __syncthreads();
+                if (trp && tid == 0) trp[2] = clock64();
+                if (tid < M * 32) {
+                    const int n = tid >> 5, r = tid & 31;   // warp n handles utterance n, lane = vocabulary row
+                    float v = (part[(size_t)n * jl + r] + part[(size_t)(M + n) * jl + r]) +
+                              (part[(size_t)(2 * M + n) * jl + r] + part[(size_t)(3 * M + n) * jl + r]) + b2s[r];
+                    // arg max over the 32 lanes, lowest index on ties: two warp reductions on an order-preserving integer
+                    // image of the value (ten dependent shuffles measured ~2.6 k cycles here)
+                    uint32_t key = __float_as_uint(v);
+                    key = (key & 0x80000000u) ? ~key : (key | 0x80000000u);
+                    const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
+                    const int best = (int)__reduce_min_sync(0xffffffffu, key == kmax ? (uint32_t)r : 0xffffffffu);
+                    if (r == 0) best_s[n] = best;
+                    if (rank == 0 && a.logits && r < V && (valid & (1u << n)))
+                        a.logits[((size_t)(utt0 + n) * a.Tp + t) * V + r] = v;
+                }
+                __syncthreads();
+                if (trp && tid == 0) trp[3] = clock64();
+                emit = 0;
+    #pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int best = best_s[m];
+                    if ((valid & (1u << m)) && best != a.blank) {
+                        if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
+                        ++n_emit[m];
+                        emit |= 1u << m;
+                    }
                 }
             }
             if (emit) pred_eval(emit);
@@ -968,16 +1128,22 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 if (valid & (1u << m)) a.n_tokens[utt0 + m] = n_emit[m];
         }
     }
+    // After a wait that ran out, stores of a peer may still be on their way to this CTA (nothing waited for them):
+    // give them time to land before anyone leaves.  The normal path has received everything that was sent to it.
+    if (dead || status_aborted(a.status, a.gen))
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
     cluster.sync();
 }
 
 using GreedyFn = void (*)(GreedyArgs);
 // rows per warp are compile-time (register arrays); pick the instantiation covering the run-time sizes
-static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab) {
+// xb: the st.async exchange is possible (every CTA owns the same, even number of units)
+static GreedyFn pick_greedy(int gate_rows, int joint_rows, int vocab, bool xb) {
     const int nrg = ceil_div(gate_rows, kGreedyWarps), nrj = ceil_div(joint_rows, kGreedyWarps),
               nrv = ceil_div(vocab, kGreedyWarps);
-    if (nrg <= 5 && nrj <= 2 && nrv <= 2) return rnnt_greedy_kernel<5, 2, 2>;
-    if (nrg <= kMaxRowsPerWarp && nrj <= 4 && nrv <= 4) return rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4>;
+    if (nrg <= 5 && nrj <= 2 && nrv <= 2) return xb ? rnnt_greedy_kernel<5, 2, 2, true> : rnnt_greedy_kernel<5, 2, 2, false>;
+    if (nrg <= kMaxRowsPerWarp && nrj <= 4 && nrv <= 4)
+        return xb ? rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4, true> : rnnt_greedy_kernel<kMaxRowsPerWarp, 4, 4, false>;
     return nullptr;
 }
 static size_t greedy_mma_smem(const pimb200_rnnt_config& c, int C) {
@@ -987,7 +1153,7 @@ static size_t greedy_mma_smem(const pimb200_rnnt_config& c, int C) {
     const int part_floats = 2 * M * RG > 4 * M * 32 ? 2 * M * RG : 4 * M * 32;
     return 3 * al((size_t)RG * PH * 2) + al((size_t)32 * JH * 2) + 2 * al((size_t)2 * M * (PH + 8) * 2) +
            al((size_t)M * JH * 2) + al((size_t)M * (JH + 8) * 2) + al((size_t)part_floats * 4) + al((size_t)M * 32 * 4) +
-           al(32 * 4) + al((size_t)RG * 4) + al((size_t)M * 4);
+           al(32 * 4) + al((size_t)RG * 4) + al((size_t)M * 4) + al(6 * 8);
 }
 static bool greedy_mma_fits(const pimb200_rnnt_config& c, int C, int max_smem) {
     const int PH = c.pred_hidden, JH = c.joint_hidden;
@@ -1038,6 +1204,9 @@ struct pimb200_rnnt {
     int resident_multi = 1;
     int smem_mask = 0;
     size_t smem_bytes = 0;
+    int* d_status = nullptr;        // status block of the greedy kernels' bounded waits: {sticky code, generation}
+    int gen = 0;                    // generation of the last greedy launch
+    int poll_limit = kGreedyPollLimit;
     std::mutex mu;
 };
 
@@ -1051,7 +1220,8 @@ static size_t greedy_smem(const pimb200_rnnt_config& c, int C, int mask, int mul
             al((size_t)multi * 4 * UP * 4) + al((size_t)multi * (V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4);
     else
         s = al((size_t)2 * PH * 2) * 2 + al((size_t)JH * 4) + al((size_t)JH * 2) + al((size_t)4 * UP * 4) +
-            al((size_t)(V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4) + al((size_t)V * 4 * UP * 4);
+            al((size_t)(V + 1) * 4) + al((size_t)V * 4) + al((size_t)4 * UP * 4) + al((size_t)V * 4 * UP * 4) +
+            al((size_t)UP * 2) + al(6 * 8);
     const size_t slice = al((size_t)4 * UP * PH * 2);
     if (mask & 1) s += slice;
     if (mask & 2) s += slice;
@@ -1067,7 +1237,7 @@ extern "C" int pimb200_rnnt_destroy(pimb200_rnnt* h) {
     pimb200_lstm_destroy(h->pre);
     pimb200_lstm_destroy(h->post);
     void* ptrs[] = {h->W1e, h->W1p, h->W2, h->b1, h->b2, h->Whh0, h->Wih1, h->Whh1, h->P0, h->bias1,
-                    h->y_pre, h->y_post, h->E};
+                    h->y_pre, h->y_post, h->E, h->d_status};
     for (void* p : ptrs) cudaFree(p);
     delete h;
     return PIMB200_OK;
@@ -1108,6 +1278,8 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
     RNNT_ALLOC(h->Whh1, (size_t)4 * PH * PH * 2);
     RNNT_ALLOC(h->P0, (size_t)V * 4 * PH * 4);
     RNNT_ALLOC(h->bias1, (size_t)4 * PH * 4);
+    RNNT_ALLOC(h->d_status, 8);
+    if (cudaMemset(h->d_status, 0, 8) != cudaSuccess) return fail(PIMB200_ERR_LAUNCH);
     __half* wih0_packed = nullptr;
     float* bias0 = nullptr;
     RNNT_ALLOC(wih0_packed, (size_t)4 * PH * PH * 2);
@@ -1143,7 +1315,7 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
     const int candidates[2] = {16, 8};
     for (int ci = 0; ci < 2 && h->cluster == 0; ++ci) {
         const int C = candidates[ci];
-        GreedyFn fn = pick_greedy(4 * ceil_div(PH, C), ceil_div(JH, C), V);
+        GreedyFn fn = pick_greedy(4 * ceil_div(PH, C), ceil_div(JH, C), V, PH % C == 0 && (PH / C) % 2 == 0);
         if (!fn || C * ceil_div(PH, C) > kGreedyThreads) continue;   // one gate thread per (unit, destination CTA)
         cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
@@ -1255,14 +1427,19 @@ extern "C" int pimb200_rnnt_last_status(pimb200_rnnt* h) {
     const int s_pre = pimb200_lstm_last_status(h->pre);
     const int s_post = pimb200_lstm_last_status(h->post);
     const int s_gemm = pimb200_gemm_last_status();
-    return s_pre != PIMB200_OK ? s_pre : (s_post != PIMB200_OK ? s_post : s_gemm);
+    int s_greedy = PIMB200_OK;   // after the calls above the device is idle
+    PIMB200_CUDA_TRY(cudaMemcpy(&s_greedy, h->d_status, 4, cudaMemcpyDeviceToHost));
+    if (s_greedy != PIMB200_OK) PIMB200_CUDA_TRY(cudaMemset(h->d_status, 0, 4));
+    return s_pre != PIMB200_OK ? s_pre : (s_post != PIMB200_OK ? s_post : (s_gemm != PIMB200_OK ? s_gemm : s_greedy));
 }
 
 // Test hook: the bounded waits of both encoder stacks (see pimb200_lstm_set_poll_limit).
 extern "C" int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit) {
     if (!h) return PIMB200_ERR_BAD_ARG;
     const int rc = pimb200_lstm_set_poll_limit(h->pre, limit);
-    return rc != PIMB200_OK ? rc : pimb200_lstm_set_poll_limit(h->post, limit);
+    if (rc != PIMB200_OK) return rc;
+    h->poll_limit = limit < kGreedyPollLimit ? limit : kGreedyPollLimit;
+    return pimb200_lstm_set_poll_limit(h->post, limit);
 }
 
 // A/B switch of both encoder stacks: layers in pairs as a wavefront for up to 8 utterances (see pimb200_lstm_set_wavefront).
@@ -1345,6 +1522,8 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     a.P0 = h->P0; a.Whh0 = h->Whh0; a.Wih1 = h->Wih1; a.Whh1 = h->Whh1; a.bias1 = h->bias1;
     a.W1p = h->W1p; a.W2 = h->W2; a.b2 = h->b2;
     a.trace = h->trace;
+    h->gen = h->gen == 0x7fffffff ? 1 : h->gen + 1;
+    a.status = h->d_status; a.gen = h->gen; a.poll_limit = h->poll_limit;
     a.PH = c.pred_hidden; a.JH = JH; a.V = c.vocab; a.blank = c.blank; a.smem_mask = h->smem_mask;
     const int C = h->cluster;
     // more utterances than clusters: several utterances per cluster in lock step
