@@ -39,6 +39,25 @@ __global__ void rnnt_add_bias_rows_kernel(float* __restrict__ P0, const float* _
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n * rows) P0[i] += bias[i % n];
 }
+// W1p[JH][PH] -> fragment order for clusters of C CTAs (JP = JH / C rows per CTA, PH / 64 k-tiles per K quarter): word
+// ((((cta * MTJ + mt) * 4 + kq) * NK + i) * 32 + lane) * 4 + r holds the two halves at row cta*JP + mt*16 + lane/4 +
+// (r & 1) * 8, columns (kq*NK + i)*16 + 2*(lane % 4) + (r >> 1) * 8 ...+1: register r of that lane's A operand.  A warp
+// then reads one k-tile of its operand as 512 contiguous bytes instead of 128 scattered words.
+__global__ void rnnt_pack_w1p_frags_kernel(const __half* __restrict__ W1p, uint32_t* __restrict__ out, int JH, int PH, int C) {
+    const int NK = PH / 64, JP = JH / C, MTJ = JP / 16;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)JH * PH / 2) return;
+    size_t w = idx;
+    const int r = (int)(w & 3); w >>= 2;
+    const int lane = (int)(w & 31); w >>= 5;
+    const int i = (int)(w % NK); w /= NK;
+    const int kq = (int)(w & 3); w >>= 2;
+    const int mt = (int)(w % MTJ); w /= MTJ;
+    const int cta = (int)w;
+    const int row = cta * JP + mt * 16 + (lane >> 2) + (r & 1) * 8;
+    const int col = (kq * NK + i) * 16 + 2 * (lane & 3) + (r >> 1) * 8;
+    out[idx] = *reinterpret_cast<const uint32_t*>(W1p + (size_t)row * PH + col);
+}
 __global__ void rnnt_widen_kernel(const __half* __restrict__ src, float* __restrict__ dst, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = __half2float(src[i]);
@@ -59,6 +78,8 @@ struct GreedyArgs {
     const float* bias1;    // [4PH]
     // joint
     const __half* W1p;     // [JH][PH]   prediction half of the first joint matrix
+    const uint4* W1pf;     // the same matrix in the order the tensor-core kernel's threads consume it (or NULL):
+                           // [CTA][m-tile][K quarter][k-tile][lane] x the four A registers of an m16n8k16 product
     const __half* W2;      // [V][JH]
     const float* b2;       // [V]
     int PH, JH, V, blank;
@@ -383,12 +404,12 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
                 if (tid + nthr < JH) zs[tid + nthr] = __float2half_rn(fmaxf(e_cur1 + Pj[tid + nthr], 0.f));
                 __syncthreads();
                 float zv[NRV];
-    #pragma unroll
+#pragma unroll
                 for (int i = 0; i < NRV; ++i) zv[i] = 0.f;
                 rows_dot<NRV>(W2, V, JH, zs, warp, lane, zv);
                 rows_reduce<NRV>(zv);
                 if (lane == 0) {
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < NRV; ++i) {
                         const int r = warp + kGreedyWarps * i;
                         if (r < V) lg[r] = zv[i] + b2s[r];
@@ -403,7 +424,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_kernel(GreedyAr
                     const float v = lg[r];
                     if (v > bv) { bv = v; best = r; }
                 }
-    #pragma unroll
+#pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
                     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
                     const int oi = __shfl_xor_sync(0xffffffffu, best, o);
@@ -746,39 +767,92 @@ __device__ __forceinline__ void stage_swizzled(__half* dst, const __half* src, i
 }
 // acc += A[mt*16 .. +16, kt0*16 .. (kt0+nkt)*16) . B, A swizzled in shared memory, B = hb[n][k] with row pitch `bp`
 // (splitting the k-tiles over independent accumulators was measured and does not shorten these short chains)
+// NKT > 0: the number of k-tiles is known at compile time (and so should K and bp be: the loop unrolls fully and the
+// addresses fold); NKT == 0: run-time count `nkt`.
+template <int NKT>
 __device__ __forceinline__ void mma_rows_smem(float* acc, const __half* A, int K, int mt, int kt0, int nkt,
                                               const __half* hb, int bp, int lane) {
     const int a_row = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
     const int a_col = (lane >> 4) * 8;
     const __half* brow = hb + (size_t)(lane >> 2) * bp + (lane & 3) * 2;
+    if constexpr (NKT > 0) {
+        const __half* arow = A + (size_t)a_row * K;
+        const int c0 = 2 * kt0 + (lane >> 4), r7 = a_row & 7;
+        brow += kt0 << 4;
+        // two chains of dependent tile products instead of one: odd k-tiles go to a second accumulator
+        float acc_odd[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < NKT; ++i) {
+            uint32_t af[4];
+            g_ldmatrix_x4(af, arow + (((c0 + 2 * i) ^ r7) << 3));
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + 16 * i);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 16 * i + 8);
+            g_mma_16816((i & 1) ? acc_odd : acc, af, b0, b1);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[q] += acc_odd[q];
+    } else {
 #pragma unroll 4
-    for (int kt = kt0; kt < kt0 + nkt; ++kt) {
-        const int k0 = kt << 4;
-        uint32_t af[4];
-        g_ldmatrix_x4(af, swz(A, a_row, k0 + a_col, K));
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
-        g_mma_16816(acc, af, b0, b1);
+        for (int kt = kt0; kt < kt0 + nkt; ++kt) {
+            const int k0 = kt << 4;
+            uint32_t af[4];
+            g_ldmatrix_x4(af, swz(A, a_row, k0 + a_col, K));
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
+            g_mma_16816(acc, af, b0, b1);
+        }
     }
 }
 // same with A read straight from global memory (row-major, pitch K) through L1
+template <int NKT>
 __device__ __forceinline__ void mma_rows_gmem(float* acc, const __half* A, int K, int mt, int kt0, int nkt,
                                               const __half* hb, int bp, int lane) {
     const int g = lane >> 2, t = lane & 3;
     const __half* a_lo = A + (size_t)(mt * 16 + g) * K + 2 * t;
     const __half* a_hi = a_lo + (size_t)8 * K;
     const __half* brow = hb + (size_t)g * bp + 2 * t;
+    if constexpr (NKT > 0) {
+        // every fragment of the product is requested before the first multiply: one trip to L1 / L2, not NKT of them
+        uint32_t af[NKT][4];
+        a_lo += kt0 << 4; a_hi += kt0 << 4; brow += kt0 << 4;
+#pragma unroll
+        for (int i = 0; i < NKT; ++i) {
+            af[i][0] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + 16 * i));
+            af[i][1] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + 16 * i));
+            af[i][2] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + 16 * i + 8));
+            af[i][3] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + 16 * i + 8));
+        }
+#pragma unroll
+        for (int i = 0; i < NKT; ++i) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + 16 * i);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 16 * i + 8);
+            g_mma_16816(acc, af[i], b0, b1);
+        }
+    } else {
 #pragma unroll 5
-    for (int kt = kt0; kt < kt0 + nkt; ++kt) {
-        const int k0 = kt << 4;
-        uint32_t af[4];
-        af[0] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0));
-        af[1] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0));
-        af[2] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0 + 8));
-        af[3] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0 + 8));
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
-        g_mma_16816(acc, af, b0, b1);
+        for (int kt = kt0; kt < kt0 + nkt; ++kt) {
+            const int k0 = kt << 4;
+            uint32_t af[4];
+            af[0] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0));
+            af[1] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0));
+            af[2] = __ldg(reinterpret_cast<const uint32_t*>(a_lo + k0 + 8));
+            af[3] = __ldg(reinterpret_cast<const uint32_t*>(a_hi + k0 + 8));
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + k0);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + k0 + 8);
+            g_mma_16816(acc, af, b0, b1);
+        }
+    }
+}
+// the same product with the A fragments already in registers
+template <int NKT>
+__device__ __forceinline__ void frags_mma(float* acc, const uint4* af, int kt0, const __half* hb, int bp, int lane) {
+    const __half* brow = hb + (size_t)(lane >> 2) * bp + (lane & 3) * 2 + (kt0 << 4);
+#pragma unroll
+    for (int i = 0; i < NKT; ++i) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(brow + 16 * i);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(brow + 16 * i + 8);
+        const uint32_t a4[4] = {af[i].x, af[i].y, af[i].z, af[i].w};
+        g_mma_16816(acc, a4, b0, b1);
     }
 }
 // accumulator tile -> part[split][n][row] (fp32): thread holds (row g, cols 2t,2t+1) and (row g+8, same cols)
@@ -790,6 +864,9 @@ __device__ __forceinline__ void store_acc(float* part, int ld, int mt, const flo
     part[(size_t)(2 * t + 1) * ld + mt * 16 + g + 8] = acc[3];
 }
 
+// PHC / JHC: pred_hidden and joint_hidden as compile-time constants (0 = taken from the arguments); with them every
+// product loop has a constant trip count and constant strides.
+template <int PHC, int JHC>
 __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(GreedyArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.num_blocks();
@@ -798,7 +875,13 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int nthr = kGreedyThreads;
     constexpr int M = kMmaUtts;
-    const int PH = a.PH, JH = a.JH, V = a.V;
+    const int PH = PHC > 0 ? PHC : a.PH, JH = JHC > 0 ? JHC : a.JH, V = a.V;
+    // constant trip counts of the product loops (0 = run time): half of K for the gate products, all of K for the
+    // state product under the exchange, a quarter of K for the joint half, a quarter of JH for the logits
+    constexpr int NK_HALF = (PHC > 0 && PHC % 32 == 0) ? PHC / 32 : 0;
+    constexpr int NK_FULL = NK_HALF > 0 ? PHC / 16 : 0;
+    constexpr int NK_PJ = (PHC > 0 && PHC % 64 == 0) ? PHC / 64 : 0;
+    constexpr int NK_LG = (JHC > 0 && JHC % 64 == 0) ? JHC / 64 : 0;
     const int UP = PH / C, u0 = rank * UP, RG = 4 * UP;      // gate rows of this CTA (multiple of 16)
     const int JP = JH / C, j0 = rank * JP;                  // joint rows of this CTA (multiple of 16)
     const int hp = PH + 8, zp = JH + 8;                      // pitches of the B-operand buffers
@@ -910,6 +993,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
         // column, the state that utterance will read: buffers are indexed [parity][n], and a column that sits the
         // evaluation out simply produces a value nobody stores.
         long long* trp = nullptr;
+        float acc_l0[4] = {0.f, 0.f, 0.f, 0.f};   // Whh0 . h0 of the coming evaluation (zero state at the start)
         // new state values of this CTA (stage[n][0..UP)) -> plane (par>>n)&1 of `buf` in every CTA, 8 bytes a store
         auto scatter_state = [&](__half* buf, unsigned mask, int x) {
             const uint32_t bar = xbar0 + 8u * (2 * x + (n_eval & 1u));
@@ -937,18 +1021,10 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             // input term of layer 0 for the symbol just emitted: fetched now, used after the first product
             float4 p0v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (mine) p0v = __ldg(reinterpret_cast<const float4*>(a.P0 + (size_t)best_s[gn] * 4 * PH + (size_t)(u0 + gj) * 4));
-            // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]) in two K halves; meanwhile role 2 computes Whh1 . h1prev
+            // ---- layer 0: z = Whh0 . h0prev (+ P0[tok]); the two K halves of the product were made by roles 0 and 1
+            //      during the previous evaluation (acc_l0), while its layer-1 state travelled
             float acc2[4] = {0.f, 0.f, 0.f, 0.f};
-            {
-                const int n = lane >> 2;
-                const unsigned pn = (par >> n) & 1u;   // column n reads the plane written by its previous evaluation
-                if (role < 2) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_rows_smem(acc, Whh0, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half,
-                                  h0buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
-                    store_acc(part + (size_t)role * M * gl, gl, mt_w, acc, lane);
-                }
-            }
+            if (role < 2) store_acc(part + (size_t)role * M * gl, gl, mt_w, acc_l0, lane);
             __syncthreads();
             if (trp && tid == 0) trp[4] = clock64();
             if (mine) {
@@ -961,28 +1037,24 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             }
             __syncthreads();
             scatter_state(h0buf, mask, 0);
-            // the state product of layer 1 does not depend on the exchange in flight: it runs while the values travel
-            if (role == 2) {
+            // the state product of layer 1 does not depend on the exchange in flight: roles 0 and 2 make its two K halves
+            // while the values travel, and continue the same sums with the input product afterwards
+            if (role == 0 || role == 2) {
                 const int n = lane >> 2;
-                const unsigned pn = (par >> n) & 1u;
-                mma_rows_smem(acc2, Whh1, PH, mt_w, 0, KTP, h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
+                const unsigned pn = (par >> n) & 1u;   // column n reads the plane written by its previous evaluation
+                mma_rows_smem<NK_HALF>(acc2, Whh1, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half,
+                                       h1buf + (size_t)((pn ^ 1u) * M) * hp, hp, lane);
             }
             xwait(0);
             if (trp && tid == 0) trp[5] = clock64();
-            // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias: role 0 takes the first K half, role 2 adds the
-            //      second half to the product it already holds
-            {
+            // ---- layer 1: z = Wih1 . h0new + Whh1 . h1prev + bias: role 0 adds the first K half of the input product to
+            //      the half it holds, role 2 the second
+            if (role == 0 || role == 2) {
                 const int n = lane >> 2;
                 const unsigned pn = (par >> n) & 1u;
                 const __half* hb = h0buf + (size_t)(pn * M) * hp;
-                if (role == 0) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_rows_smem(acc, Wih1, PH, mt_w, 0, k_half, hb, hp, lane);
-                    store_acc(part, gl, mt_w, acc, lane);
-                } else if (role == 2) {
-                    mma_rows_smem(acc2, Wih1, PH, mt_w, k_half, KTP - k_half, hb, hp, lane);
-                    store_acc(part + (size_t)M * gl, gl, mt_w, acc2, lane);
-                }
+                mma_rows_smem<NK_HALF>(acc2, Wih1, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half, hb, hp, lane);
+                store_acc(part + (size_t)(role ? M : 0) * gl, gl, mt_w, acc2, lane);
             }
             __syncthreads();
             if (mine) {
@@ -996,6 +1068,26 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
             }
             __syncthreads();
             scatter_state(h1buf, mask, 1);
+            // while the layer-1 state travels: the layer-0 state product of the NEXT evaluation.  It depends on no
+            // symbol, and column n will read the plane its latest evaluation wrote, which for the columns of this
+            // evaluation is the one received above.
+            if (role < 2) {
+                const int n = lane >> 2;
+                const unsigned pl = (((par ^ mask) >> n) & 1u) ^ 1u;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) acc_l0[q] = 0.f;
+                mma_rows_smem<NK_HALF>(acc_l0, Whh0, PH, mt_w, role ? k_half : 0, role ? KTP - k_half : k_half,
+                                       h0buf + (size_t)(pl * M) * hp, hp, lane);
+            }
+            // the weights of the joint half come from global memory (L1 / L2), in fragment order when the sizes are
+            // compiled in: one 16-byte load per k-tile and lane, asked for now and multiplied after the wait
+            uint4 wj[NK_PJ > 0 ? NK_PJ : 1];
+            const bool frag = NK_PJ > 0 && a.W1pf != nullptr;
+            if (frag && warp < 4 * MTJ) {
+                const uint4* fp = a.W1pf + ((((size_t)rank * MTJ + mtj_w) * 4 + kqj) * NK_PJ) * 32 + lane;
+#pragma unroll
+                for (int i = 0; i < NK_PJ; ++i) wj[i] = __ldg(fp + i * 32);
+            }
             xwait(1);
             if (trp && tid == 0) trp[6] = clock64();
             // ---- prediction half of the joint: Pj[n][j0 + q] = W1p[q,:] . h1new[n]; four K quarters per m-tile
@@ -1003,7 +1095,9 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 const int k_lo = kqj * perj, k_n = max(0, min(perj, KTP - k_lo));
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 const int n = lane >> 2;
-                mma_rows_gmem(acc, W1p, PH, mtj_w, k_lo, k_n, h1buf + (size_t)(((par >> n) & 1u) * M) * hp, hp, lane);
+                const __half* hb = h1buf + (size_t)(((par >> n) & 1u) * M) * hp;
+                if (frag) frags_mma<NK_PJ>(acc, wj, k_lo, hb, hp, lane);
+                else mma_rows_gmem<NK_PJ>(acc, W1p, PH, mtj_w, k_lo, k_n, hb, hp, lane);
                 store_acc(part + (size_t)kqj * M * jl, jl, mtj_w, acc, lane);
             }
             __syncthreads();
@@ -1087,7 +1181,7 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                     const int mt = warp & 1, kq = warp >> 1;
                     const int per = (KTJ + 3) / 4, k_lo = kq * per, k_n = max(0, min(per, KTJ - k_lo));
                     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_rows_smem(acc, W2s, JH, mt, k_lo, k_n, zs, zp, lane);
+                    mma_rows_smem<NK_LG>(acc, W2s, JH, mt, k_lo, k_n, zs, zp, lane);
                     store_acc(part + (size_t)kq * M * jl, jl, mt, acc, lane);
                 }
                 __syncthreads();
@@ -1108,15 +1202,23 @@ __global__ void __launch_bounds__(kGreedyThreads, 1) rnnt_greedy_mma_kernel(Gree
                 }
                 __syncthreads();
                 if (trp && tid == 0) trp[3] = clock64();
+                // every thread keeps the counts; the token of utterance m is written by lane m of the last warp, which
+                // has no part in the products that follow (one thread writing all eight held the whole cluster up)
+                // (all decisions are read before any token is written: a shared-memory load may not pass a global store
+                // that could alias it, and eight load -> compare -> store links in a row cost ~1 k cycles)
                 emit = 0;
-    #pragma unroll
+                int bests[M];
+                {
+                    const int4 b_lo = *reinterpret_cast<const int4*>(best_s), b_hi = *reinterpret_cast<const int4*>(best_s + 4);
+                    bests[0] = b_lo.x; bests[1] = b_lo.y; bests[2] = b_lo.z; bests[3] = b_lo.w;
+                    bests[4] = b_hi.x; bests[5] = b_hi.y; bests[6] = b_hi.z; bests[7] = b_hi.w;
+                }
+#pragma unroll
                 for (int m = 0; m < M; ++m) {
-                    const int best = best_s[m];
-                    if ((valid & (1u << m)) && best != a.blank) {
-                        if (rank == 0 && tid == 0) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = best;
-                        ++n_emit[m];
-                        emit |= 1u << m;
-                    }
+                    const bool em = ((valid >> m) & 1u) && bests[m] != a.blank;
+                    if (em && rank == 0 && tid == nthr - 32 + m) a.tokens[(size_t)(utt0 + m) * a.Tp + n_emit[m]] = bests[m];
+                    n_emit[m] += em ? 1 : 0;
+                    emit |= (em ? 1u : 0u) << m;
                 }
             }
             if (emit) pred_eval(emit);
@@ -1182,6 +1284,7 @@ struct pimb200_rnnt {
     pimb200_lstm* pre = nullptr;
     pimb200_lstm* post = nullptr;
     __half *W1e = nullptr, *W1p = nullptr, *W2 = nullptr, *b1 = nullptr;
+    uint4* W1pf = nullptr;          // W1p in the tensor-core kernel's fragment order, made once the cluster size is known
     float* b2 = nullptr;
     __half *Whh0 = nullptr, *Wih1 = nullptr, *Whh1 = nullptr;
     float *P0 = nullptr, *bias1 = nullptr;
@@ -1192,6 +1295,7 @@ struct pimb200_rnnt {
     long long* trace = nullptr;  // diagnostics buffer (not owned)
     GreedyFn fn = nullptr;
     bool mma_ok = false;           // tensor-core variant (kMmaUtts utterances per cluster) available
+    GreedyFn fn_mma = nullptr;     // its instantiation for this model's sizes
     size_t smem_bytes_mma = 0;
     GreedyFn fn_multi = nullptr;   // lock-step variant (kGreedyMulti utterances per cluster), when it fits
     int smem_mask_multi = 0;
@@ -1237,7 +1341,7 @@ extern "C" int pimb200_rnnt_destroy(pimb200_rnnt* h) {
     pimb200_lstm_destroy(h->pre);
     pimb200_lstm_destroy(h->post);
     void* ptrs[] = {h->W1e, h->W1p, h->W2, h->b1, h->b2, h->Whh0, h->Wih1, h->Whh1, h->P0, h->bias1,
-                    h->y_pre, h->y_post, h->E, h->d_status};
+                    h->y_pre, h->y_post, h->E, h->d_status, h->W1pf};
     for (void* p : ptrs) cudaFree(p);
     delete h;
     return PIMB200_OK;
@@ -1342,12 +1446,24 @@ extern "C" int pimb200_rnnt_create(const pimb200_rnnt_config* cfg, const pimb200
             h->smem_mask = mask;
             h->smem_bytes = smem;
             if (greedy_mma_fits(c, C, max_smem)) {
-                cudaFuncSetAttribute(rnnt_greedy_mma_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-                cudaFuncSetAttribute(rnnt_greedy_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                // the benchmark model's sizes are compiled in; any other model takes them from the arguments
+                GreedyFn fmma = (PH == 320 && JH == 512) ? rnnt_greedy_mma_kernel<320, 512> : rnnt_greedy_mma_kernel<0, 0>;
+                cudaFuncSetAttribute(fmma, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                cudaFuncSetAttribute(fmma, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
                 lc.dynamicSmemBytes = greedy_mma_smem(c, C);
                 int ncl = 0;
-                if (cudaOccupancyMaxActiveClusters(&ncl, rnnt_greedy_mma_kernel, &lc) == cudaSuccess && ncl >= 1) {
+                if (cudaOccupancyMaxActiveClusters(&ncl, fmma, &lc) == cudaSuccess && ncl >= 1) {
                     h->mma_ok = true;
+                    h->fn_mma = fmma;
+                    if (PH % 64 == 0 && cudaMalloc(&h->W1pf, (size_t)JH * PH * 2) == cudaSuccess) {
+                        const int words = JH * PH / 2;
+                        rnnt_pack_w1p_frags_kernel<<<ceil_div(words, 256), 256>>>(h->W1p, reinterpret_cast<uint32_t*>(h->W1pf),
+                                                                                  JH, PH, C);
+                        if (cudaDeviceSynchronize() != cudaSuccess) return fail(PIMB200_ERR_LAUNCH);
+                    } else {
+                        cudaGetLastError();
+                        h->W1pf = nullptr;   // the kernel then reads the row-major matrix
+                    }
                     h->resident_mma = ncl;
                     h->smem_bytes_mma = lc.dynamicSmemBytes;
                 } else {
@@ -1520,7 +1636,7 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     GreedyArgs a;
     a.E = h->E; a.tokens = tokens; a.n_tokens = n_tokens; a.logits = logits; a.n_utts = n_utts; a.Tp = Tp;
     a.P0 = h->P0; a.Whh0 = h->Whh0; a.Wih1 = h->Wih1; a.Whh1 = h->Whh1; a.bias1 = h->bias1;
-    a.W1p = h->W1p; a.W2 = h->W2; a.b2 = h->b2;
+    a.W1p = h->W1p; a.W1pf = h->W1pf; a.W2 = h->W2; a.b2 = h->b2;
     a.trace = h->trace;
     h->gen = h->gen == 0x7fffffff ? 1 : h->gen + 1;
     a.status = h->d_status; a.gen = h->gen; a.poll_limit = h->poll_limit;
@@ -1547,6 +1663,6 @@ extern "C" int pimb200_rnnt_decode(pimb200_rnnt* h, const void* feats, int T, in
     at[0].val.clusterDim.x = C; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, use_mma ? rnnt_greedy_mma_kernel : (multi ? h->fn_multi : h->fn), a));
+    PIMB200_CUDA_TRY(cudaLaunchKernelEx(&lc, use_mma ? h->fn_mma : (multi ? h->fn_multi : h->fn), a));
     return PIMB200_OK;
 }
