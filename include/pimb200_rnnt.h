@@ -73,12 +73,14 @@ int pimb200_rnnt_profile_enable(pimb200_rnnt* h, int enable);
 int pimb200_rnnt_profile_read(pimb200_rnnt* h, double* total_ms, long* recurrences, double* bytes);
 
 /* First non-zero status among the kernels a decode launched since the last call (PIMB200_ERR_TIMEOUT when a bounded
- * wait of a recurrence or of a tensor-core GEMM gave up: the outputs of that decode are then undefined); reading clears
- * it.  Synchronises the device.  A timed-out launch does not affect later launches. */
+ * wait of a recurrence, of a tensor-core GEMM or of an exchange inside the greedy kernel gave up: the outputs of that
+ * decode are then undefined); reading clears it.  Synchronises the device.  A timed-out launch does not affect later
+ * launches. */
 int pimb200_rnnt_last_status(pimb200_rnnt* h);
 
 /* ---- diagnostics and test hooks (no counterpart in the reference) ---- */
-/* Bounded waits of both encoder stacks, in polls (see pimb200_lstm_set_poll_limit): fault tests shrink it to 1. */
+/* Bounded waits of both encoder stacks and of the greedy kernel's exchange barriers, in polls (see
+ * pimb200_lstm_set_poll_limit): fault tests shrink it to 1. */
 int pimb200_rnnt_set_poll_limit(pimb200_rnnt* h, int limit);
 
 /* pimb200_lstm_set_wavefront for both encoder stacks (default on). */

@@ -84,8 +84,14 @@ class RnntDecoder:
         check(_lib.lib().pimb200_rnnt_set_wavefront(self._h, 1 if on else 0), "rnnt_set_wavefront")
 
     def set_poll_limit(self, limit: int) -> None:
-        """Test hook: iteration limit of the encoder recurrences' bounded waits."""
+        """Test hook: iteration limit of the bounded waits (encoder recurrences, greedy kernel's exchanges)."""
         check(_lib.lib().pimb200_rnnt_set_poll_limit(self._h, int(limit)), "rnnt_set_poll_limit")
+
+    def set_trace(self, buffer: Optional[torch.Tensor]) -> None:
+        """Diagnostics: int64 CUDA tensor of (T / stack_factor) * 8 elements that the greedy kernel fills with eight
+        clocks per frame of utterance 0 (``None`` switches it off).  The caller keeps the tensor alive."""
+        check(_lib.lib().pimb200_rnnt_set_trace(self._h, None if buffer is None else buffer.data_ptr()),
+              "rnnt_set_trace")
 
     def decode_into(self, feats: torch.Tensor, tokens: torch.Tensor, n_tokens: torch.Tensor,
                     logits: Optional[torch.Tensor] = None) -> None:
@@ -112,3 +118,40 @@ class RnntDecoder:
         tk = tokens.cpu()
         out = [tk[u, : n[u]].tolist() for u in range(n_utts)]
         return (out, logits) if want_logits else out
+
+
+GREEDY_TRACE_PHASES_SINGLE = ("z + logits", "arg max", "layer 0: reduce", "layer 0: gates + exchange",
+                              "layer 1: product + gates + exchange", "joint half: product",
+                              "joint half: exchange + next state products")
+GREEDY_TRACE_PHASES_GROUP = ("z", "logits product", "arg max", "layer 0: decisions + partial sums",
+                             "layer 0: gates + exchange", "layer 1: product + gates + exchange",
+                             "joint half: product + exchange")
+
+
+def greedy_frame_trace(n_utts: int, frames: int, seed: int = 0) -> dict:
+    """Mean SM cycles per phase of one greedy frame, from the kernel's own clocks (utterance 0, cluster 0, CTA 0).
+
+    Builds the benchmark model with synthetic weights (every frame emits a label: the worst case for the prediction
+    network), decodes ``n_utts`` utterances of ``frames`` feature frames once to warm up and once with the trace on.
+    One utterance runs the one-utterance kernel; more utterances than clusters run the 8-per-cluster kernel.
+    """
+    from . import synthetic as syn
+    cfg = syn.RnntConfig()
+    w = syn.make_rnnt_weights(cfg, seed=seed)
+    dev = lambda t: t.to(torch.float16).cuda().contiguous()
+    dec = RnntDecoder(cfg, [dev(p) for p in w.pre], [dev(p) for p in w.post], dev(w.embedding),
+                      [dev(p) for p in w.pred], dev(w.w1), dev(w.b1), dev(w.w2), dev(w.b2))
+    feats = torch.stack([dev(syn.make_features(frames, cfg, i)) for i in range(n_utts)])
+    dec.decode(feats)
+    Tp = frames // cfg.stack_factor
+    trace = torch.zeros(Tp * 8, dtype=torch.int64, device="cuda")
+    dec.set_trace(trace)
+    tokens = dec.decode(feats)
+    dec.set_trace(None)
+    t = trace.cpu().numpy().reshape(Tp, 8)[5:Tp - 5]
+    names = GREEDY_TRACE_PHASES_SINGLE if n_utts == 1 else GREEDY_TRACE_PHASES_GROUP
+    out = {name: float((t[:, i + 1] - t[:, i]).mean()) for i, name in enumerate(names)}
+    out["frame"] = float((t[1:, 0] - t[:-1, 0]).mean())
+    out["tokens of utterance 0"] = len(tokens[0])
+    dec.close()
+    return out

@@ -224,8 +224,9 @@ def test_rnnt_benchmark_configuration_vs_libtorch_full_length():
 
 
 def test_rnnt_timeout_is_reported_and_does_not_poison_later_decodes():
-    # Fault handling without faulting anything: the encoder recurrences' bounded waits are shrunk to one poll, so the
-    # first decode gives up; decode() must raise ERR_TIMEOUT.  A second timed-out decode is then issued through the
+    # Fault handling without faulting anything: the bounded waits of the encoder recurrences and of the greedy kernel's
+    # exchange barriers are shrunk to one poll, so the first decode gives up (a CTA of the greedy kernel that gave up stops
+    # sending and still joins the final cluster barrier); decode() must raise ERR_TIMEOUT.  A second timed-out decode is then issued through the
     # asynchronous entry point and nobody reads the status; the decode behind it (normal limit) must still be correct,
     # and the time-out must still be on record afterwards.
     from pimaicompiler_b200 import _lib
